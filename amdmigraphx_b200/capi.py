@@ -1,0 +1,258 @@
+"""ctypes binding of lib/libmgx_cuda_kernels.so (the C ABI of include/mgx_cuda.h).
+
+Used by the tests and the benchmark to drive the kernels with torch tensors as
+device buffers; the MIGraphX plug-in (libmigraphx_cuda.so) calls the same entry
+points from C++.  There is no fallback: if the library is missing, loading raises.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+KERNEL_LIB_PATH = os.path.join(_PKG, "lib", "libmgx_cuda_kernels.so")
+
+# mgx_dtype
+F32, F16, I8, U8, I32, FP8_E4M3FN = 0, 1, 2, 3, 4, 5
+# mgx_scale_mode
+SCALE_NONE, SCALE_PER_TENSOR, SCALE_PER_COL, SCALE_PER_ROW = 0, 1, 2, 3
+# mgx_act
+ACT_NONE, ACT_RELU, ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU = 0, 1, 2, 3, 4
+ACT_BY_NAME = {None: 0, "none": 0, "relu": 1, "gelu_erf": 2, "gelu_tanh": 3, "silu": 4}
+# mgx_b_layout
+B_KN, B_NK = 0, 1
+
+E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3, -4, -5
+
+EXPORTED_SYMBOLS = [
+    "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
+    "mgx_cuda_pack_int4", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm",
+    "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
+    "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
+    "mgx_cuda_status_string", "mgx_cuda_version",
+]
+
+
+class QgemmDesc(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
+                ("batch", ctypes.c_int64),
+                ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldd", ctypes.c_int64),
+                ("stride_a", ctypes.c_int64), ("stride_b", ctypes.c_int64),
+                ("stride_d", ctypes.c_int64),
+                ("ab_type", ctypes.c_int32), ("out_type", ctypes.c_int32),
+                ("b_layout", ctypes.c_int32), ("scale_mode", ctypes.c_int32),
+                ("act", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class W4Desc(ctypes.Structure):
+    _fields_ = [("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
+                ("lda", ctypes.c_int64), ("ldd", ctypes.c_int64),
+                ("group", ctypes.c_int32), ("zp_const", ctypes.c_int32),
+                ("act", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class MgxError(RuntimeError):
+    def __init__(self, code, what):
+        super().__init__(f"{what}: status {code} ({status_string(code)})")
+        self.code = code
+
+
+_lib = None
+
+
+def load():
+    """Load the kernel library (once).  Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(KERNEL_LIB_PATH):
+        raise RuntimeError(
+            f"{KERNEL_LIB_PATH} is missing: build it with `python -m amdmigraphx_b200.build` "
+            "(there is no CPU fallback)")
+    lib = ctypes.CDLL(KERNEL_LIB_PATH)
+    vp, i64, i32, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t
+    p64 = ctypes.POINTER(ctypes.c_int64)
+    lib.mgx_cuda_quantizelinear.argtypes = [vp, i32, i64, vp, p64, vp, p64, vp, i32, i64, i64, i64, vp]
+    lib.mgx_cuda_dequantizelinear.argtypes = [vp, i32, i64, vp, i32, p64, vp, p64, vp, i64, i64, i64, vp]
+    lib.mgx_cuda_unpack_int4.argtypes = [vp, vp, i32, i64, i64, vp]
+    lib.mgx_cuda_pack_int4.argtypes = [vp, vp, i32, i64, i64, vp]
+    lib.mgx_cuda_qgemm_workspace.argtypes = [ctypes.POINTER(QgemmDesc)]
+    lib.mgx_cuda_qgemm_workspace.restype = sz
+    lib.mgx_cuda_qgemm.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mgx_cuda_transpose_8bit.argtypes = [vp, vp, i64, i64, i64, vp]
+    lib.mgx_cuda_w4a16_workspace.argtypes = [ctypes.POINTER(W4Desc)]
+    lib.mgx_cuda_w4a16_workspace.restype = sz
+    for name in ("mgx_cuda_w4a16_gemv", "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16"):
+        getattr(lib, name).argtypes = [ctypes.POINTER(W4Desc), vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mgx_cuda_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+    lib.mgx_cuda_status_string.argtypes = [i32]
+    lib.mgx_cuda_status_string.restype = ctypes.c_char_p
+    lib.mgx_cuda_version.restype = ctypes.c_char_p
+    _lib = lib
+    return lib
+
+
+def status_string(code):
+    return load().mgx_cuda_status_string(int(code)).decode()
+
+
+def check(code, what):
+    if code != 0:
+        raise MgxError(code, what)
+
+
+def device_status():
+    """Synchronise the device, return and clear the kernels' status word."""
+    s = ctypes.c_int(0)
+    check(load().mgx_cuda_device_status(ctypes.byref(s)), "mgx_cuda_device_status")
+    return s.value
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dtype_code(t):
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.int8: I8, torch.uint8: U8,
+            torch.int32: I32, torch.float8_e4m3fn: FP8_E4M3FN}[t.dtype]
+
+
+def _strides2(view, rows, cols):
+    """Strides (elements) of a tensor broadcastable to [rows, cols], as MIGraphX
+    would pass it: 0 along broadcast dimensions."""
+    if view.dim() == 0 or view.numel() == 1:
+        return (ctypes.c_int64 * 2)(0, 0)
+    if view.dim() == 1:
+        if view.shape[0] == cols:
+            return (ctypes.c_int64 * 2)(0, view.stride(0))
+        raise ValueError("1-D scale must have `cols` elements")
+    s0 = 0 if view.shape[0] == 1 else view.stride(0)
+    s1 = 0 if view.shape[1] == 1 else view.stride(1)
+    return (ctypes.c_int64 * 2)(s0, s1)
+
+
+# ------------------------------------------------------------------ wrappers
+def quantizelinear(x, scale, zp=None, out_dtype=None):
+    """x [rows, cols] fp32/fp16 (row stride allowed); scale / zp broadcastable."""
+    import torch
+    lib = load()
+    rows, cols = x.shape
+    if out_dtype is None:
+        out_dtype = zp.dtype if zp is not None else torch.uint8
+    y = torch.empty((rows, cols), dtype=out_dtype, device=x.device)
+    code = lib.mgx_cuda_quantizelinear(
+        _ptr(x), _dtype_code(x), x.stride(0) if rows > 1 else cols, _ptr(scale),
+        _strides2(scale, rows, cols), _ptr(zp),
+        _strides2(zp, rows, cols) if zp is not None else None, _ptr(y), _dtype_code(y), cols,
+        rows, cols, _stream())
+    check(code, "mgx_cuda_quantizelinear")
+    return y
+
+
+def dequantizelinear(x, scale, zp=None):
+    import torch
+    lib = load()
+    rows, cols = x.shape
+    y = torch.empty((rows, cols), dtype=scale.dtype, device=x.device)
+    code = lib.mgx_cuda_dequantizelinear(
+        _ptr(x), _dtype_code(x), x.stride(0) if rows > 1 else cols, _ptr(scale),
+        _dtype_code(scale), _strides2(scale, rows, cols), _ptr(zp),
+        _strides2(zp, rows, cols) if zp is not None else None, _ptr(y), cols, rows, cols,
+        _stream())
+    check(code, "mgx_cuda_dequantizelinear")
+    return y
+
+
+def unpack_int4(packed):
+    import torch
+    rows, pc = packed.shape
+    out = torch.empty((rows, pc * 2), dtype=packed.dtype, device=packed.device)
+    check(load().mgx_cuda_unpack_int4(_ptr(packed), _ptr(out), _dtype_code(packed), rows, pc,
+                                      _stream()), "mgx_cuda_unpack_int4")
+    return out
+
+
+def pack_int4(x):
+    import torch
+    rows, c = x.shape
+    out = torch.empty((rows, c // 2), dtype=x.dtype, device=x.device)
+    check(load().mgx_cuda_pack_int4(_ptr(x), _ptr(out), _dtype_code(x), rows, c // 2, _stream()),
+          "mgx_cuda_pack_int4")
+    return out
+
+
+def transpose_8bit(src):
+    """[batch, rows, cols] or [rows, cols] bytes -> transposed, dense."""
+    import torch
+    s3 = src if src.dim() == 3 else src.unsqueeze(0)
+    b, r, c = s3.shape
+    dst = torch.empty((b, c, r), dtype=src.dtype, device=src.device)
+    check(load().mgx_cuda_transpose_8bit(_ptr(s3), _ptr(dst), r, c, b, _stream()),
+          "mgx_cuda_transpose_8bit")
+    return dst if src.dim() == 3 else dst[0]
+
+
+def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=None,
+          residual=None, out_dtype=None, out=None, workspace=None):
+    """quant_dot with the fused epilogue.  a: [M,K] or [B,M,K] int8 / float8_e4m3fn;
+    b: [K,N] (B_KN) or [N,K] (B_NK), optionally batched."""
+    import torch
+    lib = load()
+    a3 = a if a.dim() == 3 else a.unsqueeze(0)
+    b3 = b if b.dim() == 3 else b.unsqueeze(0)
+    batch, M, K = a3.shape
+    N = b3.shape[2] if b_layout == B_KN else b3.shape[1]
+    is_int = a.dtype == torch.int8
+    if out_dtype is None:
+        out_dtype = torch.int32 if (is_int and scale is None and bias is None and act is None) \
+            else torch.float32
+    d = out if out is not None else torch.empty((batch, M, N), dtype=out_dtype, device=a.device)
+    d3 = d if d.dim() == 3 else d.unsqueeze(0)
+    if scale_mode is None:
+        if scale is None:
+            scale_mode = SCALE_NONE
+        elif scale.numel() == 1:
+            scale_mode = SCALE_PER_TENSOR
+        elif scale.numel() == N:
+            scale_mode = SCALE_PER_COL
+        else:
+            scale_mode = SCALE_PER_ROW
+    desc = QgemmDesc(M=M, N=N, K=K, batch=batch, lda=a3.stride(1), ldb=b3.stride(1),
+                     ldd=d3.stride(1), stride_a=a3.stride(0), stride_b=b3.stride(0),
+                     stride_d=d3.stride(0), ab_type=_dtype_code(a), out_type=_dtype_code(d),
+                     b_layout=b_layout, scale_mode=scale_mode, act=ACT_BY_NAME[act], reserved=0)
+    need = lib.mgx_cuda_qgemm_workspace(ctypes.byref(desc))
+    if need and workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    code = lib.mgx_cuda_qgemm(ctypes.byref(desc), _ptr(a3), _ptr(b3), _ptr(d3), _ptr(scale),
+                              _ptr(bias), _ptr(residual), _ptr(workspace),
+                              0 if workspace is None else workspace.numel(), _stream())
+    check(code, "mgx_cuda_qgemm")
+    if out is not None:
+        return out
+    return d if a.dim() == 3 else d[0]
+
+
+def w4a16(a, bp, scales, zp=None, *, zp_const=8, group=128, act=None, which="auto",
+          workspace=None):
+    """a [M,K] fp16, bp [N,K/2] uint8, scales [N,K/group] fp16 -> [M,N] fp16."""
+    import torch
+    lib = load()
+    M, K = a.shape
+    N = bp.shape[0]
+    d = torch.empty((M, N), dtype=torch.float16, device=a.device)
+    desc = W4Desc(M=M, N=N, K=K, lda=a.stride(0), ldd=N, group=group, zp_const=zp_const,
+                  act=ACT_BY_NAME[act], reserved=0)
+    need = lib.mgx_cuda_w4a16_workspace(ctypes.byref(desc))
+    if need and workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    fn = {"auto": lib.mgx_cuda_w4a16, "gemv": lib.mgx_cuda_w4a16_gemv,
+          "gemm": lib.mgx_cuda_w4a16_gemm}[which]
+    code = fn(ctypes.byref(desc), _ptr(a), _ptr(bp), _ptr(scales), _ptr(zp), _ptr(d),
+              _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream())
+    check(code, f"mgx_cuda_w4a16[{which}]")
+    return d

@@ -1,0 +1,581 @@
+// quant_dot for sm_100a: int8 x int8 -> int32 and fp8(e4m3fn) x fp8 -> fp32 as a
+// persistent, warp-specialised, TMA-fed tcgen05 GEMM with the accumulator in
+// tensor memory and dequantizelinear / bias / activation / residual fused into
+// the epilogue.
+//
+// Arithmetic contract (MIGraphX `ref` target): src/targets/ref/lowering.cpp:205-249
+// -> gemm_naive (src/gemm.cpp:43-63): int8 products summed exactly, stored as
+// int32; fp8 products summed in (at least) fp32, stored as fp32.  The fused
+// epilogue reproduces dequantizelinear (src/include/migraphx/op/dequantizelinear.hpp:74-77:
+// double(x) * scale, one rounding to fp32), then add, then the activation, each
+// as a separate fp32 operation like the un-fused instructions.
+//
+// CTA = 192 threads: warp 0 = TMA producer (one lane), warp 1 = tensor-memory
+// owner + MMA issuer (one lane), warps 2..5 = epilogue (each owns the TMEM lane
+// quarter warp_id % 4).  Two accumulator buffers of BN columns let the epilogue
+// of tile i overlap the main loop of tile i+1.
+#include "common.cuh"
+#include "ptx.cuh"
+#include <cuda_fp16.h>
+
+namespace mgx {
+
+constexpr int BM        = 128; // rows of D per tile (UMMA M, one TMEM lane per row)
+constexpr int BK        = 128; // bytes (= 8-bit elements) of K per pipeline stage
+constexpr int UMMA_K    = 32;  // K per tcgen05.mma for 8-bit operands
+constexpr int NTHREADS  = 192;
+constexpr int EPI_WARP0 = 2;
+
+struct qgemm_params
+{
+    int64_t M, N, K, batch;
+    int64_t ldd, stride_d;
+    void* D;
+    const float* scale;
+    const float* bias;
+    const void* residual;
+    int tiles_m, tiles_n;
+    int64_t num_tiles;
+    int num_kb;
+    int scale_mode;
+    int act;
+};
+
+template <int BN>
+struct qgemm_smem
+{
+    static constexpr int a_bytes     = BM * BK;
+    static constexpr int b_bytes     = BN * BK;
+    static constexpr int stage_bytes = a_bytes + b_bytes;
+    static constexpr int stages      = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr int bar_bytes   = 256;
+    static constexpr int total       = stages * stage_bytes + bar_bytes + 1024; // + alignment slack
+};
+
+__device__ __forceinline__ float apply_act(float v, int act)
+{
+    switch(act)
+    {
+    case MGX_ACT_RELU: return fmaxf(v, 0.0f);
+    case MGX_ACT_GELU_ERF:
+        // (x*0.5) * (erf(x / sqrt(2)) + 1): operation order of src/op/builder/gelu.cpp:58-74
+        return __fmul_rn(__fmul_rn(v, 0.5f), __fadd_rn(erff(__fdiv_rn(v, 1.41421356237309504880f)), 1.0f));
+    case MGX_ACT_GELU_TANH: {
+        float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+        return 0.5f * v * (1.0f + tanhf(u));
+    }
+    case MGX_ACT_SILU: return v / (1.0f + expf(-v));
+    default: return v;
+    }
+}
+
+template <class T>
+__device__ __forceinline__ float load_as_float(const void* p, int64_t i);
+template <>
+__device__ __forceinline__ float load_as_float<float>(const void* p, int64_t i)
+{
+    return static_cast<const float*>(p)[i];
+}
+template <>
+__device__ __forceinline__ float load_as_float<__half>(const void* p, int64_t i)
+{
+    return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+// IS_INT: accumulator registers hold int32 (kind::i8) else fp32 bit patterns.
+// OutT: int32_t (raw accumulator), float or __half.
+template <int BN, bool IS_INT, class OutT>
+__global__ void __launch_bounds__(NTHREADS, 1)
+    qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b,
+                 const qgemm_params p)
+{
+    using S = qgemm_smem<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    uint8_t* smem           = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+    uint8_t* bar_base     = smem + S::stages * S::stage_bytes;
+    uint64_t* full_bar    = reinterpret_cast<uint64_t*>(bar_base);
+    uint64_t* empty_bar   = full_bar + S::stages;
+    uint64_t* accf_bar    = empty_bar + S::stages; // [2] accumulator ready
+    uint64_t* acce_bar    = accf_bar + 2;          // [2] accumulator drained
+    uint32_t* tmem_slot   = reinterpret_cast<uint32_t*>(acce_bar + 2);
+    volatile uint32_t* abort_flag = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    constexpr uint32_t TMEM_COLS = 2 * BN; // 128, 256 or 512: a power of two >= 32
+
+    if(threadIdx.x == 0)
+    {
+        for(int s = 0; s < S::stages; ++s)
+        {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for(int b = 0; b < 2; ++b)
+        {
+            mbar_init(&accf_bar[b], 1);
+            mbar_init(&acce_bar[b], 4); // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if(warp == 1)
+    {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t first_tile = blockIdx.x;
+    const int64_t tile_step  = gridDim.x;
+    const int64_t tiles_mn   = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+
+    if(warp == 0)
+    {
+        // ---------------------------------------------------- TMA producer
+        if(lane == 0)
+        {
+            uint32_t it = 0;
+            bool ok     = true;
+            for(int64_t t = first_tile; ok and t < p.num_tiles; t += tile_step)
+            {
+                const int b     = static_cast<int>(t / tiles_mn);
+                const int r     = static_cast<int>(t % tiles_mn);
+                const int m_blk = r % p.tiles_m;
+                const int n_blk = r / p.tiles_m;
+                for(int kb = 0; kb < p.num_kb; ++kb, ++it)
+                {
+                    const uint32_t s  = it % S::stages;
+                    const uint32_t ph = (it / S::stages) & 1u;
+                    if(not mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, 2))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + s * S::stage_bytes;
+                    uint8_t* sb = sa + S::a_bytes;
+                    mbar_expect_tx(&full_bar[s], S::stage_bytes);
+                    tma_load_3d(sa, &tmap_a, &full_bar[s], kb * BK, m_blk * BM, b);
+                    tma_load_3d(sb, &tmap_b, &full_bar[s], kb * BK, n_blk * BN, b);
+                }
+            }
+        }
+    }
+    else if(warp == 1)
+    {
+        // ---------------------------------------------------- MMA issuer
+        if(lane == 0)
+        {
+            constexpr uint32_t idesc = IS_INT ? make_idesc(2u, 1u, 1u, BM, BN)  // s32 += s8*s8
+                                              : make_idesc(1u, 0u, 0u, BM, BN); // f32 += e4m3*e4m3
+            uint32_t it  = 0;
+            uint32_t lt  = 0; // local tile counter
+            bool ok      = true;
+            for(int64_t t = first_tile; ok and t < p.num_tiles; t += tile_step, ++lt)
+            {
+                const uint32_t buf = lt & 1u;
+                if(not mbar_wait_bounded(&acce_bar[buf], ((lt >> 1) & 1u) ^ 1u, abort_flag, 4))
+                    break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for(int kb = 0; kb < p.num_kb; ++kb, ++it)
+                {
+                    const uint32_t s  = it % S::stages;
+                    const uint32_t ph = (it / S::stages) & 1u;
+                    if(not mbar_wait_bounded(&full_bar[s], ph, abort_flag, 1))
+                    {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa    = smem_u32(smem + s * S::stage_bytes);
+                    const uint64_t adesc = make_smem_desc_sw128(sa);
+                    const uint64_t bdesc = make_smem_desc_sw128(sa + S::a_bytes);
+#pragma unroll
+                    for(int k = 0; k < BK / UMMA_K; ++k)
+                    {
+                        // advancing K inside the 128-byte swizzle row: +32 B on the start address
+                        const uint64_t koff = static_cast<uint64_t>((k * UMMA_K) >> 4);
+                        if constexpr(IS_INT)
+                            mma_i8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0);
+                        else
+                            mma_f8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0);
+                    }
+                    tc_commit(&empty_bar[s]); // stage reusable once these MMAs have read it
+                }
+                if(ok)
+                    tc_commit(&accf_bar[buf]); // accumulator complete
+            }
+        }
+    }
+    else
+    {
+        // ---------------------------------------------------- epilogue
+        const int quarter     = warp & 3; // TMEM lane quarter this warp may read
+        const int row_in_tile = quarter * 32 + lane;
+        uint32_t lt           = 0;
+        for(int64_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt)
+        {
+            const int b     = static_cast<int>(t / tiles_mn);
+            const int r     = static_cast<int>(t % tiles_mn);
+            const int m_blk = r % p.tiles_m;
+            const int n_blk = r / p.tiles_m;
+            const uint32_t buf = lt & 1u;
+            if(not mbar_wait_bounded(&accf_bar[buf], (lt >> 1) & 1u, abort_flag, 3))
+                break;
+            tc_fence_after_sync();
+
+            const int64_t row  = static_cast<int64_t>(m_blk) * BM + row_in_tile;
+            const int64_t col0 = static_cast<int64_t>(n_blk) * BN;
+            const bool row_ok  = row < p.M;
+            OutT* drow = static_cast<OutT*>(p.D) + b * p.stride_d + row * p.ldd;
+            const OutT* rrow =
+                p.residual == nullptr
+                    ? nullptr
+                    : static_cast<const OutT*>(p.residual) + b * p.stride_d + row * p.ldd;
+            double row_scale = 1.0;
+            if(p.scale_mode == MGX_SCALE_PER_TENSOR)
+                row_scale = static_cast<double>(__ldg(p.scale));
+            else if(p.scale_mode == MGX_SCALE_PER_ROW and row_ok)
+                row_scale = static_cast<double>(__ldg(p.scale + row));
+            const bool vec_ok = (p.ldd % (16 / sizeof(OutT)) == 0) and
+                                ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) and
+                                (p.stride_d % (16 / sizeof(OutT)) == 0);
+
+#pragma unroll 1
+            for(int c = 0; c < BN; c += 32)
+            {
+                uint32_t acc[32];
+                __syncwarp(); // tcgen05.ld is warp-collective: re-converge after the guarded stores
+                const uint32_t taddr =
+                    tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + c;
+                tmem_ld_32x32b_x32(taddr, acc);
+                tmem_ld_wait();
+                const int64_t col = col0 + c;
+                if(not row_ok or col >= p.N)
+                    continue;
+                if constexpr(sizeof(OutT) == 4 and IS_INT and std::is_same<OutT, int32_t>::value)
+                {
+                    if(vec_ok and col + 32 <= p.N)
+                    {
+#pragma unroll
+                        for(int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<uint4*>(drow + col + j) =
+                                make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                    }
+                    else
+                    {
+                        for(int j = 0; j < 32 and col + j < p.N; ++j)
+                            drow[col + j] = static_cast<int32_t>(acc[j]);
+                    }
+                }
+                else
+                {
+                    float v[32];
+#pragma unroll
+                    for(int j = 0; j < 32; ++j)
+                    {
+                        const int64_t n = col + j;
+                        const bool n_ok = n < p.N;
+                        float x;
+                        if constexpr(IS_INT)
+                        {
+                            const int32_t a = static_cast<int32_t>(acc[j]);
+                            if(p.scale_mode == MGX_SCALE_NONE)
+                                x = static_cast<float>(a);
+                            else
+                            {
+                                const double s = p.scale_mode == MGX_SCALE_PER_COL
+                                                     ? (n_ok ? static_cast<double>(__ldg(p.scale + n)) : 0.0)
+                                                     : row_scale;
+                                x = static_cast<float>(static_cast<double>(a) * s);
+                            }
+                        }
+                        else
+                        {
+                            const float a = __uint_as_float(acc[j]);
+                            if(p.scale_mode == MGX_SCALE_NONE)
+                                x = a;
+                            else
+                            {
+                                const double s = p.scale_mode == MGX_SCALE_PER_COL
+                                                     ? (n_ok ? static_cast<double>(__ldg(p.scale + n)) : 0.0)
+                                                     : row_scale;
+                                x = static_cast<float>(static_cast<double>(a) * s);
+                            }
+                        }
+                        if(p.bias != nullptr and n_ok)
+                            x = __fadd_rn(x, __ldg(p.bias + n));
+                        x = apply_act(x, p.act);
+                        v[j] = x;
+                    }
+                    if(vec_ok and col + 32 <= p.N)
+                    {
+                        if constexpr(std::is_same<OutT, float>::value)
+                        {
+#pragma unroll
+                            for(int j = 0; j < 32; j += 4)
+                            {
+                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                if(rrow != nullptr)
+                                {
+                                    const float4 q = *reinterpret_cast<const float4*>(rrow + col + j);
+                                    o.x = __fadd_rn(o.x, q.x);
+                                    o.y = __fadd_rn(o.y, q.y);
+                                    o.z = __fadd_rn(o.z, q.z);
+                                    o.w = __fadd_rn(o.w, q.w);
+                                }
+                                *reinterpret_cast<float4*>(drow + col + j) = o;
+                            }
+                        }
+                        else if constexpr(std::is_same<OutT, __half>::value)
+                        {
+#pragma unroll
+                            for(int j = 0; j < 32; j += 8)
+                            {
+                                if(rrow != nullptr)
+                                {
+                                    const uint4 q = *reinterpret_cast<const uint4*>(rrow + col + j);
+                                    const __half* qh = reinterpret_cast<const __half*>(&q);
+#pragma unroll
+                                    for(int e = 0; e < 8; ++e)
+                                        v[j + e] = __fadd_rn(v[j + e], __half2float(qh[e]));
+                                }
+                                uint4 o;
+                                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                                for(int e = 0; e < 4; ++e)
+                                    oh[e] = __floats2half2_rn(v[j + 2 * e], v[j + 2 * e + 1]);
+                                *reinterpret_cast<uint4*>(drow + col + j) = o;
+                            }
+                        }
+                    }
+                    else
+                    {
+                        for(int j = 0; j < 32 and col + j < p.N; ++j)
+                        {
+                            float x = v[j];
+                            if constexpr(not std::is_same<OutT, int32_t>::value)
+                            {
+                                if(rrow != nullptr)
+                                    x = __fadd_rn(x, load_as_float<OutT>(rrow, col + j));
+                                if constexpr(std::is_same<OutT, float>::value)
+                                    drow[col + j] = x;
+                                else
+                                    drow[col + j] = __float2half_rn(x);
+                            }
+                        }
+                    }
+                }
+            }
+            // all TMEM reads of this buffer are complete (wait::ld above)
+            tc_fence_before_sync();
+            __syncwarp();
+            if(lane == 0)
+                mbar_arrive(&acce_bar[buf]);
+        }
+    }
+
+    // ---------------------------------------------------------- teardown
+    if(*abort_flag != 0)
+    {
+        // give copies that may still be in flight time to land before the CTA's
+        // shared memory is released
+        for(int i = 0; i < 1000; ++i)
+            __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if(warp == 1)
+    {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ------------------------------------------------------------------ host
+static int encode_operand_map(CUtensorMap* map, const void* base, int64_t k, int64_t rows,
+                              int64_t batch, int64_t ld, int64_t batch_stride, int box_rows)
+{
+    cuTensorMapEncodeTiled_t encode = get_tensor_map_encoder();
+    if(encode == nullptr)
+        return MGX_E_DRIVER;
+    cuuint64_t dims[3]    = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows),
+                             static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld),
+                             static_cast<cuuint64_t>(batch > 1 ? batch_stride : ld * rows)};
+    cuuint32_t box[3]     = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows), 1u};
+    cuuint32_t estr[3]    = {1u, 1u, 1u};
+    CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MGX_OK : MGX_E_INVALID_ARG;
+}
+
+template <int BN, bool IS_INT, class OutT>
+static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, void* D,
+                        const float* scale, const float* bias, const void* residual,
+                        int64_t ldb, int64_t stride_b, cudaStream_t stream)
+{
+    using S = qgemm_smem<BN>;
+    CUtensorMap ta, tb;
+    int rc = encode_operand_map(&ta, A, d.K, d.M, d.batch, d.lda, d.stride_a, BM);
+    if(rc != MGX_OK)
+        return rc;
+    rc = encode_operand_map(&tb, B, d.K, d.N, d.batch, ldb, stride_b, BN);
+    if(rc != MGX_OK)
+        return rc;
+    qgemm_params p{};
+    p.M          = d.M;
+    p.N          = d.N;
+    p.K          = d.K;
+    p.batch      = d.batch;
+    p.ldd        = d.ldd;
+    p.stride_d   = d.stride_d;
+    p.D          = D;
+    p.scale      = scale;
+    p.bias       = bias;
+    p.residual   = residual;
+    p.tiles_m    = static_cast<int>((d.M + BM - 1) / BM);
+    p.tiles_n    = static_cast<int>((d.N + BN - 1) / BN);
+    p.num_tiles  = static_cast<int64_t>(p.tiles_m) * p.tiles_n * d.batch;
+    p.num_kb     = static_cast<int>((d.K + BK - 1) / BK);
+    p.scale_mode = d.scale_mode;
+    p.act        = d.act;
+    auto kernel  = qgemm_kernel<BN, IS_INT, OutT>;
+    int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(kernel), S::total);
+    if(rc2 != MGX_OK)
+        return rc2;
+    const int sms = device_sm_count();
+    const int grid = static_cast<int>(p.num_tiles < sms ? p.num_tiles : sms);
+    kernel<<<grid, NTHREADS, S::total, stream>>>(ta, tb, p);
+    return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN, bool IS_INT>
+static int dispatch_out(const mgx_qgemm_desc& d, const void* A, const void* B, void* D,
+                        const float* scale, const float* bias, const void* residual, int64_t ldb,
+                        int64_t stride_b, cudaStream_t stream)
+{
+    switch(d.out_type)
+    {
+    case MGX_I32:
+        if constexpr(IS_INT)
+            return launch_qgemm<BN, true, int32_t>(d, A, B, D, scale, bias, residual, ldb, stride_b, stream);
+        else
+            return MGX_E_UNSUPPORTED;
+    case MGX_F32:
+        return launch_qgemm<BN, IS_INT, float>(d, A, B, D, scale, bias, residual, ldb, stride_b, stream);
+    case MGX_F16:
+        return launch_qgemm<BN, IS_INT, __half>(d, A, B, D, scale, bias, residual, ldb, stride_b, stream);
+    default: return MGX_E_UNSUPPORTED;
+    }
+}
+
+static int pick_bn(const mgx_qgemm_desc& d)
+{
+    const int64_t sms = device_sm_count();
+    const int64_t tm  = (d.M + BM - 1) / BM;
+    for(int bn : {256, 128})
+    {
+        if(tm * ((d.N + bn - 1) / bn) * d.batch >= sms)
+            return bn;
+    }
+    return 64;
+}
+
+} // namespace mgx
+
+using namespace mgx;
+
+extern "C" size_t mgx_cuda_qgemm_workspace(const mgx_qgemm_desc* d)
+{
+    if(d == nullptr or d->b_layout != MGX_B_KN)
+        return 0;
+    const int64_t kpad = (d->K + 15) / 16 * 16;
+    return static_cast<size_t>(d->batch) * d->N * kpad;
+}
+
+extern "C" int mgx_cuda_qgemm(const mgx_qgemm_desc* d, const void* A, const void* B, void* D,
+                              const float* scale, const float* bias, const void* residual,
+                              void* workspace, size_t workspace_bytes, void* stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(d == nullptr or A == nullptr or B == nullptr or D == nullptr)
+        return MGX_E_INVALID_ARG;
+    if(d->M <= 0 or d->N <= 0 or d->K <= 0 or d->batch <= 0)
+        return MGX_E_INVALID_ARG;
+    if(d->ab_type != MGX_I8 and d->ab_type != MGX_FP8_E4M3FN)
+        return MGX_E_UNSUPPORTED;
+    if(d->scale_mode < MGX_SCALE_NONE or d->scale_mode > MGX_SCALE_PER_ROW)
+        return MGX_E_INVALID_ARG;
+    if(d->scale_mode != MGX_SCALE_NONE and scale == nullptr)
+        return MGX_E_INVALID_ARG;
+    if(d->act < MGX_ACT_NONE or d->act > MGX_ACT_SILU)
+        return MGX_E_INVALID_ARG;
+    if(d->out_type == MGX_I32 and
+       (d->ab_type != MGX_I8 or d->scale_mode != MGX_SCALE_NONE or bias != nullptr or
+        residual != nullptr or d->act != MGX_ACT_NONE))
+        return MGX_E_UNSUPPORTED;
+    if(d->M > INT32_MAX or d->N > INT32_MAX or d->K > INT32_MAX)
+        return MGX_E_TOO_LARGE;
+    if(d->lda < d->K or d->ldd < d->N)
+        return MGX_E_INVALID_ARG;
+    if((reinterpret_cast<uintptr_t>(A) & 15u) or (d->lda % 16) or
+       (d->batch > 1 and (d->stride_a % 16)))
+        return MGX_E_ALIGNMENT;
+
+    const void* Bk   = B;
+    int64_t ldb      = d->ldb;
+    int64_t stride_b = d->stride_b;
+    if(d->b_layout == MGX_B_KN)
+    {
+        // quant_dot's [K,N] operand is re-laid out K-contiguous into the workspace
+        if(d->ldb != d->N or (d->batch > 1 and d->stride_b != d->K * d->N))
+            return MGX_E_UNSUPPORTED;
+        const size_t need = mgx_cuda_qgemm_workspace(d);
+        if(workspace == nullptr or workspace_bytes < need)
+            return MGX_E_WORKSPACE;
+        if(reinterpret_cast<uintptr_t>(workspace) & 15u)
+            return MGX_E_ALIGNMENT;
+        const int64_t kpad = (d->K + 15) / 16 * 16;
+        int rc = transpose_8bit_ld(B, workspace, d->K, d->N, d->batch, kpad, stream);
+        if(rc != MGX_OK)
+            return rc;
+        Bk       = workspace;
+        ldb      = kpad;
+        stride_b = d->N * kpad;
+    }
+    else if(d->b_layout != MGX_B_NK)
+        return MGX_E_INVALID_ARG;
+    if(ldb < d->K)
+        return MGX_E_INVALID_ARG;
+    if((reinterpret_cast<uintptr_t>(Bk) & 15u) or (ldb % 16) or
+       (d->batch > 1 and (stride_b % 16)))
+        return MGX_E_ALIGNMENT;
+
+    const bool is_int = d->ab_type == MGX_I8;
+    switch(pick_bn(*d))
+    {
+    case 256:
+        return is_int ? dispatch_out<256, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream)
+                      : dispatch_out<256, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream);
+    case 128:
+        return is_int ? dispatch_out<128, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream)
+                      : dispatch_out<128, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream);
+    default:
+        return is_int ? dispatch_out<64, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream)
+                      : dispatch_out<64, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream);
+    }
+}
+
+int mgx::qgemm_status(unsigned int* out) { return read_and_clear_status(out); }

@@ -1,0 +1,242 @@
+/*
+ * mgx_cuda.h - C ABI of the sm_100a kernel library behind the MIGraphX `cuda` target.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (passed as void*, i.e. a cudaStream_t; NULL = the legacy default stream),
+ * enqueues work on that stream and returns without synchronising.
+ *
+ * Return value: 0 on success; a negative MGX_E_* code when the arguments are
+ * rejected on the host before anything is launched; a positive value is a
+ * cudaError_t reported by the CUDA runtime/driver.  Nothing throws across
+ * this boundary.  There is no CPU fallback: an unsupported case is an error.
+ *
+ * Device-side problems (a bounded wait inside a kernel ran out) are recorded
+ * in a per-device status word, read with mgx_cuda_device_status().
+ *
+ * The reference has no C ABI at this level: its GPU target calls rocBLAS /
+ * hipBLASLt / MLIR-generated kernels from C++ operator structs.  Each entry
+ * point below names the reference interface it stands in for.
+ */
+#ifndef MGX_CUDA_H
+#define MGX_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MGX_API __attribute__((visibility("default")))
+
+/* ---- status codes ------------------------------------------------------ */
+#define MGX_OK 0
+#define MGX_E_INVALID_ARG (-1)   /* null pointer, negative size, bad enum           */
+#define MGX_E_UNSUPPORTED (-2)   /* valid request this library has no kernel for    */
+#define MGX_E_ALIGNMENT (-3)     /* pointer / leading dimension not aligned as req. */
+#define MGX_E_WORKSPACE (-4)     /* workspace missing or too small                  */
+#define MGX_E_TOO_LARGE (-5)     /* size beyond a documented fixed maximum          */
+#define MGX_E_DRIVER (-6)        /* could not obtain a driver entry point           */
+#define MGX_E_DEVICE_TIMEOUT (-7) /* a kernel's bounded wait expired (status word)  */
+
+/* ---- element types (values are part of the ABI) ------------------------ */
+typedef enum mgx_dtype
+{
+    MGX_F32        = 0,
+    MGX_F16        = 1,
+    MGX_I8         = 2,
+    MGX_U8         = 3,
+    MGX_I32        = 4,
+    MGX_FP8_E4M3FN = 5
+} mgx_dtype;
+
+/* How the fp32 scale operand of a fused dequantizelinear is indexed.  After
+ * simplify_qdq the scale reaches the op as a full [M,N] broadcast view
+ * (reference: src/simplify_qdq.cpp:243-248); the host recovers the mode from
+ * the view's strides. */
+typedef enum mgx_scale_mode
+{
+    MGX_SCALE_NONE       = 0, /* raw accumulator out (quant_dot alone)          */
+    MGX_SCALE_PER_TENSOR = 1, /* scale[0]                                       */
+    MGX_SCALE_PER_COL    = 2, /* scale[n], n = output column (per out channel)  */
+    MGX_SCALE_PER_ROW    = 3  /* scale[m]                                       */
+} mgx_scale_mode;
+
+/* Activation applied after scale and bias (the fused `pointwise` module). */
+typedef enum mgx_act
+{
+    MGX_ACT_NONE     = 0,
+    MGX_ACT_RELU     = 1,
+    MGX_ACT_GELU_ERF = 2, /* 0.5*x*(1+erf(x/sqrt(2)))  (src/op/builder/gelu.cpp:58-74) */
+    MGX_ACT_GELU_TANH = 3,
+    MGX_ACT_SILU     = 4
+} mgx_act;
+
+/* ---- quantizelinear ---------------------------------------------------- *
+ * y[r,c] = clamp(rne(x[r,c] / scale[r,c]) + zp[r,c], lowest, max)  for int8/uint8,
+ * y[r,c] = fp8(clamp(x/scale + zp, -448, 448))                     for fp8 e4m3fn.
+ * Stands in for op::quantizelinear::compute
+ * (src/include/migraphx/op/quantizelinear.hpp:71-108).
+ * x is [rows, cols] with row stride ldx (elements); y likewise with ldy.
+ * scale has x's type and is indexed scale[r*scale_strides[0] + c*scale_strides[1]]
+ * (stride 0 = broadcast, as MIGraphX passes broadcast views); zp has y's type,
+ * may be NULL (zero) and is indexed the same way with zp_strides.
+ * x_type: MGX_F32 | MGX_F16.  y_type: MGX_I8 | MGX_U8 | MGX_FP8_E4M3FN. */
+MGX_API int mgx_cuda_quantizelinear(const void* x,
+                                    int x_type,
+                                    int64_t ldx,
+                                    const void* scale,
+                                    const int64_t scale_strides[2],
+                                    const void* zp,
+                                    const int64_t zp_strides[2],
+                                    void* y,
+                                    int y_type,
+                                    int64_t ldy,
+                                    int64_t rows,
+                                    int64_t cols,
+                                    void* stream);
+
+/* ---- dequantizelinear -------------------------------------------------- *
+ * y = (x - zp) * scale, output type = scale type (MGX_F32 | MGX_F16).
+ * Stands in for op::dequantizelinear::compute
+ * (src/include/migraphx/op/dequantizelinear.hpp:60-82).
+ * x_type: MGX_I8 | MGX_U8 | MGX_I32 | MGX_FP8_E4M3FN. */
+MGX_API int mgx_cuda_dequantizelinear(const void* x,
+                                      int x_type,
+                                      int64_t ldx,
+                                      const void* scale,
+                                      int scale_type,
+                                      const int64_t scale_strides[2],
+                                      const void* zp,
+                                      const int64_t zp_strides[2],
+                                      void* y,
+                                      int64_t ldy,
+                                      int64_t rows,
+                                      int64_t cols,
+                                      void* stream);
+
+/* ---- unpack_int4 / pack_int4 (stand-alone form) ------------------------ *
+ * unpack: out[r, 2i] = in[r,i] & 0xF, out[r, 2i+1] = in[r,i] >> 4 (sign-extended
+ * when type is MGX_I8).  Reference: op::unpack_int4::compute
+ * (src/include/migraphx/op/unpack_int4.hpp:75-120), HIP kernel
+ * src/targets/gpu/kernels/include/migraphx/kernels/unpack_int4.hpp:33-54.
+ * pack is the inverse with clipping to the 4-bit range
+ * (src/include/migraphx/op/pack_int4.hpp:79-123).  The axis is the last one. */
+MGX_API int mgx_cuda_unpack_int4(const void* in, void* out, int type, int64_t rows,
+                                 int64_t packed_cols, void* stream);
+MGX_API int mgx_cuda_pack_int4(const void* in, void* out, int type, int64_t rows,
+                               int64_t packed_cols, void* stream);
+
+/* ---- quant_dot (+ fused dequantizelinear / bias / activation / residual) *
+ * D[b] = epilogue(A[b] . B[b]) for b < batch.
+ * A is [M,K], row stride lda, K contiguous.  B is the quant_dot right operand:
+ *   b_layout = MGX_B_KN : [K,N], row stride ldb, N contiguous (MIGraphX default)
+ *   b_layout = MGX_B_NK : [N,K], row stride ldb, K contiguous (a transpose view)
+ * ab_type MGX_I8 accumulates exactly in int32; MGX_FP8_E4M3FN accumulates in fp32.
+ * Epilogue, in this order (it is the order of the fused pointwise module
+ * `dequantizelinear -> add(bias) -> act -> add(residual)`):
+ *   v = acc                                   (int32 or fp32)
+ *   if scale_mode != NONE: v = float(acc) * scale[..]   (fp32 multiply, one rounding)
+ *   if bias:     v = v + bias[n]              (fp32 vector of N, separate add)
+ *   v = act(v)
+ *   if residual: v = v + float(residual[m,n]) (same type/ld as D)
+ *   D = out_type(v)
+ * out_type: MGX_I32 (only ab_type I8, scale NONE, no bias/act/residual: the raw
+ * quant_dot result), MGX_F32, MGX_F16.
+ * Stands in for rocblas_gemm<op::quant_dot>::compute
+ * (src/targets/gpu/include/migraphx/gpu/gemm.hpp:109-127), hip_gemm for fp8
+ * (src/targets/gpu/include/migraphx/gpu/hip_gemm.hpp:44-141) and the
+ * gemm+pointwise fusion of src/targets/gpu/fuse_mlir.cpp:709-807; arithmetic
+ * follows ref_quant_gemm (src/targets/ref/lowering.cpp:205-249, src/gemm.cpp:43-63).
+ * Requirements: A, B, D 16-byte aligned; lda, ldb multiples of 16 elements.
+ * With b_layout = MGX_B_KN a workspace of mgx_cuda_qgemm_workspace() bytes is
+ * needed (B is re-laid out K-contiguous once per call); constant weights should
+ * be transposed once with mgx_cuda_transpose_8bit() and passed as MGX_B_NK. */
+typedef enum mgx_b_layout
+{
+    MGX_B_KN = 0,
+    MGX_B_NK = 1
+} mgx_b_layout;
+
+typedef struct mgx_qgemm_desc
+{
+    int64_t M, N, K;
+    int64_t batch;
+    int64_t lda, ldb, ldd;                 /* row strides, elements          */
+    int64_t stride_a, stride_b, stride_d;  /* batch strides, elements        */
+    int32_t ab_type;                       /* MGX_I8 | MGX_FP8_E4M3FN        */
+    int32_t out_type;                      /* MGX_I32 | MGX_F32 | MGX_F16    */
+    int32_t b_layout;                      /* mgx_b_layout                   */
+    int32_t scale_mode;                    /* mgx_scale_mode                 */
+    int32_t act;                           /* mgx_act                        */
+    int32_t reserved;
+} mgx_qgemm_desc;
+
+MGX_API size_t mgx_cuda_qgemm_workspace(const mgx_qgemm_desc* desc);
+MGX_API int mgx_cuda_qgemm(const mgx_qgemm_desc* desc,
+                           const void* A,
+                           const void* B,
+                           void* D,
+                           const float* scale,
+                           const float* bias,
+                           const void* residual,
+                           void* workspace,
+                           size_t workspace_bytes,
+                           void* stream);
+
+/* [rows, cols] bytes -> [cols, rows] bytes, per batch (dense, ld = cols / rows).
+ * Used once per constant weight so that quant_dot's [K,N] operand becomes
+ * K-contiguous (the reference does the equivalent with its column-major trick,
+ * src/targets/gpu/gemm_impl.cpp:343-351). */
+MGX_API int mgx_cuda_transpose_8bit(const void* src, void* dst, int64_t rows, int64_t cols,
+                                    int64_t batch, void* stream);
+
+/* ---- weight-only int4 linear: unpack_int4 + dequantizelinear + dot ------ *
+ * D[M,N] = A[M,K] (fp16) . W^T where W[n,k] = fp16((q[n,k] - zp) * s[n, k/group]),
+ * q unpacked from Bp[N, K/2] bytes (low nibble = even k;
+ * src/include/migraphx/op/unpack_int4.hpp:108-115), s fp16 [N, K/group], zp either
+ * the constant zp_const (zp == NULL; 8 is the MatMulNBits default,
+ * src/onnx/parse_matmulnbits.cpp:122) or uint8 [N, K/group].  fp32 accumulate,
+ * fp16 out.  This is the IR parse_matmulnbits emits
+ * (src/onnx/parse_matmulnbits.cpp:85-158) and what the reference fuses in
+ * src/targets/gpu/fuse_mlir.cpp:1236-1276.
+ * gemv: HBM-bound kernel for decode (M <= 16), optional split-K through the
+ * workspace.  gemm: tensor-core kernel for prefill.  mgx_cuda_w4a16() picks. */
+typedef struct mgx_w4_desc
+{
+    int64_t M, N, K;
+    int64_t lda, ldd;  /* row strides of A and D, elements */
+    int32_t group;     /* quantisation group along K (multiple of 32; 128 typical) */
+    int32_t zp_const;  /* used when zp == NULL */
+    int32_t act;       /* mgx_act, applied to the fp32 accumulator before the fp16 store */
+    int32_t reserved;
+} mgx_w4_desc;
+
+MGX_API size_t mgx_cuda_w4a16_workspace(const mgx_w4_desc* desc);
+MGX_API int mgx_cuda_w4a16_gemv(const mgx_w4_desc* desc, const void* A, const void* Bp,
+                                const void* scales, const void* zp, void* D, void* workspace,
+                                size_t workspace_bytes, void* stream);
+MGX_API int mgx_cuda_w4a16_gemm(const mgx_w4_desc* desc, const void* A, const void* Bp,
+                                const void* scales, const void* zp, void* D, void* workspace,
+                                size_t workspace_bytes, void* stream);
+MGX_API int mgx_cuda_w4a16(const mgx_w4_desc* desc, const void* A, const void* Bp,
+                           const void* scales, const void* zp, void* D, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* ---- device status ------------------------------------------------------ *
+ * Reads and clears the current device's status word (synchronises the device).
+ * *status = 0 when no kernel reported a problem; otherwise a code whose low 8
+ * bits say which wait gave up (1 = TMA full barrier, 2 = stage-empty barrier,
+ * 3 = accumulator-ready barrier, 4 = accumulator-free barrier). */
+MGX_API int mgx_cuda_device_status(int* status);
+
+/* Human-readable text for a return value of this library. */
+MGX_API const char* mgx_cuda_status_string(int code);
+
+/* Library build tag: "sm_100a" plus the kernel set version. */
+MGX_API const char* mgx_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MGX_CUDA_H */

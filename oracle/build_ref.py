@@ -1,0 +1,215 @@
+#!/usr/bin/env python3
+"""Build the UNMODIFIED MIGraphX core library and its CPU `ref` target from the
+reference sources where they lie, into oracle/_ref/ (git-ignored).
+
+This is test infrastructure: the resulting libmigraphx.so / libmigraphx_ref.so are
+(1) the parity oracle (MIGraphX's own CPU interpreter target, src/targets/ref),
+(2) the timed CPU baseline, and
+(3) the host library the `cuda` target plug-in is linked against.
+
+No reference source is copied.  The reference's own build system (cmake +
+ROCmCMakeBuildTools) is not run; the few files it would generate are produced
+here with the same trivial content:
+  * migraphx/export.h, migraphx/ref/export.h  (visibility macros, cmake/ExportHeader)
+  * migraphx/version.h                        (src/version.h.in, version from CMakeLists.txt)
+  * one translation unit per group of builtin operators holding
+    MIGRAPHX_REGISTER_OP(op::<name>) (cmake/RegisterOp.cmake:24-62 over the
+    operator list at src/CMakeLists.txt:177-328; the list is parsed from that
+    file at build time)
+  * stubs for msgpack / sqlite (third-party libraries absent here) that throw.
+
+Usage: python oracle/build_ref.py [--ref /root/reference] [--jobs 8]
+"""
+import argparse
+import concurrent.futures as cf
+import hashlib
+import os
+import re
+import subprocess
+import sys
+import sysconfig
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+OUT = os.path.join(HERE, "_ref")
+
+
+def nlohmann_include():
+    cands = [
+        os.path.join(sysconfig.get_paths()["purelib"], "include", "cudnn_frontend", "thirdparty"),
+        "/usr/include",
+    ]
+    for c in cands:
+        if os.path.exists(os.path.join(c, "nlohmann", "json.hpp")):
+            return c
+    raise SystemExit("nlohmann/json.hpp not found")
+
+
+def write_if_changed(path, text):
+    os.makedirs(os.path.dirname(path), exist_ok=True)
+    if os.path.exists(path) and open(path).read() == text:
+        return
+    with open(path, "w") as f:
+        f.write(text)
+
+
+def parse_version(ref):
+    txt = open(os.path.join(ref, "CMakeLists.txt")).read()
+    m = re.search(r"rocm_setup_version\(VERSION\s+(\d+)\.(\d+)\.(\d+)", txt)
+    if not m:
+        raise SystemExit("cannot find version in reference CMakeLists.txt")
+    return tuple(int(x) for x in m.groups())
+
+
+def parse_ops(ref):
+    txt = open(os.path.join(ref, "src", "CMakeLists.txt")).read()
+    m = re.search(r"register_migraphx_ops\(\s*\n(.*?)\n\)", txt, re.S)
+    ops = m.group(1).split()
+    extra = []
+    for mm in re.finditer(r"^register_op\(migraphx HEADER (\S+) OPERATORS ([^)]*)\)", txt, re.M):
+        extra.append((mm.group(1), mm.group(2).split()))
+    return ops, extra
+
+
+def gen_files(ref, gen):
+    major, minor, patch = parse_version(ref)
+    inc = os.path.join(gen, "include", "migraphx")
+    for name, macro in (("export.h", "MIGRAPHX"), ("ref/export.h", "MIGRAPHX_REF"),
+                        ("cuda/export.h", "MIGRAPHX_CUDA")):
+        write_if_changed(os.path.join(inc, name), f"""#pragma once
+#define {macro}_EXPORT __attribute__((visibility("default")))
+#define {macro}_NO_EXPORT __attribute__((visibility("hidden")))
+""")
+    write_if_changed(os.path.join(inc, "version.h"), f"""#pragma once
+#define MIGRAPHX_VERSION_MAJOR {major}
+#define MIGRAPHX_VERSION_MINOR {minor}
+#define MIGRAPHX_VERSION_PATCH {patch}
+#define MIGRAPHX_VERSION_TWEAK ""
+#define MIGRAPHX_SO_MAJOR_VERSION ({major} * 1000 * 1000 + {minor} * 1000 + {patch})
+""")
+    ops, extra = parse_ops(ref)
+    units = []
+    group = 8
+    entries = [(f"migraphx/op/{o}.hpp", [f"op::{o}"]) for o in ops] + extra
+    for gi in range(0, len(entries), group):
+        body = ["#include <migraphx/register_op.hpp>"]
+        for hdr, _ in entries[gi:gi + group]:
+            body.append(f"#include <{hdr}>")
+        body.append("namespace migraphx {\ninline namespace MIGRAPHX_INLINE_NS {")
+        for _, names in entries[gi:gi + group]:
+            for n in names:
+                body.append(f"MIGRAPHX_REGISTER_OP({n})")
+        body.append("} // namespace MIGRAPHX_INLINE_NS\n} // namespace migraphx\n")
+        p = os.path.join(gen, "ops", f"register_ops_{gi // group:02d}.cpp")
+        write_if_changed(p, "\n".join(body))
+        units.append(p)
+    stub = os.path.join(gen, "stubs.cpp")
+    write_if_changed(stub, """// msgpack-c and sqlite3 are not available in this environment: the entry points
+// exist so the library links, and throw when used (.mxr json format still works).
+#include <migraphx/msgpack.hpp>
+#include <migraphx/sqlite.hpp>
+#include <migraphx/errors.hpp>
+namespace migraphx {
+inline namespace MIGRAPHX_INLINE_NS {
+void to_msgpack(const value&, std::function<void(const char*, std::size_t)>) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
+std::vector<char> to_msgpack(const value&) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
+value from_msgpack(const std::vector<char>&) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
+value from_msgpack(const char*, std::size_t) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
+sqlite sqlite::read(const fs::path&) { MIGRAPHX_THROW("sqlite unavailable in this build"); }
+sqlite sqlite::write(const fs::path&) { MIGRAPHX_THROW("sqlite unavailable in this build"); }
+std::vector<std::unordered_map<std::string, std::string>> sqlite::execute(const std::string&) { MIGRAPHX_THROW("sqlite unavailable in this build"); }
+} // namespace MIGRAPHX_INLINE_NS
+} // namespace migraphx
+""")
+    units.append(stub)
+    return units
+
+
+def compile_one(args):
+    src, obj, flags = args
+    if os.path.exists(obj) and os.path.getmtime(obj) >= os.path.getmtime(src):
+        return src, 0, "", 0.0
+    os.makedirs(os.path.dirname(obj), exist_ok=True)
+    t = time.time()
+    r = subprocess.run(["g++", "-c", src, "-o", obj] + flags, capture_output=True, text=True)
+    return src, r.returncode, r.stderr[-4000:], time.time() - t
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default=os.environ.get("MIGRAPHX_REFERENCE", "/root/reference"))
+    ap.add_argument("--jobs", type=int, default=max(1, min(8, os.cpu_count() or 1)))
+    a = ap.parse_args()
+    ref = a.ref
+    if not os.path.isdir(os.path.join(ref, "src")):
+        print(f"[build_ref] reference sources not found at {ref}; keeping prebuilt files")
+        return 0
+    gen = os.path.join(OUT, "gen")
+    obj = os.path.join(OUT, "obj")
+    lib = os.path.join(OUT, "lib")
+    os.makedirs(lib, exist_ok=True)
+    gen_units = gen_files(ref, gen)
+
+    src = os.path.join(ref, "src")
+    skip = {"msgpack.cpp", "sqlite.cpp"}
+    core = [os.path.join(src, f) for f in sorted(os.listdir(src))
+            if f.endswith(".cpp") and f not in skip]
+    bdir = os.path.join(src, "op", "builder")
+    core += [os.path.join(bdir, f) for f in sorted(os.listdir(bdir)) if f.endswith(".cpp")]
+    core += gen_units
+    refdir = os.path.join(src, "targets", "ref")
+    reft = [os.path.join(refdir, f) for f in ("target.cpp", "lowering.cpp")]
+
+    base = ["-std=c++17", "-fPIC", "-w", "-pthread",
+            "-DMIGRAPHX_USE_EIGEN=0", "-DMIGRAPHX_HAS_EXECUTORS=0",
+            '-DMIGRAPHX_CXX_COMPILER="g++"',
+            f"-I{gen}/include", f"-I{src}/include", f"-I{bdir}/include",
+            f"-I{refdir}/include", f"-I{nlohmann_include()}"]
+
+    def objname(s):
+        h = hashlib.sha1(s.encode()).hexdigest()[:8]
+        return os.path.join(obj, os.path.basename(s)[:-4] + "_" + h + ".o")
+
+    jobs = []
+    late = []
+    for s in core + reft:
+        # these two need many GB and >10 min each at -O2 under g++ 13; nothing on the
+        # ref pipeline or the quantized path calls them, so they are compiled
+        # unoptimised, and after the others so that they do not compete for memory.
+        heavy = os.path.basename(s) in ("rewrite_gelu.cpp", "fuse_attention.cpp")
+        (late if heavy else jobs).append((s, objname(s), base + ["-O0" if heavy else "-O2"]))
+    t0 = time.time()
+    failed = []
+    with cf.ThreadPoolExecutor(a.jobs) as ex:
+        for i, (s, rc, err, dt) in enumerate(ex.map(compile_one, jobs)):
+            if rc != 0:
+                failed.append(s)
+                print(f"[build_ref] FAILED {s}\n{err}", flush=True)
+            elif dt > 0:
+                print(f"[build_ref] {i + 1}/{len(jobs)} {os.path.basename(s)} {dt:.0f}s", flush=True)
+    for j in late:
+        s, rc, err, dt = compile_one(j)
+        if rc != 0:
+            failed.append(s)
+            print(f"[build_ref] FAILED {s}\n{err}", flush=True)
+        elif dt > 0:
+            print(f"[build_ref] {os.path.basename(s)} {dt:.0f}s", flush=True)
+    if failed:
+        print(f"[build_ref] {len(failed)} translation units failed")
+        return 1
+    core_objs = [objname(s) for s in core]
+    ref_objs = [objname(s) for s in reft]
+    libmgx = os.path.join(lib, "libmigraphx.so")
+    libref = os.path.join(lib, "libmigraphx_ref.so")
+    newest = max(os.path.getmtime(o) for o in core_objs)
+    if not os.path.exists(libmgx) or os.path.getmtime(libmgx) < newest:
+        subprocess.check_call(["g++", "-shared", "-o", libmgx] + core_objs + ["-ldl", "-lpthread"])
+    if not os.path.exists(libref) or os.path.getmtime(libref) < max(os.path.getmtime(o) for o in ref_objs + [libmgx]):
+        subprocess.check_call(["g++", "-shared", "-o", libref] + ref_objs +
+                              [f"-L{lib}", "-lmigraphx", "-Wl,-rpath,$ORIGIN", "-lpthread"])
+    print(f"[build_ref] done in {time.time() - t0:.0f}s -> {lib}")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,228 @@
+"""CPU restatement (numpy) of MIGraphX's quantized-GEMM arithmetic.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the product imports this module: it is the
+checker used by tests/, by __graft_entry__.smoke() and by bench.py's cpu_baseline
+leg.  Every function restates one operator of the reference and cites the lines it
+follows (paths relative to the MIGraphX source tree).  The restatement is pinned
+against MIGraphX's own `ref` target built from the reference sources (oracle/_ref,
+see oracle/build_ref.py and tests/golden/make_golden.py) and against the golden
+vectors of the reference's test/ref/*.cpp files (tests/golden/reference_vectors.json).
+"""
+import numpy as np
+
+# ----------------------------------------------------------------------------- fp8 e4m3fn
+# Format: 1 sign, 4 exponent (bias 7), 3 mantissa; no infinities; 0x7F / 0xFF are NaN;
+# largest finite value 448 (src/include/migraphx/float8.hpp:83-112,
+# src/include/migraphx/float8_impl.hpp:38-245).
+
+
+def _e4m3fn_table():
+    vals = np.zeros(256, dtype=np.float64)
+    for code in range(256):
+        s = -1.0 if code & 0x80 else 1.0
+        e = (code >> 3) & 0xF
+        m = code & 0x7
+        if e == 0xF and m == 0x7:
+            v = np.nan
+        elif e == 0:
+            v = s * (m / 8.0) * 2.0 ** (-6)
+        else:
+            v = s * (1.0 + m / 8.0) * 2.0 ** (e - 7)
+        vals[code] = v
+    return vals
+
+
+E4M3FN_VALUES = _e4m3fn_table()
+_POS = E4M3FN_VALUES[:0x7F]  # codes 0x00..0x7E: 0 .. 448, increasing
+_MID = (_POS[:-1] + _POS[1:]) / 2.0
+
+
+def fp8e4m3fn_decode(codes):
+    """uint8 bit patterns -> float32 values."""
+    return E4M3FN_VALUES[np.asarray(codes, dtype=np.uint8)].astype(np.float32)
+
+
+def fp8e4m3fn_encode(x):
+    """float -> uint8 bit patterns, round-to-nearest-even, for |x| <= 448
+    (the cast of float8_impl.hpp:195-245 without clipping or stochastic rounding).
+    NaN -> 0x7F with the sign bit kept."""
+    x = np.asarray(x, dtype=np.float64)
+    ax = np.abs(x)
+    idx = np.searchsorted(_MID, ax, side="left")  # first midpoint >= |x|
+    idx = np.minimum(idx, len(_POS) - 1)
+    # exact tie with the midpoint above code idx: take the even code
+    tie = (idx < len(_MID)) & (ax == _MID[np.minimum(idx, len(_MID) - 1)])
+    idx = np.where(tie & (idx % 2 == 1), idx + 1, idx)
+    code = idx.astype(np.uint8)
+    code = np.where(np.isnan(x), np.uint8(0x7F), code)
+    sign = np.signbit(x).astype(np.uint8) << 7
+    return (code | sign).astype(np.uint8)
+
+
+# ----------------------------------------------------------------------------- quantizelinear
+def quantizelinear(x, scale, zp=None, out_type="int8"):
+    """src/include/migraphx/op/quantizelinear.hpp:71-108.
+
+    Integer targets: nearbyint(x / scale) with the division in the INPUT type and
+    round-half-even, + zero point in double, clamp to the type's range.
+    fp8 target: double(x)/double(scale) + zp, clamp to +-448, one RNE cast.
+    `scale` / `zp` broadcast against x like MIGraphX's broadcast views.
+    out_type: 'int8' | 'uint8' | 'fp8e4m3fn' (returned as uint8 bit patterns)."""
+    x = np.asarray(x)
+    scale = np.broadcast_to(np.asarray(scale, dtype=x.dtype), x.shape)
+    if out_type in ("int8", "uint8"):
+        lo, hi = (-128.0, 127.0) if out_type == "int8" else (0.0, 255.0)
+        z = np.zeros(x.shape) if zp is None else np.broadcast_to(np.asarray(zp), x.shape).astype(np.float64)
+        with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+            q = x / scale  # in x's own dtype (float32 or float16)
+        q = np.rint(q.astype(np.float64)) + z
+        # std::max(min, std::min(max, q)) : a NaN q ends up at max
+        q = np.where(np.isnan(q), hi, q)
+        q = np.maximum(lo, np.minimum(hi, q))
+        return q.astype(np.int8 if out_type == "int8" else np.uint8)
+    if out_type == "fp8e4m3fn":
+        z = 0.0 if zp is None else fp8e4m3fn_decode(np.broadcast_to(np.asarray(zp), x.shape)).astype(np.float64)
+        with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
+            q = x.astype(np.float64) / scale.astype(np.float64) + z
+        q = np.where(np.isnan(q), 448.0, q)
+        q = np.maximum(-448.0, np.minimum(448.0, q))
+        # double -> float -> fp8: the float step is exact enough not to matter for a
+        # 3-bit mantissa except on ties, which the float rounding preserves
+        return fp8e4m3fn_encode(q.astype(np.float32))
+    raise ValueError(out_type)
+
+
+# ----------------------------------------------------------------------------- dequantizelinear
+def dequantizelinear(x, scale, zp=None, x_is_fp8=False):
+    """src/include/migraphx/op/dequantizelinear.hpp:60-82:
+    y = (double(x) - double(zp)) * scale, stored in scale's type."""
+    scale = np.asarray(scale)
+    xv = fp8e4m3fn_decode(x).astype(np.float64) if x_is_fp8 else np.asarray(x).astype(np.float64)
+    if zp is None:
+        zv = 0.0
+    else:
+        zv = fp8e4m3fn_decode(zp).astype(np.float64) if x_is_fp8 else np.asarray(zp).astype(np.float64)
+    s = np.broadcast_to(scale, xv.shape).astype(np.float64)
+    return ((xv - zv) * s).astype(scale.dtype)
+
+
+# ----------------------------------------------------------------------------- int4
+def unpack_int4(packed, signed=False):
+    """src/include/migraphx/op/unpack_int4.hpp:75-120, last axis:
+    out[..., 2i] = low nibble, out[..., 2i+1] = high nibble; int8 sign-extends."""
+    b = np.asarray(packed).astype(np.uint8)
+    lo = b & 0xF
+    hi = b >> 4
+    out = np.stack([lo, hi], axis=-1).reshape(b.shape[:-1] + (b.shape[-1] * 2,))
+    if signed:
+        out = ((out.astype(np.int16) ^ 8) - 8).astype(np.int8)
+    return out
+
+
+def pack_int4(x, signed=False):
+    """src/include/migraphx/op/pack_int4.hpp:79-123: clip to the 4-bit range, then
+    out[..., i] = (x[..., 2i+1] << 4) | (x[..., 2i] & 0xF)."""
+    x = np.asarray(x)
+    if signed:
+        c = np.clip(x.astype(np.int16), -8, 7).astype(np.int8).view(np.uint8)
+    else:
+        c = np.minimum(x.astype(np.uint8), 15)
+    lo = c[..., 0::2] & 0xF
+    hi = c[..., 1::2]
+    out = ((hi.astype(np.uint16) << 4) | lo).astype(np.uint8)
+    return out.view(np.int8) if signed else out
+
+
+# ----------------------------------------------------------------------------- quant_dot
+def quant_dot_int8(a, b):
+    """ref_quant_gemm -> gemm_naive (src/targets/ref/lowering.cpp:205-249,
+    src/gemm.cpp:43-63) for int8 operands: exact sum of products, stored as int32.
+    a [..., M, K], b [..., K, N]."""
+    a = np.asarray(a)
+    b = np.asarray(b)
+    # float64 matmul is exact here: |sum| <= 128*128*K < 2^53
+    c = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    return c.astype(np.int64).astype(np.int32)
+
+
+def quant_dot_fp8(a_codes, b_codes):
+    """Same routine for fp8 e4m3fn operands (bit patterns in, float32 out):
+    double accumulate, one rounding to float (src/gemm.cpp:55-61)."""
+    a = fp8e4m3fn_decode(a_codes).astype(np.float64)
+    b = fp8e4m3fn_decode(b_codes).astype(np.float64)
+    return np.matmul(a, b).astype(np.float32)
+
+
+# ----------------------------------------------------------------------------- pointwise pieces
+def _erf(x):
+    from math import erf
+    return np.vectorize(erf, otypes=[np.float64])(x)
+
+
+def gelu_erf(x):
+    """(x*0.5) * (erf(x / sqrt(2)) + 1) evaluated op by op in x's type
+    (src/op/builder/gelu.cpp:58-74)."""
+    x = np.asarray(x)
+    t = x.dtype
+    half = (x * t.type(0.5)).astype(t)
+    d = (x / t.type(np.float32(np.sqrt(2.0)))).astype(t)
+    e = _erf(d.astype(np.float64)).astype(t)
+    return (half * (e + t.type(1.0)).astype(t)).astype(t)
+
+
+def apply_act(x, act):
+    if act in (None, "none"):
+        return x
+    if act == "relu":
+        return np.maximum(x, x.dtype.type(0))
+    if act == "gelu_erf":
+        return gelu_erf(x)
+    if act == "gelu_tanh":
+        x64 = x.astype(np.float64)
+        return (0.5 * x64 * (1.0 + np.tanh(0.7978845608028654 * (x64 + 0.044715 * x64 ** 3)))).astype(x.dtype)
+    if act == "silu":
+        x64 = x.astype(np.float64)
+        return (x64 / (1.0 + np.exp(-x64))).astype(x.dtype)
+    raise ValueError(act)
+
+
+def qlinear_epilogue(acc, scale=None, bias=None, act=None, residual=None, out_dtype=np.float32):
+    """The instruction chain simplify_qdq + the model leave after quant_dot
+    (src/simplify_qdq.cpp:243-287): dequantizelinear(acc, scale) -> add(bias) ->
+    activation -> add(residual), each a separate fp32 operation; a final convert
+    when the model runs in fp16."""
+    acc = np.asarray(acc)
+    if scale is None:
+        v = acc.astype(np.float32)
+    else:
+        v = dequantizelinear(acc, np.asarray(scale, dtype=np.float32))
+    if bias is not None:
+        v = (v + np.asarray(bias, dtype=np.float32)).astype(np.float32)
+    v = apply_act(v, act)
+    if residual is not None:
+        v = (v + np.asarray(residual).astype(np.float32)).astype(np.float32)
+    return v.astype(out_dtype)
+
+
+# ----------------------------------------------------------------------------- weight-only int4
+def w4a16_dequant_weights(bp, scales, zp=None, zp_const=8, group=128):
+    """unpack_int4 + dequantizelinear to fp16 as src/onnx/parse_matmulnbits.cpp:85-158
+    builds them: W[n,k] = fp16((q[n,k] - zp[n,k/group]) * s[n,k/group])."""
+    q = unpack_int4(bp).astype(np.float64)  # [N, K]
+    n, k = q.shape
+    s = np.repeat(np.asarray(scales, dtype=np.float16).reshape(n, k // group), group, axis=1)
+    if zp is None:
+        z = float(zp_const)
+    else:
+        z = np.repeat(np.asarray(zp).reshape(n, k // group), group, axis=1).astype(np.float64)
+    return ((q - z) * s.astype(np.float64)).astype(np.float16)
+
+
+def w4a16_linear(a, bp, scales, zp=None, zp_const=8, group=128, act=None):
+    """dot(A_fp16[M,K], transpose(W_fp16[N,K])) with gemm_naive's double accumulation
+    and one rounding to fp16 (src/gemm.cpp:55-61)."""
+    w = w4a16_dequant_weights(bp, scales, zp, zp_const, group)
+    acc = np.matmul(np.asarray(a, dtype=np.float16).astype(np.float64), w.astype(np.float64).T)
+    if act not in (None, "none"):
+        acc = apply_act(acc.astype(np.float32), act).astype(np.float64)
+    return acc.astype(np.float16)

@@ -1,0 +1,158 @@
+"""Parity of the CUDA quant_dot (+ fused epilogue) against the CPU oracle, through
+the C ABI.  int32 accumulators must be bit-exact; the dequantised fp32 output must be
+within rtol 1e-5 (it is bit-exact for relu / no activation by construction); fp8 and
+fp16 outputs within rtol 2e-2 / atol 1e-2."""
+import numpy as np
+import pytest
+
+from oracle import mgx_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(x, device):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x)).to(device)
+
+
+def _rand_i8(rng, shape):
+    return rng.integers(-127, 128, size=shape, dtype=np.int8)
+
+
+INT8_SHAPES = [
+    (128, 128, 128), (128, 256, 128), (256, 1024, 1024), (64, 96, 128), (1, 64, 32),
+    (130, 72, 272), (300, 520, 1040), (129, 257, 4096), (512, 768, 3072),
+]
+
+
+@pytest.mark.parametrize("M,N,K", INT8_SHAPES)
+@pytest.mark.parametrize("layout", ["kn", "nk"])
+def test_quant_dot_int8_bit_exact(cuda_device, M, N, K, layout):
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M * 7919 + N * 31 + K)
+    a = _rand_i8(rng, (M, K))
+    b = _rand_i8(rng, (K, N))
+    ref = O.quant_dot_int8(a, b)
+    if layout == "kn":
+        got = capi.qgemm(_t(a, cuda_device), _t(b, cuda_device), b_layout=capi.B_KN)
+    else:
+        got = capi.qgemm(_t(a, cuda_device), _t(b.T, cuda_device), b_layout=capi.B_NK)
+    assert got.dtype == torch.int32
+    np.testing.assert_array_equal(got.cpu().numpy(), ref)
+
+
+def test_quant_dot_int8_extremes(cuda_device):
+    from amdmigraphx_b200 import capi
+    M, N, K = 128, 128, 2048
+    a = np.full((M, K), -128, dtype=np.int8)
+    b = np.full((K, N), -128, dtype=np.int8)
+    b[:, ::2] = 127
+    got = capi.qgemm(_t(a, cuda_device), _t(b, cuda_device))
+    np.testing.assert_array_equal(got.cpu().numpy(), O.quant_dot_int8(a, b))
+
+
+def test_quant_dot_int8_batched(cuda_device):
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(5)
+    a = _rand_i8(rng, (3, 200, 160))
+    b = _rand_i8(rng, (3, 160, 144))
+    got = capi.qgemm(_t(a, cuda_device), _t(b, cuda_device))
+    np.testing.assert_array_equal(got.cpu().numpy(), O.quant_dot_int8(a, b))
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu_erf"])
+@pytest.mark.parametrize("scale_kind", ["tensor", "col", "row"])
+def test_qlinear_int8_fused_epilogue(cuda_device, act, scale_kind):
+    """config-1 shaped block: quant_dot -> dequantizelinear -> add(bias) -> act."""
+    import torch
+    from amdmigraphx_b200 import capi
+    M, N, K = 256, 1024, 1024
+    rng = np.random.default_rng(0)
+    a = _rand_i8(rng, (M, K))
+    b = _rand_i8(rng, (K, N))
+    x_scale = np.float32(0.02)
+    if scale_kind == "tensor":
+        scale = np.array([x_scale * np.float32(0.005)], dtype=np.float32)
+        sview = scale
+    elif scale_kind == "col":
+        scale = (x_scale * rng.uniform(0.001, 0.01, size=N).astype(np.float32)).astype(np.float32)
+        sview = scale[None, :]
+    else:
+        scale = (x_scale * rng.uniform(0.001, 0.01, size=M).astype(np.float32)).astype(np.float32)
+        sview = scale[:, None]
+    bias = rng.normal(0, 0.1, size=N).astype(np.float32)
+    acc = O.quant_dot_int8(a, b)
+    ref = O.qlinear_epilogue(acc, sview, bias, act)
+    mode = {"tensor": capi.SCALE_PER_TENSOR, "col": capi.SCALE_PER_COL, "row": capi.SCALE_PER_ROW}[scale_kind]
+    got = capi.qgemm(_t(a, cuda_device), _t(b, cuda_device), scale=_t(scale, cuda_device),
+                     scale_mode=mode, bias=_t(bias, cuda_device), act=act,
+                     out_dtype=torch.float32).cpu().numpy()
+    if act in (None, "relu"):
+        np.testing.assert_array_equal(got, ref)  # same operations, same roundings
+    else:
+        np.testing.assert_allclose(got, ref, rtol=1e-5, atol=1e-6)
+
+
+def test_qlinear_int8_residual_fp16_out(cuda_device):
+    import torch
+    from amdmigraphx_b200 import capi
+    M, N, K = 384, 768, 768
+    rng = np.random.default_rng(11)
+    a = _rand_i8(rng, (M, K))
+    b = _rand_i8(rng, (K, N))
+    scale = rng.uniform(1e-5, 1e-4, size=N).astype(np.float32)
+    bias = rng.normal(0, 0.1, size=N).astype(np.float32)
+    res = rng.normal(0, 1, size=(M, N)).astype(np.float16)
+    ref = O.qlinear_epilogue(O.quant_dot_int8(a, b), scale[None, :], bias, None, res, np.float16)
+    got = capi.qgemm(_t(a, cuda_device), _t(b, cuda_device), scale=_t(scale, cuda_device),
+                     bias=_t(bias, cuda_device), residual=_t(res, cuda_device),
+                     out_dtype=torch.float16).cpu().numpy()
+    np.testing.assert_allclose(got.astype(np.float32), ref.astype(np.float32), rtol=2e-2, atol=1e-2)
+    # fp32 chain then one rounding: equal up to one fp16 ulp
+    assert np.mean(got == ref) > 0.999
+
+
+FP8_SHAPES = [(128, 128, 128), (16, 4096, 4096), (1, 512, 256), (200, 328, 1040), (1024, 512, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", FP8_SHAPES)
+def test_quant_dot_fp8(cuda_device, M, N, K):
+    """config-3 shaped: fp8 e4m3fn operands, fp32 accumulate, DQ + bias + gelu."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    af = rng.normal(0, 1, size=(M, K)).astype(np.float32)
+    bf = rng.normal(0, 1, size=(K, N)).astype(np.float32)
+    sa = np.float32(np.abs(af).max() / 448.0)
+    sb = np.float32(np.abs(bf).max() / 448.0)
+    aq = O.quantizelinear(af, sa, None, "fp8e4m3fn")
+    bq = O.quantizelinear(bf, sb, None, "fp8e4m3fn")
+    bias = rng.normal(0, 0.1, size=N).astype(np.float32)
+    acc = O.quant_dot_fp8(aq, bq)
+    scale = np.array([sa * sb], dtype=np.float32)
+    ref = O.qlinear_epilogue(acc, scale, bias, "gelu_erf")
+    a_t = _t(aq, cuda_device).view(torch.float8_e4m3fn)
+    b_t = _t(bq, cuda_device).view(torch.float8_e4m3fn)
+    raw = capi.qgemm(a_t, b_t, out_dtype=torch.float32).cpu().numpy()
+    np.testing.assert_allclose(raw, acc, rtol=2e-2, atol=1e-2)
+    # fp32 accumulation of exactly representable products: far tighter in practice
+    assert np.max(np.abs(raw - acc)) <= 1e-3 * max(1.0, np.abs(acc).max())
+    got = capi.qgemm(a_t, b_t, scale=_t(scale, cuda_device), bias=_t(bias, cuda_device),
+                     act="gelu_erf", out_dtype=torch.float32).cpu().numpy()
+    np.testing.assert_allclose(got, ref, rtol=2e-2, atol=1e-2)
+
+
+def test_qgemm_rejects_bad_arguments(cuda_device):
+    import torch
+    from amdmigraphx_b200 import capi
+    a = torch.zeros((16, 24), dtype=torch.int8, device=cuda_device)  # K % 16 != 0
+    b = torch.zeros((24, 16), dtype=torch.int8, device=cuda_device)
+    with pytest.raises(capi.MgxError) as e:
+        capi.qgemm(a, b)
+    assert e.value.code == capi.E_ALIGNMENT
+    a = torch.zeros((16, 32), dtype=torch.int8, device=cuda_device)
+    b = torch.zeros((32, 16), dtype=torch.int8, device=cuda_device)
+    with pytest.raises(capi.MgxError) as e:
+        capi.qgemm(a, b, workspace=torch.empty(8, dtype=torch.uint8, device=cuda_device))
+    assert e.value.code == capi.E_WORKSPACE

@@ -1,0 +1,47 @@
+"""Weight-only int4 linear (unpack_int4 + group dequantizelinear + dot) on the GPU against
+the CPU oracle: fp16 output within rtol 2e-2 / atol 1e-2."""
+import numpy as np
+import pytest
+
+from oracle import mgx_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(x, device):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(x)).to(device)
+
+
+def _case(rng, M, N, K, group, with_zp):
+    a = rng.normal(0, 1, size=(M, K)).astype(np.float16)
+    bp = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    s = rng.uniform(0.005, 0.02, size=(N, K // group)).astype(np.float16)
+    zp = rng.integers(0, 16, size=(N, K // group)).astype(np.uint8) if with_zp else None
+    return a, bp, s, zp
+
+
+@pytest.mark.parametrize("M,N,K,group", [
+    (1, 256, 512, 128), (1, 4096, 4096, 128), (16, 512, 1024, 128), (4, 100, 256, 32),
+    (3, 64, 11008, 128), (16, 1024, 4096, 128), (2, 40, 64, 64),
+])
+@pytest.mark.parametrize("with_zp", [False, True])
+def test_w4a16_decode(cuda_device, M, N, K, group, with_zp):
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M * 1009 + N * 17 + K + group)
+    a, bp, s, zp = _case(rng, M, N, K, group, with_zp)
+    ref = O.w4a16_linear(a, bp, s, zp, 8, group).astype(np.float32)
+    got = capi.w4a16(_t(a, cuda_device), _t(bp, cuda_device), _t(s, cuda_device),
+                     None if zp is None else _t(zp, cuda_device), group=group, which="gemv")
+    np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
+
+
+def test_w4a16_rejects_bad_arguments(cuda_device):
+    import torch
+    from amdmigraphx_b200 import capi
+    a = torch.zeros((1, 48), dtype=torch.float16, device=cuda_device)
+    bp = torch.zeros((8, 24), dtype=torch.uint8, device=cuda_device)
+    s = torch.ones((8, 1), dtype=torch.float16, device=cuda_device)
+    with pytest.raises(capi.MgxError) as e:
+        capi.w4a16(a, bp, s, group=48)
+    assert e.value.code == capi.E_UNSUPPORTED
