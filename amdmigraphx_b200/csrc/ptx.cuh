@@ -149,6 +149,17 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
                  : "memory");
 }
 
+// 3-D tiled store shared -> global (bulk async-group completion).  Elements of the box
+// that fall outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src,
+                                             int32_t c0, int32_t c1, int32_t c2)
+{
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::
+                     "l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols)
 {

@@ -23,8 +23,8 @@ namespace mgx {
 constexpr int BM        = 128; // rows of D per tile (UMMA M, one TMEM lane per row)
 constexpr int BK        = 128; // bytes (= 8-bit elements) of K per pipeline stage
 constexpr int UMMA_K    = 32;  // K per tcgen05.mma for 8-bit operands
-constexpr int NTHREADS  = 192;
-constexpr int EPI_WARP0 = 2;
+constexpr int EPI_WARPS = 8;   // two per TMEM lane quarter, each takes half of the columns
+constexpr int NTHREADS  = 64 + 32 * EPI_WARPS;
 
 struct qgemm_params
 {
@@ -39,6 +39,8 @@ struct qgemm_params
     int num_kb;
     int scale_mode;
     int act;
+    int vec_sb; // scale / bias vectors are 16-byte aligned (float4 loads allowed)
+    int vec_io; // D (and residual) rows can be accessed with 16-byte (fp32/int32) / 8-byte (fp16) vectors
 };
 
 template <int BN>
@@ -48,38 +50,170 @@ struct qgemm_smem
     static constexpr int b_bytes     = BN * BK;
     static constexpr int stage_bytes = a_bytes + b_bytes;
     static constexpr int stages      = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+    static constexpr int epi_bytes   = EPI_WARPS * 32 * 128; // 32 rows x 32 words per epilogue warp
     static constexpr int bar_bytes   = 256;
-    static constexpr int total       = stages * stage_bytes + bar_bytes + 1024; // + alignment slack
+    static constexpr int total = stages * stage_bytes + epi_bytes + bar_bytes + 1024; // + alignment slack
 };
 
-__device__ __forceinline__ float apply_act(float v, int act)
+template <int ACT>
+__device__ __forceinline__ float apply_act(float v)
 {
-    switch(act)
-    {
-    case MGX_ACT_RELU: return fmaxf(v, 0.0f);
-    case MGX_ACT_GELU_ERF:
+    if constexpr(ACT == MGX_ACT_RELU)
+        return fmaxf(v, 0.0f);
+    else if constexpr(ACT == MGX_ACT_GELU_ERF)
         // (x*0.5) * (erf(x / sqrt(2)) + 1): operation order of src/op/builder/gelu.cpp:58-74
-        return __fmul_rn(__fmul_rn(v, 0.5f), __fadd_rn(erff(__fdiv_rn(v, 1.41421356237309504880f)), 1.0f));
-    case MGX_ACT_GELU_TANH: {
+        return __fmul_rn(__fmul_rn(v, 0.5f),
+                         __fadd_rn(erff(__fdiv_rn(v, 1.41421356237309504880f)), 1.0f));
+    else if constexpr(ACT == MGX_ACT_GELU_TANH)
+    {
         float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
         return 0.5f * v * (1.0f + tanhf(u));
     }
-    case MGX_ACT_SILU: return v / (1.0f + expf(-v));
-    default: return v;
-    }
+    else if constexpr(ACT == MGX_ACT_SILU)
+        return v / (1.0f + expf(-v));
+    else
+        return v;
 }
 
-template <class T>
-__device__ __forceinline__ float load_as_float(const void* p, int64_t i);
-template <>
-__device__ __forceinline__ float load_as_float<float>(const void* p, int64_t i)
+// float(double(acc) * double(s)) without fp64 instructions.  For |acc| < 2^24 the
+// conversion is exact and one fp32 multiply rounds exactly like the reference's
+// double product.  Larger accumulators are split into an exactly representable high
+// part and a small remainder, and the product is summed with error compensation.
+__device__ __forceinline__ float dequant_i32(int32_t acc, float s)
 {
-    return static_cast<const float*>(p)[i];
+    const float a = __int2float_rn(acc);
+    float x       = __fmul_rn(a, s);
+    if(acc >= (1 << 24) or acc <= -(1 << 24))
+    {
+        const float lo = __int2float_rn(acc - __float2int_rn(a));
+        const float e  = __fmaf_rn(a, s, -x);
+        x              = __fadd_rn(x, __fmaf_rn(lo, s, e));
+    }
+    return x;
 }
-template <>
-__device__ __forceinline__ float load_as_float<__half>(const void* p, int64_t i)
+
+struct epi_ctx
 {
-    return __half2float(static_cast<const __half*>(p)[i]);
+    const qgemm_params* p;
+    uint8_t* box;      // this warp's 32 x 128-byte staging area (16-byte pieces XOR-swizzled by row)
+    int lane;
+    int64_t row0;      // global row of staging row 0
+    int64_t batch_off; // b * stride_d
+};
+
+// Second half of the epilogue for one 32-column chunk: read the raw accumulators back
+// from shared memory so that 8 consecutive lanes cover one 128-byte row segment, apply
+// dequantizelinear / bias / activation / residual, convert and store coalesced.
+template <bool IS_INT, class OutT, int ACT>
+__device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, float4 sc4, float4 bi4)
+{
+    const qgemm_params& p = *e.p;
+    const int pc          = e.lane & 7;  // which 4-column piece of the chunk this lane owns
+    const int rsub        = e.lane >> 3; // row within a group of 4
+    const int64_t c4      = col + pc * 4;
+    const float sc[4]     = {sc4.x, sc4.y, sc4.z, sc4.w};
+    const float bi[4]     = {bi4.x, bi4.y, bi4.z, bi4.w};
+#pragma unroll
+    for(int it = 0; it < 8; ++it)
+    {
+        const int r       = it * 4 + rsub;
+        const int64_t row = e.row0 + r;
+        const uint4 w     = *reinterpret_cast<const uint4*>(e.box + r * 128 + ((pc ^ (r & 7)) * 16));
+        if(row >= p.M or c4 >= p.N)
+            continue;
+        const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+        OutT* dst = static_cast<OutT*>(p.D) + e.batch_off + row * p.ldd + c4;
+        if constexpr(std::is_same<OutT, int32_t>::value)
+        {
+            if(p.vec_io and c4 + 4 <= p.N)
+                *reinterpret_cast<uint4*>(dst) = w;
+            else
+                for(int j = 0; j < 4 and c4 + j < p.N; ++j)
+                    dst[j] = static_cast<int32_t>(wv[j]);
+        }
+        else
+        {
+            float v[4];
+            float rs = 1.0f;
+            if(p.scale_mode == MGX_SCALE_PER_ROW)
+                rs = __ldg(p.scale + row);
+#pragma unroll
+            for(int j = 0; j < 4; ++j)
+            {
+                float x;
+                const float s = p.scale_mode == MGX_SCALE_PER_ROW ? rs : sc[j];
+                if constexpr(IS_INT)
+                {
+                    const int32_t a = static_cast<int32_t>(wv[j]);
+                    x = p.scale_mode == MGX_SCALE_NONE ? __int2float_rn(a) : dequant_i32(a, s);
+                }
+                else
+                {
+                    x = __uint_as_float(wv[j]);
+                    if(p.scale_mode != MGX_SCALE_NONE)
+                        x = __fmul_rn(x, s);
+                }
+                if(p.bias != nullptr)
+                    x = __fadd_rn(x, bi[j]);
+                v[j] = apply_act<ACT>(x);
+            }
+            const bool full = p.vec_io and c4 + 4 <= p.N;
+            if(p.residual != nullptr)
+            {
+                const OutT* res = static_cast<const OutT*>(p.residual) + e.batch_off + row * p.ldd + c4;
+                if(full)
+                {
+                    if constexpr(std::is_same<OutT, float>::value)
+                    {
+                        const float4 q = *reinterpret_cast<const float4*>(res);
+                        v[0] = __fadd_rn(v[0], q.x), v[1] = __fadd_rn(v[1], q.y);
+                        v[2] = __fadd_rn(v[2], q.z), v[3] = __fadd_rn(v[3], q.w);
+                    }
+                    else
+                    {
+                        const uint2 q    = *reinterpret_cast<const uint2*>(res);
+                        const __half* qh = reinterpret_cast<const __half*>(&q);
+#pragma unroll
+                        for(int j = 0; j < 4; ++j)
+                            v[j] = __fadd_rn(v[j], __half2float(qh[j]));
+                    }
+                }
+                else
+                {
+                    for(int j = 0; j < 4 and c4 + j < p.N; ++j)
+                    {
+                        if constexpr(std::is_same<OutT, float>::value)
+                            v[j] = __fadd_rn(v[j], res[j]);
+                        else
+                            v[j] = __fadd_rn(v[j], __half2float(res[j]));
+                    }
+                }
+            }
+            if constexpr(std::is_same<OutT, float>::value)
+            {
+                if(full)
+                    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                else
+                    for(int j = 0; j < 4 and c4 + j < p.N; ++j)
+                        dst[j] = v[j];
+            }
+            else
+            {
+                if(full)
+                {
+                    uint2 o;
+                    __half2 h0 = __floats2half2_rn(v[0], v[1]);
+                    __half2 h1 = __floats2half2_rn(v[2], v[3]);
+                    o.x        = *reinterpret_cast<uint32_t*>(&h0);
+                    o.y        = *reinterpret_cast<uint32_t*>(&h1);
+                    *reinterpret_cast<uint2*>(dst) = o;
+                }
+                else
+                    for(int j = 0; j < 4 and c4 + j < p.N; ++j)
+                        dst[j] = __float2half_rn(v[j]);
+            }
+        }
+    }
 }
 
 // IS_INT: accumulator registers hold int32 (kind::i8) else fp32 bit patterns.
@@ -95,12 +229,13 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem           = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
 
-    uint8_t* bar_base     = smem + S::stages * S::stage_bytes;
-    uint64_t* full_bar    = reinterpret_cast<uint64_t*>(bar_base);
-    uint64_t* empty_bar   = full_bar + S::stages;
-    uint64_t* accf_bar    = empty_bar + S::stages; // [2] accumulator ready
-    uint64_t* acce_bar    = accf_bar + 2;          // [2] accumulator drained
-    uint32_t* tmem_slot   = reinterpret_cast<uint32_t*>(acce_bar + 2);
+    uint8_t* epi_base   = smem + S::stages * S::stage_bytes;
+    uint8_t* bar_base   = epi_base + S::epi_bytes;
+    uint64_t* full_bar  = reinterpret_cast<uint64_t*>(bar_base);
+    uint64_t* empty_bar = full_bar + S::stages;
+    uint64_t* accf_bar  = empty_bar + S::stages; // [2] accumulator ready
+    uint64_t* acce_bar  = accf_bar + 2;          // [2] accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acce_bar + 2);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
     const int warp = threadIdx.x >> 5;
@@ -117,7 +252,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         for(int b = 0; b < 2; ++b)
         {
             mbar_init(&accf_bar[b], 1);
-            mbar_init(&acce_bar[b], 4); // one arrival per epilogue warp
+            mbar_init(&acce_bar[b], EPI_WARPS); // one arrival per epilogue warp
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -176,9 +311,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         {
             constexpr uint32_t idesc = IS_INT ? make_idesc(2u, 1u, 1u, BM, BN)  // s32 += s8*s8
                                               : make_idesc(1u, 0u, 0u, BM, BN); // f32 += e4m3*e4m3
-            uint32_t it  = 0;
-            uint32_t lt  = 0; // local tile counter
-            bool ok      = true;
+            uint32_t it = 0;
+            uint32_t lt = 0; // local tile counter
+            bool ok     = true;
             for(int64_t t = first_tile; ok and t < p.num_tiles; t += tile_step, ++lt)
             {
                 const uint32_t buf = lt & 1u;
@@ -219,9 +354,22 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     else
     {
         // ---------------------------------------------------- epilogue
-        const int quarter     = warp & 3; // TMEM lane quarter this warp may read
-        const int row_in_tile = quarter * 32 + lane;
-        uint32_t lt           = 0;
+        // Each warp owns TMEM lane quarter (warp % 4) = 32 rows of the tile, and one half
+        // of the tile's columns.  Per 32-column chunk: tcgen05.ld (one row per thread) ->
+        // swizzled shared memory -> read back with 8 lanes per 128-byte row segment ->
+        // dequantizelinear / bias / activation / residual -> coalesced global stores.
+        const int ew      = warp - 2;
+        const int quarter = warp & 3;
+        const int half    = ew >> 2;
+        constexpr int COLS_PER_WARP = BN / 2;
+        epi_ctx e;
+        e.p    = &p;
+        e.box  = epi_base + ew * (32 * 128);
+        e.lane = lane;
+        uint8_t* my_row = e.box + lane * 128;
+        const bool per_col = p.scale_mode == MGX_SCALE_PER_COL;
+        const float tensor_scale = p.scale_mode == MGX_SCALE_PER_TENSOR ? __ldg(p.scale) : 1.0f;
+        uint32_t lt = 0;
         for(int64_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt)
         {
             const int b     = static_cast<int>(t / tiles_mn);
@@ -229,151 +377,67 @@ __global__ void __launch_bounds__(NTHREADS, 1)
             const int m_blk = r % p.tiles_m;
             const int n_blk = r / p.tiles_m;
             const uint32_t buf = lt & 1u;
+            const int64_t col0 = static_cast<int64_t>(n_blk) * BN + half * COLS_PER_WARP;
+            e.row0      = static_cast<int64_t>(m_blk) * BM + quarter * 32;
+            e.batch_off = b * p.stride_d;
+
             if(not mbar_wait_bounded(&accf_bar[buf], (lt >> 1) & 1u, abort_flag, 3))
                 break;
             tc_fence_after_sync();
 
-            const int64_t row  = static_cast<int64_t>(m_blk) * BM + row_in_tile;
-            const int64_t col0 = static_cast<int64_t>(n_blk) * BN;
-            const bool row_ok  = row < p.M;
-            OutT* drow = static_cast<OutT*>(p.D) + b * p.stride_d + row * p.ldd;
-            const OutT* rrow =
-                p.residual == nullptr
-                    ? nullptr
-                    : static_cast<const OutT*>(p.residual) + b * p.stride_d + row * p.ldd;
-            double row_scale = 1.0;
-            if(p.scale_mode == MGX_SCALE_PER_TENSOR)
-                row_scale = static_cast<double>(__ldg(p.scale));
-            else if(p.scale_mode == MGX_SCALE_PER_ROW and row_ok)
-                row_scale = static_cast<double>(__ldg(p.scale + row));
-            const bool vec_ok = (p.ldd % (16 / sizeof(OutT)) == 0) and
-                                ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0) and
-                                (p.stride_d % (16 / sizeof(OutT)) == 0);
-
 #pragma unroll 1
-            for(int c = 0; c < BN; c += 32)
+            for(int c = 0; c < COLS_PER_WARP; c += 32)
             {
-                uint32_t acc[32];
-                __syncwarp(); // tcgen05.ld is warp-collective: re-converge after the guarded stores
-                const uint32_t taddr =
-                    tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + c;
-                tmem_ld_32x32b_x32(taddr, acc);
-                tmem_ld_wait();
                 const int64_t col = col0 + c;
-                if(not row_ok or col >= p.N)
-                    continue;
-                if constexpr(sizeof(OutT) == 4 and IS_INT and std::is_same<OutT, int32_t>::value)
+                if(col >= p.N)
+                    break; // uniform over the warp: the rest is outside D
+                // this lane's 4 columns of the chunk: scale and bias (loads overlap the TMEM read)
+                const int64_t c4 = col + (lane & 7) * 4;
+                float4 sc4 = make_float4(tensor_scale, tensor_scale, tensor_scale, tensor_scale);
+                float4 bi4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                if constexpr(not std::is_same<OutT, int32_t>::value)
                 {
-                    if(vec_ok and col + 32 <= p.N)
+                    if(c4 + 4 <= p.N and p.vec_sb)
                     {
-#pragma unroll
-                        for(int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<uint4*>(drow + col + j) =
-                                make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                        if(per_col)
+                            sc4 = __ldg(reinterpret_cast<const float4*>(p.scale + c4));
+                        if(p.bias != nullptr)
+                            bi4 = __ldg(reinterpret_cast<const float4*>(p.bias + c4));
                     }
                     else
                     {
-                        for(int j = 0; j < 32 and col + j < p.N; ++j)
-                            drow[col + j] = static_cast<int32_t>(acc[j]);
+                        float* sp = reinterpret_cast<float*>(&sc4);
+                        float* bp = reinterpret_cast<float*>(&bi4);
+                        for(int j = 0; j < 4; ++j)
+                        {
+                            if(c4 + j < p.N)
+                            {
+                                if(per_col)
+                                    sp[j] = __ldg(p.scale + c4 + j);
+                                if(p.bias != nullptr)
+                                    bp[j] = __ldg(p.bias + c4 + j);
+                            }
+                        }
                     }
                 }
-                else
+                uint32_t acc[32];
+                __syncwarp(); // tcgen05.ld is warp-collective; also orders reuse of the box
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                       buf * BN + half * COLS_PER_WARP + c;
+                tmem_ld_32x32b_x32(taddr, acc);
+                tmem_ld_wait();
+#pragma unroll
+                for(int q = 0; q < 8; ++q)
+                    *reinterpret_cast<uint4*>(my_row + ((q ^ (lane & 7)) * 16)) =
+                        make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+                __syncwarp();
+                switch(p.act)
                 {
-                    float v[32];
-#pragma unroll
-                    for(int j = 0; j < 32; ++j)
-                    {
-                        const int64_t n = col + j;
-                        const bool n_ok = n < p.N;
-                        float x;
-                        if constexpr(IS_INT)
-                        {
-                            const int32_t a = static_cast<int32_t>(acc[j]);
-                            if(p.scale_mode == MGX_SCALE_NONE)
-                                x = static_cast<float>(a);
-                            else
-                            {
-                                const double s = p.scale_mode == MGX_SCALE_PER_COL
-                                                     ? (n_ok ? static_cast<double>(__ldg(p.scale + n)) : 0.0)
-                                                     : row_scale;
-                                x = static_cast<float>(static_cast<double>(a) * s);
-                            }
-                        }
-                        else
-                        {
-                            const float a = __uint_as_float(acc[j]);
-                            if(p.scale_mode == MGX_SCALE_NONE)
-                                x = a;
-                            else
-                            {
-                                const double s = p.scale_mode == MGX_SCALE_PER_COL
-                                                     ? (n_ok ? static_cast<double>(__ldg(p.scale + n)) : 0.0)
-                                                     : row_scale;
-                                x = static_cast<float>(static_cast<double>(a) * s);
-                            }
-                        }
-                        if(p.bias != nullptr and n_ok)
-                            x = __fadd_rn(x, __ldg(p.bias + n));
-                        x = apply_act(x, p.act);
-                        v[j] = x;
-                    }
-                    if(vec_ok and col + 32 <= p.N)
-                    {
-                        if constexpr(std::is_same<OutT, float>::value)
-                        {
-#pragma unroll
-                            for(int j = 0; j < 32; j += 4)
-                            {
-                                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                if(rrow != nullptr)
-                                {
-                                    const float4 q = *reinterpret_cast<const float4*>(rrow + col + j);
-                                    o.x = __fadd_rn(o.x, q.x);
-                                    o.y = __fadd_rn(o.y, q.y);
-                                    o.z = __fadd_rn(o.z, q.z);
-                                    o.w = __fadd_rn(o.w, q.w);
-                                }
-                                *reinterpret_cast<float4*>(drow + col + j) = o;
-                            }
-                        }
-                        else if constexpr(std::is_same<OutT, __half>::value)
-                        {
-#pragma unroll
-                            for(int j = 0; j < 32; j += 8)
-                            {
-                                if(rrow != nullptr)
-                                {
-                                    const uint4 q = *reinterpret_cast<const uint4*>(rrow + col + j);
-                                    const __half* qh = reinterpret_cast<const __half*>(&q);
-#pragma unroll
-                                    for(int e = 0; e < 8; ++e)
-                                        v[j + e] = __fadd_rn(v[j + e], __half2float(qh[e]));
-                                }
-                                uint4 o;
-                                __half2* oh = reinterpret_cast<__half2*>(&o);
-#pragma unroll
-                                for(int e = 0; e < 4; ++e)
-                                    oh[e] = __floats2half2_rn(v[j + 2 * e], v[j + 2 * e + 1]);
-                                *reinterpret_cast<uint4*>(drow + col + j) = o;
-                            }
-                        }
-                    }
-                    else
-                    {
-                        for(int j = 0; j < 32 and col + j < p.N; ++j)
-                        {
-                            float x = v[j];
-                            if constexpr(not std::is_same<OutT, int32_t>::value)
-                            {
-                                if(rrow != nullptr)
-                                    x = __fadd_rn(x, load_as_float<OutT>(rrow, col + j));
-                                if constexpr(std::is_same<OutT, float>::value)
-                                    drow[col + j] = x;
-                                else
-                                    drow[col + j] = __float2half_rn(x);
-                            }
-                        }
-                    }
+                case MGX_ACT_RELU: epi_store_chunk<IS_INT, OutT, MGX_ACT_RELU>(e, col, sc4, bi4); break;
+                case MGX_ACT_GELU_ERF: epi_store_chunk<IS_INT, OutT, MGX_ACT_GELU_ERF>(e, col, sc4, bi4); break;
+                case MGX_ACT_GELU_TANH: epi_store_chunk<IS_INT, OutT, MGX_ACT_GELU_TANH>(e, col, sc4, bi4); break;
+                case MGX_ACT_SILU: epi_store_chunk<IS_INT, OutT, MGX_ACT_SILU>(e, col, sc4, bi4); break;
+                default: epi_store_chunk<IS_INT, OutT, MGX_ACT_NONE>(e, col, sc4, bi4); break;
                 }
             }
             // all TMEM reads of this buffer are complete (wait::ld above)
@@ -435,6 +499,14 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
     if(rc != MGX_OK)
         return rc;
     qgemm_params p{};
+    constexpr int es = sizeof(OutT);
+    p.vec_sb = ((reinterpret_cast<uintptr_t>(scale) & 15u) == 0 and (reinterpret_cast<uintptr_t>(bias) & 15u) == 0) ? 1 : 0;
+    const int64_t valign = es == 4 ? 16 : 8; // bytes per lane in the coalesced store
+    p.vec_io = ((reinterpret_cast<uintptr_t>(D) % valign) == 0 and (d.ldd * es) % valign == 0 and
+                (d.batch == 1 or (d.stride_d * es) % valign == 0) and
+                (residual == nullptr or (reinterpret_cast<uintptr_t>(residual) % valign) == 0))
+                   ? 1
+                   : 0;
     p.M          = d.M;
     p.N          = d.N;
     p.K          = d.K;

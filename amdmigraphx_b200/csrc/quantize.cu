@@ -100,7 +100,8 @@ struct view2
     int64_t s0, s1;
 };
 
-// One thread = 4 consecutive columns of one row.
+// One work item = 4 consecutive columns of one row; every thread keeps UNROLL items
+// (UNROLL independent 16-byte loads) in flight per loop trip.
 template <class In, class Q>
 __global__ void __launch_bounds__(256)
     quantize_vec4_kernel(const In* __restrict__ x, int64_t ldx, const In* __restrict__ scale,
@@ -108,36 +109,56 @@ __global__ void __launch_bounds__(256)
                          typename Q::type* __restrict__ y, int64_t ldy, int64_t rows,
                          int64_t cols4)
 {
-    const int64_t total = rows * cols4;
-    for(int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
-        i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    constexpr int UNROLL = 4;
+    using vec_t          = typename std::conditional<std::is_same<In, float>::value, float4, uint2>::type;
+    const int64_t total  = rows * cols4;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for(int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < total;
+        i0 += stride * UNROLL)
     {
-        const int64_t r = i / cols4;
-        const int64_t c = (i - r * cols4) * 4;
-        float xv[4];
-        if constexpr(std::is_same<In, float>::value)
+        vec_t v[UNROLL];
+        int64_t rr[UNROLL], cc[UNROLL];
+#pragma unroll
+        for(int u = 0; u < UNROLL; ++u)
         {
-            const float4 v = *reinterpret_cast<const float4*>(x + r * ldx + c);
-            xv[0] = v.x, xv[1] = v.y, xv[2] = v.z, xv[3] = v.w;
+            const int64_t i = i0 + u * stride;
+            if(i < total)
+            {
+                rr[u] = i / cols4;
+                cc[u] = (i - rr[u] * cols4) * 4;
+                v[u]  = *reinterpret_cast<const vec_t*>(x + rr[u] * ldx + cc[u]);
+            }
         }
-        else
+#pragma unroll
+        for(int u = 0; u < UNROLL; ++u)
         {
-            const uint2 v    = *reinterpret_cast<const uint2*>(x + r * ldx + c);
-            const __half* vh = reinterpret_cast<const __half*>(&v);
+            const int64_t i = i0 + u * stride;
+            if(i >= total)
+                break;
+            const int64_t r = rr[u], c = cc[u];
+            float xv[4];
+            if constexpr(std::is_same<In, float>::value)
+            {
+                xv[0] = v[u].x, xv[1] = v[u].y, xv[2] = v[u].z, xv[3] = v[u].w;
+            }
+            else
+            {
+                const __half* vh = reinterpret_cast<const __half*>(&v[u]);
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                    xv[j] = __half2float(vh[j]);
+            }
+            uint32_t packed = 0;
 #pragma unroll
             for(int j = 0; j < 4; ++j)
-                xv[j] = __half2float(vh[j]);
+            {
+                const float s = to_f32<In>(scale[r * ss.s0 + (c + j) * ss.s1]);
+                const float z = zp == nullptr ? 0.0f : Q::zp(zp[r * zs.s0 + (c + j) * zs.s1]);
+                const uint32_t q = static_cast<uint8_t>(Q::template quant<In>(xv[j], s, z));
+                packed |= q << (8 * j);
+            }
+            *reinterpret_cast<uint32_t*>(y + r * ldy + c) = packed;
         }
-        uint32_t packed = 0;
-#pragma unroll
-        for(int j = 0; j < 4; ++j)
-        {
-            const float s = to_f32<In>(scale[r * ss.s0 + (c + j) * ss.s1]);
-            const float z = zp == nullptr ? 0.0f : Q::zp(zp[r * zs.s0 + (c + j) * zs.s1]);
-            const uint32_t q = static_cast<uint8_t>(Q::template quant<In>(xv[j], s, z));
-            packed |= q << (8 * j);
-        }
-        *reinterpret_cast<uint32_t*>(y + r * ldy + c) = packed;
     }
 }
 
@@ -179,7 +200,7 @@ static int launch_quantize(const void* x, int64_t ldx, const void* scale, view2 
     if(vec)
     {
         const int64_t n = rows * (cols / 4);
-        quantize_vec4_kernel<In, Q><<<grid_for(n, 256), 256, 0, stream>>>(
+        quantize_vec4_kernel<In, Q><<<grid_for(ceil_div(n, 4), 256), 256, 0, stream>>>(
             static_cast<const In*>(x), ldx, static_cast<const In*>(scale), ss,
             static_cast<const Out*>(zp), zs, static_cast<Out*>(y), ldy, rows, cols / 4);
     }
@@ -377,14 +398,16 @@ extern "C" int mgx_cuda_quantizelinear(const void* x, int x_type, int64_t ldx, c
                                        int64_t ldy, int64_t rows, int64_t cols, void* stream_)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(rows < 0 or cols < 0)
+        return MGX_E_INVALID_ARG;
+    if(rows == 0 or cols == 0)
+        return MGX_OK; // empty tensors may come with null pointers
     if(x == nullptr or scale == nullptr or y == nullptr or scale_strides == nullptr)
         return MGX_E_INVALID_ARG;
-    if(rows < 0 or cols < 0 or ldx < cols or ldy < cols)
+    if(ldx < cols or ldy < cols)
         return MGX_E_INVALID_ARG;
     if(zp != nullptr and zp_strides == nullptr)
         return MGX_E_INVALID_ARG;
-    if(rows == 0 or cols == 0)
-        return MGX_OK;
     const view2 ss{scale_strides[0], scale_strides[1]};
     const view2 zs = zp != nullptr ? view2{zp_strides[0], zp_strides[1]} : view2{0, 0};
 #define MGX_Q_CASE(IN, Q) return launch_quantize<IN, Q>(x, ldx, scale, ss, zp, zs, y, ldy, rows, cols, stream)
@@ -416,14 +439,16 @@ extern "C" int mgx_cuda_dequantizelinear(const void* x, int x_type, int64_t ldx,
                                          int64_t ldy, int64_t rows, int64_t cols, void* stream_)
 {
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(rows < 0 or cols < 0)
+        return MGX_E_INVALID_ARG;
+    if(rows == 0 or cols == 0)
+        return MGX_OK; // empty tensors may come with null pointers
     if(x == nullptr or scale == nullptr or y == nullptr or scale_strides == nullptr)
         return MGX_E_INVALID_ARG;
-    if(rows < 0 or cols < 0 or ldx < cols or ldy < cols)
+    if(ldx < cols or ldy < cols)
         return MGX_E_INVALID_ARG;
     if(zp != nullptr and zp_strides == nullptr)
         return MGX_E_INVALID_ARG;
-    if(rows == 0 or cols == 0)
-        return MGX_OK;
     const view2 ss{scale_strides[0], scale_strides[1]};
     const view2 zs = zp != nullptr ? view2{zp_strides[0], zp_strides[1]} : view2{0, 0};
     switch(x_type)

@@ -151,7 +151,11 @@ def main():
     gen_units = gen_files(ref, gen)
 
     src = os.path.join(ref, "src")
-    skip = {"msgpack.cpp", "sqlite.cpp"}
+    # msgpack.cpp / sqlite.cpp need third-party libraries that are absent (stubs above).
+    # fuse_attention.cpp / rewrite_gelu.cpp need tens of GB of compiler memory under
+    # g++ 13; only the HIP GPU target's pass list uses them (src/targets/gpu/target.cpp),
+    # nothing in the core library or the ref target references their symbols.
+    skip = {"msgpack.cpp", "sqlite.cpp", "fuse_attention.cpp", "rewrite_gelu.cpp"}
     core = [os.path.join(src, f) for f in sorted(os.listdir(src))
             if f.endswith(".cpp") and f not in skip]
     bdir = os.path.join(src, "op", "builder")
@@ -171,13 +175,8 @@ def main():
         return os.path.join(obj, os.path.basename(s)[:-4] + "_" + h + ".o")
 
     jobs = []
-    late = []
     for s in core + reft:
-        # these two need many GB and >10 min each at -O2 under g++ 13; nothing on the
-        # ref pipeline or the quantized path calls them, so they are compiled
-        # unoptimised, and after the others so that they do not compete for memory.
-        heavy = os.path.basename(s) in ("rewrite_gelu.cpp", "fuse_attention.cpp")
-        (late if heavy else jobs).append((s, objname(s), base + ["-O0" if heavy else "-O2"]))
+        jobs.append((s, objname(s), base + ["-O2"]))
     t0 = time.time()
     failed = []
     with cf.ThreadPoolExecutor(a.jobs) as ex:
@@ -187,13 +186,6 @@ def main():
                 print(f"[build_ref] FAILED {s}\n{err}", flush=True)
             elif dt > 0:
                 print(f"[build_ref] {i + 1}/{len(jobs)} {os.path.basename(s)} {dt:.0f}s", flush=True)
-    for j in late:
-        s, rc, err, dt = compile_one(j)
-        if rc != 0:
-            failed.append(s)
-            print(f"[build_ref] FAILED {s}\n{err}", flush=True)
-        elif dt > 0:
-            print(f"[build_ref] {os.path.basename(s)} {dt:.0f}s", flush=True)
     if failed:
         print(f"[build_ref] {len(failed)} translation units failed")
         return 1
@@ -207,6 +199,8 @@ def main():
     if not os.path.exists(libref) or os.path.getmtime(libref) < max(os.path.getmtime(o) for o in ref_objs + [libmgx]):
         subprocess.check_call(["g++", "-shared", "-o", libref] + ref_objs +
                               [f"-L{lib}", "-lmigraphx", "-Wl,-rpath,$ORIGIN", "-lpthread"])
+    # symbol tables of the template-heavy library are ~350 MB; the dynamic symbols stay
+    subprocess.call(["strip", "--strip-unneeded", libmgx, libref])
     print(f"[build_ref] done in {time.time() - t0:.0f}s -> {lib}")
     return 0
 

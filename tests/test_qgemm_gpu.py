@@ -135,9 +135,9 @@ def test_quant_dot_fp8(cuda_device, M, N, K):
     a_t = _t(aq, cuda_device).view(torch.float8_e4m3fn)
     b_t = _t(bq, cuda_device).view(torch.float8_e4m3fn)
     raw = capi.qgemm(a_t, b_t, out_dtype=torch.float32).cpu().numpy()
-    np.testing.assert_allclose(raw, acc, rtol=2e-2, atol=1e-2)
-    # fp32 accumulation of exactly representable products: far tighter in practice
-    assert np.max(np.abs(raw - acc)) <= 1e-3 * max(1.0, np.abs(acc).max())
+    # un-dequantised accumulators are O(1e5..1e6) here: fp32 accumulation of exact
+    # products differs from the oracle's double accumulation only by summation rounding
+    assert np.max(np.abs(raw - acc)) <= 2e-6 * np.abs(acc).max()
     got = capi.qgemm(a_t, b_t, scale=_t(scale, cuda_device), bias=_t(bias, cuda_device),
                      act="gelu_erf", out_dtype=torch.float32).cpu().numpy()
     np.testing.assert_allclose(got, ref, rtol=2e-2, atol=1e-2)
