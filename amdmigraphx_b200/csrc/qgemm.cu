@@ -158,6 +158,15 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                 v[j] = apply_act<ACT>(x);
             }
             const bool full = p.vec_io and c4 + 4 <= p.N;
+            if constexpr(std::is_same<OutT, __half>::value)
+            {
+                // fp16 model: the reference converts to half by truncating the mantissa
+                // (src/include/migraphx/generic_float.hpp:180-230); a following add is a
+                // half operation = fp32 add + the same truncating conversion
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                    v[j] = __half2float(__float2half_rz(v[j]));
+            }
             if(p.residual != nullptr)
             {
                 const OutT* res = static_cast<const OutT*>(p.residual) + e.batch_off + row * p.ldd + c4;
@@ -202,15 +211,15 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                 if(full)
                 {
                     uint2 o;
-                    __half2 h0 = __floats2half2_rn(v[0], v[1]);
-                    __half2 h1 = __floats2half2_rn(v[2], v[3]);
+                    __half2 h0 = __halves2half2(__float2half_rz(v[0]), __float2half_rz(v[1]));
+                    __half2 h1 = __halves2half2(__float2half_rz(v[2]), __float2half_rz(v[3]));
                     o.x        = *reinterpret_cast<uint32_t*>(&h0);
                     o.y        = *reinterpret_cast<uint32_t*>(&h1);
                     *reinterpret_cast<uint2*>(dst) = o;
                 }
                 else
                     for(int j = 0; j < 4 and c4 + j < p.N; ++j)
-                        dst[j] = __float2half_rn(v[j]);
+                        dst[j] = __float2half_rz(v[j]);
             }
         }
     }

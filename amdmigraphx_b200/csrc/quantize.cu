@@ -28,9 +28,9 @@ __device__ __forceinline__ float to_f32<__half>(__half v)
 }
 
 // x / s evaluated in the input type (the reference divides `input[i] / scales[i]`
-// in the tensor's own type for integer targets).  For fp16 the quotient is
-// rounded to fp16: a correctly rounded fp32 quotient rounded again to fp16
-// equals the correctly rounded fp16 quotient (24 >= 2*11 + 2 bits).
+// in the tensor's own type for integer targets).  migraphx::half divides in fp32 and
+// converts the quotient back by shifting the mantissa, i.e. rounding toward zero
+// (src/include/migraphx/generic_float.hpp:180-230, 321-329).
 template <class T>
 __device__ __forceinline__ float div_in_type(float x, float s);
 template <>
@@ -41,7 +41,7 @@ __device__ __forceinline__ float div_in_type<float>(float x, float s)
 template <>
 __device__ __forceinline__ float div_in_type<__half>(float x, float s)
 {
-    return __half2float(__float2half_rn(__fdiv_rn(x, s)));
+    return __half2float(__float2half_rz(__fdiv_rn(x, s)));
 }
 
 struct q_i8
@@ -249,7 +249,8 @@ __global__ void __launch_bounds__(256)
         if constexpr(std::is_same<S, float>::value)
             y[r * ldy + c] = static_cast<float>(d);
         else
-            y[r * ldy + c] = __double2half(d);
+            // double -> float (nearest) -> half (toward zero), as migraphx::half converts
+            y[r * ldy + c] = __float2half_rz(static_cast<float>(d));
     }
 }
 

@@ -199,6 +199,12 @@ def main():
     if not os.path.exists(libref) or os.path.getmtime(libref) < max(os.path.getmtime(o) for o in ref_objs + [libmgx]):
         subprocess.check_call(["g++", "-shared", "-o", libref] + ref_objs +
                               [f"-L{lib}", "-lmigraphx", "-Wl,-rpath,$ORIGIN", "-lpthread"])
+    # our own C-ABI window onto the ref target (oracle/ref_oracle.cpp)
+    tool_src = os.path.join(HERE, "ref_oracle.cpp")
+    tool = os.path.join(lib, "libmgx_ref_oracle.so")
+    if not os.path.exists(tool) or os.path.getmtime(tool) < max(os.path.getmtime(tool_src), os.path.getmtime(libref)):
+        subprocess.check_call(["g++", "-shared", "-O2", "-o", tool, tool_src] + base +
+                              [f"-L{lib}", "-Wl,--no-as-needed", "-lmigraphx_ref", "-lmigraphx", "-Wl,-rpath,$ORIGIN"])
     # symbol tables of the template-heavy library are ~350 MB; the dynamic symbols stay
     subprocess.call(["strip", "--strip-unneeded", libmgx, libref])
     print(f"[build_ref] done in {time.time() - t0:.0f}s -> {lib}")

@@ -59,6 +59,22 @@ def fp8e4m3fn_encode(x):
     return (code | sign).astype(np.uint8)
 
 
+# ----------------------------------------------------------------------------- fp16
+def half_trunc(x):
+    """float -> float16 the way migraphx::half does it: the float32 mantissa is shifted
+    right, i.e. rounded TOWARD ZERO, not to nearest; float exponents beyond the half range
+    give infinity (src/include/migraphx/generic_float.hpp:180-230).  A double is first
+    converted to float32 (round to nearest) by the language."""
+    x = np.asarray(x).astype(np.float32)
+    with np.errstate(over="ignore"):
+        h = x.astype(np.float16)  # round to nearest even
+    hf = h.astype(np.float32)
+    over = (np.abs(hf) > np.abs(x)) & (np.abs(x) < 65536.0)
+    bits = h.view(np.uint16).copy()
+    bits[over] -= 1  # one step toward zero on the sign-magnitude pattern
+    return bits.view(np.float16).reshape(x.shape)
+
+
 # ----------------------------------------------------------------------------- quantizelinear
 def quantizelinear(x, scale, zp=None, out_type="int8"):
     """src/include/migraphx/op/quantizelinear.hpp:71-108.
@@ -74,7 +90,12 @@ def quantizelinear(x, scale, zp=None, out_type="int8"):
         lo, hi = (-128.0, 127.0) if out_type == "int8" else (0.0, 255.0)
         z = np.zeros(x.shape) if zp is None else np.broadcast_to(np.asarray(zp), x.shape).astype(np.float64)
         with np.errstate(divide="ignore", invalid="ignore", over="ignore"):
-            q = x / scale  # in x's own dtype (float32 or float16)
+            if x.dtype == np.float16:
+                # half / half = half(float(a) / float(b)) with the truncating conversion
+                # (generic_float.hpp:321-329)
+                q = half_trunc(x.astype(np.float32) / scale.astype(np.float32))
+            else:
+                q = x / scale
         q = np.rint(q.astype(np.float64)) + z
         # std::max(min, std::min(max, q)) : a NaN q ends up at max
         q = np.where(np.isnan(q), hi, q)
@@ -103,7 +124,10 @@ def dequantizelinear(x, scale, zp=None, x_is_fp8=False):
     else:
         zv = fp8e4m3fn_decode(zp).astype(np.float64) if x_is_fp8 else np.asarray(zp).astype(np.float64)
     s = np.broadcast_to(scale, xv.shape).astype(np.float64)
-    return ((xv - zv) * s).astype(scale.dtype)
+    y = (xv - zv) * s
+    if scale.dtype == np.float16:
+        return half_trunc(y)  # double -> float (nearest) -> half (toward zero)
+    return y.astype(scale.dtype)
 
 
 # ----------------------------------------------------------------------------- int4
@@ -154,20 +178,34 @@ def quant_dot_fp8(a_codes, b_codes):
 
 
 # ----------------------------------------------------------------------------- pointwise pieces
-def _erf(x):
-    from math import erf
-    return np.vectorize(erf, otypes=[np.float64])(x)
+_LIBM = None
+
+
+def _erff(x):
+    """erf evaluated by the C library's single-precision erff, which is what the erf
+    operator's std::erf(float) resolves to on the ref target
+    (src/include/migraphx/op/erf.hpp); it is not correctly rounded, so a double-precision
+    erf rounded to float would differ in the last bit for some inputs."""
+    global _LIBM
+    import ctypes
+    import ctypes.util
+    if _LIBM is None:
+        _LIBM = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+        _LIBM.erff.restype = ctypes.c_float
+        _LIBM.erff.argtypes = [ctypes.c_float]
+    x = np.asarray(x, dtype=np.float32)
+    f = _LIBM.erff
+    return np.fromiter((f(float(v)) for v in x.ravel()), dtype=np.float32, count=x.size).reshape(x.shape)
 
 
 def gelu_erf(x):
-    """(x*0.5) * (erf(x / sqrt(2)) + 1) evaluated op by op in x's type
+    """(x*0.5) * (erf(x / sqrt(2)) + 1) evaluated op by op in float32
     (src/op/builder/gelu.cpp:58-74)."""
-    x = np.asarray(x)
-    t = x.dtype
-    half = (x * t.type(0.5)).astype(t)
-    d = (x / t.type(np.float32(np.sqrt(2.0)))).astype(t)
-    e = _erf(d.astype(np.float64)).astype(t)
-    return (half * (e + t.type(1.0)).astype(t)).astype(t)
+    x = np.asarray(x, dtype=np.float32)
+    half = (x * np.float32(0.5)).astype(np.float32)
+    d = (x / np.float32(np.sqrt(2.0))).astype(np.float32)
+    e = _erff(d)
+    return (half * (e + np.float32(1.0)).astype(np.float32)).astype(np.float32)
 
 
 def apply_act(x, act):
@@ -199,6 +237,12 @@ def qlinear_epilogue(acc, scale=None, bias=None, act=None, residual=None, out_dt
     if bias is not None:
         v = (v + np.asarray(bias, dtype=np.float32)).astype(np.float32)
     v = apply_act(v, act)
+    if np.dtype(out_dtype) == np.float16:
+        # fp16 model: convert (truncating, see half_trunc) and then add in half arithmetic
+        v = half_trunc(v)
+        if residual is not None:
+            v = half_trunc(v.astype(np.float32) + np.asarray(residual).astype(np.float32))
+        return v
     if residual is not None:
         v = (v + np.asarray(residual).astype(np.float32)).astype(np.float32)
     return v.astype(out_dtype)
@@ -207,7 +251,8 @@ def qlinear_epilogue(acc, scale=None, bias=None, act=None, residual=None, out_dt
 # ----------------------------------------------------------------------------- weight-only int4
 def w4a16_dequant_weights(bp, scales, zp=None, zp_const=8, group=128):
     """unpack_int4 + dequantizelinear to fp16 as src/onnx/parse_matmulnbits.cpp:85-158
-    builds them: W[n,k] = fp16((q[n,k] - zp[n,k/group]) * s[n,k/group])."""
+    builds them: W[n,k] = half((q[n,k] - zp[n,k/group]) * s[n,k/group]), with MIGraphX's
+    truncating float -> half conversion."""
     q = unpack_int4(bp).astype(np.float64)  # [N, K]
     n, k = q.shape
     s = np.repeat(np.asarray(scales, dtype=np.float16).reshape(n, k // group), group, axis=1)
@@ -215,14 +260,14 @@ def w4a16_dequant_weights(bp, scales, zp=None, zp_const=8, group=128):
         z = float(zp_const)
     else:
         z = np.repeat(np.asarray(zp).reshape(n, k // group), group, axis=1).astype(np.float64)
-    return ((q - z) * s.astype(np.float64)).astype(np.float16)
+    return half_trunc((q - z) * s.astype(np.float64))
 
 
 def w4a16_linear(a, bp, scales, zp=None, zp_const=8, group=128, act=None):
     """dot(A_fp16[M,K], transpose(W_fp16[N,K])) with gemm_naive's double accumulation
-    and one rounding to fp16 (src/gemm.cpp:55-61)."""
+    and one (truncating) conversion to half (src/gemm.cpp:55-61)."""
     w = w4a16_dequant_weights(bp, scales, zp, zp_const, group)
     acc = np.matmul(np.asarray(a, dtype=np.float16).astype(np.float64), w.astype(np.float64).T)
     if act not in (None, "none"):
         acc = apply_act(acc.astype(np.float32), act).astype(np.float64)
-    return acc.astype(np.float16)
+    return half_trunc(acc)

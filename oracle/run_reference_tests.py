@@ -1,0 +1,75 @@
+#!/usr/bin/env python3
+"""Compile the reference's OWN golden tests for the quantized path, where they lie, against
+the oracle build (oracle/_ref/lib) and run them.  This checks that the locally built
+MIGraphX `ref` target - the thing the numpy restatement is pinned to - reproduces every
+known-answer vector the reference ships for this path:
+
+  test/ref/quantizelinear.cpp, dequantizelinear.cpp, unpack_int4.cpp, pack_int4.cpp,
+  pack_unpack_int4.cpp, dot_op.cpp (dot and quant_dot cases)
+
+Nothing is copied; the executable goes to oracle/_ref/bin/.  The pass/fail summary is
+written to tests/golden/reference_test_run.txt.
+
+Usage: python oracle/run_reference_tests.py [--ref /root/reference]
+"""
+import argparse
+import concurrent.futures as cf
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import build_ref  # noqa: E402
+
+FILES = ["quantizelinear.cpp", "dequantizelinear.cpp", "unpack_int4.cpp", "pack_int4.cpp",
+         "pack_unpack_int4.cpp", "dot_op.cpp", "main.cpp"]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    a = ap.parse_args()
+    out = os.path.join(HERE, "_ref")
+    lib, gen, obj = (os.path.join(out, d) for d in ("lib", "gen", "obj"))
+    bindir = os.path.join(out, "bin")
+    os.makedirs(bindir, exist_ok=True)
+    tdir = os.path.join(a.ref, "test", "ref")
+    flags = ["-std=c++17", "-O1", "-w", "-pthread", "-DMIGRAPHX_USE_EIGEN=0",
+             f"-I{gen}/include", f"-I{a.ref}/src/include", f"-I{a.ref}/test/include",
+             f"-I{a.ref}/src/targets/ref/include"]
+
+    def cc(f):
+        o = os.path.join(obj, "reftest_" + f[:-4] + ".o")
+        src = os.path.join(tdir, f)
+        if not os.path.exists(o) or os.path.getmtime(o) < os.path.getmtime(src):
+            subprocess.check_call(["g++", "-c", src, "-o", o] + flags)
+        return o
+
+    with cf.ThreadPoolExecutor(4) as ex:
+        objs = list(ex.map(cc, FILES))
+    exe = os.path.join(bindir, "ref_tests")
+    subprocess.check_call(["g++", "-o", exe] + objs + [f"-L{lib}", "-Wl,--no-as-needed",
+                                                        "-lmigraphx_ref", "-lmigraphx",
+                                                        f"-Wl,-rpath,{lib}", "-lpthread"])
+    r = subprocess.run([exe], capture_output=True, text=True)
+    text = r.stdout + r.stderr
+    lines = text.strip().splitlines()
+    ran = [l for l in lines if "[   RUN    ]" in l or "RUN" in l]
+    failed = [l for l in lines if "FAILED" in l]
+    summary = [
+        "Reference golden tests (test/ref: " + ", ".join(FILES[:-1]) + ")",
+        "run against oracle/_ref/lib (MIGraphX core + ref target built by oracle/build_ref.py)",
+        "command: python oracle/run_reference_tests.py",
+        f"exit code: {r.returncode}",
+        f"test cases run: {len(ran)}",
+        f"lines containing FAILED: {len(failed)}",
+    ] + failed[:50] + ["", "tail of output:"] + lines[-8:]
+    with open(os.path.join(os.path.dirname(HERE), "tests", "golden", "reference_test_run.txt"), "w") as f:
+        f.write("\n".join(summary) + "\n")
+    print("\n".join(summary))
+    return r.returncode
+
+
+if __name__ == "__main__":
+    sys.exit(main())

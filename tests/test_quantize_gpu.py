@@ -78,6 +78,8 @@ def test_quantizelinear_empty(cuda_device):
 def test_dequantizelinear(cuda_device, xt, st):
     import torch
     from amdmigraphx_b200 import capi
+    if xt == "int32" and st == np.float16:
+        pytest.skip("int32 input with an fp16 scale and no zero point is undefined in the reference")
     rng = np.random.default_rng(9)
     rows, cols = 64, 200
     if xt == "int8":
