@@ -1,0 +1,124 @@
+"""Synthetic workloads of the quantized-GEMM path, assembled from C-ABI calls.
+
+BertInt8LinearStack is the QDQ-linear part of a BERT-base-shaped int8 encoder stack
+(12 layers, hidden 768, FFN 3072, tokens = batch x 384): per layer four quantizelinear
+launches and four quant_dot launches whose epilogues carry dequantizelinear (per-tensor
+activation scale x per-channel weight scale), bias, erf-GELU (FFN1) or the residual add
+(O-proj, FFN2).  The Q/K/V projections share their input and are issued as one quant_dot
+with the three weight matrices concatenated along N, the horizontal fusion MIGraphX
+applies to dots with a common input.  Attention scores/softmax and LayerNorm are not part
+of this stack: the chain stays data dependent by feeding the Q slice of the QKV output
+forward.
+
+Weights are random int8 with per-output-channel scales, stored [N, K] (K contiguous), the
+layout the `cuda` target gives constant weights at finalize time.
+"""
+import numpy as np
+
+from . import capi
+
+
+class QLinear(object):
+    """One QDQ linear: y = act(dequant(quant_dot(quantizelinear(x), W)) + bias) (+ residual)."""
+
+    def __init__(self, rng, k, n, device, act_scale=0.02, act=None):
+        import torch
+        self.k, self.n, self.act = k, n, act
+        w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        w_scale = rng.uniform(0.001, 0.01, size=n).astype(np.float32)
+        x_scale = np.array([act_scale], dtype=np.float32)
+        self.w_nk_host = w
+        self.w = torch.from_numpy(w).to(device)                      # [N, K]
+        self.x_scale = torch.from_numpy(x_scale).to(device)
+        # the scale literal simplify_qdq leaves: mul(bcast(x_scale), bcast(w_scale)) in fp32
+        self.scale_host = (x_scale * w_scale).astype(np.float32)
+        self.scale = torch.from_numpy(self.scale_host).to(device)
+        self.bias_host = rng.normal(0, 0.1, size=n).astype(np.float32)
+        self.bias = torch.from_numpy(self.bias_host).to(device)
+        self.x_scale_host = x_scale
+
+    def ops(self, m):
+        return 2 * m * self.n * self.k
+
+
+class BertInt8LinearStack(object):
+    def __init__(self, device, layers=12, hidden=768, ffn=3072, tokens=3072, seed=0):
+        import torch
+        rng = np.random.default_rng(seed)
+        self.device, self.tokens, self.hidden, self.ffn = device, tokens, hidden, ffn
+        self.layers = []
+        for _ in range(layers):
+            self.layers.append({
+                "qkv": QLinear(rng, hidden, 3 * hidden, device),
+                "o": QLinear(rng, hidden, hidden, device),
+                "ffn1": QLinear(rng, hidden, ffn, device, act="gelu_erf"),
+                "ffn2": QLinear(rng, ffn, hidden, device, act_scale=0.01),
+            })
+        t = tokens
+        f16 = dict(dtype=torch.float16, device=device)
+        i8 = dict(dtype=torch.int8, device=device)
+        self.x = torch.empty((t, hidden), **f16)
+        self.xq = torch.empty((t, hidden), **i8)
+        self.qkv = torch.empty((t, 3 * hidden), **f16)
+        self.cq = torch.empty((t, hidden), **i8)
+        self.o = torch.empty((t, hidden), **f16)
+        self.oq = torch.empty((t, hidden), **i8)
+        self.h = torch.empty((t, ffn), **f16)
+        self.hq = torch.empty((t, ffn), **i8)
+        self.y = torch.empty((t, hidden), **f16)
+        self.gemm_events = None  # optional list collecting (start, end, ops) per quant_dot
+
+    # -- bookkeeping ---------------------------------------------------------------------
+    def ops_per_step(self):
+        return sum(l.ops(self.tokens) for layer in self.layers for l in layer.values())
+
+    def launches_per_step(self):
+        return len(self.layers) * 8
+
+    def weight_bytes(self):
+        return sum(l.w.numel() for layer in self.layers for l in layer.values())
+
+    # -- one QDQ linear through the C ABI --------------------------------------------------
+    def _quant(self, x, xq, lin):
+        lib = capi.load()
+        import ctypes
+        rows, cols = x.shape
+        st = (ctypes.c_int64 * 2)(0, 0)
+        capi.check(lib.mgx_cuda_quantizelinear(
+            ctypes.c_void_p(x.data_ptr()), capi.F16, x.stride(0), ctypes.c_void_p(lin.x_scale_f16.data_ptr()),
+            st, None, None, ctypes.c_void_p(xq.data_ptr()), capi.I8, xq.stride(0), rows, cols,
+            capi._stream()), "mgx_cuda_quantizelinear")
+
+    def _gemm(self, xq, lin, out, residual=None):
+        if self.gemm_events is not None:
+            import torch
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+        capi.qgemm(xq, lin.w, b_layout=capi.B_NK, scale=lin.scale, scale_mode=capi.SCALE_PER_COL,
+                   bias=lin.bias, act=lin.act, residual=residual, out=out)
+        if self.gemm_events is not None:
+            e.record()
+            self.gemm_events.append((s, e, lin.ops(xq.shape[0])))
+
+    def prepare(self):
+        """fp16 copies of the activation scales (quantizelinear takes its scale in x's type)."""
+        import torch
+        for layer in self.layers:
+            for lin in layer.values():
+                lin.x_scale_f16 = lin.x_scale.to(torch.float16)
+
+    def step(self, x_in=None):
+        """One pass over the stack; returns the last layer's output [tokens, hidden] fp16."""
+        x = self.x if x_in is None else x_in
+        for layer in self.layers:
+            self._quant(x, self.xq, layer["qkv"])
+            self._gemm(self.xq, layer["qkv"], self.qkv)
+            ctx = self.qkv[:, : self.hidden]  # stand-in for the attention context (row stride 3*hidden)
+            self._quant(ctx, self.cq, layer["o"])
+            self._gemm(self.cq, layer["o"], self.o, residual=x if x.stride(0) == self.o.stride(0) else None)
+            self._quant(self.o, self.oq, layer["ffn1"])
+            self._gemm(self.oq, layer["ffn1"], self.h)
+            self._quant(self.h, self.hq, layer["ffn2"])
+            self._gemm(self.hq, layer["ffn2"], self.y, residual=self.o)
+            x = self.y
+        return self.y
