@@ -10,9 +10,9 @@
 // double(x) * scale, one rounding to fp32), then add, then the activation, each
 // as a separate fp32 operation like the un-fused instructions.
 //
-// CTA = 192 threads: warp 0 = TMA producer (one lane), warp 1 = tensor-memory
-// owner + MMA issuer (one lane), warps 2..5 = epilogue (each owns the TMEM lane
-// quarter warp_id % 4).  Two accumulator buffers of BN columns let the epilogue
+// CTA = 576 threads: warp 0 = TMA producer (one lane), warp 1 = tensor-memory
+// owner + MMA issuer (one lane), warps 2..17 = epilogue (each owns the TMEM lane
+// quarter warp_id % 4 and a quarter of the tile's columns).  Two accumulator buffers of BN columns let the epilogue
 // of tile i overlap the main loop of tile i+1.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -23,8 +23,9 @@ namespace mgx {
 constexpr int BM        = 128; // rows of D per tile (UMMA M, one TMEM lane per row)
 constexpr int BK        = 128; // bytes (= 8-bit elements) of K per pipeline stage
 constexpr int UMMA_K    = 32;  // K per tcgen05.mma for 8-bit operands
-constexpr int EPI_WARPS = 8;   // two per TMEM lane quarter, each takes half of the columns
+constexpr int EPI_WARPS = 16;  // four per TMEM lane quarter, each takes a quarter of the columns
 constexpr int NTHREADS  = 64 + 32 * EPI_WARPS;
+constexpr int EPI_COLS  = 16;  // columns per epilogue chunk (one tcgen05.ld.32x32b.x16)
 
 struct qgemm_params
 {
@@ -50,10 +51,26 @@ struct qgemm_smem
     static constexpr int b_bytes     = BN * BK;
     static constexpr int stage_bytes = a_bytes + b_bytes;
     static constexpr int stages      = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
-    static constexpr int epi_bytes   = EPI_WARPS * 32 * 128; // 32 rows x 32 words per epilogue warp
+    static constexpr int epi_bytes   = EPI_WARPS * 32 * EPI_COLS * 4; // 32 rows x 16 words per warp
     static constexpr int bar_bytes   = 256;
     static constexpr int total = stages * stage_bytes + epi_bytes + bar_bytes + 1024; // + alignment slack
 };
+
+// erf by Abramowitz & Stegun 7.1.26 (|error| <= 1.5e-7 + fp32 rounding): one reciprocal,
+// one exponential, five fused multiply-adds.  GELU uses erf only through 1 + erf(.), so
+// an absolute error of this size is below fp32 resolution of the result.
+__device__ __forceinline__ float fast_erf(float x)
+{
+    const float ax = fabsf(x);
+    const float t  = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    float y        = fmaf(1.061405429f, t, -1.453152027f);
+    y              = fmaf(y, t, 1.421413741f);
+    y              = fmaf(y, t, -0.284496736f);
+    y              = fmaf(y, t, 0.254829592f);
+    y *= t;
+    const float r = fmaf(-y, __expf(-ax * ax), 1.0f);
+    return copysignf(r, x);
+}
 
 template <int ACT>
 __device__ __forceinline__ float apply_act(float v)
@@ -62,15 +79,14 @@ __device__ __forceinline__ float apply_act(float v)
         return fmaxf(v, 0.0f);
     else if constexpr(ACT == MGX_ACT_GELU_ERF)
         // (x*0.5) * (erf(x / sqrt(2)) + 1): operation order of src/op/builder/gelu.cpp:58-74
-        return __fmul_rn(__fmul_rn(v, 0.5f),
-                         __fadd_rn(erff(__fdiv_rn(v, 1.41421356237309504880f)), 1.0f));
+        return __fmul_rn(__fmul_rn(v, 0.5f), __fadd_rn(fast_erf(v * 0.70710678118654752440f), 1.0f));
     else if constexpr(ACT == MGX_ACT_GELU_TANH)
     {
         float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
         return 0.5f * v * (1.0f + tanhf(u));
     }
     else if constexpr(ACT == MGX_ACT_SILU)
-        return v / (1.0f + expf(-v));
+        return v / (1.0f + __expf(-v));
     else
         return v;
 }
@@ -95,37 +111,40 @@ __device__ __forceinline__ float dequant_i32(int32_t acc, float s)
 struct epi_ctx
 {
     const qgemm_params* p;
-    uint8_t* box;      // this warp's 32 x 128-byte staging area (16-byte pieces XOR-swizzled by row)
+    uint8_t* box;      // this warp's 32 x 64-byte staging area (16-byte pieces XOR-swizzled by row)
     int lane;
     int64_t row0;      // global row of staging row 0
     int64_t batch_off; // b * stride_d
 };
 
-// Second half of the epilogue for one 32-column chunk: read the raw accumulators back
-// from shared memory so that 8 consecutive lanes cover one 128-byte row segment, apply
+// Second half of the epilogue for one 16-column chunk: read the raw accumulators back
+// from shared memory so that 4 consecutive lanes cover one 64-byte row segment, apply
 // dequantizelinear / bias / activation / residual, convert and store coalesced.
 template <bool IS_INT, class OutT, int ACT>
 __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, float4 sc4, float4 bi4)
 {
     const qgemm_params& p = *e.p;
-    const int pc          = e.lane & 7;  // which 4-column piece of the chunk this lane owns
-    const int rsub        = e.lane >> 3; // row within a group of 4
+    const int pc          = e.lane & 3;  // which 4-column piece of the chunk this lane owns
+    const int rsub        = e.lane >> 2; // row within a group of 8
     const int64_t c4      = col + pc * 4;
     const float sc[4]     = {sc4.x, sc4.y, sc4.z, sc4.w};
     const float bi[4]     = {bi4.x, bi4.y, bi4.z, bi4.w};
-#pragma unroll
-    for(int it = 0; it < 8; ++it)
+    const bool full       = p.vec_io and c4 + 4 <= p.N;
+    const bool has_bias   = p.bias != nullptr;
+#pragma unroll 1
+    for(int it = 0; it < 4; ++it)
     {
-        const int r       = it * 4 + rsub;
+        const int r       = it * 8 + rsub;
         const int64_t row = e.row0 + r;
-        const uint4 w     = *reinterpret_cast<const uint4*>(e.box + r * 128 + ((pc ^ (r & 7)) * 16));
+        const uint4 w =
+            *reinterpret_cast<const uint4*>(e.box + r * 64 + ((pc ^ ((r >> 1) & 3)) * 16));
         if(row >= p.M or c4 >= p.N)
             continue;
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
         OutT* dst = static_cast<OutT*>(p.D) + e.batch_off + row * p.ldd + c4;
         if constexpr(std::is_same<OutT, int32_t>::value)
         {
-            if(p.vec_io and c4 + 4 <= p.N)
+            if(full)
                 *reinterpret_cast<uint4*>(dst) = w;
             else
                 for(int j = 0; j < 4 and c4 + j < p.N; ++j)
@@ -153,38 +172,29 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                     if(p.scale_mode != MGX_SCALE_NONE)
                         x = __fmul_rn(x, s);
                 }
-                if(p.bias != nullptr)
+                if(has_bias)
                     x = __fadd_rn(x, bi[j]);
                 v[j] = apply_act<ACT>(x);
             }
-            const bool full = p.vec_io and c4 + 4 <= p.N;
-            if constexpr(std::is_same<OutT, __half>::value)
-            {
-                // fp16 model: the reference converts to half by truncating the mantissa
-                // (src/include/migraphx/generic_float.hpp:180-230); a following add is a
-                // half operation = fp32 add + the same truncating conversion
-#pragma unroll
-                for(int j = 0; j < 4; ++j)
-                    v[j] = __half2float(__float2half_rz(v[j]));
-            }
             if(p.residual != nullptr)
             {
-                const OutT* res = static_cast<const OutT*>(p.residual) + e.batch_off + row * p.ldd + c4;
+                const OutT* res =
+                    static_cast<const OutT*>(p.residual) + e.batch_off + row * p.ldd + c4;
+                float q[4] = {0.f, 0.f, 0.f, 0.f};
                 if(full)
                 {
                     if constexpr(std::is_same<OutT, float>::value)
                     {
-                        const float4 q = *reinterpret_cast<const float4*>(res);
-                        v[0] = __fadd_rn(v[0], q.x), v[1] = __fadd_rn(v[1], q.y);
-                        v[2] = __fadd_rn(v[2], q.z), v[3] = __fadd_rn(v[3], q.w);
+                        const float4 t = *reinterpret_cast<const float4*>(res);
+                        q[0] = t.x, q[1] = t.y, q[2] = t.z, q[3] = t.w;
                     }
                     else
                     {
-                        const uint2 q    = *reinterpret_cast<const uint2*>(res);
-                        const __half* qh = reinterpret_cast<const __half*>(&q);
+                        const uint2 t    = *reinterpret_cast<const uint2*>(res);
+                        const __half* th = reinterpret_cast<const __half*>(&t);
 #pragma unroll
                         for(int j = 0; j < 4; ++j)
-                            v[j] = __fadd_rn(v[j], __half2float(qh[j]));
+                            q[j] = __half2float(th[j]);
                     }
                 }
                 else
@@ -192,10 +202,19 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                     for(int j = 0; j < 4 and c4 + j < p.N; ++j)
                     {
                         if constexpr(std::is_same<OutT, float>::value)
-                            v[j] = __fadd_rn(v[j], res[j]);
+                            q[j] = res[j];
                         else
-                            v[j] = __fadd_rn(v[j], __half2float(res[j]));
+                            q[j] = __half2float(res[j]);
                     }
+                }
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                {
+                    // fp16 model: the reference converts to half by truncating the mantissa
+                    // (src/include/migraphx/generic_float.hpp:180-230) before the half add
+                    if constexpr(std::is_same<OutT, __half>::value)
+                        v[j] = __half2float(__float2half_rz(v[j]));
+                    v[j] = __fadd_rn(v[j], q[j]);
                 }
             }
             if constexpr(std::is_same<OutT, float>::value)
@@ -209,19 +228,124 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
             else
             {
                 if(full)
-                {
-                    uint2 o;
-                    __half2 h0 = __halves2half2(__float2half_rz(v[0]), __float2half_rz(v[1]));
-                    __half2 h1 = __halves2half2(__float2half_rz(v[2]), __float2half_rz(v[3]));
-                    o.x        = *reinterpret_cast<uint32_t*>(&h0);
-                    o.y        = *reinterpret_cast<uint32_t*>(&h1);
-                    *reinterpret_cast<uint2*>(dst) = o;
-                }
+                    *reinterpret_cast<uint2*>(dst) =
+                        make_uint2(cvt_rz_f16x2(v[0], v[1]), cvt_rz_f16x2(v[2], v[3]));
                 else
                     for(int j = 0; j < 4 and c4 + j < p.N; ++j)
                         dst[j] = __float2half_rz(v[j]);
             }
         }
+    }
+}
+
+// The epilogue role, one instantiation per activation so that the code a warp executes is
+// one contiguous region (the activation is chosen once per kernel, not per element).
+// Each warp owns TMEM lane quarter (warp % 4) = 32 rows of the tile, and a quarter of the
+// tile's columns.  Per 16-column chunk: tcgen05.ld (one row per thread) -> swizzled shared
+// memory -> read back with 4 lanes per 64-byte row segment -> dequantizelinear / bias /
+// activation / residual -> coalesced global stores.
+template <int BN, bool IS_INT, class OutT, int ACT>
+__device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* epi_base,
+                                              uint64_t* accf_bar, uint64_t* acce_bar,
+                                              volatile uint32_t* abort_flag, uint32_t tmem_base,
+                                              int warp, int lane, int64_t first_tile,
+                                              int64_t tile_step, int64_t tiles_mn)
+{
+    const int ew      = warp - 2;
+    const int quarter = warp & 3;
+    const int slice   = ew >> 2;
+    constexpr int COLS_PER_WARP = BN / 4;
+    constexpr int NCHUNK        = COLS_PER_WARP / EPI_COLS;
+    epi_ctx e;
+    e.p    = &p;
+    e.box  = epi_base + ew * (32 * EPI_COLS * 4);
+    e.lane = lane;
+    uint8_t* my_row    = e.box + lane * 64;
+    const int my_swz   = (lane >> 1) & 3;
+    const bool per_col = p.scale_mode == MGX_SCALE_PER_COL;
+    const float tensor_scale = p.scale_mode == MGX_SCALE_PER_TENSOR ? __ldg(p.scale) : 1.0f;
+    uint32_t lt = 0;
+    for(int64_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt)
+    {
+        const int b     = static_cast<int>(t / tiles_mn);
+        const int r     = static_cast<int>(t % tiles_mn);
+        const int m_blk = r % p.tiles_m;
+        const int n_blk = r / p.tiles_m;
+        const uint32_t buf = lt & 1u;
+        const int64_t col0 = static_cast<int64_t>(n_blk) * BN + slice * COLS_PER_WARP;
+        e.row0      = static_cast<int64_t>(m_blk) * BM + quarter * 32;
+        e.batch_off = b * p.stride_d;
+
+        // this lane's 4 columns of a chunk: scale and bias.  The first chunk's are fetched
+        // before the wait for the accumulator (latency hidden behind the main loop), the
+        // next chunk's while the current one is processed.  The loops below are deliberately
+        // not unrolled: a tile's epilogue runs only a few times per launch, so straight-line
+        // code would be bound by instruction fetch.
+        auto load_sb = [&](int ch, float4& sc, float4& bi) {
+            sc = make_float4(tensor_scale, tensor_scale, tensor_scale, tensor_scale);
+            bi = make_float4(0.f, 0.f, 0.f, 0.f);
+            if constexpr(not std::is_same<OutT, int32_t>::value)
+            {
+                const int64_t c4 = col0 + ch * EPI_COLS + (lane & 3) * 4;
+                if(c4 + 4 <= p.N and p.vec_sb)
+                {
+                    if(per_col)
+                        sc = __ldg(reinterpret_cast<const float4*>(p.scale + c4));
+                    if(p.bias != nullptr)
+                        bi = __ldg(reinterpret_cast<const float4*>(p.bias + c4));
+                }
+                else
+                {
+                    float* sp = reinterpret_cast<float*>(&sc);
+                    float* bp = reinterpret_cast<float*>(&bi);
+                    for(int j = 0; j < 4; ++j)
+                    {
+                        if(c4 + j < p.N)
+                        {
+                            if(per_col)
+                                sp[j] = __ldg(p.scale + c4 + j);
+                            if(p.bias != nullptr)
+                                bp[j] = __ldg(p.bias + c4 + j);
+                        }
+                    }
+                }
+            }
+        };
+        float4 sc_next, bi_next;
+        load_sb(0, sc_next, bi_next);
+
+        if(not mbar_wait_bounded(&accf_bar[buf], (lt >> 1) & 1u, abort_flag, 3))
+            break;
+        tc_fence_after_sync();
+
+#pragma unroll 1
+        for(int ch = 0; ch < NCHUNK; ++ch)
+        {
+            const int64_t col = col0 + ch * EPI_COLS;
+            const float4 sc_cur = sc_next, bi_cur = bi_next;
+            if(ch + 1 < NCHUNK)
+                load_sb(ch + 1, sc_next, bi_next);
+            uint32_t acc[EPI_COLS];
+            __syncwarp(); // tcgen05.ld is warp-collective; also orders reuse of the box
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                                   buf * BN + slice * COLS_PER_WARP + ch * EPI_COLS;
+            tmem_ld_32x32b_x16(taddr, acc);
+            tmem_ld_wait();
+            if(col < p.N)
+            {
+#pragma unroll
+                for(int q = 0; q < 4; ++q)
+                    *reinterpret_cast<uint4*>(my_row + ((q ^ my_swz) * 16)) =
+                        make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+                __syncwarp();
+                epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
+            }
+        }
+        // all TMEM reads of this buffer are complete (wait::ld above)
+        tc_fence_before_sync();
+        __syncwarp();
+        if(lane == 0)
+            mbar_arrive(&acce_bar[buf]);
     }
 }
 
@@ -363,98 +487,18 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     else
     {
         // ---------------------------------------------------- epilogue
-        // Each warp owns TMEM lane quarter (warp % 4) = 32 rows of the tile, and one half
-        // of the tile's columns.  Per 32-column chunk: tcgen05.ld (one row per thread) ->
-        // swizzled shared memory -> read back with 8 lanes per 128-byte row segment ->
-        // dequantizelinear / bias / activation / residual -> coalesced global stores.
-        const int ew      = warp - 2;
-        const int quarter = warp & 3;
-        const int half    = ew >> 2;
-        constexpr int COLS_PER_WARP = BN / 2;
-        epi_ctx e;
-        e.p    = &p;
-        e.box  = epi_base + ew * (32 * 128);
-        e.lane = lane;
-        uint8_t* my_row = e.box + lane * 128;
-        const bool per_col = p.scale_mode == MGX_SCALE_PER_COL;
-        const float tensor_scale = p.scale_mode == MGX_SCALE_PER_TENSOR ? __ldg(p.scale) : 1.0f;
-        uint32_t lt = 0;
-        for(int64_t t = first_tile; t < p.num_tiles; t += tile_step, ++lt)
+#define MGX_EPILOGUE(ACT)                                                                      \
+    epilogue_role<BN, IS_INT, OutT, ACT>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base, \
+                                         warp, lane, first_tile, tile_step, tiles_mn)
+        switch(std::is_same<OutT, int32_t>::value ? MGX_ACT_NONE : p.act)
         {
-            const int b     = static_cast<int>(t / tiles_mn);
-            const int r     = static_cast<int>(t % tiles_mn);
-            const int m_blk = r % p.tiles_m;
-            const int n_blk = r / p.tiles_m;
-            const uint32_t buf = lt & 1u;
-            const int64_t col0 = static_cast<int64_t>(n_blk) * BN + half * COLS_PER_WARP;
-            e.row0      = static_cast<int64_t>(m_blk) * BM + quarter * 32;
-            e.batch_off = b * p.stride_d;
-
-            if(not mbar_wait_bounded(&accf_bar[buf], (lt >> 1) & 1u, abort_flag, 3))
-                break;
-            tc_fence_after_sync();
-
-#pragma unroll 1
-            for(int c = 0; c < COLS_PER_WARP; c += 32)
-            {
-                const int64_t col = col0 + c;
-                if(col >= p.N)
-                    break; // uniform over the warp: the rest is outside D
-                // this lane's 4 columns of the chunk: scale and bias (loads overlap the TMEM read)
-                const int64_t c4 = col + (lane & 7) * 4;
-                float4 sc4 = make_float4(tensor_scale, tensor_scale, tensor_scale, tensor_scale);
-                float4 bi4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                if constexpr(not std::is_same<OutT, int32_t>::value)
-                {
-                    if(c4 + 4 <= p.N and p.vec_sb)
-                    {
-                        if(per_col)
-                            sc4 = __ldg(reinterpret_cast<const float4*>(p.scale + c4));
-                        if(p.bias != nullptr)
-                            bi4 = __ldg(reinterpret_cast<const float4*>(p.bias + c4));
-                    }
-                    else
-                    {
-                        float* sp = reinterpret_cast<float*>(&sc4);
-                        float* bp = reinterpret_cast<float*>(&bi4);
-                        for(int j = 0; j < 4; ++j)
-                        {
-                            if(c4 + j < p.N)
-                            {
-                                if(per_col)
-                                    sp[j] = __ldg(p.scale + c4 + j);
-                                if(p.bias != nullptr)
-                                    bp[j] = __ldg(p.bias + c4 + j);
-                            }
-                        }
-                    }
-                }
-                uint32_t acc[32];
-                __syncwarp(); // tcgen05.ld is warp-collective; also orders reuse of the box
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                       buf * BN + half * COLS_PER_WARP + c;
-                tmem_ld_32x32b_x32(taddr, acc);
-                tmem_ld_wait();
-#pragma unroll
-                for(int q = 0; q < 8; ++q)
-                    *reinterpret_cast<uint4*>(my_row + ((q ^ (lane & 7)) * 16)) =
-                        make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-                __syncwarp();
-                switch(p.act)
-                {
-                case MGX_ACT_RELU: epi_store_chunk<IS_INT, OutT, MGX_ACT_RELU>(e, col, sc4, bi4); break;
-                case MGX_ACT_GELU_ERF: epi_store_chunk<IS_INT, OutT, MGX_ACT_GELU_ERF>(e, col, sc4, bi4); break;
-                case MGX_ACT_GELU_TANH: epi_store_chunk<IS_INT, OutT, MGX_ACT_GELU_TANH>(e, col, sc4, bi4); break;
-                case MGX_ACT_SILU: epi_store_chunk<IS_INT, OutT, MGX_ACT_SILU>(e, col, sc4, bi4); break;
-                default: epi_store_chunk<IS_INT, OutT, MGX_ACT_NONE>(e, col, sc4, bi4); break;
-                }
-            }
-            // all TMEM reads of this buffer are complete (wait::ld above)
-            tc_fence_before_sync();
-            __syncwarp();
-            if(lane == 0)
-                mbar_arrive(&acce_bar[buf]);
+        case MGX_ACT_RELU: MGX_EPILOGUE(MGX_ACT_RELU); break;
+        case MGX_ACT_GELU_ERF: MGX_EPILOGUE(MGX_ACT_GELU_ERF); break;
+        case MGX_ACT_GELU_TANH: MGX_EPILOGUE(MGX_ACT_GELU_TANH); break;
+        case MGX_ACT_SILU: MGX_EPILOGUE(MGX_ACT_SILU); break;
+        default: MGX_EPILOGUE(MGX_ACT_NONE); break;
         }
+#undef MGX_EPILOGUE
     }
 
     // ---------------------------------------------------------- teardown

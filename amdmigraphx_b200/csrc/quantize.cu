@@ -100,65 +100,65 @@ struct view2
     int64_t s0, s1;
 };
 
-// One work item = 4 consecutive columns of one row; every thread keeps UNROLL items
-// (UNROLL independent 16-byte loads) in flight per loop trip.
-template <class In, class Q>
+// One work item = 16 bytes of one input row (4 fp32 or 8 fp16 columns) -> 4 or 8 output
+// bytes.  Index arithmetic is done in IdxT (32-bit whenever the tensor allows it: a 64-bit
+// division per item would make the kernel ALU-bound).  UNIFORM: scale and zero point are
+// per-tensor (all strides 0) and are read once per thread.
+template <class In, class Q, class IdxT, bool UNIFORM>
 __global__ void __launch_bounds__(256)
-    quantize_vec4_kernel(const In* __restrict__ x, int64_t ldx, const In* __restrict__ scale,
-                         view2 ss, const typename Q::type* __restrict__ zp, view2 zs,
-                         typename Q::type* __restrict__ y, int64_t ldy, int64_t rows,
-                         int64_t cols4)
+    quantize_vec_kernel(const In* __restrict__ x, int64_t ldx, const In* __restrict__ scale,
+                        view2 ss, const typename Q::type* __restrict__ zp, view2 zs,
+                        typename Q::type* __restrict__ y, int64_t ldy, IdxT rows, IdxT colsv)
 {
-    constexpr int UNROLL = 4;
-    using vec_t          = typename std::conditional<std::is_same<In, float>::value, float4, uint2>::type;
-    const int64_t total  = rows * cols4;
-    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-    for(int64_t i0 = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i0 < total;
-        i0 += stride * UNROLL)
+    constexpr int VEC = 16 / sizeof(In);
+    const IdxT total  = rows * colsv;
+    const IdxT stride = static_cast<IdxT>(gridDim.x) * blockDim.x;
+    float s0 = 1.0f, z0 = 0.0f;
+    if(UNIFORM)
     {
-        vec_t v[UNROLL];
-        int64_t rr[UNROLL], cc[UNROLL];
-#pragma unroll
-        for(int u = 0; u < UNROLL; ++u)
+        s0 = to_f32<In>(scale[0]);
+        z0 = zp == nullptr ? 0.0f : Q::zp(zp[0]);
+    }
+    for(IdxT i = static_cast<IdxT>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    {
+        const IdxT r = i / colsv;
+        const IdxT c = (i - r * colsv) * VEC;
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(r) * ldx + c);
+        float xv[VEC];
+        if constexpr(std::is_same<In, float>::value)
         {
-            const int64_t i = i0 + u * stride;
-            if(i < total)
-            {
-                rr[u] = i / cols4;
-                cc[u] = (i - rr[u] * cols4) * 4;
-                v[u]  = *reinterpret_cast<const vec_t*>(x + rr[u] * ldx + cc[u]);
-            }
+            xv[0] = __uint_as_float(raw.x), xv[1] = __uint_as_float(raw.y);
+            xv[2] = __uint_as_float(raw.z), xv[3] = __uint_as_float(raw.w);
         }
-#pragma unroll
-        for(int u = 0; u < UNROLL; ++u)
+        else
         {
-            const int64_t i = i0 + u * stride;
-            if(i >= total)
-                break;
-            const int64_t r = rr[u], c = cc[u];
-            float xv[4];
-            if constexpr(std::is_same<In, float>::value)
-            {
-                xv[0] = v[u].x, xv[1] = v[u].y, xv[2] = v[u].z, xv[3] = v[u].w;
-            }
-            else
-            {
-                const __half* vh = reinterpret_cast<const __half*>(&v[u]);
+            const __half* vh = reinterpret_cast<const __half*>(&raw);
 #pragma unroll
-                for(int j = 0; j < 4; ++j)
-                    xv[j] = __half2float(vh[j]);
-            }
-            uint32_t packed = 0;
-#pragma unroll
-            for(int j = 0; j < 4; ++j)
-            {
-                const float s = to_f32<In>(scale[r * ss.s0 + (c + j) * ss.s1]);
-                const float z = zp == nullptr ? 0.0f : Q::zp(zp[r * zs.s0 + (c + j) * zs.s1]);
-                const uint32_t q = static_cast<uint8_t>(Q::template quant<In>(xv[j], s, z));
-                packed |= q << (8 * j);
-            }
-            *reinterpret_cast<uint32_t*>(y + r * ldy + c) = packed;
+            for(int j = 0; j < VEC; ++j)
+                xv[j] = __half2float(vh[j]);
         }
+        uint32_t packed[VEC / 4];
+#pragma unroll
+        for(int w = 0; w < VEC / 4; ++w)
+            packed[w] = 0;
+#pragma unroll
+        for(int j = 0; j < VEC; ++j)
+        {
+            float sv = s0, zv = z0;
+            if(not UNIFORM)
+            {
+                sv = to_f32<In>(scale[static_cast<int64_t>(r) * ss.s0 + (c + j) * ss.s1]);
+                zv = zp == nullptr ? 0.0f
+                                   : Q::zp(zp[static_cast<int64_t>(r) * zs.s0 + (c + j) * zs.s1]);
+            }
+            const uint32_t q = static_cast<uint8_t>(Q::template quant<In>(xv[j], sv, zv));
+            packed[j / 4] |= q << (8 * (j % 4));
+        }
+        typename Q::type* dst = y + static_cast<int64_t>(r) * ldy + c;
+        if constexpr(VEC == 4)
+            *reinterpret_cast<uint32_t*>(dst) = packed[0];
+        else
+            *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
     }
 }
 
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(256)
 static int grid_for(int64_t work_items, int threads)
 {
     const int64_t blocks = ceil_div(work_items, threads);
-    const int64_t cap    = static_cast<int64_t>(device_sm_count()) * 16;
+    const int64_t cap    = static_cast<int64_t>(device_sm_count()) * 8;
     return static_cast<int>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
 }
 
@@ -193,16 +193,31 @@ static int launch_quantize(const void* x, int64_t ldx, const void* scale, view2 
                            view2 zs, void* y, int64_t ldy, int64_t rows, int64_t cols,
                            cudaStream_t stream)
 {
-    using Out      = typename Q::type;
-    const bool vec = cols % 4 == 0 and ldx % 4 == 0 and ldy % 4 == 0 and
-                     (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(In))) == 0 and
-                     (reinterpret_cast<uintptr_t>(y) % 4) == 0;
+    using Out         = typename Q::type;
+    constexpr int VEC = 16 / sizeof(In);
+    const bool vec    = cols % VEC == 0 and ldx % VEC == 0 and ldy % VEC == 0 and
+                     (reinterpret_cast<uintptr_t>(x) % 16) == 0 and
+                     (reinterpret_cast<uintptr_t>(y) % VEC) == 0;
     if(vec)
     {
-        const int64_t n = rows * (cols / 4);
-        quantize_vec4_kernel<In, Q><<<grid_for(ceil_div(n, 4), 256), 256, 0, stream>>>(
-            static_cast<const In*>(x), ldx, static_cast<const In*>(scale), ss,
-            static_cast<const Out*>(zp), zs, static_cast<Out*>(y), ldy, rows, cols / 4);
+        const int64_t n    = rows * (cols / VEC);
+        const bool uniform = ss.s0 == 0 and ss.s1 == 0 and (zp == nullptr or (zs.s0 == 0 and zs.s1 == 0));
+        const bool small   = n < (int64_t{1} << 31) and rows * ldx < (int64_t{1} << 31);
+        const int grid     = grid_for(n, 256);
+#define MGX_LAUNCH_QV(IDX, UNI)                                                                  \
+    quantize_vec_kernel<In, Q, IDX, UNI><<<grid, 256, 0, stream>>>(                              \
+        static_cast<const In*>(x), ldx, static_cast<const In*>(scale), ss,                       \
+        static_cast<const Out*>(zp), zs, static_cast<Out*>(y), ldy, static_cast<IDX>(rows),      \
+        static_cast<IDX>(cols / VEC))
+        if(small and uniform)
+            MGX_LAUNCH_QV(uint32_t, true);
+        else if(small)
+            MGX_LAUNCH_QV(uint32_t, false);
+        else if(uniform)
+            MGX_LAUNCH_QV(int64_t, true);
+        else
+            MGX_LAUNCH_QV(int64_t, false);
+#undef MGX_LAUNCH_QV
     }
     else
     {

@@ -93,7 +93,7 @@ def test_qdq_block_matches_ref(cuda_device):
         got = capi.qgemm(xq, w, scale=scale, bias=bias, act=act, out_dtype=torch.float32)
         np.testing.assert_array_equal(got.cpu().numpy(), FX[key])  # same ops, same roundings
     got = capi.qgemm(xq, w, scale=scale, bias=bias, act="gelu_erf", out_dtype=torch.float32)
-    np.testing.assert_allclose(got.cpu().numpy(), FX["blk_gelu"], rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(got.cpu().numpy(), FX["blk_gelu"], rtol=1e-5, atol=3e-6)
 
 
 @pytest.mark.parametrize("tag", ["a", "b"])
