@@ -606,16 +606,31 @@ static int dispatch_out(const mgx_qgemm_desc& d, const void* A, const void* B, v
     }
 }
 
+// Tile width: the BN in {256, 128, 64} with the smallest estimated time
+//   waves x (k-blocks x cycles per k-block + epilogue cycles),
+// where a k-block costs 4 MMAs of max(BN/2, 48) cycles (below BN = 96 the 128 B/clk
+// shared-memory read rate, not the tensor pipe, bounds a 128 x BN x 32 MMA) and the
+// epilogue about 12 cycles per column.
 static int pick_bn(const mgx_qgemm_desc& d)
 {
     const int64_t sms = device_sm_count();
     const int64_t tm  = (d.M + BM - 1) / BM;
-    for(int bn : {256, 128})
+    const int64_t kb  = (d.K + BK - 1) / BK;
+    int best          = 64;
+    int64_t best_cost = INT64_MAX;
+    for(int bn : {256, 128, 64})
     {
-        if(tm * ((d.N + bn - 1) / bn) * d.batch >= sms)
-            return bn;
+        const int64_t tiles = tm * ((d.N + bn - 1) / bn) * d.batch;
+        const int64_t waves = (tiles + sms - 1) / sms;
+        const int64_t mma   = 4 * (bn / 2 > 48 ? bn / 2 : 48);
+        const int64_t cost  = waves * (kb * mma + 12 * bn) + 1500;
+        if(cost < best_cost)
+        {
+            best_cost = cost;
+            best      = bn;
+        }
     }
-    return 64;
+    return best;
 }
 
 } // namespace mgx

@@ -1,0 +1,408 @@
+// cuda_target_check: builds MIGraphX programs of the quantized-GEMM path with the public
+// module API, runs them on MIGraphX's CPU `ref` target and on the `cuda` target and compares
+// the results - the same scheme as the reference's cross-target verify harness
+// (test/verify/run_verify.cpp:176-259), for the programs this target supports.
+//
+//   cuda_target_check passes <case>          print the program after the cuda pass pipeline
+//                                            (no GPU needed: finalize is not run)
+//   cuda_target_check run <case> [offload]   compile + eval on ref and cuda, print one JSON line
+//   cuda_target_check list
+#include <migraphx/program.hpp>
+#include <migraphx/module.hpp>
+#include <migraphx/make_op.hpp>
+#include <migraphx/register_target.hpp>
+#include <migraphx/literal.hpp>
+#include <migraphx/instruction.hpp>
+#include <migraphx/pass_manager.hpp>
+#include <migraphx/fuse_pointwise.hpp>
+#include <migraphx/dead_code_elimination.hpp>
+#include <migraphx/simplify_qdq.hpp>
+#include <migraphx/generate.hpp>
+#include <migraphx/half.hpp>
+#include <chrono>
+#include <cmath>
+#include <cstring>
+#include <iostream>
+#include <map>
+#include <random>
+#include <functional>
+
+using migraphx::shape;
+using migraphx::instruction_ref;
+
+namespace {
+
+struct test_case
+{
+    migraphx::program prog;
+    migraphx::parameter_map params; // host arguments
+    bool exact    = false;          // bit-exact comparison
+    double rtol   = 1e-5;
+    double atol   = 1e-6;
+};
+
+template <class T>
+std::vector<T> rand_ints(std::mt19937& g, std::size_t n, int lo, int hi)
+{
+    std::uniform_int_distribution<int> d(lo, hi);
+    std::vector<T> v(n);
+    for(auto& x : v)
+        x = static_cast<T>(d(g));
+    return v;
+}
+
+std::vector<float> rand_normal(std::mt19937& g, std::size_t n, float sd)
+{
+    std::normal_distribution<float> d(0.0f, sd);
+    std::vector<float> v(n);
+    for(auto& x : v)
+        x = d(g);
+    return v;
+}
+
+std::vector<float> rand_uniform(std::mt19937& g, std::size_t n, float lo, float hi)
+{
+    std::uniform_real_distribution<float> d(lo, hi);
+    std::vector<float> v(n);
+    for(auto& x : v)
+        x = d(g);
+    return v;
+}
+
+instruction_ref mbcast(migraphx::module* mm, instruction_ref x, const std::vector<std::size_t>& lens)
+{
+    return mm->add_instruction(migraphx::make_op("multibroadcast", {{"out_lens", lens}}), x);
+}
+
+instruction_ref bcast_axis(migraphx::module* mm, instruction_ref x, std::size_t axis,
+                           const std::vector<std::size_t>& lens)
+{
+    return mm->add_instruction(migraphx::make_op("broadcast", {{"axis", axis}, {"out_lens", lens}}), x);
+}
+
+// Q -> DQ on the activation, DQ on the int8/fp8 weight literal, dot, + bias, activation:
+// the fake-quantised form quantize_int8 / quantize_fp8 leave behind.
+test_case qdq_linear(std::size_t m, std::size_t k, std::size_t n, shape::type_t qtype,
+                     const std::string& act, bool per_channel, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const bool fp8 = qtype == shape::fp8e4m3fn_type;
+    auto x       = mm->add_parameter("x", shape{shape::float_type, {m, k}});
+    auto xs      = mm->add_literal(migraphx::literal{shape{shape::float_type}, {fp8 ? 0.01f : 0.02f}});
+    instruction_ref xz, wq, wz;
+    if(fp8)
+    {
+        std::vector<migraphx::fp8::fp8e4m3fn> z1 = {migraphx::fp8::fp8e4m3fn(0.0f)};
+        xz = mm->add_literal(migraphx::literal{shape{qtype}, z1});
+        auto wf = rand_normal(g, k * n, 60.0f);
+        std::vector<migraphx::fp8::fp8e4m3fn> wv(k * n);
+        for(std::size_t i = 0; i < wv.size(); ++i)
+            wv[i] = migraphx::fp8::fp8e4m3fn(std::max(-448.0f, std::min(448.0f, wf[i])));
+        wq = mm->add_literal(migraphx::literal{shape{qtype, {k, n}}, wv});
+    }
+    else
+    {
+        xz = mm->add_literal(migraphx::literal{shape{qtype}, std::vector<int8_t>{0}});
+        wq = mm->add_literal(migraphx::literal{shape{qtype, {k, n}}, rand_ints<int8_t>(g, k * n, -127, 127)});
+    }
+    auto xq  = mm->add_instruction(migraphx::make_op("quantizelinear"), x, mbcast(mm, xs, {m, k}),
+                                  mbcast(mm, xz, {m, k}));
+    auto xdq = mm->add_instruction(migraphx::make_op("dequantizelinear"), xq, mbcast(mm, xs, {m, k}),
+                                   mbcast(mm, xz, {m, k}));
+    instruction_ref wdq;
+    if(per_channel)
+    {
+        auto ws = mm->add_literal(migraphx::literal{shape{shape::float_type, {n}}, rand_uniform(g, n, 0.001f, 0.01f)});
+        instruction_ref wzl;
+        if(fp8)
+            wzl = mm->add_literal(migraphx::literal{shape{qtype, {n}}, std::vector<migraphx::fp8::fp8e4m3fn>(n, migraphx::fp8::fp8e4m3fn(0.0f))});
+        else
+            wzl = mm->add_literal(migraphx::literal{shape{qtype, {n}}, std::vector<int8_t>(n, 0)});
+        wdq = mm->add_instruction(migraphx::make_op("dequantizelinear"), wq, bcast_axis(mm, ws, 1, {k, n}),
+                                  bcast_axis(mm, wzl, 1, {k, n}));
+    }
+    else
+    {
+        auto ws = mm->add_literal(migraphx::literal{shape{shape::float_type}, {0.005f}});
+        wdq = mm->add_instruction(migraphx::make_op("dequantizelinear"), wq, mbcast(mm, ws, {k, n}),
+                                  mbcast(mm, xz, {k, n}));
+    }
+    auto d    = mm->add_instruction(migraphx::make_op("dot"), xdq, wdq);
+    auto bias = mm->add_literal(migraphx::literal{shape{shape::float_type, {n}}, rand_normal(g, n, 0.1f)});
+    instruction_ref y = mm->add_instruction(migraphx::make_op("add"), d, bcast_axis(mm, bias, 1, {m, n}));
+    if(act == "relu")
+        y = mm->add_instruction(migraphx::make_op("relu"), y);
+    else if(act == "gelu")
+    {
+        auto half  = mm->add_literal(migraphx::literal{shape{shape::float_type}, {0.5f}});
+        auto one   = mm->add_literal(migraphx::literal{shape{shape::float_type}, {1.0f}});
+        auto sqrt2 = mm->add_literal(migraphx::literal{shape{shape::float_type}, {static_cast<float>(M_SQRT2)}});
+        auto mh    = mm->add_instruction(migraphx::make_op("mul"), y, mbcast(mm, half, {m, n}));
+        auto dv    = mm->add_instruction(migraphx::make_op("div"), y, mbcast(mm, sqrt2, {m, n}));
+        auto er    = mm->add_instruction(migraphx::make_op("erf"), dv);
+        auto ao    = mm->add_instruction(migraphx::make_op("add"), er, mbcast(mm, one, {m, n}));
+        y          = mm->add_instruction(migraphx::make_op("mul"), mh, ao);
+    }
+    mm->add_return({y});
+    auto xv = rand_normal(g, m * k, fp8 ? 1.5f : 1.0f);
+    migraphx::argument xa{shape{shape::float_type, {m, k}}};
+    std::memcpy(xa.data(), xv.data(), xv.size() * sizeof(float));
+    t.params["x"] = xa;
+    // ref evaluates the fake-quantised program (fp32 dot of dequantised operands); the cuda
+    // target runs quant_dot + fused dequantise.  int8: products are exact either way and only
+    // the fp32 rounding of the scaled sum differs; fp8: fp32 accumulation order.
+    t.rtol = fp8 ? 2e-2 : 1e-5;
+    t.atol = fp8 ? 1e-2 : 2e-5;
+    return t;
+}
+
+// The MatMulNBits IR (src/onnx/parse_matmulnbits.cpp:85-158): packed uint8 weights [N,K/2],
+// fp16 scales [N,K/g] broadcast over the group, zero point 8 (or explicit), transpose, dot.
+test_case int4_linear(std::size_t m, std::size_t n, std::size_t k, std::size_t g, bool with_zp,
+                      unsigned seed)
+{
+    test_case t;
+    std::mt19937 gen(seed);
+    auto* mm   = t.prog.get_main_module();
+    auto a     = mm->add_parameter("a", shape{shape::half_type, {m, k}});
+    auto bp    = mm->add_literal(migraphx::literal{shape{shape::uint8_type, {n, k / 2}},
+                                                rand_ints<uint8_t>(gen, n * k / 2, 0, 255)});
+    auto sf    = rand_uniform(gen, n * (k / g), 0.005f, 0.02f);
+    std::vector<migraphx::half> sh(sf.size());
+    for(std::size_t i = 0; i < sf.size(); ++i)
+        sh[i] = migraphx::half(sf[i]);
+    auto scales = mm->add_literal(migraphx::literal{shape{shape::half_type, {n, k / g}}, sh});
+    auto expand = [&](instruction_ref v) {
+        auto u  = mm->add_instruction(migraphx::make_op("unsqueeze", {{"axes", {2}}}), v);
+        auto mb = mm->add_instruction(
+            migraphx::make_op("multibroadcast", {{"out_lens", {n, k / g, g}}}), u);
+        return mm->add_instruction(migraphx::make_op("reshape", {{"dims", {n, k}}}), mb);
+    };
+    auto unpacked = mm->add_instruction(migraphx::make_op("unpack_int4"), bp);
+    instruction_ref zp;
+    if(with_zp)
+    {
+        auto zl = mm->add_literal(migraphx::literal{shape{shape::uint8_type, {n, k / g}},
+                                                    rand_ints<uint8_t>(gen, n * (k / g), 0, 15)});
+        zp = expand(zl);
+    }
+    else
+    {
+        auto z8 = mm->add_literal(migraphx::literal{shape{shape::uint8_type}, std::vector<uint8_t>{8}});
+        zp      = mbcast(mm, z8, {n, k});
+    }
+    auto dq = mm->add_instruction(migraphx::make_op("dequantizelinear"), unpacked, expand(scales), zp);
+    auto bt = mm->add_instruction(migraphx::make_op("transpose", {{"permutation", {1, 0}}}), dq);
+    auto y  = mm->add_instruction(migraphx::make_op("dot"), a, bt);
+    mm->add_return({y});
+    auto av = rand_normal(gen, m * k, 1.0f);
+    migraphx::argument aa{shape{shape::half_type, {m, k}}};
+    auto* ah = reinterpret_cast<migraphx::half*>(aa.data());
+    for(std::size_t i = 0; i < av.size(); ++i)
+        ah[i] = migraphx::half(av[i]);
+    t.params["a"] = aa;
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
+    return t;
+}
+
+// quantizelinear and dequantizelinear alone, on parameters.
+test_case q_dq_ops(unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    const std::size_t r = 48, c = 160;
+    auto* mm = t.prog.get_main_module();
+    auto x   = mm->add_parameter("x", shape{shape::float_type, {r, c}});
+    auto s   = mm->add_literal(migraphx::literal{shape{shape::float_type, {c}}, rand_uniform(g, c, 0.01f, 0.05f)});
+    auto z   = mm->add_literal(migraphx::literal{shape{shape::int8_type, {c}}, rand_ints<int8_t>(g, c, -20, 20)});
+    auto q   = mm->add_instruction(migraphx::make_op("quantizelinear"), x, bcast_axis(mm, s, 1, {r, c}),
+                                 bcast_axis(mm, z, 1, {r, c}));
+    // dequantizelinear on its own int8 parameter (a DQ fed by the Q above would be removed
+    // as a Q/DQ pair by simplify_qdq)
+    auto q2 = mm->add_parameter("q2", shape{shape::int8_type, {r, c}});
+    auto d  = mm->add_instruction(migraphx::make_op("dequantizelinear"), q2, bcast_axis(mm, s, 1, {r, c}),
+                                 bcast_axis(mm, z, 1, {r, c}));
+    mm->add_return({q, d});
+    auto xv = rand_normal(g, r * c, 2.0f);
+    migraphx::argument xa{shape{shape::float_type, {r, c}}};
+    std::memcpy(xa.data(), xv.data(), xv.size() * sizeof(float));
+    t.params["x"] = xa;
+    auto qv = rand_ints<int8_t>(g, r * c, -128, 127);
+    migraphx::argument qa{shape{shape::int8_type, {r, c}}};
+    std::memcpy(qa.data(), qv.data(), qv.size());
+    t.params["q2"] = qa;
+    t.exact       = true;
+    return t;
+}
+
+// quant_dot alone on int8 parameters (batched, non-constant right operand).
+test_case raw_quant_dot(unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    const std::size_t b = 2, m = 72, k = 160, n = 48;
+    auto* mm = t.prog.get_main_module();
+    auto x   = mm->add_parameter("a", shape{shape::int8_type, {b, m, k}});
+    auto w   = mm->add_parameter("b", shape{shape::int8_type, {b, k, n}});
+    mm->add_return({mm->add_instruction(migraphx::make_op("quant_dot"), x, w)});
+    auto av = rand_ints<int8_t>(g, b * m * k, -128, 127);
+    auto bv = rand_ints<int8_t>(g, b * k * n, -128, 127);
+    migraphx::argument aa{shape{shape::int8_type, {b, m, k}}}, ba{shape{shape::int8_type, {b, k, n}}};
+    std::memcpy(aa.data(), av.data(), av.size());
+    std::memcpy(ba.data(), bv.data(), bv.size());
+    t.params["a"] = aa;
+    t.params["b"] = ba;
+    t.exact       = true;
+    return t;
+}
+
+std::map<std::string, std::function<test_case()>> cases()
+{
+    return {
+        {"c1", [] { auto t = qdq_linear(256, 1024, 1024, shape::int8_type, "relu", true, 0); t.exact = true; return t; }},
+        {"c1_small", [] { auto t = qdq_linear(64, 256, 96, shape::int8_type, "relu", true, 1); t.exact = true; return t; }},
+        {"c1_semantic", [] { return qdq_linear(64, 256, 96, shape::int8_type, "relu", true, 1); }},
+        {"int8_gelu", [] { return qdq_linear(128, 256, 320, shape::int8_type, "gelu", true, 2); }},
+        {"int8_per_tensor", [] { auto t = qdq_linear(100, 128, 72, shape::int8_type, "none", false, 3); t.exact = true; return t; }},
+        {"fp8_gelu", [] { return qdq_linear(128, 512, 256, shape::fp8e4m3fn_type, "gelu", false, 4); }},
+        {"int4_decode", [] { return int4_linear(1, 256, 512, 128, false, 5); }},
+        {"int4_batch16_zp", [] { return int4_linear(16, 128, 1024, 32, true, 6); }},
+        {"q_dq_ops", [] { return q_dq_ops(7); }},
+        {"raw_quant_dot", [] { return raw_quant_dot(8); }},
+    };
+}
+
+struct cmp_result
+{
+    double max_abs = 0, max_rel = 0;
+    std::size_t mismatched = 0, n = 0;
+};
+
+cmp_result compare(const migraphx::argument& ref, const migraphx::argument& got, bool exact, double rtol,
+                   double atol)
+{
+    cmp_result r;
+    if(ref.get_shape().lens() != got.get_shape().lens() or ref.get_shape().type() != got.get_shape().type())
+    {
+        r.mismatched = 1u << 30;
+        return r;
+    }
+    r.n = ref.get_shape().elements();
+    if(exact)
+    {
+        const auto es = ref.get_shape().type_size();
+        for(std::size_t i = 0; i < r.n; ++i)
+            if(std::memcmp(ref.data() + i * es, got.data() + i * es, es) != 0)
+                ++r.mismatched;
+        return r;
+    }
+    std::vector<double> a(r.n), b(r.n);
+    ref.visit([&](auto v) { std::size_t i = 0; for(auto x : v) a[i++] = static_cast<double>(x); });
+    got.visit([&](auto v) { std::size_t i = 0; for(auto x : v) b[i++] = static_cast<double>(x); });
+    for(std::size_t i = 0; i < r.n; ++i)
+    {
+        const double d = std::fabs(a[i] - b[i]);
+        r.max_abs      = std::max(r.max_abs, d);
+        if(std::fabs(a[i]) > 0)
+            r.max_rel = std::max(r.max_rel, d / std::fabs(a[i]));
+        if(not(d <= atol + rtol * std::fabs(a[i])))
+            ++r.mismatched;
+    }
+    return r;
+}
+
+} // namespace
+
+int main(int argc, char** argv)
+{
+    const auto all = cases();
+    if(argc < 2 or std::string(argv[1]) == "list")
+    {
+        for(const auto& c : all)
+            std::cout << c.first << "\n";
+        return 0;
+    }
+    const std::string mode = argv[1];
+    const std::string name = argc > 2 ? argv[2] : "c1_small";
+    const bool offload     = argc > 3 and std::string(argv[3]) == "offload";
+    const bool prefused    = argc > 3 and std::string(argv[3]) == "prefused";
+    if(all.count(name) == 0)
+    {
+        std::cerr << "unknown case " << name << "\n";
+        return 2;
+    }
+    try
+    {
+        test_case t = all.at(name)();
+        auto cuda_t = migraphx::make_target("cuda");
+        if(mode == "passes")
+        {
+            migraphx::program p = t.prog;
+            auto ctx            = cuda_t.get_context();
+            migraphx::compile_options opts;
+            opts.offload_copy = offload;
+            if(prefused)
+                migraphx::run_passes(p, {migraphx::simplify_qdq{}, migraphx::dead_code_elimination{},
+                                         migraphx::fuse_pointwise{}, migraphx::dead_code_elimination{}});
+            migraphx::run_passes(p, cuda_t.get_passes(ctx, opts));
+            std::cout << p << std::endl;
+            return 0;
+        }
+        // reference result
+        migraphx::program pr = t.prog;
+        if(t.exact)
+            migraphx::run_passes(pr, {migraphx::simplify_qdq{}, migraphx::dead_code_elimination{}});
+        pr.compile(migraphx::make_target("ref"));
+        auto t0       = std::chrono::steady_clock::now();
+        auto ref_out  = pr.eval(t.params);
+        double ref_s  = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        // cuda result
+        migraphx::program pc = t.prog;
+        if(prefused)
+            migraphx::run_passes(pc, {migraphx::simplify_qdq{}, migraphx::dead_code_elimination{},
+                                      migraphx::fuse_pointwise{}, migraphx::dead_code_elimination{}});
+        migraphx::compile_options opts;
+        opts.offload_copy = offload;
+        pc.compile(cuda_t, opts);
+        migraphx::parameter_map pm;
+        for(const auto& ps : pc.get_parameter_shapes())
+        {
+            if(t.params.count(ps.first) > 0)
+                pm[ps.first] = offload ? t.params.at(ps.first) : cuda_t.copy_to(t.params.at(ps.first));
+            else
+                pm[ps.first] = cuda_t.allocate(ps.second);
+        }
+        auto cuda_out = pc.eval(pm);
+        pc.finish();
+        auto t1 = std::chrono::steady_clock::now();
+        const int reps = 20;
+        for(int i = 0; i < reps; ++i)
+            cuda_out = pc.eval(pm);
+        pc.finish();
+        double cuda_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t1).count() / reps;
+        bool ok = ref_out.size() == cuda_out.size();
+        std::cout << "{\"case\": \"" << name << "\", \"offload\": " << (offload ? "true" : "false")
+                  << ", \"prefused\": " << (prefused ? "true" : "false") << ", \"outputs\": [";
+        for(std::size_t i = 0; i < ref_out.size() and i < cuda_out.size(); ++i)
+        {
+            auto host = offload ? cuda_out[i] : cuda_t.copy_from(cuda_out[i]);
+            auto c    = compare(ref_out[i], host, t.exact, t.rtol, t.atol);
+            ok        = ok and c.mismatched == 0;
+            std::cout << (i ? ", " : "") << "{\"n\": " << c.n << ", \"mismatched\": " << c.mismatched
+                      << ", \"max_abs\": " << c.max_abs << ", \"max_rel\": " << c.max_rel << "}";
+        }
+        std::cout << "], \"exact\": " << (t.exact ? "true" : "false") << ", \"ref_seconds\": " << ref_s
+                  << ", \"cuda_seconds\": " << cuda_s << ", \"pass\": " << (ok ? "true" : "false") << "}"
+                  << std::endl;
+        return ok ? 0 : 1;
+    }
+    catch(const std::exception& e)
+    {
+        std::cout << "{\"case\": \"" << name << "\", \"error\": \"" << e.what() << "\", \"pass\": false}"
+                  << std::endl;
+        return 3;
+    }
+}

@@ -1,0 +1,245 @@
+// Operators of the `cuda` target.  Every compute operator follows the convention of
+// MIGraphX's device targets (src/targets/gpu/include/migraphx/gpu/gemm.hpp:109-127): the
+// output buffer is the LAST input and is what compute() returns (output_alias), so that the
+// generic replace_allocate / memory_coloring passes can plan all buffers into one arena.
+#ifndef MGX_CUDA_OPS_HPP
+#define MGX_CUDA_OPS_HPP
+
+#include "cuda_target.hpp"
+#include <migraphx/literal.hpp>
+#include <migraphx/reflect.hpp>
+#include <migraphx/functional.hpp>
+
+namespace migraphx {
+inline namespace MIGRAPHX_INLINE_NS {
+namespace cuda {
+
+// ---- memory ---------------------------------------------------------------------------
+struct op_allocate
+{
+    shape s{};
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.s, "shape"));
+    }
+    std::string name() const { return "cuda::allocate"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+};
+
+// Arena / parameter replacement created by preallocate_param: allocated once at finalize.
+struct op_preallocate
+{
+    shape s{};
+    std::string id{};
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.s, "shape"), f(self.id, "id"));
+    }
+    std::string name() const { return "cuda::preallocate"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    void finalize(context& ctx, const shape&, const std::vector<shape>&) const;
+};
+
+// A constant uploaded to the device once, at finalize.
+struct op_literal
+{
+    literal l{};
+    std::string id{};
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.l, "literal"), f(self.id, "id"));
+    }
+    std::string name() const { return "cuda::literal"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    void finalize(context& ctx, const shape&, const std::vector<shape>&) const;
+    friend std::ostream& operator<<(std::ostream& os, const op_literal& x)
+    {
+        os << x.name() << "[id=" << x.id << "]";
+        return os;
+    }
+};
+
+struct op_copy_to // (host, device_out) -> device_out
+{
+    std::string name() const { return "cuda::copy_to"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {1}; }
+};
+
+struct op_copy_from // (device) -> new host buffer; synchronises the stream
+{
+    std::string name() const { return "cuda::copy_from"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+};
+
+struct op_copy // (device_src, device_out) -> device_out
+{
+    std::string name() const { return "cuda::copy"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {1}; }
+};
+
+struct op_sync_stream
+{
+    std::string name() const { return "cuda::sync_stream"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const
+    {
+        if(args.empty())
+            return {};
+        return {0};
+    }
+};
+
+// ---- stream scheduling (inserted by the generic schedule pass through schedule_model) ----
+struct op_set_stream
+{
+    std::size_t stream = 0;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.stream, "stream"));
+    }
+    std::string name() const { return "cuda::set_stream"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    void finalize(context& ctx, const shape&, const std::vector<shape>&) const;
+};
+
+struct op_record_event
+{
+    std::size_t event = 0;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.event, "event"));
+    }
+    std::string name() const { return "cuda::record_event"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    void finalize(context& ctx, const shape&, const std::vector<shape>&) const;
+};
+
+struct op_wait_event
+{
+    std::size_t event = 0;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.event, "event"));
+    }
+    std::string name() const { return "cuda::wait_event"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+};
+
+// ---- quantized path ---------------------------------------------------------------------
+// quantizelinear: inputs (x, scale view, [zero-point view], out).  Replaces
+// op::quantizelinear (src/include/migraphx/op/quantizelinear.hpp).
+struct op_quantizelinear
+{
+    bool has_zp = false;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.has_zp, "has_zp"));
+    }
+    std::string name() const { return "cuda::quantizelinear"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// dequantizelinear: inputs (x, scale view, [zero-point view], out).
+struct op_dequantizelinear
+{
+    bool has_zp = false;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.has_zp, "has_zp"));
+    }
+    std::string name() const { return "cuda::dequantizelinear"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// unpack_int4 / pack_int4 along the last axis: inputs (x, out).
+struct op_unpack_int4
+{
+    std::string name() const { return "cuda::unpack_int4"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+struct op_pack_int4
+{
+    std::string name() const { return "cuda::pack_int4"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// quant_dot with the fused epilogue dequantizelinear -> add(bias) -> activation ->
+// add(residual) -> convert.  Inputs, in order:
+//   A [..,M,K], B ([..,K,N] or, when b_nk, [..,N,K]), [scale (fp32 vector or scalar)],
+//   [bias (fp32 [N])], [residual (out's shape and type)], [workspace], out.
+struct op_qgemm
+{
+    int scale_mode    = 0; // mgx_scale_mode
+    int act           = 0; // mgx_act
+    bool has_bias     = false;
+    bool has_residual = false;
+    bool b_nk         = false; // B was re-laid out [N,K] at compile time
+    bool has_workspace = false;
+    int out_type       = static_cast<int>(shape::int32_type); // shape::type_t of the result
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.scale_mode, "scale_mode"), f(self.act, "act"),
+                    f(self.has_bias, "has_bias"), f(self.has_residual, "has_residual"),
+                    f(self.b_nk, "b_nk"), f(self.has_workspace, "has_workspace"),
+                    f(self.out_type, "out_type"));
+    }
+    std::string name() const { return "cuda::qgemm"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// Weight-only int4 linear (unpack_int4 + dequantizelinear + transpose + dot fused).
+// Inputs: A fp16 [M,K], packed weights uint8 [N,K/2], scales fp16 [N,K/group],
+// [zero points uint8 [N,K/group]], [workspace], out fp16 [M,N].
+struct op_w4a16
+{
+    int group          = 128;
+    int zp_const       = 8;
+    bool has_zp        = false;
+    bool has_workspace = false;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.group, "group"), f(self.zp_const, "zp_const"), f(self.has_zp, "has_zp"),
+                    f(self.has_workspace, "has_workspace"));
+    }
+    std::string name() const { return "cuda::w4a16"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+} // namespace cuda
+} // namespace MIGRAPHX_INLINE_NS
+} // namespace migraphx
+#endif

@@ -1,0 +1,157 @@
+// The MIGraphX `cuda` target for B200: context, target, passes and models.
+//
+// Plug-in boundary (MIGraphX): src/include/migraphx/target.hpp:130-146 (name / get_passes /
+// get_context / copy_to / copy_from / allocate), context.hpp:93-111, operation.hpp:504-557,
+// register_target.hpp:53-73.  Everything below that boundary is host code that enqueues the
+// kernels of include/mgx_cuda.h on the context's CUDA stream.  There is no CPU fallback: an
+// instruction the target has no kernel for makes compile() throw.
+#ifndef MGX_CUDA_TARGET_HPP
+#define MGX_CUDA_TARGET_HPP
+
+#include <migraphx/config.hpp>
+#include <migraphx/argument.hpp>
+#include <migraphx/compile_options.hpp>
+#include <migraphx/context.hpp>
+#include <migraphx/instruction_ref.hpp>
+#include <migraphx/operation.hpp>
+#include <migraphx/pass.hpp>
+#include <migraphx/shape.hpp>
+#include <migraphx/value.hpp>
+#include <migraphx/any_ptr.hpp>
+#include <cuda_runtime.h>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace migraphx {
+inline namespace MIGRAPHX_INLINE_NS {
+struct module;
+struct module_pass_manager;
+namespace cuda {
+
+#define MGX_CUDA_EXPORT __attribute__((visibility("default")))
+
+// Throws a migraphx::exception when a CUDA runtime call or a kernel-library call failed.
+void check_cuda(cudaError_t e, const char* what);
+void check_mgx(int status, const char* what);
+
+// Device buffer of s.bytes() (+1, so that empty shapes still own an address) owned by the
+// returned argument (cudaFree on release).
+MGX_CUDA_EXPORT argument allocate_device(const shape& s);
+MGX_CUDA_EXPORT argument to_device(const argument& host);
+MGX_CUDA_EXPORT argument from_device(const argument& dev);
+
+struct context_state
+{
+    int device = 0;
+    std::vector<cudaStream_t> streams; // owned
+    std::vector<cudaEvent_t> events;   // owned, created on demand
+    std::size_t current   = 0;
+    cudaStream_t external = nullptr; // a caller's queue bound with set_queue()
+    bool has_external     = false;
+    cudaEvent_t begin_event  = nullptr;
+    cudaEvent_t finish_event = nullptr;
+    std::unordered_map<std::string, argument> preallocations;
+    bool ready = false;
+    context_state(int dev, std::size_t nstreams);
+    void init(); // creates the streams and events (first use)
+    ~context_state();
+    context_state(const context_state&)            = delete;
+    context_state& operator=(const context_state&) = delete;
+};
+
+// One per compiled program (program::compile, src/program.cpp:327); copies share state.
+struct MGX_CUDA_EXPORT context
+{
+    explicit context(int device = 0, std::size_t nstreams = 1);
+
+    int device() const { return state->device; }
+    std::size_t nstreams() const { return state->streams.size(); }
+    cudaStream_t stream() const;
+    void set_stream(std::size_t n);
+    cudaEvent_t event(std::size_t id);
+    void store_preallocation(const std::string& id, const argument& a);
+    argument get_preallocation(const std::string& id) const;
+
+    // migraphx::context interface
+    void finish() const;
+    value to_value() const;
+    void from_value(const value& v);
+    any_ptr get_queue();
+    void set_queue(any_ptr queue);
+    void restore_queue();
+    void wait_for(any_ptr queue);
+    void finish_on(any_ptr queue);
+
+    std::shared_ptr<context_state> state;
+};
+
+struct MGX_CUDA_EXPORT target
+{
+    std::string name() const;
+    std::vector<pass> get_passes(migraphx::context& ctx, const compile_options& options) const;
+    migraphx::context get_context() const;
+    argument copy_to(const argument& arg) const;
+    argument copy_from(const argument& arg) const;
+    argument allocate(const shape& s) const;
+};
+
+// allocation_model (src/include/migraphx/allocation_model.hpp:62-75)
+struct allocation_model
+{
+    std::string name() const { return "cuda::allocate"; }
+    std::string copy() const { return "cuda::copy"; }
+    operation allocate(const shape& s) const;
+    operation preallocate(const shape& s, const std::string& id) const;
+    bool needs_out_params() const { return true; }
+};
+
+// schedule_model (src/include/migraphx/schedule_model.hpp:65-78)
+struct schedule_model
+{
+    std::size_t streams = 1;
+    std::size_t concurrency() const { return streams; }
+    void sched(module& m, instruction_ref ins, std::size_t n) const;
+    void wait(module& m, instruction_ref ins, std::size_t wait_id) const;
+    void record(module& m, instruction_ref ins, std::size_t wait_id) const;
+    std::size_t weight(const operation& op) const;
+};
+
+// ---- passes -------------------------------------------------------------------------
+// Puts the instructions of `pointwise` sub-modules (the output of fuse_pointwise) back
+// into the enclosing module so that the lowering sees plain operator chains.
+struct inline_pointwise
+{
+    std::string name() const { return "cuda::inline_pointwise"; }
+    void apply(module& m) const;
+};
+
+// Replaces the quantized-GEMM sub-graphs by cuda::* operators and throws on anything the
+// target cannot run.
+struct lowering
+{
+    context* ctx      = nullptr;
+    bool offload_copy = false;
+    std::string name() const { return "cuda::lowering"; }
+    void apply(module_pass_manager& mpm) const;
+};
+
+// @literal -> cuda::literal (device-resident constant, uploaded at finalize).
+struct write_literals
+{
+    std::string name() const { return "cuda::write_literals"; }
+    void apply(module& m) const;
+};
+
+// Synchronises the stream before results copied to the host are returned.
+struct sync_device
+{
+    std::string name() const { return "cuda::sync_device"; }
+    void apply(module& m) const;
+};
+
+} // namespace cuda
+} // namespace MIGRAPHX_INLINE_NS
+} // namespace migraphx
+#endif

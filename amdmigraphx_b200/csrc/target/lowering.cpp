@@ -1,0 +1,735 @@
+// cuda::lowering - replaces the quantized-GEMM sub-graphs of a MIGraphX module by the
+// operators of the `cuda` target and refuses everything else (no CPU fallback).
+//
+// What arrives here (after simplify_qdq, src/simplify_qdq.cpp:225-290):
+//   quant_dot(xq, wq) -> dequantizelinear(acc, mul(bcast(x_scale), bcast(w_scale)))
+//        [-> convert(half)] [-> add(broadcast(bias))] [-> relu | erf-GELU] [-> add(residual)]
+// and, for weight-only int4 (src/onnx/parse_matmulnbits.cpp:85-158):
+//   dot(A, transpose(dequantizelinear(unpack_int4(packed), scales[N,K], zero_points[N,K])))
+// The HIP target does the equivalent in src/targets/gpu/lowering.cpp:62-613 (operator
+// replacement + output allocation) and src/targets/gpu/fuse_mlir.cpp:709-807, 1161-1276
+// (GEMM + pointwise / dequantize / unpack_int4 fusion); nothing is shared with that code.
+#include "cuda_ops.hpp"
+#include <migraphx/errors.hpp>
+#include <migraphx/instruction.hpp>
+#include <migraphx/iterator_for.hpp>
+#include <migraphx/literal.hpp>
+#include <migraphx/make_op.hpp>
+#include <migraphx/module.hpp>
+#include <migraphx/pass_manager.hpp>
+#include <migraphx/ranges.hpp>
+#include <migraphx/stringutils.hpp>
+#include <migraphx/half.hpp>
+#include "../../../include/mgx_cuda.h"
+#include <cmath>
+#include <cstring>
+#include <set>
+#include <unordered_set>
+
+namespace migraphx {
+inline namespace MIGRAPHX_INLINE_NS {
+namespace cuda {
+
+namespace {
+
+// Context-free operators whose compute() only re-describes the buffer (no data is read):
+// they work on device pointers unchanged.
+bool is_view_op(const std::string& n)
+{
+    static const std::set<std::string> views = {
+        "broadcast", "multibroadcast", "transpose", "reshape_lazy", "squeeze", "unsqueeze",
+        "flatten", "slice", "identity", "load", "get_tuple_elem", "step"};
+    return views.count(n) > 0;
+}
+
+bool is_builtin(const std::string& n) { return not n.empty() and n.front() == '@'; }
+
+instruction_ref insert_allocation(module& m, instruction_ref pos, const shape& s)
+{
+    return m.insert_instruction(pos, make_op("allocate", {{"shape", to_value(s)}}));
+}
+
+// Host copy of a constant instruction's value as fp32, element by element in logical order.
+std::vector<float> eval_as_floats(instruction_ref ins)
+{
+    argument a = ins->eval();
+    if(a.empty())
+        MIGRAPHX_THROW("cuda::lowering: expected a compile-time constant");
+    std::vector<float> out(a.get_shape().elements());
+    a.visit([&](auto v) {
+        std::size_t i = 0;
+        for(auto x : v)
+            out[i++] = static_cast<float>(x);
+    });
+    return out;
+}
+
+enum class bcast_kind
+{
+    scalar,
+    per_col,
+    per_row,
+    full
+};
+
+struct const_vector
+{
+    bcast_kind kind = bcast_kind::full;
+    std::vector<float> values; // 1, cols or rows values
+};
+
+// Classifies a constant of the data tensor's dims seen as [rows, cols].
+const_vector classify_constant(instruction_ref ins)
+{
+    const auto& s    = ins->get_shape();
+    const auto vals  = eval_as_floats(ins);
+    const_vector r;
+    if(vals.empty())
+        return r;
+    const std::size_t cols = s.ndim() == 0 ? 1 : s.lens().back();
+    const std::size_t rows = vals.size() / cols;
+    auto same              = [](float a, float b) { return std::memcmp(&a, &b, sizeof(float)) == 0; };
+    bool all_same = true, col_const = true, row_const = true;
+    for(std::size_t i = 0; i < vals.size() and (all_same or col_const or row_const); ++i)
+    {
+        const std::size_t rr = i / cols, cc = i % cols;
+        if(not same(vals[i], vals[0]))
+            all_same = false;
+        if(not same(vals[i], vals[cc]))
+            col_const = false; // differs from row 0 in the same column
+        if(not same(vals[i], vals[rr * cols]))
+            row_const = false; // differs from column 0 in the same row
+    }
+    if(all_same)
+    {
+        r.kind   = bcast_kind::scalar;
+        r.values = {vals[0]};
+    }
+    else if(col_const)
+    {
+        r.kind = bcast_kind::per_col;
+        r.values.assign(vals.begin(), vals.begin() + cols);
+    }
+    else if(row_const and s.ndim() == 2)
+    {
+        r.kind = bcast_kind::per_row;
+        r.values.resize(rows);
+        for(std::size_t i = 0; i < rows; ++i)
+            r.values[i] = vals[i * cols];
+    }
+    return r;
+}
+
+bool is_const_scalar(instruction_ref ins, float expect, float tol)
+{
+    if(not ins->can_eval())
+        return false;
+    auto c = classify_constant(ins);
+    return c.kind == bcast_kind::scalar and std::fabs(c.values[0] - expect) <= tol;
+}
+
+instruction_ref other_input(instruction_ref ins, instruction_ref x)
+{
+    return ins->inputs()[0] == x ? ins->inputs()[1] : ins->inputs()[0];
+}
+
+instruction_ref single_user(const module& m, instruction_ref ins)
+{
+    return ins->outputs().size() == 1 ? ins->outputs().front() : m.end();
+}
+
+bool valid(instruction_ref ins, const module& m) { return ins != m.end(); }
+
+// Matches the erf-GELU instruction sequence of src/op/builder/gelu.cpp:58-74 rooted at x:
+//   mul(x, 0.5), div(x, sqrt(2)) -> erf -> add(., 1), mul(mul_half, add_one).
+// Returns the final mul, or m.end().
+instruction_ref match_gelu_erf(const module& m, instruction_ref x, std::vector<instruction_ref>& chain)
+{
+    if(x->outputs().size() != 2)
+        return m.end();
+    instruction_ref mul_half = m.end(), div = m.end();
+    for(auto u : x->outputs())
+    {
+        if(u->name() == "mul" and is_const_scalar(other_input(u, x), 0.5f, 1e-6f))
+            mul_half = u;
+        else if(u->name() == "div" and u->inputs()[0] == x and
+                is_const_scalar(u->inputs()[1], 1.41421356f, 1e-3f))
+            div = u;
+    }
+    if(mul_half == m.end() or div == m.end())
+        return m.end();
+    auto erf = single_user(m, div);
+    if(not valid(erf, m) or erf->name() != "erf")
+        return m.end();
+    auto add_one = single_user(m, erf);
+    if(not valid(add_one, m) or add_one->name() != "add" or
+       not is_const_scalar(other_input(add_one, erf), 1.0f, 1e-6f))
+        return m.end();
+    auto fin = single_user(m, add_one);
+    if(not valid(fin, m) or fin->name() != "mul" or single_user(m, mul_half) != fin)
+        return m.end();
+    chain.insert(chain.end(), {mul_half, div, erf, add_one, fin});
+    return fin;
+}
+
+instruction_ref add_float_literal(module& m, const std::vector<float>& v)
+{
+    return m.add_literal(literal{shape{shape::float_type, {v.size()}}, v});
+}
+
+// A constant 8-bit matrix [.., K, N] (any strides) as a standard [.., N, K] literal.
+instruction_ref add_transposed_8bit_literal(module& m, instruction_ref b)
+{
+    argument a    = b->eval();
+    const auto& s = a.get_shape();
+    const auto nd = s.ndim();
+    auto lens     = s.lens();
+    const std::size_t k = lens[nd - 2], n = lens[nd - 1];
+    std::size_t batch = 1;
+    for(std::size_t i = 0; i + 2 < nd; ++i)
+        batch *= lens[i];
+    std::vector<char> out(batch * n * k);
+    const char* src = a.data();
+    std::vector<std::size_t> idx(nd, 0);
+    for(std::size_t bi = 0; bi < batch; ++bi)
+    {
+        std::size_t rem = bi;
+        for(std::size_t d = nd - 2; d-- > 0;)
+        {
+            idx[d] = rem % lens[d];
+            rem /= lens[d];
+        }
+        for(std::size_t kk = 0; kk < k; ++kk)
+        {
+            idx[nd - 2] = kk;
+            for(std::size_t nn = 0; nn < n; ++nn)
+            {
+                idx[nd - 1] = nn;
+                out[(bi * n + nn) * k + kk] = src[s.index(idx)];
+            }
+        }
+    }
+    std::swap(lens[nd - 2], lens[nd - 1]);
+    return m.add_literal(literal{shape{s.type(), lens}, out.data()});
+}
+
+} // namespace
+
+namespace {
+
+struct lowerer
+{
+    module& m;
+    std::unordered_set<instruction*> consumed; // fused into an earlier replacement
+
+    void consume(instruction_ref ins) { consumed.insert(&*ins); }
+    bool is_consumed(instruction_ref ins) const { return consumed.count(&*ins) > 0; }
+
+    [[noreturn]] void unsupported(instruction_ref ins, const std::string& why) const
+    {
+        MIGRAPHX_THROW("cuda target: cannot run '" + ins->name() + "' (" + why +
+                       "); the target has no CPU fallback");
+    }
+
+    // ---------------------------------------------------------------- quant_dot chain
+    void lower_quant_dot(instruction_ref qd)
+    {
+        if(qd->inputs().size() != 2)
+            unsupported(qd, "only the two-operand form is supported");
+        auto a = qd->inputs()[0];
+        auto b = qd->inputs()[1];
+        const auto in_type = a->get_shape().type();
+        if(in_type != shape::int8_type and in_type != shape::fp8e4m3fn_type)
+            unsupported(qd, "operands must be int8 or fp8e4m3fn");
+
+        op_qgemm op;
+        op.out_type = static_cast<int>(qd->get_shape().type()); // int32 or float
+        std::vector<instruction_ref> chain; // instructions folded into the epilogue
+        instruction_ref last  = qd;
+        instruction_ref scale = m.end(), bias = m.end(), residual = m.end();
+
+        // dequantizelinear(acc, constant scale) without zero point
+        auto dq = single_user(m, last);
+        if(valid(dq, m) and dq->name() == "dequantizelinear" and dq->inputs().size() == 2 and
+           dq->inputs()[0] == last and dq->inputs()[1]->can_eval() and
+           dq->get_shape().type() == shape::float_type)
+        {
+            auto c = classify_constant(dq->inputs()[1]);
+            if(c.kind != bcast_kind::full)
+            {
+                op.scale_mode = c.kind == bcast_kind::scalar
+                                    ? MGX_SCALE_PER_TENSOR
+                                    : (c.kind == bcast_kind::per_col ? MGX_SCALE_PER_COL
+                                                                     : MGX_SCALE_PER_ROW);
+                scale       = add_float_literal(m, c.values);
+                op.out_type = static_cast<int>(shape::float_type);
+                chain.push_back(dq);
+                last = dq;
+            }
+        }
+        if(last != qd or in_type == shape::fp8e4m3fn_type)
+        {
+            // the rest of the epilogue only follows a float value
+            bool progress = true;
+            bool seen_act = false;
+            while(progress)
+            {
+                progress = false;
+                auto u   = single_user(m, last);
+                if(not valid(u, m) or last->get_shape().type() == shape::int32_type)
+                    break;
+                if(u->name() == "convert" and u->get_shape().type() == shape::half_type and
+                   residual == m.end() and
+                   static_cast<shape::type_t>(op.out_type) == shape::float_type)
+                {
+                    op.out_type = static_cast<int>(shape::half_type);
+                    chain.push_back(u);
+                    last     = u;
+                    progress = true;
+                    continue;
+                }
+                if(u->name() == "add" and residual == m.end())
+                {
+                    auto other = other_input(u, last);
+                    if(other->can_eval() and bias == m.end() and not seen_act)
+                    {
+                        auto c = classify_constant(other);
+                        if(c.kind == bcast_kind::per_col or c.kind == bcast_kind::scalar)
+                        {
+                            std::vector<float> v = c.values;
+                            if(c.kind == bcast_kind::scalar)
+                                v.assign(u->get_shape().lens().back(), c.values[0]);
+                            bias = add_float_literal(m, v);
+                            chain.push_back(u);
+                            last     = u;
+                            progress = true;
+                            continue;
+                        }
+                    }
+                    else if(not other->can_eval() and other->get_shape() == u->get_shape() and
+                            other->get_shape().standard())
+                    {
+                        residual = other;
+                        chain.push_back(u);
+                        last     = u;
+                        progress = true;
+                        continue;
+                    }
+                }
+                if(u->name() == "relu" and not seen_act and residual == m.end())
+                {
+                    op.act   = MGX_ACT_RELU;
+                    seen_act = true;
+                    chain.push_back(u);
+                    last     = u;
+                    progress = true;
+                    continue;
+                }
+            }
+            if(not seen_act and residual == m.end())
+            {
+                std::vector<instruction_ref> g;
+                auto fin = match_gelu_erf(m, last, g);
+                if(fin != m.end())
+                {
+                    op.act = MGX_ACT_GELU_ERF;
+                    chain.insert(chain.end(), g.begin(), g.end());
+                    last = fin;
+                    // a residual add may still follow the activation
+                    auto u = single_user(m, last);
+                    if(valid(u, m) and u->name() == "add")
+                    {
+                        auto other = other_input(u, last);
+                        if(not other->can_eval() and other->get_shape() == u->get_shape() and
+                           other->get_shape().standard())
+                        {
+                            residual = other;
+                            chain.push_back(u);
+                            last = u;
+                        }
+                    }
+                }
+            }
+        }
+        if(static_cast<shape::type_t>(op.out_type) != last->get_shape().type())
+            op.out_type = static_cast<int>(last->get_shape().type());
+        if(residual != m.end() and residual->get_shape().type() != last->get_shape().type())
+            unsupported(last, "residual type differs from the output type");
+
+        // B operand: constants are re-laid out K-contiguous once, here
+        std::vector<instruction_ref> args = {a, b};
+        instruction_ref workspace = m.end();
+        if(b->can_eval())
+        {
+            args[1]  = add_transposed_8bit_literal(m, b);
+            op.b_nk  = true;
+        }
+        else
+        {
+            if(not b->get_shape().standard())
+                unsupported(qd, "a non-constant right operand must be a standard [K,N] tensor");
+            const auto& bl       = b->get_shape().lens();
+            const std::size_t k  = bl[bl.size() - 2];
+            const std::size_t kp = (k + 15) / 16 * 16;
+            const std::size_t ws = b->get_shape().elements() / k * kp;
+            workspace            = insert_allocation(m, last, shape{shape::int8_type, {ws}});
+            op.has_workspace     = true;
+        }
+        if(op.scale_mode != MGX_SCALE_NONE)
+            args.push_back(scale);
+        if(bias != m.end())
+        {
+            op.has_bias = true;
+            args.push_back(bias);
+        }
+        if(residual != m.end())
+        {
+            op.has_residual = true;
+            args.push_back(residual);
+        }
+        if(workspace != m.end())
+            args.push_back(workspace);
+        args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+        for(auto c : chain)
+        {
+            consume(c);
+            // constant operands used only by the fused chain need no folding of their own
+            for(auto i : c->inputs())
+                if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
+                    consume(i);
+        }
+        consume(qd);
+        auto rep = m.replace_instruction(last, op, args);
+        consume(rep);
+    }
+
+    // ---------------------------------------------------------------- weight-only int4
+    // dot(A, transpose(dequantizelinear(unpack_int4(packed), scales, [zero points])))
+    bool lower_w4a16(instruction_ref dot)
+    {
+        if(dot->inputs().size() != 2)
+            return false;
+        auto a  = dot->inputs()[0];
+        auto bt = dot->inputs()[1];
+        if(a->get_shape().type() != shape::half_type or bt->name() != "transpose" or
+           bt->get_shape().ndim() != 2)
+            return false;
+        auto dq = bt->inputs()[0];
+        if(dq->name() != "dequantizelinear" or dq->get_shape().type() != shape::half_type)
+            return false;
+        auto unpack = dq->inputs()[0];
+        if(unpack->name() != "unpack_int4" or unpack->get_shape().type() != shape::uint8_type)
+            return false;
+        auto packed = unpack->inputs()[0];
+        if(not packed->get_shape().standard() or packed->get_shape().ndim() != 2)
+            return false;
+        if(not dq->inputs()[1]->can_eval())
+            unsupported(dot, "int4 scales must be compile-time constants");
+        if(dq->inputs().size() == 3 and not dq->inputs()[2]->can_eval())
+            unsupported(dot, "int4 zero points must be compile-time constants");
+        const std::size_t n = unpack->get_shape().lens()[0];
+        const std::size_t k = unpack->get_shape().lens()[1];
+        if(a->get_shape().lens().back() != k or not a->get_shape().standard())
+            return false;
+
+        // group size: the largest divisor g of K (a multiple of 32) for which scales and
+        // zero points are constant inside every run of g columns
+        const auto sv = eval_as_floats(dq->inputs()[1]);
+        std::vector<float> zv;
+        if(dq->inputs().size() == 3)
+            zv = eval_as_floats(dq->inputs()[2]);
+        auto blocks_const = [&](const std::vector<float>& v, std::size_t g) {
+            for(std::size_t r = 0; r < n; ++r)
+                for(std::size_t c = 0; c < k; ++c)
+                    if(v[r * k + c] != v[r * k + (c / g) * g])
+                        return false;
+            return true;
+        };
+        std::size_t group = 0;
+        for(std::size_t g = k; g >= 32; g /= 2)
+        {
+            if(k % g != 0 or g % 32 != 0)
+                continue;
+            if(blocks_const(sv, g) and (zv.empty() or blocks_const(zv, g)))
+            {
+                group = g;
+                break;
+            }
+            if(g % 2 != 0)
+                break;
+        }
+        if(group == 0)
+            unsupported(dot, "int4 group size must be a multiple of 32 dividing K");
+        const std::size_t gpr = k / group;
+        std::vector<half> scales(n * gpr);
+        for(std::size_t r = 0; r < n; ++r)
+            for(std::size_t g = 0; g < gpr; ++g)
+                scales[r * gpr + g] = half(sv[r * k + g * group]);
+        op_w4a16 op;
+        op.group = static_cast<int>(group);
+        std::vector<instruction_ref> args = {
+            a, packed, m.add_literal(literal{shape{shape::half_type, {n, gpr}}, scales})};
+        if(not zv.empty())
+        {
+            bool uniform = true;
+            for(auto z : zv)
+                if(z != zv[0])
+                    uniform = false;
+            if(uniform)
+                op.zp_const = static_cast<int>(zv[0]);
+            else
+            {
+                std::vector<uint8_t> zps(n * gpr);
+                for(std::size_t r = 0; r < n; ++r)
+                    for(std::size_t g = 0; g < gpr; ++g)
+                        zps[r * gpr + g] = static_cast<uint8_t>(zv[r * k + g * group]);
+                op.has_zp = true;
+                args.push_back(m.add_literal(literal{shape{shape::uint8_type, {n, gpr}}, zps}));
+            }
+        }
+        else
+            op.zp_const = 0;
+        mgx_w4_desc d{};
+        d.M = static_cast<int64_t>(a->get_shape().elements() / k);
+        d.N = static_cast<int64_t>(n);
+        d.K = static_cast<int64_t>(k);
+        d.group = op.group;
+        const std::size_t ws = mgx_cuda_w4a16_workspace(&d);
+        if(ws > 0)
+        {
+            op.has_workspace = true;
+            args.push_back(insert_allocation(m, dot, shape{shape::int8_type, {ws}}));
+        }
+        args.push_back(insert_allocation(m, dot, dot->get_shape().as_standard()));
+        consume(bt);
+        consume(dq);
+        consume(unpack);
+        for(std::size_t i = 1; i < dq->inputs().size(); ++i)
+            if(dq->inputs()[i]->outputs().size() == 1 and not is_builtin(dq->inputs()[i]->name()))
+                consume(dq->inputs()[i]);
+        auto rep = m.replace_instruction(dot, op, args);
+        consume(rep);
+        return true;
+    }
+
+    // ---------------------------------------------------------------- single operators
+    template <class Op>
+    void lower_elementwise(instruction_ref ins, Op op)
+    {
+        auto args = ins->inputs();
+        op.has_zp = args.size() == 3;
+        if(not args[0]->get_shape().standard() and args[0]->get_shape().ndim() != 2)
+            unsupported(ins, "input must be standard or a 2-D row-strided view");
+        args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
+        consume(m.replace_instruction(ins, op, args));
+    }
+
+    template <class Op>
+    void lower_int4(instruction_ref ins, Op op)
+    {
+        const auto v  = ins->get_operator().to_value();
+        const auto nd = static_cast<int64_t>(ins->get_shape().ndim());
+        const auto ax = v.contains("axis") ? v.at("axis").template to<int64_t>() : -1;
+        if(ax != -1 and ax != nd - 1)
+            unsupported(ins, "only the last axis is supported");
+        if(not ins->inputs()[0]->get_shape().standard())
+            unsupported(ins, "input must be a standard tensor");
+        auto args = ins->inputs();
+        args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
+        consume(m.replace_instruction(ins, op, args));
+    }
+
+    bool skip(instruction_ref ins) const
+    {
+        if(is_consumed(ins))
+            return true;
+        const auto name = ins->name();
+        if(is_builtin(name) or is_view_op(name) or name == "allocate" or starts_with(name, "cuda::"))
+            return true;
+        // dead: removed by dead_code_elimination
+        return ins->outputs().empty() and ins != std::prev(m.end());
+    }
+
+    void run()
+    {
+        std::vector<instruction_ref> order;
+        for(auto ins : iterator_for(m))
+            order.push_back(ins);
+        // GEMM sub-graphs first: their operands (packed int4 weights, scale expressions) must
+        // still be in their original form, not folded into dense constants
+        for(auto ins : order)
+        {
+            if(skip(ins))
+                continue;
+            if(ins->name() == "quant_dot")
+                lower_quant_dot(ins);
+            else if(ins->name() == "dot")
+            {
+                if(not lower_w4a16(ins))
+                    unsupported(ins, "only the weight-only int4 form "
+                                     "dot(A, transpose(dequantizelinear(unpack_int4(W)))) is supported");
+            }
+        }
+        for(auto ins : order)
+        {
+            if(skip(ins))
+                continue;
+            const auto name = ins->name();
+            if(ins->can_eval())
+            {
+                // a constant sub-graph (e.g. quantizelinear of a weight literal) is
+                // evaluated once, now, and becomes a literal
+                argument v = ins->eval();
+                argument sv = v.get_shape().standard() ? v : make_standard(v);
+                m.replace_instruction(ins, m.add_literal(literal{sv.get_shape(), sv.data()}));
+                continue;
+            }
+            if(name == "quantizelinear")
+                lower_elementwise(ins, op_quantizelinear{});
+            else if(name == "dequantizelinear")
+                lower_elementwise(ins, op_dequantizelinear{});
+            else if(name == "unpack_int4")
+                lower_int4(ins, op_unpack_int4{});
+            else if(name == "pack_int4")
+                lower_int4(ins, op_pack_int4{});
+            else
+                unsupported(ins, "no kernel");
+        }
+    }
+
+    // packed row-major copy of a host argument with arbitrary strides
+    static argument make_standard(const argument& v)
+    {
+        argument out{v.get_shape().as_standard()};
+        const auto& s      = v.get_shape();
+        const std::size_t es = s.type_size();
+        for(std::size_t i = 0; i < s.elements(); ++i)
+            std::memcpy(out.data() + i * es, v.data() + s.index(i) * es, es);
+        return out;
+    }
+};
+
+} // namespace
+
+void lowering::apply(module_pass_manager& mpm) const
+{
+    module& m = mpm.get_module();
+    lowerer l{m, {}};
+    l.run();
+    if(not offload_copy)
+        return;
+    // offload_copy: parameters arrive as host buffers and results are returned on the host
+    // (compile_options.hpp:33-45; the HIP target does this in src/targets/gpu/lowering.cpp:122-161)
+    std::vector<instruction_ref> params;
+    for(auto ins : iterator_for(m))
+        if(ins->name() == "@param" and not ins->outputs().empty())
+            params.push_back(ins);
+    for(auto p : params)
+    {
+        auto pos   = std::next(p);
+        auto alloc = insert_allocation(m, pos, p->get_shape());
+        auto c     = m.insert_instruction(pos, op_copy_to{}, p, alloc);
+        m.replace_instruction(p, c);
+    }
+    auto ret = std::prev(m.end());
+    if(ret->name() == "@return")
+    {
+        for(const auto& in : std::vector<instruction_ref>(ret->inputs()))
+        {
+            auto h = m.insert_instruction(ret, op_copy_from{}, in);
+            instruction::replace_argument(ret, in, h);
+        }
+    }
+    else
+        m.add_instruction(op_copy_from{}, ret);
+}
+
+// ------------------------------------------------------------------ inline_pointwise
+void inline_pointwise::apply(module& m) const
+{
+    std::vector<instruction_ref> pws;
+    for(auto ins : iterator_for(m))
+        if(ins->name() == "pointwise")
+            pws.push_back(ins);
+    for(auto ins : pws)
+    {
+        auto* pm    = ins->module_inputs().front();
+        auto pnames = pm->get_parameter_names();
+        std::sort(pnames.begin(), pnames.end());
+        std::unordered_map<instruction_ref, instruction_ref> map;
+        const auto& inputs = ins->inputs();
+        const auto lens    = ins->get_shape().lens();
+        instruction_ref result = m.end();
+        for(auto sub : iterator_for(*pm))
+        {
+            if(sub->name() == "@param")
+            {
+                const auto pname = any_cast<builtin::param>(sub->get_operator()).parameter;
+                const auto pos   = std::find(pnames.begin(), pnames.end(), pname) - pnames.begin();
+                map[sub]         = inputs.at(pos);
+            }
+            else if(sub->name() == "@literal")
+            {
+                auto l   = m.add_literal(sub->get_literal());
+                map[sub] = m.insert_instruction(
+                    ins, make_op("multibroadcast", {{"out_lens", lens}}), l);
+            }
+            else if(sub->name() == "@return")
+            {
+                result = map.at(sub->inputs().front());
+            }
+            else
+            {
+                std::vector<instruction_ref> args;
+                for(auto i : sub->inputs())
+                    args.push_back(map.at(i));
+                map[sub] = m.insert_instruction(ins, sub->get_operator(), args);
+                result   = map[sub];
+            }
+        }
+        if(result == m.end())
+            MIGRAPHX_THROW("cuda::inline_pointwise: empty pointwise module");
+        m.replace_instruction(ins, result);
+    }
+}
+
+// ------------------------------------------------------------------ write_literals
+void write_literals::apply(module& m) const
+{
+    std::size_t n = 0;
+    for(auto ins : iterator_for(m))
+    {
+        if(ins->name() != "@literal")
+            continue;
+        if(ins->outputs().empty())
+            continue;
+        op_literal op;
+        op.l  = ins->get_literal();
+        op.id = m.name() + ":@literal:" + std::to_string(n++);
+        m.replace_instruction(ins, op);
+    }
+}
+
+// ------------------------------------------------------------------ sync_device
+void sync_device::apply(module& m) const
+{
+    auto last = std::prev(m.end());
+    if(last->name() != "@return")
+        return;
+    // results that stay on the device: make sure the work that produces them has been
+    // submitted and finished before eval() hands the buffers back
+    auto inputs = last->inputs();
+    if(inputs.empty())
+        return;
+    const bool all_host = std::all_of(inputs.begin(), inputs.end(), [](auto i) {
+        return i->name() == "cuda::copy_from";
+    });
+    if(all_host)
+        return; // copy_from already synchronises
+    auto sync = m.insert_instruction(last, op_sync_stream{}, inputs.front());
+    instruction::replace_argument(last, inputs.front(), sync);
+}
+
+} // namespace cuda
+} // namespace MIGRAPHX_INLINE_NS
+} // namespace migraphx

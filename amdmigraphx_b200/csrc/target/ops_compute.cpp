@@ -1,0 +1,305 @@
+// The compute operators of the `cuda` target: thin host wrappers that turn MIGraphX
+// arguments (shapes with strides, broadcast views) into calls of the C ABI in
+// include/mgx_cuda.h on the context's stream.
+#include "cuda_ops.hpp"
+#include <migraphx/check_shapes.hpp>
+#include <migraphx/errors.hpp>
+#include <migraphx/register_op.hpp>
+#include "../../../include/mgx_cuda.h"
+
+namespace migraphx {
+inline namespace MIGRAPHX_INLINE_NS {
+namespace cuda {
+
+namespace {
+
+int mgx_type(shape::type_t t)
+{
+    switch(t)
+    {
+    case shape::float_type: return MGX_F32;
+    case shape::half_type: return MGX_F16;
+    case shape::int8_type: return MGX_I8;
+    case shape::uint8_type: return MGX_U8;
+    case shape::int32_type: return MGX_I32;
+    case shape::fp8e4m3fn_type: return MGX_FP8_E4M3FN;
+    default: MIGRAPHX_THROW("cuda target: element type not supported by the kernels");
+    }
+}
+
+struct rows_cols
+{
+    int64_t rows = 0, cols = 0, ld = 0;
+};
+
+// A data tensor seen as [rows, cols] with a row stride: the last axis is the column axis.
+rows_cols as_matrix(const shape& s, const char* what)
+{
+    rows_cols r;
+    if(s.ndim() == 0 or s.elements() == 0)
+        return r;
+    r.cols = static_cast<int64_t>(s.lens().back());
+    r.rows = static_cast<int64_t>(s.elements()) / r.cols;
+    if(s.standard())
+    {
+        r.ld = r.cols;
+        return r;
+    }
+    if(s.ndim() == 2 and (s.strides()[1] == 1 or r.cols == 1) and
+       static_cast<int64_t>(s.strides()[0]) >= r.cols)
+    {
+        r.ld = static_cast<int64_t>(s.strides()[0]);
+        return r;
+    }
+    MIGRAPHX_THROW(std::string("cuda target: ") + what + " needs a standard or row-strided tensor");
+}
+
+// Strides (elements) with which a scale / zero-point view of the data tensor's dims is
+// indexed as [rows, cols]: MIGraphX hands these operands over as broadcast views
+// (stride 0 along broadcast axes; src/simplify_qdq.cpp:106-117).
+void bcast_strides(const shape& s, const rows_cols& m, int64_t out[2], const char* what)
+{
+    const auto& st = s.strides();
+    const auto& ln = s.lens();
+    const auto n   = s.ndim();
+    out[1]         = (n == 0 or ln.back() == 1) ? 0 : static_cast<int64_t>(st.back());
+    bool lead_zero = true;
+    for(std::size_t i = 0; i + 1 < n; ++i)
+        if(ln[i] != 1 and st[i] != 0)
+            lead_zero = false;
+    if(lead_zero)
+    {
+        out[0] = 0;
+        return;
+    }
+    if(s.standard())
+    {
+        out[0] = m.cols;
+        out[1] = 1;
+        return;
+    }
+    if(n == 2)
+    {
+        out[0] = static_cast<int64_t>(st[0]);
+        return;
+    }
+    MIGRAPHX_THROW(std::string("cuda target: ") + what + " view cannot be indexed as [rows, cols]");
+}
+
+} // namespace
+
+// ------------------------------------------------------------------ quantizelinear
+shape op_quantizelinear::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(has_zp ? 4 : 3);
+    return inputs.back();
+}
+
+argument op_quantizelinear::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& xs  = args[0].get_shape();
+    const auto& out = args.back();
+    const auto m    = as_matrix(xs, "quantizelinear input");
+    const auto mo   = as_matrix(out.get_shape(), "quantizelinear output");
+    int64_t ss[2] = {0, 0}, zs[2] = {0, 0};
+    bcast_strides(args[1].get_shape(), m, ss, "quantizelinear scale");
+    if(has_zp)
+        bcast_strides(args[2].get_shape(), m, zs, "quantizelinear zero point");
+    check_mgx(mgx_cuda_quantizelinear(args[0].data(), mgx_type(xs.type()), m.ld, args[1].data(), ss,
+                                      has_zp ? args[2].data() : nullptr, zs, out.data(),
+                                      mgx_type(out.get_shape().type()), mo.ld, m.rows, m.cols,
+                                      ctx.stream()),
+              "mgx_cuda_quantizelinear");
+    return out;
+}
+
+// ------------------------------------------------------------------ dequantizelinear
+shape op_dequantizelinear::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(has_zp ? 4 : 3);
+    return inputs.back();
+}
+
+argument op_dequantizelinear::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& xs  = args[0].get_shape();
+    const auto& out = args.back();
+    const auto m    = as_matrix(xs, "dequantizelinear input");
+    const auto mo   = as_matrix(out.get_shape(), "dequantizelinear output");
+    int64_t ss[2] = {0, 0}, zs[2] = {0, 0};
+    bcast_strides(args[1].get_shape(), m, ss, "dequantizelinear scale");
+    if(has_zp)
+        bcast_strides(args[2].get_shape(), m, zs, "dequantizelinear zero point");
+    check_mgx(mgx_cuda_dequantizelinear(args[0].data(), mgx_type(xs.type()), m.ld, args[1].data(),
+                                        mgx_type(args[1].get_shape().type()), ss,
+                                        has_zp ? args[2].data() : nullptr, zs, out.data(), mo.ld,
+                                        m.rows, m.cols, ctx.stream()),
+              "mgx_cuda_dequantizelinear");
+    return out;
+}
+
+// ------------------------------------------------------------------ int4 pack / unpack
+shape op_unpack_int4::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(2).standard();
+    return inputs.back();
+}
+argument op_unpack_int4::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto m = as_matrix(args[0].get_shape(), "unpack_int4 input");
+    check_mgx(mgx_cuda_unpack_int4(args[0].data(), args[1].data(),
+                                   mgx_type(args[0].get_shape().type()), m.rows, m.cols, ctx.stream()),
+              "mgx_cuda_unpack_int4");
+    return args[1];
+}
+
+shape op_pack_int4::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(2).standard();
+    return inputs.back();
+}
+argument op_pack_int4::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto m = as_matrix(args[1].get_shape(), "pack_int4 output");
+    check_mgx(mgx_cuda_pack_int4(args[0].data(), args[1].data(), mgx_type(args[0].get_shape().type()),
+                                 m.rows, m.cols, ctx.stream()),
+              "mgx_cuda_pack_int4");
+    return args[1];
+}
+
+// ------------------------------------------------------------------ quant_dot (+ epilogue)
+shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
+{
+    const std::size_t expect = 3 + (scale_mode != MGX_SCALE_NONE) + has_bias + has_residual + has_workspace;
+    check_shapes{inputs, *this}.has(expect);
+    const auto& a = inputs[0];
+    const auto& b = inputs[1];
+    if(a.ndim() < 2 or b.ndim() != a.ndim())
+        MIGRAPHX_THROW("cuda::qgemm: operands must have the same rank >= 2");
+    if(a.type() != b.type())
+        MIGRAPHX_THROW("cuda::qgemm: operand types differ");
+    const auto k  = a.lens().back();
+    const auto kb = b_nk ? b.lens().back() : b.lens()[b.ndim() - 2];
+    if(k != kb)
+        MIGRAPHX_THROW("cuda::qgemm: inner dimensions differ");
+    auto lens   = a.lens();
+    lens.back() = b_nk ? b.lens()[b.ndim() - 2] : b.lens().back();
+    const shape expected{static_cast<shape::type_t>(out_type), lens};
+    if(inputs.back().lens() != expected.lens() or inputs.back().type() != expected.type())
+        MIGRAPHX_THROW("cuda::qgemm: output buffer does not match the result shape");
+    return inputs.back();
+}
+
+argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    std::size_t i          = 2;
+    const argument* scale  = scale_mode != MGX_SCALE_NONE ? &args[i++] : nullptr;
+    const argument* bias   = has_bias ? &args[i++] : nullptr;
+    const argument* resid  = has_residual ? &args[i++] : nullptr;
+    const argument* wspace = has_workspace ? &args[i++] : nullptr;
+    const argument& out    = args.back();
+    const auto& as         = args[0].get_shape();
+    const auto& bs         = args[1].get_shape();
+    const auto& ds         = out.get_shape();
+    const auto nd          = as.ndim();
+    if(not ds.standard())
+        MIGRAPHX_THROW("cuda::qgemm: output must be a standard tensor");
+    if(resid != nullptr and resid->get_shape() != ds)
+        MIGRAPHX_THROW("cuda::qgemm: residual must have the output's shape");
+
+    mgx_qgemm_desc d{};
+    d.M = static_cast<int64_t>(as.lens()[nd - 2]);
+    d.K = static_cast<int64_t>(as.lens()[nd - 1]);
+    d.N = static_cast<int64_t>(ds.lens()[nd - 1]);
+    int64_t batch = 1;
+    for(std::size_t j = 0; j + 2 < nd; ++j)
+        batch *= static_cast<int64_t>(as.lens()[j]);
+    if(as.strides()[nd - 1] != 1 and d.K != 1)
+        MIGRAPHX_THROW("cuda::qgemm: A must be K-contiguous");
+    d.lda = static_cast<int64_t>(as.strides()[nd - 2]);
+    d.ldb = static_cast<int64_t>(bs.strides()[nd - 2]);
+    d.ldd = d.N;
+    if(bs.strides()[nd - 1] != 1)
+        MIGRAPHX_THROW("cuda::qgemm: B must be contiguous along its last axis");
+    bool b_shared = true; // B is the same matrix for every batch entry (broadcast view)
+    for(std::size_t j = 0; j + 2 < nd; ++j)
+        if(bs.lens()[j] != 1 and bs.strides()[j] != 0)
+            b_shared = false;
+    if(batch > 1)
+    {
+        // batch entries must be evenly spaced: standard leading dimensions
+        const auto rows_a = static_cast<int64_t>(as.strides()[nd - 3]);
+        d.stride_a        = rows_a;
+        d.stride_d        = d.M * d.N;
+        if(b_shared and rows_a == d.M * d.lda)
+        {
+            // one weight matrix for all entries: fold the batch into the rows
+            d.M *= batch;
+            batch = 1;
+        }
+        else
+            d.stride_b = static_cast<int64_t>(bs.strides()[nd - 3]);
+    }
+    d.batch      = batch;
+    d.ab_type    = mgx_type(as.type());
+    d.out_type   = mgx_type(ds.type());
+    d.b_layout   = b_nk ? MGX_B_NK : MGX_B_KN;
+    d.scale_mode = scale_mode;
+    d.act        = act;
+    check_mgx(mgx_cuda_qgemm(&d, args[0].data(), args[1].data(), out.data(),
+                             scale != nullptr ? reinterpret_cast<const float*>(scale->data()) : nullptr,
+                             bias != nullptr ? reinterpret_cast<const float*>(bias->data()) : nullptr,
+                             resid != nullptr ? resid->data() : nullptr,
+                             wspace != nullptr ? wspace->data() : nullptr,
+                             wspace != nullptr ? wspace->get_shape().bytes() : 0, ctx.stream()),
+              "mgx_cuda_qgemm");
+    return out;
+}
+
+// ------------------------------------------------------------------ weight-only int4 linear
+shape op_w4a16::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(4 + has_zp + has_workspace);
+    const auto& a  = inputs[0];
+    const auto& bp = inputs[1];
+    if(a.type() != shape::half_type or bp.type() != shape::uint8_type or bp.ndim() != 2)
+        MIGRAPHX_THROW("cuda::w4a16: expects fp16 activations and 2-D uint8 packed weights");
+    if(a.lens().back() != 2 * bp.lens()[1])
+        MIGRAPHX_THROW("cuda::w4a16: K of the activations and of the packed weights differ");
+    return inputs.back();
+}
+
+argument op_w4a16::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    std::size_t i          = 3;
+    const argument* zp     = has_zp ? &args[i++] : nullptr;
+    const argument* wspace = has_workspace ? &args[i++] : nullptr;
+    const argument& out    = args.back();
+    const auto m           = as_matrix(args[0].get_shape(), "w4a16 activations");
+    mgx_w4_desc d{};
+    d.M        = m.rows;
+    d.K        = m.cols;
+    d.N        = static_cast<int64_t>(args[1].get_shape().lens()[0]);
+    d.lda      = m.ld;
+    d.ldd      = d.N;
+    d.group    = group;
+    d.zp_const = zp_const;
+    d.act      = MGX_ACT_NONE;
+    check_mgx(mgx_cuda_w4a16(&d, args[0].data(), args[1].data(), args[2].data(),
+                             zp != nullptr ? zp->data() : nullptr, out.data(),
+                             wspace != nullptr ? wspace->data() : nullptr,
+                             wspace != nullptr ? wspace->get_shape().bytes() : 0, ctx.stream()),
+              "mgx_cuda_w4a16");
+    return out;
+}
+
+MIGRAPHX_REGISTER_OP(op_quantizelinear)
+MIGRAPHX_REGISTER_OP(op_dequantizelinear)
+MIGRAPHX_REGISTER_OP(op_unpack_int4)
+MIGRAPHX_REGISTER_OP(op_pack_int4)
+MIGRAPHX_REGISTER_OP(op_qgemm)
+MIGRAPHX_REGISTER_OP(op_w4a16)
+
+} // namespace cuda
+} // namespace MIGRAPHX_INLINE_NS
+} // namespace migraphx
