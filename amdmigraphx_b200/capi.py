@@ -25,6 +25,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
     "mgx_cuda_pack_int4", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm",
+    "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
     "mgx_cuda_status_string", "mgx_cuda_version",
@@ -77,6 +78,8 @@ def load():
     lib.mgx_cuda_qgemm_workspace.argtypes = [ctypes.POINTER(QgemmDesc)]
     lib.mgx_cuda_qgemm_workspace.restype = sz
     lib.mgx_cuda_qgemm.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mgx_cuda_qgemm_static_scratch_limit.restype = sz
+    lib.mgx_cuda_qgemm_static_scratch.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp]
     lib.mgx_cuda_transpose_8bit.argtypes = [vp, vp, i64, i64, i64, vp]
     lib.mgx_cuda_w4a16_workspace.argtypes = [ctypes.POINTER(W4Desc)]
     lib.mgx_cuda_w4a16_workspace.restype = sz

@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include <cuda_fp16.h>
+#include <mutex>
 
 namespace mgx {
 
@@ -719,3 +720,59 @@ extern "C" int mgx_cuda_qgemm(const mgx_qgemm_desc* d, const void* A, const void
 }
 
 int mgx::qgemm_status(unsigned int* out) { return read_and_clear_status(out); }
+
+// ------------------------------------------------------------------ allocation-free variant
+// Scratch for mgx_cuda_qgemm_static_scratch(): lives in the library's device image, one copy
+// per GPU that loads the library, held until the process exits.
+namespace {
+constexpr size_t static_scratch_bytes = size_t{16} << 20; // 16 MiB
+static __device__ __align__(256) uint8_t g_static_scratch[static_scratch_bytes];
+
+// Device address of g_static_scratch on the current device.  In host code the array's name
+// is only a handle for the runtime, not a device pointer, so the address is looked up once
+// per device (with that device current) and cached.
+int static_scratch_address(void** out)
+{
+    constexpr int max_devices = 64;
+    static std::mutex m;
+    static void* cached[max_devices] = {};
+    int dev       = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if(e != cudaSuccess)
+        return static_cast<int>(e);
+    if(dev < 0 or dev >= max_devices)
+        return MGX_E_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(m);
+    if(cached[dev] == nullptr)
+    {
+        void* p = nullptr;
+        e       = cudaGetSymbolAddress(&p, g_static_scratch);
+        if(e != cudaSuccess)
+            return static_cast<int>(e);
+        cached[dev] = p;
+    }
+    *out = cached[dev];
+    return MGX_OK;
+}
+} // namespace
+
+extern "C" size_t mgx_cuda_qgemm_static_scratch_limit(void) { return static_scratch_bytes; }
+
+extern "C" int mgx_cuda_qgemm_static_scratch(const mgx_qgemm_desc* d, const void* A, const void* B,
+                                             void* D, const float* scale, const float* bias,
+                                             const void* residual, void* stream)
+{
+    if(d == nullptr)
+        return MGX_E_INVALID_ARG;
+    const size_t need = mgx_cuda_qgemm_workspace(d);
+    if(need > static_scratch_bytes)
+        return MGX_E_TOO_LARGE;
+    void* scratch = nullptr;
+    if(need > 0)
+    {
+        const int rc = static_scratch_address(&scratch);
+        if(rc != MGX_OK)
+            return rc;
+    }
+    return mgx_cuda_qgemm(d, A, B, D, scale, bias, residual, scratch, need, stream);
+}

@@ -184,6 +184,32 @@ MGX_API int mgx_cuda_qgemm(const mgx_qgemm_desc* desc,
                            size_t workspace_bytes,
                            void* stream);
 
+/* The same operation for callers that must not allocate device memory and have no buffer
+ * of their own to lend: a runtime that carved up all device memory when the model was
+ * compiled (MIGraphX plans one arena per program and never allocates during eval), a
+ * serving loop in which cudaMalloc's implicit device synchronisation is not acceptable, or
+ * a host with a fixed memory budget.  It has no counterpart in the reference.
+ * The re-laid-out copy of a [K,N] right operand (b_layout = MGX_B_KN) goes into a fixed
+ * 16 MiB array that is part of this library's device image: every GPU that loads the
+ * library holds those 16 MiB until the process exits.  Requests whose
+ * mgx_cuda_qgemm_workspace() exceeds mgx_cuda_qgemm_static_scratch_limit() are rejected
+ * with MGX_E_TOO_LARGE.  No cudaMalloc / cudaFree / allocating library routine is called.
+ * The first call on each device looks the array's device address up (one cheap runtime
+ * query); make that first call before starting a stream capture on that device.
+ * All calls on a device share the one array: two calls whose kernels may overlap on the
+ * GPU (different streams without an ordering between them) race on it; calls on one stream
+ * are safe.  The array keeps the previous call's bytes; nothing in it needs to start at
+ * zero because every byte the GEMM reads is rewritten by the same call first. */
+MGX_API size_t mgx_cuda_qgemm_static_scratch_limit(void);
+MGX_API int mgx_cuda_qgemm_static_scratch(const mgx_qgemm_desc* desc,
+                                          const void* A,
+                                          const void* B,
+                                          void* D,
+                                          const float* scale,
+                                          const float* bias,
+                                          const void* residual,
+                                          void* stream);
+
 /* [rows, cols] bytes -> [cols, rows] bytes, per batch (dense, ld = cols / rows).
  * Used once per constant weight so that quant_dot's [K,N] operand becomes
  * K-contiguous (the reference does the equivalent with its column-major trick,
