@@ -150,6 +150,230 @@ __global__ void __launch_bounds__(256) w4a16_splitk_reduce_kernel(const w4_param
     }
 }
 
+// ------------------------------------------------------------------ tensor-core decode kernel
+// M <= 16 rows of activations against packed int4 weights, HBM-bound by design: the weights
+// are read once, 16 bytes per thread, straight into registers, dequantised there and fed to
+// mma.sync.m16n8k16 (the register-operand tensor-core path: the B fragment is produced in
+// registers, which tcgen05 - operands in shared / tensor memory - cannot take).
+//
+// Work split: a block owns ROWS_PER_BLOCK = 128 output columns (4 warps x 4 n-tiles of 8) and
+// one K slice; every warp walks the whole slice in chunks of 128 k.  Within a warp, lane
+// (g = lane / 4, t = lane % 4) loads, for each of its 4 n-tiles, the 16 bytes holding
+// k = chunk + 32 t .. + 31 of weight row (tile * 8 + g): four lanes cover 64 contiguous bytes.
+// The reduction index of an MMA may be permuted freely as long as A and B agree: word w
+// (8 nibbles, k = 8 w .. 8 w + 7) yields the half2 pairs (k0,k4) (k1,k5) (k2,k6) (k3,k7) by
+// mask-and-or, which are the B registers of two MMAs; A is staged in shared memory already
+// permuted to the same order, so one 16-byte shared load gives the matching A registers.
+constexpr int W4_ROWS_PER_BLOCK = 128;
+constexpr int W4_TILES          = 4;   // n-tiles of 8 columns per warp
+constexpr int W4_CHUNK          = 128; // k per loop trip
+constexpr int W4_MAX_SLICE      = 512;
+constexpr int W4_STAGES         = 4;   // chunks of packed weights in flight per warp (cp.async ring)
+constexpr int W4_RING_BYTES     = W4_STAGES * W4_TILES * 32 * 16; // per warp
+
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+                 "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// HI: activations have more than 8 rows (the upper half of the MMA's M = 16 is used).
+template <bool HI>
+__global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params p)
+{
+    extern __shared__ __align__(16) uint8_t smem_a[];
+    const int warp  = threadIdx.x >> 5;
+    const int lane  = threadIdx.x & 31;
+    const int g     = lane >> 2;
+    const int t     = lane & 3;
+    const int split = blockIdx.y;
+    const int64_t k_begin = split * p.k_per_split;
+    const int64_t k_end   = min(p.K, k_begin + p.k_per_split);
+    const int slice       = static_cast<int>(k_end - k_begin); // multiple of 128
+    const int rows_a      = HI ? 16 : 8;
+    const int pitch       = slice * 2 + 64; // bytes; = 64 mod 128 keeps the 16-byte loads conflict free
+
+    const int64_t n_base = static_cast<int64_t>(blockIdx.x) * W4_ROWS_PER_BLOCK + warp * (W4_TILES * 8);
+    const int nchunks    = slice / W4_CHUNK;
+    const bool active    = n_base < p.N;
+
+    // weight rows of this lane (clamped: rows past N are loaded from the last row and dropped)
+    const uint8_t* brow[W4_TILES];
+#pragma unroll
+    for(int j = 0; j < W4_TILES; ++j)
+    {
+        int64_t n = n_base + j * 8 + g;
+        n         = n < p.N ? n : p.N - 1;
+        brow[j]   = p.Bp + n * (p.K / 2) + (k_begin + t * 32) / 2;
+    }
+
+    // ---- packed weights stream through a per-warp ring in shared memory: W4_STAGES chunks
+    //      (2 KB each) are in flight per warp, which is what hides the HBM latency; every
+    //      lane later reads back exactly the 16 bytes it copied
+    uint8_t* ring = smem_a + rows_a * pitch + warp * W4_RING_BYTES + lane * 16;
+    auto issue = [&](int c) {
+        if(active and c < nchunks)
+        {
+            const uint32_t dst = smem_u32(ring + (c % W4_STAGES) * (W4_TILES * 512));
+#pragma unroll
+            for(int j = 0; j < W4_TILES; ++j)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 512),
+                             "l"(brow[j] + c * (W4_CHUNK / 2))
+                             : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for(int c = 0; c < W4_STAGES - 1; ++c)
+        issue(c);
+
+    // ---- stage A[0..rows_a) x [k_begin, k_end) in shared memory, permuted per 8 k:
+    //      position (chunk, w, t) holds halves of k = chunk*128 + t*32 + w*8 + {0,4,1,5,2,6,3,7}
+    const int units = rows_a * (slice / 8);
+    for(int u = threadIdx.x; u < units; u += blockDim.x)
+    {
+        const int m  = u / (slice / 8);
+        const int k8 = u - m * (slice / 8); // which group of 8 k inside the slice
+        uint4 v      = make_uint4(0u, 0u, 0u, 0u);
+        if(m < p.M)
+            v = *reinterpret_cast<const uint4*>(p.A + m * p.lda + k_begin + k8 * 8);
+        // v = halves h0..h7 ; wanted order h0 h4 h1 h5 h2 h6 h3 h7
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410); // h0 | h4
+        o.y = __byte_perm(v.x, v.z, 0x7632); // h1 | h5
+        o.z = __byte_perm(v.y, v.w, 0x5410); // h2 | h6
+        o.w = __byte_perm(v.y, v.w, 0x7632); // h3 | h7
+        const int chunk = k8 >> 4;       // 16 groups of 8 per 128-k chunk
+        const int tt    = (k8 >> 2) & 3; // k offset / 32 inside the chunk
+        const int w     = k8 & 3;        // word inside the lane's 32 k
+        *reinterpret_cast<uint4*>(smem_a + m * pitch + chunk * 256 + (w * 4 + tt) * 16) = o;
+    }
+    __syncthreads();
+
+    // Arithmetic without fp16 or conversion instructions (both run at a fraction of the
+    // fp32 rate on this GPU and would bound the kernel): the MMA's B operand is the bit
+    // pattern 0x6400 | q, i.e. the fp16 number 1024 + q, produced by one shift and one
+    // logic operation per two weights.  Per group of 128 k the tensor core accumulates
+    //   P[m,n] = sum_k a[m,k] * (1024 + q[n,k])   and, with a B operand of ones,   S[m] = sum_k a[m,k];
+    // the group's contribution is then  s[n] * (P[m,n] - (1024 + zp[n]) * S[m])  in fp32.
+    // (Products are exact in the tensor core; the reference rounds every dequantised weight
+    // to fp16 first, so this is the more accurate of the two, well inside the tolerance.)
+    float acc[W4_TILES][4];
+#pragma unroll
+    for(int j = 0; j < W4_TILES; ++j)
+#pragma unroll
+        for(int q = 0; q < 4; ++q)
+            acc[j][q] = 0.0f;
+
+    // scale / zero-point rows of the two output columns (2t, 2t+1) this lane owns per tile
+    const __half* scol[W4_TILES][2];
+    const uint8_t* zcol[W4_TILES][2];
+#pragma unroll
+    for(int j = 0; j < W4_TILES; ++j)
+#pragma unroll
+        for(int e = 0; e < 2; ++e)
+        {
+            int64_t n  = n_base + j * 8 + 2 * t + e;
+            n          = n < p.N ? n : p.N - 1;
+            scol[j][e] = p.scales + n * p.groups_per_row;
+            zcol[j][e] = p.zp == nullptr ? nullptr : p.zp + n * p.groups_per_row;
+        }
+
+    {
+        const uint8_t* a_lo = smem_a + g * pitch + t * 16;
+        const uint8_t* a_hi = smem_a + (g + 8) * pitch + t * 16;
+        constexpr uint32_t ones = 0x3C003C00u; // half2(1, 1)
+#pragma unroll 1
+        for(int c = 0; c < nchunks; ++c)
+        {
+            issue(c + W4_STAGES - 1);
+            asm volatile("cp.async.wait_group %0;" ::"n"(W4_STAGES - 1) : "memory");
+            if(not active)
+                continue;
+            uint4 wcur[W4_TILES];
+#pragma unroll
+            for(int j = 0; j < W4_TILES; ++j)
+                wcur[j] = *reinterpret_cast<const uint4*>(ring + (c % W4_STAGES) * (W4_TILES * 512) + j * 512);
+            // this group's scales and zero points (loads overlap the MMAs below)
+            const int gi = static_cast<int>((k_begin + static_cast<int64_t>(c) * W4_CHUNK) / p.group);
+            float sc[W4_TILES][2], zc[W4_TILES][2];
+#pragma unroll
+            for(int j = 0; j < W4_TILES; ++j)
+#pragma unroll
+                for(int e = 0; e < 2; ++e)
+                {
+                    sc[j][e] = __half2float(scol[j][e][gi]);
+                    zc[j][e] = static_cast<float>(1024 + (zcol[j][e] == nullptr ? p.zp_const : static_cast<int>(zcol[j][e][gi])));
+                }
+            float pg[W4_TILES][4];
+            float sg[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for(int j = 0; j < W4_TILES; ++j)
+#pragma unroll
+                for(int q = 0; q < 4; ++q)
+                    pg[j][q] = 0.0f;
+#pragma unroll
+            for(int w = 0; w < 4; ++w)
+            {
+                const uint4 alo = *reinterpret_cast<const uint4*>(a_lo + c * 256 + w * 64);
+                uint4 ahi       = make_uint4(0u, 0u, 0u, 0u);
+                if(HI)
+                    ahi = *reinterpret_cast<const uint4*>(a_hi + c * 256 + w * 64);
+                mma_m16n8k16(sg, alo.x, ahi.x, alo.y, ahi.y, ones, ones);
+                mma_m16n8k16(sg, alo.z, ahi.z, alo.w, ahi.w, ones, ones);
+#pragma unroll
+                for(int j = 0; j < W4_TILES; ++j)
+                {
+                    const uint32_t word = w == 0 ? wcur[j].x : (w == 1 ? wcur[j].y : (w == 2 ? wcur[j].z : wcur[j].w));
+                    const uint32_t b0 = (word & 0x000F000Fu) | 0x64006400u;         // (k0, k4)
+                    const uint32_t b1 = ((word >> 4) & 0x000F000Fu) | 0x64006400u;  // (k1, k5)
+                    const uint32_t b2 = ((word >> 8) & 0x000F000Fu) | 0x64006400u;  // (k2, k6)
+                    const uint32_t b3 = ((word >> 12) & 0x000F000Fu) | 0x64006400u; // (k3, k7)
+                    mma_m16n8k16(pg[j], alo.x, ahi.x, alo.y, ahi.y, b0, b1);
+                    mma_m16n8k16(pg[j], alo.z, ahi.z, alo.w, ahi.w, b2, b3);
+                }
+            }
+            // sg[0] = S[row g], sg[2] = S[row g + 8] (every column of the ones tile is the same)
+#pragma unroll
+            for(int j = 0; j < W4_TILES; ++j)
+            {
+                acc[j][0] = fmaf(sc[j][0], fmaf(-zc[j][0], sg[0], pg[j][0]), acc[j][0]);
+                acc[j][1] = fmaf(sc[j][1], fmaf(-zc[j][1], sg[0], pg[j][1]), acc[j][1]);
+                acc[j][2] = fmaf(sc[j][0], fmaf(-zc[j][0], sg[2], pg[j][2]), acc[j][2]);
+                acc[j][3] = fmaf(sc[j][1], fmaf(-zc[j][1], sg[2], pg[j][3]), acc[j][3]);
+            }
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    // ---- results: c0,c1 = row g, columns 2t, 2t+1 of the tile; c2,c3 = row g + 8
+#pragma unroll
+    for(int j = 0; j < W4_TILES; ++j)
+    {
+        const int64_t n = n_base + j * 8 + 2 * t;
+#pragma unroll
+        for(int half_idx = 0; half_idx < (HI ? 2 : 1); ++half_idx)
+        {
+            const int m = g + half_idx * 8;
+            if(m >= p.M)
+                continue;
+#pragma unroll
+            for(int e = 0; e < 2; ++e)
+            {
+                if(n + e >= p.N)
+                    continue;
+                const float v = acc[j][half_idx * 2 + e];
+                if(p.splits > 1)
+                    p.partial[(static_cast<int64_t>(split) * p.M + m) * p.N + n + e] = v;
+                else
+                    p.D[m * p.ldd + n + e] = __float2half_rn(w4_act(v, p.act));
+            }
+        }
+    }
+}
+
 static int validate_w4(const mgx_w4_desc* d, const void* A, const void* Bp, const void* scales,
                        void* D)
 {
@@ -171,9 +395,29 @@ static int validate_w4(const mgx_w4_desc* d, const void* A, const void* Bp, cons
     return MGX_OK;
 }
 
-// Split K only when the columns alone cannot fill the machine.
+static bool use_mma_path(const mgx_w4_desc& d)
+{
+    // a group must cover whole 128-k chunks: the per-group scale is applied after the MMAs
+    return d.K % W4_CHUNK == 0 and d.group % W4_CHUNK == 0 and d.M <= 16;
+}
+
+// K is split so that about three 128-column blocks per SM are in flight and no slice is
+// longer than W4_MAX_SLICE (shared-memory copy of the activations); slices are multiples of
+// 128 k.  The simple kernel splits K only when the columns alone cannot fill the machine.
 static int pick_splits(const mgx_w4_desc& d)
 {
+    if(use_mma_path(d))
+    {
+        const int64_t nblocks = ceil_div(d.N, W4_ROWS_PER_BLOCK);
+        const int64_t chunks  = d.K / W4_CHUNK;
+        int64_t s             = ceil_div(static_cast<int64_t>(device_sm_count()) * 3, nblocks);
+        const int64_t min_s   = ceil_div(d.K, W4_MAX_SLICE);
+        if(s < min_s)
+            s = min_s;
+        if(s > chunks)
+            s = chunks;
+        return static_cast<int>(s < 1 ? 1 : s);
+    }
     const int64_t warps_wanted = static_cast<int64_t>(device_sm_count()) * 16;
     if(d.N >= warps_wanted)
         return 1;
@@ -198,7 +442,10 @@ extern "C" size_t mgx_cuda_w4a16_workspace(const mgx_w4_desc* d)
         return 0;
     if(d->M > 16)
         return 0;
-    const int s = pick_splits(*d);
+    int s            = pick_splits(*d);
+    const int64_t kq = use_mma_path(*d) ? W4_CHUNK : 32;
+    const int64_t kp = ceil_div(ceil_div(d->K, s), kq) * kq;
+    s                = static_cast<int>(ceil_div(d->K, kp));
     return s > 1 ? static_cast<size_t>(s) * d->M * d->N * sizeof(float) : 0;
 }
 
@@ -227,8 +474,11 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     p.groups_per_row = static_cast<int>(d->K / d->group);
     p.zp_const       = d->zp_const;
     p.act            = d->act;
+    const bool mma   = use_mma_path(*d);
     p.splits         = pick_splits(*d);
-    p.k_per_split    = ceil_div(ceil_div(d->K, p.splits), 32) * 32;
+    const int64_t kq = mma ? W4_CHUNK : 32;
+    p.k_per_split    = ceil_div(ceil_div(d->K, p.splits), kq) * kq;
+    p.splits         = static_cast<int>(ceil_div(d->K, p.k_per_split));
     if(p.splits > 1)
     {
         const size_t need = static_cast<size_t>(p.splits) * d->M * d->N * sizeof(float);
@@ -238,14 +488,39 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
             return MGX_E_ALIGNMENT;
         p.partial = static_cast<float*>(workspace);
     }
-    const int warps = 8;
-    dim3 grid(static_cast<unsigned>(ceil_div(d->N, warps)), static_cast<unsigned>(p.splits));
-    if(d->M == 1)
-        w4a16_gemv_simple_kernel<1><<<grid, warps * 32, 0, stream>>>(p);
-    else if(d->M <= 4)
-        w4a16_gemv_simple_kernel<4><<<grid, warps * 32, 0, stream>>>(p);
+    if(mma)
+    {
+        const bool hi     = d->M > 8;
+        const int smem    = (hi ? 16 : 8) * (static_cast<int>(p.k_per_split) * 2 + 64) + 4 * W4_RING_BYTES;
+        // the opt-in is made once per kernel with the largest size any launch can ask for
+        constexpr int smem_max = 16 * (W4_MAX_SLICE * 2 + 64) + 4 * W4_RING_BYTES;
+        dim3 grid(static_cast<unsigned>(ceil_div(d->N, W4_ROWS_PER_BLOCK)), static_cast<unsigned>(p.splits));
+        if(hi)
+        {
+            int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_gemv_mma_kernel<true>), smem_max);
+            if(rc2 != MGX_OK)
+                return rc2;
+            w4a16_gemv_mma_kernel<true><<<grid, 128, smem, stream>>>(p);
+        }
+        else
+        {
+            int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_gemv_mma_kernel<false>), smem_max);
+            if(rc2 != MGX_OK)
+                return rc2;
+            w4a16_gemv_mma_kernel<false><<<grid, 128, smem, stream>>>(p);
+        }
+    }
     else
-        w4a16_gemv_simple_kernel<16><<<grid, warps * 32, 0, stream>>>(p);
+    {
+        const int warps = 8;
+        dim3 grid(static_cast<unsigned>(ceil_div(d->N, warps)), static_cast<unsigned>(p.splits));
+        if(d->M == 1)
+            w4a16_gemv_simple_kernel<1><<<grid, warps * 32, 0, stream>>>(p);
+        else if(d->M <= 4)
+            w4a16_gemv_simple_kernel<4><<<grid, warps * 32, 0, stream>>>(p);
+        else
+            w4a16_gemv_simple_kernel<16><<<grid, warps * 32, 0, stream>>>(p);
+    }
     cudaError_t e = cudaGetLastError();
     if(e != cudaSuccess)
         return static_cast<int>(e);
