@@ -21,7 +21,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "lib")
 OBJ = os.path.join(PKG, "build")
 
-KERNEL_SOURCES = ["runtime.cu", "quantize.cu", "qgemm.cu", "w4a16.cu"]
+KERNEL_SOURCES = ["runtime.cu", "quantize.cu", "qgemm.cu", "w4a16.cu", "comm.cu"]
 KERNEL_LIB = os.path.join(LIB, "libmgx_cuda_kernels.so")
 
 NVCC_FLAGS = [
@@ -75,7 +75,7 @@ def build_kernels(verbose=False, force=False):
     objs = [j[1] for j in jobs]
     if force or _newer(KERNEL_LIB, objs):
         cmd = [nvcc_path(), "-shared", "-o", KERNEL_LIB] + objs + [
-            "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static"]
+            "-gencode", "arch=compute_100a,code=sm_100a", "-cudart", "static", "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}{r.stderr}")

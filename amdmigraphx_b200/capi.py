@@ -29,6 +29,8 @@ EXPORTED_SYMBOLS = [
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
     "mgx_cuda_status_string", "mgx_cuda_version",
+    "mgx_cuda_comm_unique_id", "mgx_cuda_comm_create", "mgx_cuda_comm_destroy",
+    "mgx_cuda_comm_set_default", "mgx_cuda_comm_default", "mgx_cuda_all_reduce",
 ]
 
 
@@ -85,6 +87,13 @@ def load():
     lib.mgx_cuda_w4a16_workspace.restype = sz
     for name in ("mgx_cuda_w4a16_gemv", "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16"):
         getattr(lib, name).argtypes = [ctypes.POINTER(W4Desc), vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mgx_cuda_comm_unique_id.argtypes = [vp]
+    lib.mgx_cuda_comm_create.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
+    lib.mgx_cuda_comm_destroy.argtypes = [vp]
+    lib.mgx_cuda_comm_set_default.argtypes = [vp]
+    lib.mgx_cuda_comm_set_default.restype = None
+    lib.mgx_cuda_comm_default.restype = vp
+    lib.mgx_cuda_all_reduce.argtypes = [vp, sz, i32, vp, vp]
     lib.mgx_cuda_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
     lib.mgx_cuda_status_string.argtypes = [i32]
     lib.mgx_cuda_status_string.restype = ctypes.c_char_p
@@ -259,3 +268,33 @@ def w4a16(a, bp, scales, zp=None, *, zp_const=8, group=128, act=None, which="aut
               _ptr(workspace), 0 if workspace is None else workspace.numel(), _stream())
     check(code, f"mgx_cuda_w4a16[{which}]")
     return d
+
+
+# ------------------------------------------------------------------ tensor parallel
+class Communicator(object):
+    """One NCCL communicator per process, created from a 128-byte id that rank 0 makes and the
+    caller distributes (here: through torch.distributed's store / broadcast)."""
+
+    def __init__(self, unique_id_bytes, nranks, rank):
+        lib = load()
+        self.handle = ctypes.c_void_p()
+        buf = ctypes.create_string_buffer(bytes(unique_id_bytes), 128)
+        check(lib.mgx_cuda_comm_create(buf, nranks, rank, ctypes.byref(self.handle)),
+              "mgx_cuda_comm_create")
+        self.nranks, self.rank = nranks, rank
+
+    @staticmethod
+    def make_unique_id():
+        buf = ctypes.create_string_buffer(128)
+        check(load().mgx_cuda_comm_unique_id(buf), "mgx_cuda_comm_unique_id")
+        return buf.raw
+
+    def all_reduce_(self, t):
+        check(load().mgx_cuda_all_reduce(_ptr(t), t.numel(), _dtype_code(t), self.handle, _stream()),
+              "mgx_cuda_all_reduce")
+        return t
+
+    def destroy(self):
+        if self.handle:
+            load().mgx_cuda_comm_destroy(self.handle)
+            self.handle = ctypes.c_void_p()

@@ -239,6 +239,18 @@ struct op_w4a16
     std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
 };
 
+// In-place sum all-reduce across the tensor-parallel ranks (one process per GPU) over the
+// process's default NCCL communicator (mgx_cuda_comm_set_default).  Input: the partial result
+// of a row-split linear; output: the same buffer holding the sum.  New: the reference has no
+// collective operator.
+struct op_all_reduce
+{
+    std::string name() const { return "cuda::all_reduce"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {0}; }
+};
+
 } // namespace cuda
 } // namespace MIGRAPHX_INLINE_NS
 } // namespace migraphx

@@ -293,6 +293,22 @@ argument op_w4a16::compute(context& ctx, const shape&, const std::vector<argumen
     return out;
 }
 
+// ------------------------------------------------------------------ all_reduce
+shape op_all_reduce::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(1).standard();
+    return inputs.front();
+}
+
+argument op_all_reduce::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& s = args[0].get_shape();
+    check_mgx(mgx_cuda_all_reduce(args[0].data(), s.elements(), mgx_type(s.type()), nullptr, ctx.stream()),
+              "mgx_cuda_all_reduce");
+    return args[0];
+}
+
+MIGRAPHX_REGISTER_OP(op_all_reduce)
 MIGRAPHX_REGISTER_OP(op_quantizelinear)
 MIGRAPHX_REGISTER_OP(op_dequantizelinear)
 MIGRAPHX_REGISTER_OP(op_unpack_int4)

@@ -190,14 +190,13 @@ __global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params 
     const int g     = lane >> 2;
     const int t     = lane & 3;
     const int split = blockIdx.y;
-    const int64_t k_begin = split * p.k_per_split;
-    const int64_t k_end   = min(p.K, k_begin + p.k_per_split);
-    const int slice       = static_cast<int>(k_end - k_begin); // multiple of 128
+    const int64_t k_lo    = split * p.k_per_split;
+    const int64_t k_hi    = min(p.K, k_lo + p.k_per_split);
+    const int64_t m_base  = static_cast<int64_t>(blockIdx.z) * 16; // slab of activations rows
     const int rows_a      = HI ? 16 : 8;
-    const int pitch       = slice * 2 + 64; // bytes; = 64 mod 128 keeps the 16-byte loads conflict free
+    constexpr int pitch   = W4_MAX_SLICE * 2 + 64; // bytes; = 64 mod 128 keeps the 16-byte loads conflict free
 
     const int64_t n_base = static_cast<int64_t>(blockIdx.x) * W4_ROWS_PER_BLOCK + warp * (W4_TILES * 8);
-    const int nchunks    = slice / W4_CHUNK;
     const bool active    = n_base < p.N;
 
     // weight rows of this lane (clamped: rows past N are loaded from the last row and dropped)
@@ -207,51 +206,8 @@ __global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params 
     {
         int64_t n = n_base + j * 8 + g;
         n         = n < p.N ? n : p.N - 1;
-        brow[j]   = p.Bp + n * (p.K / 2) + (k_begin + t * 32) / 2;
+        brow[j]   = p.Bp + n * (p.K / 2) + (t * 32) / 2;
     }
-
-    // ---- packed weights stream through a per-warp ring in shared memory: W4_STAGES chunks
-    //      (2 KB each) are in flight per warp, which is what hides the HBM latency; every
-    //      lane later reads back exactly the 16 bytes it copied
-    uint8_t* ring = smem_a + rows_a * pitch + warp * W4_RING_BYTES + lane * 16;
-    auto issue = [&](int c) {
-        if(active and c < nchunks)
-        {
-            const uint32_t dst = smem_u32(ring + (c % W4_STAGES) * (W4_TILES * 512));
-#pragma unroll
-            for(int j = 0; j < W4_TILES; ++j)
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 512),
-                             "l"(brow[j] + c * (W4_CHUNK / 2))
-                             : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    };
-#pragma unroll
-    for(int c = 0; c < W4_STAGES - 1; ++c)
-        issue(c);
-
-    // ---- stage A[0..rows_a) x [k_begin, k_end) in shared memory, permuted per 8 k:
-    //      position (chunk, w, t) holds halves of k = chunk*128 + t*32 + w*8 + {0,4,1,5,2,6,3,7}
-    const int units = rows_a * (slice / 8);
-    for(int u = threadIdx.x; u < units; u += blockDim.x)
-    {
-        const int m  = u / (slice / 8);
-        const int k8 = u - m * (slice / 8); // which group of 8 k inside the slice
-        uint4 v      = make_uint4(0u, 0u, 0u, 0u);
-        if(m < p.M)
-            v = *reinterpret_cast<const uint4*>(p.A + m * p.lda + k_begin + k8 * 8);
-        // v = halves h0..h7 ; wanted order h0 h4 h1 h5 h2 h6 h3 h7
-        uint4 o;
-        o.x = __byte_perm(v.x, v.z, 0x5410); // h0 | h4
-        o.y = __byte_perm(v.x, v.z, 0x7632); // h1 | h5
-        o.z = __byte_perm(v.y, v.w, 0x5410); // h2 | h6
-        o.w = __byte_perm(v.y, v.w, 0x7632); // h3 | h7
-        const int chunk = k8 >> 4;       // 16 groups of 8 per 128-k chunk
-        const int tt    = (k8 >> 2) & 3; // k offset / 32 inside the chunk
-        const int w     = k8 & 3;        // word inside the lane's 32 k
-        *reinterpret_cast<uint4*>(smem_a + m * pitch + chunk * 256 + (w * 4 + tt) * 16) = o;
-    }
-    __syncthreads();
 
     // Arithmetic without fp16 or conversion instructions (both run at a fraction of the
     // fp32 rate on this GPU and would bound the kernel): the MMA's B operand is the bit
@@ -281,6 +237,58 @@ __global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params 
             scol[j][e] = p.scales + n * p.groups_per_row;
             zcol[j][e] = p.zp == nullptr ? nullptr : p.zp + n * p.groups_per_row;
         }
+
+    // the block's K range is walked in slices of at most W4_MAX_SLICE (the shared-memory copy
+    // of the activations), each slice in chunks of 128 k
+#pragma unroll 1
+    for(int64_t k_begin = k_lo; k_begin < k_hi; k_begin += W4_MAX_SLICE)
+    {
+    const int slice   = static_cast<int>(min(static_cast<int64_t>(W4_MAX_SLICE), k_hi - k_begin));
+    const int nchunks = slice / W4_CHUNK;
+    if(k_begin != k_lo)
+        __syncthreads(); // everyone is done with the previous slice's activations
+    // ---- packed weights stream through a per-warp ring in shared memory: W4_STAGES chunks
+    //      (2 KB each) are in flight per warp, which is what hides the HBM latency; every
+    //      lane later reads back exactly the 16 bytes it copied
+    uint8_t* ring = smem_a + rows_a * pitch + warp * W4_RING_BYTES + lane * 16;
+    auto issue = [&](int c) {
+        if(active and c < nchunks)
+        {
+            const uint32_t dst = smem_u32(ring + (c % W4_STAGES) * (W4_TILES * 512));
+#pragma unroll
+            for(int j = 0; j < W4_TILES; ++j)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + j * 512),
+                             "l"(brow[j] + (k_begin + static_cast<int64_t>(c) * W4_CHUNK) / 2)
+                             : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for(int c = 0; c < W4_STAGES - 1; ++c)
+        issue(c);
+
+    // ---- stage A[0..rows_a) x [k_begin, k_end) in shared memory, permuted per 8 k:
+    //      position (chunk, w, t) holds halves of k = chunk*128 + t*32 + w*8 + {0,4,1,5,2,6,3,7}
+    const int units = rows_a * (slice / 8);
+    for(int u = threadIdx.x; u < units; u += blockDim.x)
+    {
+        const int m  = u / (slice / 8);
+        const int k8 = u - m * (slice / 8); // which group of 8 k inside the slice
+        uint4 v      = make_uint4(0u, 0u, 0u, 0u);
+        if(m_base + m < p.M)
+            v = *reinterpret_cast<const uint4*>(p.A + (m_base + m) * p.lda + k_begin + k8 * 8);
+        // v = halves h0..h7 ; wanted order h0 h4 h1 h5 h2 h6 h3 h7
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410); // h0 | h4
+        o.y = __byte_perm(v.x, v.z, 0x7632); // h1 | h5
+        o.z = __byte_perm(v.y, v.w, 0x5410); // h2 | h6
+        o.w = __byte_perm(v.y, v.w, 0x7632); // h3 | h7
+        const int chunk = k8 >> 4;       // 16 groups of 8 per 128-k chunk
+        const int tt    = (k8 >> 2) & 3; // k offset / 32 inside the chunk
+        const int w     = k8 & 3;        // word inside the lane's 32 k
+        *reinterpret_cast<uint4*>(smem_a + m * pitch + chunk * 256 + (w * 4 + tt) * 16) = o;
+    }
+    __syncthreads();
 
     {
         const uint8_t* a_lo = smem_a + g * pitch + t * 16;
@@ -348,6 +356,7 @@ __global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params 
         }
         asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
+    } // slices
     // ---- results: c0,c1 = row g, columns 2t, 2t+1 of the tile; c2,c3 = row g + 8
 #pragma unroll
     for(int j = 0; j < W4_TILES; ++j)
@@ -356,7 +365,7 @@ __global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params 
 #pragma unroll
         for(int half_idx = 0; half_idx < (HI ? 2 : 1); ++half_idx)
         {
-            const int m = g + half_idx * 8;
+            const int64_t m = m_base + g + half_idx * 8;
             if(m >= p.M)
                 continue;
 #pragma unroll
@@ -398,7 +407,7 @@ static int validate_w4(const mgx_w4_desc* d, const void* A, const void* Bp, cons
 static bool use_mma_path(const mgx_w4_desc& d)
 {
     // a group must cover whole 128-k chunks: the per-group scale is applied after the MMAs
-    return d.K % W4_CHUNK == 0 and d.group % W4_CHUNK == 0 and d.M <= 16;
+    return d.K % W4_CHUNK == 0 and d.group % W4_CHUNK == 0;
 }
 
 // K is split so that about three 128-column blocks per SM are in flight and no slice is
@@ -408,14 +417,15 @@ static int pick_splits(const mgx_w4_desc& d)
 {
     if(use_mma_path(d))
     {
-        const int64_t nblocks = ceil_div(d.N, W4_ROWS_PER_BLOCK);
+        // blocks = column blocks x 16-row slabs of the activations; K is split only as far
+        // as needed to put about three blocks on every SM
+        const int64_t nblocks = ceil_div(d.N, W4_ROWS_PER_BLOCK) * ceil_div(d.M, 16);
         const int64_t chunks  = d.K / W4_CHUNK;
         int64_t s             = ceil_div(static_cast<int64_t>(device_sm_count()) * 3, nblocks);
-        const int64_t min_s   = ceil_div(d.K, W4_MAX_SLICE);
-        if(s < min_s)
-            s = min_s;
         if(s > chunks)
             s = chunks;
+        if(s > 32)
+            s = 32;
         return static_cast<int>(s < 1 ? 1 : s);
     }
     const int64_t warps_wanted = static_cast<int64_t>(device_sm_count()) * 16;
@@ -440,7 +450,7 @@ extern "C" size_t mgx_cuda_w4a16_workspace(const mgx_w4_desc* d)
 {
     if(d == nullptr or d->M <= 0 or d->N <= 0 or d->K <= 0)
         return 0;
-    if(d->M > 16)
+    if(d->M > 16 and not use_mma_path(*d))
         return 0;
     int s            = pick_splits(*d);
     const int64_t kq = use_mma_path(*d) ? W4_CHUNK : 32;
@@ -457,7 +467,7 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     int rc = validate_w4(d, A, Bp, scales, D);
     if(rc != MGX_OK)
         return rc;
-    if(d->M > 16)
+    if(d->M > 16 and not use_mma_path(*d))
         return MGX_E_UNSUPPORTED;
     w4_params p{};
     p.A              = static_cast<const __half*>(A);
@@ -491,10 +501,14 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     if(mma)
     {
         const bool hi     = d->M > 8;
-        const int smem    = (hi ? 16 : 8) * (static_cast<int>(p.k_per_split) * 2 + 64) + 4 * W4_RING_BYTES;
+        const int smem    = (hi ? 16 : 8) * (W4_MAX_SLICE * 2 + 64) + 4 * W4_RING_BYTES;
         // the opt-in is made once per kernel with the largest size any launch can ask for
         constexpr int smem_max = 16 * (W4_MAX_SLICE * 2 + 64) + 4 * W4_RING_BYTES;
-        dim3 grid(static_cast<unsigned>(ceil_div(d->N, W4_ROWS_PER_BLOCK)), static_cast<unsigned>(p.splits));
+        const int64_t slabs = ceil_div(d->M, 16);
+        if(slabs > 65535)
+            return MGX_E_TOO_LARGE;
+        dim3 grid(static_cast<unsigned>(ceil_div(d->N, W4_ROWS_PER_BLOCK)), static_cast<unsigned>(p.splits),
+                  static_cast<unsigned>(slabs));
         if(hi)
         {
             int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_gemv_mma_kernel<true>), smem_max);
@@ -534,18 +548,18 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     return static_cast<int>(e);
 }
 
+// More than 16 rows of activations (prefill): the same tensor-core kernel over 16-row slabs
+// of A (grid.z), every slab re-reading the packed weights through L2.
 extern "C" int mgx_cuda_w4a16_gemm(const mgx_w4_desc* d, const void* A, const void* Bp,
                                    const void* scales, const void* zp, void* D, void* workspace,
                                    size_t workspace_bytes, void* stream_)
 {
-    (void)workspace;
-    (void)workspace_bytes;
-    (void)zp;
-    (void)stream_;
     int rc = validate_w4(d, A, Bp, scales, D);
     if(rc != MGX_OK)
         return rc;
-    return MGX_E_UNSUPPORTED;
+    if(not use_mma_path(*d))
+        return MGX_E_UNSUPPORTED;
+    return mgx_cuda_w4a16_gemv(d, A, Bp, scales, zp, D, workspace, workspace_bytes, stream_);
 }
 
 extern "C" int mgx_cuda_w4a16(const mgx_w4_desc* d, const void* A, const void* Bp,

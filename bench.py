@@ -171,6 +171,81 @@ def run_reference_arm(args):
     return 0
 
 
+# ------------------------------------------------------------------ secondary measurements
+def _graph_time_us(fn, launches, stream):
+    """Average device time of one call of fn, measured over a CUDA graph of `launches` calls."""
+    import torch
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for _ in range(launches):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (2 * launches) * 1e3
+
+
+def secondary_measurements(dev, peaks):
+    """The other halves of the headline metric, on one GPU: large int8 / fp8 QDQ GEMMs (config 3's
+    biggest point) and the int4 weight-only linears of one Llama-2-7B-shaped decoder layer at
+    batch 1 and 16 (config 4; linears only - attention and norms are not part of this path)."""
+    import torch
+    from amdmigraphx_b200 import capi
+    out = {}
+    stream = torch.cuda.Stream()
+    peak8 = 2.0 * float(peaks["bf16_tflops"])
+    M = N = K = 8192
+    for name, fp8 in (("int8_qdq_gemm_8192", False), ("fp8_qdq_gemm_8192", True)):
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
+        b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
+        if fp8:
+            a = (a.float() / 64).to(torch.float8_e4m3fn)
+            b = (b.float() / 64).to(torch.float8_e4m3fn)
+        scale = torch.rand(N, device=dev) * 1e-4
+        bias = torch.randn(N, device=dev)
+        d = torch.empty((1, M, N), dtype=torch.float32, device=dev)
+        us = _graph_time_us(lambda: capi.qgemm(a, b, b_layout=capi.B_NK, scale=scale, bias=bias,
+                                               act="gelu_erf", out=d), 4, stream)
+        tops = 2.0 * M * N * K / us / 1e6
+        out[name] = {"us": us, "tops": tops, "frac_of_2x_bf16_burst": tops / peak8,
+                     "frac_of_4500_datasheet": tops / 4500.0,
+                     "what": "M=N=K=8192, dequantizelinear + bias + GELU fused, fp32 out"}
+        del a, b, d
+    hid, ffn, group = 4096, 11008, 128
+    shapes = [(hid, hid)] * 4 + [(ffn, hid), (ffn, hid), (hid, ffn)]  # q k v o gate up down: (N, K)
+    layers = 3  # 3 x 101 MB of packed weights: larger than L2
+    weights = []
+    for _ in range(layers):
+        weights.append([(torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev),
+                         (torch.rand(n, k // group, device=dev) * 0.015 + 0.005).half()) for (n, k) in shapes])
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    wbytes = sum(n * k // 2 + n * (k // group) * 2 for (n, k) in shapes)
+    for batch in (1, 16):
+        xs = {k: torch.randn(batch, k, device=dev, dtype=torch.float16) for k in (hid, ffn)}
+
+        def layer_pass():
+            for lw in weights:
+                for (bp, sc) in lw:
+                    capi.w4a16(xs[bp.shape[1] * 2], bp, sc, group=group, workspace=ws)
+        us = _graph_time_us(layer_pass, 2, stream) / layers
+        gbs = wbytes / us / 1e3
+        out[f"int4_decode_batch{batch}"] = {
+            "us_per_layer_linears": us, "tokens_per_s_linears_only_32_layers": batch / (32 * us * 1e-6),
+            "weight_gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
+            "what": "7 int4 weight-only linears of a Llama-2-7B-shaped layer (group 128, fp16 scales), "
+                    "packed weights + scales bytes / time"}
+    return out
+
+
 # ------------------------------------------------------------------ own arm
 def run_own_arm(args):
     import torch
@@ -307,6 +382,8 @@ def run_own_arm(args):
             "gpu_launches": args.steps * launches_step,
             "clocks": clocks, "device_status": status,
         }
+        if world == 1 and not args.no_secondary:
+            line["secondary"] = secondary_measurements(dev, peaks)
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sample()
         print(json.dumps(line), flush=True)
@@ -322,6 +399,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)

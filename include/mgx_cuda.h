@@ -226,8 +226,8 @@ MGX_API int mgx_cuda_transpose_8bit(const void* src, void* dst, int64_t rows, in
  * fp16 out.  This is the IR parse_matmulnbits emits
  * (src/onnx/parse_matmulnbits.cpp:85-158) and what the reference fuses in
  * src/targets/gpu/fuse_mlir.cpp:1236-1276.
- * gemv: HBM-bound kernel for decode (M <= 16), optional split-K through the
- * workspace.  gemm: tensor-core kernel for prefill.  mgx_cuda_w4a16() picks. */
+ * gemv: decode (M <= 16), split-K through the workspace (mgx_cuda_w4a16_workspace bytes).
+ * gemm: any M (prefill); needs K % 128 == 0 and group % 128 == 0.  mgx_cuda_w4a16() picks. */
 typedef struct mgx_w4_desc
 {
     int64_t M, N, K;
@@ -248,6 +248,22 @@ MGX_API int mgx_cuda_w4a16_gemm(const mgx_w4_desc* desc, const void* A, const vo
 MGX_API int mgx_cuda_w4a16(const mgx_w4_desc* desc, const void* A, const void* Bp,
                            const void* scales, const void* zp, void* D, void* workspace,
                            size_t workspace_bytes, void* stream);
+
+/* ---- tensor-parallel exchange -------------------------------------------- *
+ * In-place sum all-reduce over NCCL (NVLink / NVSwitch) on the caller's stream: the exchange
+ * step after the row-split linears (o_proj, down_proj) of a tensor-parallel int4 decoder.
+ * The reference has no collective; there is no counterpart.  NCCL is loaded at run time
+ * (libnccl.so.2 or $MGX_NCCL_LIB); MGX_E_DRIVER if it cannot be found, 2000 + ncclResult_t
+ * on an NCCL error.  One communicator per process (one process per GPU): rank 0 obtains a
+ * 128-byte id with mgx_cuda_comm_unique_id() and hands it to the other ranks out of band.
+ * comm == NULL in mgx_cuda_all_reduce means the process default set with
+ * mgx_cuda_comm_set_default() (what the cuda::all_reduce operator uses). */
+MGX_API int mgx_cuda_comm_unique_id(void* id128);
+MGX_API int mgx_cuda_comm_create(const void* id128, int nranks, int rank, void** comm);
+MGX_API int mgx_cuda_comm_destroy(void* comm);
+MGX_API void mgx_cuda_comm_set_default(void* comm);
+MGX_API void* mgx_cuda_comm_default(void);
+MGX_API int mgx_cuda_all_reduce(void* buf, size_t count, int dtype, void* comm, void* stream);
 
 /* ---- device status ------------------------------------------------------ *
  * Reads and clears the current device's status word (synchronises the device).

@@ -36,6 +36,18 @@ def test_w4a16_decode(cuda_device, M, N, K, group, with_zp):
     np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 256, 1024), (512, 512, 1024), (100, 136, 2304)])
+def test_w4a16_prefill(cuda_device, M, N, K):
+    """More than 16 rows (prefill phase of the int4 decoder): same tolerance."""
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + N + K)
+    a, bp, s, zp = _case(rng, M, N, K, 128, True)
+    ref = O.w4a16_linear(a, bp, s, zp, 8, 128).astype(np.float32)
+    got = capi.w4a16(_t(a, cuda_device), _t(bp, cuda_device), _t(s, cuda_device), _t(zp, cuda_device),
+                     group=128, which="gemm")
+    np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
+
+
 def test_w4a16_rejects_bad_arguments(cuda_device):
     import torch
     from amdmigraphx_b200 import capi
