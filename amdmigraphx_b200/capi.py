@@ -24,7 +24,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm",
+    "mgx_cuda_pack_int4", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -43,6 +43,12 @@ class QgemmDesc(ctypes.Structure):
                 ("ab_type", ctypes.c_int32), ("out_type", ctypes.c_int32),
                 ("b_layout", ctypes.c_int32), ("scale_mode", ctypes.c_int32),
                 ("act", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+
+
+class QgemmQout(ctypes.Structure):
+    _fields_ = [("q", ctypes.c_void_p), ("ldq", ctypes.c_int64), ("stride_q", ctypes.c_int64),
+                ("q_type", ctypes.c_int32), ("scale", ctypes.c_float),
+                ("zero_point", ctypes.c_float), ("reserved", ctypes.c_int32)]
 
 
 class W4Desc(ctypes.Structure):
@@ -80,6 +86,8 @@ def load():
     lib.mgx_cuda_qgemm_workspace.argtypes = [ctypes.POINTER(QgemmDesc)]
     lib.mgx_cuda_qgemm_workspace.restype = sz
     lib.mgx_cuda_qgemm.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.mgx_cuda_qgemm_ex.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp,
+                                      ctypes.POINTER(QgemmQout), vp, sz, vp]
     lib.mgx_cuda_qgemm_static_scratch_limit.restype = sz
     lib.mgx_cuda_qgemm_static_scratch.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp]
     lib.mgx_cuda_transpose_8bit.argtypes = [vp, vp, i64, i64, i64, vp]
@@ -209,9 +217,12 @@ def transpose_8bit(src):
 
 
 def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=None,
-          residual=None, out_dtype=None, out=None, workspace=None):
+          residual=None, out_dtype=None, out=None, workspace=None, q_out=None, q_scale=None,
+          q_zero_point=0.0, write_d=True):
     """quant_dot with the fused epilogue.  a: [M,K] or [B,M,K] int8 / float8_e4m3fn;
-    b: [K,N] (B_KN) or [N,K] (B_NK), optionally batched."""
+    b: [K,N] (B_KN) or [N,K] (B_NK), optionally batched.  q_out (int8 / float8 tensor of the
+    output's shape) additionally receives quantizelinear(result, q_scale, q_zero_point);
+    write_d=False skips the un-quantised result."""
     import torch
     lib = load()
     a3 = a if a.dim() == 3 else a.unsqueeze(0)
@@ -240,9 +251,19 @@ def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=No
     need = lib.mgx_cuda_qgemm_workspace(ctypes.byref(desc))
     if need and workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
-    code = lib.mgx_cuda_qgemm(ctypes.byref(desc), _ptr(a3), _ptr(b3), _ptr(d3), _ptr(scale),
-                              _ptr(bias), _ptr(residual), _ptr(workspace),
-                              0 if workspace is None else workspace.numel(), _stream())
+    if q_out is None:
+        code = lib.mgx_cuda_qgemm(ctypes.byref(desc), _ptr(a3), _ptr(b3), _ptr(d3), _ptr(scale),
+                                  _ptr(bias), _ptr(residual), _ptr(workspace),
+                                  0 if workspace is None else workspace.numel(), _stream())
+    else:
+        q3 = q_out if q_out.dim() == 3 else q_out.unsqueeze(0)
+        qd = QgemmQout(q=q3.data_ptr(), ldq=q3.stride(1), stride_q=q3.stride(0),
+                       q_type=_dtype_code(q3), scale=float(q_scale), zero_point=float(q_zero_point),
+                       reserved=0)
+        code = lib.mgx_cuda_qgemm_ex(ctypes.byref(desc), _ptr(a3), _ptr(b3),
+                                     _ptr(d3) if write_d else None, _ptr(scale), _ptr(bias),
+                                     _ptr(residual), ctypes.byref(qd), _ptr(workspace),
+                                     0 if workspace is None else workspace.numel(), _stream())
     check(code, "mgx_cuda_qgemm")
     if out is not None:
         return out

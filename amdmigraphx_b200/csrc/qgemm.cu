@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "ptx.cuh"
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <mutex>
 
 namespace mgx {
@@ -41,6 +42,13 @@ struct qgemm_params
     int num_kb;
     int scale_mode;
     int act;
+    void* Dq;          // optional second output: quantizelinear(D) as int8 / fp8 (may be the only one)
+    int64_t ldq, stride_q;
+    float q_scale;     // per-tensor scale of that quantizelinear, already in D's type
+    float q_zp;
+    float q_rcp;       // 1 / q_scale refined to full precision
+    int q_fp8;         // 0: int8, 1: fp8 e4m3fn
+    int write_d;       // D itself is wanted
     int vec_sb; // scale / bias vectors are 16-byte aligned (float4 loads allowed)
     int vec_io; // D (and residual) rows can be accessed with 16-byte (fp32/int32) / 8-byte (fp16) vectors
 };
@@ -92,12 +100,29 @@ __device__ __forceinline__ float apply_act(float v)
         return v;
 }
 
+// Conversions (int <-> float, float <-> half, rounding to integer) issue on a pipe with an
+// eighth of the fp32 rate on this GPU; the epilogue handles 32 K values per tile, so they are
+// replaced by exact integer / fp32-add tricks wherever the value range allows.
+//
+// float(acc), exact, for |acc| < 2^22: 0x4B400000 is 1.5 * 2^23, whose ulp is 1.
+__device__ __forceinline__ float int_to_float_small(int32_t acc)
+{
+    return __int_as_float(0x4B400000 + acc) - 12582912.0f;
+}
+
+__device__ __forceinline__ bool fits_small(int32_t a)
+{
+    return static_cast<uint32_t>(a + (1 << 22)) < (1u << 23);
+}
+
 // float(double(acc) * double(s)) without fp64 instructions.  For |acc| < 2^24 the
 // conversion is exact and one fp32 multiply rounds exactly like the reference's
 // double product.  Larger accumulators are split into an exactly representable high
 // part and a small remainder, and the product is summed with error compensation.
 __device__ __forceinline__ float dequant_i32(int32_t acc, float s)
 {
+    if(fits_small(acc))
+        return __fmul_rn(int_to_float_small(acc), s);
     const float a = __int2float_rn(acc);
     float x       = __fmul_rn(a, s);
     if(acc >= (1 << 24) or acc <= -(1 << 24))
@@ -109,6 +134,17 @@ __device__ __forceinline__ float dequant_i32(int32_t acc, float s)
     return x;
 }
 
+// float(half_rz(v)): fp32 value with the mantissa cut to fp16's 10 bits.  Exact for
+// 2^-14 <= |v| < 65536 and for zero; the rare values in fp16's subnormal range (or beyond
+// its maximum) take the real conversion.
+__device__ __forceinline__ float truncate_to_half_precision(float v)
+{
+    const float av = fabsf(v);
+    if(v == 0.0f or (av >= 6.103515625e-5f and av < 65536.0f))
+        return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    return __half2float(__float2half_rz(v));
+}
+
 struct epi_ctx
 {
     const qgemm_params* p;
@@ -116,6 +152,7 @@ struct epi_ctx
     int lane;
     int64_t row0;      // global row of staging row 0
     int64_t batch_off; // b * stride_d
+    int64_t batch_off_q; // b * stride_q
 };
 
 // Second half of the epilogue for one 16-column chunk: read the raw accumulators back
@@ -165,7 +202,7 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                 if constexpr(IS_INT)
                 {
                     const int32_t a = static_cast<int32_t>(wv[j]);
-                    x = p.scale_mode == MGX_SCALE_NONE ? __int2float_rn(a) : dequant_i32(a, s);
+                    x = p.scale_mode == MGX_SCALE_NONE ? (fits_small(a) ? int_to_float_small(a) : __int2float_rn(a)) : dequant_i32(a, s);
                 }
                 else
                 {
@@ -214,26 +251,80 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                     // fp16 model: the reference converts to half by truncating the mantissa
                     // (src/include/migraphx/generic_float.hpp:180-230) before the half add
                     if constexpr(std::is_same<OutT, __half>::value)
-                        v[j] = __half2float(__float2half_rz(v[j]));
+                        v[j] = truncate_to_half_precision(v[j]);
                     v[j] = __fadd_rn(v[j], q[j]);
                 }
             }
-            if constexpr(std::is_same<OutT, float>::value)
+            if constexpr(std::is_same<OutT, __half>::value)
             {
-                if(full)
-                    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-                else
-                    for(int j = 0; j < 4 and c4 + j < p.N; ++j)
-                        dst[j] = v[j];
+                // the stored value is the truncated half; a fused quantizelinear sees that value
+                if(p.Dq != nullptr)
+                {
+#pragma unroll
+                    for(int j = 0; j < 4; ++j)
+                        v[j] = truncate_to_half_precision(v[j]);
+                }
             }
-            else
+            if(p.write_d)
             {
-                if(full)
-                    *reinterpret_cast<uint2*>(dst) =
-                        make_uint2(cvt_rz_f16x2(v[0], v[1]), cvt_rz_f16x2(v[2], v[3]));
+                if constexpr(std::is_same<OutT, float>::value)
+                {
+                    if(full)
+                        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+                    else
+                        for(int j = 0; j < 4 and c4 + j < p.N; ++j)
+                            dst[j] = v[j];
+                }
+                else
+                {
+                    if(full)
+                        *reinterpret_cast<uint2*>(dst) =
+                            make_uint2(cvt_rz_f16x2(v[0], v[1]), cvt_rz_f16x2(v[2], v[3]));
+                    else
+                        for(int j = 0; j < 4 and c4 + j < p.N; ++j)
+                            dst[j] = __float2half_rz(v[j]);
+                }
+            }
+            if(p.Dq != nullptr)
+            {
+                // quantizelinear of the value just produced (per-tensor scale and zero point):
+                // x / s in D's type (fp16: fp32 quotient truncated to half, as migraphx::half
+                // divides), round half to even, + zero point, saturate
+                uint32_t packed = 0;
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                {
+                    // correctly rounded v / s from the reciprocal computed once per kernel
+                    // (one refinement of the quotient, as the division routine does)
+                    float qv        = __fmul_rn(v[j], p.q_rcp);
+                    const float rem = __fmaf_rn(-p.q_scale, qv, v[j]);
+                    qv              = __fmaf_rn(rem, p.q_rcp, qv);
+                    uint32_t b;
+                    if(p.q_fp8)
+                    {
+                        qv = fmaxf(-448.0f, fminf(448.0f, qv + p.q_zp));
+                        b  = static_cast<uint32_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
+                    }
+                    else
+                    {
+                        if constexpr(std::is_same<OutT, __half>::value)
+                            qv = __uint_as_float(__float_as_uint(qv) & 0xFFFFE000u); // half quotient, truncated
+                        // saturate first (keeps the magic-number rounding in range), then round
+                        // half to even by adding 1.5 * 2^23; the low mantissa bits are the integer
+                        qv = fmaxf(-300.0f, fminf(300.0f, qv));
+                        const float r = __fadd_rn(qv, 12582912.0f);
+                        int qi        = __float_as_int(r) - 0x4B400000 + static_cast<int>(p.q_zp);
+                        qi            = max(-128, min(127, qi));
+                        b             = static_cast<uint32_t>(qi) & 0xFFu;
+                    }
+                    packed |= b << (8 * j);
+                }
+                uint8_t* qdst = static_cast<uint8_t*>(p.Dq) + e.batch_off_q + row * p.ldq + c4;
+                if(c4 + 4 <= p.N and ((reinterpret_cast<uintptr_t>(qdst) & 3u) == 0))
+                    *reinterpret_cast<uint32_t*>(qdst) = packed;
                 else
                     for(int j = 0; j < 4 and c4 + j < p.N; ++j)
-                        dst[j] = __float2half_rz(v[j]);
+                        qdst[j] = static_cast<uint8_t>(packed >> (8 * j));
             }
         }
     }
@@ -276,6 +367,7 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
         const int64_t col0 = static_cast<int64_t>(n_blk) * BN + slice * COLS_PER_WARP;
         e.row0      = static_cast<int64_t>(m_blk) * BM + quarter * 32;
         e.batch_off = b * p.stride_d;
+        e.batch_off_q = b * p.stride_q;
 
         // this lane's 4 columns of a chunk: scale and bias.  The first chunk's are fetched
         // before the wait for the accumulator (latency hidden behind the main loop), the
@@ -520,6 +612,17 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 }
 
 // ------------------------------------------------------------------ host
+struct qout_args
+{
+    void* Dq        = nullptr;
+    int64_t ldq     = 0;
+    int64_t stride_q = 0;
+    float scale     = 1.0f;
+    float zp        = 0.0f;
+    int fp8         = 0;
+    int write_d     = 1;
+};
+
 static int encode_operand_map(CUtensorMap* map, const void* base, int64_t k, int64_t rows,
                               int64_t batch, int64_t ld, int64_t batch_stride, int box_rows)
 {
@@ -542,7 +645,7 @@ static int encode_operand_map(CUtensorMap* map, const void* base, int64_t k, int
 template <int BN, bool IS_INT, class OutT>
 static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, void* D,
                         const float* scale, const float* bias, const void* residual,
-                        int64_t ldb, int64_t stride_b, cudaStream_t stream)
+                        int64_t ldb, int64_t stride_b, const qout_args& qo, cudaStream_t stream)
 {
     using S = qgemm_smem<BN>;
     CUtensorMap ta, tb;
@@ -577,6 +680,14 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
     p.num_kb     = static_cast<int>((d.K + BK - 1) / BK);
     p.scale_mode = d.scale_mode;
     p.act        = d.act;
+    p.Dq         = qo.Dq;
+    p.ldq        = qo.ldq;
+    p.stride_q   = qo.stride_q;
+    p.q_scale    = qo.scale;
+    p.q_rcp      = static_cast<float>(1.0 / static_cast<double>(qo.scale));
+    p.q_zp       = qo.zp;
+    p.q_fp8      = qo.fp8;
+    p.write_d    = qo.write_d;
     auto kernel  = qgemm_kernel<BN, IS_INT, OutT>;
     int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(kernel), S::total);
     if(rc2 != MGX_OK)
@@ -590,28 +701,29 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
 template <int BN, bool IS_INT>
 static int dispatch_out(const mgx_qgemm_desc& d, const void* A, const void* B, void* D,
                         const float* scale, const float* bias, const void* residual, int64_t ldb,
-                        int64_t stride_b, cudaStream_t stream)
+                        int64_t stride_b, const qout_args& qo, cudaStream_t stream)
 {
     switch(d.out_type)
     {
     case MGX_I32:
         if constexpr(IS_INT)
-            return launch_qgemm<BN, true, int32_t>(d, A, B, D, scale, bias, residual, ldb, stride_b, stream);
+            return launch_qgemm<BN, true, int32_t>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
         else
             return MGX_E_UNSUPPORTED;
     case MGX_F32:
-        return launch_qgemm<BN, IS_INT, float>(d, A, B, D, scale, bias, residual, ldb, stride_b, stream);
+        return launch_qgemm<BN, IS_INT, float>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
     case MGX_F16:
-        return launch_qgemm<BN, IS_INT, __half>(d, A, B, D, scale, bias, residual, ldb, stride_b, stream);
+        return launch_qgemm<BN, IS_INT, __half>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
     default: return MGX_E_UNSUPPORTED;
     }
 }
 
 // Tile width: the BN in {256, 128, 64} with the smallest estimated time
-//   waves x (k-blocks x cycles per k-block + epilogue cycles),
-// where a k-block costs 4 MMAs of max(BN/2, 48) cycles (below BN = 96 the 128 B/clk
-// shared-memory read rate, not the tensor pipe, bounds a 128 x BN x 32 MMA) and the
-// epilogue about 12 cycles per column.
+//   waves x (k-blocks x cycles per k-block + epilogue cycles) + launch.
+// A k-block (128 bytes of K) moves 128 x (128 + BN) operand bytes from L2 into the SM;
+// measured on B200 that stream sustains about 64 B/clk per SM with every SM loading, which
+// - not the tensor pipe (4 MMAs x BN/2 cycles) - bounds the main loop: 2 x (128 + BN) cycles.
+// The epilogue costs about 12 cycles per output column of the tile.
 static int pick_bn(const mgx_qgemm_desc& d)
 {
     const int64_t sms = device_sm_count();
@@ -623,7 +735,7 @@ static int pick_bn(const mgx_qgemm_desc& d)
     {
         const int64_t tiles = tm * ((d.N + bn - 1) / bn) * d.batch;
         const int64_t waves = (tiles + sms - 1) / sms;
-        const int64_t mma   = 4 * (bn / 2 > 48 ? bn / 2 : 48);
+        const int64_t mma   = 2 * (128 + bn);
         const int64_t cost  = waves * (kb * mma + 12 * bn) + 1500;
         if(cost < best_cost)
         {
@@ -650,9 +762,39 @@ extern "C" int mgx_cuda_qgemm(const mgx_qgemm_desc* d, const void* A, const void
                               const float* scale, const float* bias, const void* residual,
                               void* workspace, size_t workspace_bytes, void* stream_)
 {
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if(d == nullptr or A == nullptr or B == nullptr or D == nullptr)
+    if(D == nullptr)
         return MGX_E_INVALID_ARG;
+    return mgx_cuda_qgemm_ex(d, A, B, D, scale, bias, residual, nullptr, workspace, workspace_bytes,
+                             stream_);
+}
+
+extern "C" int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* d, const void* A, const void* B, void* D,
+                                 const float* scale, const float* bias, const void* residual,
+                                 const mgx_qgemm_qout* q, void* workspace, size_t workspace_bytes,
+                                 void* stream_)
+{
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(d == nullptr or A == nullptr or B == nullptr)
+        return MGX_E_INVALID_ARG;
+    qout_args qo;
+    if(q != nullptr and q->q != nullptr)
+    {
+        if(q->q_type != MGX_I8 and q->q_type != MGX_FP8_E4M3FN)
+            return MGX_E_UNSUPPORTED;
+        if(d->out_type == MGX_I32 or q->ldq < d->N or not(q->scale > 0.0f))
+            return MGX_E_INVALID_ARG;
+        qo.Dq       = q->q;
+        qo.ldq      = q->ldq;
+        qo.stride_q = q->stride_q;
+        qo.scale    = q->scale;
+        qo.zp       = q->zero_point;
+        qo.fp8      = q->q_type == MGX_FP8_E4M3FN ? 1 : 0;
+        qo.write_d  = D != nullptr ? 1 : 0;
+    }
+    else if(D == nullptr)
+        return MGX_E_INVALID_ARG;
+    if(D == nullptr)
+        D = qo.Dq; // never written (write_d = 0); keeps the pointer checks below uniform
     if(d->M <= 0 or d->N <= 0 or d->K <= 0 or d->batch <= 0)
         return MGX_E_INVALID_ARG;
     if(d->ab_type != MGX_I8 and d->ab_type != MGX_FP8_E4M3FN)
@@ -708,14 +850,14 @@ extern "C" int mgx_cuda_qgemm(const mgx_qgemm_desc* d, const void* A, const void
     switch(pick_bn(*d))
     {
     case 256:
-        return is_int ? dispatch_out<256, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream)
-                      : dispatch_out<256, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream);
+        return is_int ? dispatch_out<256, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream)
+                      : dispatch_out<256, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream);
     case 128:
-        return is_int ? dispatch_out<128, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream)
-                      : dispatch_out<128, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream);
+        return is_int ? dispatch_out<128, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream)
+                      : dispatch_out<128, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream);
     default:
-        return is_int ? dispatch_out<64, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream)
-                      : dispatch_out<64, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, stream);
+        return is_int ? dispatch_out<64, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream)
+                      : dispatch_out<64, false>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream);
     }
 }
 

@@ -162,6 +162,83 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// Per-tensor int8 quantizelinear without conversion instructions (int <-> float, float <-> half
+// and round-to-integer issue at an eighth of the fp32 rate on this GPU and would bound the
+// kernel well below the HBM rate).  Bit-identical to Q::quant for q_i8:
+//  * fp16 -> fp32: the half's exponent and mantissa bits are moved to the fp32 position and the
+//    value is rescaled by 2^112 (exact, also for subnormal halves);
+//  * x / s: quotient from the reciprocal computed once, refined with the remainder;
+//  * fp16 input: the quotient is cut to 10 mantissa bits (migraphx::half's truncating conversion);
+//  * round half to even and float -> int by adding 1.5 * 2^23 after saturating.
+template <class In, class IdxT>
+__global__ void __launch_bounds__(256)
+    quantize_i8_uniform_kernel(const In* __restrict__ x, int64_t ldx, const In* __restrict__ scale,
+                               const int8_t* __restrict__ zp, int8_t* __restrict__ y, int64_t ldy,
+                               IdxT rows, IdxT colsv)
+{
+    constexpr int VEC = 16 / sizeof(In);
+    const IdxT total  = rows * colsv;
+    const IdxT stride = static_cast<IdxT>(gridDim.x) * blockDim.x;
+    const float s     = to_f32<In>(scale[0]);
+    const float rcp   = static_cast<float>(1.0 / static_cast<double>(s));
+    const int z       = zp == nullptr ? 0 : static_cast<int>(zp[0]);
+    const bool plain  = s > 0.0f and isfinite(rcp);
+    for(IdxT i = static_cast<IdxT>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride)
+    {
+        const IdxT r = i / colsv;
+        const IdxT c = (i - r * colsv) * VEC;
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + static_cast<int64_t>(r) * ldx + c);
+        float xv[VEC];
+        if constexpr(std::is_same<In, float>::value)
+        {
+            xv[0] = __uint_as_float(raw.x), xv[1] = __uint_as_float(raw.y);
+            xv[2] = __uint_as_float(raw.z), xv[3] = __uint_as_float(raw.w);
+        }
+        else
+        {
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for(int k = 0; k < 4; ++k)
+            {
+                const uint32_t lo = ((w[k] & 0x7FFFu) << 13) | ((w[k] & 0x8000u) << 16);
+                const uint32_t hi = ((w[k] >> 3) & 0x0FFFE000u) | (w[k] & 0x80000000u);
+                xv[2 * k]     = __uint_as_float(lo) * 5.192296858534828e33f; // 2^112
+                xv[2 * k + 1] = __uint_as_float(hi) * 5.192296858534828e33f;
+            }
+        }
+        uint32_t packed[VEC / 4];
+#pragma unroll
+        for(int w = 0; w < VEC / 4; ++w)
+            packed[w] = 0;
+#pragma unroll
+        for(int j = 0; j < VEC; ++j)
+        {
+            uint32_t b;
+            if(plain)
+            {
+                float q         = __fmul_rn(xv[j], rcp);
+                const float rem = __fmaf_rn(-s, q, xv[j]);
+                q               = __fmaf_rn(rem, rcp, q);
+                if constexpr(not std::is_same<In, float>::value)
+                    q = __uint_as_float(__float_as_uint(q) & 0xFFFFE000u);
+                q             = fmaxf(-300.0f, fminf(300.0f, q));
+                const float t = __fadd_rn(q, 12582912.0f);
+                int qi        = __float_as_int(t) - 0x4B400000 + z;
+                qi            = max(-128, min(127, qi));
+                b             = static_cast<uint32_t>(qi) & 0xFFu;
+            }
+            else
+                b = static_cast<uint8_t>(q_i8::quant<In>(xv[j], s, static_cast<float>(z)));
+            packed[j / 4] |= b << (8 * (j % 4));
+        }
+        int8_t* dst = y + static_cast<int64_t>(r) * ldy + c;
+        if constexpr(VEC == 4)
+            *reinterpret_cast<uint32_t*>(dst) = packed[0];
+        else
+            *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
+    }
+}
+
 template <class In, class Q>
 __global__ void __launch_bounds__(256)
     quantize_scalar_kernel(const In* __restrict__ x, int64_t ldx, const In* __restrict__ scale,
@@ -209,6 +286,17 @@ static int launch_quantize(const void* x, int64_t ldx, const void* scale, view2 
         static_cast<const In*>(x), ldx, static_cast<const In*>(scale), ss,                       \
         static_cast<const Out*>(zp), zs, static_cast<Out*>(y), ldy, static_cast<IDX>(rows),      \
         static_cast<IDX>(cols / VEC))
+        if constexpr(std::is_same<Q, q_i8>::value)
+        {
+            if(small and uniform)
+            {
+                quantize_i8_uniform_kernel<In, uint32_t><<<grid, 256, 0, stream>>>(
+                    static_cast<const In*>(x), ldx, static_cast<const In*>(scale),
+                    static_cast<const int8_t*>(zp), static_cast<int8_t*>(y), ldy,
+                    static_cast<uint32_t>(rows), static_cast<uint32_t>(cols / VEC));
+                return static_cast<int>(cudaGetLastError());
+            }
+        }
         if(small and uniform)
             MGX_LAUNCH_QV(uint32_t, true);
         else if(small)

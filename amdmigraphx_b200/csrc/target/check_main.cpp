@@ -158,6 +158,46 @@ test_case qdq_linear(std::size_t m, std::size_t k, std::size_t n, shape::type_t 
     return t;
 }
 
+// Two chained QDQ linears (an MLP): the quantizelinear between them is fed by the first GEMM's
+// epilogue.  keep_hidden also returns the un-quantised hidden tensor (two outputs of one GEMM).
+test_case qdq_mlp(std::size_t m, std::size_t k, std::size_t h, std::size_t n, bool keep_hidden, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm  = t.prog.get_main_module();
+    auto x    = mm->add_parameter("x", shape{shape::float_type, {m, k}});
+    auto zero = mm->add_literal(migraphx::literal{shape{shape::int8_type}, std::vector<int8_t>{0}});
+    auto qdq  = [&](instruction_ref v, float sc, const std::vector<std::size_t>& lens) {
+        auto s  = mm->add_literal(migraphx::literal{shape{shape::float_type}, {sc}});
+        auto q  = mm->add_instruction(migraphx::make_op("quantizelinear"), v, mbcast(mm, s, lens), mbcast(mm, zero, lens));
+        return mm->add_instruction(migraphx::make_op("dequantizelinear"), q, mbcast(mm, s, lens), mbcast(mm, zero, lens));
+    };
+    auto weight = [&](std::size_t kk, std::size_t nn) {
+        auto wq = mm->add_literal(migraphx::literal{shape{shape::int8_type, {kk, nn}}, rand_ints<int8_t>(g, kk * nn, -127, 127)});
+        auto ws = mm->add_literal(migraphx::literal{shape{shape::float_type, {nn}}, rand_uniform(g, nn, 0.001f, 0.01f)});
+        auto wz = mm->add_literal(migraphx::literal{shape{shape::int8_type, {nn}}, std::vector<int8_t>(nn, 0)});
+        return mm->add_instruction(migraphx::make_op("dequantizelinear"), wq, bcast_axis(mm, ws, 1, {kk, nn}),
+                                   bcast_axis(mm, wz, 1, {kk, nn}));
+    };
+    auto d1 = mm->add_instruction(migraphx::make_op("dot"), qdq(x, 0.02f, {m, k}), weight(k, h));
+    auto b1 = mm->add_literal(migraphx::literal{shape{shape::float_type, {h}}, rand_normal(g, h, 0.1f)});
+    auto a1 = mm->add_instruction(migraphx::make_op("add"), d1, bcast_axis(mm, b1, 1, {m, h}));
+    auto r1 = mm->add_instruction(migraphx::make_op("relu"), a1);
+    auto d2 = mm->add_instruction(migraphx::make_op("dot"), qdq(r1, 0.05f, {m, h}), weight(h, n));
+    auto b2 = mm->add_literal(migraphx::literal{shape{shape::float_type, {n}}, rand_normal(g, n, 0.1f)});
+    auto y  = mm->add_instruction(migraphx::make_op("add"), d2, bcast_axis(mm, b2, 1, {m, n}));
+    if(keep_hidden)
+        mm->add_return({y, r1});
+    else
+        mm->add_return({y});
+    auto xv = rand_normal(g, m * k, 1.0f);
+    migraphx::argument xa{shape{shape::float_type, {m, k}}};
+    std::memcpy(xa.data(), xv.data(), xv.size() * sizeof(float));
+    t.params["x"] = xa;
+    t.exact       = true;
+    return t;
+}
+
 // The MatMulNBits IR (src/onnx/parse_matmulnbits.cpp:85-158): packed uint8 weights [N,K/2],
 // fp16 scales [N,K/g] broadcast over the group, zero point 8 (or explicit), transpose, dot.
 test_case int4_linear(std::size_t m, std::size_t n, std::size_t k, std::size_t g, bool with_zp,
@@ -271,6 +311,8 @@ std::map<std::string, std::function<test_case()>> cases()
         {"int4_decode", [] { return int4_linear(1, 256, 512, 128, false, 5); }},
         {"int4_batch16_zp", [] { return int4_linear(16, 128, 1024, 32, true, 6); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
+        {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
+        {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},
         {"raw_quant_dot", [] { return raw_quant_dot(8); }},
     };
 }

@@ -203,19 +203,38 @@ struct op_qgemm
     bool has_residual = false;
     bool b_nk         = false; // B was re-laid out [N,K] at compile time
     bool has_workspace = false;
-    int out_type       = static_cast<int>(shape::int32_type); // shape::type_t of the result
+    int out_type       = static_cast<int>(shape::int32_type); // shape::type_t of the (un-quantised) result
+    // fused trailing quantizelinear (per-tensor): q_type = 0 (none) or the shape::type_t of the
+    // quantised tensor.  write_d = false: the quantised tensor is the only result (it is the
+    // last input); write_d = true: it is an extra input just before the output buffer and is
+    // read back through cuda::second_output.
+    int q_type    = 0;
+    float q_scale = 1.0f;
+    float q_zp    = 0.0f;
+    bool write_d  = true;
     template <class Self, class F>
     static auto reflect(Self& self, F f)
     {
         return pack(f(self.scale_mode, "scale_mode"), f(self.act, "act"),
                     f(self.has_bias, "has_bias"), f(self.has_residual, "has_residual"),
                     f(self.b_nk, "b_nk"), f(self.has_workspace, "has_workspace"),
-                    f(self.out_type, "out_type"));
+                    f(self.out_type, "out_type"), f(self.q_type, "q_type"),
+                    f(self.q_scale, "q_scale"), f(self.q_zp, "q_zp"), f(self.write_d, "write_d"));
     }
     std::string name() const { return "cuda::qgemm"; }
     shape compute_shape(const std::vector<shape>& inputs) const;
     argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
     std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// (producer result, buffer the producer also wrote) -> that buffer: gives the second result
+// of an operator with two outputs its own instruction, ordered after the producer.
+struct op_second_output
+{
+    std::string name() const { return "cuda::second_output"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {1}; }
 };
 
 // Weight-only int4 linear (unpack_int4 + dequantizelinear + transpose + dot fused).

@@ -389,7 +389,43 @@ struct lowerer
         }
         if(workspace != m.end())
             args.push_back(workspace);
-        args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+        // a trailing per-tensor quantizelinear (the next quantized operator's input) is done
+        // by the same epilogue
+        instruction_ref qz = m.end();
+        if(last != qd and last->get_shape().type() != shape::int32_type)
+        {
+            for(auto u : last->outputs())
+            {
+                if(u->name() != "quantizelinear" or u->inputs().size() != 3 or u->inputs()[0] != last)
+                    continue;
+                const auto qt = u->get_shape().type();
+                if(qt != shape::int8_type and qt != shape::fp8e4m3fn_type)
+                    continue;
+                if(not u->inputs()[1]->can_eval() or not u->inputs()[2]->can_eval())
+                    continue;
+                auto cs = classify_constant(u->inputs()[1]);
+                auto cz = classify_constant(u->inputs()[2]);
+                if(cs.kind != bcast_kind::scalar or cz.kind != bcast_kind::scalar or not(cs.values[0] > 0))
+                    continue;
+                op.q_type  = static_cast<int>(qt);
+                op.q_scale = cs.values[0];
+                op.q_zp    = cz.values[0];
+                qz         = u;
+                break;
+            }
+        }
+        const bool only_q = qz != m.end() and last->outputs().size() == 1;
+        if(only_q)
+        {
+            op.write_d = false;
+            args.push_back(insert_allocation(m, qz, qz->get_shape().as_standard()));
+        }
+        else
+        {
+            if(qz != m.end())
+                args.push_back(insert_allocation(m, last, qz->get_shape().as_standard()));
+            args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+        }
         for(auto c : chain)
         {
             consume(c);
@@ -399,8 +435,16 @@ struct lowerer
                     consume(i);
         }
         consume(qd);
+        if(only_q)
+        {
+            consume(last);
+            consume(m.replace_instruction(qz, op, args));
+            return;
+        }
         auto rep = m.replace_instruction(last, op, args);
         consume(rep);
+        if(qz != m.end())
+            consume(m.replace_instruction(qz, op_second_output{}, rep, args[args.size() - 2]));
     }
 
     // ---------------------------------------------------------------- weight-only int4

@@ -170,7 +170,8 @@ argument op_pack_int4::compute(context& ctx, const shape&, const std::vector<arg
 // ------------------------------------------------------------------ quant_dot (+ epilogue)
 shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
 {
-    const std::size_t expect = 3 + (scale_mode != MGX_SCALE_NONE) + has_bias + has_residual + has_workspace;
+    const bool dual          = q_type != 0 and write_d;
+    const std::size_t expect = 3 + (scale_mode != MGX_SCALE_NONE) + has_bias + has_residual + has_workspace + dual;
     check_shapes{inputs, *this}.has(expect);
     const auto& a = inputs[0];
     const auto& b = inputs[1];
@@ -184,9 +185,16 @@ shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
         MIGRAPHX_THROW("cuda::qgemm: inner dimensions differ");
     auto lens   = a.lens();
     lens.back() = b_nk ? b.lens()[b.ndim() - 2] : b.lens().back();
-    const shape expected{static_cast<shape::type_t>(out_type), lens};
+    const bool only_q = q_type != 0 and not write_d;
+    const shape expected{static_cast<shape::type_t>(only_q ? q_type : out_type), lens};
     if(inputs.back().lens() != expected.lens() or inputs.back().type() != expected.type())
         MIGRAPHX_THROW("cuda::qgemm: output buffer does not match the result shape");
+    if(dual)
+    {
+        const auto& qb = inputs[inputs.size() - 2];
+        if(qb.lens() != lens or qb.type() != static_cast<shape::type_t>(q_type) or not qb.standard())
+            MIGRAPHX_THROW("cuda::qgemm: quantised output buffer does not match");
+    }
     return inputs.back();
 }
 
@@ -197,6 +205,9 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     const argument* bias   = has_bias ? &args[i++] : nullptr;
     const argument* resid  = has_residual ? &args[i++] : nullptr;
     const argument* wspace = has_workspace ? &args[i++] : nullptr;
+    const bool dual        = q_type != 0 and write_d;
+    const bool only_q      = q_type != 0 and not write_d;
+    const argument* qbuf   = dual ? &args[i++] : (only_q ? &args.back() : nullptr);
     const argument& out    = args.back();
     const auto& as         = args[0].get_shape();
     const auto& bs         = args[1].get_shape();
@@ -204,7 +215,7 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     const auto nd          = as.ndim();
     if(not ds.standard())
         MIGRAPHX_THROW("cuda::qgemm: output must be a standard tensor");
-    if(resid != nullptr and resid->get_shape() != ds)
+    if(resid != nullptr and resid->get_shape().lens() != ds.lens())
         MIGRAPHX_THROW("cuda::qgemm: residual must have the output's shape");
 
     mgx_qgemm_desc d{};
@@ -242,16 +253,27 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     }
     d.batch      = batch;
     d.ab_type    = mgx_type(as.type());
-    d.out_type   = mgx_type(ds.type());
+    d.out_type   = mgx_type(static_cast<shape::type_t>(out_type));
     d.b_layout   = b_nk ? MGX_B_NK : MGX_B_KN;
     d.scale_mode = scale_mode;
     d.act        = act;
-    check_mgx(mgx_cuda_qgemm(&d, args[0].data(), args[1].data(), out.data(),
-                             scale != nullptr ? reinterpret_cast<const float*>(scale->data()) : nullptr,
-                             bias != nullptr ? reinterpret_cast<const float*>(bias->data()) : nullptr,
-                             resid != nullptr ? resid->data() : nullptr,
-                             wspace != nullptr ? wspace->data() : nullptr,
-                             wspace != nullptr ? wspace->get_shape().bytes() : 0, ctx.stream()),
+    mgx_qgemm_qout qo{};
+    if(qbuf != nullptr)
+    {
+        qo.q          = qbuf->data();
+        qo.ldq        = d.N;
+        qo.stride_q   = d.M * d.N;
+        qo.q_type     = mgx_type(static_cast<shape::type_t>(q_type));
+        qo.scale      = q_scale;
+        qo.zero_point = q_zp;
+    }
+    check_mgx(mgx_cuda_qgemm_ex(&d, args[0].data(), args[1].data(), only_q ? nullptr : out.data(),
+                                scale != nullptr ? reinterpret_cast<const float*>(scale->data()) : nullptr,
+                                bias != nullptr ? reinterpret_cast<const float*>(bias->data()) : nullptr,
+                                resid != nullptr ? resid->data() : nullptr,
+                                qbuf != nullptr ? &qo : nullptr,
+                                wspace != nullptr ? wspace->data() : nullptr,
+                                wspace != nullptr ? wspace->get_shape().bytes() : 0, ctx.stream()),
               "mgx_cuda_qgemm");
     return out;
 }
@@ -308,6 +330,17 @@ argument op_all_reduce::compute(context& ctx, const shape&, const std::vector<ar
     return args[0];
 }
 
+shape op_second_output::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(2);
+    return inputs.at(1);
+}
+argument op_second_output::compute(context&, const shape&, const std::vector<argument>& args) const
+{
+    return args.at(1);
+}
+
+MIGRAPHX_REGISTER_OP(op_second_output)
 MIGRAPHX_REGISTER_OP(op_all_reduce)
 MIGRAPHX_REGISTER_OP(op_quantizelinear)
 MIGRAPHX_REGISTER_OP(op_dequantizelinear)

@@ -42,8 +42,9 @@ class QLinear(object):
 
 
 class BertInt8LinearStack(object):
-    def __init__(self, device, layers=12, hidden=768, ffn=3072, tokens=3072, seed=0):
+    def __init__(self, device, layers=12, hidden=768, ffn=3072, tokens=3072, seed=0, fuse_quant=True):
         import torch
+        self.fuse_quant = fuse_quant
         rng = np.random.default_rng(seed)
         self.device, self.tokens, self.hidden, self.ffn = device, tokens, hidden, ffn
         self.layers = []
@@ -73,6 +74,10 @@ class BertInt8LinearStack(object):
         return sum(l.ops(self.tokens) for layer in self.layers for l in layer.values())
 
     def launches_per_step(self):
+        # fused: the quantizelinear feeding O-proj's successor, FFN2 and the next layer's QKV
+        # runs inside the producing GEMM's epilogue; only the attention-context one stays
+        if self.fuse_quant:
+            return len(self.layers) * 5 + 1
         return len(self.layers) * 8
 
     def weight_bytes(self):
@@ -89,13 +94,14 @@ class BertInt8LinearStack(object):
             st, None, None, ctypes.c_void_p(xq.data_ptr()), capi.I8, xq.stride(0), rows, cols,
             capi._stream()), "mgx_cuda_quantizelinear")
 
-    def _gemm(self, xq, lin, out, residual=None):
+    def _gemm(self, xq, lin, out, residual=None, q_out=None, q_lin=None, write_d=True):
         if self.gemm_events is not None:
             import torch
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
         capi.qgemm(xq, lin.w, b_layout=capi.B_NK, scale=lin.scale, scale_mode=capi.SCALE_PER_COL,
-                   bias=lin.bias, act=lin.act, residual=residual, out=out)
+                   bias=lin.bias, act=lin.act, residual=residual, out=out, q_out=q_out,
+                   q_scale=None if q_lin is None else q_lin.x_scale_f16_host, write_d=write_d)
         if self.gemm_events is not None:
             e.record()
             self.gemm_events.append((s, e, lin.ops(xq.shape[0])))
@@ -106,19 +112,37 @@ class BertInt8LinearStack(object):
         for layer in self.layers:
             for lin in layer.values():
                 lin.x_scale_f16 = lin.x_scale.to(torch.float16)
+                lin.x_scale_f16_host = float(np.float16(lin.x_scale_host[0]))
 
     def step(self, x_in=None):
         """One pass over the stack; returns the last layer's output [tokens, hidden] fp16."""
         x = self.x if x_in is None else x_in
-        for layer in self.layers:
-            self._quant(x, self.xq, layer["qkv"])
+        if not self.fuse_quant:
+            for layer in self.layers:
+                self._quant(x, self.xq, layer["qkv"])
+                self._gemm(self.xq, layer["qkv"], self.qkv)
+                ctx = self.qkv[:, : self.hidden]  # stand-in for the attention context (row stride 3*hidden)
+                self._quant(ctx, self.cq, layer["o"])
+                self._gemm(self.cq, layer["o"], self.o, residual=x if x.stride(0) == self.o.stride(0) else None)
+                self._quant(self.o, self.oq, layer["ffn1"])
+                self._gemm(self.oq, layer["ffn1"], self.h)
+                self._quant(self.h, self.hq, layer["ffn2"])
+                self._gemm(self.hq, layer["ffn2"], self.y, residual=self.o)
+                x = self.y
+            return self.y
+        # fused form: every quantizelinear whose input is produced by a GEMM epilogue runs there
+        # (dequantizelinear -> add -> [gelu] -> [add] -> quantizelinear is one pointwise module)
+        self._quant(x, self.xq, self.layers[0]["qkv"])
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1]["qkv"] if i + 1 < len(self.layers) else None
             self._gemm(self.xq, layer["qkv"], self.qkv)
-            ctx = self.qkv[:, : self.hidden]  # stand-in for the attention context (row stride 3*hidden)
+            ctx = self.qkv[:, : self.hidden]
             self._quant(ctx, self.cq, layer["o"])
-            self._gemm(self.cq, layer["o"], self.o, residual=x if x.stride(0) == self.o.stride(0) else None)
-            self._quant(self.o, self.oq, layer["ffn1"])
-            self._gemm(self.oq, layer["ffn1"], self.h)
-            self._quant(self.h, self.hq, layer["ffn2"])
-            self._gemm(self.hq, layer["ffn2"], self.y, residual=self.o)
+            self._gemm(self.cq, layer["o"], self.o, residual=x if x.stride(0) == self.o.stride(0) else None,
+                       q_out=self.oq, q_lin=layer["ffn1"])
+            # FFN1's fp16 output has no other consumer: only its quantised form is written
+            self._gemm(self.oq, layer["ffn1"], self.h, q_out=self.hq, q_lin=layer["ffn2"], write_d=False)
+            self._gemm(self.hq, layer["ffn2"], self.y, residual=self.o,
+                       q_out=self.xq if nxt is not None else None, q_lin=nxt)
             x = self.y
         return self.y

@@ -5,8 +5,9 @@
     python bench.py --impl reference --gpus N --steps K --warmup W
 
 Workload (own arm): the QDQ linears of a BERT-base-shaped int8 encoder stack, batch 8 x
-384 tokens per GPU (amdmigraphx_b200/workloads.py): per step 48 quantizelinear + 48
-quant_dot launches (dequantizelinear / bias / GELU / residual fused in the epilogue).
+384 tokens per GPU (amdmigraphx_b200/workloads.py): per step 48 quant_dot launches with dequantizelinear /
+bias / GELU / residual and the next operator's quantizelinear fused in the epilogue, plus the
+13 quantizelinear launches whose input no GEMM produces.
 Metric: int8 QDQ GEMM throughput in TOPS = 2*M*N*K of the quant_dots / step time.
 Ranks are independent replicas over their own batch (no data-path collective): weak scaling.
 
@@ -291,7 +292,7 @@ def run_own_arm(args):
         for i in range(max(3, args.warmup)):
             stacks[i % nsets].step()
         torch.cuda.synchronize()
-        # one CUDA graph per set: the 96 launches of a step replay without host work
+        # one CUDA graph per set: the launches of a step replay without host work
         graphs = []
         for st in stacks:
             g = torch.cuda.CUDAGraph()
@@ -366,7 +367,8 @@ def run_own_arm(args):
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": WORKLOAD, "tokens_per_gpu": stacks[0].tokens,
-                       "ops_per_step_per_gpu": ops_step, "launch": "one CUDA graph of 96 kernels per step",
+                       "ops_per_step_per_gpu": ops_step, "launch": f"one CUDA graph of {launches_step} kernels per step (quantizelinear fused "
+                                 "into the producing GEMM epilogue wherever a GEMM produces its input)",
                        "l2": f"{nsets} rotating weight+activation sets of {set_bytes / 1e6:.0f} MB "
                              "(> 126 MB L2 in total)",
                        "parallelism": f"{world} independent replicas, batch-sharded, no collective"},

@@ -184,6 +184,36 @@ MGX_API int mgx_cuda_qgemm(const mgx_qgemm_desc* desc,
                            size_t workspace_bytes,
                            void* stream);
 
+/* quant_dot whose epilogue also (or only) writes quantizelinear(D): the pointwise module
+ * `dequantizelinear -> add -> act -> [add] -> quantizelinear` that fuse_pointwise forms when
+ * the next operator is another quantized GEMM (src/fuse_pointwise.cpp:91-139).  The
+ * quantizelinear has a per-tensor scale (given in D's type, as the operator takes it) and
+ * zero point: q = saturate(rne(D / scale) + zero_point) for MGX_I8, fp8(clamp(D / scale +
+ * zero_point)) for MGX_FP8_E4M3FN, computed from the value D holds (after the conversion to
+ * out_type).  D may be NULL when only the quantized tensor is needed. */
+typedef struct mgx_qgemm_qout
+{
+    void* q;            /* [M,N] per batch, 8-bit                 */
+    int64_t ldq;        /* row stride, elements                   */
+    int64_t stride_q;   /* batch stride, elements                 */
+    int32_t q_type;     /* MGX_I8 | MGX_FP8_E4M3FN                */
+    float scale;        /* > 0                                    */
+    float zero_point;   /* integral for MGX_I8                    */
+    int32_t reserved;
+} mgx_qgemm_qout;
+
+MGX_API int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* desc,
+                              const void* A,
+                              const void* B,
+                              void* D,
+                              const float* scale,
+                              const float* bias,
+                              const void* residual,
+                              const mgx_qgemm_qout* qout,
+                              void* workspace,
+                              size_t workspace_bytes,
+                              void* stream);
+
 /* The same operation for callers that must not allocate device memory and have no buffer
  * of their own to lend: a runtime that carved up all device memory when the model was
  * compiled (MIGraphX plans one arena per program and never allocates during eval), a

@@ -64,3 +64,14 @@ def test_offload_copy_inserts_copies():
 def test_non_constant_right_operand_gets_a_workspace():
     out = _passes("raw_quant_dot")
     assert "has_workspace=1" in out and "int32_type, {2, 72, 48}" in out
+
+
+def test_quantizelinear_between_two_linears_is_fused_into_the_first():
+    out = _passes("mlp_fused_q")
+    gemms = [l for l in out.splitlines() if "cuda::qgemm" in l]
+    assert len(gemms) == 2
+    # first GEMM: relu + trailing quantizelinear (int8, scale 0.05), only the int8 tensor is written
+    assert "q_type=5" in gemms[0] and "write_d=0" in gemms[0] and "int8_type, {96, 320}" in gemms[0]
+    assert out.count("cuda::quantizelinear") == 1  # only the one on the program input is left
+    out = _passes("mlp_two_outputs")
+    assert "cuda::second_output" in out and "write_d=1" in out

@@ -156,3 +156,34 @@ def test_qgemm_rejects_bad_arguments(cuda_device):
     with pytest.raises(capi.MgxError) as e:
         capi.qgemm(a, b, workspace=torch.empty(8, dtype=torch.uint8, device=cuda_device))
     assert e.value.code == capi.E_WORKSPACE
+
+
+@pytest.mark.parametrize("out", ["f16", "f32"])
+@pytest.mark.parametrize("qtype", ["int8", "fp8e4m3fn"])
+@pytest.mark.parametrize("write_d", [True, False])
+def test_qlinear_fused_output_quantizelinear(cuda_device, out, qtype, write_d):
+    """dequantizelinear -> add -> relu -> quantizelinear in one epilogue: the quantised tensor is
+    bit-identical to quantizelinear applied to the stored result."""
+    import torch
+    from amdmigraphx_b200 import capi
+    M, N, K = 200, 328, 512
+    rng = np.random.default_rng(21)
+    a = _rand_i8(rng, (M, K))
+    b = _rand_i8(rng, (K, N))
+    scale = rng.uniform(1e-5, 1e-4, size=N).astype(np.float32)
+    bias = rng.normal(0, 0.1, size=N).astype(np.float32)
+    odt_np, odt = (np.float16, torch.float16) if out == "f16" else (np.float32, torch.float32)
+    y_ref = O.qlinear_epilogue(O.quant_dot_int8(a, b), scale[None, :], bias, "relu", None, odt_np)
+    q_scale = odt_np(0.0125)
+    q_ref = O.quantizelinear(y_ref, np.array([q_scale], dtype=odt_np), None, qtype)
+    qdt = torch.int8 if qtype == "int8" else torch.float8_e4m3fn
+    q = torch.zeros((M, N), dtype=qdt, device=cuda_device)
+    y = torch.full((M, N), 7.0, dtype=odt, device=cuda_device)
+    capi.qgemm(_t(a, cuda_device), _t(b, cuda_device), scale=_t(scale, cuda_device),
+               bias=_t(bias, cuda_device), act="relu", out=y, q_out=q, q_scale=float(q_scale),
+               write_d=write_d)
+    np.testing.assert_array_equal(q.view(torch.uint8).cpu().numpy(), q_ref.view(np.uint8))
+    if write_d:
+        np.testing.assert_array_equal(y.cpu().numpy(), y_ref)
+    else:
+        assert float(y.min()) == 7.0 and float(y.max()) == 7.0  # untouched
