@@ -383,6 +383,169 @@ __global__ void __launch_bounds__(128, 4) w4a16_gemv_mma_kernel(const w4_params 
     }
 }
 
+// ------------------------------------------------------------------ batch-1 / batch-2 decode kernel
+// One or two activation rows: the tensor core has nothing to amortise, so this kernel runs
+// on the fp32 pipe and is built around instruction count (about three per weight):
+//  * a block of 8 warps owns 64 output columns and one K range; a warp owns 8 of them and
+//    walks K in chunks of 1024: lane l reads the 16 bytes holding k = chunk + 32 l .. + 31 of
+//    each of its 8 weight rows (a warp reads 512 contiguous bytes per row);
+//  * the nibble at bit 4j of a word, OR-ed into the mantissa of 2^23, is the fp32 number
+//    2^23 + q * 2^(4j): one logic instruction per weight, no shifts (the upper three nibbles
+//    come from the word shifted right by 12).  Subtracting 2^23 + zp * 2^(4j) leaves
+//    (q - zp) * 2^(4j) exactly, and the activations are pre-multiplied by 2^(-4j) when the
+//    block stages them (as fp32) in shared memory, so one subtract and one FMA finish a weight;
+//  * the group's scale is applied once per lane and chunk (a lane's 32 k lie in one group),
+//    i.e. products are accumulated exactly and scaled afterwards - more accurate than the
+//    reference's per-weight fp16 rounding, well inside the tolerance.
+constexpr int W1_ROWS_PER_WARP = 8;
+constexpr int W1_WARPS         = 8;
+constexpr int W1_CHUNK         = 1024;
+
+template <int MT>
+__global__ void __launch_bounds__(W1_WARPS * 32) w4a16_gemv_fp32_kernel(const w4_params p)
+{
+    __shared__ __align__(16) float a_s[MT][W1_CHUNK];
+    const int warp  = threadIdx.x >> 5;
+    const int lane  = threadIdx.x & 31;
+    const int split = blockIdx.y;
+    const int64_t k_lo = split * p.k_per_split;
+    const int64_t k_hi = min(p.K, k_lo + p.k_per_split);
+    const int64_t n0   = (static_cast<int64_t>(blockIdx.x) * W1_WARPS + warp) * W1_ROWS_PER_WARP;
+
+    const uint8_t* brow[W1_ROWS_PER_WARP];
+    const __half* srow[W1_ROWS_PER_WARP];
+    const uint8_t* zrow[W1_ROWS_PER_WARP];
+#pragma unroll
+    for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+    {
+        int64_t n = n0 + r;
+        n         = n < p.N ? n : p.N - 1;
+        brow[r]   = p.Bp + n * (p.K / 2) + lane * 16;
+        srow[r]   = p.scales + n * p.groups_per_row;
+        zrow[r]   = p.zp == nullptr ? nullptr : p.zp + n * p.groups_per_row;
+    }
+    float acc[MT][W1_ROWS_PER_WARP];
+#pragma unroll
+    for(int m = 0; m < MT; ++m)
+#pragma unroll
+        for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+            acc[m][r] = 0.0f;
+
+    // position of nibble e (k = 8 w + e) after the extraction below: e < 5 stays at bit 4e,
+    // e = 5, 6, 7 come from (word >> 12) at bits 8, 12, 16
+#define MGX_W1_POS(e) ((e) < 5 ? (e) : (e) - 3)
+
+#pragma unroll 1
+    for(int64_t kc = k_lo; kc < k_hi; kc += W1_CHUNK)
+    {
+        const int len = static_cast<int>(min(static_cast<int64_t>(W1_CHUNK), k_hi - kc)); // multiple of 32
+        // this lane's weights of the chunk, all rows in flight before anything is consumed
+        uint4 wv[W1_ROWS_PER_WARP];
+        const bool lane_on = lane * 32 < len;
+#pragma unroll
+        for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+            wv[r] = lane_on ? __ldg(reinterpret_cast<const uint4*>(brow[r] + kc / 2)) : make_uint4(0u, 0u, 0u, 0u);
+        __syncthreads(); // previous chunk's activations are no longer read
+        for(int i = threadIdx.x; i < MT * W1_CHUNK; i += blockDim.x)
+        {
+            const int m = i / W1_CHUNK, k = i - m * W1_CHUNK;
+            float v     = 0.0f;
+            if(k < len and m < p.M)
+                v = __half2float(p.A[m * p.lda + kc + k]);
+            // 2^(-4 pos): exact scaling by a power of two
+            a_s[m][k] = v * __uint_as_float(static_cast<uint32_t>(127 - 4 * MGX_W1_POS(k & 7)) << 23);
+        }
+        __syncthreads();
+        if(not lane_on or n0 >= p.N)
+            continue;
+        const int gi = static_cast<int>((kc + lane * 32) / p.group);
+        float part[MT][W1_ROWS_PER_WARP];
+        float asum[MT]; // sum of this lane's 32 activations (for the zero-point term)
+#pragma unroll
+        for(int m = 0; m < MT; ++m)
+        {
+            asum[m] = 0.0f;
+#pragma unroll
+            for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+                part[m][r] = 0.0f;
+        }
+#pragma unroll
+        for(int w = 0; w < 4; ++w)
+        {
+            float a[MT][8];
+#pragma unroll
+            for(int m = 0; m < MT; ++m)
+            {
+                const float4 lo = *reinterpret_cast<const float4*>(&a_s[m][lane * 32 + w * 8]);
+                const float4 hi = *reinterpret_cast<const float4*>(&a_s[m][lane * 32 + w * 8 + 4]);
+                a[m][0] = lo.x, a[m][1] = lo.y, a[m][2] = lo.z, a[m][3] = lo.w;
+                a[m][4] = hi.x, a[m][5] = hi.y, a[m][6] = hi.z, a[m][7] = hi.w;
+#pragma unroll
+                for(int e = 0; e < 8; ++e) // undo the 2^(-4 pos) pre-scaling: exact
+                    asum[m] = fmaf(a[m][e], static_cast<float>(1 << (4 * MGX_W1_POS(e))), asum[m]);
+            }
+#pragma unroll
+            for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+            {
+                const uint32_t word = w == 0 ? wv[r].x : (w == 1 ? wv[r].y : (w == 2 ? wv[r].z : wv[r].w));
+                const uint32_t hi12 = word >> 12;
+#pragma unroll
+                for(int e = 0; e < 8; ++e)
+                {
+                    const uint32_t src  = e < 5 ? word : hi12;
+                    const uint32_t bits = (src & (0xFu << (4 * MGX_W1_POS(e)))) | 0x4B000000u;
+                    const float v       = __uint_as_float(bits) - 8388608.0f; // q * 2^(4 pos), exact
+#pragma unroll
+                    for(int m = 0; m < MT; ++m)
+                        part[m][r] = fmaf(v, a[m][e], part[m][r]);
+                }
+            }
+        }
+#pragma unroll
+        for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+        {
+            const float sc = __half2float(__ldg(srow[r] + gi));
+            const float z  = static_cast<float>(zrow[r] == nullptr ? p.zp_const : static_cast<int>(__ldg(zrow[r] + gi)));
+#pragma unroll
+            for(int m = 0; m < MT; ++m)
+                acc[m][r] = fmaf(sc, fmaf(-z, asum[m], part[m][r]), acc[m][r]);
+        }
+    }
+#undef MGX_W1_POS
+    // ---- reduce over the lanes (each holds a different part of K) and store
+#pragma unroll
+    for(int m = 0; m < MT; ++m)
+#pragma unroll
+        for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+        {
+            float v = acc[m][r];
+#pragma unroll
+            for(int o = 16; o > 0; o >>= 1)
+                v += __shfl_xor_sync(0xffffffffu, v, o);
+            acc[m][r] = v;
+        }
+    if(lane == 0)
+    {
+#pragma unroll
+        for(int m = 0; m < MT; ++m)
+        {
+            if(m >= p.M)
+                continue;
+#pragma unroll
+            for(int r = 0; r < W1_ROWS_PER_WARP; ++r)
+            {
+                const int64_t n = n0 + r;
+                if(n >= p.N)
+                    continue;
+                if(p.splits > 1)
+                    p.partial[(static_cast<int64_t>(split) * p.M + m) * p.N + n] = acc[m][r];
+                else
+                    p.D[m * p.ldd + n] = __float2half_rn(w4_act(acc[m][r], p.act));
+            }
+        }
+    }
+}
+
 static int validate_w4(const mgx_w4_desc* d, const void* A, const void* Bp, const void* scales,
                        void* D)
 {
@@ -404,8 +567,13 @@ static int validate_w4(const mgx_w4_desc* d, const void* A, const void* Bp, cons
     return MGX_OK;
 }
 
+// one or two activation rows: the fp32-pipe kernel
+static bool use_fp32_path(const mgx_w4_desc& d) { return d.M <= 2 and d.group % 32 == 0 and d.K % 32 == 0; }
+
 static bool use_mma_path(const mgx_w4_desc& d)
 {
+    if(use_fp32_path(d))
+        return false;
     // a group must cover whole 128-k chunks: the per-group scale is applied after the MMAs
     return d.K % W4_CHUNK == 0 and d.group % W4_CHUNK == 0;
 }
@@ -415,6 +583,16 @@ static bool use_mma_path(const mgx_w4_desc& d)
 // 128 k.  The simple kernel splits K only when the columns alone cannot fill the machine.
 static int pick_splits(const mgx_w4_desc& d)
 {
+    if(use_fp32_path(d))
+    {
+        // blocks of 64 columns; split K (in whole 1024-k chunks) until ~4 blocks sit on every SM
+        const int64_t nblocks = ceil_div(d.N, W1_WARPS * W1_ROWS_PER_WARP);
+        const int64_t chunks  = ceil_div(d.K, W1_CHUNK);
+        int64_t s             = ceil_div(static_cast<int64_t>(device_sm_count()) * 4, nblocks);
+        if(s > chunks)
+            s = chunks;
+        return static_cast<int>(s < 1 ? 1 : s);
+    }
     if(use_mma_path(d))
     {
         // blocks = column blocks x 16-row slabs of the activations; K is split only as far
@@ -453,7 +631,7 @@ extern "C" size_t mgx_cuda_w4a16_workspace(const mgx_w4_desc* d)
     if(d->M > 16 and not use_mma_path(*d))
         return 0;
     int s            = pick_splits(*d);
-    const int64_t kq = use_mma_path(*d) ? W4_CHUNK : 32;
+    const int64_t kq = use_fp32_path(*d) ? W1_CHUNK : (use_mma_path(*d) ? W4_CHUNK : 32);
     const int64_t kp = ceil_div(ceil_div(d->K, s), kq) * kq;
     s                = static_cast<int>(ceil_div(d->K, kp));
     return s > 1 ? static_cast<size_t>(s) * d->M * d->N * sizeof(float) : 0;
@@ -485,8 +663,9 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     p.zp_const       = d->zp_const;
     p.act            = d->act;
     const bool mma   = use_mma_path(*d);
+    const bool fp32p = use_fp32_path(*d);
     p.splits         = pick_splits(*d);
-    const int64_t kq = mma ? W4_CHUNK : 32;
+    const int64_t kq = fp32p ? W1_CHUNK : (mma ? W4_CHUNK : 32);
     p.k_per_split    = ceil_div(ceil_div(d->K, p.splits), kq) * kq;
     p.splits         = static_cast<int>(ceil_div(d->K, p.k_per_split));
     if(p.splits > 1)
@@ -498,7 +677,15 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
             return MGX_E_ALIGNMENT;
         p.partial = static_cast<float*>(workspace);
     }
-    if(mma)
+    if(fp32p)
+    {
+        dim3 grid(static_cast<unsigned>(ceil_div(d->N, W1_WARPS * W1_ROWS_PER_WARP)), static_cast<unsigned>(p.splits));
+        if(d->M == 1)
+            w4a16_gemv_fp32_kernel<1><<<grid, W1_WARPS * 32, 0, stream>>>(p);
+        else
+            w4a16_gemv_fp32_kernel<2><<<grid, W1_WARPS * 32, 0, stream>>>(p);
+    }
+    else if(mma)
     {
         const bool hi     = d->M > 8;
         const int smem    = (hi ? 16 : 8) * (W4_MAX_SLICE * 2 + 64) + 4 * W4_RING_BYTES;
