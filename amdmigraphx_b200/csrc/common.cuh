@@ -33,6 +33,14 @@ int transpose_8bit_ld(const void* src, void* dst, int64_t rows, int64_t cols, in
 // Status words of the translation units that own bounded waits.
 int qgemm_status(unsigned int* out);
 int w4a16_status(unsigned int* out);
+int w4a16_tc_status(unsigned int* out);
+
+// tcgen05 int4 decode path (w4a16_tc.cu)
+bool w4a16_tc_applicable(const mgx_w4_desc& d);
+size_t w4a16_tc_workspace(const mgx_w4_desc& d);
+int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const void* scales,
+                    const void* zp, void* D, void* workspace, size_t workspace_bytes,
+                    cudaStream_t stream);
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -74,14 +74,17 @@ extern "C" int mgx_cuda_device_status(int* status)
     cudaError_t e = cudaDeviceSynchronize();
     if(e != cudaSuccess)
         return static_cast<int>(e);
-    unsigned int a = 0, b = 0;
+    unsigned int a = 0, b = 0, c = 0;
     int rc = mgx::qgemm_status(&a);
     if(rc != 0)
         return rc;
     rc = mgx::w4a16_status(&b);
     if(rc != 0)
         return rc;
-    *status = static_cast<int>(a != 0 ? a : b);
+    rc = mgx::w4a16_tc_status(&c);
+    if(rc != 0)
+        return rc;
+    *status = static_cast<int>(a != 0 ? a : (b != 0 ? b : c));
     return MGX_OK;
 }
 

@@ -11,6 +11,7 @@
 // Here: q - zp is exact in fp16, the product with the fp16 scale is rounded once to
 // fp16 (__hmul2), products with A are accumulated in fp32 and rounded once to fp16.
 #include "common.cuh"
+#include <cstdlib>
 #include "ptx.cuh"
 #include <cuda_fp16.h>
 
@@ -624,17 +625,31 @@ using namespace mgx;
 
 int mgx::w4a16_status(unsigned int* out) { return read_and_clear_status(out); }
 
+// MGX_CUDA_W4_TC=0 keeps decode on the CUDA-core / mma.sync kernels (for comparisons).
+static bool tc_enabled()
+{
+    static const bool on = [] {
+        const char* e = std::getenv("MGX_CUDA_W4_TC");
+        return e == nullptr or e[0] != '0';
+    }();
+    return on;
+}
+
 extern "C" size_t mgx_cuda_w4a16_workspace(const mgx_w4_desc* d)
 {
     if(d == nullptr or d->M <= 0 or d->N <= 0 or d->K <= 0)
         return 0;
+    // enough for either decode path: the tensor-core one is taken only when the
+    // pointers it is later given are 16-byte aligned
+    const size_t tc = tc_enabled() and w4a16_tc_applicable(*d) ? w4a16_tc_workspace(*d) + 256 : 0;
     if(d->M > 16 and not use_mma_path(*d))
-        return 0;
+        return tc;
     int s            = pick_splits(*d);
     const int64_t kq = use_fp32_path(*d) ? W1_CHUNK : (use_mma_path(*d) ? W4_CHUNK : 32);
     const int64_t kp = ceil_div(ceil_div(d->K, s), kq) * kq;
     s                = static_cast<int>(ceil_div(d->K, kp));
-    return s > 1 ? static_cast<size_t>(s) * d->M * d->N * sizeof(float) : 0;
+    const size_t cc  = s > 1 ? static_cast<size_t>(s) * d->M * d->N * sizeof(float) : 0;
+    return tc > cc ? tc : cc;
 }
 
 extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const void* Bp,
@@ -645,6 +660,17 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     int rc = validate_w4(d, A, Bp, scales, D);
     if(rc != MGX_OK)
         return rc;
+    if(tc_enabled() and w4a16_tc_applicable(*d) and
+       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bp)) & 15u) == 0)
+    {
+        // 256-byte aligned view of the caller's workspace
+        auto addr          = reinterpret_cast<uintptr_t>(workspace);
+        const size_t shift = workspace == nullptr ? 0 : (256 - (addr & 255u)) & 255u;
+        if(workspace == nullptr or workspace_bytes < shift)
+            return MGX_E_WORKSPACE;
+        return w4a16_tc_launch(*d, A, Bp, scales, zp, D, static_cast<uint8_t*>(workspace) + shift,
+                               workspace_bytes - shift, stream);
+    }
     if(d->M > 16 and not use_mma_path(*d))
         return MGX_E_UNSUPPORTED;
     w4_params p{};
