@@ -37,6 +37,8 @@ int w4a16_tc_status(unsigned int* out);
 
 // tcgen05 int4 decode path (w4a16_tc.cu)
 bool w4a16_tc_applicable(const mgx_w4_desc& d);
+bool w4a16_tc_pointers_ok(const mgx_w4_desc& d, const void* A, const void* Bp, const void* scales,
+                          const void* zp);
 size_t w4a16_tc_workspace(const mgx_w4_desc& d);
 int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const void* scales,
                     const void* zp, void* D, void* workspace, size_t workspace_bytes,

@@ -290,6 +290,49 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 
+// Narrow forms of the same shape: 2, 4 and 8 columns.
+__device__ __forceinline__ void tmem_ld_32x32b_x2(uint32_t taddr, uint32_t (&r)[2])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x4(uint32_t taddr, uint32_t (&r)[4])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                   "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// N columns (2, 4, 8, 16 or 32) of the warp's lane quarter.
+template <int N>
+__device__ __forceinline__ void tmem_ld_32x32b(uint32_t taddr, uint32_t (&r)[N])
+{
+    static_assert(N == 2 or N == 4 or N == 8 or N == 16 or N == 32, "unsupported width");
+    if constexpr(N == 2)
+        tmem_ld_32x32b_x2(taddr, r);
+    else if constexpr(N == 4)
+        tmem_ld_32x32b_x4(taddr, r);
+    else if constexpr(N == 8)
+        tmem_ld_32x32b_x8(taddr, r);
+    else if constexpr(N == 16)
+        tmem_ld_32x32b_x16(taddr, r);
+    else
+        tmem_ld_32x32b_x32(taddr, r);
+}
+
 // Two floats -> packed half2 with round-toward-zero (lo in the low half).
 __device__ __forceinline__ uint32_t cvt_rz_f16x2(float lo, float hi)
 {

@@ -660,8 +660,7 @@ extern "C" int mgx_cuda_w4a16_gemv(const mgx_w4_desc* d, const void* A, const vo
     int rc = validate_w4(d, A, Bp, scales, D);
     if(rc != MGX_OK)
         return rc;
-    if(tc_enabled() and w4a16_tc_applicable(*d) and
-       ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bp)) & 15u) == 0)
+    if(tc_enabled() and w4a16_tc_applicable(*d) and w4a16_tc_pointers_ok(*d, A, Bp, scales, zp))
     {
         // 256-byte aligned view of the caller's workspace
         auto addr          = reinterpret_cast<uintptr_t>(workspace);

@@ -32,27 +32,28 @@
 
 namespace mgx {
 
+
 constexpr int TC_ROWS     = 128; // output columns (weight rows) per CTA tile = UMMA M
 constexpr int TC_GROUP_K  = 128; // k per group
 constexpr int TC_SUPER    = 4;   // groups per work item (each row gives 256 contiguous bytes)
 constexpr int TC_PACKED   = TC_ROWS * TC_GROUP_K / 2; // 8192 bytes of packed weights per group
 constexpr int TC_WSTAGE   = TC_SUPER * TC_PACKED;     // 32768
 constexpr int TC_TSTAGES  = 2;   // A operand buffers in tensor memory
-constexpr int TC_THREADS  = 384;
+constexpr int TC_THREADS  = 480;
+constexpr int TC_ISSUERS  = 4;   // MMA-issuing threads, one per group of a work item
 constexpr int TC_ACC_COLS = 128; // accumulator columns per buffer (two buffers)
 constexpr int TC_A_COL0   = 256; // first tensor-memory column of the A operand buffers
 constexpr int TC_A_COLS   = TC_GROUP_K / 4; // 32 columns per group
-constexpr int TC_EPI      = 2 * (2 * 8 * 128 * 4 + 128 * 4) + 64; // two buffers of epilogue metadata
+constexpr int TC_EPI      = 3 * 128 * (5 + 3 + 1) * 4 + 64; // epilogue metadata
 
-// ring depths by B-operand width: weights (32 KB each), activation tiles (4 NB x 128 bytes)
+// ring depth by B-operand width; a stage = 32 KB of weights + 4 NB x 128 bytes of activations
 template <int NB>
 struct tc_cfg
 {
-    static constexpr int wstages = NB == 16 ? 5 : 4;
-    static constexpr int astages = NB == 16 ? 4 : 3;
-    static constexpr int astage  = TC_SUPER * NB * TC_GROUP_K;
-    static constexpr int ring    = wstages * TC_WSTAGE + astages * astage;
-    static constexpr int smem    = ring + 512 + TC_EPI + 1024;
+    static constexpr int stages = NB == 16 ? 5 : 4;
+    static constexpr int stage  = TC_WSTAGE + TC_SUPER * NB * TC_GROUP_K;
+    static constexpr int ring   = stages * stage;
+    static constexpr int smem   = ring + 512 + TC_EPI + 1024;
 };
 
 struct tc_params
@@ -60,7 +61,7 @@ struct tc_params
     const __half* scales;
     const uint8_t* zp; // may be null
     const float* sa;   // [MB] per-row activation scale
-    const float* sv;   // [K/128][MB] per-group sums of the quantised activations
+    const int* sv;     // [K/128][MB] per-group sums of the quantised activations
     __half* D;
     float* partial;    // [slots][M][N]
     int* counters;     // [tiles] segments finished, zeroed by the pre-kernel
@@ -81,34 +82,38 @@ __device__ __forceinline__ void grid_launch_dependents()
 
 // ------------------------------------------------------------------ activation pre-kernel
 // grid = MB blocks (one per padded activation row), 1024 threads; a thread owns 8 consecutive k.
-// Output: aq rows [0, MB) = h, rows [MB, 2 MB) = l, inside every 8 k the evens first, then the
-// odds (the order the unpacked nibbles have); sv; sa; zeroed tile counters.
-template <int MB>
+// Every activation becomes q = round(a / sa) = 128 h + l.  Two layouts of the int8 rows the
+// tensor core multiplies with the weights (K bytes per row, 128 per group):
+//   RAW = false (2 rows per activation row m): row 2 m = h, row 2 m + 1 = l; inside every 8 k the
+//         evens first, then the odds (the order of the nibbles unpacked to bytes);
+//   RAW = true  (4 rows per m), for a weight operand whose first 64 bytes of a group are the LOW
+//         nibbles L_j = q[2j] and whose last 64 bytes are the packed bytes B_j = 16 q[2j+1] + L_j
+//         themselves: rows [e | 0] and [-o | o] for each of h and l, e_j = a[2j], o_j = a[2j+1], so
+//         that  sum_j L_j e_j  and  sum_j (B_j - L_j) o_j = 16 sum_j q[2j+1] o_j  come out.
+// Also written: sv (per-group sums of q), sa, zeroed tile counters.
+template <int MB, bool RAW>
 __global__ void __launch_bounds__(1024)
     w4_prepare_acts_kernel(const __half* __restrict__ A, int64_t lda, int64_t M, int64_t K,
-                           int8_t* __restrict__ aq, float* __restrict__ sa, float* __restrict__ sv,
+                           int8_t* __restrict__ aq, float* __restrict__ sa, int* __restrict__ sv,
                            int* __restrict__ counters, int ncounters)
 {
     // the main kernel may start (and stream weights) right away; it waits for this grid's
     // completion before it touches anything written here
     grid_launch_dependents();
+    constexpr int RPM = RAW ? 4 : 2; // int8 rows per activation row
     __shared__ float red[32];
     __shared__ float s_scale;
     const int m   = blockIdx.x;
     const int tid = threadIdx.x;
-    int8_t* hi    = aq + static_cast<int64_t>(m) * K;
-    int8_t* lo    = aq + static_cast<int64_t>(MB + m) * K;
+    int8_t* rows  = aq + static_cast<int64_t>(RPM * m) * K;
     for(int i = blockIdx.x * 1024 + tid; i < ncounters; i += gridDim.x * 1024)
         counters[i] = 0;
     if(m >= M)
     {
-        for(int64_t k = tid * 16; k < K; k += 1024 * 16)
-        {
-            *reinterpret_cast<uint4*>(hi + k) = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(lo + k) = make_uint4(0u, 0u, 0u, 0u);
-        }
+        for(int64_t k = tid * 16; k < RPM * K; k += 1024 * 16)
+            *reinterpret_cast<uint4*>(rows + k) = make_uint4(0u, 0u, 0u, 0u);
         for(int64_t g = tid; g < K / 128; g += 1024)
-            sv[g * MB + m] = 0.0f;
+            sv[g * MB + m] = 0;
         if(tid == 0)
             sa[m] = 0.0f;
         return;
@@ -157,7 +162,8 @@ __global__ void __launch_bounds__(1024)
                                             : make_uint4(0u, 0u, 0u, 0u));
         const __half* vh = reinterpret_cast<const __half*>(&v);
         int sum          = 0;
-        uint32_t hw[2] = {0u, 0u}, lw[2] = {0u, 0u};
+        // bytes of the evens (e = 0, 2, 4, 6) and of the odds, for h and for l
+        uint32_t he = 0u, ho = 0u, le = 0u, lo = 0u, nho = 0u, nlo = 0u;
 #pragma unroll
         for(int e = 0; e < 8; ++e)
         {
@@ -166,21 +172,47 @@ __global__ void __launch_bounds__(1024)
             const int h = (q + 64 + 128 * 256) / 128 - 256; // round(q / 128) for any sign
             const int l = q - 128 * h;
             sum += q;
-            const int pos = (e & 1) * 4 + (e >> 1); // evens first, then odds
-            hw[pos >> 2] |= static_cast<uint32_t>(h & 0xFF) << (8 * (pos & 3));
-            lw[pos >> 2] |= static_cast<uint32_t>(l & 0xFF) << (8 * (pos & 3));
+            const int sh = 8 * (e >> 1);
+            if(e & 1)
+            {
+                ho |= static_cast<uint32_t>(h & 0xFF) << sh;
+                lo |= static_cast<uint32_t>(l & 0xFF) << sh;
+                nho |= static_cast<uint32_t>(-h & 0xFF) << sh;
+                nlo |= static_cast<uint32_t>(-l & 0xFF) << sh;
+            }
+            else
+            {
+                he |= static_cast<uint32_t>(h & 0xFF) << sh;
+                le |= static_cast<uint32_t>(l & 0xFF) << sh;
+            }
         }
         if(valid)
         {
-            *reinterpret_cast<uint2*>(hi + k) = make_uint2(hw[0], hw[1]);
-            *reinterpret_cast<uint2*>(lo + k) = make_uint2(lw[0], lw[1]);
+            if constexpr(RAW)
+            {
+                // byte j = k / 2 of the group's low half, 64 + j of its high half
+                const int64_t o = (k & ~int64_t{127}) + ((k & 127) >> 1);
+                *reinterpret_cast<uint32_t*>(rows + o)              = he;
+                *reinterpret_cast<uint32_t*>(rows + o + 64)         = 0u;
+                *reinterpret_cast<uint32_t*>(rows + K + o)          = nho;
+                *reinterpret_cast<uint32_t*>(rows + K + o + 64)     = ho;
+                *reinterpret_cast<uint32_t*>(rows + 2 * K + o)      = le;
+                *reinterpret_cast<uint32_t*>(rows + 2 * K + o + 64) = 0u;
+                *reinterpret_cast<uint32_t*>(rows + 3 * K + o)      = nlo;
+                *reinterpret_cast<uint32_t*>(rows + 3 * K + o + 64) = lo;
+            }
+            else
+            {
+                *reinterpret_cast<uint2*>(rows + k)     = make_uint2(he, ho);
+                *reinterpret_cast<uint2*>(rows + K + k) = make_uint2(le, lo);
+            }
         }
         // 16 consecutive threads hold one group of 128 k
 #pragma unroll
         for(int o = 8; o > 0; o >>= 1)
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if(valid and (tid & 15) == 0)
-            sv[(k >> 7) * MB + m] = static_cast<float>(sum);
+            sv[(k >> 7) * MB + m] = sum;
     }
 }
 
@@ -194,76 +226,75 @@ __global__ void __launch_bounds__(1024)
 // order, so the sum does not depend on timing.
 struct tc_walk
 {
-    int F, F_hi, SG, G;
-    int g; // group cursor inside the current tile
-    __device__ tc_walk(int f_lo, int f_hi, int sg, int groups)
-        : F(f_lo), F_hi(f_hi), SG(sg), G(groups), g((f_lo % sg) * TC_SUPER)
+    int tile, sg, left, SG, G; // cursor (tile, block), work items left
+    __device__ tc_walk(int f_lo, int f_hi, int sg_per_tile, int groups)
+        : tile(f_lo / sg_per_tile),
+          sg(f_lo - (f_lo / sg_per_tile) * sg_per_tile),
+          left(f_hi - f_lo),
+          SG(sg_per_tile),
+          G(groups)
     {
     }
     // next pass: at most `cap` (a multiple of TC_SUPER) groups of one tile
-    __device__ bool next(int cap, int& tile, int& g0, int& count, bool& seg_last)
+    __device__ bool next(int cap, int& tile_out, int& g0, int& count, bool& seg_last)
     {
-        if(F >= F_hi)
+        if(left <= 0)
             return false;
-        tile                 = F / SG;
-        const int seg_end_sg = min(F_hi - tile * SG, SG);
-        const int seg_end_g  = min(G, seg_end_sg * TC_SUPER);
-        g0                   = g;
-        count                = min(cap, seg_end_g - g);
-        g += count;
-        seg_last = g == seg_end_g;
-        if(seg_last)
+        tile_out       = tile;
+        g0             = sg * TC_SUPER;
+        const int nblk = min(cap / TC_SUPER, min(left, SG - sg));
+        count          = min(G, (sg + nblk) * TC_SUPER) - g0;
+        sg += nblk;
+        left -= nblk;
+        seg_last = sg == SG or left == 0;
+        if(sg == SG)
         {
-            F = tile * SG + seg_end_sg;
-            g = 0;
+            sg = 0;
+            ++tile;
         }
         return true;
     }
 };
 
-// int32 known to lie in (-2^22, 2^22) -> float without the conversion pipe
-__device__ __forceinline__ float small_int_to_float(uint32_t v)
-{
-    return __uint_as_float(v + 0x4B400000u) - 12582912.0f;
-}
-
-// NB: activation rows in the B operand (= UMMA N): 16 (M <= 8: 8 h rows + 8 l rows) or 32.
-template <int NB>
+// MR: activation rows folded by the epilogue (M <= MR <= MB).
+// RAW: the weight operand of a group is [64 bytes of low nibbles | the 64 packed bytes] and every
+// activation row has 4 rows in the B operand (see the pre-kernel); otherwise it is the 128
+// nibbles unpacked to bytes and 2 rows.  RAW costs one logic operation per eight weights
+// instead of three, and twice the accumulator columns per activation row.
+template <int NB, int MR, bool RAW>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_a,
                     const tc_params p)
 {
     using cfg            = tc_cfg<NB>;
-    constexpr int MB     = NB / 2;           // padded activation rows
+    constexpr int CPM    = RAW ? 4 : 2;      // accumulator columns per activation row
+    constexpr int MB     = NB / CPM;         // padded activation rows
     constexpr int GPP    = TC_ACC_COLS / NB; // groups per pass (one accumulator buffer): 8 or 4
-    constexpr int WST    = cfg::wstages;
-    constexpr int AST    = cfg::astages;
+    constexpr int WST    = cfg::stages;
     constexpr int ABYTES = NB * TC_GROUP_K;  // activation rows of one group
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = smem_u32(smem_raw);
     uint8_t* smem           = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-    uint8_t* act_ring       = smem + WST * TC_WSTAGE;
     uint8_t* bar_base       = smem + cfg::ring;
-    uint64_t* wfull_bar     = reinterpret_cast<uint64_t*>(bar_base); // weights landed
-    uint64_t* wempty_bar    = wfull_bar + WST;                       // weights read by all rows
-    uint64_t* afull_bar     = wempty_bar + WST;                      // activation tile landed
-    uint64_t* afree_bar     = afull_bar + AST;                       // MMAs that read it retired
-    uint64_t* unp_bar       = afree_bar + AST;                       // A operand in tensor memory
-    uint64_t* tfree_bar     = unp_bar + TC_TSTAGES;                  // MMAs that read it retired
+    uint64_t* full_bar      = reinterpret_cast<uint64_t*>(bar_base); // weights + activations landed
+    uint64_t* empty_bar     = full_bar + WST;   // weights read by all rows, MMAs retired
+    uint64_t* unp_bar       = empty_bar + WST;  // A operand in tensor memory
+    uint64_t* tfree_bar     = unp_bar + TC_TSTAGES; // MMAs that read it retired
     uint64_t* accf_bar      = tfree_bar + TC_TSTAGES;
     uint64_t* acce_bar      = accf_bar + 2;
-    uint64_t* epi_bar       = acce_bar + 2;
-    uint64_t* mfull_bar     = epi_bar + 1; // metadata of a pass staged
-    uint64_t* mempty_bar    = mfull_bar + 2;
-    uint32_t* tmem_slot     = reinterpret_cast<uint32_t*>(mempty_bar + 2);
+    uint64_t* meta_bar      = acce_bar + 2;     // [3] epilogue metadata of a pass staged
+    uint64_t* mfree_bar     = meta_bar + 3;     // [3] ... and folded
+    uint64_t* epi_bar       = mfree_bar + 3;
+    uint32_t* tmem_slot     = reinterpret_cast<uint32_t*>(epi_bar + 1);
     volatile uint32_t* abort_flag = tmem_slot + 1;
-    // epilogue metadata, two buffers: per output column and group of a pass the scale and
-    // scale x zero point, GPP x MB activation group sums; one word for the tile-counter broadcast
-    float* epi_sc = reinterpret_cast<float*>(bar_base + 512); // [2][8][128]
-    float* epi_sz = epi_sc + 2 * 8 * 128;                     // [2][8][128]
-    float* epi_sv = epi_sz + 2 * 8 * 128;                     // [2][128]
-    int* epi_flag = reinterpret_cast<int*>(epi_sv + 2 * 128);
+    // epilogue metadata, three buffers each: per output column the aligned 32-bit words that
+    // hold the scales (at most 5) and zero points (at most 3) of a pass, GPP x MB activation
+    // group sums; a word for the tile-counter broadcast
+    uint32_t* epi_sw = reinterpret_cast<uint32_t*>(bar_base + 512);     // [3][128][5]
+    uint32_t* epi_zw = epi_sw + 3 * 128 * 5;                            // [3][128][3]
+    int* epi_sv      = reinterpret_cast<int*>(epi_zw + 3 * 128 * 3);    // [3][128]
+    int* epi_flag    = epi_sv + 3 * 128;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -272,22 +303,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     {
         for(int s = 0; s < WST; ++s)
         {
-            mbar_init(&wfull_bar[s], 1);
-            mbar_init(&wempty_bar[s], 128);
-        }
-        for(int s = 0; s < AST; ++s)
-        {
-            mbar_init(&afull_bar[s], 1);
-            mbar_init(&afree_bar[s], 1);
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 128 + TC_ISSUERS);
         }
         for(int b = 0; b < 2; ++b)
         {
             mbar_init(&unp_bar[b], 128);
-            mbar_init(&tfree_bar[b], 1);
-            mbar_init(&accf_bar[b], 1);
+            mbar_init(&tfree_bar[b], TC_ISSUERS);
+            mbar_init(&accf_bar[b], TC_ISSUERS);
             mbar_init(&acce_bar[b], 4);
-            mbar_init(&mfull_bar[b], 32);
-            mbar_init(&mempty_bar[b], 4);
+        }
+        for(int b = 0; b < 3; ++b)
+        {
+            mbar_init(&meta_bar[b], 64);
+            mbar_init(&mfree_bar[b], 4);
         }
         mbar_init(epi_bar, 128);
         *abort_flag = 0;
@@ -310,111 +339,60 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     const int f_lo   = min(p.items_total, static_cast<int>(blockIdx.x) * p.items_per_cta);
     const int f_hi   = min(p.items_total, f_lo + p.items_per_cta);
     const int nsuper = f_hi - f_lo;
+    // MMA issuers: warps 1, 10, 11, 12 -> group 0..3 of every work item
+    const int issuer = warp == 1 ? 0 : (warp >= 10 and warp <= 12 ? warp - 9 : -1);
 
     if(warp == 0)
     {
-        // ---------------------------------------------------- TMA producer: packed weights
-        // (constants of the model: no need to wait for the pre-kernel)
+        // ---------------------------------------------------- TMA producer
+        // A stage = 4 groups of packed weights (two requests of 128 rows x 128 bytes) + the
+        // activation rows of the same groups.  The weights are constants of the model and
+        // are requested at once; the activation rows are written by the pre-kernel, whose
+        // completion is awaited before their first request.
         if(lane == 0)
         {
             int tile = f_lo / SG, sg = f_lo - tile * SG;
+            int a_sg = sg; // the activation requests trail the weight requests at the start
+            const int head = min(nsuper, WST);
             for(int j = 0; j < nsuper; ++j)
             {
                 const uint32_t s  = j % WST;
                 const uint32_t ph = (j / WST) & 1u;
-                if(not mbar_wait_bounded(&wempty_bar[s], ph ^ 1u, abort_flag, 2))
+                if(not mbar_wait_bounded(&empty_bar[s], ph ^ 1u, abort_flag, 2))
                     break;
+                uint8_t* st = smem + s * cfg::stage;
                 // groups past the end of K are zero-filled and still counted
-                mbar_expect_tx(&wfull_bar[s], TC_WSTAGE);
-                tma_load_2d(smem + s * TC_WSTAGE, &tmap_w, &wfull_bar[s], sg * (TC_WSTAGE / TC_ROWS),
-                            tile * TC_ROWS);
-                tma_load_2d(smem + s * TC_WSTAGE + TC_WSTAGE / 2, &tmap_w, &wfull_bar[s],
+                mbar_expect_tx(&full_bar[s], cfg::stage);
+                tma_load_2d(st, &tmap_w, &full_bar[s], sg * (TC_WSTAGE / TC_ROWS), tile * TC_ROWS);
+                tma_load_2d(st + TC_WSTAGE / 2, &tmap_w, &full_bar[s],
                             sg * (TC_WSTAGE / TC_ROWS) + 128, tile * TC_ROWS);
+                if(j >= head)
+                    tma_load_3d(st + TC_WSTAGE, &tmap_a, &full_bar[s], 0, 0, sg * TC_SUPER);
                 if(++sg == SG)
                 {
                     sg = 0;
                     ++tile;
                 }
-            }
-        }
-    }
-    else if(warp == 10)
-    {
-        // ---------------------------------------------------- TMA producer: activation rows
-        if(lane == 0)
-        {
-            grid_dependency_wait(); // written by the pre-kernel
-            int sg = f_lo % SG;
-            for(int j = 0; j < nsuper; ++j)
-            {
-                const uint32_t s  = j % AST;
-                const uint32_t ph = (j / AST) & 1u;
-                if(not mbar_wait_bounded(&afree_bar[s], ph ^ 1u, abort_flag, 7))
-                    break;
-                mbar_expect_tx(&afull_bar[s], cfg::astage);
-                tma_load_3d(act_ring + s * cfg::astage, &tmap_a, &afull_bar[s], 0, 0, sg * TC_SUPER);
-                if(++sg == SG)
-                    sg = 0;
-            }
-        }
-    }
-    else if(warp == 11)
-    {
-        // ---------------------------------------------------- epilogue metadata, a pass ahead
-        // Global loads (scales, zero points, activation group sums) and their conversions
-        // happen here, so that the epilogue warps never wait for global memory.  A lane
-        // serves four output columns.
-        grid_dependency_wait(); // sv comes from the pre-kernel
-        const int ratio = p.group / TC_GROUP_K;
-        tc_walk walk(f_lo, f_hi, SG, G);
-        int tile, g0, count;
-        bool seg_last;
-        for(uint32_t pc = 0; walk.next(GPP, tile, g0, count, seg_last); ++pc)
-        {
-            const uint32_t b = pc & 1u;
-            if(not __all_sync(0xffffffffu, mbar_wait_bounded(&mempty_bar[b], ((pc >> 1) & 1u) ^ 1u,
-                                                             abort_flag, 9)))
-                break;
-            unsigned short rs[4][GPP];
-            uint8_t rz[4][GPP];
-#pragma unroll
-            for(int c = 0; c < 4; ++c)
-            {
-                const int64_t n  = static_cast<int64_t>(tile) * TC_ROWS + c * 32 + lane;
-                const int64_t nn = n < p.N ? n : p.N - 1;
-                const unsigned short* srow =
-                    reinterpret_cast<const unsigned short*>(p.scales) + nn * p.groups_per_row;
-                const uint8_t* zrow = p.zp == nullptr ? nullptr : p.zp + nn * p.groups_per_row;
-#pragma unroll
-                for(int gl = 0; gl < GPP; ++gl)
+                if(j == head - 1)
                 {
-                    const int gi = (g0 + min(gl, count - 1)) / ratio;
-                    rs[c][gl]    = __ldg(srow + gi);
-                    rz[c][gl]    = zrow == nullptr ? static_cast<uint8_t>(p.zp_const) : __ldg(zrow + gi);
+                    grid_dependency_wait();
+                    for(int i = 0; i < head; ++i)
+                    {
+                        tma_load_3d(smem + i * cfg::stage + TC_WSTAGE, &tmap_a, &full_bar[i], 0, 0,
+                                    a_sg * TC_SUPER);
+                        if(++a_sg == SG)
+                            a_sg = 0;
+                    }
                 }
             }
-            // GPP x MB = 128 group sums: four per lane
-            float4 sv4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if((lane * 4) / MB < count)
-                sv4 = __ldg(reinterpret_cast<const float4*>(p.sv + static_cast<int64_t>(g0) * MB) + lane);
-#pragma unroll
-            for(int c = 0; c < 4; ++c)
-            {
-#pragma unroll
-                for(int gl = 0; gl < GPP; ++gl)
-                {
-                    const float sc = __half2float(__ushort_as_half(rs[c][gl]));
-                    epi_sc[(b * 8 + gl) * 128 + c * 32 + lane] = sc;
-                    epi_sz[(b * 8 + gl) * 128 + c * 32 + lane] = sc * static_cast<float>(rz[c][gl]);
-                }
-            }
-            *reinterpret_cast<float4*>(epi_sv + b * 128 + lane * 4) = sv4;
-            mbar_arrive(&mfull_bar[b]);
         }
     }
-    else if(warp == 1)
+    else if(issuer >= 0)
     {
-        // ---------------------------------------------------- MMA issuer
+        // ---------------------------------------------------- MMA issuers
+        // One thread of each of four warps issues the four k-steps of "its" group of every
+        // work item: an issue costs a thread some 80 cycles, so one thread alone could not
+        // keep up with the weight stream.
         if(lane == 0)
         {
             // D s32 += A u8 (weights, tensor memory) * B s8 (activation rows, K-major shared
@@ -433,46 +411,109 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 tc_fence_after_sync();
                 for(int gl = 0; gl < count; gl += TC_SUPER, ++j)
                 {
-                    const uint32_t a  = j % AST;
-                    const uint32_t ap = (j / AST) & 1u;
+                    const uint32_t s  = j % WST;
                     const uint32_t t  = j & 1u;
                     const uint32_t tp = (j >> 1) & 1u;
-                    if(not mbar_wait_bounded(&unp_bar[t], tp, abort_flag, 5) or
-                       not mbar_wait_bounded(&afull_bar[a], ap, abort_flag, 1))
+                    // implies that the stage's TMA requests have landed
+                    if(not mbar_wait_bounded(&unp_bar[t], tp, abort_flag, 5))
                     {
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const int cnt = min(TC_SUPER, count - gl);
-                    const uint32_t b_smem = smem_u32(act_ring + a * cfg::astage);
-                    for(int q = 0; q < cnt; ++q)
+                    if(gl + issuer < count)
                     {
-                        const uint64_t bdesc  = make_smem_desc_sw128(b_smem + q * ABYTES);
-                        const uint32_t a_tmem = tmem_base + TC_A_COL0 + (t * TC_SUPER + q) * TC_A_COLS;
-                        const uint32_t d_tmem = tmem_base + buf * TC_ACC_COLS + (gl + q) * NB;
+                        const uint32_t b_smem = smem_u32(smem + s * cfg::stage + TC_WSTAGE + issuer * ABYTES);
+                        const uint64_t bdesc  = make_smem_desc_sw128(b_smem);
+                        const uint32_t a_tmem = tmem_base + TC_A_COL0 + (t * TC_SUPER + issuer) * TC_A_COLS;
+                        const uint32_t d_tmem = tmem_base + buf * TC_ACC_COLS + (gl + issuer) * NB;
 #pragma unroll
                         for(int k = 0; k < 4; ++k)
-                        {
-                            const uint64_t koff = static_cast<uint64_t>((k * 32) >> 4);
-                            mma_i8_tmem_a(d_tmem, a_tmem + k * 8, bdesc + koff, idesc, k != 0);
-                        }
+                            mma_i8_tmem_a(d_tmem, a_tmem + k * 8,
+                                          bdesc + static_cast<uint64_t>((k * 32) >> 4), idesc, k != 0);
                     }
                     tc_commit(&tfree_bar[t]);
-                    tc_commit(&afree_bar[a]);
+                    tc_commit(&empty_bar[s]);
                 }
                 if(ok)
                     tc_commit(&accf_bar[buf]);
             }
         }
     }
+    else if(warp >= 13)
+    {
+        // ---------------------------------------------------- epilogue metadata, up to 3 passes ahead
+        // cp.async copies of the aligned words around the scales and zero points of a pass
+        // (consecutive lanes copy consecutive words of a column's run, so a request touches
+        // few sectors) and of the activation group sums.  Each of the two warps serves 64
+        // output columns.
+        grid_dependency_wait(); // sv comes from the pre-kernel
+        const int half  = warp - 13;
+        const int rshift = 31 - __clz(p.group / TC_GROUP_K); // groups are powers of two
+        const uint32_t sbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.scales) & 3u);
+        const uint32_t zbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.zp) & 3u);
+        const char* sptr = reinterpret_cast<const char*>(p.scales) - sbase0; // 4-byte aligned
+        const char* zptr = reinterpret_cast<const char*>(p.zp) - zbase0;
+        auto cp_async4 = [](const void* dst, const void* src) {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src)
+                         : "memory");
+        };
+        tc_walk walk(f_lo, f_hi, SG, G);
+        int tile, g0, count;
+        bool seg_last;
+        for(uint32_t pc = 0; walk.next(GPP, tile, g0, count, seg_last); ++pc)
+        {
+            const uint32_t vb = pc % 3u;
+            if(not mbar_wait_bounded(&mfree_bar[vb], ((pc / 3u) & 1u) ^ 1u, abort_flag, 9))
+                break;
+            const int gi0 = g0 >> rshift;
+            const int ng  = ((g0 + count - 1) >> rshift) - gi0 + 1;
+            const int n0  = tile * TC_ROWS + half * 64;
+            // scales: up to 5 words per column
+#pragma unroll 2
+            for(int idx = lane; idx < 64 * 5; idx += 32)
+            {
+                const int r = idx / 5, w = idx - r * 5;
+                const int n = min(n0 + r, static_cast<int>(p.N) - 1);
+                // byte offsets from the aligned base: first scale, end of the run
+                const uint32_t s = sbase0 + static_cast<uint32_t>(n * p.groups_per_row + gi0) * 2u;
+                const uint32_t a = s & ~3u;
+                const int nw     = static_cast<int>((((s + ng * 2 + 3u) & ~3u) - a) >> 2);
+                if(w < nw)
+                    cp_async4(epi_sw + (vb * 128 + half * 64 + r) * 5 + w, sptr + a + 4 * w);
+            }
+            if(p.zp != nullptr)
+            {
+#pragma unroll 2
+                for(int idx = lane; idx < 64 * 3; idx += 32)
+                {
+                    const int r = idx / 3, w = idx - r * 3;
+                    const int n = min(n0 + r, static_cast<int>(p.N) - 1);
+                    const uint32_t z = zbase0 + static_cast<uint32_t>(n * p.groups_per_row + gi0);
+                    const uint32_t a = z & ~3u;
+                    const int nw     = static_cast<int>((((z + ng + 3u) & ~3u) - a) >> 2);
+                    if(w < nw)
+                        cp_async4(epi_zw + (vb * 128 + half * 64 + r) * 3 + w, zptr + a + 4 * w);
+                }
+            }
+            // group sums: count x MB floats, half of them per warp
+            for(int i = half * 64 + lane; i < count * MB; i += 32)
+                if(i < half * 64 + 64)
+                    cp_async4(epi_sv + vb * 128 + i, p.sv + static_cast<int64_t>(g0) * MB + i);
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
+                             smem_u32(&meta_bar[vb]))
+                         : "memory");
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    }
     else if(warp < 6)
     {
         // ---------------------------------------------------- unpack: nibbles -> bytes
         // One thread per weight row: 64 packed bytes per group from shared memory (128-byte
         // swizzle, so a quarter warp's 16-byte reads fall in eight different bank groups), 32
-        // words of bytes to this row's lane of tensor memory.  Inside every 8 k the evens come
-        // first, then the odds; the activation rows are stored in the same order.
+        // words to this row's lane of tensor memory: either the nibbles as bytes (inside every
+        // 8 k the evens first, then the odds; the activation rows are stored in the same order)
+        // or the low nibbles followed by the packed bytes as they are (RAW).
         const int row            = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int sw             = row & 7;
@@ -484,7 +525,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             const uint32_t t  = j & 1u;
             const uint32_t tp = (j >> 1) & 1u;
             // the tensor-memory stores below are warp-wide: leave only as a whole warp
-            if(not __all_sync(0xffffffffu, mbar_wait_bounded(&wfull_bar[s], ph, abort_flag, 1)))
+            if(not __all_sync(0xffffffffu, mbar_wait_bounded(&full_bar[s], ph, abort_flag, 1)))
                 break;
             if(not __all_sync(0xffffffffu, mbar_wait_bounded(&tfree_bar[t], tp ^ 1u, abort_flag, 8)))
                 break;
@@ -496,24 +537,34 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if(q < cnt)
                 {
                     // [pair of groups][row][128 bytes], 16-byte chunks swizzled by the row
-                    const uint8_t* pk = smem + s * TC_WSTAGE + (q >> 1) * (2 * TC_PACKED) + row * 128;
+                    const uint8_t* pk = smem + s * cfg::stage + (q >> 1) * (2 * TC_PACKED) + row * 128;
                     uint32_t u[32];
 #pragma unroll
                     for(int c = 0; c < 4; ++c)
                     {
                         const uint4 w =
                             *reinterpret_cast<const uint4*>(pk + ((((q & 1) * 4 + c) ^ sw) << 4));
-                        u[8 * c + 0] = w.x & 0x0F0F0F0Fu, u[8 * c + 1] = (w.x >> 4) & 0x0F0F0F0Fu;
-                        u[8 * c + 2] = w.y & 0x0F0F0F0Fu, u[8 * c + 3] = (w.y >> 4) & 0x0F0F0F0Fu;
-                        u[8 * c + 4] = w.z & 0x0F0F0F0Fu, u[8 * c + 5] = (w.z >> 4) & 0x0F0F0F0Fu;
-                        u[8 * c + 6] = w.w & 0x0F0F0F0Fu, u[8 * c + 7] = (w.w >> 4) & 0x0F0F0F0Fu;
+                        if constexpr(RAW)
+                        {
+                            u[4 * c + 0] = w.x & 0x0F0F0F0Fu, u[16 + 4 * c + 0] = w.x;
+                            u[4 * c + 1] = w.y & 0x0F0F0F0Fu, u[16 + 4 * c + 1] = w.y;
+                            u[4 * c + 2] = w.z & 0x0F0F0F0Fu, u[16 + 4 * c + 2] = w.z;
+                            u[4 * c + 3] = w.w & 0x0F0F0F0Fu, u[16 + 4 * c + 3] = w.w;
+                        }
+                        else
+                        {
+                            u[8 * c + 0] = w.x & 0x0F0F0F0Fu, u[8 * c + 1] = (w.x >> 4) & 0x0F0F0F0Fu;
+                            u[8 * c + 2] = w.y & 0x0F0F0F0Fu, u[8 * c + 3] = (w.y >> 4) & 0x0F0F0F0Fu;
+                            u[8 * c + 4] = w.z & 0x0F0F0F0Fu, u[8 * c + 5] = (w.z >> 4) & 0x0F0F0F0Fu;
+                            u[8 * c + 6] = w.w & 0x0F0F0F0Fu, u[8 * c + 7] = (w.w >> 4) & 0x0F0F0F0Fu;
+                        }
                     }
                     tmem_st_32x32b_x32(tmem_base + lane_addr + TC_A_COL0 +
                                            (t * TC_SUPER + q) * TC_A_COLS,
                                        u);
                 }
             }
-            mbar_arrive(&wempty_bar[s]); // the packed blocks are in registers
+            mbar_arrive(&empty_bar[s]); // the packed blocks are in registers
             tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(&unp_bar[t]);
@@ -524,16 +575,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     else
     {
         // ---------------------------------------------------- epilogue: fold the groups
-        // Scales, zero points and activation group sums of the pass are already in shared
-        // memory (metadata warp).  All arithmetic stays off the conversion pipe: |P_hi|,
-        // |P_lo| < 2^18.
-        grid_dependency_wait(); // sv, sa and the tile counters come from the pre-kernel
+        // Scale, zero point and activation group sums of a pass are already in shared memory
+        // (metadata warps).  Column 2 m of a group's accumulator is P_hi, column 2 m + 1 P_lo
+        // of activation row m; only the MR rows in use are read.  All arithmetic stays off
+        // the conversion pipe except one half -> float per group: |P_hi|, |P_lo| < 2^18.
+        grid_dependency_wait(); // sa and the tile counters come from the pre-kernel
         const int quarter = warp & 3;
-        const int te      = threadIdx.x - 192; // 0..127
+        const int te      = threadIdx.x - 192;   // 0..127
         const int col     = quarter * 32 + lane; // output column inside the tile = TMEM lane
-        float out[MB];
+        const int rshift  = 31 - __clz(p.group / TC_GROUP_K); // groups are powers of two
+        const uint32_t sbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.scales) & 3u);
+        const uint32_t zbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.zp) & 3u);
+        float out[MR];
 #pragma unroll
-        for(int m = 0; m < MB; ++m)
+        for(int m = 0; m < MR; ++m)
             out[m] = 0.0f;
         tc_walk walk(f_lo, f_hi, SG, G);
         uint32_t epi_phase = 0;
@@ -544,78 +599,113 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             ++epi_phase;
             return __all_sync(0xffffffffu, r);
         };
-        // one group: out[m] += sc (128 P_hi + P_lo) - sc z Sv
-        auto fold = [&](const uint32_t(&acc)[NB], int gl, const float* scb, const float* szb,
-                        const float* svb) {
-            const float sc = scb[gl * 128 + col];
-            const float sz = szb[gl * 128 + col];
-#pragma unroll
-            for(int m = 0; m < MB; ++m)
+        // one group: out[m] += sc (Q[m] - z Sv[m]) with Q = sum_k q a_int, in exact integer
+        // arithmetic up to the one conversion.  soff / zoff: byte offset of the group's scale /
+        // zero point inside this column's staged words
+        constexpr int C  = CPM * MR; // accumulator columns read per group
+        const bool has_zp = p.zp != nullptr;
+        auto fold = [&](const uint32_t(&acc)[C], int gl, uint32_t vb, uint32_t soff, uint32_t zoff) {
+            const uint32_t sw = epi_sw[(vb * 128 + col) * 5 + (soff >> 2)];
+            const uint32_t sh = (soff & 2u) ? sw >> 16 : sw & 0xFFFFu;
+            float sc          = __half2float(__ushort_as_half(static_cast<unsigned short>(sh)));
+            // without zero points the staged word is not meaningful and not used
+            const uint32_t zw = epi_zw[(vb * 128 + col) * 3 + (has_zp ? zoff >> 2 : 0u)];
+            int z = has_zp ? static_cast<int>((zw >> (8u * (zoff & 3u))) & 0xFFu) : p.zp_const;
+            if constexpr(RAW)
             {
-                const float fh = small_int_to_float(acc[m]);
-                const float fl = small_int_to_float(acc[MB + m]);
-                out[m]         = fmaf(sc, fmaf(fh, 128.0f, fl), out[m]);
-                out[m]         = fmaf(-sz, svb[gl * MB + m], out[m]);
+                sc *= 0.0625f; // Q is computed times 16
+                z *= 16;
+            }
+            const int* svb = epi_sv + vb * 128 + gl * MB;
+#pragma unroll
+            for(int m = 0; m < MR; ++m)
+            {
+                int q;
+                if constexpr(RAW)
+                {
+                    // columns: sum L e_h, 16 sum q_odd o_h, sum L e_l, 16 sum q_odd o_l;
+                    // 16 Q = 2048 E_h + 128 O_h + 16 E_l + O_l
+                    q = static_cast<int>(acc[4 * m]) * 2048 + static_cast<int>(acc[4 * m + 3]);
+                    q = static_cast<int>(acc[4 * m + 1]) * 128 + q;
+                    q = static_cast<int>(acc[4 * m + 2]) * 16 + q;
+                }
+                else
+                    q = static_cast<int>(acc[2 * m]) * 128 + static_cast<int>(acc[2 * m + 1]);
+                q      = q - z * svb[m];
+                out[m] = fmaf(sc, static_cast<float>(q), out[m]);
             }
         };
+        // groups read from tensor memory per trip (all loads in flight before the first fold)
+        constexpr int TR = C <= 4 ? 8 : (C <= 8 ? 4 : 2);
         int tile, g0, count;
         bool seg_last;
         bool ok = true;
         for(uint32_t pc = 0; ok and walk.next(GPP, tile, g0, count, seg_last); ++pc)
         {
             const uint32_t buf = pc & 1u;
+            const uint32_t vb  = pc % 3u;
             if(not __all_sync(0xffffffffu,
-                              mbar_wait_bounded(&mfull_bar[buf], (pc >> 1) & 1u, abort_flag, 10)) or
-               not __all_sync(0xffffffffu,
+                              mbar_wait_bounded(&meta_bar[vb], (pc / 3u) & 1u, abort_flag, 10)))
+                break;
+            if(not __all_sync(0xffffffffu,
                               mbar_wait_bounded(&accf_bar[buf], (pc >> 1) & 1u, abort_flag, 3)))
                 break;
             tc_fence_after_sync();
-            const float* svb     = epi_sv + buf * 128;
-            const float* scb     = epi_sc + buf * 8 * 128;
-            const float* szb     = epi_sz + buf * 8 * 128;
+            const int gi0 = g0 >> rshift;
+            const int n   = min(tile * TC_ROWS + col, static_cast<int>(p.N) - 1);
+            const uint32_t sbyte =
+                (sbase0 + static_cast<uint32_t>(n * p.groups_per_row + gi0) * 2u) & 3u;
+            const uint32_t zbyte = (zbase0 + static_cast<uint32_t>(n * p.groups_per_row + gi0)) & 3u;
+            // quantisation group of group gl, relative to gi0
+            auto grel = [&](int gl) { return static_cast<uint32_t>(((g0 + gl) >> rshift) - gi0); };
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                                    buf * TC_ACC_COLS;
-            // two groups per trip: the second TMEM read is in flight while the first is folded
 #pragma unroll 1
-            for(int gl = 0; gl < count; gl += 2)
+            for(int gl = 0; gl < count; gl += TR)
             {
-                uint32_t acc0[NB], acc1[NB];
-                const bool two = gl + 1 < count; // the same for the whole warp
-                if constexpr(NB == 16)
+                uint32_t acc[TR][C];
+                if(gl + TR <= count)
                 {
-                    tmem_ld_32x32b_x16(tbase + gl * NB, acc0);
-                    if(two)
-                        tmem_ld_32x32b_x16(tbase + (gl + 1) * NB, acc1);
+                    // full trip: straight-line code, the folds interleave
+#pragma unroll
+                    for(int t = 0; t < TR; ++t)
+                        tmem_ld_32x32b<C>(tbase + (gl + t) * NB, acc[t]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int t = 0; t < TR; ++t)
+                        fold(acc[t], gl + t, vb, sbyte + 2u * grel(gl + t), zbyte + grel(gl + t));
                 }
                 else
                 {
-                    tmem_ld_32x32b_x32(tbase + gl * NB, acc0);
-                    if(two)
-                        tmem_ld_32x32b_x32(tbase + (gl + 1) * NB, acc1);
+#pragma unroll
+                    for(int t = 0; t < TR; ++t)
+                        if(gl + t < count) // the same for the whole warp
+                            tmem_ld_32x32b<C>(tbase + (gl + t) * NB, acc[t]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int t = 0; t < TR; ++t)
+                        if(gl + t < count)
+                            fold(acc[t], gl + t, vb, sbyte + 2u * grel(gl + t), zbyte + grel(gl + t));
                 }
-                tmem_ld_wait();
-                fold(acc0, gl, scb, szb, svb);
-                if(two)
-                    fold(acc1, gl + 1, scb, szb, svb);
             }
             tc_fence_before_sync();
             __syncwarp();
             if(lane == 0)
             {
                 mbar_arrive(&acce_bar[buf]);
-                mbar_arrive(&mempty_bar[buf]);
+                mbar_arrive(&mfree_bar[vb]);
             }
             if(seg_last)
             {
                 // this CTA's share of the tile is complete
-                const int64_t n  = static_cast<int64_t>(tile) * TC_ROWS + quarter * 32 + lane;
+                const int64_t nc = static_cast<int64_t>(tile) * TC_ROWS + col;
                 const bool whole = f_lo <= tile * SG and f_hi >= (tile + 1) * SG;
                 if(whole)
                 {
 #pragma unroll
-                    for(int m = 0; m < MB; ++m)
-                        if(m < p.M and n < p.N)
-                            p.D[m * p.ldd + n] = __float2half_rn(out[m] * __ldg(p.sa + m));
+                    for(int m = 0; m < MR; ++m)
+                        if(m < p.M and nc < p.N)
+                            p.D[m * p.ldd + nc] = __float2half_rn(out[m] * __ldg(p.sa + m));
                 }
                 else
                 {
@@ -623,9 +713,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const int last  = ((tile + 1) * SG - 1) / p.items_per_cta;
                     const int slot  = static_cast<int>(blockIdx.x) - first;
 #pragma unroll
-                    for(int m = 0; m < MB; ++m)
-                        if(m < p.M and n < p.N)
-                            p.partial[(static_cast<int64_t>(slot) * p.M + m) * p.N + n] = out[m];
+                    for(int m = 0; m < MR; ++m)
+                        if(m < p.M and nc < p.N)
+                            p.partial[(static_cast<int64_t>(slot) * p.M + m) * p.N + nc] = out[m];
                     __threadfence();
                     ok = epi_sync();
                     if(ok and te == 0)
@@ -636,20 +726,20 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                         // every other segment of the tile is in memory: add them in slot order
                         __threadfence();
 #pragma unroll
-                        for(int m = 0; m < MB; ++m)
+                        for(int m = 0; m < MR; ++m)
                         {
-                            if(m < p.M and n < p.N)
+                            if(m < p.M and nc < p.N)
                             {
                                 float v = 0.0f;
                                 for(int s = 0; s <= last - first; ++s)
-                                    v += __ldcg(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + n);
-                                p.D[m * p.ldd + n] = __float2half_rn(v * __ldg(p.sa + m));
+                                    v += __ldcg(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + nc);
+                                p.D[m * p.ldd + nc] = __float2half_rn(v * __ldg(p.sa + m));
                             }
                         }
                     }
                 }
 #pragma unroll
-                for(int m = 0; m < MB; ++m)
+                for(int m = 0; m < MR; ++m)
                     out[m] = 0.0f;
             }
         }
@@ -684,8 +774,9 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 tc_plan make_plan(const mgx_w4_desc& d)
 {
     tc_plan pl{};
-    pl.nb            = d.M <= 8 ? 16 : 32;
-    pl.mb            = pl.nb / 2;
+    // up to 8 rows: 4 int8 rows per activation row (RAW operand); up to 16: 2 rows
+    pl.nb            = d.M <= 4 ? 16 : 32;
+    pl.mb            = d.M <= 4 ? 4 : (d.M <= 8 ? 8 : 16);
     pl.tiles         = static_cast<int>(ceil_div(d.N, TC_ROWS));
     pl.groups        = static_cast<int>(d.K / TC_GROUP_K);
     pl.blocks        = (pl.groups + TC_SUPER - 1) / TC_SUPER;
@@ -721,11 +812,11 @@ int encode_grouped(CUtensorMap* map, const void* base, uint32_t inner, uint64_t 
     return r == CUDA_SUCCESS ? MGX_OK : MGX_E_INVALID_ARG;
 }
 
-template <int NB>
+template <int NB, int MR, bool RAW>
 int launch_main(int grid, const CUtensorMap& tw, const CUtensorMap& ta, const tc_params& p,
                 cudaStream_t stream)
 {
-    int rc = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_tc_kernel<NB>), tc_cfg<NB>::smem);
+    int rc = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_tc_kernel<NB, MR, RAW>), tc_cfg<NB>::smem);
     if(rc != MGX_OK)
         return rc;
     // programmatic dependent launch: the kernel may start while the pre-kernel still runs
@@ -740,7 +831,7 @@ int launch_main(int grid, const CUtensorMap& tw, const CUtensorMap& ta, const tc
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs                                          = attr;
     cfg.numAttrs                                       = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<NB>, tw, ta, p));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<NB, MR, RAW>, tw, ta, p));
 }
 
 } // namespace
@@ -748,8 +839,21 @@ int launch_main(int grid, const CUtensorMap& tw, const CUtensorMap& ta, const tc
 bool w4a16_tc_applicable(const mgx_w4_desc& d)
 {
     return d.M >= 1 and d.M <= 16 and d.K % TC_GROUP_K == 0 and d.group % TC_GROUP_K == 0 and
-           d.act == MGX_ACT_NONE and d.lda % 8 == 0 and
-           ceil_div(d.N, TC_ROWS) * (d.K / TC_GROUP_K) < (int64_t{1} << 30);
+           ((d.group / TC_GROUP_K) & (d.group / TC_GROUP_K - 1)) == 0 and d.act == MGX_ACT_NONE and
+           d.lda % 8 == 0 and
+           ceil_div(d.N, TC_ROWS) * (d.K / TC_GROUP_K) < (int64_t{1} << 30) and
+           (d.N + TC_ROWS) * (d.K / d.group) < (int64_t{1} << 30);
+}
+
+// The kernel copies the aligned 32-bit word around every scale and zero point, and fetches
+// weights and activations in 16-byte units.
+bool w4a16_tc_pointers_ok(const mgx_w4_desc& d, const void* A, const void* Bp, const void* scales,
+                          const void* zp)
+{
+    const int64_t nmeta = d.N * (d.K / d.group);
+    return ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(Bp)) & 15u) == 0 and
+           (reinterpret_cast<uintptr_t>(scales) & 3u) == 0 and nmeta % 2 == 0 and
+           (zp == nullptr or ((reinterpret_cast<uintptr_t>(zp) & 3u) == 0 and nmeta % 4 == 0));
 }
 
 size_t w4a16_tc_workspace(const mgx_w4_desc& d) { return make_plan(d).total; }
@@ -762,12 +866,12 @@ int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const v
     if(workspace == nullptr or workspace_bytes < pl.total)
         return MGX_E_WORKSPACE;
     if((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 or
-       ((reinterpret_cast<uintptr_t>(Bp) | reinterpret_cast<uintptr_t>(A)) & 15u) != 0)
+       not w4a16_tc_pointers_ok(d, A, Bp, scales, zp))
         return MGX_E_ALIGNMENT;
     auto* ws       = static_cast<uint8_t*>(workspace);
     auto* aq       = reinterpret_cast<int8_t*>(ws);
     auto* sa       = reinterpret_cast<float*>(ws + pl.off_sa);
-    auto* sv       = reinterpret_cast<float*>(ws + pl.off_sv);
+    auto* sv       = reinterpret_cast<int*>(ws + pl.off_sv);
     auto* counters = reinterpret_cast<int*>(ws + pl.off_counters);
     auto* part     = reinterpret_cast<float*>(ws + pl.off_partial);
     CUtensorMap tw, ta;
@@ -794,12 +898,16 @@ int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const v
                         CU_TENSOR_MAP_SWIZZLE_128B);
     if(rc != MGX_OK)
         return rc;
-    if(pl.nb == 16)
-        w4_prepare_acts_kernel<8><<<8, 1024, 0, stream>>>(static_cast<const __half*>(A), d.lda, d.M,
-                                                          d.K, aq, sa, sv, counters, pl.tiles);
+    const auto* a16 = static_cast<const __half*>(A);
+    if(pl.mb == 4)
+        w4_prepare_acts_kernel<4, true><<<4, 1024, 0, stream>>>(a16, d.lda, d.M, d.K, aq, sa, sv,
+                                                                counters, pl.tiles);
+    else if(pl.mb == 8)
+        w4_prepare_acts_kernel<8, true><<<8, 1024, 0, stream>>>(a16, d.lda, d.M, d.K, aq, sa, sv,
+                                                                counters, pl.tiles);
     else
-        w4_prepare_acts_kernel<16><<<16, 1024, 0, stream>>>(static_cast<const __half*>(A), d.lda, d.M,
-                                                            d.K, aq, sa, sv, counters, pl.tiles);
+        w4_prepare_acts_kernel<16, false><<<16, 1024, 0, stream>>>(a16, d.lda, d.M, d.K, aq, sa, sv,
+                                                                   counters, pl.tiles);
     cudaError_t e = cudaGetLastError();
     if(e != cudaSuccess)
         return static_cast<int>(e);
@@ -821,8 +929,15 @@ int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const v
     p.act            = d.act;
     p.items_total    = pl.items_total;
     p.items_per_cta  = pl.items_per_cta;
-    return pl.nb == 16 ? launch_main<16>(pl.grid, tw, ta, p, stream)
-                       : launch_main<32>(pl.grid, tw, ta, p, stream);
+    if(d.M == 1)
+        return launch_main<16, 1, true>(pl.grid, tw, ta, p, stream);
+    if(d.M == 2)
+        return launch_main<16, 2, true>(pl.grid, tw, ta, p, stream);
+    if(d.M <= 4)
+        return launch_main<16, 4, true>(pl.grid, tw, ta, p, stream);
+    if(d.M <= 8)
+        return launch_main<32, 8, true>(pl.grid, tw, ta, p, stream);
+    return launch_main<32, 16, false>(pl.grid, tw, ta, p, stream);
 }
 
 int w4a16_tc_status(unsigned int* out) { return read_and_clear_status(out); }

@@ -25,6 +25,7 @@ def _case(rng, M, N, K, group, with_zp):
     (1, 256, 512, 128), (1, 4096, 4096, 128), (16, 512, 1024, 128), (4, 100, 256, 32),
     (3, 64, 11008, 128), (16, 1024, 4096, 128), (2, 40, 64, 64),
     (8, 1000, 2048, 256), (5, 4096, 8192, 128), (12, 130, 640, 128), (9, 20000, 1024, 512),
+    (2, 512, 1024, 128), (4, 384, 2048, 128), (7, 3000, 1536, 128), (1, 8192, 28672, 128),
 ])
 @pytest.mark.parametrize("with_zp", [False, True])
 def test_w4a16_decode(cuda_device, M, N, K, group, with_zp):
