@@ -23,8 +23,8 @@
 //               unpacked bytes never cross shared memory
 //   warp 1      MMA issuer (A from tensor memory, B = activation rows in shared memory)
 //   warp 11     loads and converts the epilogue's scales / zero points / group sums a pass ahead
-//   warps 6..9  epilogue fold out of two accumulator buffers; the last CTA to finish a tile
-//               that several CTAs share adds their partial sums in a fixed order
+//   warps 6..9  epilogue fold out of two accumulator buffers; the last warp to finish its 32
+//               columns of a tile that several CTAs share adds their partial sums in a fixed order
 // Only plain TMA loads; every wait is bounded.
 #include "common.cuh"
 #include "ptx.cuh"
@@ -64,7 +64,7 @@ struct tc_params
     const int* sv;     // [K/128][MB] per-group sums of the quantised activations
     __half* D;
     float* partial;    // [slots][M][N]
-    int* counters;     // [tiles] segments finished, zeroed by the pre-kernel
+    int* counters;     // [tiles][4] warps (by lane quarter) done with a shared tile, zeroed by the pre-kernel
     int64_t M, N, K, ldd;
     int group, groups_per_row, zp_const, act;
     int items_total, items_per_cta; // (tile, 4-group block) work items, see the main kernel
@@ -100,6 +100,9 @@ __global__ void __launch_bounds__(1024)
     // the main kernel may start (and stream weights) right away; it waits for this grid's
     // completion before it touches anything written here
     grid_launch_dependents();
+    // this kernel itself may have been started before the previous kernel of the stream has
+    // finished (which may still read the workspace, or be writing A)
+    grid_dependency_wait();
     constexpr int RPM = RAW ? 4 : 2; // int8 rows per activation row
     __shared__ float red[32];
     __shared__ float s_scale;
@@ -285,20 +288,21 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     uint64_t* acce_bar      = accf_bar + 2;
     uint64_t* meta_bar      = acce_bar + 2;     // [3] epilogue metadata of a pass staged
     uint64_t* mfree_bar     = meta_bar + 3;     // [3] ... and folded
-    uint64_t* epi_bar       = mfree_bar + 3;
-    uint32_t* tmem_slot     = reinterpret_cast<uint32_t*>(epi_bar + 1);
+    uint32_t* tmem_slot     = reinterpret_cast<uint32_t*>(mfree_bar + 3);
     volatile uint32_t* abort_flag = tmem_slot + 1;
     // epilogue metadata, three buffers each: per output column the aligned 32-bit words that
     // hold the scales (at most 5) and zero points (at most 3) of a pass, GPP x MB activation
-    // group sums; a word for the tile-counter broadcast
+    // group sums
     uint32_t* epi_sw = reinterpret_cast<uint32_t*>(bar_base + 512);     // [3][128][5]
     uint32_t* epi_zw = epi_sw + 3 * 128 * 5;                            // [3][128][3]
     int* epi_sv      = reinterpret_cast<int*>(epi_zw + 3 * 128 * 3);    // [3][128]
-    int* epi_flag    = epi_sv + 3 * 128;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    // the next kernel of the stream may be started early if it asks for it (the pre-kernel of
+    // the next linear does: it waits for this grid's completion before it reads or writes)
+    grid_launch_dependents();
     if(threadIdx.x == 0)
     {
         for(int s = 0; s < WST; ++s)
@@ -318,7 +322,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             mbar_init(&meta_bar[b], 64);
             mbar_init(&mfree_bar[b], 4);
         }
-        mbar_init(epi_bar, 128);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmap_w);
@@ -581,7 +584,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // the conversion pipe except one half -> float per group: |P_hi|, |P_lo| < 2^18.
         grid_dependency_wait(); // sa and the tile counters come from the pre-kernel
         const int quarter = warp & 3;
-        const int te      = threadIdx.x - 192;   // 0..127
         const int col     = quarter * 32 + lane; // output column inside the tile = TMEM lane
         const int rshift  = 31 - __clz(p.group / TC_GROUP_K); // groups are powers of two
         const uint32_t sbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.scales) & 3u);
@@ -591,14 +593,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         for(int m = 0; m < MR; ++m)
             out[m] = 0.0f;
         tc_walk walk(f_lo, f_hi, SG, G);
-        uint32_t epi_phase = 0;
-        // all 128 epilogue threads meet here (bounded)
-        auto epi_sync = [&]() {
-            mbar_arrive(epi_bar);
-            const bool r = mbar_wait_bounded(epi_bar, epi_phase & 1u, abort_flag, 6);
-            ++epi_phase;
-            return __all_sync(0xffffffffu, r);
-        };
         // one group: out[m] += sc (Q[m] - z Sv[m]) with Q = sum_k q a_int, in exact integer
         // arithmetic up to the one conversion.  soff / zoff: byte offset of the group's scale /
         // zero point inside this column's staged words
@@ -716,26 +710,42 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     for(int m = 0; m < MR; ++m)
                         if(m < p.M and nc < p.N)
                             p.partial[(static_cast<int64_t>(slot) * p.M + m) * p.N + nc] = out[m];
-                    __threadfence();
-                    ok = epi_sync();
-                    if(ok and te == 0)
-                        *epi_flag = atomicAdd(p.counters + tile, 1);
-                    ok = ok and epi_sync();
-                    if(ok and *epi_flag == last - first)
+                    // The tile's 32 columns of this warp are complete when the warps of the same
+                    // lane quarter of all its CTAs have counted themselves in; the last one adds
+                    // the slots.  The counting atomic releases this warp's stores (ordered before
+                    // it by the warp barrier) and acquires the other warps'.
+                    __syncwarp();
+                    int old = 0;
+                    if(lane == 0)
+                        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
+                                     : "=r"(old)
+                                     : "l"(p.counters + tile * 4 + quarter)
+                                     : "memory");
+                    old = __shfl_sync(0xffffffffu, old, 0);
+                    if(old == last - first)
                     {
-                        // every other segment of the tile is in memory: add them in slot order
-                        __threadfence();
+                        // the MR loads of a slot are in flight together; slots add up in order
+                        float v[MR];
 #pragma unroll
                         for(int m = 0; m < MR; ++m)
+                            v[m] = 0.0f;
+#pragma unroll 4
+                        for(int s = 0; s <= last - first; ++s)
                         {
-                            if(m < p.M and nc < p.N)
-                            {
-                                float v = 0.0f;
-                                for(int s = 0; s <= last - first; ++s)
-                                    v += __ldcg(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + nc);
-                                p.D[m * p.ldd + nc] = __float2half_rn(v * __ldg(p.sa + m));
-                            }
+                            float t[MR];
+#pragma unroll
+                            for(int m = 0; m < MR; ++m)
+                                t[m] = m < p.M and nc < p.N
+                                           ? __ldcg(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + nc)
+                                           : 0.0f;
+#pragma unroll
+                            for(int m = 0; m < MR; ++m)
+                                v[m] += t[m];
                         }
+#pragma unroll
+                        for(int m = 0; m < MR; ++m)
+                            if(m < p.M and nc < p.N)
+                                p.D[m * p.ldd + nc] = __float2half_rn(v[m] * __ldg(p.sa + m));
                     }
                 }
 #pragma unroll
@@ -789,7 +799,7 @@ tc_plan make_plan(const mgx_w4_desc& d)
     pl.off_sa       = align_up(static_cast<size_t>(pl.nb) * d.K, 256);
     pl.off_sv       = pl.off_sa + 256;
     pl.off_counters = align_up(pl.off_sv + static_cast<size_t>(pl.groups) * pl.mb * sizeof(float), 256);
-    pl.off_partial  = align_up(pl.off_counters + static_cast<size_t>(pl.tiles) * sizeof(int), 256);
+    pl.off_partial  = align_up(pl.off_counters + static_cast<size_t>(pl.tiles) * 4 * sizeof(int), 256);
     pl.total        = pl.off_partial + static_cast<size_t>(pl.slots) * d.M * d.N * sizeof(float);
     return pl;
 }
@@ -899,18 +909,32 @@ int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const v
     if(rc != MGX_OK)
         return rc;
     const auto* a16 = static_cast<const __half*>(A);
-    if(pl.mb == 4)
-        w4_prepare_acts_kernel<4, true><<<4, 1024, 0, stream>>>(a16, d.lda, d.M, d.K, aq, sa, sv,
-                                                                counters, pl.tiles);
-    else if(pl.mb == 8)
-        w4_prepare_acts_kernel<8, true><<<8, 1024, 0, stream>>>(a16, d.lda, d.M, d.K, aq, sa, sv,
-                                                                counters, pl.tiles);
-    else
-        w4_prepare_acts_kernel<16, false><<<16, 1024, 0, stream>>>(a16, d.lda, d.M, d.K, aq, sa, sv,
-                                                                   counters, pl.tiles);
-    cudaError_t e = cudaGetLastError();
-    if(e != cudaSuccess)
-        return static_cast<int>(e);
+    {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim          = dim3(static_cast<unsigned>(pl.mb));
+        cfg.blockDim         = dim3(1024);
+        cfg.dynamicSmemBytes = 0;
+        cfg.stream           = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs    = attr;
+        cfg.numAttrs = 1;
+        const int64_t lda = d.lda, M = d.M, K = d.K;
+        const int ntiles  = pl.tiles * 4; // one counter per tile and lane quarter
+        cudaError_t e     = cudaSuccess;
+        if(pl.mb == 4)
+            e = cudaLaunchKernelEx(&cfg, w4_prepare_acts_kernel<4, true>, a16, lda, M, K, aq, sa, sv,
+                                   counters, ntiles);
+        else if(pl.mb == 8)
+            e = cudaLaunchKernelEx(&cfg, w4_prepare_acts_kernel<8, true>, a16, lda, M, K, aq, sa, sv,
+                                   counters, ntiles);
+        else
+            e = cudaLaunchKernelEx(&cfg, w4_prepare_acts_kernel<16, false>, a16, lda, M, K, aq, sa,
+                                   sv, counters, ntiles);
+        if(e != cudaSuccess)
+            return static_cast<int>(e);
+    }
     tc_params p{};
     p.scales         = static_cast<const __half*>(scales);
     p.zp             = static_cast<const uint8_t*>(zp);
