@@ -404,8 +404,27 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
                 }
             }
         };
+        // The residual is read inside the store loop; asking for its lines a chunk ahead turns
+        // those reads into L1 hits (the loop is not unrolled, so their latency would be exposed).
+        auto prefetch_res = [&](int ch) {
+            if constexpr(not std::is_same<OutT, int32_t>::value)
+            {
+                const int64_t c4 = col0 + ch * EPI_COLS + (lane & 3) * 4;
+                if(p.residual == nullptr or c4 >= p.N)
+                    return;
+#pragma unroll
+                for(int it = 0; it < 4; ++it)
+                {
+                    const int64_t row = e.row0 + it * 8 + (lane >> 2);
+                    if(row < p.M)
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(
+                            static_cast<const OutT*>(p.residual) + e.batch_off + row * p.ldd + c4));
+                }
+            }
+        };
         float4 sc_next, bi_next;
         load_sb(0, sc_next, bi_next);
+        prefetch_res(0);
 
         if(not mbar_wait_bounded(&accf_bar[buf], (lt >> 1) & 1u, abort_flag, 3))
             break;
@@ -417,7 +436,10 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
             const int64_t col = col0 + ch * EPI_COLS;
             const float4 sc_cur = sc_next, bi_cur = bi_next;
             if(ch + 1 < NCHUNK)
+            {
                 load_sb(ch + 1, sc_next, bi_next);
+                prefetch_res(ch + 1);
+            }
             uint32_t acc[EPI_COLS];
             __syncwarp(); // tcgen05.ld is warp-collective; also orders reuse of the box
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +

@@ -23,6 +23,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--act", default="gelu_erf")
     ap.add_argument("--out", default="f16", choices=["f16", "f32", "raw"])
+    ap.add_argument("--residual", action="store_true", help="add a residual of the output type")
+    ap.add_argument("--qout", action="store_true", help="also write the int8 quantizelinear of the output")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     M, N, K = a.m, a.n, a.k
@@ -41,7 +43,10 @@ def main():
             fn = lambda: capi.qgemm(A, B, b_layout=capi.B_NK, out=out)  # noqa: E731
         else:
             out = torch.empty((1, M, N), dtype=torch.float16 if a.out == "f16" else torch.float32, device=dev)
-            fn = lambda: capi.qgemm(A, B, b_layout=capi.B_NK, scale=scale, bias=bias, act=act, out=out)  # noqa: E731
+            res = torch.randn((1, M, N), device=dev).to(out.dtype) if a.residual else None
+            qo = torch.empty((1, M, N), dtype=torch.int8, device=dev) if a.qout else None
+            fn = lambda: capi.qgemm(A, B, b_layout=capi.B_NK, scale=scale, bias=bias, act=act, out=out,  # noqa: E731
+                                    residual=res, q_out=qo, q_scale=0.02 if a.qout else None)
         work, unit = 2.0 * M * N * K, "TOPS"
     elif a.case == "quantize":
         x = torch.randn((M, N), device=dev)

@@ -244,6 +244,25 @@ def secondary_measurements(dev, peaks):
             "weight_gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
             "what": "7 int4 weight-only linears of a Llama-2-7B-shaped layer (group 128, fp16 scales), "
                     "packed weights + scales bytes / time"}
+    del weights
+    # one large weight matrix (the gate/up projection of a Llama-2-70B-shaped layer): the HBM
+    # stream without the per-launch costs that dominate the small matrices above
+    n, k = 28672, 8192
+    big = [(torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev),
+            (torch.rand(n, k // group, device=dev) * 0.015 + 0.005).half()) for _ in range(3)]
+    bbytes = n * k // 2 + n * (k // group) * 2
+    for batch in (1, 16):
+        x = torch.randn(batch, k, device=dev, dtype=torch.float16)
+
+        def big_pass():
+            for (bp, sc) in big:
+                capi.w4a16(x, bp, sc, group=group, workspace=ws)
+        us = _graph_time_us(big_pass, 2, stream) / len(big)
+        gbs = bbytes / us / 1e3
+        out[f"int4_decode_28672x8192_batch{batch}"] = {
+            "us": us, "weight_gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
+            "what": "one int4 weight-only linear N=28672 K=8192 (group 128), 3 rotating weight "
+                    "copies of 117 MB"}
     return out
 
 
@@ -310,20 +329,27 @@ def run_own_arm(args):
         barrier()
         ms_total = e0.elapsed_time(e1)
 
-        # ---- roofline leg: every quant_dot launch bracketed by CUDA events on its stream
+        # ---- roofline leg: the 48 quant_dot launches of a step by themselves (one CUDA graph per
+        # set, no other kernel between them), CUDA events around K replays on the launching stream
+        gemm_graphs = []
         for st in stacks:
-            st.gemm_events = []
-        ksteps = min(args.steps, 12)
-        for i in range(ksteps):
-            stacks[i % nsets].step()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                st.step(gemm_only=True)
+            gemm_graphs.append(g)
+        for i in range(3):
+            gemm_graphs[i % nsets].replay()
         torch.cuda.synchronize()
-        g_ms, g_ops, g_n = 0.0, 0, 0
-        for st in stacks:
-            for (s, e, ops) in st.gemm_events:
-                g_ms += s.elapsed_time(e)
-                g_ops += ops
-                g_n += 1
-            st.gemm_events = None
+        ksteps = max(3, min(args.steps, 30))
+        r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        r0.record()
+        for i in range(ksteps):
+            gemm_graphs[i % nsets].replay()
+        r1.record()
+        torch.cuda.synchronize()
+        g_n = ksteps * stacks[0].gemms_per_step()
+        g_ms = r0.elapsed_time(r1)
+        g_ops = ksteps * ops_step
 
         # ---- end-to-end leg: host buffers in, host buffer out, copies inside the timed region
         t, hid = stacks[0].tokens, stacks[0].hidden
@@ -374,7 +400,8 @@ def run_own_arm(args):
                        "parallelism": f"{world} independent replicas, batch-sharded, no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak8, "unit": "TFLOP/s",
                          "frac": achieved / peak8, "traffic": None,
-                         "kernel": "qgemm_kernel (tcgen05 kind::i8), all 48 quant_dot launches of a step",
+                         "kernel": "qgemm_kernel (tcgen05 kind::i8): the 48 quant_dot launches of a step replayed "
+                                   "as a graph of their own, fused epilogues included",
                          "launches_timed": g_n, "avg_launch_us": g_ms / max(1, g_n) * 1e3,
                          "peak_basis": f"2 x {basis} bf16 burst ({peaks['bf16_tflops']} TFLOP/s): "
                                        "8-bit operands issue at twice the bf16 rate"},
