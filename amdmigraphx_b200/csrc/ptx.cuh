@@ -80,11 +80,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 {
     uint32_t ok;
+    // the time hint lets the hardware park the thread until the phase completes (or that many
+    // nanoseconds pass) instead of having it spin through the issue slots of working warps
     asm volatile("{\n\t.reg .pred p;\n\t"
-                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok)
-                 : "r"(smem_u32(bar)), "r"(parity)
+                 : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
                  : "memory");
     return ok != 0;
 }
@@ -120,6 +122,22 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
             }
         }
     }
+}
+
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the
+// previous kernel of its stream still runs; it must call grid_dependency_wait() before it reads
+// anything that kernel writes, and before it writes anything that kernel may still read.  The
+// wait returns at once when the kernel was launched without the attribute.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Allows the next kernel of the stream (if it was launched with the attribute) to start now.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 // ---------------------------------------------------------------- TMA

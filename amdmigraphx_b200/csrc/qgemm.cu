@@ -50,6 +50,7 @@ struct qgemm_params
     int q_fp8;         // 0: int8, 1: fp8 e4m3fn
     int write_d;       // D itself is wanted
     int vec_sb; // scale / bias vectors are 16-byte aligned (float4 loads allowed)
+    int fast;   // the whole problem takes the epilogue's check-free path (see epi_store_chunk_fast)
     int vec_io; // D (and residual) rows can be accessed with 16-byte (fp32/int32) / 8-byte (fp16) vectors
 };
 
@@ -330,6 +331,124 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
     }
 }
 
+// Four values at once: float(half_rz(v)) by masking, with the exact conversion only when one of
+// them is zero, subnormal as a half, or beyond its range (rare).
+__device__ __forceinline__ void truncate4_to_half_precision(float (&v)[4])
+{
+    const uint32_t a0 = __float_as_uint(v[0]) & 0x7FFFFFFFu, a1 = __float_as_uint(v[1]) & 0x7FFFFFFFu;
+    const uint32_t a2 = __float_as_uint(v[2]) & 0x7FFFFFFFu, a3 = __float_as_uint(v[3]) & 0x7FFFFFFFu;
+    const uint32_t lo = min(min(a0, a1), min(a2, a3));
+    const uint32_t hi = max(max(a0, a1), max(a2, a3));
+    if(lo >= 0x38800000u and hi < 0x47800000u) // 2^-14 <= |v| < 2^16 for all four
+    {
+#pragma unroll
+        for(int j = 0; j < 4; ++j)
+            v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
+    }
+    else
+    {
+#pragma unroll
+        for(int j = 0; j < 4; ++j)
+            v[j] = truncate_to_half_precision(v[j]);
+    }
+}
+
+// The chunk's store phase when nothing needs checking: every row and column of every tile is in
+// range, all accesses are vectors, the scale is per column or per tensor (already in sc4; 1.0 when
+// there is none), bi4 is -0.0 without a bias (x + -0.0 == x for every x), an optional
+// quantizelinear output is int8 with 4-byte aligned rows.  Same arithmetic as epi_store_chunk.
+template <bool IS_INT, class OutT, int ACT>
+__device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t col, float4 sc4, float4 bi4)
+{
+    const qgemm_params& p = *e.p;
+    const int pc          = e.lane & 3;
+    const int rsub        = e.lane >> 2;
+    const float sc[4]     = {sc4.x, sc4.y, sc4.z, sc4.w};
+    const float bi[4]     = {bi4.x, bi4.y, bi4.z, bi4.w};
+    const int64_t off     = e.batch_off + (e.row0 + rsub) * p.ldd + col + pc * 4;
+    OutT* dst             = static_cast<OutT*>(p.D) + off;
+    const OutT* res       = static_cast<const OutT*>(p.residual) + off;
+    uint8_t* qdst = static_cast<uint8_t*>(p.Dq) + e.batch_off_q + (e.row0 + rsub) * p.ldq + col + pc * 4;
+    const int64_t dstep = 8 * p.ldd, qstep = 8 * p.ldq;
+    const bool has_res = p.residual != nullptr, has_q = p.Dq != nullptr, wr = p.write_d != 0;
+    // saturation before rounding: bounds are integers, so round-to-nearest stays inside
+    const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
+    const int q_bias = static_cast<int>(p.q_zp) - 0x4B400000;
+    const uint8_t* box = e.box + rsub * 64;
+#pragma unroll 1
+    for(int it = 0; it < 4; ++it)
+    {
+        const int r   = it * 8 + rsub;
+        const uint4 w = *reinterpret_cast<const uint4*>(box + it * 512 + ((pc ^ ((r >> 1) & 3)) * 16));
+        const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
+        float v[4];
+#pragma unroll
+        for(int j = 0; j < 4; ++j)
+        {
+            float x;
+            if constexpr(IS_INT)
+                x = dequant_i32(static_cast<int32_t>(wv[j]), sc[j]);
+            else
+                x = __fmul_rn(__uint_as_float(wv[j]), sc[j]);
+            v[j] = apply_act<ACT>(__fadd_rn(x, bi[j]));
+        }
+        if(has_res)
+        {
+            float q[4];
+            if constexpr(std::is_same<OutT, float>::value)
+            {
+                const float4 t = *reinterpret_cast<const float4*>(res);
+                q[0] = t.x, q[1] = t.y, q[2] = t.z, q[3] = t.w;
+            }
+            else
+            {
+                const uint2 t    = *reinterpret_cast<const uint2*>(res);
+                const __half* th = reinterpret_cast<const __half*>(&t);
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                    q[j] = __half2float(th[j]);
+                truncate4_to_half_precision(v); // the half add works on the truncated half
+            }
+#pragma unroll
+            for(int j = 0; j < 4; ++j)
+                v[j] = __fadd_rn(v[j], q[j]);
+        }
+        if constexpr(std::is_same<OutT, __half>::value)
+        {
+            if(has_q)
+                truncate4_to_half_precision(v); // quantizelinear sees the stored half
+        }
+        if(wr)
+        {
+            if constexpr(std::is_same<OutT, float>::value)
+                *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            else
+                *reinterpret_cast<uint2*>(dst) =
+                    make_uint2(cvt_rz_f16x2(v[0], v[1]), cvt_rz_f16x2(v[2], v[3]));
+        }
+        if(has_q)
+        {
+            uint32_t b[4];
+#pragma unroll
+            for(int j = 0; j < 4; ++j)
+            {
+                float qv        = __fmul_rn(v[j], p.q_rcp);
+                const float rem = __fmaf_rn(-p.q_scale, qv, v[j]);
+                qv              = __fmaf_rn(rem, p.q_rcp, qv);
+                if constexpr(std::is_same<OutT, __half>::value)
+                    qv = __uint_as_float(__float_as_uint(qv) & 0xFFFFE000u); // half quotient, truncated
+                qv   = fmaxf(q_lo, fminf(q_hi, qv));
+                b[j] = static_cast<uint32_t>(__float_as_int(__fadd_rn(qv, 12582912.0f)) + q_bias);
+            }
+            *reinterpret_cast<uint32_t*>(qdst) =
+                __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+        }
+        dst += dstep;
+        res += dstep;
+        qdst += qstep;
+    }
+}
+
 // The epilogue role, one instantiation per activation so that the code a warp executes is
 // one contiguous region (the activation is chosen once per kernel, not per element).
 // Each warp owns TMEM lane quarter (warp % 4) = 32 rows of the tile, and a quarter of the
@@ -376,7 +495,7 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
         // code would be bound by instruction fetch.
         auto load_sb = [&](int ch, float4& sc, float4& bi) {
             sc = make_float4(tensor_scale, tensor_scale, tensor_scale, tensor_scale);
-            bi = make_float4(0.f, 0.f, 0.f, 0.f);
+            bi = p.fast ? make_float4(-0.f, -0.f, -0.f, -0.f) : make_float4(0.f, 0.f, 0.f, 0.f);
             if constexpr(not std::is_same<OutT, int32_t>::value)
             {
                 const int64_t c4 = col0 + ch * EPI_COLS + (lane & 3) * 4;
@@ -453,7 +572,12 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
                     *reinterpret_cast<uint4*>(my_row + ((q ^ my_swz) * 16)) =
                         make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
                 __syncwarp();
-                epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
+                if constexpr(std::is_same<OutT, int32_t>::value)
+                    epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
+                else if(p.fast)
+                    epi_store_chunk_fast<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
+                else
+                    epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
             }
         }
         // all TMEM reads of this buffer are complete (wait::ld above)
@@ -489,6 +613,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     constexpr uint32_t TMEM_COLS = 2 * BN; // 128, 256 or 512: a power of two >= 32
+
+    // the next kernel of the stream may set itself up while this one runs
+    grid_launch_dependents();
 
     if(threadIdx.x == 0)
     {
@@ -526,6 +653,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         // ---------------------------------------------------- TMA producer
         if(lane == 0)
         {
+            // everything up to here overlapped the previous kernel of the stream; its results
+            // (this kernel's operands) are complete after the wait
+            grid_dependency_wait();
             uint32_t it = 0;
             bool ok     = true;
             for(int64_t t = first_tile; ok and t < p.num_tiles; t += tile_step)
@@ -602,6 +732,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     else
     {
         // ---------------------------------------------------- epilogue
+        // (reads residual / scale / bias and writes D: only after the previous kernel is done)
+        grid_dependency_wait();
 #define MGX_EPILOGUE(ACT)                                                                      \
     epilogue_role<BN, IS_INT, OutT, ACT>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base, \
                                          warp, lane, first_tile, tile_step, tiles_mn)
@@ -710,14 +842,40 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
     p.q_zp       = qo.zp;
     p.q_fp8      = qo.fp8;
     p.write_d    = qo.write_d;
+    // the epilogue's check-free path: whole tiles in M, whole 16-column chunks in N, vector
+    // access everywhere, no per-row scale, quantizelinear output (if any) int8 in aligned words.
+    // The residual shares D's leading dimension and must allow the same vector width.
+    {
+        const size_t es     = std::is_same<OutT, __half>::value ? 2 : 4;
+        const size_t valign = es * 4;
+        const bool res_ok   = residual == nullptr or (reinterpret_cast<uintptr_t>(residual) % valign) == 0;
+        const bool q_ok     = qo.Dq == nullptr or
+                          (qo.fp8 == 0 and (reinterpret_cast<uintptr_t>(qo.Dq) & 3u) == 0 and
+                           qo.ldq % 4 == 0 and qo.stride_q % 4 == 0);
+        p.fast = (not std::is_same<OutT, int32_t>::value and p.vec_io and p.vec_sb and res_ok and q_ok and
+                  d.scale_mode != MGX_SCALE_PER_ROW and d.M % BM == 0 and d.N % EPI_COLS == 0)
+                     ? 1
+                     : 0;
+    }
     auto kernel  = qgemm_kernel<BN, IS_INT, OutT>;
     int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(kernel), S::total);
     if(rc2 != MGX_OK)
         return rc2;
     const int sms = device_sm_count();
     const int grid = static_cast<int>(p.num_tiles < sms ? p.num_tiles : sms);
-    kernel<<<grid, NTHREADS, S::total, stream>>>(ta, tb, p);
-    return static_cast<int>(cudaGetLastError());
+    // programmatic dependent launch: set-up (tensor-memory allocation, barriers, descriptor
+    // prefetch) overlaps the tail of the previous kernel of the stream
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim         = dim3(NTHREADS);
+    cfg.dynamicSmemBytes = S::total;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs                                          = attr;
+    cfg.numAttrs                                       = 1;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
 }
 
 template <int BN, bool IS_INT>

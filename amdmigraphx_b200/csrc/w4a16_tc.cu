@@ -70,16 +70,6 @@ struct tc_params
     int items_total, items_per_cta; // (tile, 4-group block) work items, see the main kernel
 };
 
-__device__ __forceinline__ void grid_dependency_wait()
-{
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-
-__device__ __forceinline__ void grid_launch_dependents()
-{
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-
 // ------------------------------------------------------------------ activation pre-kernel
 // grid = MB blocks (one per padded activation row), 1024 threads; a thread owns 8 consecutive k.
 // Every activation becomes q = round(a / sa) = 128 h + l.  Two layouts of the int8 rows the

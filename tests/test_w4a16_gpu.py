@@ -50,6 +50,37 @@ def test_w4a16_prefill(cuda_device, M, N, K):
     np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
 
 
+def test_w4a16_decode_is_reproducible(cuda_device):
+    """Tiles shared between thread blocks add their partial sums in a fixed order: two runs of
+    the same problem give identical bits, for every row count the decode kernel specialises on."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(5)
+    for M in (1, 2, 4, 8, 16):
+        a, bp, s, zp = _case(rng, M, 1536, 4096, 128, True)
+        args = (_t(a, cuda_device), _t(bp, cuda_device), _t(s, cuda_device), _t(zp, cuda_device))
+        first = capi.w4a16(*args, group=128, which="gemv").clone()
+        for _ in range(3):
+            again = capi.w4a16(*args, group=128, which="gemv")
+            assert torch.equal(first, again)
+
+
+def test_w4a16_decode_unaligned_metadata_falls_back(cuda_device):
+    """Scales that are not 4-byte aligned cannot take the tensor-core kernel (it copies aligned
+    words); the call still succeeds on the fallback kernels with the same tolerance."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(6)
+    a, bp, s, zp = _case(rng, 2, 256, 1024, 128, False)
+    ref = O.w4a16_linear(a, bp, s, None, 8, 128).astype(np.float32)
+    buf = torch.zeros(s.size + 1, dtype=torch.float16, device=cuda_device)
+    s_dev = buf[1:].view(s.shape)  # 2 bytes past a 4-byte boundary
+    s_dev.copy_(_t(s, cuda_device))
+    assert s_dev.data_ptr() % 4 == 2
+    got = capi.w4a16(_t(a, cuda_device), _t(bp, cuda_device), s_dev, None, group=128, which="gemv")
+    np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
+
+
 def test_w4a16_rejects_bad_arguments(cuda_device):
     import torch
     from amdmigraphx_b200 import capi
