@@ -254,8 +254,10 @@ struct tc_walk
 // activation row has 4 rows in the B operand (see the pre-kernel); otherwise it is the 128
 // nibbles unpacked to bytes and 2 rows.  RAW costs one logic operation per eight weights
 // instead of three, and twice the accumulator columns per activation row.
-template <int NB, int MR, bool RAW>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// ESETS: sets of four epilogue warps; with two, each set folds half of the MR rows (the second
+// set is warps 15..18).
+template <int NB, int MR, bool RAW, int ESETS>
+__global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
     w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     const __grid_constant__ CUtensorMap tmap_a,
                     const tc_params p)
@@ -305,12 +307,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             mbar_init(&unp_bar[b], 128);
             mbar_init(&tfree_bar[b], TC_ISSUERS);
             mbar_init(&accf_bar[b], TC_ISSUERS);
-            mbar_init(&acce_bar[b], 4);
+            mbar_init(&acce_bar[b], 4 * ESETS);
         }
         for(int b = 0; b < 3; ++b)
         {
             mbar_init(&meta_bar[b], 64);
-            mbar_init(&mfree_bar[b], 4);
+            mbar_init(&mfree_bar[b], 4 * ESETS);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -433,7 +435,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             }
         }
     }
-    else if(warp >= 13)
+    else if(warp == 13 or warp == 14)
     {
         // ---------------------------------------------------- epilogue metadata, up to 3 passes ahead
         // cp.async copies of the aligned words around the scales and zero points of a pass
@@ -573,20 +575,23 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         // of activation row m; only the MR rows in use are read.  All arithmetic stays off
         // the conversion pipe except one half -> float per group: |P_hi|, |P_lo| < 2^18.
         grid_dependency_wait(); // sa and the tile counters come from the pre-kernel
+        constexpr int MRW = MR / ESETS;          // rows this warp folds ...
+        const int eset    = warp >= 15 ? 1 : 0;
+        const int m0      = eset * MRW;          // ... starting at this one
         const int quarter = warp & 3;
         const int col     = quarter * 32 + lane; // output column inside the tile = TMEM lane
         const int rshift  = 31 - __clz(p.group / TC_GROUP_K); // groups are powers of two
         const uint32_t sbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.scales) & 3u);
         const uint32_t zbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.zp) & 3u);
-        float out[MR];
+        float out[MRW];
 #pragma unroll
-        for(int m = 0; m < MR; ++m)
+        for(int m = 0; m < MRW; ++m)
             out[m] = 0.0f;
         tc_walk walk(f_lo, f_hi, SG, G);
         // one group: out[m] += sc (Q[m] - z Sv[m]) with Q = sum_k q a_int, in exact integer
         // arithmetic up to the one conversion.  soff / zoff: byte offset of the group's scale /
         // zero point inside this column's staged words
-        constexpr int C  = CPM * MR; // accumulator columns read per group
+        constexpr int C  = CPM * MRW; // accumulator columns read per group
         const bool has_zp = p.zp != nullptr;
         auto fold = [&](const uint32_t(&acc)[C], int gl, uint32_t vb, uint32_t soff, uint32_t zoff) {
             const uint32_t sw = epi_sw[(vb * 128 + col) * 5 + (soff >> 2)];
@@ -600,9 +605,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 sc *= 0.0625f; // Q is computed times 16
                 z *= 16;
             }
-            const int* svb = epi_sv + vb * 128 + gl * MB;
+            const int* svb = epi_sv + vb * 128 + gl * MB + m0;
 #pragma unroll
-            for(int m = 0; m < MR; ++m)
+            for(int m = 0; m < MRW; ++m)
             {
                 int q;
                 if constexpr(RAW)
@@ -643,7 +648,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
             // quantisation group of group gl, relative to gi0
             auto grel = [&](int gl) { return static_cast<uint32_t>(((g0 + gl) >> rshift) - gi0); };
             const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                                   buf * TC_ACC_COLS;
+                                   buf * TC_ACC_COLS + CPM * m0;
 #pragma unroll 1
             for(int gl = 0; gl < count; gl += TR)
             {
@@ -687,9 +692,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                 if(whole)
                 {
 #pragma unroll
-                    for(int m = 0; m < MR; ++m)
-                        if(m < p.M and nc < p.N)
-                            p.D[m * p.ldd + nc] = __float2half_rn(out[m] * __ldg(p.sa + m));
+                    for(int m = 0; m < MRW; ++m)
+                        if(m0 + m < p.M and nc < p.N)
+                            p.D[(m0 + m) * p.ldd + nc] = __float2half_rn(out[m] * __ldg(p.sa + m0 + m));
                 }
                 else
                 {
@@ -697,9 +702,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     const int last  = ((tile + 1) * SG - 1) / p.items_per_cta;
                     const int slot  = static_cast<int>(blockIdx.x) - first;
 #pragma unroll
-                    for(int m = 0; m < MR; ++m)
-                        if(m < p.M and nc < p.N)
-                            p.partial[(static_cast<int64_t>(slot) * p.M + m) * p.N + nc] = out[m];
+                    for(int m = 0; m < MRW; ++m)
+                        if(m0 + m < p.M and nc < p.N)
+                            p.partial[(static_cast<int64_t>(slot) * p.M + m0 + m) * p.N + nc] = out[m];
                     // The tile's 32 columns of this warp are complete when the warps of the same
                     // lane quarter of all its CTAs have counted themselves in; the last one adds
                     // the slots.  The counting atomic releases this warp's stores (ordered before
@@ -709,37 +714,37 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
                     if(lane == 0)
                         asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;"
                                      : "=r"(old)
-                                     : "l"(p.counters + tile * 4 + quarter)
+                                     : "l"(p.counters + (tile * 4 + quarter) * ESETS + eset)
                                      : "memory");
                     old = __shfl_sync(0xffffffffu, old, 0);
                     if(old == last - first)
                     {
                         // the MR loads of a slot are in flight together; slots add up in order
-                        float v[MR];
+                        float v[MRW];
 #pragma unroll
-                        for(int m = 0; m < MR; ++m)
+                        for(int m = 0; m < MRW; ++m)
                             v[m] = 0.0f;
 #pragma unroll 4
                         for(int s = 0; s <= last - first; ++s)
                         {
-                            float t[MR];
+                            float t[MRW];
 #pragma unroll
-                            for(int m = 0; m < MR; ++m)
-                                t[m] = m < p.M and nc < p.N
-                                           ? __ldcg(p.partial + (static_cast<int64_t>(s) * p.M + m) * p.N + nc)
+                            for(int m = 0; m < MRW; ++m)
+                                t[m] = m0 + m < p.M and nc < p.N
+                                           ? __ldcg(p.partial + (static_cast<int64_t>(s) * p.M + m0 + m) * p.N + nc)
                                            : 0.0f;
 #pragma unroll
-                            for(int m = 0; m < MR; ++m)
+                            for(int m = 0; m < MRW; ++m)
                                 v[m] += t[m];
                         }
 #pragma unroll
-                        for(int m = 0; m < MR; ++m)
-                            if(m < p.M and nc < p.N)
-                                p.D[m * p.ldd + nc] = __float2half_rn(v[m] * __ldg(p.sa + m));
+                        for(int m = 0; m < MRW; ++m)
+                            if(m0 + m < p.M and nc < p.N)
+                                p.D[(m0 + m) * p.ldd + nc] = __float2half_rn(v[m] * __ldg(p.sa + m0 + m));
                     }
                 }
 #pragma unroll
-                for(int m = 0; m < MR; ++m)
+                for(int m = 0; m < MRW; ++m)
                     out[m] = 0.0f;
             }
         }
@@ -789,7 +794,7 @@ tc_plan make_plan(const mgx_w4_desc& d)
     pl.off_sa       = align_up(static_cast<size_t>(pl.nb) * d.K, 256);
     pl.off_sv       = pl.off_sa + 256;
     pl.off_counters = align_up(pl.off_sv + static_cast<size_t>(pl.groups) * pl.mb * sizeof(float), 256);
-    pl.off_partial  = align_up(pl.off_counters + static_cast<size_t>(pl.tiles) * 4 * sizeof(int), 256);
+    pl.off_partial  = align_up(pl.off_counters + static_cast<size_t>(pl.tiles) * 8 * sizeof(int), 256);
     pl.total        = pl.off_partial + static_cast<size_t>(pl.slots) * d.M * d.N * sizeof(float);
     return pl;
 }
@@ -812,18 +817,18 @@ int encode_grouped(CUtensorMap* map, const void* base, uint32_t inner, uint64_t 
     return r == CUDA_SUCCESS ? MGX_OK : MGX_E_INVALID_ARG;
 }
 
-template <int NB, int MR, bool RAW>
+template <int NB, int MR, bool RAW, int ESETS>
 int launch_main(int grid, const CUtensorMap& tw, const CUtensorMap& ta, const tc_params& p,
                 cudaStream_t stream)
 {
-    int rc = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_tc_kernel<NB, MR, RAW>), tc_cfg<NB>::smem);
+    int rc = ensure_smem_optin(reinterpret_cast<const void*>(w4a16_tc_kernel<NB, MR, RAW, ESETS>), tc_cfg<NB>::smem);
     if(rc != MGX_OK)
         return rc;
     // programmatic dependent launch: the kernel may start while the pre-kernel still runs
     // and waits for it (griddepcontrol.wait) only where it reads what the pre-kernel wrote
     cudaLaunchConfig_t cfg{};
     cfg.gridDim          = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim         = dim3(TC_THREADS);
+    cfg.blockDim         = dim3(TC_THREADS + (ESETS - 1) * 128);
     cfg.dynamicSmemBytes = tc_cfg<NB>::smem;
     cfg.stream           = stream;
     cudaLaunchAttribute attr[1];
@@ -831,7 +836,7 @@ int launch_main(int grid, const CUtensorMap& tw, const CUtensorMap& ta, const tc
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs                                          = attr;
     cfg.numAttrs                                       = 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<NB, MR, RAW>, tw, ta, p));
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, w4a16_tc_kernel<NB, MR, RAW, ESETS>, tw, ta, p));
 }
 
 } // namespace
@@ -911,7 +916,7 @@ int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const v
         cfg.attrs    = attr;
         cfg.numAttrs = 1;
         const int64_t lda = d.lda, M = d.M, K = d.K;
-        const int ntiles  = pl.tiles * 4; // one counter per tile and lane quarter
+        const int ntiles  = pl.tiles * 8; // one counter per tile, lane quarter and epilogue warp set
         cudaError_t e     = cudaSuccess;
         if(pl.mb == 4)
             e = cudaLaunchKernelEx(&cfg, w4_prepare_acts_kernel<4, true>, a16, lda, M, K, aq, sa, sv,
@@ -944,14 +949,14 @@ int w4a16_tc_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const v
     p.items_total    = pl.items_total;
     p.items_per_cta  = pl.items_per_cta;
     if(d.M == 1)
-        return launch_main<16, 1, true>(pl.grid, tw, ta, p, stream);
+        return launch_main<16, 1, true, 1>(pl.grid, tw, ta, p, stream);
     if(d.M == 2)
-        return launch_main<16, 2, true>(pl.grid, tw, ta, p, stream);
+        return launch_main<16, 2, true, 1>(pl.grid, tw, ta, p, stream);
     if(d.M <= 4)
-        return launch_main<16, 4, true>(pl.grid, tw, ta, p, stream);
+        return launch_main<16, 4, true, 1>(pl.grid, tw, ta, p, stream);
     if(d.M <= 8)
-        return launch_main<32, 8, true>(pl.grid, tw, ta, p, stream);
-    return launch_main<32, 16, false>(pl.grid, tw, ta, p, stream);
+        return launch_main<32, 8, true, 2>(pl.grid, tw, ta, p, stream);
+    return launch_main<32, 16, false, 2>(pl.grid, tw, ta, p, stream);
 }
 
 int w4a16_tc_status(unsigned int* out) { return read_and_clear_status(out); }

@@ -221,6 +221,23 @@ def secondary_measurements(dev, peaks):
                      "frac_of_4500_datasheet": tops / 4500.0,
                      "what": "M=N=K=8192, dequantizelinear + bias + GELU fused, fp32 out"}
         del a, b, d
+    # config 3: the fp8 e4m3fn QDQ GEMM sweep (per-tensor scale, bias + GELU fused, fp32 out)
+    sweep = {}
+    for (n, k) in ((4096, 4096), (8192, 8192), (14336, 4096)):
+        b = (torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev).float() / 64).to(torch.float8_e4m3fn)
+        scale = torch.full((1,), 3e-4, device=dev)
+        bias = torch.randn(n, device=dev)
+        for m in (1, 16, 128, 1024, 4096, 8192):
+            a = (torch.randint(-127, 128, (m, k), dtype=torch.int8, device=dev).float() / 64).to(torch.float8_e4m3fn)
+            d = torch.empty((1, m, n), dtype=torch.float32, device=dev)
+            us = _graph_time_us(lambda: capi.qgemm(a, b, b_layout=capi.B_NK, scale=scale,
+                                                   scale_mode=capi.SCALE_PER_TENSOR, bias=bias,
+                                                   act="gelu_erf", out=d), 4, stream)
+            sweep[f"M{m}_N{n}_K{k}"] = {"us": round(us, 2), "tops": round(2.0 * m * n * k / us / 1e6, 1)}
+            del a, d
+        del b
+    out["fp8_qdq_gemm_sweep"] = {"points": sweep, "what": "e4m3fn x e4m3fn -> fp32, per-tensor scale, bias + "
+                                 "erf-GELU fused; 4 launches per CUDA graph, operands L2-resident for the small points"}
     hid, ffn, group = 4096, 11008, 128
     shapes = [(hid, hid)] * 4 + [(ffn, hid), (ffn, hid), (hid, ffn)]  # q k v o gate up down: (N, K)
     layers = 3  # 3 x 101 MB of packed weights: larger than L2
@@ -244,6 +261,17 @@ def secondary_measurements(dev, peaks):
             "weight_gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
             "what": "7 int4 weight-only linears of a Llama-2-7B-shaped layer (group 128, fp16 scales), "
                     "packed weights + scales bytes / time"}
+    # prefill: the same seven linears at 512 tokens
+    xs = {k: torch.randn(512, k, device=dev, dtype=torch.float16) for k in (hid, ffn)}
+
+    def prefill_pass():
+        for (bp, sc) in weights[0]:
+            capi.w4a16(xs[bp.shape[1] * 2], bp, sc, group=group, workspace=ws)
+    us = _graph_time_us(prefill_pass, 1, stream)
+    flops = sum(2.0 * 512 * n * k for (n, k) in shapes)
+    out["int4_prefill_512"] = {"us_per_layer_linears": us, "tflops": flops / us / 1e6,
+                               "what": "7 int4 weight-only linears of a Llama-2-7B-shaped layer at 512 tokens "
+                                       "(16-row slabs on mma.sync, not tuned)"}
     del weights
     # one large weight matrix (the gate/up projection of a Llama-2-70B-shaped layer): the HBM
     # stream without the per-launch costs that dominate the small matrices above
