@@ -34,6 +34,12 @@ int transpose_8bit_ld(const void* src, void* dst, int64_t rows, int64_t cols, in
 int qgemm_status(unsigned int* out);
 int w4a16_status(unsigned int* out);
 int w4a16_tc_status(unsigned int* out);
+int w4a16_prefill_status(unsigned int* out);
+
+// tcgen05 int4 prefill path (w4a16_prefill.cu)
+bool w4a16_prefill_applicable(const mgx_w4_desc& d, const void* A, const void* Bp);
+int w4a16_prefill_launch(const mgx_w4_desc& d, const void* A, const void* Bp, const void* scales,
+                         const void* zp, void* D, cudaStream_t stream);
 
 // tcgen05 int4 decode path (w4a16_tc.cu)
 bool w4a16_tc_applicable(const mgx_w4_desc& d);

@@ -277,6 +277,16 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
                  : "memory");
 }
 
+// Same with the A operand in tensor memory (row i in lane i, two K elements per 32-bit column).
+__device__ __forceinline__ void mma_f16_tmem_a(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                               uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives
 // lane (base_lane + t), columns col .. col+31.  A warp may only touch the lane
 // quarter (warp_id % 4) * 32 .. +31.

@@ -769,6 +769,10 @@ extern "C" int mgx_cuda_w4a16_gemm(const mgx_w4_desc* d, const void* A, const vo
     int rc = validate_w4(d, A, Bp, scales, D);
     if(rc != MGX_OK)
         return rc;
+    // more than 16 rows: dequantise-in-flight tcgen05 GEMM (MGX_CUDA_W4_TC=0 keeps the
+    // mma.sync slabs, for comparisons)
+    if(tc_enabled() and w4a16_prefill_applicable(*d, A, Bp))
+        return w4a16_prefill_launch(*d, A, Bp, scales, zp, D, static_cast<cudaStream_t>(stream_));
     if(not use_mma_path(*d))
         return MGX_E_UNSUPPORTED;
     return mgx_cuda_w4a16_gemv(d, A, Bp, scales, zp, D, workspace, workspace_bytes, stream_);

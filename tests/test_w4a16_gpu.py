@@ -38,15 +38,18 @@ def test_w4a16_decode(cuda_device, M, N, K, group, with_zp):
     np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
 
 
-@pytest.mark.parametrize("M,N,K", [(17, 256, 1024), (512, 512, 1024), (100, 136, 2304)])
-def test_w4a16_prefill(cuda_device, M, N, K):
+@pytest.mark.parametrize("M,N,K,group,with_zp", [
+    (17, 256, 1024, 128, True), (512, 512, 1024, 128, True), (100, 136, 2304, 128, True),
+    (300, 1000, 2048, 256, False), (129, 20000, 512, 128, True), (256, 384, 4096, 512, False),
+])
+def test_w4a16_prefill(cuda_device, M, N, K, group, with_zp):
     """More than 16 rows (prefill phase of the int4 decoder): same tolerance."""
     from amdmigraphx_b200 import capi
     rng = np.random.default_rng(M + N + K)
-    a, bp, s, zp = _case(rng, M, N, K, 128, True)
-    ref = O.w4a16_linear(a, bp, s, zp, 8, 128).astype(np.float32)
-    got = capi.w4a16(_t(a, cuda_device), _t(bp, cuda_device), _t(s, cuda_device), _t(zp, cuda_device),
-                     group=128, which="gemm")
+    a, bp, s, zp = _case(rng, M, N, K, group, with_zp)
+    ref = O.w4a16_linear(a, bp, s, zp, 8, group).astype(np.float32)
+    got = capi.w4a16(_t(a, cuda_device), _t(bp, cuda_device), _t(s, cuda_device),
+                     None if zp is None else _t(zp, cuda_device), group=group, which="gemm")
     np.testing.assert_allclose(got.cpu().numpy().astype(np.float32), ref, rtol=2e-2, atol=1e-2)
 
 
