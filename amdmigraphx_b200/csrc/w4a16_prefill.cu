@@ -10,10 +10,10 @@
 // (the reference materialises them: src/onnx/parse_matmulnbits.cpp:85-158 IR on the ref target).
 //
 // CTA tile = 128 output columns x 128 activation rows, all of K; persistent over tiles.
-// CTA = 352 threads:
+// CTA = 480 threads:
 //   warp 0       TMA producer: per 128-k group 8 KB of packed weights and 2 x 16 KB of activations
-//   warps 2..5   dequantise (nibbles -> fp16 pairs with byte permutes, one subtract and one
-//                multiply per pair) -> tcgen05.st
+//   warps 2..5, 11..14  dequantise (nibbles -> fp16 pairs with byte permutes, one subtract and
+//                one multiply per pair) -> tcgen05.st
 //   warps 1, 10  MMA issuers: each owns one fp32 accumulator (128 columns of tensor memory) and
 //                half of every group's k-steps, so the order of additions into an accumulator is
 //                fixed; the epilogue adds the two
@@ -36,7 +36,7 @@ constexpr int PF_TSTAGES = 4;                             // A operand buffers i
 constexpr int PF_A_COL0  = 256;
 constexpr int PF_A_COLS  = PF_GROUP_K / 2;                // 64 columns per group
 constexpr int PF_SMEM    = PF_STAGES * PF_STAGE + 512 + 1024;
-constexpr int PF_THREADS = 352;
+constexpr int PF_THREADS = 480;
 
 struct pf_params
 {
@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
     uint8_t* smem           = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     uint8_t* bar_base       = smem + PF_STAGES * PF_STAGE;
     uint64_t* full_bar      = reinterpret_cast<uint64_t*>(bar_base);
-    uint64_t* empty_bar     = full_bar + PF_STAGES;  // weights read (128) + MMAs retired (2)
+    uint64_t* empty_bar     = full_bar + PF_STAGES;  // weights read (256) + MMAs retired (2)
     uint64_t* unp_bar       = empty_bar + PF_STAGES; // A operand in tensor memory
     uint64_t* tfree_bar     = unp_bar + PF_TSTAGES;  // MMAs that read it retired (2)
     uint64_t* accf_bar      = tfree_bar + PF_TSTAGES;
@@ -75,11 +75,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
         for(int s = 0; s < PF_STAGES; ++s)
         {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], 128 + 2);
+            mbar_init(&empty_bar[s], 256 + 2);
         }
         for(int s = 0; s < PF_TSTAGES; ++s)
         {
-            mbar_init(&unp_bar[s], 128);
+            mbar_init(&unp_bar[s], 256);
             mbar_init(&tfree_bar[s], 2);
         }
         mbar_init(accf_bar, 2);
@@ -178,12 +178,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
             }
         }
     }
-    else if(warp < 6)
+    else if(warp < 6 or warp >= 11)
     {
         // ---------------------------------------------------- dequantise: nibbles -> fp16
-        // One thread per weight row: 64 packed bytes per group (64-byte swizzle: a quarter warp's
-        // 16-byte reads fall in eight different bank groups) -> 64 words of two fp16 each, in k
-        // order, to this row's lane of tensor memory.
+        // Two threads per weight row (warps 2..5 take the first 64 k of a group, warps 11..14 the
+        // second): 32 packed bytes (64-byte swizzle: a quarter warp's 16-byte reads fall in eight
+        // different bank groups) -> 32 words of two fp16 each, in k order, to this row's lane of
+        // tensor memory.
         const int row            = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const int sw             = (row >> 1) & 3;
@@ -226,8 +227,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
                 const __half2 zz2 = *reinterpret_cast<const __half2*>(&zz);
                 const __half2 ss2 = *reinterpret_cast<const __half2*>(&ss);
                 const uint8_t* pk = smem + s * PF_STAGE + row * 64;
-#pragma unroll
-                for(int half = 0; half < 2; ++half)
+                const int half = warp >= 11 ? 1 : 0;
                 {
                     uint32_t u[32];
 #pragma unroll

@@ -271,7 +271,7 @@ def secondary_measurements(dev, peaks):
     flops = sum(2.0 * 512 * n * k for (n, k) in shapes)
     out["int4_prefill_512"] = {"us_per_layer_linears": us, "tflops": flops / us / 1e6,
                                "what": "7 int4 weight-only linears of a Llama-2-7B-shaped layer at 512 tokens "
-                                       "(16-row slabs on mma.sync, not tuned)"}
+                                       "(tcgen05 fp16 GEMM, weights dequantised in flight into tensor memory)"}
     del weights
     # one large weight matrix (the gate/up projection of a Llama-2-70B-shaped layer): the HBM
     # stream without the per-launch costs that dominate the small matrices above
