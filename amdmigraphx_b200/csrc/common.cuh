@@ -35,6 +35,14 @@ int qgemm_status(unsigned int* out);
 int w4a16_status(unsigned int* out);
 int w4a16_tc_status(unsigned int* out);
 int w4a16_prefill_status(unsigned int* out);
+int qgemv_status(unsigned int* out);
+
+// skinny-M quant_dot (qgemv.cu)
+bool qgemv_applicable(const mgx_qgemm_desc& d, bool has_residual, bool has_qout);
+size_t qgemv_workspace(const mgx_qgemm_desc& d);
+int qgemv_launch(const mgx_qgemm_desc& d, const void* A, const void* B, void* D, const float* scale,
+                 const float* bias, int64_t ldb, void* workspace, size_t workspace_bytes,
+                 cudaStream_t stream);
 
 // tcgen05 int4 prefill path (w4a16_prefill.cu)
 bool w4a16_prefill_applicable(const mgx_w4_desc& d, const void* A, const void* Bp);

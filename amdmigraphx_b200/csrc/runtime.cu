@@ -74,7 +74,7 @@ extern "C" int mgx_cuda_device_status(int* status)
     cudaError_t e = cudaDeviceSynchronize();
     if(e != cudaSuccess)
         return static_cast<int>(e);
-    unsigned int a = 0, b = 0, c = 0, d = 0;
+    unsigned int a = 0, b = 0, c = 0, d = 0, g = 0;
     int rc = mgx::qgemm_status(&a);
     if(rc != 0)
         return rc;
@@ -87,7 +87,10 @@ extern "C" int mgx_cuda_device_status(int* status)
     rc = mgx::w4a16_prefill_status(&d);
     if(rc != 0)
         return rc;
-    *status = static_cast<int>(a != 0 ? a : (b != 0 ? b : (c != 0 ? c : d)));
+    rc = mgx::qgemv_status(&g);
+    if(rc != 0)
+        return rc;
+    *status = static_cast<int>(a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : g))));
     return MGX_OK;
 }
 

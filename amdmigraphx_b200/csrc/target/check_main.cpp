@@ -310,6 +310,8 @@ std::map<std::string, std::function<test_case()>> cases()
         {"fp8_gelu", [] { return qdq_linear(128, 512, 256, shape::fp8e4m3fn_type, "gelu", false, 4); }},
         {"int4_decode", [] { return int4_linear(1, 256, 512, 128, false, 5); }},
         {"int4_batch16_zp", [] { return int4_linear(16, 128, 1024, 32, true, 6); }},
+        {"int4_batch8_zp", [] { return int4_linear(8, 384, 1024, 128, true, 7); }},
+        {"int4_prefill", [] { return int4_linear(96, 256, 512, 128, true, 8); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
         {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
         {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},

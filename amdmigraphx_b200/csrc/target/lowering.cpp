@@ -363,6 +363,26 @@ struct lowerer
         {
             args[1]  = add_transposed_8bit_literal(m, b);
             op.b_nk  = true;
+            // decode-sized launches (at most 16 rows) stream the weights once through the
+            // skinny-M kernel, which wants room for partial sums
+            const auto& al = a->get_shape().lens();
+            const auto& bl = b->get_shape().lens();
+            if(al.size() == 2 and bl.size() == 2 and residual == m.end())
+            {
+                mgx_qgemm_desc d{};
+                d.M          = static_cast<int64_t>(al[0]);
+                d.K          = static_cast<int64_t>(al[1]);
+                d.N          = static_cast<int64_t>(bl[1]);
+                d.batch      = 1;
+                d.b_layout   = MGX_B_NK;
+                d.scale_mode = op.scale_mode;
+                const std::size_t ws = mgx_cuda_qgemm_workspace(&d);
+                if(ws > 0)
+                {
+                    workspace        = insert_allocation(m, last, shape{shape::int8_type, {ws}});
+                    op.has_workspace = true;
+                }
+            }
         }
         else
         {

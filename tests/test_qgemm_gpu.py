@@ -187,3 +187,94 @@ def test_qlinear_fused_output_quantizelinear(cuda_device, out, qtype, write_d):
         np.testing.assert_array_equal(y.cpu().numpy(), y_ref)
     else:
         assert float(y.min()) == 7.0 and float(y.max()) == 7.0  # untouched
+
+
+# ---------------------------------------------------------------- at most 16 rows: weight-streaming kernel
+SKINNY = [(1, 256, 512), (5, 1000, 2064), (16, 4096, 4096), (3, 130, 48), (16, 20000, 1024), (2, 384, 11008)]
+
+
+@pytest.mark.parametrize("M,N,K", SKINNY)
+def test_skinny_quant_dot_int8_bit_exact(cuda_device, M, N, K):
+    """[N,K] weights, decode-sized M: split-K partial sums are integers, the result is exact."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + N + K)
+    a = _rand_i8(rng, (M, K))
+    w = _rand_i8(rng, (N, K))
+    got = capi.qgemm(_t(a, cuda_device), _t(w, cuda_device), b_layout=capi.B_NK)
+    assert got.dtype == torch.int32
+    np.testing.assert_array_equal(got.cpu().numpy(), O.quant_dot_int8(a, w.T))
+
+
+@pytest.mark.parametrize("act", [None, "relu", "gelu_erf"])
+@pytest.mark.parametrize("scale_kind,out", [("tensor", "f32"), ("col", "f32"), ("col", "f16")])
+def test_skinny_qlinear_int8_fused_epilogue(cuda_device, act, scale_kind, out):
+    import torch
+    from amdmigraphx_b200 import capi
+    M, N, K = 8, 3072, 768
+    rng = np.random.default_rng(3)
+    a = _rand_i8(rng, (M, K))
+    w = _rand_i8(rng, (N, K))
+    if scale_kind == "tensor":
+        scale = np.array([1e-4], dtype=np.float32)
+        sview, mode = scale, capi.SCALE_PER_TENSOR
+    else:
+        scale = rng.uniform(2e-5, 2e-4, size=N).astype(np.float32)
+        sview, mode = scale[None, :], capi.SCALE_PER_COL
+    bias = rng.normal(0, 0.1, size=N).astype(np.float32)
+    odt = np.float32 if out == "f32" else np.float16
+    ref = O.qlinear_epilogue(O.quant_dot_int8(a, w.T), sview, bias, act, None, odt)
+    got = capi.qgemm(_t(a, cuda_device), _t(w, cuda_device), b_layout=capi.B_NK,
+                     scale=_t(scale, cuda_device), scale_mode=mode, bias=_t(bias, cuda_device), act=act,
+                     out_dtype=torch.float32 if out == "f32" else torch.float16).cpu().numpy()
+    if act in (None, "relu"):
+        np.testing.assert_array_equal(got, ref)
+    elif out == "f32":
+        np.testing.assert_allclose(got, ref, rtol=1e-5, atol=3e-6)
+    else:
+        np.testing.assert_allclose(got.astype(np.float32), ref.astype(np.float32), rtol=2e-3, atol=1e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 1536, 8192), (7, 200, 336)])
+def test_skinny_quant_dot_fp8(cuda_device, M, N, K):
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + 3 * N + 7 * K)
+    af = rng.normal(0, 1, size=(M, K)).astype(np.float32)
+    wf = rng.normal(0, 1, size=(N, K)).astype(np.float32)
+    sa = np.float32(np.abs(af).max() / 448.0)
+    sw = np.float32(np.abs(wf).max() / 448.0)
+    aq = O.quantizelinear(af, sa, None, "fp8e4m3fn")
+    wq = O.quantizelinear(wf, sw, None, "fp8e4m3fn")
+    bias = rng.normal(0, 0.1, size=N).astype(np.float32)
+    acc = O.quant_dot_fp8(aq, np.ascontiguousarray(wq.T))
+    scale = np.array([sa * sw], dtype=np.float32)
+    ref = O.qlinear_epilogue(acc, scale, bias, "gelu_erf")
+    a_t = _t(aq, cuda_device).view(torch.float8_e4m3fn)
+    w_t = _t(wq, cuda_device).view(torch.float8_e4m3fn)
+    raw = capi.qgemm(a_t, w_t, b_layout=capi.B_NK, out_dtype=torch.float32).cpu().numpy()
+    assert np.max(np.abs(raw - acc)) <= 2e-6 * np.abs(acc).max()
+    got = capi.qgemm(a_t, w_t, b_layout=capi.B_NK, scale=_t(scale, cuda_device),
+                     scale_mode=capi.SCALE_PER_TENSOR, bias=_t(bias, cuda_device), act="gelu_erf",
+                     out_dtype=torch.float32).cpu().numpy()
+    np.testing.assert_allclose(got, ref, rtol=2e-2, atol=1e-2)
+
+
+def test_skinny_without_workspace_runs_as_tiles(cuda_device):
+    """The workspace is optional for [N,K] weights: without it the tiled kernel takes the call."""
+    import ctypes
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(9)
+    a = _rand_i8(rng, (4, 256))
+    w = _rand_i8(rng, (384, 256))
+    lib = capi.load()
+    at, wt = _t(a, cuda_device), _t(w, cuda_device)
+    d = torch.empty((4, 384), dtype=torch.int32, device=cuda_device)
+    desc = capi.QgemmDesc(M=4, N=384, K=256, batch=1, lda=256, ldb=256, ldd=384, stride_a=0, stride_b=0,
+                          stride_d=0, ab_type=capi.I8, out_type=capi.I32, b_layout=capi.B_NK,
+                          scale_mode=capi.SCALE_NONE, act=0, reserved=0)
+    assert lib.mgx_cuda_qgemm_workspace(ctypes.byref(desc)) > 0
+    capi.check(lib.mgx_cuda_qgemm(ctypes.byref(desc), capi._ptr(at), capi._ptr(wt), capi._ptr(d), None,
+                                  None, None, None, 0, capi._stream()), "mgx_cuda_qgemm")
+    np.testing.assert_array_equal(d.cpu().numpy(), O.quant_dot_int8(a, w.T))
