@@ -3,7 +3,7 @@ driver bin/cuda_target_check.
 
 The plug-in is host C++17 compiled against MIGraphX's headers and linked to libmigraphx.so
 and to the kernel library.  MIGraphX itself is not part of this repository: the headers
-are taken from a MIGraphX source tree (MIGRAPHX_SOURCE_DIR, default /root/reference) and
+are taken from a MIGraphX source tree (MIGRAPHX_SOURCE_DIR) and
 the library from MIGRAPHX_LIB_DIR (default oracle/_ref/lib, where oracle/build_ref.py puts
 its build of the unmodified sources).  When the headers are absent (for example on a GPU
 box that only received the prebuilt files) the existing binaries are kept.

@@ -18,7 +18,7 @@ here with the same trivial content:
     file at build time)
   * stubs for msgpack / sqlite (third-party libraries absent here) that throw.
 
-Usage: python oracle/build_ref.py [--ref /root/reference] [--jobs 8]
+Usage: python oracle/build_ref.py [--ref <MIGraphX source tree>] [--jobs 8]
 """
 import argparse
 import concurrent.futures as cf

@@ -10,7 +10,7 @@ known-answer vector the reference ships for this path:
 Nothing is copied; the executable goes to oracle/_ref/bin/.  The pass/fail summary is
 written to tests/golden/reference_test_run.txt.
 
-Usage: python oracle/run_reference_tests.py [--ref /root/reference]
+Usage: python oracle/run_reference_tests.py [--ref <MIGraphX source tree>]
 """
 import argparse
 import concurrent.futures as cf
