@@ -177,6 +177,10 @@ __global__ void __launch_bounds__(256)
                                IdxT rows, IdxT colsv)
 {
     constexpr int VEC = 16 / sizeof(In);
+    // chained launches: the next kernel of the stream may set itself up now; this one reads
+    // the previous kernel's output only after that kernel has completed
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const IdxT total  = rows * colsv;
     const IdxT stride = static_cast<IdxT>(gridDim.x) * blockDim.x;
     const float s     = to_f32<In>(scale[0]);
@@ -290,11 +294,21 @@ static int launch_quantize(const void* x, int64_t ldx, const void* scale, view2 
         {
             if(small and uniform)
             {
-                quantize_i8_uniform_kernel<In, uint32_t><<<grid, 256, 0, stream>>>(
-                    static_cast<const In*>(x), ldx, static_cast<const In*>(scale),
-                    static_cast<const int8_t*>(zp), static_cast<int8_t*>(y), ldy,
-                    static_cast<uint32_t>(rows), static_cast<uint32_t>(cols / VEC));
-                return static_cast<int>(cudaGetLastError());
+                cudaLaunchConfig_t cfg{};
+                cfg.gridDim          = dim3(static_cast<unsigned>(grid));
+                cfg.blockDim         = dim3(256);
+                cfg.dynamicSmemBytes = 0;
+                cfg.stream           = stream;
+                cudaLaunchAttribute attr[1];
+                attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr[0].val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs    = attr;
+                cfg.numAttrs = 1;
+                return static_cast<int>(cudaLaunchKernelEx(
+                    &cfg, quantize_i8_uniform_kernel<In, uint32_t>, static_cast<const In*>(x), ldx,
+                    static_cast<const In*>(scale), static_cast<const int8_t*>(zp),
+                    static_cast<int8_t*>(y), ldy, static_cast<uint32_t>(rows),
+                    static_cast<uint32_t>(cols / VEC)));
             }
         }
         if(small and uniform)
