@@ -4,34 +4,37 @@
 //   D[m,n] = sum_g  s[n,g] * sum_{k in g} (q[n,k] - zp[n,g]) * a[m,k]
 //
 // is evaluated with INTEGER tensor-core arithmetic.  A small pre-kernel writes every
-// activation row as two int8 rows (a ~ sa[m] * (128 h + l), |error| <= sa/2, i.e. 15 bits of
-// the row's range) and the per-group sums Sv[g,m] = sum_k (128 h + l).  The main kernel then
-// computes, per group g of 128 k and per 128 output columns, with kind::i8 MMAs whose A operand
-// is the UNSIGNED nibble q (unpacked to bytes: two logic operations per eight weights, nothing
-// else touches a weight) and whose B operand are the h / l rows:
-//   P_hi[n,m] = sum_k q h,   P_lo[n,m] = sum_k q l        (exact int32, one TMEM column each)
-// and the epilogue folds   s[n,g] * (128 P_hi + P_lo - zp[n,g] * Sv[g,m])   into fp32 registers.
+// activation row as int8 rows (a ~ sa[m] * (128 h + l), |error| <= sa/2, i.e. 15 bits of the
+// row's range) and the per-group sums Sv[g,m] = sum_k (128 h + l).  The main kernel computes,
+// per group g of 128 k and per 128 output columns, with kind::i8 MMAs whose A operand are the
+// UNSIGNED weights and whose B operand are the activation rows, exact int32 sums
+// Q[n,m] = sum_k q[n,k] a_int[m,k] (spread over 2 or 4 accumulator columns per activation row,
+// see RAW below), and the epilogue folds  s[n,g] * (Q - zp[n,g] * Sv[g,m])  into fp32 registers.
 // The only inexact steps are the 15-bit activation rounding and the fp32 sum over groups; the
 // reference (src/onnx/parse_matmulnbits.cpp:85-158 IR on the ref target) rounds every
 // dequantised weight to fp16 instead, which is the coarser of the two.
 //
-// CTA = 384 threads, one CTA per SM:
-//   warp 0      TMA producer of packed weights: 4 groups = two requests of 128 rows x 128 bytes
-//   warp 10     TMA producer of the activation rows of the same 4 groups
-//   warps 2..5  unpack: one thread per weight row, shared memory -> registers -> the row's lane
-//               of TENSOR MEMORY (tcgen05.st); the MMA reads its A operand from there, so the
-//               unpacked bytes never cross shared memory
-//   warp 1      MMA issuer (A from tensor memory, B = activation rows in shared memory)
-//   warp 11     loads and converts the epilogue's scales / zero points / group sums a pass ahead
-//   warps 6..9  epilogue fold out of two accumulator buffers; the last warp to finish its 32
-//               columns of a tile that several CTAs share adds their partial sums in a fixed order
+// CTA = 480 threads (608 with a second set of epilogue warps), one CTA per SM:
+//   warp 0        TMA producer: per work item (4 groups) two requests of 128 rows x 128 bytes of
+//                 packed weights and one of the activation rows of the same groups
+//   warps 2..5    unpack: one thread per weight row, shared memory -> registers -> the row's lane
+//                 of TENSOR MEMORY (tcgen05.st); the MMA reads its A operand from there, so the
+//                 unpacked bytes never cross shared memory
+//   warps 1, 10..12  MMA issuers, one thread each: group i of every work item (an issue costs a
+//                 thread about 80 cycles)
+//   warps 13, 14  cp.async copies of the epilogue's scales / zero points / group sums, up to
+//                 three passes ahead
+//   warps 6..9 (and 15..18)  epilogue fold out of two accumulator buffers; the last warp to
+//                 finish its 32 columns of a tile that several CTAs share adds the partial sums
+//                 in a fixed order
+// Launches are chained programmatically: the main kernel streams weights while the pre-kernel
+// (and the tail of the previous kernel of the stream) still runs.
 // Only plain TMA loads; every wait is bounded.
 #include "common.cuh"
 #include "ptx.cuh"
 #include <cuda_fp16.h>
 
 namespace mgx {
-
 
 constexpr int TC_ROWS     = 128; // output columns (weight rows) per CTA tile = UMMA M
 constexpr int TC_GROUP_K  = 128; // k per group
