@@ -52,6 +52,7 @@ struct qgemm_params
     int write_d;       // D itself is wanted
     int vec_sb; // scale / bias vectors are 16-byte aligned (float4 loads allowed)
     int fast;   // the whole problem takes the epilogue's check-free path (see epi_store_chunk_fast)
+    int acc24;  // every accumulator is below 2^24 in magnitude (int8 operands, K < 1024)
     int vec_io; // D (and residual) rows can be accessed with 16-byte (fp32/int32) / 8-byte (fp16) vectors
 };
 
@@ -292,6 +293,7 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     uint8_t* qdst = static_cast<uint8_t*>(p.Dq) + e.batch_off_q + (e.row0 + rsub) * p.ldq + col + pc * 4;
     const int64_t dstep = 8 * p.ldd, qstep = 8 * p.ldq;
     const bool has_res = p.residual != nullptr, has_q = p.Dq != nullptr, wr = p.write_d != 0;
+    const bool acc24   = p.acc24 != 0;
     // saturation before rounding: bounds are integers, so round-to-nearest stays inside
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
     const int q_bias = static_cast<int>(p.q_zp) - 0x4B400000;
@@ -308,7 +310,12 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
         {
             float x;
             if constexpr(IS_INT)
-                x = dequant_i32(static_cast<int32_t>(wv[j]), sc[j]);
+            {
+                // |acc| < 2^24: the conversion is exact and the one fp32 multiply rounds like the
+                // reference's double product; no range test, no large-accumulator path
+                x = acc24 ? __fmul_rn(__int2float_rn(static_cast<int32_t>(wv[j])), sc[j])
+                          : dequant_i32(static_cast<int32_t>(wv[j]), sc[j]);
+            }
             else
                 x = __fmul_rn(__uint_as_float(wv[j]), sc[j]);
             v[j] = apply_act<ACT>(__fadd_rn(x, bi[j]));
@@ -778,6 +785,7 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
                      ? 1
                      : 0;
     }
+    p.acc24      = (IS_INT and d.K < 1024) ? 1 : 0; // |a b| <= 2^14 for int8 operands
     auto kernel  = qgemm_kernel<BN, IS_INT, OutT>;
     int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(kernel), S::total);
     if(rc2 != MGX_OK)
