@@ -253,19 +253,27 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
     }
 }
 
-// Four values at once: float(half_rz(v)) by masking, with the exact conversion only when one of
-// them is zero, subnormal as a half, or beyond its range (rare).
+// float(half_rz(v)) for |v| < 65536 without a conversion and without a branch: normal halves
+// keep the top 10 mantissa bits; below 2^-14 a half is a multiple of 2^-24, and |v| + 0.5 rounded
+// toward zero keeps exactly those bits (the spacing of fp32 in [0.5, 1) is 2^-24).
+__device__ __forceinline__ float half_rz_in_range(float v)
+{
+    const float av    = fabsf(v);
+    const float big   = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    const float small = copysignf(__fsub_rn(__fadd_rz(av, 0.5f), 0.5f), v);
+    return av < 6.103515625e-5f ? small : big;
+}
+
+// Four values at once; the real conversion only when one of them is beyond the half range
+// (or not a number).
 __device__ __forceinline__ void truncate4_to_half_precision(float (&v)[4])
 {
-    const uint32_t a0 = __float_as_uint(v[0]) & 0x7FFFFFFFu, a1 = __float_as_uint(v[1]) & 0x7FFFFFFFu;
-    const uint32_t a2 = __float_as_uint(v[2]) & 0x7FFFFFFFu, a3 = __float_as_uint(v[3]) & 0x7FFFFFFFu;
-    const uint32_t lo = min(min(a0, a1), min(a2, a3));
-    const uint32_t hi = max(max(a0, a1), max(a2, a3));
-    if(lo >= 0x38800000u and hi < 0x47800000u) // 2^-14 <= |v| < 2^16 for all four
+    const float hi = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    if(hi < 65536.0f)
     {
 #pragma unroll
         for(int j = 0; j < 4; ++j)
-            v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
+            v[j] = half_rz_in_range(v[j]);
     }
     else
     {

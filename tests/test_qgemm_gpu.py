@@ -278,3 +278,26 @@ def test_skinny_without_workspace_runs_as_tiles(cuda_device):
     capi.check(lib.mgx_cuda_qgemm(ctypes.byref(desc), capi._ptr(at), capi._ptr(wt), capi._ptr(d), None,
                                   None, None, None, 0, capi._stream()), "mgx_cuda_qgemm")
     np.testing.assert_array_equal(d.cpu().numpy(), O.quant_dot_int8(a, w.T))
+
+
+@pytest.mark.parametrize("act", [None, "relu"])
+def test_qlinear_int8_fp16_tiny_outputs_bit_exact(cuda_device, act):
+    """fp16 outputs in the subnormal range of a half (and exact zeros from relu), with a residual
+    and a fused quantizelinear so that every truncation site of the epilogue sees them."""
+    import torch
+    from amdmigraphx_b200 import capi
+    M, N, K = 256, 512, 256
+    rng = np.random.default_rng(21)
+    a = _rand_i8(rng, (M, K))
+    w = _rand_i8(rng, (N, K))
+    # accumulators ~1e5 x scales 1e-11..1e-9 -> |values| from 1e-8 to 1e-4
+    scale = (10.0 ** rng.uniform(-11, -9, size=N)).astype(np.float32)
+    bias = (rng.normal(0, 1, size=N) * 1e-6).astype(np.float32)
+    res = (rng.normal(0, 1, size=(M, N)) * 3e-6).astype(np.float16)
+    acc = O.quant_dot_int8(a, w.T)
+    ref = O.qlinear_epilogue(acc, scale[None, :], bias, act, res, np.float16)
+    got = capi.qgemm(_t(a, cuda_device), _t(w, cuda_device), b_layout=capi.B_NK, scale=_t(scale, cuda_device),
+                     bias=_t(bias, cuda_device), act=act, residual=_t(res, cuda_device),
+                     out_dtype=torch.float16).cpu().numpy()
+    assert np.count_nonzero(np.abs(ref.astype(np.float32)) < 6.1e-5) > ref.size // 2
+    np.testing.assert_array_equal(got, ref)
