@@ -313,21 +313,33 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
         const uint4 w = *reinterpret_cast<const uint4*>(box + it * 512 + ((pc ^ ((r >> 1) & 3)) * 16));
         const uint32_t wv[4] = {w.x, w.y, w.z, w.w};
         float v[4];
-#pragma unroll
-        for(int j = 0; j < 4; ++j)
+        if constexpr(IS_INT)
         {
-            float x;
-            if constexpr(IS_INT)
+            // one uniform branch around all four values, so that only one variant is issued
+            if(acc24)
             {
                 // |acc| < 2^24: the conversion is exact and the one fp32 multiply rounds like the
                 // reference's double product; no range test, no large-accumulator path
-                x = acc24 ? __fmul_rn(__int2float_rn(static_cast<int32_t>(wv[j])), sc[j])
-                          : dequant_i32(static_cast<int32_t>(wv[j]), sc[j]);
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                    v[j] = __fmul_rn(__int2float_rn(static_cast<int32_t>(wv[j])), sc[j]);
             }
             else
-                x = __fmul_rn(__uint_as_float(wv[j]), sc[j]);
-            v[j] = apply_act<ACT>(__fadd_rn(x, bi[j]));
+            {
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                    v[j] = dequant_i32(static_cast<int32_t>(wv[j]), sc[j]);
+            }
         }
+        else
+        {
+#pragma unroll
+            for(int j = 0; j < 4; ++j)
+                v[j] = __fmul_rn(__uint_as_float(wv[j]), sc[j]);
+        }
+#pragma unroll
+        for(int j = 0; j < 4; ++j)
+            v[j] = apply_act<ACT>(__fadd_rn(v[j], bi[j]));
         if(has_res)
         {
             float q[4];
