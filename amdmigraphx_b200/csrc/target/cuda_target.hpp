@@ -54,6 +54,20 @@ struct context_state
     cudaEvent_t finish_event = nullptr;
     std::unordered_map<std::string, argument> preallocations;
     bool ready = false;
+    // CUDA-graph replay of the instruction stream (cuda::graph_begin / cuda::graph_end)
+    enum class graph_mode
+    {
+        off,       // not used for this program
+        warm,      // still executing instruction by instruction
+        capturing, // this eval is being captured
+        ready      // a graph is instantiated for `graph_params`
+    };
+    graph_mode gmode        = graph_mode::off;
+    int warm_evals          = 0;
+    bool replaying          = false; // the graph was launched: launching operators do nothing
+    cudaGraph_t graph       = nullptr;
+    cudaGraphExec_t gexec   = nullptr;
+    std::vector<const void*> graph_params; // parameter buffers the graph was captured with
     context_state(int dev, std::size_t nstreams);
     void init(); // creates the streams and events (first use)
     ~context_state();
@@ -73,6 +87,12 @@ struct MGX_CUDA_EXPORT context
     cudaEvent_t event(std::size_t id);
     void store_preallocation(const std::string& id, const argument& a);
     argument get_preallocation(const std::string& id) const;
+    // true while a captured graph stands in for the instruction stream: operators that would
+    // launch work return their output buffer instead
+    bool replaying() const { return state->replaying; }
+    void graph_begin(const std::vector<const void*>& params);
+    void graph_end();
+    void enable_graph();
 
     // migraphx::context interface
     void finish() const;
@@ -141,6 +161,20 @@ struct lowering
 struct write_literals
 {
     std::string name() const { return "cuda::write_literals"; }
+    void apply(module& m) const;
+};
+
+// Brackets the launching instructions of the main module with cuda::graph_begin /
+// cuda::graph_end: from the third eval() on, the whole instruction stream is one
+// cudaGraphLaunch as long as the caller passes the same parameter buffers (host time per
+// eval() is then independent of the number of instructions; src/program.cpp:472-565 is the
+// loop this short-cuts).  Not applied with offload_copy, several streams or collectives;
+// MIGRAPHX_CUDA_GRAPH=0 turns it off.
+struct insert_graph_ops
+{
+    context* ctx      = nullptr;
+    bool offload_copy = false;
+    std::string name() const { return "cuda::insert_graph_ops"; }
     void apply(module& m) const;
 };
 

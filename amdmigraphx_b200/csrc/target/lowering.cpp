@@ -22,6 +22,7 @@
 #include <migraphx/half.hpp>
 #include "../../../include/mgx_cuda.h"
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <set>
 #include <unordered_set>
@@ -775,6 +776,52 @@ void write_literals::apply(module& m) const
 }
 
 // ------------------------------------------------------------------ sync_device
+// ------------------------------------------------------------------ insert_graph_ops
+void insert_graph_ops::apply(module& m) const
+{
+    const char* env = std::getenv("MIGRAPHX_CUDA_GRAPH");
+    if(ctx == nullptr or offload_copy or ctx->nstreams() > 1 or (env != nullptr and env[0] == '0'))
+        return;
+    auto launches = [](const std::string& n) {
+        return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
+               n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or n == "cuda::copy";
+    };
+    instruction_ref first = m.end();
+    std::size_t nlaunch   = 0;
+    for(auto ins : iterator_for(m))
+    {
+        const auto n = ins->name();
+        // host copies, explicit synchronisation and collectives stay outside graphs
+        if(n == "cuda::copy_to" or n == "cuda::copy_from" or n == "cuda::all_reduce" or
+           n == "cuda::set_stream" or n == "cuda::record_event" or n == "cuda::wait_event")
+            return;
+        if(launches(n))
+        {
+            if(first == m.end())
+                first = ins;
+            ++nlaunch;
+        }
+    }
+    auto last = std::prev(m.end());
+    if(nlaunch == 0 or last->name() != "@return" or last->inputs().empty())
+        return;
+    // graph_begin must see every parameter buffer: parameters move in front of it
+    std::vector<instruction_ref> params;
+    for(auto ins : iterator_for(m))
+        if(ins->name() == "@param")
+            params.push_back(ins);
+    for(auto p : params)
+        m.move_instruction(p, first);
+    m.insert_instruction(first, op_graph_begin{}, params);
+    // graph_end passes the first result through, in front of the final synchronisation
+    auto res = last->inputs().front();
+    auto pos = res->name() == "cuda::sync_stream" ? res : last;
+    auto src = res->name() == "cuda::sync_stream" ? res->inputs().front() : res;
+    auto end = m.insert_instruction(pos, op_graph_end{}, src);
+    instruction::replace_argument(pos, src, end);
+    ctx->enable_graph();
+}
+
 void sync_device::apply(module& m) const
 {
     auto last = std::prev(m.end());

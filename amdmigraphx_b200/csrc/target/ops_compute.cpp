@@ -99,6 +99,8 @@ argument op_quantizelinear::compute(context& ctx, const shape&, const std::vecto
 {
     const auto& xs  = args[0].get_shape();
     const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
     const auto m    = as_matrix(xs, "quantizelinear input");
     const auto mo   = as_matrix(out.get_shape(), "quantizelinear output");
     int64_t ss[2] = {0, 0}, zs[2] = {0, 0};
@@ -124,6 +126,8 @@ argument op_dequantizelinear::compute(context& ctx, const shape&, const std::vec
 {
     const auto& xs  = args[0].get_shape();
     const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
     const auto m    = as_matrix(xs, "dequantizelinear input");
     const auto mo   = as_matrix(out.get_shape(), "dequantizelinear output");
     int64_t ss[2] = {0, 0}, zs[2] = {0, 0};
@@ -146,6 +150,8 @@ shape op_unpack_int4::compute_shape(const std::vector<shape>& inputs) const
 }
 argument op_unpack_int4::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
+    if(ctx.replaying())
+        return args[1];
     const auto m = as_matrix(args[0].get_shape(), "unpack_int4 input");
     check_mgx(mgx_cuda_unpack_int4(args[0].data(), args[1].data(),
                                    mgx_type(args[0].get_shape().type()), m.rows, m.cols, ctx.stream()),
@@ -160,6 +166,8 @@ shape op_pack_int4::compute_shape(const std::vector<shape>& inputs) const
 }
 argument op_pack_int4::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
+    if(ctx.replaying())
+        return args[1];
     const auto m = as_matrix(args[1].get_shape(), "pack_int4 output");
     check_mgx(mgx_cuda_pack_int4(args[0].data(), args[1].data(), mgx_type(args[0].get_shape().type()),
                                  m.rows, m.cols, ctx.stream()),
@@ -200,6 +208,8 @@ shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
 
 argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
+    if(ctx.replaying())
+        return args.back(); // the output buffer (the un-quantised one of a pair)
     std::size_t i          = 2;
     const argument* scale  = scale_mode != MGX_SCALE_NONE ? &args[i++] : nullptr;
     const argument* bias   = has_bias ? &args[i++] : nullptr;
@@ -293,6 +303,8 @@ shape op_w4a16::compute_shape(const std::vector<shape>& inputs) const
 
 argument op_w4a16::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
+    if(ctx.replaying())
+        return args.back();
     std::size_t i          = 3;
     const argument* zp     = has_zp ? &args[i++] : nullptr;
     const argument* wspace = has_workspace ? &args[i++] : nullptr;

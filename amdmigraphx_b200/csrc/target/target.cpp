@@ -118,6 +118,7 @@ std::vector<pass> target::get_passes(migraphx::context& gctx, const compile_opti
         eliminate_allocation{"cuda::allocate"},
         check_context<context>{},
         dead_code_elimination{},
+        insert_graph_ops{&ctx, options.offload_copy},
     };
 }
 
