@@ -278,6 +278,111 @@ test_case q_dq_ops(unsigned seed)
     return t;
 }
 
+// Element-wise operators outside the GEMM patterns (the "next" part of the path): an fp16
+// bias + erf-GELU + residual chain as a BERT layer has it between its linears.
+test_case pw_gelu_f16(unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    const std::size_t r = 96, c = 320;
+    auto* mm  = t.prog.get_main_module();
+    const shape xs{shape::half_type, {r, c}};
+    auto x    = mm->add_parameter("x", xs);
+    auto res  = mm->add_parameter("res", xs);
+    auto bv   = rand_normal(g, c, 0.3f);
+    std::vector<migraphx::half> bh(bv.begin(), bv.end());
+    auto bias = mm->add_literal(migraphx::literal{shape{shape::half_type, {c}}, bh});
+    auto lit  = [&](float v) {
+        auto l = mm->add_literal(migraphx::literal{shape{shape::half_type}, {migraphx::half(v)}});
+        return mm->add_instruction(migraphx::make_op("multibroadcast", {{"out_lens", xs.lens()}}), l);
+    };
+    auto xb   = mm->add_instruction(migraphx::make_op("add"), x, bcast_axis(mm, bias, 1, {r, c}));
+    auto u    = mm->add_instruction(migraphx::make_op("mul"), xb, lit(0.70710678f));
+    auto e    = mm->add_instruction(migraphx::make_op("erf"), u);
+    auto e1   = mm->add_instruction(migraphx::make_op("add"), e, lit(1.0f));
+    auto h    = mm->add_instruction(migraphx::make_op("mul"), xb, lit(0.5f));
+    auto ge   = mm->add_instruction(migraphx::make_op("mul"), h, e1);
+    auto y    = mm->add_instruction(migraphx::make_op("add"), ge, res);
+    mm->add_return({y});
+    auto fill = [&](const char* name, float sd) {
+        auto v = rand_normal(g, r * c, sd);
+        std::vector<migraphx::half> hv(v.begin(), v.end());
+        migraphx::argument a{xs};
+        std::memcpy(a.data(), hv.data(), hv.size() * sizeof(migraphx::half));
+        t.params[name] = a;
+    };
+    fill("x", 1.5f);
+    fill("res", 1.0f);
+    // libm and CUDA erf differ in the last place; every fp16 operator truncates like the reference
+    t.rtol = 4e-3;
+    t.atol = 2e-3;
+    return t;
+}
+
+// fp32 operators with exactly rounded results: bit-exact against ref.
+test_case pw_arith_f32(unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    const std::size_t b = 3, r = 40, c = 72;
+    auto* mm = t.prog.get_main_module();
+    const shape xs{shape::float_type, {b, r, c}};
+    auto x   = mm->add_parameter("x", xs);
+    auto y   = mm->add_parameter("y", xs);
+    auto sv  = rand_uniform(g, c, 0.5f, 2.0f);
+    auto s   = mm->add_literal(migraphx::literal{shape{shape::float_type, {c}}, sv});
+    auto sb  = mm->add_instruction(migraphx::make_op("broadcast", {{"axis", 2}, {"out_lens", xs.lens()}}), s);
+    auto d   = mm->add_instruction(migraphx::make_op("div"), x, sb);
+    auto a   = mm->add_instruction(migraphx::make_op("abs"), d);
+    auto q   = mm->add_instruction(migraphx::make_op("sqrt"), a);
+    auto gt  = mm->add_instruction(migraphx::make_op("greater"), x, y);
+    auto mn  = mm->add_instruction(migraphx::make_op("min"), x, y);
+    auto w   = mm->add_instruction(migraphx::make_op("where"), gt, q, mn);
+    auto rl  = mm->add_instruction(migraphx::make_op("relu"), w);
+    auto rs  = mm->add_instruction(migraphx::make_op("sub"), rl, y);
+    auto n   = mm->add_instruction(migraphx::make_op("neg"), rs);
+    auto rc  = mm->add_instruction(migraphx::make_op("recip"), mm->add_instruction(migraphx::make_op("add"), a, sb));
+    auto out = mm->add_instruction(migraphx::make_op("mul"), n, rc);
+    auto hf  = mm->add_instruction(migraphx::make_op("convert", {{"target_type", migraphx::to_value(shape::half_type)}}), out);
+    mm->add_return({out, hf});
+    for(const char* name : {"x", "y"})
+    {
+        auto v = rand_normal(g, b * r * c, 2.0f);
+        migraphx::argument arg{xs};
+        std::memcpy(arg.data(), v.data(), v.size() * sizeof(float));
+        t.params[name] = arg;
+    }
+    t.exact = true;
+    return t;
+}
+
+// transcendental operators in fp32: within rtol 1e-5 of ref (libm vs CUDA math library).
+test_case pw_transcendental_f32(unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    const std::size_t r = 64, c = 200;
+    auto* mm = t.prog.get_main_module();
+    const shape xs{shape::float_type, {r, c}};
+    auto x   = mm->add_parameter("x", xs);
+    auto th  = mm->add_instruction(migraphx::make_op("tanh"), x);
+    auto sg  = mm->add_instruction(migraphx::make_op("sigmoid"), x);
+    auto ex  = mm->add_instruction(migraphx::make_op("exp"), th);
+    auto lg  = mm->add_instruction(migraphx::make_op("log"), mm->add_instruction(migraphx::make_op("add"), ex, sg));
+    auto er  = mm->add_instruction(migraphx::make_op("erf"), x);
+    auto rq  = mm->add_instruction(migraphx::make_op("rsqrt"), mm->add_instruction(migraphx::make_op("add"), ex, ex));
+    auto o1  = mm->add_instruction(migraphx::make_op("mul"), lg, er);
+    auto o2  = mm->add_instruction(migraphx::make_op("add"), o1, rq);
+    mm->add_return({o2});
+    auto v = rand_normal(g, r * c, 1.5f);
+    migraphx::argument arg{xs};
+    std::memcpy(arg.data(), v.data(), v.size() * sizeof(float));
+    t.params["x"] = arg;
+    t.rtol = 1e-5;
+    t.atol = 1e-6;
+    return t;
+}
+
 // quant_dot alone on int8 parameters (batched, non-constant right operand).
 test_case raw_quant_dot(unsigned seed)
 {
@@ -312,6 +417,9 @@ std::map<std::string, std::function<test_case()>> cases()
         {"int4_batch16_zp", [] { return int4_linear(16, 128, 1024, 32, true, 6); }},
         {"int4_batch8_zp", [] { return int4_linear(8, 384, 1024, 128, true, 7); }},
         {"int4_prefill", [] { return int4_linear(96, 256, 512, 128, true, 8); }},
+        {"pw_gelu_f16", [] { return pw_gelu_f16(9); }},
+        {"pw_arith_f32", [] { return pw_arith_f32(10); }},
+        {"pw_transcendental_f32", [] { return pw_transcendental_f32(11); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
         {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
         {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},

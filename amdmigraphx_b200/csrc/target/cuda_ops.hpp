@@ -259,6 +259,26 @@ struct op_second_output
     std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {1}; }
 };
 
+// Element-wise instructions evaluated per output element (mgx_cuda_pointwise): value i is input i
+// for i < n inputs, then the instructions' results; the last result is the output.  Inputs: the
+// operands (strided / broadcast views of the output's index space), then the output buffer.
+struct op_pointwise
+{
+    std::vector<int> ops;    // mgx_pw_op per instruction
+    std::vector<int> types;  // shape::type_t of every result
+    std::vector<int> srcs;   // three operand indices per instruction
+    std::vector<float> imms; // one immediate per instruction
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.ops, "ops"), f(self.types, "types"), f(self.srcs, "srcs"), f(self.imms, "imms"));
+    }
+    std::string name() const { return "cuda::pointwise"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
+};
+
 // Weight-only int4 linear (unpack_int4 + dequantizelinear + transpose + dot fused).
 // Inputs: A fp16 [M,K], packed weights uint8 [N,K/2], scales fp16 [N,K/group],
 // [zero points uint8 [N,K/group]], [workspace], out fp16 [M,N].

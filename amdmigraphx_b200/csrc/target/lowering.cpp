@@ -25,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <set>
+#include <unordered_map>
 #include <unordered_set>
 
 namespace migraphx {
@@ -589,6 +590,44 @@ struct lowerer
         consume(m.replace_instruction(ins, op, args));
     }
 
+    // A single element-wise operator (src/include/migraphx/op/{unary,binary}.hpp and friends)
+    // becomes a one-instruction cuda::pointwise.
+    bool lower_elementwise_op(instruction_ref ins)
+    {
+        static const std::unordered_map<std::string, int> table = {
+            {"add", MGX_PW_ADD},       {"sub", MGX_PW_SUB},         {"mul", MGX_PW_MUL},
+            {"div", MGX_PW_DIV},       {"min", MGX_PW_MIN},         {"max", MGX_PW_MAX},
+            {"pow", MGX_PW_POW},       {"neg", MGX_PW_NEG},         {"abs", MGX_PW_ABS},
+            {"exp", MGX_PW_EXP},       {"log", MGX_PW_LOG},         {"sqrt", MGX_PW_SQRT},
+            {"rsqrt", MGX_PW_RSQRT},   {"recip", MGX_PW_RECIP},     {"tanh", MGX_PW_TANH},
+            {"sigmoid", MGX_PW_SIGMOID}, {"erf", MGX_PW_ERF},       {"relu", MGX_PW_RELU},
+            {"sin", MGX_PW_SIN},       {"cos", MGX_PW_COS},         {"floor", MGX_PW_FLOOR},
+            {"ceil", MGX_PW_CEIL},     {"round", MGX_PW_ROUND},     {"nearbyint", MGX_PW_NEARBYINT},
+            {"convert", MGX_PW_CONVERT}, {"where", MGX_PW_WHERE},   {"clip", MGX_PW_CLIP},
+            {"equal", MGX_PW_EQUAL},   {"greater", MGX_PW_GREATER}, {"less", MGX_PW_LESS},
+            {"leaky_relu", MGX_PW_LEAKY_RELU}, {"identity", MGX_PW_IDENTITY}};
+        auto it = table.find(ins->name());
+        if(it == table.end())
+            return false;
+        auto args = ins->inputs();
+        if(args.empty() or args.size() > 3)
+            return false;
+        const auto& os = ins->get_shape();
+        for(auto a : args)
+            if(a->get_shape().lens() != os.lens())
+                unsupported(ins, "operands must have the output's dimensions");
+        op_pointwise op;
+        op.ops   = {it->second};
+        op.types = {static_cast<int>(os.type())};
+        op.srcs  = {0, args.size() > 1 ? 1 : 0, args.size() > 2 ? 2 : 0};
+        op.imms  = {0.0f};
+        if(ins->name() == "leaky_relu")
+            op.imms[0] = ins->get_operator().to_value().at("alpha").to<float>();
+        args.push_back(insert_allocation(m, ins, os.as_standard()));
+        consume(m.replace_instruction(ins, op, args));
+        return true;
+    }
+
     template <class Op>
     void lower_int4(instruction_ref ins, Op op)
     {
@@ -657,6 +696,8 @@ struct lowerer
                 lower_int4(ins, op_unpack_int4{});
             else if(name == "pack_int4")
                 lower_int4(ins, op_pack_int4{});
+            else if(lower_elementwise_op(ins))
+                continue;
             else
                 unsupported(ins, "no kernel");
         }
@@ -784,7 +825,8 @@ void insert_graph_ops::apply(module& m) const
         return;
     auto launches = [](const std::string& n) {
         return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
-               n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or n == "cuda::copy";
+               n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or
+               n == "cuda::copy" or n == "cuda::pointwise";
     };
     instruction_ref first = m.end();
     std::size_t nlaunch   = 0;

@@ -352,6 +352,76 @@ argument op_second_output::compute(context&, const shape&, const std::vector<arg
     return args.at(1);
 }
 
+// ------------------------------------------------------------------ element-wise
+static int pw_type(shape::type_t t)
+{
+    // a bool is a byte holding 0 or 1
+    return t == shape::bool_type ? MGX_I8 : mgx_type(t);
+}
+
+shape op_pointwise::compute_shape(const std::vector<shape>& inputs) const
+{
+    if(inputs.empty() or ops.empty() or types.size() != ops.size() or srcs.size() != 3 * ops.size() or
+       imms.size() != ops.size())
+        MIGRAPHX_THROW("cuda::pointwise: malformed instruction list");
+    if(inputs.size() - 1 > MGX_PW_MAXIN or ops.size() > MGX_PW_MAXINSN)
+        MIGRAPHX_THROW("cuda::pointwise: too many inputs or instructions");
+    const auto& out = inputs.back();
+    for(std::size_t i = 0; i + 1 < inputs.size(); ++i)
+        if(inputs[i].lens() != out.lens())
+            MIGRAPHX_THROW("cuda::pointwise: every operand must have the output's dimensions");
+    if(not out.standard())
+        MIGRAPHX_THROW("cuda::pointwise: output must be a standard tensor");
+    return out;
+}
+
+argument op_pointwise::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& os = out.get_shape();
+    mgx_pw_desc d{};
+    // more dimensions than the kernel indexes: fold the leading ones when every operand is packed
+    std::vector<std::size_t> lens = os.lens();
+    bool flat = lens.size() > MGX_PW_MAXDIMS;
+    if(flat)
+    {
+        for(std::size_t i = 0; i + 1 < args.size(); ++i)
+            if(not args[i].get_shape().standard())
+                MIGRAPHX_THROW("cuda::pointwise: more than 5 dimensions need packed operands");
+        lens = {os.elements()};
+    }
+    d.ndim    = static_cast<int32_t>(lens.size());
+    d.ninputs = static_cast<int32_t>(args.size() - 1);
+    d.ninsns  = static_cast<int32_t>(ops.size());
+    for(std::size_t k = 0; k < lens.size(); ++k)
+        d.lens[k] = static_cast<int64_t>(lens[k]);
+    const void* ptrs[MGX_PW_MAXIN] = {};
+    for(std::size_t i = 0; i + 1 < args.size(); ++i)
+    {
+        const auto& s = args[i].get_shape();
+        d.in_type[i]  = pw_type(s.type());
+        ptrs[i]       = args[i].data();
+        if(flat)
+            d.in_strides[i][0] = 1;
+        else
+            for(std::size_t k = 0; k < lens.size(); ++k)
+                d.in_strides[i][k] = static_cast<int64_t>(s.strides()[k]);
+    }
+    for(std::size_t n = 0; n < ops.size(); ++n)
+    {
+        d.insn[n].op   = ops[n];
+        d.insn[n].type = pw_type(static_cast<shape::type_t>(types[n]));
+        d.insn[n].imm  = imms[n];
+        for(int j = 0; j < 3; ++j)
+            d.insn[n].src[j] = srcs[3 * n + j];
+    }
+    check_mgx(mgx_cuda_pointwise(&d, ptrs, out.data(), ctx.stream()), "mgx_cuda_pointwise");
+    return out;
+}
+
+MIGRAPHX_REGISTER_OP(op_pointwise)
 MIGRAPHX_REGISTER_OP(op_second_output)
 MIGRAPHX_REGISTER_OP(op_all_reduce)
 MIGRAPHX_REGISTER_OP(op_quantizelinear)

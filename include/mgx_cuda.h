@@ -96,6 +96,55 @@ MGX_API int mgx_cuda_quantizelinear(const void* x,
                                     int64_t cols,
                                     void* stream);
 
+/* ---- generic element-wise operator ("next" row: the non-GEMM part of a program) --------- *
+ * Evaluates a short list of scalar instructions per output element, the way
+ * op::pointwise::compute (src/include/migraphx/op/pointwise.hpp:81-114) evaluates the
+ * instructions of its sub-module: value i is input i for i < ninputs, otherwise the result of
+ * instruction i - ninputs; the last instruction's result is the output.  Every result is
+ * converted to its instruction's type before it is used again (MGX_F16: truncating, as
+ * migraphx::half converts, src/include/migraphx/generic_float.hpp:180-230), so a chain of
+ * fp16 operators rounds where the reference rounds.  Inputs are strided views of the output's
+ * index space (stride 0 = broadcast); the output is a packed row-major tensor of `lens`. */
+#define MGX_PW_MAXDIMS 5
+#define MGX_PW_MAXIN 8
+#define MGX_PW_MAXINSN 32
+
+typedef enum mgx_pw_op {
+    MGX_PW_ADD = 0, MGX_PW_SUB, MGX_PW_MUL, MGX_PW_DIV, MGX_PW_MIN, MGX_PW_MAX, MGX_PW_POW,
+    MGX_PW_NEG, MGX_PW_ABS, MGX_PW_EXP, MGX_PW_LOG, MGX_PW_SQRT, MGX_PW_RSQRT, MGX_PW_RECIP,
+    MGX_PW_TANH, MGX_PW_SIGMOID, MGX_PW_ERF, MGX_PW_RELU, MGX_PW_SIN, MGX_PW_COS,
+    MGX_PW_FLOOR, MGX_PW_CEIL, MGX_PW_ROUND, MGX_PW_NEARBYINT,
+    MGX_PW_CONVERT,    /* to the instruction's type */
+    MGX_PW_WHERE,      /* src0 != 0 ? src1 : src2 */
+    MGX_PW_CLIP,       /* min(max(src0, src1), src2) */
+    MGX_PW_EQUAL, MGX_PW_GREATER, MGX_PW_LESS,
+    MGX_PW_LEAKY_RELU, /* src0 > 0 ? src0 : src0 * imm */
+    MGX_PW_CONST,      /* imm */
+    MGX_PW_IDENTITY,
+    MGX_PW_OP_COUNT
+} mgx_pw_op;
+
+typedef struct mgx_pw_insn {
+    int32_t op;       /* mgx_pw_op */
+    int32_t type;     /* mgx_dtype of the result (MGX_I8 also stands for bool) */
+    int32_t src[3];   /* indices of the operand values */
+    float imm;
+} mgx_pw_insn;
+
+typedef struct mgx_pw_desc {
+    int32_t ndim;                       /* 1 .. MGX_PW_MAXDIMS */
+    int32_t ninputs;                    /* 0 .. MGX_PW_MAXIN */
+    int32_t ninsns;                     /* 1 .. MGX_PW_MAXINSN */
+    int32_t reserved;
+    int64_t lens[MGX_PW_MAXDIMS];       /* output dimensions */
+    int32_t in_type[MGX_PW_MAXIN];      /* mgx_dtype of every input */
+    int64_t in_strides[MGX_PW_MAXIN][MGX_PW_MAXDIMS]; /* in elements */
+    mgx_pw_insn insn[MGX_PW_MAXINSN];
+} mgx_pw_desc;
+
+/* inputs: ninputs device pointers.  out: packed tensor of the last instruction's type. */
+MGX_API int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* inputs, void* out, void* stream);
+
 /* ---- dequantizelinear -------------------------------------------------- *
  * y = (x - zp) * scale, output type = scale type (MGX_F32 | MGX_F16).
  * Stands in for op::dequantizelinear::compute
