@@ -164,6 +164,15 @@ struct write_literals
     void apply(module& m) const;
 };
 
+// Merges a cuda::pointwise whose result has a single user into that user when the user is a
+// cuda::pointwise too (what fuse_pointwise does for the reference's targets): chains of
+// element-wise operators become one launch.
+struct fuse_cuda_pointwise
+{
+    std::string name() const { return "cuda::fuse_pointwise"; }
+    void apply(module& m) const;
+};
+
 // Brackets the launching instructions of the main module with cuda::graph_begin /
 // cuda::graph_end: from the third eval() on, the whole instruction stream is one
 // cudaGraphLaunch as long as the caller passes the same parameter buffers (host time per

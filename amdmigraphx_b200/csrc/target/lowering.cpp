@@ -21,6 +21,7 @@
 #include <migraphx/stringutils.hpp>
 #include <migraphx/half.hpp>
 #include "../../../include/mgx_cuda.h"
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -817,6 +818,91 @@ void write_literals::apply(module& m) const
 }
 
 // ------------------------------------------------------------------ sync_device
+// ------------------------------------------------------------------ fuse_cuda_pointwise
+void fuse_cuda_pointwise::apply(module& m) const
+{
+    bool changed = true;
+    while(changed)
+    {
+        changed = false;
+        for(auto user : iterator_for(m))
+        {
+            if(user->name() != "cuda::pointwise")
+                continue;
+            auto uop = any_cast<op_pointwise>(user->get_operator());
+            auto uin = user->inputs(); // operands..., output buffer
+            // an operand produced by another cuda::pointwise that nothing else reads
+            std::size_t which = uin.size();
+            for(std::size_t i = 0; i + 1 < uin.size(); ++i)
+                if(uin[i]->name() == "cuda::pointwise" and
+                   std::all_of(uin[i]->outputs().begin(), uin[i]->outputs().end(),
+                               [&](auto o) { return o == user; }) and
+                   std::count(uin.begin(), uin.end(), uin[i]) == 1)
+                {
+                    which = i;
+                    break;
+                }
+            if(which == uin.size())
+                continue;
+            auto prod = uin[which];
+            auto pop  = any_cast<op_pointwise>(prod->get_operator());
+            auto pin  = prod->inputs();
+            // merged operand list: the producer's operands, then the user's other operands
+            std::vector<instruction_ref> operands(pin.begin(), pin.end() - 1);
+            std::vector<int> umap(uin.size() - 1, -1); // user's operand index -> merged value index
+            for(std::size_t i = 0; i + 1 < uin.size(); ++i)
+            {
+                if(i == which)
+                    continue;
+                auto it = std::find(operands.begin(), operands.end(), uin[i]);
+                if(it == operands.end())
+                {
+                    operands.push_back(uin[i]);
+                    it = std::prev(operands.end());
+                }
+                umap[i] = static_cast<int>(it - operands.begin());
+            }
+            const std::size_t nin = operands.size();
+            const std::size_t np  = pop.ops.size();
+            if(nin > MGX_PW_MAXIN or np + uop.ops.size() > MGX_PW_MAXINSN)
+                continue;
+            op_pointwise f;
+            const int pin_n = static_cast<int>(pin.size() - 1);
+            auto pmap = [&](int v) { return v < pin_n ? v : static_cast<int>(nin) + (v - pin_n); };
+            for(std::size_t n = 0; n < np; ++n)
+            {
+                f.ops.push_back(pop.ops[n]);
+                f.types.push_back(pop.types[n]);
+                f.imms.push_back(pop.imms[n]);
+                for(int j = 0; j < 3; ++j)
+                    f.srcs.push_back(pmap(pop.srcs[3 * n + j]));
+            }
+            const int uin_n   = static_cast<int>(uin.size() - 1);
+            const int presult = static_cast<int>(nin + np - 1);
+            auto umapv        = [&](int v) {
+                if(v >= uin_n)
+                    return static_cast<int>(nin + np) + (v - uin_n);
+                return v == static_cast<int>(which) ? presult : umap[static_cast<std::size_t>(v)];
+            };
+            for(std::size_t n = 0; n < uop.ops.size(); ++n)
+            {
+                f.ops.push_back(uop.ops[n]);
+                f.types.push_back(uop.types[n]);
+                f.imms.push_back(uop.imms[n]);
+                for(int j = 0; j < 3; ++j)
+                    f.srcs.push_back(umapv(uop.srcs[3 * n + j]));
+            }
+            operands.push_back(uin.back());
+            m.replace_instruction(user, f, operands);
+            // the producer is dead now; while it exists it still counts as a user of its operands
+            if(prod->outputs().empty())
+                m.remove_instruction(prod);
+            changed = true;
+            break; // the instruction list changed under the iterator
+        }
+    }
+}
+
 // ------------------------------------------------------------------ insert_graph_ops
 void insert_graph_ops::apply(module& m) const
 {

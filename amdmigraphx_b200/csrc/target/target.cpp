@@ -105,6 +105,8 @@ std::vector<pass> target::get_passes(migraphx::context& gctx, const compile_opti
         dead_code_elimination{},
         lowering{&ctx, options.offload_copy},
         dead_code_elimination{},
+        fuse_cuda_pointwise{},
+        dead_code_elimination{},
         replace_allocate{allocation_model{}, options.offload_copy},
         dead_code_elimination{},
         adjust_allocation{allocation_model{}},
