@@ -291,6 +291,53 @@ def w4a16(a, bp, scales, zp=None, *, zp_const=8, group=128, act=None, which="aut
     return d
 
 
+# ------------------------------------------------------------------ element-wise
+PW_MAXDIMS, PW_MAXIN, PW_MAXINSN = 5, 8, 32
+PW_OPS = ["add", "sub", "mul", "div", "min", "max", "pow", "neg", "abs", "exp", "log", "sqrt", "rsqrt",
+          "recip", "tanh", "sigmoid", "erf", "relu", "sin", "cos", "floor", "ceil", "round", "nearbyint",
+          "convert", "where", "clip", "equal", "greater", "less", "leaky_relu", "const", "identity"]
+
+
+class PwInsn(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_int32), ("type", ctypes.c_int32), ("src", ctypes.c_int32 * 3),
+                ("imm", ctypes.c_float)]
+
+
+class PwDesc(ctypes.Structure):
+    _fields_ = [("ndim", ctypes.c_int32), ("ninputs", ctypes.c_int32), ("ninsns", ctypes.c_int32),
+                ("reserved", ctypes.c_int32), ("lens", ctypes.c_int64 * PW_MAXDIMS),
+                ("in_type", ctypes.c_int32 * PW_MAXIN),
+                ("in_strides", (ctypes.c_int64 * PW_MAXDIMS) * PW_MAXIN),
+                ("insn", PwInsn * PW_MAXINSN)]
+
+
+def pointwise(inputs, program, lens):
+    """inputs: tensors viewed (expanded) to `lens`; program: list of (op name, result dtype code,
+    (src0, src1, src2), imm).  Returns the packed result of the last instruction."""
+    import torch
+    lib = load()
+    d = PwDesc()
+    d.ndim, d.ninputs, d.ninsns = len(lens), len(inputs), len(program)
+    for k, n in enumerate(lens):
+        d.lens[k] = n
+    for i, t in enumerate(inputs):
+        assert tuple(t.shape) == tuple(lens)
+        d.in_type[i] = _dtype_code(t)
+        for k in range(len(lens)):
+            d.in_strides[i][k] = t.stride(k)
+    for n, (op, ty, src, imm) in enumerate(program):
+        d.insn[n].op, d.insn[n].type, d.insn[n].imm = PW_OPS.index(op), ty, imm
+        for j in range(3):
+            d.insn[n].src[j] = src[j] if j < len(src) else 0
+    tdt = {F32: torch.float32, F16: torch.float16, I8: torch.int8, U8: torch.uint8, I32: torch.int32}
+    out = torch.empty(tuple(lens), dtype=tdt[program[-1][1]], device=inputs[0].device)
+    ptrs = (ctypes.c_void_p * max(1, len(inputs)))(*[t.data_ptr() for t in inputs])
+    lib.mgx_cuda_pointwise.restype = ctypes.c_int
+    check(lib.mgx_cuda_pointwise(ctypes.byref(d), ptrs, ctypes.c_void_p(out.data_ptr()), _stream()),
+          "mgx_cuda_pointwise")
+    return out
+
+
 # ------------------------------------------------------------------ tensor parallel
 class Communicator(object):
     """One NCCL communicator per process, created from a 128-byte id that rank 0 makes and the
