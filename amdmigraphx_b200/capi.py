@@ -24,7 +24,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
+    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -335,6 +335,38 @@ def pointwise(inputs, program, lens):
     lib.mgx_cuda_pointwise.restype = ctypes.c_int
     check(lib.mgx_cuda_pointwise(ctypes.byref(d), ptrs, ctypes.c_void_p(out.data_ptr()), _stream()),
           "mgx_cuda_pointwise")
+    return out
+
+
+REDUCE_OPS = ["sum", "mean", "max", "min"]
+
+
+def reduce_rows(x, op):
+    """reduce_sum / reduce_mean / reduce_max / reduce_min over the last axis of a 2-D tensor
+    (rows may be strided); returns [rows, 1] of x's type."""
+    import torch
+    lib = load()
+    assert x.dim() == 2 and x.stride(1) == 1
+    out = torch.empty((x.shape[0], 1), dtype=x.dtype, device=x.device)
+    lib.mgx_cuda_reduce.restype = ctypes.c_int
+    check(lib.mgx_cuda_reduce(ctypes.c_void_p(x.data_ptr()), _dtype_code(x), ctypes.c_int64(x.stride(0)),
+                              ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]),
+                              REDUCE_OPS.index(op), ctypes.c_void_p(out.data_ptr()), _stream()),
+          "mgx_cuda_reduce")
+    return out
+
+
+def softmax(x):
+    """softmax over the last axis of a 2-D tensor (rows may be strided)."""
+    import torch
+    lib = load()
+    assert x.dim() == 2 and x.stride(1) == 1
+    out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    lib.mgx_cuda_softmax.restype = ctypes.c_int
+    check(lib.mgx_cuda_softmax(ctypes.c_void_p(x.data_ptr()), _dtype_code(x), ctypes.c_int64(x.stride(0)),
+                               ctypes.c_void_p(out.data_ptr()), ctypes.c_int64(out.stride(0)),
+                               ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]), _stream()),
+          "mgx_cuda_softmax")
     return out
 
 

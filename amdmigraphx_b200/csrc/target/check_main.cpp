@@ -383,6 +383,83 @@ test_case pw_transcendental_f32(unsigned seed)
     return t;
 }
 
+// LayerNorm as the ONNX parser decomposes it (reduce_mean, sub, mul, reduce_mean, add eps,
+// rsqrt, mul, scale, bias) over the innermost axis of a [batch, seq, hidden] tensor.
+test_case layernorm(shape::type_t type, std::size_t b, std::size_t sq, std::size_t hid, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const shape xs{type, {b, sq, hid}};
+    auto x    = mm->add_parameter("x", xs);
+    auto make = [&](const std::vector<float>& v, const std::vector<std::size_t>& lens) {
+        if(type == shape::half_type)
+        {
+            std::vector<migraphx::half> h(v.begin(), v.end());
+            return mm->add_literal(migraphx::literal{shape{type, lens}, h});
+        }
+        return mm->add_literal(migraphx::literal{shape{type, lens}, v});
+    };
+    auto full = [&](migraphx::instruction_ref r) {
+        return mm->add_instruction(migraphx::make_op("multibroadcast", {{"out_lens", xs.lens()}}), r);
+    };
+    auto gamma = make(rand_uniform(g, hid, 0.5f, 1.5f), {hid});
+    auto beta  = make(rand_normal(g, hid, 0.2f), {hid});
+    auto eps   = make({1e-5f}, {1});
+    auto mean  = mm->add_instruction(migraphx::make_op("reduce_mean", {{"axes", {2}}}), x);
+    auto d     = mm->add_instruction(migraphx::make_op("sub"), x, full(mean));
+    auto d2    = mm->add_instruction(migraphx::make_op("mul"), d, d);
+    auto var   = mm->add_instruction(migraphx::make_op("reduce_mean", {{"axes", {-1}}}), d2);
+    auto lens1 = var->get_shape().lens();
+    auto epsb  = mm->add_instruction(migraphx::make_op("multibroadcast", {{"out_lens", lens1}}), eps);
+    auto rs    = mm->add_instruction(migraphx::make_op("rsqrt"), mm->add_instruction(migraphx::make_op("add"), var, epsb));
+    auto nrm   = mm->add_instruction(migraphx::make_op("mul"), d, full(rs));
+    auto sc    = mm->add_instruction(migraphx::make_op("mul"), nrm, full(gamma));
+    auto y     = mm->add_instruction(migraphx::make_op("add"), sc, full(beta));
+    auto mx    = mm->add_instruction(migraphx::make_op("reduce_max", {{"axes", {2}}}), x);
+    auto mn    = mm->add_instruction(migraphx::make_op("reduce_min", {{"axes", {2}}}), x);
+    auto sm    = mm->add_instruction(migraphx::make_op("reduce_sum", {{"axes", {2}}}), x);
+    mm->add_return({y, mx, mn, sm});
+    auto v = rand_normal(g, b * sq * hid, 1.0f);
+    migraphx::argument arg{xs};
+    if(type == shape::half_type)
+    {
+        std::vector<migraphx::half> h(v.begin(), v.end());
+        std::memcpy(arg.data(), h.data(), h.size() * sizeof(migraphx::half));
+    }
+    else
+        std::memcpy(arg.data(), v.data(), v.size() * sizeof(float));
+    t.params["x"] = arg;
+    // the reference sums sequentially in double, the kernel as an fp32 tree
+    t.rtol = type == shape::half_type ? 1e-2 : 1e-5;
+    t.atol = type == shape::half_type ? 1e-2 : 2e-5;
+    return t;
+}
+
+// softmax over the innermost axis of attention-score shaped input [batch, heads, q, k].
+test_case softmax_rows(shape::type_t type, std::size_t b, std::size_t h, std::size_t q, std::size_t k, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const shape xs{type, {b, h, q, k}};
+    auto x   = mm->add_parameter("x", xs);
+    mm->add_return({mm->add_instruction(migraphx::make_op("softmax", {{"axis", 3}}), x)});
+    auto v = rand_normal(g, xs.elements(), 3.0f);
+    migraphx::argument arg{xs};
+    if(type == shape::half_type)
+    {
+        std::vector<migraphx::half> hv(v.begin(), v.end());
+        std::memcpy(arg.data(), hv.data(), hv.size() * sizeof(migraphx::half));
+    }
+    else
+        std::memcpy(arg.data(), v.data(), v.size() * sizeof(float));
+    t.params["x"] = arg;
+    t.rtol = type == shape::half_type ? 4e-3 : 1e-5;
+    t.atol = type == shape::half_type ? 1e-5 : 1e-8;
+    return t;
+}
+
 // quant_dot alone on int8 parameters (batched, non-constant right operand).
 test_case raw_quant_dot(unsigned seed)
 {
@@ -420,6 +497,11 @@ std::map<std::string, std::function<test_case()>> cases()
         {"pw_gelu_f16", [] { return pw_gelu_f16(9); }},
         {"pw_arith_f32", [] { return pw_arith_f32(10); }},
         {"pw_transcendental_f32", [] { return pw_transcendental_f32(11); }},
+        {"layernorm_f32", [] { return layernorm(shape::float_type, 2, 48, 768, 12); }},
+        {"layernorm_f16", [] { return layernorm(shape::half_type, 3, 20, 1000, 13); }},
+        {"softmax_f32", [] { return softmax_rows(shape::float_type, 2, 4, 56, 200, 14); }},
+        {"softmax_f16", [] { return softmax_rows(shape::half_type, 1, 3, 40, 1500, 15); }},
+        {"softmax_f32_long", [] { return softmax_rows(shape::float_type, 1, 1, 6, 9000, 16); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
         {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
         {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},

@@ -279,6 +279,31 @@ struct op_pointwise
     std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
 };
 
+// reduce_sum / reduce_mean / reduce_max / reduce_min over the innermost axis
+// (src/include/migraphx/op/reduce_op.hpp).  Inputs: x (standard), out (x's lens, last = 1).
+struct op_reduce
+{
+    int mode = 0; // mgx_reduce_op
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.mode, "mode"));
+    }
+    std::string name() const { return "cuda::reduce"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
+};
+
+// softmax over the innermost axis (src/include/migraphx/op/softmax.hpp).  Inputs: x, out.
+struct op_softmax
+{
+    std::string name() const { return "cuda::softmax"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
+};
+
 // Weight-only int4 linear (unpack_int4 + dequantizelinear + transpose + dot fused).
 // Inputs: A fp16 [M,K], packed weights uint8 [N,K/2], scales fp16 [N,K/group],
 // [zero points uint8 [N,K/group]], [workspace], out fp16 [M,N].

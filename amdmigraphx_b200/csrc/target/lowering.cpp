@@ -629,6 +629,48 @@ struct lowerer
         return true;
     }
 
+    // reduce_* and softmax over the innermost axis
+    bool lower_row_op(instruction_ref ins)
+    {
+        static const std::unordered_map<std::string, int> modes = {{"reduce_sum", MGX_REDUCE_SUM},
+                                                                   {"reduce_mean", MGX_REDUCE_MEAN},
+                                                                   {"reduce_max", MGX_REDUCE_MAX},
+                                                                   {"reduce_min", MGX_REDUCE_MIN}};
+        const auto name    = ins->name();
+        const bool softmax = name == "softmax";
+        auto it            = modes.find(name);
+        if(not softmax and it == modes.end())
+            return false;
+        if(ins->inputs().size() != 1)
+            unsupported(ins, "variable axes are not supported");
+        const auto& xs = ins->inputs()[0]->get_shape();
+        const auto nd  = static_cast<int64_t>(xs.ndim());
+        const auto v   = ins->get_operator().to_value();
+        if(softmax)
+        {
+            const auto ax = v.at("axis").to<int64_t>();
+            if(ax != -1 and ax != nd - 1)
+                unsupported(ins, "only the innermost axis is supported");
+        }
+        else
+        {
+            const auto axes = v.at("axes").to_vector<int64_t>();
+            if(axes.size() != 1 or (axes[0] != -1 and axes[0] != nd - 1))
+                unsupported(ins, "only the innermost axis is supported");
+        }
+        if(not xs.standard())
+            unsupported(ins, "input must be a standard tensor");
+        if(xs.type() != shape::float_type and xs.type() != shape::half_type)
+            unsupported(ins, "float and half only");
+        auto args = ins->inputs();
+        args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
+        if(softmax)
+            consume(m.replace_instruction(ins, op_softmax{}, args));
+        else
+            consume(m.replace_instruction(ins, op_reduce{it->second}, args));
+        return true;
+    }
+
     template <class Op>
     void lower_int4(instruction_ref ins, Op op)
     {
@@ -698,6 +740,8 @@ struct lowerer
             else if(name == "pack_int4")
                 lower_int4(ins, op_pack_int4{});
             else if(lower_elementwise_op(ins))
+                continue;
+            else if(lower_row_op(ins))
                 continue;
             else
                 unsupported(ins, "no kernel");
@@ -912,7 +956,7 @@ void insert_graph_ops::apply(module& m) const
     auto launches = [](const std::string& n) {
         return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
                n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or
-               n == "cuda::copy" or n == "cuda::pointwise";
+               n == "cuda::copy" or n == "cuda::pointwise" or n == "cuda::reduce" or n == "cuda::softmax";
     };
     instruction_ref first = m.end();
     std::size_t nlaunch   = 0;

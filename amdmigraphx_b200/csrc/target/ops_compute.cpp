@@ -421,6 +421,63 @@ argument op_pointwise::compute(context& ctx, const shape&, const std::vector<arg
     return out;
 }
 
+// ------------------------------------------------------------------ reductions, softmax
+static void check_rows(const std::string& name, const shape& x)
+{
+    if(not x.standard() or x.ndim() == 0)
+        MIGRAPHX_THROW(name + ": input must be a standard tensor");
+    if(x.type() != shape::float_type and x.type() != shape::half_type)
+        MIGRAPHX_THROW(name + ": float and half only");
+}
+
+shape op_reduce::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(2);
+    check_rows(name(), inputs[0]);
+    auto lens   = inputs[0].lens();
+    lens.back() = 1;
+    if(inputs[1].lens() != lens or inputs[1].type() != inputs[0].type() or not inputs[1].standard())
+        MIGRAPHX_THROW("cuda::reduce: output must be the packed input with a last dimension of 1");
+    return inputs[1];
+}
+
+argument op_reduce::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& xs     = args[0].get_shape();
+    const int64_t cols = static_cast<int64_t>(xs.lens().back());
+    const int64_t rows = static_cast<int64_t>(xs.elements()) / cols;
+    check_mgx(mgx_cuda_reduce(args[0].data(), mgx_type(xs.type()), cols, rows, cols, mode, out.data(), ctx.stream()),
+              "mgx_cuda_reduce");
+    return out;
+}
+
+shape op_softmax::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(2);
+    check_rows(name(), inputs[0]);
+    if(inputs[1].lens() != inputs[0].lens() or inputs[1].type() != inputs[0].type() or not inputs[1].standard())
+        MIGRAPHX_THROW("cuda::softmax: output must be a packed tensor of the input's shape");
+    return inputs[1];
+}
+
+argument op_softmax::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& xs     = args[0].get_shape();
+    const int64_t cols = static_cast<int64_t>(xs.lens().back());
+    const int64_t rows = static_cast<int64_t>(xs.elements()) / cols;
+    check_mgx(mgx_cuda_softmax(args[0].data(), mgx_type(xs.type()), cols, out.data(), cols, rows, cols, ctx.stream()),
+              "mgx_cuda_softmax");
+    return out;
+}
+
+MIGRAPHX_REGISTER_OP(op_reduce)
+MIGRAPHX_REGISTER_OP(op_softmax)
 MIGRAPHX_REGISTER_OP(op_pointwise)
 MIGRAPHX_REGISTER_OP(op_second_output)
 MIGRAPHX_REGISTER_OP(op_all_reduce)

@@ -145,6 +145,23 @@ typedef struct mgx_pw_desc {
 /* inputs: ninputs device pointers.  out: packed tensor of the last instruction's type. */
 MGX_API int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* inputs, void* out, void* stream);
 
+/* ---- reductions over the last axis and softmax ("next" rows: LayerNorm, attention) ------ *
+ * x is [rows, cols] with row stride ldx (elements), y[rows] packed.  Stands in for
+ * op::reduce_sum / reduce_mean / reduce_max / reduce_min (src/include/migraphx/op/reduce_op.hpp:
+ * 180-203: the reference accumulates in double; here fp32 partial sums are combined as a tree,
+ * within 1e-6 relative of it) restricted to the innermost axis.  Types: MGX_F32 | MGX_F16,
+ * the result has x's type (fp16: truncating conversion). */
+typedef enum mgx_reduce_op { MGX_REDUCE_SUM = 0, MGX_REDUCE_MEAN = 1, MGX_REDUCE_MAX = 2, MGX_REDUCE_MIN = 3 } mgx_reduce_op;
+
+MGX_API int mgx_cuda_reduce(const void* x, int type, int64_t ldx, int64_t rows, int64_t cols, int op,
+                            void* y, void* stream);
+
+/* y[r, c] = exp(x[r, c] - max_c x[r, :]) / sum_c exp(...), over the innermost axis, with the
+ * reference's intermediate roundings (ref_softmax, src/targets/ref/lowering.cpp:253-320: the
+ * exponentials are stored in the output type before they are summed and divided). */
+MGX_API int mgx_cuda_softmax(const void* x, int type, int64_t ldx, void* y, int64_t ldy, int64_t rows,
+                             int64_t cols, void* stream);
+
 /* ---- dequantizelinear -------------------------------------------------- *
  * y = (x - zp) * scale, output type = scale type (MGX_F32 | MGX_F16).
  * Stands in for op::dequantizelinear::compute
