@@ -29,6 +29,8 @@ int ensure_smem_optin(const void* kernel, int bytes);
 // stride ld_dst >= rows (padding bytes are left untouched).
 int transpose_8bit_ld(const void* src, void* dst, int64_t rows, int64_t cols, int64_t batch,
                       int64_t ld_dst, cudaStream_t stream);
+int transpose_16bit_ld(const void* src, void* dst, int64_t rows, int64_t cols, int64_t batch,
+                       int64_t ld_dst, cudaStream_t stream);
 
 // Status words of the translation units that own bounded waits.
 int qgemm_status(unsigned int* out);

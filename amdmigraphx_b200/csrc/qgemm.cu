@@ -538,7 +538,9 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
 
 // IS_INT: accumulator registers hold int32 (kind::i8) else fp32 bit patterns.
 // OutT: int32_t (raw accumulator), float or __half.
-template <int BN, bool IS_INT, class OutT>
+// F16: the operands are fp16 (kind::f16, 64 elements of K per 128-byte stage row); the byte
+// layout of the pipeline is the one of the 8-bit kinds.
+template <int BN, bool IS_INT, class OutT, bool F16 = false>
 __global__ void __launch_bounds__(NTHREADS, 1)
     qgemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b,
@@ -636,7 +638,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         if(lane == 0)
         {
             constexpr uint32_t idesc = IS_INT ? make_idesc(2u, 1u, 1u, BM, BN)  // s32 += s8*s8
-                                              : make_idesc(1u, 0u, 0u, BM, BN); // f32 += e4m3*e4m3
+                                              : make_idesc(1u, 0u, 0u, BM, BN); // f32 += e4m3*e4m3 (f16*f16)
             uint32_t it = 0;
             uint32_t lt = 0; // local tile counter
             bool ok     = true;
@@ -667,6 +669,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                         const uint64_t koff = static_cast<uint64_t>((k * UMMA_K) >> 4);
                         if constexpr(IS_INT)
                             mma_i8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0);
+                        else if constexpr(F16)
+                            mma_f16(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0);
                         else
                             mma_f8(d_tmem, adesc + koff, bdesc + koff, idesc, (kb | k) != 0);
                     }
@@ -744,17 +748,18 @@ static int encode_operand_map(CUtensorMap* map, const void* base, int64_t k, int
     return r == CUDA_SUCCESS ? MGX_OK : MGX_E_INVALID_ARG;
 }
 
-template <int BN, bool IS_INT, class OutT>
+template <int BN, bool IS_INT, class OutT, bool F16 = false>
 static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, void* D,
                         const float* scale, const float* bias, const void* residual,
                         int64_t ldb, int64_t stride_b, const qout_args& qo, cudaStream_t stream)
 {
     using S = qgemm_smem<BN>;
     CUtensorMap ta, tb;
-    int rc = encode_operand_map(&ta, A, d.K, d.M, d.batch, d.lda, d.stride_a, BM);
+    constexpr int64_t ab = F16 ? 2 : 1; // bytes per operand element: the maps address bytes
+    int rc = encode_operand_map(&ta, A, d.K * ab, d.M, d.batch, d.lda * ab, d.stride_a * ab, BM);
     if(rc != MGX_OK)
         return rc;
-    rc = encode_operand_map(&tb, B, d.K, d.N, d.batch, ldb, stride_b, BN);
+    rc = encode_operand_map(&tb, B, d.K * ab, d.N, d.batch, ldb * ab, stride_b * ab, BN);
     if(rc != MGX_OK)
         return rc;
     qgemm_params p{};
@@ -779,7 +784,7 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
     p.tiles_m    = static_cast<int>((d.M + BM - 1) / BM);
     p.tiles_n    = static_cast<int>((d.N + BN - 1) / BN);
     p.num_tiles  = static_cast<int64_t>(p.tiles_m) * p.tiles_n * d.batch;
-    p.num_kb     = static_cast<int>((d.K + BK - 1) / BK);
+    p.num_kb     = static_cast<int>((d.K * ab + BK - 1) / BK);
     p.scale_mode = d.scale_mode;
     p.act        = d.act;
     p.Dq         = qo.Dq;
@@ -806,7 +811,7 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
                      : 0;
     }
     p.acc24      = (IS_INT and d.K < 1024) ? 1 : 0; // |a b| <= 2^14 for int8 operands
-    auto kernel  = qgemm_kernel<BN, IS_INT, OutT>;
+    auto kernel  = qgemm_kernel<BN, IS_INT, OutT, F16>;
     int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(kernel), S::total);
     if(rc2 != MGX_OK)
         return rc2;
@@ -827,7 +832,7 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
     return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, ta, tb, p));
 }
 
-template <int BN, bool IS_INT>
+template <int BN, bool IS_INT, bool F16 = false>
 static int dispatch_out(const mgx_qgemm_desc& d, const void* A, const void* B, void* D,
                         const float* scale, const float* bias, const void* residual, int64_t ldb,
                         int64_t stride_b, const qout_args& qo, cudaStream_t stream)
@@ -840,9 +845,9 @@ static int dispatch_out(const mgx_qgemm_desc& d, const void* A, const void* B, v
         else
             return MGX_E_UNSUPPORTED;
     case MGX_F32:
-        return launch_qgemm<BN, IS_INT, float>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
+        return launch_qgemm<BN, IS_INT, float, F16>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
     case MGX_F16:
-        return launch_qgemm<BN, IS_INT, __half>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
+        return launch_qgemm<BN, IS_INT, __half, F16>(d, A, B, D, scale, bias, residual, ldb, stride_b, qo, stream);
     default: return MGX_E_UNSUPPORTED;
     }
 }
@@ -857,7 +862,7 @@ static int pick_bn(const mgx_qgemm_desc& d)
 {
     const int64_t sms = device_sm_count();
     const int64_t tm  = (d.M + BM - 1) / BM;
-    const int64_t kb  = (d.K + BK - 1) / BK;
+    const int64_t kb  = (d.K * (d.ab_type == MGX_F16 ? 2 : 1) + BK - 1) / BK;
     int best          = 64;
     int64_t best_cost = INT64_MAX;
     for(int bn : {256, 128, 64})
@@ -887,10 +892,12 @@ extern "C" size_t mgx_cuda_qgemm_workspace(const mgx_qgemm_desc* d)
     {
         // optional: with it, launches of at most 16 rows take the weight-streaming kernel
         // (partial sums of tiles shared between thread blocks); without it they run as tiles
-        if(d->M > 0 and d->N > 0 and d->K > 0 and qgemv_applicable(*d, false, false))
+        if(d->M > 0 and d->N > 0 and d->K > 0 and d->ab_type != MGX_F16 and qgemv_applicable(*d, false, false))
             return qgemv_workspace(*d);
         return 0;
     }
+    if(d->ab_type == MGX_F16)
+        return static_cast<size_t>(d->batch) * d->N * ((d->K + 7) / 8 * 8) * 2;
     const int64_t kpad = (d->K + 15) / 16 * 16;
     return static_cast<size_t>(d->batch) * d->N * kpad;
 }
@@ -934,7 +941,11 @@ extern "C" int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* d, const void* A, const v
         D = qo.Dq; // never written (write_d = 0); keeps the pointer checks below uniform
     if(d->M <= 0 or d->N <= 0 or d->K <= 0 or d->batch <= 0)
         return MGX_E_INVALID_ARG;
-    if(d->ab_type != MGX_I8 and d->ab_type != MGX_FP8_E4M3FN)
+    if(d->ab_type != MGX_I8 and d->ab_type != MGX_FP8_E4M3FN and d->ab_type != MGX_F16)
+        return MGX_E_UNSUPPORTED;
+    const bool f16       = d->ab_type == MGX_F16;
+    const int64_t ealign = f16 ? 8 : 16; // elements per 16 bytes
+    if(f16 and qo.Dq != nullptr)
         return MGX_E_UNSUPPORTED;
     if(d->scale_mode < MGX_SCALE_NONE or d->scale_mode > MGX_SCALE_PER_ROW)
         return MGX_E_INVALID_ARG;
@@ -950,8 +961,8 @@ extern "C" int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* d, const void* A, const v
         return MGX_E_TOO_LARGE;
     if(d->lda < d->K or d->ldd < d->N)
         return MGX_E_INVALID_ARG;
-    if((reinterpret_cast<uintptr_t>(A) & 15u) or (d->lda % 16) or
-       (d->batch > 1 and (d->stride_a % 16)))
+    if((reinterpret_cast<uintptr_t>(A) & 15u) or (d->lda % ealign) or
+       (d->batch > 1 and (d->stride_a % ealign)))
         return MGX_E_ALIGNMENT;
 
     const void* Bk   = B;
@@ -967,8 +978,9 @@ extern "C" int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* d, const void* A, const v
             return MGX_E_WORKSPACE;
         if(reinterpret_cast<uintptr_t>(workspace) & 15u)
             return MGX_E_ALIGNMENT;
-        const int64_t kpad = (d->K + 15) / 16 * 16;
-        int rc = transpose_8bit_ld(B, workspace, d->K, d->N, d->batch, kpad, stream);
+        const int64_t kpad = (d->K + ealign - 1) / ealign * ealign;
+        int rc = f16 ? transpose_16bit_ld(B, workspace, d->K, d->N, d->batch, kpad, stream)
+                     : transpose_8bit_ld(B, workspace, d->K, d->N, d->batch, kpad, stream);
         if(rc != MGX_OK)
             return rc;
         Bk       = workspace;
@@ -979,15 +991,24 @@ extern "C" int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* d, const void* A, const v
         return MGX_E_INVALID_ARG;
     if(ldb < d->K)
         return MGX_E_INVALID_ARG;
-    if((reinterpret_cast<uintptr_t>(Bk) & 15u) or (ldb % 16) or
-       (d->batch > 1 and (stride_b % 16)))
+    if((reinterpret_cast<uintptr_t>(Bk) & 15u) or (ldb % ealign) or
+       (d->batch > 1 and (stride_b % ealign)))
         return MGX_E_ALIGNMENT;
 
     // at most 16 rows: stream the weights once, if the caller lent the workspace for it
-    if(qgemv_applicable(*d, residual != nullptr, qo.Dq != nullptr) and workspace != nullptr and
+    if(not f16 and qgemv_applicable(*d, residual != nullptr, qo.Dq != nullptr) and workspace != nullptr and
        workspace_bytes >= qgemv_workspace(*d))
         return qgemv_launch(*d, A, Bk, D, scale, bias, ldb, workspace, workspace_bytes, stream);
     const bool is_int = d->ab_type == MGX_I8;
+    if(f16)
+    {
+        switch(pick_bn(*d))
+        {
+        case 256: return dispatch_out<256, false, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream);
+        case 128: return dispatch_out<128, false, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream);
+        default: return dispatch_out<64, false, true>(*d, A, Bk, D, scale, bias, residual, ldb, stride_b, qo, stream);
+        }
+    }
     switch(pick_bn(*d))
     {
     case 256:

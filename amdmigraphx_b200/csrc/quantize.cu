@@ -506,6 +506,53 @@ int transpose_8bit_ld(const void* src, void* dst, int64_t rows, int64_t cols, in
     return static_cast<int>(cudaGetLastError());
 }
 
+// ------------------------------------------------------------ 16-bit transpose
+// 32 x 32 tile of 16-bit elements through shared memory (the [K,N] operand of an fp16 dot
+// re-laid out K-contiguous); rows of dst beyond `rows` up to ld_dst are not written.
+__global__ void __launch_bounds__(256)
+    transpose_16bit_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int64_t rows,
+                           int64_t cols, int64_t ld_dst)
+{
+    __shared__ uint16_t tile[32][32 + 2];
+    const int64_t b   = blockIdx.z;
+    const uint16_t* s = src + b * rows * cols;
+    uint16_t* d       = dst + b * cols * ld_dst;
+    const int64_t r0  = static_cast<int64_t>(blockIdx.y) * 32;
+    const int64_t c0  = static_cast<int64_t>(blockIdx.x) * 32;
+    const int tx      = threadIdx.x & 31;
+    const int ty      = threadIdx.x >> 5; // 8 row slots
+#pragma unroll
+    for(int i = 0; i < 4; ++i)
+    {
+        const int rr    = ty + i * 8;
+        const int64_t r = r0 + rr, c = c0 + tx;
+        tile[rr][tx]    = (r < rows and c < cols) ? s[r * cols + c] : uint16_t{0};
+    }
+    __syncthreads();
+#pragma unroll
+    for(int i = 0; i < 4; ++i)
+    {
+        const int cc    = ty + i * 8; // column of src = row of dst
+        const int64_t c = c0 + cc, r = r0 + tx;
+        if(c < cols and r < rows)
+            d[c * ld_dst + r] = tile[tx][cc];
+    }
+}
+
+int transpose_16bit_ld(const void* src, void* dst, int64_t rows, int64_t cols, int64_t batch,
+                       int64_t ld_dst, cudaStream_t stream)
+{
+    if(src == nullptr or dst == nullptr or rows <= 0 or cols <= 0 or batch <= 0 or ld_dst < rows)
+        return MGX_E_INVALID_ARG;
+    const int64_t gx = ceil_div(cols, 32), gy = ceil_div(rows, 32);
+    if(gy > 65535 or batch > 65535)
+        return MGX_E_TOO_LARGE;
+    dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy), static_cast<unsigned>(batch));
+    transpose_16bit_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(src),
+                                                     static_cast<uint16_t*>(dst), rows, cols, ld_dst);
+    return static_cast<int>(cudaGetLastError());
+}
+
 } // namespace mgx
 
 using namespace mgx;

@@ -460,6 +460,80 @@ test_case softmax_rows(shape::type_t type, std::size_t b, std::size_t h, std::si
     return t;
 }
 
+// Multi-head attention on fp16 tensors as the ONNX parser lays it out: [batch, seq, heads * dim]
+// projections reshaped and transposed into heads, Q.K^T scaled, softmax, P.V, heads merged back.
+test_case attention_f16(std::size_t b, std::size_t h, std::size_t sq, std::size_t d, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const shape xs{shape::half_type, {b, sq, h * d}};
+    auto heads = [&](const char* name, std::vector<int64_t> perm) {
+        auto p = mm->add_parameter(name, xs);
+        auto r = mm->add_instruction(migraphx::make_op("reshape", {{"dims", {b, sq, h, d}}}), p);
+        return mm->add_instruction(migraphx::make_op("transpose", {{"permutation", perm}}), r);
+    };
+    auto q  = heads("q", {0, 2, 1, 3});
+    auto kt = heads("k", {0, 2, 3, 1});
+    auto v  = heads("v", {0, 2, 1, 3});
+    auto sc = mm->add_instruction(migraphx::make_op("dot"), q, kt);
+    auto l  = mm->add_literal(migraphx::literal{shape{shape::half_type}, {migraphx::half(1.0f / std::sqrt(static_cast<float>(d)))}});
+    auto lb = mm->add_instruction(migraphx::make_op("multibroadcast", {{"out_lens", sc->get_shape().lens()}}), l);
+    auto ss = mm->add_instruction(migraphx::make_op("mul"), sc, lb);
+    auto p  = mm->add_instruction(migraphx::make_op("softmax", {{"axis", 3}}), ss);
+    auto o  = mm->add_instruction(migraphx::make_op("dot"), p, v);
+    auto ot = mm->add_instruction(migraphx::make_op("transpose", {{"permutation", {0, 2, 1, 3}}}), o);
+    auto oc = mm->add_instruction(migraphx::make_op("contiguous"), ot);
+    auto y  = mm->add_instruction(migraphx::make_op("reshape", {{"dims", {b, sq, h * d}}}), oc);
+    mm->add_return({y});
+    for(const char* name : {"q", "k", "v"})
+    {
+        auto vals = rand_normal(g, xs.elements(), 1.0f);
+        std::vector<migraphx::half> hv(vals.begin(), vals.end());
+        migraphx::argument arg{xs};
+        std::memcpy(arg.data(), hv.data(), hv.size() * sizeof(migraphx::half));
+        t.params[name] = arg;
+    }
+    // fp32 accumulation on the tensor cores against the reference's double, every fp16 result truncated
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
+    return t;
+}
+
+// dot on fp16 operands: a constant [K,N] weight (re-laid out once) and a non-constant one.
+test_case dot_f16(std::size_t bt, std::size_t m, std::size_t n, std::size_t k, bool const_b, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const shape as{shape::half_type, bt > 1 ? std::vector<std::size_t>{bt, m, k} : std::vector<std::size_t>{m, k}};
+    const shape bs{shape::half_type, bt > 1 ? std::vector<std::size_t>{bt, k, n} : std::vector<std::size_t>{k, n}};
+    auto fill = [&](const shape& s, float sd) {
+        auto vals = rand_normal(g, s.elements(), sd);
+        std::vector<migraphx::half> hv(vals.begin(), vals.end());
+        migraphx::argument arg{s};
+        std::memcpy(arg.data(), hv.data(), hv.size() * sizeof(migraphx::half));
+        return arg;
+    };
+    auto a = mm->add_parameter("a", as);
+    migraphx::instruction_ref bi;
+    if(const_b)
+    {
+        auto barg = fill(bs, 0.5f);
+        bi        = mm->add_literal(migraphx::literal{bs, barg.data()});
+    }
+    else
+    {
+        bi            = mm->add_parameter("b", bs);
+        t.params["b"] = fill(bs, 0.5f);
+    }
+    mm->add_return({mm->add_instruction(migraphx::make_op("dot"), a, bi)});
+    t.params["a"] = fill(as, 1.0f);
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
+    return t;
+}
+
 // quant_dot alone on int8 parameters (batched, non-constant right operand).
 test_case raw_quant_dot(unsigned seed)
 {
@@ -502,6 +576,9 @@ std::map<std::string, std::function<test_case()>> cases()
         {"softmax_f32", [] { return softmax_rows(shape::float_type, 2, 4, 56, 200, 14); }},
         {"softmax_f16", [] { return softmax_rows(shape::half_type, 1, 3, 40, 1500, 15); }},
         {"softmax_f32_long", [] { return softmax_rows(shape::float_type, 1, 1, 6, 9000, 16); }},
+        {"attention_f16", [] { return attention_f16(2, 4, 64, 32, 17); }},
+        {"dot_f16_const", [] { return dot_f16(1, 200, 136, 264, true, 18); }},
+        {"dot_f16_batched", [] { return dot_f16(3, 72, 50, 96, false, 19); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
         {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
         {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},

@@ -181,6 +181,7 @@ instruction_ref add_float_literal(module& m, const std::vector<float>& v)
 }
 
 // A constant 8-bit matrix [.., K, N] (any strides) as a standard [.., N, K] literal.
+// [.., K, N] constant -> [.., N, K] literal (8- or 16-bit elements)
 instruction_ref add_transposed_8bit_literal(module& m, instruction_ref b)
 {
     argument a    = b->eval();
@@ -191,7 +192,8 @@ instruction_ref add_transposed_8bit_literal(module& m, instruction_ref b)
     std::size_t batch = 1;
     for(std::size_t i = 0; i + 2 < nd; ++i)
         batch *= lens[i];
-    std::vector<char> out(batch * n * k);
+    const std::size_t es = s.type_size();
+    std::vector<char> out(batch * n * k * es);
     const char* src = a.data();
     std::vector<std::size_t> idx(nd, 0);
     for(std::size_t bi = 0; bi < batch; ++bi)
@@ -208,7 +210,7 @@ instruction_ref add_transposed_8bit_literal(module& m, instruction_ref b)
             for(std::size_t nn = 0; nn < n; ++nn)
             {
                 idx[nd - 1] = nn;
-                out[(bi * n + nn) * k + kk] = src[s.index(idx)];
+                std::memcpy(&out[((bi * n + nn) * k + kk) * es], src + s.index(idx) * es, es);
             }
         }
     }
@@ -606,7 +608,8 @@ struct lowerer
             {"ceil", MGX_PW_CEIL},     {"round", MGX_PW_ROUND},     {"nearbyint", MGX_PW_NEARBYINT},
             {"convert", MGX_PW_CONVERT}, {"where", MGX_PW_WHERE},   {"clip", MGX_PW_CLIP},
             {"equal", MGX_PW_EQUAL},   {"greater", MGX_PW_GREATER}, {"less", MGX_PW_LESS},
-            {"leaky_relu", MGX_PW_LEAKY_RELU}, {"identity", MGX_PW_IDENTITY}};
+            {"leaky_relu", MGX_PW_LEAKY_RELU}, {"identity", MGX_PW_IDENTITY},
+            {"contiguous", MGX_PW_IDENTITY}};
         auto it = table.find(ins->name());
         if(it == table.end())
             return false;
@@ -671,6 +674,95 @@ struct lowerer
         return true;
     }
 
+    // packed copy of a strided view (what op::contiguous computes), made by the element-wise kernel
+    instruction_ref standard_copy(instruction_ref pos, instruction_ref x)
+    {
+        op_pointwise op;
+        op.ops   = {MGX_PW_IDENTITY};
+        op.types = {static_cast<int>(x->get_shape().type())};
+        op.srcs  = {0, 0, 0};
+        op.imms  = {0.0f};
+        auto buf = insert_allocation(m, pos, x->get_shape().as_standard());
+        auto c   = m.insert_instruction(pos, op, x, buf);
+        consume(c);
+        return c;
+    }
+
+    // reshape copies its input in logical order (src/include/migraphx/op/reshape.hpp:207-217):
+    // a view of the packed tensor
+    void lower_reshape(instruction_ref ins)
+    {
+        if(ins->inputs().size() != 1)
+            unsupported(ins, "only the one-operand form is supported");
+        auto x = ins->inputs()[0];
+        if(not x->get_shape().standard())
+            x = standard_copy(ins, x);
+        m.replace_instruction(ins, make_op("reshape_lazy", {{"dims", ins->get_shape().lens()}}), x);
+    }
+
+    // dot on fp16 operands (attention's Q.K^T and P.V, un-quantised linears): the tiled GEMM with
+    // kind::f16 operands and fp32 accumulation, result truncated to fp16 (the reference's gemm
+    // accumulates in double, src/include/migraphx/gemm.hpp).
+    bool lower_half_dot(instruction_ref ins)
+    {
+        if(ins->inputs().size() != 2)
+            return false;
+        auto a = ins->inputs()[0];
+        auto b = ins->inputs()[1];
+        const auto& as = a->get_shape();
+        const auto& bs = b->get_shape();
+        if(as.type() != shape::half_type or bs.type() != shape::half_type or as.ndim() < 2 or
+           bs.ndim() != as.ndim())
+            return false;
+        const auto nd = as.ndim();
+        const auto k  = as.lens()[nd - 1];
+        for(std::size_t j = 0; j + 2 < nd; ++j)
+            if(as.lens()[j] != bs.lens()[j])
+                return false;
+        // rows of 16-byte multiples (the tensor maps' stride rule)
+        if(k % 8 != 0)
+            unsupported(ins, "the inner dimension of an fp16 dot must be a multiple of 8");
+        // a transposed / sliced left operand (attention heads) is packed first
+        const bool a_ok = as.strides()[nd - 1] == 1 and as.strides()[nd - 2] % 8 == 0 and
+                          (nd == 2 or as.standard());
+        if(not a_ok)
+            a = standard_copy(ins, a);
+        op_qgemm op;
+        op.out_type = static_cast<int>(shape::half_type);
+        std::vector<instruction_ref> args = {a, b};
+        instruction_ref workspace         = m.end();
+        bool transposed_view = bs.strides()[nd - 1] != 1 and bs.strides()[nd - 2] == 1 and
+                               bs.strides()[nd - 1] % 8 == 0;
+        // every batch entry evenly spaced, like a standard tensor's
+        for(std::size_t j = 0; j + 3 < nd; ++j)
+            if(bs.strides()[j] != bs.strides()[j + 1] * bs.lens()[j + 1])
+                transposed_view = false;
+        if(nd > 2 and bs.strides()[nd - 3] % 8 != 0)
+            transposed_view = false;
+        if(b->can_eval() and k % 8 == 0)
+        {
+            args[1] = add_transposed_8bit_literal(m, b);
+            op.b_nk = true;
+        }
+        else if(transposed_view)
+        {
+        }
+        else
+        {
+            if(not bs.standard())
+                args[1] = standard_copy(ins, b);
+            const std::size_t kp = (k + 7) / 8 * 8;
+            const std::size_t ws = bs.elements() / k * kp * 2;
+            workspace            = insert_allocation(m, ins, shape{shape::int8_type, {ws}});
+            op.has_workspace     = true;
+        }
+        if(workspace != m.end())
+            args.push_back(workspace);
+        args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
+        consume(m.replace_instruction(ins, op, args));
+        return true;
+    }
+
     template <class Op>
     void lower_int4(instruction_ref ins, Op op)
     {
@@ -712,9 +804,9 @@ struct lowerer
                 lower_quant_dot(ins);
             else if(ins->name() == "dot")
             {
-                if(not lower_w4a16(ins))
-                    unsupported(ins, "only the weight-only int4 form "
-                                     "dot(A, transpose(dequantizelinear(unpack_int4(W)))) is supported");
+                if(not lower_w4a16(ins) and not lower_half_dot(ins))
+                    unsupported(ins, "only fp16 operands and the weight-only int4 form "
+                                     "dot(A, transpose(dequantizelinear(unpack_int4(W)))) are supported");
             }
         }
         for(auto ins : order)
@@ -739,6 +831,8 @@ struct lowerer
                 lower_int4(ins, op_unpack_int4{});
             else if(name == "pack_int4")
                 lower_int4(ins, op_pack_int4{});
+            else if(name == "reshape")
+                lower_reshape(ins);
             else if(lower_elementwise_op(ins))
                 continue;
             else if(lower_row_op(ins))
@@ -977,13 +1071,14 @@ void insert_graph_ops::apply(module& m) const
     auto last = std::prev(m.end());
     if(nlaunch == 0 or last->name() != "@return" or last->inputs().empty())
         return;
-    // graph_begin must see every parameter buffer: parameters move in front of it
+    // graph_begin must see every parameter buffer: parameters (which views ahead of the first
+    // launch may already use) move to the front of the module
     std::vector<instruction_ref> params;
     for(auto ins : iterator_for(m))
         if(ins->name() == "@param")
             params.push_back(ins);
     for(auto p : params)
-        m.move_instruction(p, first);
+        m.move_instruction(p, m.begin());
     m.insert_instruction(first, op_graph_begin{}, params);
     // graph_end passes the first result through, in front of the final synchronisation
     auto res = last->inputs().front();

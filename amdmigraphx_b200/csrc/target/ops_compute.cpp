@@ -187,6 +187,8 @@ shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
         MIGRAPHX_THROW("cuda::qgemm: operands must have the same rank >= 2");
     if(a.type() != b.type())
         MIGRAPHX_THROW("cuda::qgemm: operand types differ");
+    if(a.type() == shape::half_type and (scale_mode != MGX_SCALE_NONE or q_type != 0))
+        MIGRAPHX_THROW("cuda::qgemm: an fp16 dot takes no scale and no fused quantizelinear");
     const auto k  = a.lens().back();
     const auto kb = b_nk ? b.lens().back() : b.lens()[b.ndim() - 2];
     if(k != kb)
@@ -240,7 +242,15 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     d.lda = static_cast<int64_t>(as.strides()[nd - 2]);
     d.ldb = static_cast<int64_t>(bs.strides()[nd - 2]);
     d.ldd = d.N;
-    if(bs.strides()[nd - 1] != 1)
+    // a [K,N] operand that is the transpose view of a K-contiguous [N,K] tensor (Q . K^T of
+    // attention) is already in the layout the kernel reads
+    bool view_nk = false;
+    if(not b_nk and bs.strides()[nd - 1] != 1 and bs.strides()[nd - 2] == 1)
+    {
+        view_nk = true;
+        d.ldb   = static_cast<int64_t>(bs.strides()[nd - 1]);
+    }
+    else if(bs.strides()[nd - 1] != 1)
         MIGRAPHX_THROW("cuda::qgemm: B must be contiguous along its last axis");
     bool b_shared = true; // B is the same matrix for every batch entry (broadcast view)
     for(std::size_t j = 0; j + 2 < nd; ++j)
@@ -264,7 +274,7 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     d.batch      = batch;
     d.ab_type    = mgx_type(as.type());
     d.out_type   = mgx_type(static_cast<shape::type_t>(out_type));
-    d.b_layout   = b_nk ? MGX_B_NK : MGX_B_KN;
+    d.b_layout   = (b_nk or view_nk) ? MGX_B_NK : MGX_B_KN;
     d.scale_mode = scale_mode;
     d.act        = act;
     mgx_qgemm_qout qo{};

@@ -199,6 +199,9 @@ MGX_API int mgx_cuda_pack_int4(const void* in, void* out, int type, int64_t rows
  *   b_layout = MGX_B_KN : [K,N], row stride ldb, N contiguous (MIGraphX default)
  *   b_layout = MGX_B_NK : [N,K], row stride ldb, K contiguous (a transpose view)
  * ab_type MGX_I8 accumulates exactly in int32; MGX_FP8_E4M3FN accumulates in fp32.
+ * ab_type MGX_F16 is op::dot on fp16 operands (attention, un-quantised linears): fp32
+ * accumulation, out_type MGX_F16 (truncating conversion) or MGX_F32, scale_mode NONE as a rule,
+ * no fused quantizelinear; lda, ldb and the batch strides are multiples of 8 elements.
  * Epilogue, in this order (it is the order of the fused pointwise module
  * `dequantizelinear -> add(bias) -> act -> add(residual)`):
  *   v = acc                                   (int32 or fp32)
@@ -230,7 +233,7 @@ typedef struct mgx_qgemm_desc
     int64_t batch;
     int64_t lda, ldb, ldd;                 /* row strides, elements          */
     int64_t stride_a, stride_b, stride_d;  /* batch strides, elements        */
-    int32_t ab_type;                       /* MGX_I8 | MGX_FP8_E4M3FN        */
+    int32_t ab_type;                       /* MGX_I8 | MGX_FP8_E4M3FN | MGX_F16 */
     int32_t out_type;                      /* MGX_I32 | MGX_F32 | MGX_F16    */
     int32_t b_layout;                      /* mgx_b_layout                   */
     int32_t scale_mode;                    /* mgx_scale_mode                 */
