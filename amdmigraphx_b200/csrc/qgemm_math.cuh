@@ -13,13 +13,19 @@ namespace mgx {
 __device__ __forceinline__ float fast_erf(float x)
 {
     const float ax = fabsf(x);
-    const float t  = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+    // the reciprocal's operand is >= 1 and an exponential below 2^-126 may flush to zero (the
+    // result is then exactly 1, as it rounds to anyway): the flush-to-zero forms are single
+    // instructions, the default forms carry extra range handling
+    float t;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, ax, 1.0f)));
     float y        = fmaf(1.061405429f, t, -1.453152027f);
     y              = fmaf(y, t, 1.421413741f);
     y              = fmaf(y, t, -0.284496736f);
     y              = fmaf(y, t, 0.254829592f);
     y *= t;
-    const float r = fmaf(-y, __expf(-ax * ax), 1.0f);
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(ax * ax * -1.4426950408889634f));
+    const float r = fmaf(-y, e, 1.0f);
     return copysignf(r, x);
 }
 
