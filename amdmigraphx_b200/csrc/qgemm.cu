@@ -53,6 +53,7 @@ struct qgemm_params
     int vec_sb; // scale / bias vectors are 16-byte aligned (float4 loads allowed)
     int fast;   // the whole problem takes the epilogue's check-free path (see epi_store_chunk_fast)
     int acc24;  // every accumulator is below 2^24 in magnitude (int8 operands, K < 1024)
+    int q_mask; // the fused quantizelinear may take the mantissa-cut value (see launch_qgemm)
     int vec_io; // D (and residual) rows can be accessed with 16-byte (fp32/int32) / 8-byte (fp16) vectors
 };
 
@@ -302,6 +303,7 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     const int64_t dstep = 8 * p.ldd, qstep = 8 * p.ldq;
     const bool has_res = p.residual != nullptr, has_q = p.Dq != nullptr, wr = p.write_d != 0;
     const bool acc24   = p.acc24 != 0;
+    const bool q_mask  = has_q and p.q_mask != 0;
     // saturation before rounding: bounds are integers, so round-to-nearest stays inside
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
     const int q_bias = static_cast<int>(p.q_zp) - 0x4B400000;
@@ -363,8 +365,18 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
         }
         if constexpr(std::is_same<OutT, __half>::value)
         {
-            if(has_q)
-                truncate4_to_half_precision(v); // quantizelinear sees the stored half
+            // quantizelinear sees the stored half
+            if(q_mask)
+            {
+                // cutting the mantissa is enough: values in the half subnormal range quantise to
+                // zero either way, values beyond the half range saturate either way, and the
+                // store below truncates by itself
+#pragma unroll
+                for(int j = 0; j < 4; ++j)
+                    v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
+            }
+            else if(has_q)
+                truncate4_to_half_precision(v);
         }
         if(wr)
         {
@@ -811,6 +823,10 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
                      : 0;
     }
     p.acc24      = (IS_INT and d.K < 1024) ? 1 : 0; // |a b| <= 2^14 for int8 operands
+    // |v| < 2^-14 (half subnormals) divided by a scale >= 2^-12 stays below 1/4: quantises to zero
+    // whatever its low bits; no zero point may shift the rounding boundary
+    p.q_mask     = (qo.Dq != nullptr and qo.fp8 == 0 and qo.scale >= 0.000244140625f and
+                    qo.zp == static_cast<float>(static_cast<int>(qo.zp))) ? 1 : 0;
     auto kernel  = qgemm_kernel<BN, IS_INT, OutT, F16>;
     int rc2 = ensure_smem_optin(reinterpret_cast<const void*>(kernel), S::total);
     if(rc2 != MGX_OK)
