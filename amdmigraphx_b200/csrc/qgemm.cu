@@ -15,6 +15,7 @@
 // quarter warp_id % 4 and a quarter of the tile's columns).  Two accumulator buffers of BN columns let the epilogue
 // of tile i overlap the main loop of tile i+1.
 #include "common.cuh"
+#include <cstdlib>
 #include "ptx.cuh"
 #include "qgemm_math.cuh"
 #include <cuda_fp16.h>
@@ -876,6 +877,14 @@ static int dispatch_out(const mgx_qgemm_desc& d, const void* A, const void* B, v
 // The epilogue costs about 12 cycles per output column of the tile.
 static int pick_bn(const mgx_qgemm_desc& d)
 {
+    // tuning knob: MGX_CUDA_QGEMM_BN = 64 | 128 | 256 forces the tile width
+    static const int forced = [] {
+        const char* e = std::getenv("MGX_CUDA_QGEMM_BN");
+        const int v   = e != nullptr ? std::atoi(e) : 0;
+        return (v == 64 or v == 128 or v == 256) ? v : 0;
+    }();
+    if(forced != 0)
+        return forced;
     const int64_t sms = device_sm_count();
     const int64_t tm  = (d.M + BM - 1) / BM;
     const int64_t kb  = (d.K * (d.ab_type == MGX_F16 ? 2 : 1) + BK - 1) / BK;
