@@ -75,3 +75,45 @@ def test_quantizelinear_between_two_linears_is_fused_into_the_first():
     assert out.count("cuda::quantizelinear") == 1  # only the one on the program input is left
     out = _passes("mlp_two_outputs")
     assert "cuda::second_output" in out and "write_d=1" in out
+
+
+def test_layernorm_lowers_to_reductions_and_fused_pointwise():
+    out = _passes("layernorm_f32")
+    # two reduce_mean of the decomposition plus the max / min / sum the case also returns
+    assert out.count("cuda::reduce[mode=1]") == 2
+    for mode in (0, 2, 3):
+        assert "cuda::reduce[mode=%d]" % mode in out
+    # scale + shift + normalise end up in one launch
+    assert any(l.count(",") > 8 and "cuda::pointwise[ops={2, 2, 0}" in l for l in out.splitlines())
+    assert "reduce_mean" not in out
+
+
+def test_attention_lowers_to_fp16_gemms_softmax_and_packed_copies():
+    out = _passes("attention_f16")
+    gemms = [l for l in out.splitlines() if "cuda::qgemm" in l]
+    assert len(gemms) == 2 and all("scale_mode=0" in g and "out_type=1" in g for g in gemms)
+    assert out.count("cuda::softmax") == 1
+    # reshape of the packed parameters is a view; the head transposes are copied once
+    assert "reshape_lazy" in out and " reshape[" not in out and "contiguous" not in out
+    assert out.count("cuda::pointwise[ops={32}") >= 3
+    # the parameters precede the views that read them, and the graph bracket sees them all
+    assert "cuda::graph_begin(main:#output_0,v,k,q)" in out
+
+
+def test_constant_fp16_weight_is_relaid_out_once():
+    out = _passes("dot_f16_const")
+    line = [l for l in out.splitlines() if "cuda::qgemm" in l][0]
+    assert "b_nk=1" in line and "has_workspace=0" in line
+    assert "half_type, {136, 264}" in out  # the [K,N] literal became [N,K]
+    out = _passes("dot_f16_batched")
+    line = [l for l in out.splitlines() if "cuda::qgemm" in l][0]
+    assert "b_nk=0" in line and "has_workspace=1" in line
+
+
+def test_bert_layer_compiles_into_one_graph():
+    out = _passes("bert_layer_int8")
+    assert out.count("cuda::qgemm") == 8  # six QDQ linears, Q.K^T, P.V
+    assert out.count("cuda::graph_begin") == 1 and out.count("cuda::graph_end") == 1
+    # FFN1: GELU and the quantizelinear feeding FFN2 run in its epilogue
+    assert any("act=2" in l and "q_type=5" in l and "write_d=0" in l for l in out.splitlines())
+    assert "cuda::softmax" in out and out.count("cuda::reduce[mode=1]") == 4
