@@ -309,7 +309,7 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
     const int q_bias = static_cast<int>(p.q_zp) - 0x4B400000;
     const uint8_t* box = e.box + rsub * 64;
-#pragma unroll 1
+#pragma unroll 2
     for(int it = 0; it < 4; ++it)
     {
         const int r   = it * 8 + rsub;
@@ -416,7 +416,7 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
 // tile's columns.  Per 16-column chunk: tcgen05.ld (one row per thread) -> swizzled shared
 // memory -> read back with 4 lanes per 64-byte row segment -> dequantizelinear / bias /
 // activation / residual -> coalesced global stores.
-template <int BN, bool IS_INT, class OutT, int ACT>
+template <int BN, bool IS_INT, class OutT, int ACT, bool FAST>
 __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* epi_base,
                                               uint64_t* accf_bar, uint64_t* acce_bar,
                                               volatile uint32_t* abort_flag, uint32_t tmem_base,
@@ -456,7 +456,7 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
         // code would be bound by instruction fetch.
         auto load_sb = [&](int ch, float4& sc, float4& bi) {
             sc = make_float4(tensor_scale, tensor_scale, tensor_scale, tensor_scale);
-            bi = p.fast ? make_float4(-0.f, -0.f, -0.f, -0.f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            bi = FAST ? make_float4(-0.f, -0.f, -0.f, -0.f) : make_float4(0.f, 0.f, 0.f, 0.f);
             if constexpr(not std::is_same<OutT, int32_t>::value)
             {
                 const int64_t c4 = col0 + ch * EPI_COLS + (lane & 3) * 4;
@@ -533,9 +533,7 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
                     *reinterpret_cast<uint4*>(my_row + ((q ^ my_swz) * 16)) =
                         make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
                 __syncwarp();
-                if constexpr(std::is_same<OutT, int32_t>::value)
-                    epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
-                else if(p.fast)
+                if constexpr(FAST and not std::is_same<OutT, int32_t>::value)
                     epi_store_chunk_fast<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
                 else
                     epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
@@ -699,9 +697,15 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         // ---------------------------------------------------- epilogue
         // (reads residual / scale / bias and writes D: only after the previous kernel is done)
         grid_dependency_wait();
-#define MGX_EPILOGUE(ACT)                                                                      \
-    epilogue_role<BN, IS_INT, OutT, ACT>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base, \
-                                         warp, lane, first_tile, tile_step, tiles_mn)
+        // the check-free variant is chosen once per launch: the tile loop a warp runs holds
+        // only the store path it takes
+#define MGX_EPILOGUE(ACT)                                                                                   \
+    if(p.fast)                                                                                              \
+        epilogue_role<BN, IS_INT, OutT, ACT, true>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base,  \
+                                                   warp, lane, first_tile, tile_step, tiles_mn);            \
+    else                                                                                                    \
+        epilogue_role<BN, IS_INT, OutT, ACT, false>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base, \
+                                                    warp, lane, first_tile, tile_step, tiles_mn)
         switch(std::is_same<OutT, int32_t>::value ? MGX_ACT_NONE : p.act)
         {
         case MGX_ACT_RELU: MGX_EPILOGUE(MGX_ACT_RELU); break;
