@@ -271,7 +271,15 @@ __device__ __forceinline__ float half_rz_in_range(float v)
 __device__ __forceinline__ void truncate4_to_half_precision(float (&v)[4])
 {
     const float hi = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    if(hi < 65536.0f)
+    const float lo = fminf(fminf(fabsf(v[0]), fabsf(v[1])), fminf(fabsf(v[2]), fabsf(v[3])));
+    if(hi < 65536.0f and lo >= 6.103515625e-5f)
+    {
+        // all four are normal halves (the common case): cut the mantissa
+#pragma unroll
+        for(int j = 0; j < 4; ++j)
+            v[j] = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
+    }
+    else if(hi < 65536.0f)
     {
 #pragma unroll
         for(int j = 0; j < 4; ++j)
