@@ -6,6 +6,7 @@ points from C++.  There is no fallback: if the library is missing, loading raise
 """
 import ctypes
 import os
+import numpy as np
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 KERNEL_LIB_PATH = os.path.join(_PKG, "lib", "libmgx_cuda_kernels.so")
@@ -24,7 +25,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
+    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -367,6 +368,48 @@ def softmax(x):
                                ctypes.c_void_p(out.data_ptr()), ctypes.c_int64(out.stride(0)),
                                ctypes.c_int64(x.shape[0]), ctypes.c_int64(x.shape[1]), _stream()),
           "mgx_cuda_softmax")
+    return out
+
+
+def gather(data, indices, axis):
+    """op::gather on a packed tensor; indices int32 / int64 of any shape."""
+    import torch
+    lib = load()
+    assert data.is_contiguous() and indices.is_contiguous()
+    axis = axis % data.dim()
+    outer = int(np.prod(data.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(data.shape[axis + 1:], dtype=np.int64)) * data.element_size()
+    out = torch.empty(tuple(data.shape[:axis]) + tuple(indices.shape) + tuple(data.shape[axis + 1:]),
+                      dtype=data.dtype, device=data.device)
+    code = {torch.int32: I32, torch.int64: 6}[indices.dtype]
+    lib.mgx_cuda_gather.restype = ctypes.c_int
+    check(lib.mgx_cuda_gather(ctypes.c_void_p(data.data_ptr()), ctypes.c_int64(outer),
+                              ctypes.c_int64(data.shape[axis]), ctypes.c_int64(inner),
+                              ctypes.c_void_p(indices.data_ptr()), code, ctypes.c_int64(indices.numel()),
+                              ctypes.c_void_p(out.data_ptr()), _stream()), "mgx_cuda_gather")
+    return out
+
+
+def concat(tensors, axis):
+    """op::concat of packed tensors along `axis`: one row copy per input."""
+    import torch
+    lib = load()
+    axis = axis % tensors[0].dim()
+    lens = list(tensors[0].shape)
+    lens[axis] = sum(t.shape[axis] for t in tensors)
+    out = torch.empty(tuple(lens), dtype=tensors[0].dtype, device=tensors[0].device)
+    es = out.element_size()
+    outer = int(np.prod(lens[:axis], dtype=np.int64))
+    inner = int(np.prod(lens[axis + 1:], dtype=np.int64)) * es
+    lib.mgx_cuda_copy_rows.restype = ctypes.c_int
+    off = 0
+    for t in tensors:
+        assert t.is_contiguous()
+        rb = t.shape[axis] * inner
+        check(lib.mgx_cuda_copy_rows(ctypes.c_void_p(t.data_ptr()), ctypes.c_int64(rb),
+                                     ctypes.c_void_p(out.data_ptr() + off), ctypes.c_int64(lens[axis] * inner),
+                                     ctypes.c_int64(outer), ctypes.c_int64(rb), _stream()), "mgx_cuda_copy_rows")
+        off += rb
     return out
 
 

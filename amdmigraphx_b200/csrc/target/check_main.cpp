@@ -625,6 +625,54 @@ test_case bert_layer_int8(std::size_t b, std::size_t sq, std::size_t h, std::siz
     return t;
 }
 
+// Token embedding, rotary position embedding (rotate-half form: slice, neg, concat) and the
+// KV-cache append of a decoder layer: gather, strided views, element-wise fp16 and concat.
+test_case embed_rope_f16(std::size_t b, std::size_t sq, std::size_t past, std::size_t hid, std::size_t vocab, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    auto half_lit = [&](const std::vector<float>& v, const std::vector<std::size_t>& lens) {
+        std::vector<migraphx::half> h(v.begin(), v.end());
+        return mm->add_literal(migraphx::literal{shape{shape::half_type, lens}, h});
+    };
+    auto ids   = mm->add_parameter("ids", shape{shape::int64_type, {b, sq}});
+    auto cache = mm->add_parameter("cache", shape{shape::half_type, {b, past, hid}});
+    auto table = half_lit(rand_normal(g, vocab * hid, 1.0f), {vocab, hid});
+    std::vector<float> cv(sq * hid), sv(sq * hid);
+    for(std::size_t p = 0; p < sq; ++p)
+        for(std::size_t i = 0; i < hid; ++i)
+        {
+            const double ang = static_cast<double>(past + p) * std::pow(10000.0, -2.0 * static_cast<double>(i % (hid / 2)) / hid);
+            cv[p * hid + i]  = static_cast<float>(std::cos(ang));
+            sv[p * hid + i]  = static_cast<float>(std::sin(ang));
+        }
+    auto cosl = half_lit(cv, {sq, hid});
+    auto sinl = half_lit(sv, {sq, hid});
+    auto x    = mm->add_instruction(migraphx::make_op("gather", {{"axis", 0}}), table, ids);
+    const std::vector<std::size_t> lens = {b, sq, hid};
+    auto x1   = mm->add_instruction(migraphx::make_op("slice", {{"axes", {2}}, {"starts", {0}}, {"ends", {hid / 2}}}), x);
+    auto x2   = mm->add_instruction(migraphx::make_op("slice", {{"axes", {2}}, {"starts", {hid / 2}}, {"ends", {hid}}}), x);
+    auto rot  = mm->add_instruction(migraphx::make_op("concat", {{"axis", 2}}), mm->add_instruction(migraphx::make_op("neg"), x2), x1);
+    auto xc   = mm->add_instruction(migraphx::make_op("mul"), x, mbcast(mm, cosl, lens));
+    auto rs   = mm->add_instruction(migraphx::make_op("mul"), rot, mbcast(mm, sinl, lens));
+    auto y    = mm->add_instruction(migraphx::make_op("add"), xc, rs);
+    auto kv   = mm->add_instruction(migraphx::make_op("concat", {{"axis", 1}}), cache, y);
+    mm->add_return({kv, y});
+    std::uniform_int_distribution<int64_t> pick(-static_cast<int64_t>(vocab), static_cast<int64_t>(vocab) - 1);
+    migraphx::argument ia{shape{shape::int64_type, {b, sq}}};
+    for(std::size_t i = 0; i < b * sq; ++i)
+        reinterpret_cast<int64_t*>(ia.data())[i] = pick(g); // negative indices count from the end
+    t.params["ids"] = ia;
+    auto cvv = rand_normal(g, b * past * hid, 1.0f);
+    std::vector<migraphx::half> ch(cvv.begin(), cvv.end());
+    migraphx::argument ca{shape{shape::half_type, {b, past, hid}}};
+    std::memcpy(ca.data(), ch.data(), ch.size() * sizeof(migraphx::half));
+    t.params["cache"] = ca;
+    t.exact = true; // exactly rounded fp16 operators and byte moves
+    return t;
+}
+
 // quant_dot alone on int8 parameters (batched, non-constant right operand).
 test_case raw_quant_dot(unsigned seed)
 {
@@ -671,6 +719,7 @@ std::map<std::string, std::function<test_case()>> cases()
         {"dot_f16_const", [] { return dot_f16(1, 200, 136, 264, true, 18); }},
         {"dot_f16_batched", [] { return dot_f16(3, 72, 50, 96, false, 19); }},
         {"bert_layer_int8", [] { return bert_layer_int8(2, 64, 4, 64, 1024, 20); }},
+        {"embed_rope_f16", [] { return embed_rope_f16(2, 24, 40, 128, 500, 21); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},
         {"mlp_fused_q", [] { return qdq_mlp(96, 256, 320, 128, false, 9); }},
         {"mlp_two_outputs", [] { return qdq_mlp(96, 256, 320, 128, true, 10); }},

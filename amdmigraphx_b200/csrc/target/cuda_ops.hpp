@@ -304,6 +304,38 @@ struct op_softmax
     std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
 };
 
+// gather along `axis` of a standard tensor (src/include/migraphx/op/gather.hpp).
+// Inputs: data, indices (int32 / int64), out.
+struct op_gather
+{
+    int64_t axis = 0;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.axis, "axis"));
+    }
+    std::string name() const { return "cuda::gather"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
+};
+
+// concat of standard tensors along `axis` (src/include/migraphx/op/concat.hpp): one strided
+// row copy per input.  Inputs: the tensors, out.
+struct op_concat
+{
+    int64_t axis = 0;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.axis, "axis"));
+    }
+    std::string name() const { return "cuda::concat"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
+};
+
 // Weight-only int4 linear (unpack_int4 + dequantizelinear + transpose + dot fused).
 // Inputs: A fp16 [M,K], packed weights uint8 [N,K/2], scales fp16 [N,K/group],
 // [zero points uint8 [N,K/group]], [workspace], out fp16 [M,N].

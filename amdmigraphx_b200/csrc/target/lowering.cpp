@@ -632,6 +632,35 @@ struct lowerer
         return true;
     }
 
+    // gather and concat: byte movers on packed tensors (strided operands are packed first)
+    bool lower_mover(instruction_ref ins)
+    {
+        const auto name = ins->name();
+        if(name != "gather" and name != "concat")
+            return false;
+        auto v        = ins->get_operator().to_value();
+        auto axis     = v.at("axis").to<int64_t>();
+        const auto nd = static_cast<int64_t>(ins->inputs()[0]->get_shape().ndim());
+        if(axis < 0)
+            axis += nd;
+        auto args = ins->inputs();
+        for(auto& a : args)
+            if(not a->get_shape().standard())
+                a = standard_copy(ins, a);
+        if(name == "gather")
+        {
+            const auto it = args[1]->get_shape().type();
+            if(it != shape::int32_type and it != shape::int64_type)
+                unsupported(ins, "indices must be int32 or int64");
+        }
+        args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
+        if(name == "gather")
+            consume(m.replace_instruction(ins, op_gather{axis}, args));
+        else
+            consume(m.replace_instruction(ins, op_concat{axis}, args));
+        return true;
+    }
+
     // reduce_* and softmax over the innermost axis
     bool lower_row_op(instruction_ref ins)
     {
@@ -836,6 +865,8 @@ struct lowerer
             else if(lower_elementwise_op(ins))
                 continue;
             else if(lower_row_op(ins))
+                continue;
+            else if(lower_mover(ins))
                 continue;
             else
                 unsupported(ins, "no kernel");
@@ -1050,7 +1081,8 @@ void insert_graph_ops::apply(module& m) const
     auto launches = [](const std::string& n) {
         return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
                n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or
-               n == "cuda::copy" or n == "cuda::pointwise" or n == "cuda::reduce" or n == "cuda::softmax";
+               n == "cuda::copy" or n == "cuda::pointwise" or n == "cuda::reduce" or n == "cuda::softmax" or
+               n == "cuda::gather" or n == "cuda::concat";
     };
     instruction_ref first = m.end();
     std::size_t nlaunch   = 0;

@@ -486,6 +486,87 @@ argument op_softmax::compute(context& ctx, const shape&, const std::vector<argum
     return out;
 }
 
+// ------------------------------------------------------------------ gather, concat
+shape op_gather::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(3);
+    if(not inputs[0].standard() or not inputs[1].standard() or not inputs[2].standard())
+        MIGRAPHX_THROW("cuda::gather: operands must be standard tensors");
+    if(inputs[1].type() != shape::int32_type and inputs[1].type() != shape::int64_type)
+        MIGRAPHX_THROW("cuda::gather: indices must be int32 or int64");
+    if(axis < 0 or axis >= static_cast<int64_t>(inputs[0].ndim()) or inputs[2].type() != inputs[0].type())
+        MIGRAPHX_THROW("cuda::gather: bad axis or output type");
+    return inputs[2];
+}
+
+argument op_gather::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& ds = args[0].get_shape();
+    int64_t outer = 1, inner = static_cast<int64_t>(ds.type_size());
+    for(int64_t i = 0; i < axis; ++i)
+        outer *= static_cast<int64_t>(ds.lens()[i]);
+    for(std::size_t i = axis + 1; i < ds.ndim(); ++i)
+        inner *= static_cast<int64_t>(ds.lens()[i]);
+    const auto& is = args[1].get_shape();
+    check_mgx(mgx_cuda_gather(args[0].data(), outer, static_cast<int64_t>(ds.lens()[axis]), inner, args[1].data(),
+                              is.type() == shape::int32_type ? MGX_I32 : MGX_I64,
+                              static_cast<int64_t>(is.elements()), out.data(), ctx.stream()),
+              "mgx_cuda_gather");
+    return out;
+}
+
+shape op_concat::compute_shape(const std::vector<shape>& inputs) const
+{
+    if(inputs.size() < 2)
+        MIGRAPHX_THROW("cuda::concat: needs at least one tensor and the output buffer");
+    const auto& out = inputs.back();
+    if(axis < 0 or axis >= static_cast<int64_t>(out.ndim()) or not out.standard())
+        MIGRAPHX_THROW("cuda::concat: bad axis or output layout");
+    std::size_t along = 0;
+    for(std::size_t i = 0; i + 1 < inputs.size(); ++i)
+    {
+        const auto& s = inputs[i];
+        if(not s.standard() or s.type() != out.type() or s.ndim() != out.ndim())
+            MIGRAPHX_THROW("cuda::concat: inputs must be standard tensors of the output's type and rank");
+        for(std::size_t d = 0; d < s.ndim(); ++d)
+            if(static_cast<int64_t>(d) != axis and s.lens()[d] != out.lens()[d])
+                MIGRAPHX_THROW("cuda::concat: dimensions other than the axis must match");
+        along += s.lens()[axis];
+    }
+    if(along != out.lens()[axis])
+        MIGRAPHX_THROW("cuda::concat: the inputs do not fill the output");
+    return out;
+}
+
+argument op_concat::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& os = out.get_shape();
+    int64_t outer = 1, inner = static_cast<int64_t>(os.type_size());
+    for(int64_t i = 0; i < axis; ++i)
+        outer *= static_cast<int64_t>(os.lens()[i]);
+    for(std::size_t i = axis + 1; i < os.ndim(); ++i)
+        inner *= static_cast<int64_t>(os.lens()[i]);
+    const int64_t dst_pitch = static_cast<int64_t>(os.lens()[axis]) * inner;
+    int64_t off             = 0;
+    for(std::size_t i = 0; i + 1 < args.size(); ++i)
+    {
+        const int64_t row_bytes = static_cast<int64_t>(args[i].get_shape().lens()[axis]) * inner;
+        check_mgx(mgx_cuda_copy_rows(args[i].data(), row_bytes, out.data() + off, dst_pitch, outer, row_bytes,
+                                     ctx.stream()),
+                  "mgx_cuda_copy_rows");
+        off += row_bytes;
+    }
+    return out;
+}
+
+MIGRAPHX_REGISTER_OP(op_gather)
+MIGRAPHX_REGISTER_OP(op_concat)
 MIGRAPHX_REGISTER_OP(op_reduce)
 MIGRAPHX_REGISTER_OP(op_softmax)
 MIGRAPHX_REGISTER_OP(op_pointwise)

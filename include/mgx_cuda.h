@@ -47,7 +47,8 @@ typedef enum mgx_dtype
     MGX_I8         = 2,
     MGX_U8         = 3,
     MGX_I32        = 4,
-    MGX_FP8_E4M3FN = 5
+    MGX_FP8_E4M3FN = 5,
+    MGX_I64        = 6 /* indices of mgx_cuda_gather only */
 } mgx_dtype;
 
 /* How the fp32 scale operand of a fused dequantizelinear is indexed.  After
@@ -161,6 +162,21 @@ MGX_API int mgx_cuda_reduce(const void* x, int type, int64_t ldx, int64_t rows, 
  * exponentials are stored in the output type before they are summed and divided). */
 MGX_API int mgx_cuda_softmax(const void* x, int type, int64_t ldx, void* y, int64_t ldy, int64_t rows,
                              int64_t cols, void* stream);
+
+/* ---- gather, concat (byte movers of the "next" rows: embeddings, KV-cache append) -------- *
+ * out[o, j, :] = data[o, indices[j], :] for o < outer, j < nidx, rows of inner_bytes bytes:
+ * op::gather (src/include/migraphx/op/gather.hpp:107-150) on a packed tensor whose dimensions
+ * before / after the axis are folded into outer / inner_bytes.  Negative indices count from the
+ * end; an index out of range gives zeros (the reference throws on the host).
+ * index_type: MGX_I32 | MGX_I64. */
+MGX_API int mgx_cuda_gather(const void* data, int64_t outer, int64_t axis_len, int64_t inner_bytes,
+                            const void* indices, int index_type, int64_t nidx, void* out, void* stream);
+
+/* dst[r, 0:row_bytes] = src[r, 0:row_bytes] for r < rows with independent row pitches (bytes):
+ * one input of op::concat (src/include/migraphx/op/concat.hpp:147-163) copied into its slice of
+ * the packed result. */
+MGX_API int mgx_cuda_copy_rows(const void* src, int64_t src_pitch, void* dst, int64_t dst_pitch,
+                               int64_t rows, int64_t row_bytes, void* stream);
 
 /* ---- dequantizelinear -------------------------------------------------- *
  * y = (x - zp) * scale, output type = scale type (MGX_F32 | MGX_F16).
