@@ -718,6 +718,8 @@ std::map<std::string, std::function<test_case()>> cases()
         {"attention_f16", [] { return attention_f16(2, 4, 64, 32, 17); }},
         {"dot_f16_const", [] { return dot_f16(1, 200, 136, 264, true, 18); }},
         {"dot_f16_batched", [] { return dot_f16(3, 72, 50, 96, false, 19); }},
+        {"dot_f16_odd_k", [] { return dot_f16(2, 50, 64, 197, false, 22); }},
+        {"dot_f16_odd_k_const", [] { return dot_f16(1, 33, 40, 13, true, 23); }},
         {"bert_layer_int8", [] { return bert_layer_int8(2, 64, 4, 64, 1024, 20); }},
         {"embed_rope_f16", [] { return embed_rope_f16(2, 24, 40, 128, 500, 21); }},
         {"q_dq_ops", [] { return q_dq_ops(7); }},

@@ -304,6 +304,17 @@ struct op_softmax
     std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
 };
 
+// Copy of a standard tensor into a buffer whose rows (innermost dimension) are padded to a
+// multiple of 16 bytes, the row pitch the tensor maps of the GEMM kernels need.  The padding is
+// never read (the maps are bounded by the logical row length).  Inputs: x, out (padded strides).
+struct op_pad_rows
+{
+    std::string name() const { return "cuda::pad_rows"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
+};
+
 // gather along `axis` of a standard tensor (src/include/migraphx/op/gather.hpp).
 // Inputs: data, indices (int32 / int64), out.
 struct op_gather

@@ -748,14 +748,24 @@ struct lowerer
         for(std::size_t j = 0; j + 2 < nd; ++j)
             if(as.lens()[j] != bs.lens()[j])
                 return false;
-        // rows of 16-byte multiples (the tensor maps' stride rule)
-        if(k % 8 != 0)
-            unsupported(ins, "the inner dimension of an fp16 dot must be a multiple of 8");
         // a transposed / sliced left operand (attention heads) is packed first
         const bool a_ok = as.strides()[nd - 1] == 1 and as.strides()[nd - 2] % 8 == 0 and
                           (nd == 2 or as.standard());
-        if(not a_ok)
+        if(not a_ok and not as.standard())
             a = standard_copy(ins, a);
+        if(k % 8 != 0)
+        {
+            // rows of 16-byte multiples (the tensor maps' stride rule): copy into padded rows
+            const std::size_t kp = (k + 7) / 8 * 8;
+            auto lens            = as.lens();
+            std::vector<std::size_t> strides(nd, 1);
+            strides[nd - 2] = kp;
+            for(std::size_t j = nd - 2; j-- > 0;)
+                strides[j] = strides[j + 1] * lens[j + 1];
+            auto buf = insert_allocation(m, ins, shape{shape::half_type, lens, strides});
+            a        = m.insert_instruction(ins, op_pad_rows{}, a, buf);
+            consume(a);
+        }
         op_qgemm op;
         op.out_type = static_cast<int>(shape::half_type);
         std::vector<instruction_ref> args = {a, b};
@@ -1082,7 +1092,7 @@ void insert_graph_ops::apply(module& m) const
         return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
                n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or
                n == "cuda::copy" or n == "cuda::pointwise" or n == "cuda::reduce" or n == "cuda::softmax" or
-               n == "cuda::gather" or n == "cuda::concat";
+               n == "cuda::gather" or n == "cuda::concat" or n == "cuda::pad_rows";
     };
     instruction_ref first = m.end();
     std::size_t nlaunch   = 0;

@@ -565,6 +565,34 @@ argument op_concat::compute(context& ctx, const shape&, const std::vector<argume
     return out;
 }
 
+shape op_pad_rows::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(2);
+    const auto& x = inputs[0];
+    const auto& o = inputs[1];
+    if(not x.standard() or x.ndim() < 1 or o.lens() != x.lens() or o.type() != x.type() or
+       o.strides().back() != 1)
+        MIGRAPHX_THROW("cuda::pad_rows: expects a standard input and an output of the same dimensions");
+    return o;
+}
+
+argument op_pad_rows::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& xs      = args[0].get_shape();
+    const auto& os      = out.get_shape();
+    const int64_t es    = static_cast<int64_t>(xs.type_size());
+    const int64_t cols  = static_cast<int64_t>(xs.lens().back());
+    const int64_t rows  = static_cast<int64_t>(xs.elements()) / cols;
+    const int64_t pitch = xs.ndim() > 1 ? static_cast<int64_t>(os.strides()[xs.ndim() - 2]) : cols;
+    check_mgx(mgx_cuda_copy_rows(args[0].data(), cols * es, out.data(), pitch * es, rows, cols * es, ctx.stream()),
+              "mgx_cuda_copy_rows");
+    return out;
+}
+
+MIGRAPHX_REGISTER_OP(op_pad_rows)
 MIGRAPHX_REGISTER_OP(op_gather)
 MIGRAPHX_REGISTER_OP(op_concat)
 MIGRAPHX_REGISTER_OP(op_reduce)

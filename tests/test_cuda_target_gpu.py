@@ -19,7 +19,8 @@ CASES = ["c1_small", "c1_semantic", "int8_gelu", "int8_per_tensor", "fp8_gelu", 
          "int4_batch16_zp", "int4_batch8_zp", "int4_prefill", "q_dq_ops", "raw_quant_dot", "mlp_fused_q", "mlp_two_outputs",
          "pw_gelu_f16", "pw_arith_f32", "pw_transcendental_f32",
          "layernorm_f32", "layernorm_f16", "softmax_f32", "softmax_f16", "softmax_f32_long",
-         "attention_f16", "dot_f16_const", "dot_f16_batched", "bert_layer_int8", "embed_rope_f16"]
+         "attention_f16", "dot_f16_const", "dot_f16_batched", "bert_layer_int8", "embed_rope_f16",
+         "dot_f16_odd_k", "dot_f16_odd_k_const"]
 
 
 def _run(case, mode=None):

@@ -117,3 +117,22 @@ def test_bert_layer_compiles_into_one_graph():
     # FFN1: GELU and the quantizelinear feeding FFN2 run in its epilogue
     assert any("act=2" in l and "q_type=5" in l and "write_d=0" in l for l in out.splitlines())
     assert "cuda::softmax" in out and out.count("cuda::reduce[mode=1]") == 4
+
+
+def test_embedding_rope_and_cache_append_lower_to_movers():
+    out = _passes("embed_rope_f16")
+    assert "cuda::gather[axis=0]" in out
+    assert "cuda::concat[axis=2]" in out and "cuda::concat[axis=1]" in out
+    # the two halves are views (slice) read by the element-wise kernel, not copies of x
+    assert out.count("slice[") == 2
+    # cos / sin mix in one launch
+    assert "cuda::pointwise[ops={2, 2, 0}" in out
+
+
+def test_fp16_dot_with_unaligned_inner_dimension_pads_rows():
+    out = _passes("dot_f16_odd_k")
+    assert "cuda::pad_rows" in out and "{2, 50, 197}, {10000, 200, 1}" in out
+    out = _passes("dot_f16_odd_k_const")
+    # 13 is no multiple of 8: the constant stays [K,N] and is re-laid out per evaluation
+    line = [l for l in out.splitlines() if "cuda::qgemm" in l][0]
+    assert "b_nk=0" in line and "has_workspace=1" in line and "cuda::pad_rows" in out
