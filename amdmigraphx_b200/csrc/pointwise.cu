@@ -5,6 +5,7 @@
 // type and back, so fp16 chains round (truncate) exactly where the reference's migraphx::half
 // arithmetic does, and integer results wrap / saturate the way a cast to that type does.
 #include "common.cuh"
+#include "ptx.cuh"
 #include "qgemm_math.cuh"
 #include <cuda_fp16.h>
 
@@ -55,72 +56,236 @@ __device__ __forceinline__ void pw_store(void* p, int type, int64_t i, float v)
     }
 }
 
+// V consecutive elements of the innermost dimension per thread: the multi-index is decomposed
+// once per V elements, contiguous operands are read and the result written as 16-byte vectors,
+// and every instruction is dispatched once per V elements.  Operands that are inputs are read
+// from global memory where they are used and the last result goes straight to the store, so only
+// the intermediate results of a chain pass through r[slot][v], which the program indexes and
+// which therefore lives in (L1-resident) local memory.
+// operands an operator reads
+__device__ __forceinline__ int pw_arity(int op)
+{
+    switch(op)
+    {
+    case MGX_PW_CONST: return 0;
+    case MGX_PW_ADD:
+    case MGX_PW_SUB:
+    case MGX_PW_MUL:
+    case MGX_PW_DIV:
+    case MGX_PW_MIN:
+    case MGX_PW_MAX:
+    case MGX_PW_POW:
+    case MGX_PW_EQUAL:
+    case MGX_PW_GREATER:
+    case MGX_PW_LESS: return 2;
+    case MGX_PW_WHERE:
+    case MGX_PW_CLIP: return 3;
+    default: return 1;
+    }
+}
+
+template <int V>
+__device__ __forceinline__ void pw_load_vec(const void* p, int type, int64_t off, int64_t stride, float (&r)[V])
+{
+    if(stride == 0)
+    {
+        const float x = pw_load(p, type, off);
+#pragma unroll
+        for(int v = 0; v < V; ++v)
+            r[v] = x;
+        return;
+    }
+    if constexpr(V == 8)
+    {
+        if(stride == 1 and type == MGX_F16 and ((reinterpret_cast<uintptr_t>(p) + 2 * off) & 15u) == 0)
+        {
+            const uint4 w     = *reinterpret_cast<const uint4*>(static_cast<const __half*>(p) + off);
+            const __half2* h2 = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+            for(int v = 0; v < 4; ++v)
+            {
+                const float2 f = __half22float2(h2[v]);
+                r[2 * v]       = f.x;
+                r[2 * v + 1]   = f.y;
+            }
+            return;
+        }
+        if(stride == 1 and type == MGX_F32 and ((reinterpret_cast<uintptr_t>(p) + 4 * off) & 15u) == 0)
+        {
+            const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + off);
+            const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(p) + off + 4);
+            r[0] = a.x, r[1] = a.y, r[2] = a.z, r[3] = a.w, r[4] = b.x, r[5] = b.y, r[6] = b.z, r[7] = b.w;
+            return;
+        }
+    }
+#pragma unroll
+    for(int v = 0; v < V; ++v)
+        r[v] = pw_load(p, type, off + v * stride);
+}
+
+template <int V>
+__device__ __forceinline__ void pw_store_vec(void* p, int type, int64_t i, const float (&r)[V])
+{
+    if constexpr(V == 8)
+    {
+        if(type == MGX_F16 and ((reinterpret_cast<uintptr_t>(p) + 2 * i) & 15u) == 0)
+        {
+            uint4 w;
+            w.x = cvt_rz_f16x2(r[0], r[1]);
+            w.y = cvt_rz_f16x2(r[2], r[3]);
+            w.z = cvt_rz_f16x2(r[4], r[5]);
+            w.w = cvt_rz_f16x2(r[6], r[7]);
+            *reinterpret_cast<uint4*>(static_cast<__half*>(p) + i) = w;
+            return;
+        }
+        if(type == MGX_F32 and ((reinterpret_cast<uintptr_t>(p) + 4 * i) & 15u) == 0)
+        {
+            float* o                         = static_cast<float*>(p) + i;
+            *reinterpret_cast<float4*>(o)     = make_float4(r[0], r[1], r[2], r[3]);
+            *reinterpret_cast<float4*>(o + 4) = make_float4(r[4], r[5], r[6], r[7]);
+            return;
+        }
+    }
+#pragma unroll
+    for(int v = 0; v < V; ++v)
+        pw_store(p, type, i + v, r[v]);
+}
+
+#define MGX_PW_EACH(expr)          \
+    _Pragma("unroll") for(int v = 0; v < V; ++v) \
+    {                              \
+        const float x = rx[v], y = ry[v], z = rz[v]; \
+        (void)y;                   \
+        (void)z;                   \
+        ro[v] = (expr);            \
+    }                              \
+    break
+
+template <int V, class IndexT>
 __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ pw_args a)
 {
     const mgx_pw_desc& d = a.d;
-    float r[MGX_PW_MAXIN + MGX_PW_MAXINSN];
-    for(int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < a.total;
-        idx += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    float r[MGX_PW_MAXINSN][V];
+    const int last       = d.ndim - 1;
+    const IndexT nvec    = static_cast<IndexT>(a.total / V);
+    for(IndexT vec = blockIdx.x * static_cast<IndexT>(256) + threadIdx.x; vec < nvec;
+        vec += static_cast<IndexT>(gridDim.x) * 256)
     {
-        // multi-index of the output element -> offset into every (strided, broadcast) input
+        // multi-index of the first element -> offset into every (strided, broadcast) input
+        const IndexT idx = vec * V;
         int64_t off[MGX_PW_MAXIN];
         for(int i = 0; i < d.ninputs; ++i)
             off[i] = 0;
-        int64_t rem = idx;
-        for(int k = d.ndim - 1; k >= 0; --k)
+        IndexT rem = idx;
+        for(int k = last; k >= 0; --k)
         {
-            const int64_t c = rem % d.lens[k];
-            rem /= d.lens[k];
+            const IndexT len = static_cast<IndexT>(d.lens[k]);
+            const IndexT q   = rem / len;
+            const IndexT c   = rem - q * len;
+            rem              = q;
             for(int i = 0; i < d.ninputs; ++i)
-                off[i] += c * d.in_strides[i][k];
+                off[i] += static_cast<int64_t>(c) * d.in_strides[i][k];
         }
-        for(int i = 0; i < d.ninputs; ++i)
-            r[i] = pw_load(a.in[i], d.in_type[i], off[i]);
+        auto fetch = [&](int src, float(&dst)[V]) {
+            if(src < d.ninputs)
+                pw_load_vec<V>(a.in[src], d.in_type[src], off[src], d.in_strides[src][last], dst);
+            else
+            {
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                    dst[v] = r[src - d.ninputs][v];
+            }
+        };
         for(int n = 0; n < d.ninsns; ++n)
         {
             const mgx_pw_insn& ins = d.insn[n];
-            const float x = r[ins.src[0]], y = r[ins.src[1]], z = r[ins.src[2]];
-            float v;
+            float rx[V], ry[V], rz[V], ro[V];
+            const int arity = pw_arity(ins.op);
+            if(arity >= 1)
+                fetch(ins.src[0], rx);
+            if(arity >= 2)
+                fetch(ins.src[1], ry);
+            if(arity >= 3)
+                fetch(ins.src[2], rz);
+            if(arity < 3)
+            {
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                {
+                    rz[v] = 0.0f;
+                    if(arity < 2)
+                        ry[v] = 0.0f;
+                    if(arity < 1)
+                        rx[v] = 0.0f;
+                }
+            }
+            const float imm = ins.imm;
             switch(ins.op)
             {
-            case MGX_PW_ADD: v = __fadd_rn(x, y); break;
-            case MGX_PW_SUB: v = __fsub_rn(x, y); break;
-            case MGX_PW_MUL: v = __fmul_rn(x, y); break;
-            case MGX_PW_DIV: v = __fdiv_rn(x, y); break;
-            case MGX_PW_MIN: v = y < x ? y : x; break; // std::min
-            case MGX_PW_MAX: v = x < y ? y : x; break; // std::max
-            case MGX_PW_POW: v = powf(x, y); break;
-            case MGX_PW_NEG: v = -x; break;
-            case MGX_PW_ABS: v = fabsf(x); break;
-            case MGX_PW_EXP: v = expf(x); break;
-            case MGX_PW_LOG: v = logf(x); break;
-            case MGX_PW_SQRT: v = __fsqrt_rn(x); break;
-            case MGX_PW_RSQRT: v = __fdiv_rn(1.0f, __fsqrt_rn(x)); break;
-            case MGX_PW_RECIP: v = __fdiv_rn(1.0f, x); break;
-            case MGX_PW_TANH: v = tanhf(x); break;
-            case MGX_PW_SIGMOID: v = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); break;
-            case MGX_PW_ERF: v = erff(x); break;
-            case MGX_PW_RELU: v = x < 0.0f ? 0.0f : x; break; // std::max(0, x)
-            case MGX_PW_SIN: v = sinf(x); break;
-            case MGX_PW_COS: v = cosf(x); break;
-            case MGX_PW_FLOOR: v = floorf(x); break;
-            case MGX_PW_CEIL: v = ceilf(x); break;
-            case MGX_PW_ROUND: v = roundf(x); break;
-            case MGX_PW_NEARBYINT: v = nearbyintf(x); break;
-            case MGX_PW_CONVERT: v = x; break;
-            case MGX_PW_WHERE: v = x != 0.0f ? y : z; break;
-            case MGX_PW_CLIP: v = fminf(fmaxf(x, y), z); break;
-            case MGX_PW_EQUAL: v = x == y ? 1.0f : 0.0f; break;
-            case MGX_PW_GREATER: v = x > y ? 1.0f : 0.0f; break;
-            case MGX_PW_LESS: v = x < y ? 1.0f : 0.0f; break;
-            case MGX_PW_LEAKY_RELU: v = x > 0.0f ? x : __fmul_rn(x, ins.imm); break;
-            case MGX_PW_CONST: v = ins.imm; break;
-            default: v = x; break;
+            case MGX_PW_ADD: MGX_PW_EACH(__fadd_rn(x, y));
+            case MGX_PW_SUB: MGX_PW_EACH(__fsub_rn(x, y));
+            case MGX_PW_MUL: MGX_PW_EACH(__fmul_rn(x, y));
+            case MGX_PW_DIV: MGX_PW_EACH(__fdiv_rn(x, y));
+            case MGX_PW_MIN: MGX_PW_EACH(y < x ? y : x); // std::min
+            case MGX_PW_MAX: MGX_PW_EACH(x < y ? y : x); // std::max
+            case MGX_PW_POW: MGX_PW_EACH(powf(x, y));
+            case MGX_PW_NEG: MGX_PW_EACH(-x);
+            case MGX_PW_ABS: MGX_PW_EACH(fabsf(x));
+            case MGX_PW_EXP: MGX_PW_EACH(expf(x));
+            case MGX_PW_LOG: MGX_PW_EACH(logf(x));
+            case MGX_PW_SQRT: MGX_PW_EACH(__fsqrt_rn(x));
+            case MGX_PW_RSQRT: MGX_PW_EACH(__fdiv_rn(1.0f, __fsqrt_rn(x)));
+            case MGX_PW_RECIP: MGX_PW_EACH(__fdiv_rn(1.0f, x));
+            case MGX_PW_TANH: MGX_PW_EACH(tanhf(x));
+            case MGX_PW_SIGMOID: MGX_PW_EACH(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
+            case MGX_PW_ERF: MGX_PW_EACH(erff(x));
+            case MGX_PW_RELU: MGX_PW_EACH(x < 0.0f ? 0.0f : x); // std::max(0, x)
+            case MGX_PW_SIN: MGX_PW_EACH(sinf(x));
+            case MGX_PW_COS: MGX_PW_EACH(cosf(x));
+            case MGX_PW_FLOOR: MGX_PW_EACH(floorf(x));
+            case MGX_PW_CEIL: MGX_PW_EACH(ceilf(x));
+            case MGX_PW_ROUND: MGX_PW_EACH(roundf(x));
+            case MGX_PW_NEARBYINT: MGX_PW_EACH(nearbyintf(x));
+            case MGX_PW_WHERE: MGX_PW_EACH(x != 0.0f ? y : z);
+            case MGX_PW_CLIP: MGX_PW_EACH(fminf(fmaxf(x, y), z));
+            case MGX_PW_EQUAL: MGX_PW_EACH(x == y ? 1.0f : 0.0f);
+            case MGX_PW_GREATER: MGX_PW_EACH(x > y ? 1.0f : 0.0f);
+            case MGX_PW_LESS: MGX_PW_EACH(x < y ? 1.0f : 0.0f);
+            case MGX_PW_LEAKY_RELU: MGX_PW_EACH(x > 0.0f ? x : __fmul_rn(x, imm));
+            case MGX_PW_CONST: MGX_PW_EACH(imm);
+            default: MGX_PW_EACH(x); // convert, identity
             }
-            r[d.ninputs + n] = pw_as_type(v, ins.type);
+            if(n == d.ninsns - 1)
+            {
+                // the store converts (fp16: truncates) by itself
+                pw_store_vec<V>(a.out, ins.type, static_cast<int64_t>(idx), ro);
+                break;
+            }
+            if(ins.type != MGX_F32)
+            {
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                    ro[v] = pw_as_type(ro[v], ins.type);
+            }
+#pragma unroll
+            for(int v = 0; v < V; ++v)
+                r[n][v] = ro[v];
         }
-        pw_store(a.out, d.insn[d.ninsns - 1].type, idx, r[d.ninputs + d.ninsns - 1]);
     }
+}
+#undef MGX_PW_EACH
+
+template <int V>
+static int launch_pointwise(const pw_args& a, cudaStream_t stream)
+{
+    const int64_t nvec   = a.total / V;
+    const int64_t blocks = ceil_div(nvec, 256);
+    const int grid       = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
+    if(a.total < (int64_t{1} << 31))
+        pointwise_kernel<V, uint32_t><<<grid, 256, 0, stream>>>(a);
+    else
+        pointwise_kernel<V, int64_t><<<grid, 256, 0, stream>>>(a);
+    return static_cast<int>(cudaGetLastError());
 }
 
 } // namespace mgx
@@ -162,8 +327,12 @@ extern "C" int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* input
     }
     if(a.total == 0)
         return MGX_OK;
-    const int64_t blocks = ceil_div(a.total, 256);
-    const int grid       = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
-    pointwise_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream_)>>>(a);
-    return static_cast<int>(cudaGetLastError());
+    // vectors never straddle a row: V divides the innermost length
+    const int64_t inner = d->lens[d->ndim - 1];
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(inner % 8 == 0)
+        return launch_pointwise<8>(a, stream);
+    if(inner % 2 == 0)
+        return launch_pointwise<2>(a, stream);
+    return launch_pointwise<1>(a, stream);
 }

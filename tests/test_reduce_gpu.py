@@ -67,6 +67,34 @@ def test_reduce_f16_strided_rows(cuda_device, op):
         assert np.mean(got == reft) > 0.9
 
 
+@pytest.mark.parametrize("op", ["sum", "max"])
+@pytest.mark.parametrize("cols", [704, 8192])
+def test_reduce_f16_vector_path_strided_rows(cuda_device, op, cols):
+    """Rows whose pitch and length allow 16-byte loads (a warp per row, a block per long row)."""
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(cols)
+    full = rng.normal(0, 1.0, (37, cols + 64)).astype(np.float16)
+    xt = _t(full, cuda_device)[:, :cols]
+    got = capi.reduce_rows(xt, op).cpu().numpy().astype(np.float32)
+    ref = _ref_reduce(full[:, :cols].astype(np.float32), op)
+    if op == "max":
+        assert np.array_equal(got, ref.astype(np.float32))
+    else:
+        reft = O.half_trunc(ref.astype(np.float32)).astype(np.float32)
+        ulp = np.maximum(np.abs(reft) * 2.0 ** -10, 2.0 ** -24)
+        assert np.all(np.abs(got - reft) <= ulp)
+
+
+def test_softmax_strided_rows_vector_path(cuda_device):
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(8)
+    full = rng.normal(0, 3.0, (50, 512)).astype(np.float32)
+    xt = _t(full, cuda_device)[:, :384]
+    got = capi.softmax(xt).cpu().numpy()
+    np.testing.assert_allclose(got, _ref_softmax(full[:, :384], False), rtol=1e-5, atol=1e-10)
+
+
 @pytest.mark.parametrize("rows,cols", [(3, 5), (128, 384), (40, 1500), (9, 4096), (4, 8192), (3, 10000)])
 def test_softmax_f32(cuda_device, rows, cols):
     from amdmigraphx_b200 import capi
