@@ -17,6 +17,9 @@ struct pw_args
     const void* in[MGX_PW_MAXIN];
     void* out;
     int64_t total;
+    // division by lens[k] for indices below 2^31: q = (n * magic[k]) >> shift[k]
+    uint64_t magic[MGX_PW_MAXDIMS];
+    int shift[MGX_PW_MAXDIMS];
 };
 
 __device__ __forceinline__ float pw_load(const void* p, int type, int64_t i)
@@ -177,15 +180,22 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ 
         for(int i = 0; i < d.ninputs; ++i)
             off[i] = 0;
         IndexT rem = idx;
-        for(int k = last; k >= 0; --k)
+        for(int k = last; k > 0; --k)
         {
             const IndexT len = static_cast<IndexT>(d.lens[k]);
-            const IndexT q   = rem / len;
-            const IndexT c   = rem - q * len;
-            rem              = q;
+            IndexT q;
+            if constexpr(sizeof(IndexT) == 4)
+                q = static_cast<IndexT>((static_cast<uint64_t>(rem) * a.magic[k]) >> a.shift[k]);
+            else
+                q = rem / len;
+            const IndexT c = rem - q * len;
+            rem            = q;
             for(int i = 0; i < d.ninputs; ++i)
                 off[i] += static_cast<int64_t>(c) * d.in_strides[i][k];
         }
+        // the outermost index needs no division
+        for(int i = 0; i < d.ninputs; ++i)
+            off[i] += static_cast<int64_t>(rem) * d.in_strides[i][0];
         auto fetch = [&](int src, float(&dst)[V]) {
             if(src < d.ninputs)
                 pw_load_vec<V>(a.in[src], d.in_type[src], off[src], d.in_strides[src][last], dst);
@@ -327,8 +337,54 @@ extern "C" int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* input
     }
     if(a.total == 0)
         return MGX_OK;
+    // fewer dimensions, fewer divisions per element: drop dimensions of length 1 and merge a
+    // dimension into its inner neighbour where every operand steps through both as through one
+    {
+        mgx_pw_desc& c = a.d;
+        int nd         = 0;
+        for(int k = 0; k < d->ndim; ++k)
+        {
+            if(d->lens[k] == 1)
+                continue;
+            bool merge = nd > 0;
+            for(int i = 0; merge and i < d->ninputs; ++i)
+                if(c.in_strides[i][nd - 1] != d->in_strides[i][k] * d->lens[k])
+                    merge = false;
+            if(merge)
+            {
+                c.lens[nd - 1] *= d->lens[k];
+                for(int i = 0; i < d->ninputs; ++i)
+                    c.in_strides[i][nd - 1] = d->in_strides[i][k];
+            }
+            else
+            {
+                c.lens[nd] = d->lens[k];
+                for(int i = 0; i < d->ninputs; ++i)
+                    c.in_strides[i][nd] = d->in_strides[i][k];
+                ++nd;
+            }
+        }
+        if(nd == 0)
+        {
+            // a single element
+            c.lens[0] = 1;
+            for(int i = 0; i < d->ninputs; ++i)
+                c.in_strides[i][0] = 0;
+            nd = 1;
+        }
+        c.ndim = nd;
+        for(int k = 0; k < nd; ++k)
+        {
+            const uint64_t len = static_cast<uint64_t>(c.lens[k]);
+            int l              = 0;
+            while((uint64_t{1} << l) < len)
+                ++l;
+            a.shift[k] = 31 + l;
+            a.magic[k] = ((uint64_t{1} << a.shift[k]) + len - 1) / len;
+        }
+    }
     // vectors never straddle a row: V divides the innermost length
-    const int64_t inner = d->lens[d->ndim - 1];
+    const int64_t inner = a.d.lens[a.d.ndim - 1];
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if(inner % 8 == 0)
         return launch_pointwise<8>(a, stream);
