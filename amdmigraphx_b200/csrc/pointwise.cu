@@ -20,6 +20,9 @@ struct pw_args
     // division by lens[k] for indices below 2^31: q = (n * magic[k]) >> shift[k]
     uint64_t magic[MGX_PW_MAXDIMS];
     int shift[MGX_PW_MAXDIMS];
+    // bit n: the result of instruction n is read by an instruction other than n + 1 (it must be
+    // kept in r[]; the result of the previous instruction is always at hand in registers)
+    uint32_t keep;
 };
 
 __device__ __forceinline__ float pw_load(const void* p, int type, int64_t i)
@@ -196,9 +199,20 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ 
         // the outermost index needs no division
         for(int i = 0; i < d.ninputs; ++i)
             off[i] += static_cast<int64_t>(rem) * d.in_strides[i][0];
+        float prev[V];
+#pragma unroll
+        for(int v = 0; v < V; ++v)
+            prev[v] = 0.0f;
+        int prev_slot = -1;
         auto fetch = [&](int src, float(&dst)[V]) {
             if(src < d.ninputs)
                 pw_load_vec<V>(a.in[src], d.in_type[src], off[src], d.in_strides[src][last], dst);
+            else if(src == prev_slot)
+            {
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                    dst[v] = prev[v];
+            }
             else
             {
 #pragma unroll
@@ -277,9 +291,16 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ 
                 for(int v = 0; v < V; ++v)
                     ro[v] = pw_as_type(ro[v], ins.type);
             }
+            prev_slot = d.ninputs + n;
 #pragma unroll
             for(int v = 0; v < V; ++v)
-                r[n][v] = ro[v];
+                prev[v] = ro[v];
+            if((a.keep >> n) & 1u)
+            {
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                    r[n][v] = ro[v];
+            }
         }
     }
 }
@@ -335,6 +356,11 @@ extern "C" int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* input
                 if(not(s == 0 and d->ninputs + n == 0)) // constants have no operands
                     return MGX_E_INVALID_ARG;
     }
+    for(int n = 0; n < d->ninsns; ++n)
+        for(int m = n + 2; m < d->ninsns; ++m)
+            for(int sidx : d->insn[m].src)
+                if(sidx == d->ninputs + n)
+                    a.keep |= 1u << n;
     if(a.total == 0)
         return MGX_OK;
     // fewer dimensions, fewer divisions per element: drop dimensions of length 1 and merge a
