@@ -157,14 +157,19 @@ __device__ __forceinline__ void pw_store_vec(void* p, int type, int64_t i, const
         pw_store(p, type, i + v, r[v]);
 }
 
-#define MGX_PW_EACH(expr)          \
+#define MGX_PW_EACH1(expr)                       \
     _Pragma("unroll") for(int v = 0; v < V; ++v) \
-    {                              \
-        const float x = rx[v], y = ry[v], z = rz[v]; \
-        (void)y;                   \
-        (void)z;                   \
-        ro[v] = (expr);            \
-    }                              \
+    {                                            \
+        const float x = rx[v];                   \
+        ro[v]         = (expr);                  \
+    }                                            \
+    break
+#define MGX_PW_EACH2(expr)                       \
+    _Pragma("unroll") for(int v = 0; v < V; ++v) \
+    {                                            \
+        const float x = rx[v], y = ry[v];        \
+        ro[v]         = (expr);                  \
+    }                                            \
     break
 
 template <int V, class IndexT>
@@ -223,61 +228,72 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ 
         for(int n = 0; n < d.ninsns; ++n)
         {
             const mgx_pw_insn& ins = d.insn[n];
-            float rx[V], ry[V], rz[V], ro[V];
+            float ro[V];
+            const float imm = ins.imm;
             const int arity = pw_arity(ins.op);
-            if(arity >= 1)
+            // one dispatch per arity: only the operands an operator reads are fetched
+            if(arity == 2)
+            {
+                float rx[V], ry[V];
                 fetch(ins.src[0], rx);
-            if(arity >= 2)
                 fetch(ins.src[1], ry);
-            if(arity >= 3)
+                switch(ins.op)
+                {
+                case MGX_PW_ADD: MGX_PW_EACH2(__fadd_rn(x, y));
+                case MGX_PW_SUB: MGX_PW_EACH2(__fsub_rn(x, y));
+                case MGX_PW_MUL: MGX_PW_EACH2(__fmul_rn(x, y));
+                case MGX_PW_DIV: MGX_PW_EACH2(__fdiv_rn(x, y));
+                case MGX_PW_MIN: MGX_PW_EACH2(y < x ? y : x); // std::min
+                case MGX_PW_MAX: MGX_PW_EACH2(x < y ? y : x); // std::max
+                case MGX_PW_POW: MGX_PW_EACH2(powf(x, y));
+                case MGX_PW_EQUAL: MGX_PW_EACH2(x == y ? 1.0f : 0.0f);
+                case MGX_PW_GREATER: MGX_PW_EACH2(x > y ? 1.0f : 0.0f);
+                default: MGX_PW_EACH2(x < y ? 1.0f : 0.0f); // less
+                }
+            }
+            else if(arity == 1)
+            {
+                float rx[V];
+                fetch(ins.src[0], rx);
+                switch(ins.op)
+                {
+                case MGX_PW_NEG: MGX_PW_EACH1(-x);
+                case MGX_PW_ABS: MGX_PW_EACH1(fabsf(x));
+                case MGX_PW_EXP: MGX_PW_EACH1(expf(x));
+                case MGX_PW_LOG: MGX_PW_EACH1(logf(x));
+                case MGX_PW_SQRT: MGX_PW_EACH1(__fsqrt_rn(x));
+                case MGX_PW_RSQRT: MGX_PW_EACH1(__fdiv_rn(1.0f, __fsqrt_rn(x)));
+                case MGX_PW_RECIP: MGX_PW_EACH1(__fdiv_rn(1.0f, x));
+                case MGX_PW_TANH: MGX_PW_EACH1(tanhf(x));
+                case MGX_PW_SIGMOID: MGX_PW_EACH1(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
+                case MGX_PW_ERF: MGX_PW_EACH1(erff(x));
+                case MGX_PW_RELU: MGX_PW_EACH1(x < 0.0f ? 0.0f : x); // std::max(0, x)
+                case MGX_PW_SIN: MGX_PW_EACH1(sinf(x));
+                case MGX_PW_COS: MGX_PW_EACH1(cosf(x));
+                case MGX_PW_FLOOR: MGX_PW_EACH1(floorf(x));
+                case MGX_PW_CEIL: MGX_PW_EACH1(ceilf(x));
+                case MGX_PW_ROUND: MGX_PW_EACH1(roundf(x));
+                case MGX_PW_NEARBYINT: MGX_PW_EACH1(nearbyintf(x));
+                case MGX_PW_LEAKY_RELU: MGX_PW_EACH1(x > 0.0f ? x : __fmul_rn(x, imm));
+                default: MGX_PW_EACH1(x); // convert, identity
+                }
+            }
+            else if(arity == 3)
+            {
+                float rx[V], ry[V], rz[V];
+                fetch(ins.src[0], rx);
+                fetch(ins.src[1], ry);
                 fetch(ins.src[2], rz);
-            if(arity < 3)
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                    ro[v] = ins.op == MGX_PW_WHERE ? (rx[v] != 0.0f ? ry[v] : rz[v])
+                                                   : fminf(fmaxf(rx[v], ry[v]), rz[v]); // clip
+            }
+            else
             {
 #pragma unroll
                 for(int v = 0; v < V; ++v)
-                {
-                    rz[v] = 0.0f;
-                    if(arity < 2)
-                        ry[v] = 0.0f;
-                    if(arity < 1)
-                        rx[v] = 0.0f;
-                }
-            }
-            const float imm = ins.imm;
-            switch(ins.op)
-            {
-            case MGX_PW_ADD: MGX_PW_EACH(__fadd_rn(x, y));
-            case MGX_PW_SUB: MGX_PW_EACH(__fsub_rn(x, y));
-            case MGX_PW_MUL: MGX_PW_EACH(__fmul_rn(x, y));
-            case MGX_PW_DIV: MGX_PW_EACH(__fdiv_rn(x, y));
-            case MGX_PW_MIN: MGX_PW_EACH(y < x ? y : x); // std::min
-            case MGX_PW_MAX: MGX_PW_EACH(x < y ? y : x); // std::max
-            case MGX_PW_POW: MGX_PW_EACH(powf(x, y));
-            case MGX_PW_NEG: MGX_PW_EACH(-x);
-            case MGX_PW_ABS: MGX_PW_EACH(fabsf(x));
-            case MGX_PW_EXP: MGX_PW_EACH(expf(x));
-            case MGX_PW_LOG: MGX_PW_EACH(logf(x));
-            case MGX_PW_SQRT: MGX_PW_EACH(__fsqrt_rn(x));
-            case MGX_PW_RSQRT: MGX_PW_EACH(__fdiv_rn(1.0f, __fsqrt_rn(x)));
-            case MGX_PW_RECIP: MGX_PW_EACH(__fdiv_rn(1.0f, x));
-            case MGX_PW_TANH: MGX_PW_EACH(tanhf(x));
-            case MGX_PW_SIGMOID: MGX_PW_EACH(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))));
-            case MGX_PW_ERF: MGX_PW_EACH(erff(x));
-            case MGX_PW_RELU: MGX_PW_EACH(x < 0.0f ? 0.0f : x); // std::max(0, x)
-            case MGX_PW_SIN: MGX_PW_EACH(sinf(x));
-            case MGX_PW_COS: MGX_PW_EACH(cosf(x));
-            case MGX_PW_FLOOR: MGX_PW_EACH(floorf(x));
-            case MGX_PW_CEIL: MGX_PW_EACH(ceilf(x));
-            case MGX_PW_ROUND: MGX_PW_EACH(roundf(x));
-            case MGX_PW_NEARBYINT: MGX_PW_EACH(nearbyintf(x));
-            case MGX_PW_WHERE: MGX_PW_EACH(x != 0.0f ? y : z);
-            case MGX_PW_CLIP: MGX_PW_EACH(fminf(fmaxf(x, y), z));
-            case MGX_PW_EQUAL: MGX_PW_EACH(x == y ? 1.0f : 0.0f);
-            case MGX_PW_GREATER: MGX_PW_EACH(x > y ? 1.0f : 0.0f);
-            case MGX_PW_LESS: MGX_PW_EACH(x < y ? 1.0f : 0.0f);
-            case MGX_PW_LEAKY_RELU: MGX_PW_EACH(x > 0.0f ? x : __fmul_rn(x, imm));
-            case MGX_PW_CONST: MGX_PW_EACH(imm);
-            default: MGX_PW_EACH(x); // convert, identity
+                    ro[v] = imm;
             }
             if(n == d.ninsns - 1)
             {
@@ -285,7 +301,30 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ 
                 pw_store_vec<V>(a.out, ins.type, static_cast<int64_t>(idx), ro);
                 break;
             }
-            if(ins.type != MGX_F32)
+            if(ins.type == MGX_F16)
+            {
+                // all values normal halves (the common case): cut the mantissas
+                float hi = 0.0f, lo = 65536.0f;
+#pragma unroll
+                for(int v = 0; v < V; ++v)
+                {
+                    hi = fmaxf(hi, fabsf(ro[v]));
+                    lo = fminf(lo, fabsf(ro[v]));
+                }
+                if(hi < 65536.0f and lo >= 6.103515625e-5f)
+                {
+#pragma unroll
+                    for(int v = 0; v < V; ++v)
+                        ro[v] = __uint_as_float(__float_as_uint(ro[v]) & 0xFFFFE000u);
+                }
+                else
+                {
+#pragma unroll
+                    for(int v = 0; v < V; ++v)
+                        ro[v] = truncate_to_half_precision(ro[v]);
+                }
+            }
+            else if(ins.type != MGX_F32)
             {
 #pragma unroll
                 for(int v = 0; v < V; ++v)
@@ -304,7 +343,8 @@ __global__ void __launch_bounds__(256) pointwise_kernel(const __grid_constant__ 
         }
     }
 }
-#undef MGX_PW_EACH
+#undef MGX_PW_EACH1
+#undef MGX_PW_EACH2
 
 template <int V>
 static int launch_pointwise(const pw_args& a, cudaStream_t stream)
