@@ -351,7 +351,16 @@ static int launch_pointwise(const pw_args& a, cudaStream_t stream)
 {
     const int64_t nvec   = a.total / V;
     const int64_t blocks = ceil_div(nvec, 256);
-    const int grid       = static_cast<int>(blocks < 148 * 8 ? blocks : 148 * 8);
+    // one wave of resident blocks: a grid-stride loop over more blocks than fit at once would
+    // leave a partial second wave
+    static const int resident = [] {
+        int n = 0;
+        if(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, pointwise_kernel<V, uint32_t>, 256, 0) != cudaSuccess or n < 1)
+            n = 4;
+        return n;
+    }();
+    const int64_t cap = static_cast<int64_t>(device_sm_count()) * resident;
+    const int grid    = static_cast<int>(blocks < cap ? blocks : cap);
     if(a.total < (int64_t{1} << 31))
         pointwise_kernel<V, uint32_t><<<grid, 256, 0, stream>>>(a);
     else

@@ -355,6 +355,17 @@ __global__ void __launch_bounds__(256) softmax_rows_vec_kernel(const T* __restri
     }
 }
 
+// blocks of 256 threads that are resident at once on the whole device, at most `blocks`
+template <class K>
+static int resident_grid(K kernel, int64_t blocks)
+{
+    int n = 0;
+    if(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 256, 0) != cudaSuccess or n < 1)
+        n = 4;
+    const int64_t cap = static_cast<int64_t>(device_sm_count()) * n;
+    return static_cast<int>(blocks < cap ? blocks : cap);
+}
+
 template <class T>
 static bool rows_vectorisable(const void* p, int64_t ld, int64_t cols)
 {
@@ -409,22 +420,28 @@ int launch_softmax(const void* x, int64_t ldx, void* y, int64_t ldy, int64_t row
     {
         constexpr int N  = vec_of<T>::n;
         const int64_t nv = cols / N;
-        const int gw     = static_cast<int>(ceil_div(rows, int64_t{8}) < 148 * 8 ? ceil_div(rows, int64_t{8}) : 148 * 8);
         bool done        = true;
+        // grid = one wave of resident blocks (the kernels loop over rows)
+#define MGX_SOFTMAX(VPL, WPR)                                                                             \
+    {                                                                                                     \
+        auto k = softmax_rows_vec_kernel<T, VPL, WPR>;                                                    \
+        k<<<resident_grid(k, ceil_div(rows, int64_t{8 / WPR})), 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols); \
+    }
         if(nv <= 32)
-            softmax_rows_vec_kernel<T, 1, 1><<<gw, 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols);
+            MGX_SOFTMAX(1, 1)
         else if(nv <= 64)
-            softmax_rows_vec_kernel<T, 2, 1><<<gw, 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols);
+            MGX_SOFTMAX(2, 1)
         else if(nv <= 128)
-            softmax_rows_vec_kernel<T, 4, 1><<<gw, 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols);
+            MGX_SOFTMAX(4, 1)
         else if(nv <= 256)
-            softmax_rows_vec_kernel<T, 1, 8><<<grid, 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols);
+            MGX_SOFTMAX(1, 8)
         else if(nv <= 512)
-            softmax_rows_vec_kernel<T, 2, 8><<<grid, 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols);
+            MGX_SOFTMAX(2, 8)
         else if(nv <= 1024)
-            softmax_rows_vec_kernel<T, 4, 8><<<grid, 256, 0, s>>>(xp, ldx, yp, ldy, rows, cols);
+            MGX_SOFTMAX(4, 8)
         else
             done = false;
+#undef MGX_SOFTMAX
         if(done)
             return static_cast<int>(cudaGetLastError());
     }
