@@ -221,6 +221,16 @@ def secondary_measurements(dev, peaks):
                      "frac_of_4500_datasheet": tops / 4500.0,
                      "what": "M=N=K=8192, dequantizelinear + bias + GELU fused, fp32 out"}
         del a, b, d
+    # "next" row: dot on fp16 operands (attention, un-quantised linears), the same kernel with
+    # kind::f16 MMAs; fp32 accumulation, fp16 out
+    a = torch.randn((M, K), device=dev).half()
+    b = torch.randn((N, K), device=dev).half()
+    d = torch.empty((1, M, N), dtype=torch.float16, device=dev)
+    us = _graph_time_us(lambda: capi.qgemm(a, b, b_layout=capi.B_NK, out=d), 4, stream)
+    tf = 2.0 * M * N * K / us / 1e6
+    out["fp16_dot_8192"] = {"us": us, "tflops": tf, "frac_of_bf16_burst": tf / float(peaks["bf16_tflops"]),
+                            "what": "M=N=K=8192 fp16 x fp16 -> fp32 accumulate -> fp16 out"}
+    del a, b, d
     # config 3: the fp8 e4m3fn QDQ GEMM sweep (per-tensor scale, bias + GELU fused, fp32 out)
     sweep = {}
     for (n, k) in ((4096, 4096), (8192, 8192), (14336, 4096)):
