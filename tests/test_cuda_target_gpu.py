@@ -37,7 +37,8 @@ def test_program_matches_ref(cuda_device, case):
     assert res.get("pass"), res
 
 
-@pytest.mark.parametrize("case", ["c1_small", "int8_gelu", "int4_decode"])
+@pytest.mark.parametrize("case", ["c1_small", "int8_gelu", "int4_decode", "attention_f16", "bert_layer_int8",
+                                  "embed_rope_f16"])
 def test_program_matches_ref_with_offload_copy(cuda_device, case):
     res = _run(case, "offload")
     assert res.get("pass"), res
