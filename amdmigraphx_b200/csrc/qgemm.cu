@@ -297,7 +297,10 @@ __device__ __forceinline__ void truncate4_to_half_precision(float (&v)[4])
 // range, all accesses are vectors, the scale is per column or per tensor (already in sc4; 1.0 when
 // there is none), bi4 is -0.0 without a bias (x + -0.0 == x for every x), an optional
 // quantizelinear output is int8 with 4-byte aligned rows.  Same arithmetic as epi_store_chunk.
-template <bool IS_INT, class OutT, int ACT>
+// MODE 1: residual / quantizelinear / D chosen by the launch's parameters; 2: D only;
+// 3: residual, D and quantizelinear; 4: quantizelinear only (the combinations of an encoder
+// layer's four GEMMs get branch-free loops of their own).
+template <bool IS_INT, class OutT, int ACT, int MODE>
 __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t col, float4 sc4, float4 bi4)
 {
     const qgemm_params& p = *e.p;
@@ -310,9 +313,12 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     const OutT* res       = static_cast<const OutT*>(p.residual) + off;
     uint8_t* qdst = static_cast<uint8_t*>(p.Dq) + e.batch_off_q + (e.row0 + rsub) * p.ldq + col + pc * 4;
     const int64_t dstep = 8 * p.ldd, qstep = 8 * p.ldq;
-    const bool has_res = p.residual != nullptr, has_q = p.Dq != nullptr, wr = p.write_d != 0;
-    const bool acc24   = p.acc24 != 0;
-    const bool q_mask  = has_q and p.q_mask != 0;
+    // 5 = 2 and 6 = 4 with accumulators below 2^24 (and the mantissa-cut quantizelinear input)
+    const bool has_res = MODE == 1 ? p.residual != nullptr : MODE == 3;
+    const bool has_q   = MODE == 1 ? p.Dq != nullptr : (MODE == 3 or MODE == 4 or MODE == 6);
+    const bool wr      = MODE == 1 ? p.write_d != 0 : (MODE != 4 and MODE != 6);
+    const bool acc24   = MODE >= 5 ? true : p.acc24 != 0;
+    const bool q_mask  = MODE == 6 ? true : (has_q and p.q_mask != 0);
     // saturation before rounding: bounds are integers, so round-to-nearest stays inside
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
     const int q_bias = static_cast<int>(p.q_zp) - 0x4B400000;
@@ -424,7 +430,7 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
 // tile's columns.  Per 16-column chunk: tcgen05.ld (one row per thread) -> swizzled shared
 // memory -> read back with 4 lanes per 64-byte row segment -> dequantizelinear / bias /
 // activation / residual -> coalesced global stores.
-template <int BN, bool IS_INT, class OutT, int ACT, bool FAST>
+template <int BN, bool IS_INT, class OutT, int ACT, int MODE>
 __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* epi_base,
                                               uint64_t* accf_bar, uint64_t* acce_bar,
                                               volatile uint32_t* abort_flag, uint32_t tmem_base,
@@ -464,7 +470,7 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
         // code would be bound by instruction fetch.
         auto load_sb = [&](int ch, float4& sc, float4& bi) {
             sc = make_float4(tensor_scale, tensor_scale, tensor_scale, tensor_scale);
-            bi = FAST ? make_float4(-0.f, -0.f, -0.f, -0.f) : make_float4(0.f, 0.f, 0.f, 0.f);
+            bi = MODE != 0 ? make_float4(-0.f, -0.f, -0.f, -0.f) : make_float4(0.f, 0.f, 0.f, 0.f);
             if constexpr(not std::is_same<OutT, int32_t>::value)
             {
                 const int64_t c4 = col0 + ch * EPI_COLS + (lane & 3) * 4;
@@ -541,8 +547,8 @@ __device__ __forceinline__ void epilogue_role(const qgemm_params& p, uint8_t* ep
                     *reinterpret_cast<uint4*>(my_row + ((q ^ my_swz) * 16)) =
                         make_uint4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
                 __syncwarp();
-                if constexpr(FAST and not std::is_same<OutT, int32_t>::value)
-                    epi_store_chunk_fast<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
+                if constexpr(MODE != 0 and not std::is_same<OutT, int32_t>::value)
+                    epi_store_chunk_fast<IS_INT, OutT, ACT, MODE>(e, col, sc_cur, bi_cur);
                 else
                     epi_store_chunk<IS_INT, OutT, ACT>(e, col, sc_cur, bi_cur);
             }
@@ -707,13 +713,27 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         grid_dependency_wait();
         // the check-free variant is chosen once per launch: the tile loop a warp runs holds
         // only the store path it takes
-#define MGX_EPILOGUE(ACT)                                                                                   \
-    if(p.fast)                                                                                              \
-        epilogue_role<BN, IS_INT, OutT, ACT, true>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base,  \
-                                                   warp, lane, first_tile, tile_step, tiles_mn);            \
-    else                                                                                                    \
-        epilogue_role<BN, IS_INT, OutT, ACT, false>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base, \
-                                                    warp, lane, first_tile, tile_step, tiles_mn)
+#define MGX_EPI_MODE(ACT, MODE)                                                                           \
+    epilogue_role<BN, IS_INT, OutT, ACT, MODE>(p, epi_base, accf_bar, acce_bar, abort_flag, tmem_base, warp, \
+                                               lane, first_tile, tile_step, tiles_mn)
+#define MGX_EPILOGUE(ACT)                    \
+    switch(mode)                             \
+    {                                        \
+    case 0: MGX_EPI_MODE(ACT, 0); break;     \
+    case 2: MGX_EPI_MODE(ACT, 2); break;     \
+    case 3: MGX_EPI_MODE(ACT, 3); break;     \
+    case 4: MGX_EPI_MODE(ACT, 4); break;     \
+    case 5: MGX_EPI_MODE(ACT, 5); break;     \
+    case 6: MGX_EPI_MODE(ACT, 6); break;     \
+    default: MGX_EPI_MODE(ACT, 1); break;    \
+    }
+        const bool m_res = p.residual != nullptr, m_q = p.Dq != nullptr, m_wr = p.write_d != 0;
+        const bool m_24  = IS_INT and p.acc24 != 0;
+        const int mode   = p.fast == 0 ? 0
+                           : (not m_res and not m_q and m_wr) ? (m_24 ? 5 : 2)
+                           : (m_res and m_q and m_wr)         ? 3
+                           : (not m_res and m_q and not m_wr) ? ((m_24 and p.q_mask != 0) ? 6 : 4)
+                                                              : 1;
         switch(std::is_same<OutT, int32_t>::value ? MGX_ACT_NONE : p.act)
         {
         case MGX_ACT_RELU: MGX_EPILOGUE(MGX_ACT_RELU); break;
@@ -723,6 +743,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         default: MGX_EPILOGUE(MGX_ACT_NONE); break;
         }
 #undef MGX_EPILOGUE
+#undef MGX_EPI_MODE
     }
 
     // ---------------------------------------------------------- teardown
