@@ -462,10 +462,10 @@ def run_own_arm(args):
                              "(> 126 MB L2 in total)",
                        "parallelism": f"{world} independent replicas, batch-sharded, no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak8, "unit": "TFLOP/s",
-                         "frac": achieved / peak8, "traffic": 4831488,
+                         "frac": achieved / peak8, "traffic": 4846848,
                          "traffic_note": "dram__bytes_read + write of one FFN1-shaped launch (3072x3072x768, GELU + "
                                          "fused quantizelinear) from the ncu capture summarised under profiles/: "
-                                         "4.82 MB read, 0.01 MB written (the 9.4 MB int8 output stays in the 126 MB "
+                                         "4.84 MB read, 0.005 MB written (the 9.4 MB int8 output stays in the 126 MB "
                                          "L2); algorithmic operand bytes 4.72 MB",
                          "kernel": "qgemm_kernel (tcgen05 kind::i8): the 48 quant_dot launches of a step replayed "
                                    "as a graph of their own, fused epilogues included",
