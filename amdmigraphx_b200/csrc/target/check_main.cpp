@@ -441,6 +441,31 @@ test_case layernorm(shape::type_t type, std::size_t b, std::size_t sq, std::size
     return t;
 }
 
+// reductions over axes other than the innermost one: global average pooling over two trailing
+// axes, a sum over the middle axis, a maximum over the outermost.
+test_case reduce_axes(unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const shape xs{shape::float_type, {6, 20, 48}};
+    auto x  = mm->add_parameter("x", xs);
+    auto gp = mm->add_instruction(migraphx::make_op("reduce_mean", {{"axes", {1, 2}}}), x);
+    auto sm = mm->add_instruction(migraphx::make_op("reduce_sum", {{"axes", {1}}}), x);
+    auto mx = mm->add_instruction(migraphx::make_op("reduce_max", {{"axes", {0}}}), x);
+    auto mn = mm->add_instruction(migraphx::make_op("reduce_min", {{"axes", {0, 2}}}), x);
+    // consumers, so that the views are read by kernels too
+    auto s2 = mm->add_instruction(migraphx::make_op("add"), sm, mbcast(mm, gp, sm->get_shape().lens()));
+    mm->add_return({s2, mx, mn, gp});
+    auto v = rand_normal(g, xs.elements(), 1.0f);
+    migraphx::argument arg{xs};
+    std::memcpy(arg.data(), v.data(), v.size() * sizeof(float));
+    t.params["x"] = arg;
+    t.rtol = 1e-5;
+    t.atol = 2e-5;
+    return t;
+}
+
 // softmax over the innermost axis of attention-score shaped input [batch, heads, q, k].
 test_case softmax_rows(shape::type_t type, std::size_t b, std::size_t h, std::size_t q, std::size_t k, unsigned seed)
 {
@@ -712,6 +737,7 @@ std::map<std::string, std::function<test_case()>> cases()
         {"pw_transcendental_f32", [] { return pw_transcendental_f32(11); }},
         {"layernorm_f32", [] { return layernorm(shape::float_type, 2, 48, 768, 12); }},
         {"layernorm_f16", [] { return layernorm(shape::half_type, 3, 20, 1000, 13); }},
+        {"reduce_axes", [] { return reduce_axes(24); }},
         {"softmax_f32", [] { return softmax_rows(shape::float_type, 2, 4, 56, 200, 14); }},
         {"softmax_f16", [] { return softmax_rows(shape::half_type, 1, 3, 40, 1500, 15); }},
         {"softmax_f32_long", [] { return softmax_rows(shape::float_type, 1, 1, 6, 9000, 16); }},

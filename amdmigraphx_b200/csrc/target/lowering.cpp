@@ -684,22 +684,59 @@ struct lowerer
             if(ax != -1 and ax != nd - 1)
                 unsupported(ins, "only the innermost axis is supported");
         }
-        else
-        {
-            const auto axes = v.at("axes").to_vector<int64_t>();
-            if(axes.size() != 1 or (axes[0] != -1 and axes[0] != nd - 1))
-                unsupported(ins, "only the innermost axis is supported");
-        }
-        if(not xs.standard())
-            unsupported(ins, "input must be a standard tensor");
         if(xs.type() != shape::float_type and xs.type() != shape::half_type)
             unsupported(ins, "float and half only");
         auto args = ins->inputs();
-        args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
         if(softmax)
+        {
+            if(not xs.standard())
+                args[0] = standard_copy(ins, args[0]);
+            args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
             consume(m.replace_instruction(ins, op_softmax{}, args));
-        else
+            return true;
+        }
+        // reductions: the reduced axes become the trailing ones of a packed tensor
+        std::vector<bool> reduced(nd, false);
+        for(auto a : v.at("axes").to_vector<int64_t>())
+        {
+            a = a < 0 ? a + nd : a;
+            if(a < 0 or a >= nd)
+                unsupported(ins, "axis out of range");
+            reduced[a] = true;
+        }
+        std::vector<int64_t> perm;
+        for(int64_t d = 0; d < nd; ++d)
+            if(not reduced[d])
+                perm.push_back(d);
+        const std::size_t kept = perm.size();
+        for(int64_t d = 0; d < nd; ++d)
+            if(reduced[d])
+                perm.push_back(d);
+        if(kept == static_cast<std::size_t>(nd))
+            unsupported(ins, "no axis to reduce");
+        bool trailing = true;
+        for(int64_t d = 0; d < nd; ++d)
+            if(perm[d] != d)
+                trailing = false;
+        if(trailing)
+        {
+            if(not xs.standard())
+                args[0] = standard_copy(ins, args[0]);
+            args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
             consume(m.replace_instruction(ins, op_reduce{it->second}, args));
+            return true;
+        }
+        // other axes: a transposed packed copy first; the result (reduced dimensions of length 1)
+        // has the element order of the operator's output, so a view gives it its dimensions
+        auto xt = m.insert_instruction(ins, make_op("transpose", {{"permutation", perm}}), args[0]);
+        auto xc = standard_copy(ins, xt);
+        auto ol = xc->get_shape().lens();
+        for(std::size_t d = kept; d < ol.size(); ++d)
+            ol[d] = 1;
+        auto buf = insert_allocation(m, ins, shape{xs.type(), ol});
+        auto red = m.insert_instruction(ins, op_reduce{it->second}, xc, buf);
+        consume(red);
+        m.replace_instruction(ins, make_op("reshape_lazy", {{"dims", ins->get_shape().lens()}}), red);
         return true;
     }
 

@@ -444,10 +444,21 @@ shape op_reduce::compute_shape(const std::vector<shape>& inputs) const
 {
     check_shapes{inputs, *this}.has(2);
     check_rows(name(), inputs[0]);
-    auto lens   = inputs[0].lens();
-    lens.back() = 1;
-    if(inputs[1].lens() != lens or inputs[1].type() != inputs[0].type() or not inputs[1].standard())
-        MIGRAPHX_THROW("cuda::reduce: output must be the packed input with a last dimension of 1");
+    // the output is the packed input with its trailing dimensions (at least the last) set to 1
+    const auto& xl = inputs[0].lens();
+    const auto& ol = inputs[1].lens();
+    bool ok        = ol.size() == xl.size() and ol.back() == 1 and inputs[1].type() == inputs[0].type() and
+              inputs[1].standard();
+    bool tail = true; // still inside the reduced trailing dimensions
+    for(std::size_t i = xl.size(); ok and i-- > 0;)
+    {
+        if(tail and ol[i] == 1)
+            continue;
+        tail = false;
+        ok   = ol[i] == xl[i];
+    }
+    if(not ok)
+        MIGRAPHX_THROW("cuda::reduce: output must be the packed input with trailing dimensions of 1");
     return inputs[1];
 }
 
@@ -457,8 +468,8 @@ argument op_reduce::compute(context& ctx, const shape&, const std::vector<argume
     if(ctx.replaying())
         return out;
     const auto& xs     = args[0].get_shape();
-    const int64_t cols = static_cast<int64_t>(xs.lens().back());
-    const int64_t rows = static_cast<int64_t>(xs.elements()) / cols;
+    const int64_t rows = static_cast<int64_t>(out.get_shape().elements());
+    const int64_t cols = static_cast<int64_t>(xs.elements()) / rows;
     check_mgx(mgx_cuda_reduce(args[0].data(), mgx_type(xs.type()), cols, rows, cols, mode, out.data(), ctx.stream()),
               "mgx_cuda_reduce");
     return out;

@@ -20,7 +20,7 @@ CASES = ["c1_small", "c1_semantic", "int8_gelu", "int8_per_tensor", "fp8_gelu", 
          "pw_gelu_f16", "pw_arith_f32", "pw_transcendental_f32",
          "layernorm_f32", "layernorm_f16", "softmax_f32", "softmax_f16", "softmax_f32_long",
          "attention_f16", "dot_f16_const", "dot_f16_batched", "bert_layer_int8", "embed_rope_f16",
-         "dot_f16_odd_k", "dot_f16_odd_k_const"]
+         "dot_f16_odd_k", "dot_f16_odd_k_const", "reduce_axes"]
 
 
 def _run(case, mode=None):

@@ -136,3 +136,11 @@ def test_fp16_dot_with_unaligned_inner_dimension_pads_rows():
     # 13 is no multiple of 8: the constant stays [K,N] and is re-laid out per evaluation
     line = [l for l in out.splitlines() if "cuda::qgemm" in l][0]
     assert "b_nk=0" in line and "has_workspace=1" in line and "cuda::pad_rows" in out
+
+
+def test_reductions_over_other_axes_use_a_transposed_copy():
+    out = _passes("reduce_axes")
+    # trailing axes {1, 2}: reduced in place; axis 1, axis 0 and axes {0, 2}: transposed copy first
+    assert out.count("cuda::reduce[") == 4
+    assert out.count("transpose[") == 3 and out.count("cuda::pointwise[ops={32}") == 3
+    assert "reshape_lazy[dims={6, 1, 48}]" in out and "reshape_lazy[dims={1, 20, 1}]" in out
