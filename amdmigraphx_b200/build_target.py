@@ -3,9 +3,10 @@ driver bin/cuda_target_check.
 
 The plug-in is host C++17 compiled against MIGraphX's headers and linked to libmigraphx.so
 and to the kernel library.  MIGraphX itself is not part of this repository: the headers
-are taken from a MIGraphX source tree (MIGRAPHX_SOURCE_DIR) and
-the library from MIGRAPHX_LIB_DIR (default oracle/_ref/lib, where oracle/build_ref.py puts
-its build of the unmodified sources).  When the headers are absent (for example on a GPU
+are taken from a MIGraphX source tree (MIGRAPHX_SOURCE_DIR, default: a directory named
+`reference` next to this repository) and the library from MIGRAPHX_LIB_DIR (default
+baseline/_ref/lib, where oracle/build_ref.py puts its build of the unmodified sources; the
+parity driver also links MIGraphX's CPU `ref` target from oracle/_ref/lib).  When the headers are absent (for example on a GPU
 box that only received the prebuilt files) the existing binaries are kept.
 """
 import concurrent.futures as cf
@@ -21,13 +22,14 @@ BIN = os.path.join(PKG, "bin")
 OBJ = os.path.join(PKG, "build")
 TARGET_LIB = os.path.join(LIB, "libmigraphx_cuda.so")
 CHECK_BIN = os.path.join(BIN, "cuda_target_check")
+RUNNER_LIB = os.path.join(LIB, "libmgx_cuda_runner.so")
 SOURCES = ["runtime.cpp", "ops_compute.cpp", "lowering.cpp", "target.cpp"]
 
 
 def _paths():
-    mgx_src = os.environ.get("MIGRAPHX_SOURCE_DIR", "/root/reference")
-    mgx_lib = os.environ.get("MIGRAPHX_LIB_DIR", os.path.join(ROOT, "oracle", "_ref", "lib"))
-    gen = os.environ.get("MIGRAPHX_GENERATED_INCLUDE", os.path.join(ROOT, "oracle", "_ref", "gen", "include"))
+    mgx_src = os.environ.get("MIGRAPHX_SOURCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+    mgx_lib = os.environ.get("MIGRAPHX_LIB_DIR", os.path.join(ROOT, "baseline", "_ref", "lib"))
+    gen = os.environ.get("MIGRAPHX_GENERATED_INCLUDE", os.path.join(ROOT, "baseline", "_ref", "gen", "include"))
     return mgx_src, mgx_lib, gen
 
 
@@ -67,20 +69,31 @@ def build_target(verbose=False, force=False):
         cmd = ["g++", "-shared", "-o", TARGET_LIB] + objs + [
             f"-L{LIB}", "-lmgx_cuda_kernels", f"-L{mgx_lib}", "-lmigraphx",
             f"-L{cuda_lib}", "-lcudart",
-            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../oracle/_ref/lib", f"-Wl,-rpath,{cuda_lib}"]
+            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../baseline/_ref/lib", f"-Wl,-rpath,{cuda_lib}"]
         subprocess.check_call(cmd)
         # register_target.cpp:61-79 looks for libmigraphx_<name>.so.<SOMAJOR> first
         link = TARGET_LIB + ".2016000"
         if os.path.lexists(link):
             os.unlink(link)
         os.symlink(os.path.basename(TARGET_LIB), link)
+    # the benchmark's window onto program::compile / program::eval (links the plug-in only)
+    runner_src = os.path.join(SRC, "runner.cpp")
+    if os.path.exists(runner_src) and (force or _newer(RUNNER_LIB, [runner_src, TARGET_LIB] + headers)):
+        cmd = ["g++", "-shared", runner_src, "-o", RUNNER_LIB] + flags + [
+            f"-L{LIB}", f"-L{mgx_lib}", "-Wl,--no-as-needed", "-lmigraphx_cuda", "-lmigraphx",
+            f"-L{cuda_lib}", "-lcudart", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../baseline/_ref/lib",
+            f"-Wl,-rpath,{cuda_lib}"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed for {runner_src}:\n{r.stderr[-6000:]}")
     check_src = os.path.join(SRC, "check_main.cpp")
     if os.path.exists(check_src) and (force or _newer(CHECK_BIN, [check_src, TARGET_LIB] + headers)):
+        ref_lib = os.path.join(ROOT, "oracle", "_ref", "lib")  # the checker: MIGraphX's CPU ref target
         cmd = ["g++", check_src, "-o", CHECK_BIN] + flags + [
-            f"-L{LIB}", f"-L{mgx_lib}", "-Wl,--no-as-needed", "-lmigraphx_cuda", "-lmigraphx_ref",
+            f"-L{LIB}", f"-L{mgx_lib}", f"-L{ref_lib}", "-Wl,--no-as-needed", "-lmigraphx_cuda", "-lmigraphx_ref",
             "-lmigraphx", "-lmgx_cuda_kernels", f"-L{cuda_lib}", "-lcudart",
-            "-Wl,-rpath,$ORIGIN/../lib", "-Wl,-rpath,$ORIGIN/../../oracle/_ref/lib",
-            f"-Wl,-rpath,{cuda_lib}"]
+            "-Wl,-rpath,$ORIGIN/../lib", "-Wl,-rpath,$ORIGIN/../../baseline/_ref/lib",
+            "-Wl,-rpath,$ORIGIN/../../oracle/_ref/lib", f"-Wl,-rpath,{cuda_lib}"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"g++ failed for {check_src}:\n{r.stderr[-6000:]}")

@@ -29,7 +29,7 @@ EXPORTED_SYMBOLS = [
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
-    "mgx_cuda_status_string", "mgx_cuda_version",
+    "mgx_cuda_status_string", "mgx_cuda_version", "mgx_cuda_selftest_bounded_wait",
     "mgx_cuda_comm_unique_id", "mgx_cuda_comm_create", "mgx_cuda_comm_destroy",
     "mgx_cuda_comm_set_default", "mgx_cuda_comm_default", "mgx_cuda_all_reduce",
 ]
@@ -89,6 +89,7 @@ def load():
     lib.mgx_cuda_qgemm.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.mgx_cuda_qgemm_ex.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp,
                                       ctypes.POINTER(QgemmQout), vp, sz, vp]
+    lib.mgx_cuda_selftest_bounded_wait.argtypes = [ctypes.c_uint64, vp, vp]
     lib.mgx_cuda_qgemm_static_scratch_limit.restype = sz
     lib.mgx_cuda_qgemm_static_scratch.argtypes = [ctypes.POINTER(QgemmDesc), vp, vp, vp, vp, vp, vp, vp]
     lib.mgx_cuda_transpose_8bit.argtypes = [vp, vp, i64, i64, i64, vp]

@@ -664,6 +664,9 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         {
             constexpr uint32_t idesc = IS_INT ? make_idesc(2u, 1u, 1u, BM, BN)  // s32 += s8*s8
                                               : make_idesc(1u, 0u, 0u, BM, BN); // f32 += e4m3*e4m3 (f16*f16)
+            // the operands arrive only after the previous kernel of the stream is done: the
+            // bounded waits below must not count that time
+            grid_dependency_wait();
             uint32_t it = 0;
             uint32_t lt = 0; // local tile counter
             bool ok     = true;
@@ -1126,9 +1129,18 @@ extern "C" int mgx_cuda_qgemm_static_scratch(const mgx_qgemm_desc* d, const void
 {
     if(d == nullptr)
         return MGX_E_INVALID_ARG;
-    const size_t need = mgx_cuda_qgemm_workspace(d);
+    if(d->M <= 0 or d->N <= 0 or d->K <= 0 or d->batch <= 0)
+        return MGX_E_INVALID_ARG;
+    size_t need = mgx_cuda_qgemm_workspace(d);
     if(need > static_scratch_bytes)
-        return MGX_E_TOO_LARGE;
+    {
+        // a [K,N] operand has to be re-laid out into the scratch: no way around the limit.
+        // For [N,K] operands the scratch only enables the weight-streaming kernel for at most
+        // 16 rows; beyond the limit the tiled kernel runs, which needs none.
+        if(d->b_layout == MGX_B_KN)
+            return MGX_E_TOO_LARGE;
+        need = 0;
+    }
     void* scratch = nullptr;
     if(need > 0)
     {

@@ -161,6 +161,7 @@ __global__ void __launch_bounds__(GV_THREADS, 1)
             int tile, kb0, count;
             bool ok = true;
             int i   = 0;
+            grid_dependency_wait(); // the bounded waits below must not count the previous kernel's time
             for(uint32_t sc = 0; ok and walk.next(tile, kb0, count); ++sc)
             {
                 const uint32_t buf = sc & 1u;

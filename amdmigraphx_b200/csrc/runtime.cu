@@ -1,10 +1,32 @@
 // Library-wide host helpers: driver entry point lookup, per-device caches,
 // status reporting.
 #include "common.cuh"
+#include "ptx.cuh"
 #include <atomic>
 #include <mutex>
 
 namespace mgx {
+
+// One thread waits, with a time limit, on a barrier phase that nothing ever completes: the
+// expiry path every kernel of this library shares (status word written, abort flag raised, the
+// kernel returns normally) exercised by itself.  Nothing faults and the context stays usable.
+__global__ void bounded_wait_probe_kernel(unsigned long long limit_ns, unsigned int code,
+                                          unsigned int* gave_up)
+{
+    __shared__ uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if(threadIdx.x == 0)
+    {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+        const bool done = mbar_wait_bounded(&bar, 0u, &abort_flag, code, limit_ns);
+        if(gave_up != nullptr)
+            *gave_up = done ? 0u : abort_flag;
+    }
+}
+
+static int runtime_status(unsigned int* out) { return read_and_clear_status(out); }
 
 cuTensorMapEncodeTiled_t get_tensor_map_encoder()
 {
@@ -74,8 +96,11 @@ extern "C" int mgx_cuda_device_status(int* status)
     cudaError_t e = cudaDeviceSynchronize();
     if(e != cudaSuccess)
         return static_cast<int>(e);
-    unsigned int a = 0, b = 0, c = 0, d = 0, g = 0;
-    int rc = mgx::qgemm_status(&a);
+    unsigned int a = 0, b = 0, c = 0, d = 0, g = 0, r = 0;
+    int rc = mgx::runtime_status(&r);
+    if(rc != 0)
+        return rc;
+    rc = mgx::qgemm_status(&a);
     if(rc != 0)
         return rc;
     rc = mgx::w4a16_status(&b);
@@ -90,8 +115,17 @@ extern "C" int mgx_cuda_device_status(int* status)
     rc = mgx::qgemv_status(&g);
     if(rc != 0)
         return rc;
-    *status = static_cast<int>(a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : g))));
+    *status = static_cast<int>(a != 0 ? a : (b != 0 ? b : (c != 0 ? c : (d != 0 ? d : (g != 0 ? g : r)))));
     return MGX_OK;
+}
+
+extern "C" int mgx_cuda_selftest_bounded_wait(uint64_t limit_ns, void* gave_up, void* stream)
+{
+    if(limit_ns == 0 or limit_ns > 100000000ull)
+        return MGX_E_INVALID_ARG; // at most 0.1 s: this is a probe, not a way to park a GPU
+    mgx::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        limit_ns, 99u, static_cast<unsigned int*>(gave_up));
+    return static_cast<int>(cudaGetLastError());
 }
 
 extern "C" const char* mgx_cuda_status_string(int code)

@@ -53,6 +53,9 @@ struct context_state
     cudaEvent_t begin_event  = nullptr;
     cudaEvent_t finish_event = nullptr;
     std::unordered_map<std::string, argument> preallocations;
+    // page-locked host buffers handed out for results copied back to the host (offload_copy):
+    // a buffer is reused once the caller has dropped the argument that referred to it
+    std::vector<std::pair<std::size_t, std::shared_ptr<void>>> host_pool;
     bool ready = false;
     // CUDA-graph replay of the instruction stream (cuda::graph_begin / cuda::graph_end)
     enum class graph_mode
@@ -85,6 +88,8 @@ struct MGX_CUDA_EXPORT context
     cudaStream_t stream() const;
     void set_stream(std::size_t n);
     cudaEvent_t event(std::size_t id);
+    // page-locked host buffer of s.bytes() that nobody else holds (see context_state::host_pool)
+    argument pinned_host(const shape& s);
     void store_preallocation(const std::string& id, const argument& a);
     argument get_preallocation(const std::string& id) const;
     // true while a captured graph stands in for the instruction stream: operators that would
@@ -177,8 +182,9 @@ struct fuse_cuda_pointwise
 // cuda::graph_end: from the third eval() on, the whole instruction stream is one
 // cudaGraphLaunch as long as the caller passes the same parameter buffers (host time per
 // eval() is then independent of the number of instructions; src/program.cpp:472-565 is the
-// loop this short-cuts).  Not applied with offload_copy, several streams or collectives;
-// MIGRAPHX_CUDA_GRAPH=0 turns it off.
+// loop this short-cuts).  With offload_copy the bracket lies between the last host-to-device and
+// the first device-to-host copy (the copies' device buffers are arena addresses, which never
+// change).  Not applied with several streams or collectives; MIGRAPHX_CUDA_GRAPH=0 turns it off.
 struct insert_graph_ops
 {
     context* ctx      = nullptr;

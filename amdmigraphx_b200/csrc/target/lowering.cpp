@@ -81,8 +81,8 @@ struct const_vector
     std::vector<float> values; // 1, cols or rows values
 };
 
-// Classifies a constant of the data tensor's dims seen as [rows, cols].
-const_vector classify_constant(instruction_ref ins)
+// Classifies a constant of the data tensor's dims seen as [rows, cols] by evaluating all of it.
+const_vector classify_constant_dense(instruction_ref ins)
 {
     const auto& s    = ins->get_shape();
     const auto vals  = eval_as_floats(ins);
@@ -121,6 +121,90 @@ const_vector classify_constant(instruction_ref ins)
             r.values[i] = vals[i * cols];
     }
     return r;
+}
+
+// The same answer read off the structure of the expression where that is possible - broadcasts
+// of small literals and fp32 products of them, which is what simplify_qdq builds for scales
+// (src/simplify_qdq.cpp:243-248) and what biases and scalar constants look like - so that a
+// [tokens, features] view of a handful of numbers is never materialised.  false: not recognised.
+bool classify_structural(instruction_ref ins, const_vector& out)
+{
+    const auto& s  = ins->get_shape();
+    const auto nd  = s.ndim();
+    const auto name = ins->name();
+    if(nd == 0 or s.elements() == 0)
+        return false;
+    if(name == "multibroadcast" or name == "broadcast")
+    {
+        auto x = ins->inputs().front();
+        if(not x->can_eval() or ins->inputs().size() != 1)
+            return false;
+        const auto& st = s.strides();
+        const auto& ln = s.lens();
+        std::size_t moving = 0, axis = 0; // axes the view actually steps along
+        for(std::size_t i = 0; i < nd; ++i)
+            if(ln[i] != 1 and st[i] != 0)
+            {
+                ++moving;
+                axis = i;
+            }
+        if(moving > 1)
+            return false;
+        const auto vals = eval_as_floats(x);
+        if(moving == 0)
+        {
+            if(vals.empty())
+                return false;
+            out.kind   = bcast_kind::scalar;
+            out.values = {vals[0]};
+            return true;
+        }
+        if(vals.size() != ln[axis] or st[axis] != 1)
+            return false;
+        if(axis == nd - 1)
+            out.kind = bcast_kind::per_col;
+        else if(axis == nd - 2 and nd == 2)
+            out.kind = bcast_kind::per_row;
+        else
+            return false;
+        out.values = vals;
+        return true;
+    }
+    if(name == "mul" and s.type() == shape::float_type and ins->inputs().size() == 2)
+    {
+        const_vector a, b;
+        if(not classify_structural(ins->inputs()[0], a) or not classify_structural(ins->inputs()[1], b))
+            return false;
+        if(a.kind == bcast_kind::scalar)
+            std::swap(a, b);
+        if(b.kind != bcast_kind::scalar and b.kind != a.kind)
+            return false;
+        out.kind = a.kind;
+        out.values.resize(a.values.size());
+        for(std::size_t i = 0; i < a.values.size(); ++i)
+            out.values[i] = a.values[i] * (b.kind == bcast_kind::scalar ? b.values[0] : b.values[i]);
+        // a vector whose entries are all equal is a scalar to the kernels
+        return true;
+    }
+    return false;
+}
+
+const_vector classify_constant(instruction_ref ins)
+{
+    const_vector r;
+    if(classify_structural(ins, r))
+    {
+        if(r.kind != bcast_kind::scalar and not r.values.empty() and
+           std::all_of(r.values.begin(), r.values.end(), [&](float v) {
+               return std::memcmp(&v, &r.values[0], sizeof(float)) == 0;
+           }))
+        {
+            r.kind   = bcast_kind::scalar;
+            r.values = {r.values[0]};
+        }
+        return r;
+    }
+    return classify_constant_dense(ins);
 }
 
 bool is_const_scalar(instruction_ref ins, float expect, float tol)
@@ -195,22 +279,42 @@ instruction_ref add_transposed_8bit_literal(module& m, instruction_ref b)
     const std::size_t es = s.type_size();
     std::vector<char> out(batch * n * k * es);
     const char* src = a.data();
-    std::vector<std::size_t> idx(nd, 0);
-    for(std::size_t bi = 0; bi < batch; ++bi)
+    if(s.standard() and (es == 1 or es == 2))
     {
-        std::size_t rem = bi;
-        for(std::size_t d = nd - 2; d-- > 0;)
+        // packed input: a blocked transpose per batch entry
+        constexpr std::size_t tb = 64;
+        auto run = [&](auto* dst, const auto* sp) {
+            for(std::size_t bi = 0; bi < batch; ++bi)
+                for(std::size_t k0 = 0; k0 < k; k0 += tb)
+                    for(std::size_t n0 = 0; n0 < n; n0 += tb)
+                        for(std::size_t nn = n0; nn < std::min(n, n0 + tb); ++nn)
+                            for(std::size_t kk = k0; kk < std::min(k, k0 + tb); ++kk)
+                                dst[(bi * n + nn) * k + kk] = sp[(bi * k + kk) * n + nn];
+        };
+        if(es == 1)
+            run(reinterpret_cast<uint8_t*>(out.data()), reinterpret_cast<const uint8_t*>(src));
+        else
+            run(reinterpret_cast<uint16_t*>(out.data()), reinterpret_cast<const uint16_t*>(src));
+    }
+    else
+    {
+        std::vector<std::size_t> idx(nd, 0);
+        for(std::size_t bi = 0; bi < batch; ++bi)
         {
-            idx[d] = rem % lens[d];
-            rem /= lens[d];
-        }
-        for(std::size_t kk = 0; kk < k; ++kk)
-        {
-            idx[nd - 2] = kk;
-            for(std::size_t nn = 0; nn < n; ++nn)
+            std::size_t rem = bi;
+            for(std::size_t d = nd - 2; d-- > 0;)
             {
-                idx[nd - 1] = nn;
-                std::memcpy(&out[((bi * n + nn) * k + kk) * es], src + s.index(idx) * es, es);
+                idx[d] = rem % lens[d];
+                rem /= lens[d];
+            }
+            for(std::size_t kk = 0; kk < k; ++kk)
+            {
+                idx[nd - 2] = kk;
+                for(std::size_t nn = 0; nn < n; ++nn)
+                {
+                    idx[nd - 1] = nn;
+                    std::memcpy(&out[((bi * n + nn) * k + kk) * es], src + s.index(idx) * es, es);
+                }
             }
         }
     }
@@ -361,6 +465,15 @@ struct lowerer
         if(residual != m.end() and residual->get_shape().type() != last->get_shape().type())
             unsupported(last, "residual type differs from the output type");
 
+        // A: K-contiguous rows; with batch dimensions the entries must be evenly spaced, so a
+        // transposed / sliced view (heads of an attention block) is packed first
+        {
+            const auto& as = a->get_shape();
+            const auto nd  = as.ndim();
+            const bool rows_ok = as.strides()[nd - 1] == 1 and as.strides()[nd - 2] % 16 == 0;
+            if(not as.standard() and (nd > 2 or not rows_ok))
+                a = standard_copy(qd, a);
+        }
         // B operand: constants are re-laid out K-contiguous once, here
         std::vector<instruction_ref> args = {a, b};
         instruction_ref workspace = m.end();
@@ -514,18 +627,18 @@ struct lowerer
                         return false;
             return true;
         };
+        // every multiple of 32 that divides K is a candidate, largest first (K / group need
+        // not be a power of two: K = 11008 or 28672 with groups of 128)
         std::size_t group = 0;
-        for(std::size_t g = k; g >= 32; g /= 2)
+        for(std::size_t g = k / 32 * 32; g >= 32; g -= 32)
         {
-            if(k % g != 0 or g % 32 != 0)
+            if(k % g != 0)
                 continue;
             if(blocks_const(sv, g) and (zv.empty() or blocks_const(zv, g)))
             {
                 group = g;
                 break;
             }
-            if(g % 2 != 0)
-                break;
         }
         if(group == 0)
             unsupported(dot, "int4 group size must be a multiple of 32 dividing K");
@@ -1123,33 +1236,55 @@ void fuse_cuda_pointwise::apply(module& m) const
 void insert_graph_ops::apply(module& m) const
 {
     const char* env = std::getenv("MIGRAPHX_CUDA_GRAPH");
-    if(ctx == nullptr or offload_copy or ctx->nstreams() > 1 or (env != nullptr and env[0] == '0'))
+    if(ctx == nullptr or ctx->nstreams() > 1 or (env != nullptr and env[0] == '0'))
         return;
     auto launches = [](const std::string& n) {
         return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
                n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or
                n == "cuda::copy" or n == "cuda::pointwise" or n == "cuda::reduce" or n == "cuda::softmax" or
-               n == "cuda::gather" or n == "cuda::concat" or n == "cuda::pad_rows";
+               n == "cuda::gather" or n == "cuda::concat" or n == "cuda::pad_rows" or
+               n == "cuda::layernorm" or n == "cuda::attention";
     };
-    instruction_ref first = m.end();
-    std::size_t nlaunch   = 0;
+    instruction_ref first = m.end(), last_launch = m.end();
+    instruction_ref last_copy_to = m.end(), first_copy_from = m.end();
+    std::size_t nlaunch = 0;
     for(auto ins : iterator_for(m))
     {
         const auto n = ins->name();
-        // host copies, explicit synchronisation and collectives stay outside graphs
-        if(n == "cuda::copy_to" or n == "cuda::copy_from" or n == "cuda::all_reduce" or
-           n == "cuda::set_stream" or n == "cuda::record_event" or n == "cuda::wait_event")
+        // explicit synchronisation and collectives stay outside graphs
+        if(n == "cuda::all_reduce" or n == "cuda::set_stream" or n == "cuda::record_event" or
+           n == "cuda::wait_event")
             return;
+        if(n == "cuda::copy_to")
+        {
+            if(first != m.end())
+                return; // a host-to-device copy after the first launch: no single bracket
+            last_copy_to = ins;
+        }
+        if(n == "cuda::copy_from" and first_copy_from == m.end())
+            first_copy_from = ins;
         if(launches(n))
         {
+            if(first_copy_from != m.end())
+                return; // a launch after the first device-to-host copy
             if(first == m.end())
                 first = ins;
+            last_launch = ins;
             ++nlaunch;
         }
     }
     auto last = std::prev(m.end());
     if(nlaunch == 0 or last->name() != "@return" or last->inputs().empty())
         return;
+    if(offload_copy)
+    {
+        // host copies in, the bracket, host copies out.  The device sides of the copies are
+        // arena addresses, the same for every eval(), so the graph depends on no parameter.
+        m.insert_instruction(first, op_graph_begin{});
+        m.insert_instruction(std::next(last_launch), op_graph_end{});
+        ctx->enable_graph();
+        return;
+    }
     // graph_begin must see every parameter buffer: parameters (which views ahead of the first
     // launch may already use) move to the front of the module
     std::vector<instruction_ref> params;

@@ -258,7 +258,16 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
             b_shared = false;
     if(batch > 1)
     {
-        // batch entries must be evenly spaced: standard leading dimensions
+        // batch entries must be evenly spaced: the leading dimensions step like a standard
+        // tensor's (one stride serves every entry)
+        for(std::size_t j = 0; j + 3 < nd; ++j)
+        {
+            if(as.lens()[j] != 1 and as.strides()[j] != as.strides()[j + 1] * as.lens()[j + 1])
+                MIGRAPHX_THROW("cuda::qgemm: the batch entries of A are not evenly spaced");
+            if(not b_shared and bs.lens()[j] != 1 and
+               bs.strides()[j] != bs.strides()[j + 1] * bs.lens()[j + 1])
+                MIGRAPHX_THROW("cuda::qgemm: the batch entries of B are not evenly spaced");
+        }
         const auto rows_a = static_cast<int64_t>(as.strides()[nd - 3]);
         d.stride_a        = rows_a;
         d.stride_d        = d.M * d.N;

@@ -124,6 +124,19 @@ cudaEvent_t context::event(std::size_t id)
     return state->events[id];
 }
 
+argument context::pinned_host(const shape& s)
+{
+    const std::size_t bytes = s.bytes() + 1;
+    for(auto& e : state->host_pool)
+        if(e.first >= bytes and e.first <= 2 * bytes and e.second.use_count() == 1)
+            return argument{s, e.second};
+    void* p = nullptr;
+    check_cuda(cudaHostAlloc(&p, bytes, cudaHostAllocDefault), "cudaHostAlloc");
+    std::shared_ptr<void> owner(p, [](void* q) { (void)cudaFreeHost(q); });
+    state->host_pool.emplace_back(bytes, owner);
+    return argument{s, owner};
+}
+
 void context::store_preallocation(const std::string& id, const argument& a)
 {
     state->preallocations[id] = a;
@@ -349,7 +362,8 @@ shape op_copy_from::compute_shape(const std::vector<shape>& inputs) const
 }
 argument op_copy_from::compute(context& ctx, const shape& out, const std::vector<argument>& args) const
 {
-    argument host{out};
+    // page-locked, so that the copy runs at the link's speed and truly asynchronously
+    argument host = ctx.pinned_host(out);
     if(out.bytes() > 0)
     {
         check_cuda(cudaMemcpyAsync(host.data(), args[0].data(), out.bytes(), cudaMemcpyDeviceToHost,

@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1)
             const uint32_t d_tmem    = tmem_base + issuer * PF_TOKENS;
             uint32_t it = 0, lt = 0;
             bool ok     = true;
+            grid_dependency_wait(); // the bounded waits below must not count the previous kernel's time
             for(int t = blockIdx.x; ok and t < p.num_tiles; t += gridDim.x, ++lt)
             {
                 if(not mbar_wait_bounded(acce_bar, (lt & 1u) ^ 1u, abort_flag, 4))

@@ -401,6 +401,9 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
             bool seg_last;
             bool ok = true;
             int j   = 0;
+            // the activation planes come from the previous kernel of the stream: the bounded
+            // waits below must not count its run time
+            grid_dependency_wait();
             for(uint32_t pc = 0; ok and walk.next(GPP, tile, g0, count, seg_last); ++pc)
             {
                 const uint32_t buf = pc & 1u;

@@ -145,3 +145,67 @@ class BertInt8LinearStack(object):
                        q_out=self.xq if nxt is not None else None, q_lin=nxt)
             x = self.y
         return self.y
+
+
+class EncoderGemms(object):
+    """The quant_dot launches of one step of the BERT-shaped int8 encoder program, issued through
+    the C ABI with the shapes, epilogues and output types the `cuda` target's lowering gives them
+    (csrc/target/lowering.cpp): per layer the Q/K/V projections (one launch of N = 3 x hidden when
+    the lowering fuses them, else three), the attention output projection (+ residual), FFN1
+    (+ erf-GELU, only its int8 quantizelinear written) and FFN2 (+ residual); fp16 results.
+    The int8 inputs hold random data: this chain exists to time the dominant kernel by itself."""
+
+    def __init__(self, device, tokens, layers=12, hidden=768, ffn=3072, seed=0, qkv_fused=True):
+        import torch
+        rng = np.random.default_rng(seed)
+        self.tokens, self.hidden, self.ffn, self.qkv_fused = tokens, hidden, ffn, qkv_fused
+        self.layers = []
+        for _ in range(layers):
+            layer = {}
+            if qkv_fused:
+                layer["qkv"] = QLinear(rng, hidden, 3 * hidden, device)
+            else:
+                for name in ("q", "k", "v"):
+                    layer[name] = QLinear(rng, hidden, hidden, device)
+            layer["o"] = QLinear(rng, hidden, hidden, device)
+            layer["ffn1"] = QLinear(rng, hidden, ffn, device, act="gelu_erf")
+            layer["ffn2"] = QLinear(rng, ffn, hidden, device, act_scale=0.01)
+            self.layers.append(layer)
+        t = tokens
+        f16 = dict(dtype=torch.float16, device=device)
+        self.xq = torch.randint(-127, 128, (t, hidden), dtype=torch.int8, device=device)
+        self.cq = torch.randint(-127, 128, (t, hidden), dtype=torch.int8, device=device)
+        self.hq = torch.empty((t, ffn), dtype=torch.int8, device=device)
+        self.qkv = torch.empty((t, 3 * hidden), **f16)
+        self.res = torch.randn((t, hidden), **f16)
+        self.o = torch.empty((t, hidden), **f16)
+        self.y = torch.empty((t, hidden), **f16)
+
+    def ops_per_step(self):
+        return sum(l.ops(self.tokens) for layer in self.layers for l in layer.values())
+
+    def gemms_per_step(self):
+        return sum(len(layer) for layer in self.layers)
+
+    def distinct_shapes(self):
+        t, h, f = self.tokens, self.hidden, self.ffn
+        return [(t, 3 * h if self.qkv_fused else h, h, "f16", None), (t, f, h, "f16", "gelu_erf"),
+                (t, h, f, "f16", None)]
+
+    def _gemm(self, xq, lin, out, residual=None, q_out=None, q_scale=None, write_d=True):
+        capi.qgemm(xq, lin.w, b_layout=capi.B_NK, scale=lin.scale, scale_mode=capi.SCALE_PER_COL,
+                   bias=lin.bias, act=lin.act, residual=residual, out=out, q_out=q_out,
+                   q_scale=q_scale, write_d=write_d)
+
+    def step(self):
+        h = self.hidden
+        for layer in self.layers:
+            if self.qkv_fused:
+                self._gemm(self.xq, layer["qkv"], self.qkv)
+            else:
+                for i, name in enumerate(("q", "k", "v")):
+                    self._gemm(self.xq, layer[name], self.qkv[:, i * h:(i + 1) * h])
+            self._gemm(self.cq, layer["o"], self.o, residual=self.res)
+            self._gemm(self.xq, layer["ffn1"], self.o, q_out=self.hq, q_scale=0.03, write_d=False)
+            self._gemm(self.hq, layer["ffn2"], self.y, residual=self.res)
+        return self.y

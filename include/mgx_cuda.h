@@ -304,17 +304,21 @@ MGX_API int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* desc,
  * compiled (MIGraphX plans one arena per program and never allocates during eval), a
  * serving loop in which cudaMalloc's implicit device synchronisation is not acceptable, or
  * a host with a fixed memory budget.  It has no counterpart in the reference.
- * The re-laid-out copy of a [K,N] right operand (b_layout = MGX_B_KN) goes into a fixed
+ * The scratch of the call - the re-laid-out copy of a [K,N] right operand (b_layout =
+ * MGX_B_KN), or the tile counters and partial sums of the weight-streaming kernel that
+ * [N,K] operands with at most 16 rows take - goes into a fixed
  * 16 MiB array that is part of this library's device image: every GPU that loads the
  * library holds those 16 MiB until the process exits.  Requests whose
  * mgx_cuda_qgemm_workspace() exceeds mgx_cuda_qgemm_static_scratch_limit() are rejected
- * with MGX_E_TOO_LARGE.  No cudaMalloc / cudaFree / allocating library routine is called.
+ * with MGX_E_TOO_LARGE when the operand is [K,N]; with [N,K] operands (whose scratch is
+ * optional) they run as tiles without scratch instead.  No cudaMalloc / cudaFree / allocating library routine is called.
  * The first call on each device looks the array's device address up (one cheap runtime
  * query); make that first call before starting a stream capture on that device.
  * All calls on a device share the one array: two calls whose kernels may overlap on the
  * GPU (different streams without an ordering between them) race on it; calls on one stream
- * are safe.  The array keeps the previous call's bytes; nothing in it needs to start at
- * zero because every byte the GEMM reads is rewritten by the same call first. */
+ * are safe.  The array keeps the previous call's bytes; what has to start at
+ * zero (the tile counters of the weight-streaming kernel) is cleared by the call itself,
+ * and every other byte the kernels read is rewritten by the same call first. */
 MGX_API size_t mgx_cuda_qgemm_static_scratch_limit(void);
 MGX_API int mgx_cuda_qgemm_static_scratch(const mgx_qgemm_desc* desc,
                                           const void* A,
@@ -386,6 +390,14 @@ MGX_API int mgx_cuda_all_reduce(void* buf, size_t count, int dtype, void* comm, 
  * bits say which wait gave up (1 = TMA full barrier, 2 = stage-empty barrier,
  * 3 = accumulator-ready barrier, 4 = accumulator-free barrier). */
 MGX_API int mgx_cuda_device_status(int* status);
+
+/* Self-test of the bounded waits: launches one thread that waits at most limit_ns
+ * (1 .. 1e8) nanoseconds on a barrier phase that nothing completes.  The wait gives up the
+ * way every kernel's waits do: it records code 99 in the device status word (read it with
+ * mgx_cuda_device_status) and the kernel returns normally; *gave_up (a device uint32, may
+ * be NULL) receives 99.  Nothing faults and the context stays usable.  No counterpart in
+ * the reference (its kernels have no bounded waits). */
+MGX_API int mgx_cuda_selftest_bounded_wait(uint64_t limit_ns, void* gave_up, void* stream);
 
 /* Human-readable text for a return value of this library. */
 MGX_API const char* mgx_cuda_status_string(int code);

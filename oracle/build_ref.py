@@ -1,11 +1,16 @@
 #!/usr/bin/env python3
 """Build the UNMODIFIED MIGraphX core library and its CPU `ref` target from the
-reference sources where they lie, into oracle/_ref/ (git-ignored).
+reference sources where they lie (both destinations are git-ignored):
 
-This is test infrastructure: the resulting libmigraphx.so / libmigraphx_ref.so are
-(1) the parity oracle (MIGraphX's own CPU interpreter target, src/targets/ref),
-(2) the timed CPU baseline, and
-(3) the host library the `cuda` target plug-in is linked against.
+  baseline/_ref/lib/libmigraphx.so   the host library (IR, passes, program::compile / eval)
+                                     the `cuda` target plug-in plugs into, and
+  baseline/_ref/gen/include          the few headers the reference's cmake would generate;
+  oracle/_ref/lib/libmigraphx_ref.so MIGraphX's own CPU interpreter target (src/targets/ref):
+                                     the parity oracle and the timed CPU baseline, with
+  oracle/_ref/lib/libmgx_ref_oracle.so  this repository's C-ABI window onto it.
+
+Only what is under oracle/_ref is test infrastructure; nothing the product links or loads
+lives there.
 
 No reference source is copied.  The reference's own build system (cmake +
 ROCmCMakeBuildTools) is not run; the few files it would generate are produced
@@ -31,7 +36,15 @@ import sysconfig
 import time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-OUT = os.path.join(HERE, "_ref")
+ROOT = os.path.dirname(HERE)
+OUT = os.path.join(HERE, "_ref")            # ref target, oracle window, object cache
+HOST = os.path.join(ROOT, "baseline", "_ref")  # host library + generated headers
+
+
+def reference_dir():
+    """The MIGraphX source tree: $MIGRAPHX_SOURCE_DIR, else a directory named `reference` next
+    to this repository."""
+    return os.environ.get("MIGRAPHX_SOURCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def nlohmann_include():
@@ -137,17 +150,19 @@ def compile_one(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("MIGRAPHX_REFERENCE", "/root/reference"))
+    ap.add_argument("--ref", default=reference_dir())
     ap.add_argument("--jobs", type=int, default=max(1, min(8, os.cpu_count() or 1)))
     a = ap.parse_args()
     ref = a.ref
     if not os.path.isdir(os.path.join(ref, "src")):
         print(f"[build_ref] reference sources not found at {ref}; keeping prebuilt files")
         return 0
-    gen = os.path.join(OUT, "gen")
+    gen = os.path.join(HOST, "gen")
     obj = os.path.join(OUT, "obj")
     lib = os.path.join(OUT, "lib")
+    hostlib = os.path.join(HOST, "lib")
     os.makedirs(lib, exist_ok=True)
+    os.makedirs(hostlib, exist_ok=True)
     gen_units = gen_files(ref, gen)
 
     src = os.path.join(ref, "src")
@@ -191,23 +206,27 @@ def main():
         return 1
     core_objs = [objname(s) for s in core]
     ref_objs = [objname(s) for s in reft]
-    libmgx = os.path.join(lib, "libmigraphx.so")
+    libmgx = os.path.join(hostlib, "libmigraphx.so")
     libref = os.path.join(lib, "libmigraphx_ref.so")
     newest = max(os.path.getmtime(o) for o in core_objs)
     if not os.path.exists(libmgx) or os.path.getmtime(libmgx) < newest:
         subprocess.check_call(["g++", "-shared", "-o", libmgx] + core_objs + ["-ldl", "-lpthread"])
     if not os.path.exists(libref) or os.path.getmtime(libref) < max(os.path.getmtime(o) for o in ref_objs + [libmgx]):
         subprocess.check_call(["g++", "-shared", "-o", libref] + ref_objs +
-                              [f"-L{lib}", "-lmigraphx", "-Wl,-rpath,$ORIGIN", "-lpthread"])
+                              [f"-L{hostlib}", "-lmigraphx", "-Wl,-rpath,$ORIGIN/../../../baseline/_ref/lib",
+                               "-lpthread"])
     # our own C-ABI window onto the ref target (oracle/ref_oracle.cpp)
     tool_src = os.path.join(HERE, "ref_oracle.cpp")
     tool = os.path.join(lib, "libmgx_ref_oracle.so")
-    if not os.path.exists(tool) or os.path.getmtime(tool) < max(os.path.getmtime(tool_src), os.path.getmtime(libref)):
+    builders = os.path.join(ROOT, "amdmigraphx_b200", "csrc", "target", "programs.hpp")
+    if not os.path.exists(tool) or os.path.getmtime(tool) < max(os.path.getmtime(tool_src), os.path.getmtime(libref),
+                                                                os.path.getmtime(builders)):
         subprocess.check_call(["g++", "-shared", "-O2", "-o", tool, tool_src] + base +
-                              [f"-L{lib}", "-Wl,--no-as-needed", "-lmigraphx_ref", "-lmigraphx", "-Wl,-rpath,$ORIGIN"])
+                              [f"-L{lib}", f"-L{hostlib}", "-Wl,--no-as-needed", "-lmigraphx_ref", "-lmigraphx",
+                               "-Wl,-rpath,$ORIGIN", "-Wl,-rpath,$ORIGIN/../../../baseline/_ref/lib"])
     # symbol tables of the template-heavy library are ~350 MB; the dynamic symbols stay
     subprocess.call(["strip", "--strip-unneeded", libmgx, libref])
-    print(f"[build_ref] done in {time.time() - t0:.0f}s -> {lib}")
+    print(f"[build_ref] done in {time.time() - t0:.0f}s -> {hostlib}, {lib}")
     return 0
 
 

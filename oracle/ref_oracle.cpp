@@ -25,6 +25,9 @@
 #include <string>
 #include <thread>
 #include <vector>
+// the program builders the product's benchmark and parity driver use (header-only, MIGraphX
+// public API only): the CPU baseline evaluates the very same programs
+#include "../amdmigraphx_b200/csrc/target/programs.hpp"
 
 namespace {
 
@@ -156,6 +159,51 @@ __attribute__((visibility("default"))) int ref_run_op(const char* op_name,
     catch(...)
     {
         last_error = "unknown exception";
+        return 1;
+    }
+}
+
+
+// The BERT-shaped int8 encoder program of the benchmark (amdmigraphx_b200/csrc/target/programs.hpp,
+// `layers` layers, `batch` sequences of `seq` tokens, typical fixed activation scales) compiled
+// for the ref target and evaluated `warmup` (untimed) + `repeat` times.  *seconds: the sum over the
+// `repeat` timed eval() calls;
+// *quant_ops: 2*M*N*K summed over its QDQ linears.  simplify_qdq is applied first, so that the
+// linears run as quant_dot (ref's own integer GEMM) like on every GPU target.
+__attribute__((visibility("default"))) int ref_time_bert(int64_t batch, int64_t seq, int64_t layers,
+                                                          int64_t hidden, int64_t heads, int64_t ffn,
+                                                          int64_t vocab, int warmup, int repeat,
+                                                          double* seconds, double* quant_ops)
+{
+    try
+    {
+        mgx_programs::bert_config c;
+        c.batch  = static_cast<std::size_t>(batch);
+        c.seq    = static_cast<std::size_t>(seq);
+        c.layers = static_cast<std::size_t>(layers);
+        c.hidden = static_cast<std::size_t>(hidden);
+        c.heads  = static_cast<std::size_t>(heads);
+        c.ffn    = static_cast<std::size_t>(ffn);
+        c.vocab  = static_cast<std::size_t>(vocab);
+        auto bp  = mgx_programs::bert_encoder_int8_calibrated(c, false);
+        migraphx::run_passes(bp.prog, {migraphx::simplify_qdq{}, migraphx::dead_code_elimination{}});
+        bp.prog.compile(migraphx::make_target("ref"));
+        migraphx::parameter_map pm;
+        pm["ids"]   = mgx_programs::bert_ids(c, 7);
+        for(int it = 0; it < warmup; ++it)
+            (void)bp.prog.eval(pm);
+        auto t0 = std::chrono::steady_clock::now();
+        for(int it = 0; it < (repeat < 1 ? 1 : repeat); ++it)
+            (void)bp.prog.eval(pm);
+        if(seconds != nullptr)
+            *seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+        if(quant_ops != nullptr)
+            *quant_ops = bp.quant_ops;
+        return 0;
+    }
+    catch(const std::exception& e)
+    {
+        last_error = e.what();
         return 1;
     }
 }

@@ -43,8 +43,22 @@ def load():
         lib.ref_run_op.argtypes = [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_int,
                                    ctypes.POINTER(_Tensor), ctypes.POINTER(_Tensor),
                                    ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+        lib.ref_time_bert.argtypes = [ctypes.c_int64] * 7 + [ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_double),
+                                                            ctypes.POINTER(ctypes.c_double)]
         _lib = lib
     return _lib
+
+
+def time_bert_encoder(batch, seq, layers, hidden=768, heads=12, ffn=3072, vocab=30522, warmup=0, repeat=1):
+    """Total seconds of `repeat` eval() calls (after `warmup` untimed ones) of the benchmark's
+    BERT-shaped int8 encoder program on the ref target (all host threads MIGraphX's par_for uses)
+    and the 2*M*N*K of its QDQ linears per eval()."""
+    secs, ops = ctypes.c_double(0), ctypes.c_double(0)
+    rc = load().ref_time_bert(batch, seq, layers, hidden, heads, ffn, vocab, warmup, repeat,
+                              ctypes.byref(secs), ctypes.byref(ops))
+    if rc != 0:
+        raise RuntimeError("ref_time_bert: " + load().ref_last_error().decode())
+    return secs.value, ops.value
 
 
 def hardware_threads():

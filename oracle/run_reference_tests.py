@@ -8,7 +8,7 @@ known-answer vector the reference ships for this path:
   pack_unpack_int4.cpp, dot_op.cpp (dot and quant_dot cases)
 
 Nothing is copied; the executable goes to oracle/_ref/bin/.  The pass/fail summary is
-written to tests/golden/reference_test_run.txt.
+printed; tests/test_reference_golden_tests.py runs this where the reference sources exist.
 
 Usage: python oracle/run_reference_tests.py [--ref <MIGraphX source tree>]
 """
@@ -28,10 +28,12 @@ FILES = ["quantizelinear.cpp", "dequantizelinear.cpp", "unpack_int4.cpp", "pack_
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=build_ref.reference_dir())
     a = ap.parse_args()
     out = os.path.join(HERE, "_ref")
-    lib, gen, obj = (os.path.join(out, d) for d in ("lib", "gen", "obj"))
+    lib, obj = (os.path.join(out, d) for d in ("lib", "obj"))
+    gen = os.path.join(build_ref.HOST, "gen")
+    hostlib = os.path.join(build_ref.HOST, "lib")
     bindir = os.path.join(out, "bin")
     os.makedirs(bindir, exist_ok=True)
     tdir = os.path.join(a.ref, "test", "ref")
@@ -49,9 +51,9 @@ def main():
     with cf.ThreadPoolExecutor(4) as ex:
         objs = list(ex.map(cc, FILES))
     exe = os.path.join(bindir, "ref_tests")
-    subprocess.check_call(["g++", "-o", exe] + objs + [f"-L{lib}", "-Wl,--no-as-needed",
+    subprocess.check_call(["g++", "-o", exe] + objs + [f"-L{lib}", f"-L{hostlib}", "-Wl,--no-as-needed",
                                                         "-lmigraphx_ref", "-lmigraphx",
-                                                        f"-Wl,-rpath,{lib}", "-lpthread"])
+                                                        f"-Wl,-rpath,{lib}", f"-Wl,-rpath,{hostlib}", "-lpthread"])
     r = subprocess.run([exe], capture_output=True, text=True)
     text = r.stdout + r.stderr
     lines = text.strip().splitlines()
@@ -59,14 +61,12 @@ def main():
     failed = [l for l in lines if "FAILED" in l]
     summary = [
         "Reference golden tests (test/ref: " + ", ".join(FILES[:-1]) + ")",
-        "run against oracle/_ref/lib (MIGraphX core + ref target built by oracle/build_ref.py)",
+        "run against the MIGraphX core + ref target built by oracle/build_ref.py",
         "command: python oracle/run_reference_tests.py",
         f"exit code: {r.returncode}",
         f"test cases run: {len(ran)}",
         f"lines containing FAILED: {len(failed)}",
     ] + failed[:50] + ["", "tail of output:"] + lines[-8:]
-    with open(os.path.join(os.path.dirname(HERE), "tests", "golden", "reference_test_run.txt"), "w") as f:
-        f.write("\n".join(summary) + "\n")
     print("\n".join(summary))
     return r.returncode
 

@@ -20,7 +20,22 @@ CASES = ["c1_small", "c1_semantic", "int8_gelu", "int8_per_tensor", "fp8_gelu", 
          "pw_gelu_f16", "pw_arith_f32", "pw_transcendental_f32",
          "layernorm_f32", "layernorm_f16", "softmax_f32", "softmax_f16", "softmax_f32_long",
          "attention_f16", "dot_f16_const", "dot_f16_batched", "bert_layer_int8", "embed_rope_f16",
-         "dot_f16_odd_k", "dot_f16_odd_k_const", "reduce_axes"]
+         "dot_f16_odd_k", "dot_f16_odd_k_const", "reduce_axes",
+         "int4_group_k28672", "int4_group_k96", "quant_dot_transposed_a"]
+
+# The configurations of the benchmark at their real dimensions.  Where MIGraphX's CPU interpreter
+# would need minutes, it evaluates a seeded sample of rows of the same problem (same weights) and
+# those rows of the cuda result are compared ("ref_rows" in the driver's output).
+C3_SWEEP = [f"c3_m{m}_n{n}_k{k}" for m in (1, 16, 128, 1024, 4096, 8192)
+            for (n, k) in ((4096, 4096), (8192, 8192), (14336, 4096))]
+C2_LINEARS = [f"c2_{name}_m{m}" for m in (3072, 384) for name in ("qkv", "ffn1", "ffn2")]
+C4_LINEARS = [f"c4_m{m}_n{n}_k{k}" for m in (1, 16, 512)
+              for (n, k) in ((4096, 4096), (11008, 4096), (4096, 11008))]
+C5_LINEARS = [f"c5_m16_n{n}_k{k}" for (n, k) in ((8192, 8192), (1024, 8192), (28672, 8192), (8192, 28672),
+                                                  (4096, 8192), (512, 8192), (14336, 8192), (8192, 14336),
+                                                  (8192, 4096))]
+CONFIG_SIZE = (["c2_layer", "int8_8192", "int8_8192_raw", "int4_heavy_tail_m1", "int4_heavy_tail_m16",
+                "int4_heavy_tail_m512"] + C2_LINEARS + C3_SWEEP + C4_LINEARS + C5_LINEARS)
 
 
 def _run(case, mode=None):
@@ -33,6 +48,12 @@ def _run(case, mode=None):
 
 @pytest.mark.parametrize("case", CASES)
 def test_program_matches_ref(cuda_device, case):
+    res = _run(case)
+    assert res.get("pass"), res
+
+
+@pytest.mark.parametrize("case", CONFIG_SIZE)
+def test_config_size_program_matches_ref(cuda_device, case):
     res = _run(case)
     assert res.get("pass"), res
 

@@ -144,3 +144,36 @@ def test_reductions_over_other_axes_use_a_transposed_copy():
     assert out.count("cuda::reduce[") == 4
     assert out.count("transpose[") == 3 and out.count("cuda::pointwise[ops={32}") == 3
     assert "reshape_lazy[dims={6, 1, 48}]" in out and "reshape_lazy[dims={1, 20, 1}]" in out
+
+
+def test_int4_group_size_when_k_over_group_is_not_a_power_of_two():
+    # K = 28672 (Llama-2-70B down projection) with groups of 128: 224 groups per row
+    out = _passes("int4_group_k28672")
+    assert "cuda::w4a16[group=128,zp_const=8,has_zp=0" in out and "half_type, {64, 224}" in out
+    out = _passes("int4_group_k96")
+    assert "cuda::w4a16[group=32" in out and "has_zp=1" in out and "half_type, {64, 3}" in out
+
+
+def test_transposed_batched_left_operand_is_packed_first():
+    out = _passes("quant_dot_transposed_a")
+    lines = out.splitlines()
+    gemm = [l for l in lines if "cuda::qgemm" in l][0]
+    # the transposed view goes through a packed copy; quant_dot reads the copy, not the view
+    copy = [l for l in lines if "cuda::pointwise[ops={32}" in l and "int8_type, {2, 3, 24, 32}, {2304, 768, 32, 1}" in l]
+    assert len(copy) == 1
+    assert copy[0].split(" = ")[0] in gemm
+
+
+def test_offload_copy_program_is_graph_bracketed():
+    out = _passes("int8_gelu", "offload")
+    order = [n for l in out.splitlines() for n in ("cuda::copy_to", "cuda::graph_begin", "cuda::qgemm",
+                                                   "cuda::graph_end", "cuda::copy_from") if "= " + n in l]
+    assert order.index("cuda::copy_to") < order.index("cuda::graph_begin") < order.index("cuda::qgemm") \
+        < order.index("cuda::graph_end") < order.index("cuda::copy_from")
+
+
+def test_config2_layer_lowers_at_real_dimensions():
+    out = _passes("c2_layer")
+    gemms = [l for l in out.splitlines() if "cuda::qgemm" in l]
+    assert any("half_type, {384, 768}" in l for l in gemms)
+    assert "cuda::gather" in out and "cuda::softmax" in out or "cuda::attention" in out
