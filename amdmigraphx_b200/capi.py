@@ -25,7 +25,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
+    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -298,6 +298,52 @@ PW_MAXDIMS, PW_MAXIN, PW_MAXINSN = 5, 8, 32
 PW_OPS = ["add", "sub", "mul", "div", "min", "max", "pow", "neg", "abs", "exp", "log", "sqrt", "rsqrt",
           "recip", "tanh", "sigmoid", "erf", "relu", "sin", "cos", "floor", "ceil", "round", "nearbyint",
           "convert", "where", "clip", "equal", "greater", "less", "leaky_relu", "const", "identity"]
+
+
+class LayernormDesc(ctypes.Structure):
+    _fields_ = [("rows", ctypes.c_int64), ("cols", ctypes.c_int64), ("ldx", ctypes.c_int64),
+                ("ldy", ctypes.c_int64), ("ldq", ctypes.c_int64), ("type", ctypes.c_int32),
+                ("eps", ctypes.c_float), ("q_type", ctypes.c_int32), ("q_scale", ctypes.c_float),
+                ("q_zero_point", ctypes.c_float), ("reserved", ctypes.c_int32)]
+
+
+def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0, write_y=True):
+    """LayerNorm over the last axis of a 2-D tensor; returns (y or None, q or None) where q is the
+    int8 quantizelinear(y, q_scale, q_zero_point) written by the same launch."""
+    import torch
+    lib = load()
+    rows, cols = x.shape
+    y = torch.empty_like(x) if write_y else None
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device) if q_scale is not None else None
+    d = LayernormDesc(rows=rows, cols=cols, ldx=x.stride(0), ldy=cols, ldq=cols, type=_dtype_code(x), eps=eps,
+                      q_type=I8, q_scale=float(q_scale or 1.0), q_zero_point=float(q_zero_point), reserved=0)
+    lib.mgx_cuda_layernorm.argtypes = [ctypes.POINTER(LayernormDesc)] + [ctypes.c_void_p] * 6
+    check(lib.mgx_cuda_layernorm(ctypes.byref(d), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(q), _stream()),
+          "mgx_cuda_layernorm")
+    return y, q
+
+
+class AttentionDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("batch", "seq", "heads", "head_dim", "ldq", "ldk", "ldv", "ldo", "ldoq")] + \
+               [("scale", ctypes.c_float), ("q_scale", ctypes.c_float), ("q_zero_point", ctypes.c_float),
+                ("reserved", ctypes.c_int32)]
+
+
+def attention(q, k, v, batch, seq, heads, scale, q_scale=None, q_zero_point=0.0, write_o=True):
+    """softmax(scale * Q K^T) V per batch entry and head on [batch*seq, heads*64] fp16 matrices (row
+    strided views allowed); returns (o or None, oq or None)."""
+    import torch
+    lib = load()
+    width = heads * 64
+    o = torch.empty((batch * seq, width), dtype=torch.float16, device=q.device) if write_o else None
+    oq = torch.empty((batch * seq, width), dtype=torch.int8, device=q.device) if q_scale is not None else None
+    d = AttentionDesc(batch=batch, seq=seq, heads=heads, head_dim=64, ldq=q.stride(0), ldk=k.stride(0),
+                      ldv=v.stride(0), ldo=width, ldoq=width, scale=float(scale), q_scale=float(q_scale or 1.0),
+                      q_zero_point=float(q_zero_point), reserved=0)
+    lib.mgx_cuda_attention.argtypes = [ctypes.POINTER(AttentionDesc)] + [ctypes.c_void_p] * 6
+    check(lib.mgx_cuda_attention(ctypes.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(oq), _stream()),
+          "mgx_cuda_attention")
+    return o, oq
 
 
 class PwInsn(ctypes.Structure):

@@ -1,0 +1,319 @@
+// Multi-head attention on fp16 tensors as one kernel: softmax(scale * Q K^T) V per (batch, head),
+// the fusion of the instruction chain an encoder layer holds between its projections
+//   reshape [B,S,H,D] -> transpose -> dot(Q, K^T) -> mul(scale) -> softmax -> dot(P, V) -> transpose
+//   -> reshape [B*S, H*D]
+// (what the reference's GPU target hands to its fused attention kernels,
+// src/targets/gpu/fuse_mlir.cpp:1161-1234 / src/fuse_attention.cpp).  Q, K and V are read in place
+// from row-strided [B*S, H*D] matrices (a head is a 64-column slice of a row), so the head split
+// and merge need no copies; the result can additionally (or only) be written through a
+// per-tensor quantizelinear as int8, the input of the quantized output projection.
+//
+// Arithmetic: fp16 tensor-core products with fp32 accumulation; scores are rounded the way the
+// separate operators round them (dot -> half, * scale -> half, both truncating like
+// migraphx::half), the softmax runs in fp32 over key blocks with a running maximum and sum, the
+// probabilities enter the second product as fp16.  Against the reference's chain (every operator
+// rounded to half): within the fp16 tolerance of the tests (rtol 2e-2 / atol 1e-2).
+//
+// One CTA = 4 warps = 64 query rows of one head; keys / values stream through shared memory in
+// 64-row blocks (cp.async double buffering, 16-byte chunks XOR-swizzled against bank conflicts);
+// mma.sync.m16n8k16 with ldmatrix fragments.  This is a "next"-row kernel off the quantized-GEMM
+// path proper: it is sized by its 3.6 GFLOP per encoder layer, not by the tensor-core peak.
+#include "common.cuh"
+#include "qgemm_math.cuh"
+#include "ptx.cuh"
+#include <cuda_fp16.h>
+#include <cfloat>
+
+namespace mgx {
+
+constexpr int AT_D  = 64; // head dimension
+constexpr int AT_BM = 64; // query rows per CTA (16 per warp)
+constexpr int AT_BN = 64; // keys per block
+
+struct attention_params
+{
+    const __half* q;
+    const __half* k;
+    const __half* v;
+    __half* o;
+    int8_t* oq;
+    int64_t ldq, ldk, ldv, ldo, ldoq;
+    int seq, heads;
+    float scale;
+    float q_scale, q_rcp, q_zp;
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid)
+{
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    const int bytes  = valid ? 16 : 0; // zero-fill when the row is outside the sequence
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem)
+{
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem)
+{
+    const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(s));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                 "{%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// A [rows, 64] fp16 tile in shared memory: 128-byte rows, the 16-byte chunk index XOR-ed with the
+// row's low three bits.
+__device__ __forceinline__ __half* tile_ptr(__half* tile, int row, int chunk)
+{
+    return tile + row * AT_D + ((chunk ^ (row & 7)) << 3);
+}
+
+// 64 rows x 64 columns starting at g (row stride ld), rows at or beyond `rows_left` zero-filled
+__device__ __forceinline__ void load_tile(__half* tile, const __half* g, int64_t ld, int rows_left, int tid)
+{
+#pragma unroll
+    for(int i = 0; i < 4; ++i)
+    {
+        const int c   = tid + i * 128; // 512 chunks of 16 bytes
+        const int row = c >> 3, chunk = c & 7;
+        const bool ok = row < rows_left;
+        cp_async_16(tile_ptr(tile, row, chunk), g + (ok ? row : 0) * ld + chunk * 8, ok);
+    }
+}
+
+__global__ void __launch_bounds__(128) attention_f16_kernel(const attention_params p)
+{
+    __shared__ __align__(128) __half sq[AT_BM * AT_D];
+    __shared__ __align__(128) __half sk[2][AT_BN * AT_D];
+    __shared__ __align__(128) __half sv[2][AT_BN * AT_D];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int q0   = blockIdx.x * AT_BM;
+    const int head = blockIdx.y;
+    const int64_t row_base = static_cast<int64_t>(blockIdx.z) * p.seq; // first row of this sequence
+    const __half* qg = p.q + (row_base + q0) * p.ldq + head * AT_D;
+    const __half* kg = p.k + row_base * p.ldk + head * AT_D;
+    const __half* vg = p.v + row_base * p.ldv + head * AT_D;
+    const int nblocks = (p.seq + AT_BN - 1) / AT_BN;
+
+    load_tile(sq, qg, p.ldq, p.seq - q0, tid);
+    load_tile(sk[0], kg, p.ldk, p.seq, tid);
+    load_tile(sv[0], vg, p.ldv, p.seq, tid);
+    cp_async_commit();
+
+    uint32_t qa[4][4]; // this warp's 16 query rows: A fragments of the four 16-wide k steps
+    float o[8][4];     // output accumulators: 8 column tiles of 8
+#pragma unroll
+    for(int j = 0; j < 8; ++j)
+        o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    float m_run[2] = {-FLT_MAX, -FLT_MAX}; // running maxima of rows g and g + 8
+    float l_run[2] = {0.0f, 0.0f};         // running sums (this thread's share)
+    constexpr float log2e = 1.4426950408889634f;
+
+    for(int kb = 0; kb < nblocks; ++kb)
+    {
+        const int buf = kb & 1;
+        if(kb + 1 < nblocks)
+        {
+            const int k1 = (kb + 1) * AT_BN;
+            load_tile(sk[buf ^ 1], kg + static_cast<int64_t>(k1) * p.ldk, p.ldk, p.seq - k1, tid);
+            load_tile(sv[buf ^ 1], vg + static_cast<int64_t>(k1) * p.ldv, p.ldv, p.seq - k1, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        }
+        else
+            cp_async_wait<0>();
+        __syncthreads();
+        if(kb == 0)
+        {
+#pragma unroll
+            for(int ks = 0; ks < 4; ++ks)
+                ldmatrix_x4(qa[ks], tile_ptr(sq, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * ks + (lane >> 4)));
+        }
+        // ---- S = Q K^T for this key block: 16 rows x 64 keys per warp
+        float s[8][4];
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+        for(int ks = 0; ks < 4; ++ks)
+        {
+#pragma unroll
+            for(int jp = 0; jp < 4; ++jp) // two key tiles of 8 per ldmatrix.x4
+            {
+                uint32_t kf[4];
+                ldmatrix_x4(kf, tile_ptr(sk[buf], jp * 16 + (lane & 7) + (lane >> 4) * 8, 2 * ks + ((lane >> 3) & 1)));
+                mma_16816(s[2 * jp], qa[ks], kf[0], kf[1]);
+                mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
+            }
+        }
+        // ---- scores as the separate operators round them, keys beyond the sequence masked
+        const int kbase = kb * AT_BN;
+        float mx[2] = {-FLT_MAX, -FLT_MAX};
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+#pragma unroll
+            for(int e = 0; e < 4; ++e)
+            {
+                float x = truncate_to_half_precision(s[j][e]);
+                x       = truncate_to_half_precision(x * p.scale);
+                const int key = kbase + j * 8 + 2 * t + (e & 1);
+                x       = key < p.seq ? x : -FLT_MAX;
+                s[j][e] = x;
+                mx[e >> 1] = fmaxf(mx[e >> 1], x);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for(int r = 0; r < 2; ++r)
+        {
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+            mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+            const float m_new = fmaxf(m_run[r], mx[r]);
+            corr[r]  = exp2f((m_run[r] - m_new) * log2e);
+            m_run[r] = m_new;
+            l_run[r] *= corr[r];
+        }
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+            o[j][0] *= corr[0], o[j][1] *= corr[0];
+            o[j][2] *= corr[1], o[j][3] *= corr[1];
+        }
+        // ---- P = exp(s - max) as fp16 A fragments; O += P V
+        uint32_t pa[4][4];
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+            float e[4];
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+            {
+                e[i] = exp2f((s[j][i] - m_run[i >> 1]) * log2e);
+                l_run[i >> 1] += e[i];
+            }
+            const __half2 lo = __floats2half2_rn(e[0], e[1]); // row g
+            const __half2 hi = __floats2half2_rn(e[2], e[3]); // row g + 8
+            // key tile j covers k columns 8j .. 8j+7 of the 16-wide step j / 2
+            pa[j >> 1][(j & 1) * 2]     = *reinterpret_cast<const uint32_t*>(&lo);
+            pa[j >> 1][(j & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+#pragma unroll
+        for(int ks = 0; ks < 4; ++ks) // 16 keys per step
+        {
+#pragma unroll
+            for(int jp = 0; jp < 4; ++jp) // two output column tiles per ldmatrix.x4.trans
+            {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, tile_ptr(sv[buf], ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * jp + (lane >> 4)));
+                mma_16816(o[2 * jp], pa[ks], vf[0], vf[1]);
+                mma_16816(o[2 * jp + 1], pa[ks], vf[2], vf[3]);
+            }
+        }
+        __syncthreads(); // the other buffer is overwritten by the next iteration's loads
+    }
+    // ---- normalise and store rows g and g + 8 of this warp's 16
+#pragma unroll
+    for(int r = 0; r < 2; ++r)
+    {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+    const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
+#pragma unroll
+    for(int r = 0; r < 2; ++r)
+    {
+        const int row = q0 + warp * 16 + g + r * 8;
+        if(row >= p.seq)
+            continue;
+        const float inv = 1.0f / l_run[r];
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+            const float a = truncate_to_half_precision(o[j][2 * r] * inv);
+            const float b = truncate_to_half_precision(o[j][2 * r + 1] * inv);
+            const int col = head * AT_D + j * 8 + 2 * t;
+            if(p.o != nullptr)
+                *reinterpret_cast<uint32_t*>(p.o + (row_base + row) * p.ldo + col) = cvt_rz_f16x2(a, b);
+            if(p.oq != nullptr)
+            {
+                // quantizelinear of the half result: quotient in half (truncated), round half to even
+                uint32_t qb[2];
+                const float vals[2] = {a, b};
+#pragma unroll
+                for(int e = 0; e < 2; ++e)
+                {
+                    float qv        = __fmul_rn(vals[e], p.q_rcp);
+                    const float rem = __fmaf_rn(-p.q_scale, qv, vals[e]);
+                    qv              = truncate_to_half_precision(__fmaf_rn(rem, p.q_rcp, qv));
+                    qv              = fmaxf(q_lo, fminf(q_hi, qv));
+                    qb[e] = static_cast<uint32_t>(__float_as_int(__fadd_rn(qv, 12582912.0f)) - 0x4B400000 +
+                                                  static_cast<int>(p.q_zp)) & 0xFFu;
+                }
+                *reinterpret_cast<uint16_t*>(p.oq + (row_base + row) * p.ldoq + col) =
+                    static_cast<uint16_t>(qb[0] | (qb[1] << 8));
+            }
+        }
+    }
+}
+
+} // namespace mgx
+
+extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
+                                  void* oq, void* stream_)
+{
+    using namespace mgx;
+    if(d == nullptr or q == nullptr or k == nullptr or v == nullptr or (o == nullptr and oq == nullptr))
+        return MGX_E_INVALID_ARG;
+    if(d->batch <= 0 or d->seq <= 0 or d->heads <= 0)
+        return MGX_E_INVALID_ARG;
+    if(d->head_dim != AT_D)
+        return MGX_E_UNSUPPORTED;
+    const int64_t width = d->heads * AT_D;
+    if(d->ldq < width or d->ldk < width or d->ldv < width or (o != nullptr and d->ldo < width) or
+       (oq != nullptr and d->ldoq < width))
+        return MGX_E_INVALID_ARG;
+    auto misaligned = [](const void* ptr, int64_t ld, int es, int bytes) {
+        return (reinterpret_cast<uintptr_t>(ptr) % bytes) != 0 or (ld * es) % bytes != 0;
+    };
+    if(misaligned(q, d->ldq, 2, 16) or misaligned(k, d->ldk, 2, 16) or misaligned(v, d->ldv, 2, 16) or
+       (o != nullptr and misaligned(o, d->ldo, 2, 4)) or (oq != nullptr and misaligned(oq, d->ldoq, 1, 2)))
+        return MGX_E_ALIGNMENT;
+    if(oq != nullptr and not(d->q_scale > 0.0f))
+        return MGX_E_INVALID_ARG;
+    if(d->heads > 65535 or d->batch > 65535 or d->seq > (1 << 24))
+        return MGX_E_TOO_LARGE;
+    attention_params p{};
+    p.q = static_cast<const __half*>(q), p.k = static_cast<const __half*>(k), p.v = static_cast<const __half*>(v);
+    p.o       = static_cast<__half*>(o);
+    p.oq      = static_cast<int8_t*>(oq);
+    p.ldq     = d->ldq, p.ldk = d->ldk, p.ldv = d->ldv, p.ldo = d->ldo, p.ldoq = d->ldoq;
+    p.seq     = static_cast<int>(d->seq);
+    p.heads   = static_cast<int>(d->heads);
+    p.scale   = d->scale;
+    p.q_scale = d->q_scale;
+    p.q_rcp   = oq != nullptr ? static_cast<float>(1.0 / static_cast<double>(d->q_scale)) : 0.0f;
+    p.q_zp    = d->q_zero_point;
+    const dim3 grid(static_cast<unsigned>((d->seq + AT_BM - 1) / AT_BM), static_cast<unsigned>(d->heads),
+                    static_cast<unsigned>(d->batch));
+    attention_f16_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream_)>>>(p);
+    return static_cast<int>(cudaGetLastError());
+}

@@ -122,11 +122,14 @@ std::map<std::string, std::function<test_case()>> cases()
         {"pw_transcendental_f32", [] { return pw_transcendental_f32(11); }},
         {"layernorm_f32", [] { return layernorm(shape::float_type, 2, 48, 768, 12); }},
         {"layernorm_f16", [] { return layernorm(shape::half_type, 3, 20, 1000, 13); }},
+        {"layernorm_f32_odd", [] { return layernorm(shape::float_type, 2, 30, 770, 26); }},
+        {"layernorm_f16_odd", [] { return layernorm(shape::half_type, 2, 30, 1004, 27); }},
         {"reduce_axes", [] { return reduce_axes(24); }},
         {"softmax_f32", [] { return softmax_rows(shape::float_type, 2, 4, 56, 200, 14); }},
         {"softmax_f16", [] { return softmax_rows(shape::half_type, 1, 3, 40, 1500, 15); }},
         {"softmax_f32_long", [] { return softmax_rows(shape::float_type, 1, 1, 6, 9000, 16); }},
         {"attention_f16", [] { return attention_f16(2, 4, 64, 32, 17); }},
+        {"attention_f16_d64", [] { return attention_f16(2, 3, 200, 64, 25); }},
         {"dot_f16_const", [] { return dot_f16(1, 200, 136, 264, true, 18); }},
         {"dot_f16_batched", [] { return dot_f16(3, 72, 50, 96, false, 19); }},
         {"dot_f16_odd_k", [] { return dot_f16(2, 50, 64, 197, false, 22); }},
@@ -149,7 +152,7 @@ struct cmp_result
 };
 
 cmp_result compare(const migraphx::argument& ref, migraphx::argument got, bool exact, double rtol,
-                   double atol, const std::vector<std::size_t>* sample_rows = nullptr)
+                   double atol, const std::vector<std::size_t>* sample_rows = nullptr, bool atol_row_rms = false)
 {
     cmp_result r;
     if(sample_rows != nullptr)
@@ -180,13 +183,22 @@ cmp_result compare(const migraphx::argument& ref, migraphx::argument got, bool e
     std::vector<double> a(r.n), b(r.n);
     ref.visit([&](auto v) { std::size_t i = 0; for(auto x : v) a[i++] = static_cast<double>(x); });
     got.visit([&](auto v) { std::size_t i = 0; for(auto x : v) b[i++] = static_cast<double>(x); });
+    const std::size_t cols = ref.get_shape().ndim() == 0 ? 1 : ref.get_shape().lens().back();
+    double row_atol        = atol;
     for(std::size_t i = 0; i < r.n; ++i)
     {
+        if(atol_row_rms and i % cols == 0)
+        {
+            double ss = 0;
+            for(std::size_t j = i; j < i + cols; ++j)
+                ss += a[j] * a[j];
+            row_atol = atol * std::max(1.0, std::sqrt(ss / static_cast<double>(cols)));
+        }
         const double d = std::fabs(a[i] - b[i]);
         r.max_abs      = std::max(r.max_abs, d);
         if(std::fabs(a[i]) > 0)
             r.max_rel = std::max(r.max_rel, d / std::fabs(a[i]));
-        if(not(d <= atol + rtol * std::fabs(a[i])))
+        if(not(d <= row_atol + rtol * std::fabs(a[i])))
             ++r.mismatched;
     }
     return r;
@@ -279,7 +291,7 @@ int main(int argc, char** argv)
         for(std::size_t i = 0; i < ref_out.size() and i < cuda_out.size(); ++i)
         {
             auto host = offload ? cuda_out[i] : cuda_t.copy_from(cuda_out[i]);
-            auto c    = compare(ref_out[i], host, t.exact, t.rtol, t.atol, rows);
+            auto c    = compare(ref_out[i], host, t.exact, t.rtol, t.atol, rows, t.atol_row_rms);
             ok        = ok and c.mismatched == 0;
             std::cout << (i ? ", " : "") << "{\"n\": " << c.n << ", \"mismatched\": " << c.mismatched
                       << ", \"max_abs\": " << c.max_abs << ", \"max_rel\": " << c.max_rel << "}";
@@ -304,7 +316,7 @@ int main(int argc, char** argv)
             rebind_ok = out2.size() == ref_out.size();
             for(std::size_t i = 0; i < ref_out.size() and i < out2.size(); ++i)
                 rebind_ok = rebind_ok and
-                            compare(ref_out[i], cuda_t.copy_from(out2[i]), t.exact, t.rtol, t.atol, rows).mismatched == 0;
+                            compare(ref_out[i], cuda_t.copy_from(out2[i]), t.exact, t.rtol, t.atol, rows, t.atol_row_rms).mismatched == 0;
             ok = ok and rebind_ok;
         }
         std::cout << "], \"exact\": " << (t.exact ? "true" : "false") << ", \"ref_seconds\": " << ref_s

@@ -295,6 +295,59 @@ struct op_reduce
     std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
 };
 
+// LayerNorm over the innermost axis in one launch (mgx_cuda_layernorm), the fusion of the chain
+// reduce_mean, sub, mul, reduce_mean, add(eps), rsqrt, mul, [mul(gamma)], [add(beta)] the ONNX
+// parser emits (src/onnx/parse_layernorm.cpp:100-140), optionally with the per-tensor
+// quantizelinear that reads its result.  Inputs: x, [gamma [cols]], [beta [cols]], then - as for
+// cuda::qgemm - the quantised buffer (q_type != 0) and / or the output buffer; the last input is
+// what compute() returns.
+struct op_layernorm
+{
+    float eps      = 1e-5f;
+    bool has_gamma = false;
+    bool has_beta  = false;
+    int q_type     = 0; // shape::type_t of the fused quantizelinear's result, 0 = none
+    float q_scale  = 1.0f;
+    float q_zp     = 0.0f;
+    bool write_y   = true;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.eps, "eps"), f(self.has_gamma, "has_gamma"), f(self.has_beta, "has_beta"),
+                    f(self.q_type, "q_type"), f(self.q_scale, "q_scale"), f(self.q_zp, "q_zp"),
+                    f(self.write_y, "write_y"));
+    }
+    std::string name() const { return "cuda::layernorm"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// Multi-head attention without a mask in one launch (mgx_cuda_attention): softmax(scale * Q K^T) V
+// per batch entry and head, heads split from and merged into [batch * seq, heads * head_dim]
+// matrices in place.  Inputs: Q, K, V (2-D fp16, unit column stride), then - as for cuda::qgemm - the
+// quantised buffer (q_type != 0) and / or the output buffer; the last input is what compute() returns.
+struct op_attention
+{
+    std::size_t batch = 1, seq = 1, heads = 1, head_dim = 64;
+    float scale   = 1.0f;
+    int q_type    = 0; // shape::type_t of the fused quantizelinear's result, 0 = none
+    float q_scale = 1.0f;
+    float q_zp    = 0.0f;
+    bool write_o  = true;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.batch, "batch"), f(self.seq, "seq"), f(self.heads, "heads"), f(self.head_dim, "head_dim"),
+                    f(self.scale, "scale"), f(self.q_type, "q_type"), f(self.q_scale, "q_scale"),
+                    f(self.q_zp, "q_zp"), f(self.write_o, "write_o"));
+    }
+    std::string name() const { return "cuda::attention"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
 // softmax over the innermost axis (src/include/migraphx/op/softmax.hpp).  Inputs: x, out.
 struct op_softmax
 {

@@ -694,6 +694,390 @@ struct lowerer
         return true;
     }
 
+    // ---------------------------------------------------------------- horizontal fusion
+    // Quantized linears that read the same activations with the same kind of epilogue (the Q, K and
+    // V projections of an attention block) become one cuda::qgemm over the concatenated weights;
+    // the former results are column slices of its output.  Only done when every reader takes
+    // row-strided matrices (cuda::attention), so no slice ever has to be packed again.
+    void fuse_horizontal_qgemms()
+    {
+        std::vector<instruction_ref> gemms;
+        for(auto ins : iterator_for(m))
+            if(ins->name() == "cuda::qgemm")
+                gemms.push_back(ins);
+        std::unordered_set<instruction*> done;
+        for(auto first : gemms)
+        {
+            if(done.count(&*first) > 0)
+                continue;
+            const auto fop = any_cast<op_qgemm>(first->get_operator());
+            auto eligible  = [&](instruction_ref g) {
+                const auto op = any_cast<op_qgemm>(g->get_operator());
+                const auto& in = g->inputs();
+                if(not op.b_nk or op.has_residual or op.has_workspace or op.q_type != 0 or not op.has_bias or
+                   op.scale_mode != MGX_SCALE_PER_COL or in.size() != 5 or in[0]->get_shape().ndim() != 2)
+                    return false;
+                if(in[1]->name() != "@literal" or in[2]->name() != "@literal" or in[3]->name() != "@literal")
+                    return false;
+                if(g->outputs().empty())
+                    return false;
+                return std::all_of(g->outputs().begin(), g->outputs().end(),
+                                   [](auto o) { return o->name() == "cuda::attention"; });
+            };
+            if(not eligible(first))
+                continue;
+            std::vector<instruction_ref> group = {first};
+            for(auto g : gemms)
+            {
+                if(g == first or done.count(&*g) > 0 or not eligible(g) or g->inputs()[0] != first->inputs()[0])
+                    continue;
+                const auto op = any_cast<op_qgemm>(g->get_operator());
+                if(op.act == fop.act and op.out_type == fop.out_type and
+                   g->inputs()[1]->get_shape().type() == first->inputs()[1]->get_shape().type())
+                    group.push_back(g);
+            }
+            if(group.size() < 2)
+                continue;
+            // concatenated [N, K] weights, scales and biases
+            const std::size_t k = first->inputs()[1]->get_shape().lens()[1];
+            std::vector<char> w;
+            std::vector<float> sc, bi;
+            std::vector<std::size_t> widths;
+            for(auto g : group)
+            {
+                auto wl = g->inputs()[1]->get_literal();
+                auto sl = g->inputs()[2]->get_literal();
+                auto bl = g->inputs()[3]->get_literal();
+                w.insert(w.end(), wl.data(), wl.data() + wl.get_shape().bytes());
+                const auto* sp = reinterpret_cast<const float*>(sl.data());
+                const auto* bp = reinterpret_cast<const float*>(bl.data());
+                sc.insert(sc.end(), sp, sp + sl.get_shape().elements());
+                bi.insert(bi.end(), bp, bp + bl.get_shape().elements());
+                widths.push_back(wl.get_shape().lens()[0]);
+            }
+            const std::size_t n  = sc.size();
+            const std::size_t mm = first->inputs()[0]->get_shape().lens()[0];
+            auto wlit = m.add_literal(literal{shape{first->inputs()[1]->get_shape().type(), {n, k}}, w.data()});
+            auto slit = add_float_literal(m, sc);
+            auto blit = add_float_literal(m, bi);
+            // in front of the earliest member, so that every reader comes later
+            instruction_ref pos = group.front();
+            for(auto ins : iterator_for(m))
+                if(std::find(group.begin(), group.end(), ins) != group.end())
+                {
+                    pos = ins;
+                    break;
+                }
+            auto out   = insert_allocation(m, pos, shape{static_cast<shape::type_t>(fop.out_type), {mm, n}});
+            auto fused = m.insert_instruction(pos, fop, {first->inputs()[0], wlit, slit, blit, out});
+            consume(fused);
+            std::size_t c0 = 0;
+            for(std::size_t i = 0; i < group.size(); ++i)
+            {
+                done.insert(&*group[i]);
+                m.replace_instruction(group[i],
+                                      make_op("slice", {{"axes", {1}}, {"starts", {c0}}, {"ends", {c0 + widths[i]}}}),
+                                      fused);
+                c0 += widths[i];
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- attention
+    // softmax(mul(dot(Qh, Kh^T), scale)) . Vh with Qh / Kh / Vh the head views
+    // transpose(reshape[B,S,H,D](X)) of [B*S, H*D] fp16 matrices, and the result merged back by
+    // transpose -> contiguous -> reshape: one cuda::attention that reads the heads in place.
+    bool lower_attention(instruction_ref sm)
+    {
+        const auto& ps = sm->get_shape();
+        if(ps.type() != shape::half_type or ps.ndim() != 4)
+            return false;
+        const auto ax = sm->get_operator().to_value().at("axis").to<int64_t>();
+        if(ax != 3 and ax != -1)
+            return false;
+        auto is_transpose = [](instruction_ref t, std::vector<int64_t> perm) {
+            return t->name() == "transpose" and
+                   t->get_operator().to_value().at("permutation").to_vector<int64_t>() == perm;
+        };
+        // [B,S,H,D] view of a [B*S, H*D] (or [B,S,H*D]) matrix; returns the matrix
+        auto head_source = [&](instruction_ref t, std::vector<int64_t> perm, std::size_t b, std::size_t sq,
+                               std::size_t h, std::size_t d) -> instruction_ref {
+            if(not is_transpose(t, perm) or t->outputs().size() != 1)
+                return m.end();
+            auto r = t->inputs().front();
+            if((r->name() != "reshape" and r->name() != "reshape_lazy") or r->outputs().size() != 1 or
+               r->get_shape().lens() != std::vector<std::size_t>{b, sq, h, d})
+                return m.end();
+            auto x         = r->inputs().front();
+            const auto& xs = x->get_shape();
+            if(xs.type() != shape::half_type or xs.elements() != b * sq * h * d or xs.lens().back() != h * d or
+               xs.strides().back() != 1)
+                return m.end();
+            // rows evenly spaced: a packed tensor, or a 2-D view with a row stride (a column slice)
+            if(not xs.standard() and not(xs.ndim() == 2 and xs.strides()[0] % 8 == 0))
+                return m.end();
+            return x;
+        };
+        auto ss = sm->inputs().front();
+        instruction_ref sc = ss;
+        float scale        = 1.0f;
+        std::vector<instruction_ref> chain = {sm};
+        if(ss->name() == "mul" and ss->outputs().size() == 1)
+        {
+            instruction_ref c = m.end();
+            for(auto i : ss->inputs())
+                if(i->can_eval())
+                    c = i;
+            if(c == m.end())
+                return false;
+            auto cv = classify_constant(c);
+            if(cv.kind != bcast_kind::scalar)
+                return false;
+            scale = cv.values[0];
+            sc    = other_input(ss, c);
+            chain.push_back(ss);
+        }
+        if(sc->name() != "dot" or sc->outputs().size() != 1)
+            return false;
+        const auto& sl = ps.lens(); // [B, H, S, S]
+        const std::size_t b = sl[0], h = sl[1], sq = sl[2];
+        if(sl[3] != sq)
+            return false;
+        const std::size_t d = sc->inputs()[0]->get_shape().lens().back();
+        if(d != 64)
+            return false;
+        auto qx = head_source(sc->inputs()[0], {0, 2, 1, 3}, b, sq, h, d);
+        auto kx = head_source(sc->inputs()[1], {0, 2, 3, 1}, b, sq, h, d);
+        if(qx == m.end() or kx == m.end())
+            return false;
+        auto cx = single_user(m, sm);
+        if(not valid(cx, m) or cx->name() != "dot" or cx->inputs()[0] != sm)
+            return false;
+        auto vx = head_source(cx->inputs()[1], {0, 2, 1, 3}, b, sq, h, d);
+        if(vx == m.end())
+            return false;
+        auto ct = single_user(m, cx);
+        if(not valid(ct, m) or not is_transpose(ct, {0, 2, 1, 3}))
+            return false;
+        auto cc = single_user(m, ct);
+        if(not valid(cc, m) or cc->name() != "contiguous")
+            return false;
+        auto cr = single_user(m, cc);
+        if(not valid(cr, m) or (cr->name() != "reshape" and cr->name() != "reshape_lazy") or
+           cr->get_shape().lens().back() != h * d)
+            return false;
+        chain.insert(chain.end(), {sc, cx, ct, cc, sc->inputs()[0], sc->inputs()[1], cx->inputs()[1],
+                                   sc->inputs()[0]->inputs()[0], sc->inputs()[1]->inputs()[0],
+                                   cx->inputs()[1]->inputs()[0]});
+        op_attention op;
+        op.batch = b, op.seq = sq, op.heads = h, op.head_dim = d;
+        op.scale = scale;
+        std::vector<instruction_ref> args = {qx, kx, vx};
+        instruction_ref last = cr;
+        instruction_ref qz   = m.end();
+        for(auto o : last->outputs())
+        {
+            if(o->name() != "quantizelinear" or o->inputs().size() != 3 or o->inputs()[0] != last or
+               o->get_shape().type() != shape::int8_type or not o->inputs()[1]->can_eval() or
+               not o->inputs()[2]->can_eval())
+                continue;
+            auto cs = classify_constant(o->inputs()[1]);
+            auto cz = classify_constant(o->inputs()[2]);
+            if(cs.kind != bcast_kind::scalar or cz.kind != bcast_kind::scalar or not(cs.values[0] > 0))
+                continue;
+            op.q_type  = static_cast<int>(shape::int8_type);
+            op.q_scale = cs.values[0];
+            op.q_zp    = cz.values[0];
+            qz         = o;
+            break;
+        }
+        for(auto c : chain)
+        {
+            consume(c);
+            for(auto i : c->inputs())
+                if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
+                    consume(i);
+        }
+        const bool only_q = qz != m.end() and last->outputs().size() == 1;
+        if(only_q)
+        {
+            op.write_o = false;
+            args.push_back(insert_allocation(m, qz, qz->get_shape().as_standard()));
+            consume(last);
+            consume(m.replace_instruction(qz, op, args));
+            return true;
+        }
+        if(qz != m.end())
+            args.push_back(insert_allocation(m, last, qz->get_shape().as_standard()));
+        args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+        auto rep = m.replace_instruction(last, op, args);
+        consume(rep);
+        if(qz != m.end())
+            consume(m.replace_instruction(qz, op_second_output{}, rep, args[args.size() - 2]));
+        return true;
+    }
+
+    // ---------------------------------------------------------------- LayerNorm
+    // mean = reduce_mean(x, last axis); d = sub(x, bcast(mean)); var = reduce_mean(mul(d, d) |
+    // sqdiff(x, bcast(mean))); rs = rsqrt(add(var, eps)); y = mul(d, bcast(rs)) [* gamma] [+ beta]
+    // (src/onnx/parse_layernorm.cpp:100-140) becomes one cuda::layernorm; a per-tensor
+    // quantizelinear of y joins it.  Anything that does not match exactly is left to the
+    // single-operator lowering.
+    bool lower_layernorm(instruction_ref mean)
+    {
+        auto x         = mean->inputs().front();
+        const auto& xs = x->get_shape();
+        const auto nd  = xs.ndim();
+        if(nd < 2 or not xs.standard() or (xs.type() != shape::float_type and xs.type() != shape::half_type))
+            return false;
+        if(not mgx_cuda_layernorm_supported(xs.type() == shape::half_type ? MGX_F16 : MGX_F32,
+                                            static_cast<int64_t>(xs.lens().back())))
+            return false;
+        auto last_axis_only = [&](instruction_ref r) {
+            auto axes = r->get_operator().to_value().at("axes").to_vector<int64_t>();
+            return axes.size() == 1 and (axes[0] == -1 or axes[0] == static_cast<int64_t>(nd) - 1);
+        };
+        auto is_bcast_of = [&](instruction_ref b, instruction_ref src) {
+            return b->name() == "multibroadcast" and b->inputs().size() == 1 and b->inputs()[0] == src and
+                   b->get_shape().lens() == xs.lens();
+        };
+        auto users = [](instruction_ref i) {
+            std::set<instruction*> u;
+            for(auto o : i->outputs())
+                u.insert(&*o);
+            return u;
+        };
+        if(not last_axis_only(mean) or mean->outputs().size() != 1)
+            return false;
+        auto mb = mean->outputs().front();
+        if(not is_bcast_of(mb, mean))
+            return false;
+        instruction_ref d = m.end(), sq = m.end();
+        for(auto u : mb->outputs())
+        {
+            if(u->name() == "sub" and u->inputs()[0] == x and u->inputs()[1] == mb)
+                d = u;
+            else if(u->name() == "sqdiff" and u->inputs()[0] == x and u->inputs()[1] == mb)
+                sq = u;
+            else
+                return false;
+        }
+        if(d == m.end())
+            return false;
+        instruction_ref nv = m.end();
+        for(auto u : d->outputs())
+        {
+            if(u->name() == "mul" and u->inputs()[0] == d and u->inputs()[1] == d and sq == m.end())
+                sq = u;
+            else if(u->name() == "mul" and u->inputs()[0] == d and u != sq)
+                nv = u;
+            else if(u != sq)
+                return false;
+        }
+        if(sq == m.end() or nv == m.end() or users(d).size() != (sq->name() == "mul" ? 2u : 1u))
+            return false;
+        auto var = single_user(m, sq);
+        if(not valid(var, m) or var->name() != "reduce_mean" or not last_axis_only(var))
+            return false;
+        auto ve = single_user(m, var);
+        if(not valid(ve, m) or ve->name() != "add" or not other_input(ve, var)->can_eval())
+            return false;
+        auto ec = classify_constant(other_input(ve, var));
+        if(ec.kind != bcast_kind::scalar)
+            return false;
+        auto rs = single_user(m, ve);
+        if(not valid(rs, m) or rs->name() != "rsqrt")
+            return false;
+        auto mb2 = single_user(m, rs);
+        if(not valid(mb2, m) or not is_bcast_of(mb2, rs) or single_user(m, mb2) != nv or nv->inputs()[1] != mb2)
+            return false;
+        op_layernorm op;
+        op.eps = ec.values[0];
+        std::vector<instruction_ref> chain = {mean, mb, d, sq, var, ve, rs, mb2, nv};
+        instruction_ref last = nv;
+        std::vector<instruction_ref> args = {x};
+        auto per_col_literal = [&](instruction_ref c) {
+            auto cv = classify_constant(c);
+            if(cv.kind == bcast_kind::scalar)
+                cv.values.assign(xs.lens().back(), cv.values[0]);
+            else if(cv.kind != bcast_kind::per_col)
+                return m.end();
+            if(xs.type() == shape::half_type)
+            {
+                std::vector<half> h(cv.values.begin(), cv.values.end());
+                return m.add_literal(literal{shape{shape::half_type, {h.size()}}, h});
+            }
+            return add_float_literal(m, cv.values);
+        };
+        auto u = single_user(m, last);
+        if(valid(u, m) and u->name() == "mul" and other_input(u, last)->can_eval())
+        {
+            auto g = per_col_literal(other_input(u, last));
+            if(g != m.end())
+            {
+                op.has_gamma = true;
+                args.push_back(g);
+                chain.push_back(u);
+                last = u;
+                u    = single_user(m, last);
+            }
+        }
+        if(valid(u, m) and u->name() == "add" and other_input(u, last)->can_eval())
+        {
+            auto b = per_col_literal(other_input(u, last));
+            if(b != m.end())
+            {
+                op.has_beta = true;
+                args.push_back(b);
+                chain.push_back(u);
+                last = u;
+            }
+        }
+        // a per-tensor quantizelinear of the result is done by the same kernel
+        instruction_ref qz = m.end();
+        for(auto o : last->outputs())
+        {
+            if(o->name() != "quantizelinear" or o->inputs().size() != 3 or o->inputs()[0] != last)
+                continue;
+            const auto qt = o->get_shape().type();
+            if((qt != shape::int8_type and qt != shape::fp8e4m3fn_type) or not o->inputs()[1]->can_eval() or
+               not o->inputs()[2]->can_eval())
+                continue;
+            auto cs = classify_constant(o->inputs()[1]);
+            auto cz = classify_constant(o->inputs()[2]);
+            if(cs.kind != bcast_kind::scalar or cz.kind != bcast_kind::scalar or not(cs.values[0] > 0))
+                continue;
+            op.q_type  = static_cast<int>(qt);
+            op.q_scale = cs.values[0];
+            op.q_zp    = cz.values[0];
+            qz         = o;
+            break;
+        }
+        const bool only_q = qz != m.end() and last->outputs().size() == 1;
+        for(auto c : chain)
+        {
+            consume(c);
+            for(auto i : c->inputs())
+                if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
+                    consume(i);
+        }
+        if(only_q)
+        {
+            op.write_y = false;
+            args.push_back(insert_allocation(m, qz, qz->get_shape().as_standard()));
+            consume(m.replace_instruction(qz, op, args));
+            return true;
+        }
+        if(qz != m.end())
+            args.push_back(insert_allocation(m, last, qz->get_shape().as_standard()));
+        args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+        auto rep = m.replace_instruction(last, op, args);
+        consume(rep);
+        if(qz != m.end())
+            consume(m.replace_instruction(qz, op_second_output{}, rep, args[args.size() - 2]));
+        return true;
+    }
+
     // ---------------------------------------------------------------- single operators
     template <class Op>
     void lower_elementwise(instruction_ref ins, Op op)
@@ -983,7 +1367,11 @@ struct lowerer
         std::vector<instruction_ref> order;
         for(auto ins : iterator_for(m))
             order.push_back(ins);
-        // GEMM sub-graphs first: their operands (packed int4 weights, scale expressions) must
+        // whole attention blocks first (their two dots must not be lowered one by one)
+        for(auto ins : order)
+            if(not skip(ins) and ins->name() == "softmax")
+                lower_attention(ins);
+        // GEMM sub-graphs next: their operands (packed int4 weights, scale expressions) must
         // still be in their original form, not folded into dense constants
         for(auto ins : order)
         {
@@ -997,6 +1385,13 @@ struct lowerer
                     unsupported(ins, "only fp16 operands and the weight-only int4 form "
                                      "dot(A, transpose(dequantizelinear(unpack_int4(W)))) are supported");
             }
+        }
+        for(auto ins : order)
+        {
+            if(skip(ins))
+                continue;
+            if(ins->name() == "reduce_mean" and ins->inputs().size() == 1)
+                lower_layernorm(ins);
         }
         for(auto ins : order)
         {
@@ -1031,6 +1426,7 @@ struct lowerer
             else
                 unsupported(ins, "no kernel");
         }
+        fuse_horizontal_qgemms();
     }
 
     // packed row-major copy of a host argument with arbitrary strides

@@ -484,6 +484,104 @@ argument op_reduce::compute(context& ctx, const shape&, const std::vector<argume
     return out;
 }
 
+// ------------------------------------------------------------------ layernorm
+shape op_layernorm::compute_shape(const std::vector<shape>& inputs) const
+{
+    const std::size_t n = 1 + has_gamma + has_beta + (q_type != 0 ? 1 : 0) + (write_y ? 1 : 0);
+    check_shapes{inputs, *this}.has(n);
+    const auto& x = inputs[0];
+    if(x.type() != shape::float_type and x.type() != shape::half_type)
+        MIGRAPHX_THROW("cuda::layernorm: float and half only");
+    if(not mgx_cuda_layernorm_supported(mgx_type(x.type()), static_cast<int64_t>(x.lens().back())))
+        MIGRAPHX_THROW("cuda::layernorm: row length not supported");
+    for(std::size_t i = 1; i < inputs.size(); ++i)
+        if(i > static_cast<std::size_t>(has_gamma + has_beta) and inputs[i].lens() != x.lens())
+            MIGRAPHX_THROW("cuda::layernorm: buffers must have the input's dimensions");
+    return inputs.back();
+}
+
+argument op_layernorm::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    if(ctx.replaying())
+        return args.back();
+    std::size_t i         = 1;
+    const argument* gamma = has_gamma ? &args[i++] : nullptr;
+    const argument* beta  = has_beta ? &args[i++] : nullptr;
+    const argument* qbuf  = q_type != 0 ? &args[i++] : nullptr;
+    const argument* ybuf  = write_y ? &args[i++] : nullptr;
+    const auto m          = as_matrix(args[0].get_shape(), "layernorm input");
+    mgx_layernorm_desc d{};
+    d.rows = m.rows;
+    d.cols = m.cols;
+    d.ldx  = m.ld;
+    d.ldy  = ybuf != nullptr ? as_matrix(ybuf->get_shape(), "layernorm output").ld : 0;
+    d.ldq  = qbuf != nullptr ? as_matrix(qbuf->get_shape(), "layernorm quantised output").ld : 0;
+    d.type = mgx_type(args[0].get_shape().type());
+    d.eps  = eps;
+    if(qbuf != nullptr)
+    {
+        d.q_type       = mgx_type(static_cast<shape::type_t>(q_type));
+        d.q_scale      = q_scale;
+        d.q_zero_point = q_zp;
+    }
+    check_mgx(mgx_cuda_layernorm(&d, args[0].data(), gamma != nullptr ? gamma->data() : nullptr,
+                                 beta != nullptr ? beta->data() : nullptr, ybuf != nullptr ? ybuf->data() : nullptr,
+                                 qbuf != nullptr ? qbuf->data() : nullptr, ctx.stream()),
+              "mgx_cuda_layernorm");
+    return args.back();
+}
+
+// ------------------------------------------------------------------ attention
+shape op_attention::compute_shape(const std::vector<shape>& inputs) const
+{
+    const std::size_t n = 3 + (q_type != 0 ? 1 : 0) + (write_o ? 1 : 0);
+    check_shapes{inputs, *this}.has(n);
+    const std::size_t rows = batch * seq, width = heads * head_dim;
+    for(std::size_t i = 0; i < 3; ++i)
+    {
+        const auto& s = inputs[i];
+        if(s.type() != shape::half_type or s.elements() != rows * width or s.lens().back() != width or
+           s.strides().back() != 1)
+            MIGRAPHX_THROW("cuda::attention: Q, K and V must be fp16 [batch * seq, heads * head_dim] matrices");
+    }
+    for(std::size_t i = 3; i < inputs.size(); ++i)
+        if(inputs[i].elements() != rows * width or not inputs[i].standard())
+            MIGRAPHX_THROW("cuda::attention: result buffers must be packed [batch * seq, heads * head_dim]");
+    return inputs.back();
+}
+
+argument op_attention::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    if(ctx.replaying())
+        return args.back();
+    std::size_t i        = 3;
+    const argument* qbuf = q_type != 0 ? &args[i++] : nullptr;
+    const argument* obuf = write_o ? &args[i++] : nullptr;
+    // row stride of a [.., width] tensor whose leading dimensions step like a packed matrix's rows
+    auto row_stride = [&](const shape& s) {
+        const auto nd = s.ndim();
+        return static_cast<int64_t>(nd >= 2 ? s.strides()[nd - 2] : s.lens().back());
+    };
+    mgx_attention_desc d{};
+    d.batch    = static_cast<int64_t>(batch);
+    d.seq      = static_cast<int64_t>(seq);
+    d.heads    = static_cast<int64_t>(heads);
+    d.head_dim = static_cast<int64_t>(head_dim);
+    d.ldq      = row_stride(args[0].get_shape());
+    d.ldk      = row_stride(args[1].get_shape());
+    d.ldv      = row_stride(args[2].get_shape());
+    d.ldo      = static_cast<int64_t>(heads * head_dim);
+    d.ldoq     = d.ldo;
+    d.scale    = scale;
+    d.q_scale  = q_scale;
+    d.q_zero_point = q_zp;
+    check_mgx(mgx_cuda_attention(&d, args[0].data(), args[1].data(), args[2].data(),
+                                 obuf != nullptr ? obuf->data() : nullptr, qbuf != nullptr ? qbuf->data() : nullptr,
+                                 ctx.stream()),
+              "mgx_cuda_attention");
+    return args.back();
+}
+
 shape op_softmax::compute_shape(const std::vector<shape>& inputs) const
 {
     check_shapes{inputs, *this}.has(2);
@@ -617,6 +715,8 @@ MIGRAPHX_REGISTER_OP(op_gather)
 MIGRAPHX_REGISTER_OP(op_concat)
 MIGRAPHX_REGISTER_OP(op_reduce)
 MIGRAPHX_REGISTER_OP(op_softmax)
+MIGRAPHX_REGISTER_OP(op_layernorm)
+MIGRAPHX_REGISTER_OP(op_attention)
 MIGRAPHX_REGISTER_OP(op_pointwise)
 MIGRAPHX_REGISTER_OP(op_second_output)
 MIGRAPHX_REGISTER_OP(op_all_reduce)

@@ -4,12 +4,14 @@
 //   D[m,n] = sum_g  s[n,g] * sum_{k in g} (q[n,k] - zp[n,g]) * a[m,k]
 //
 // is evaluated with INTEGER tensor-core arithmetic.  A small pre-kernel writes every
-// activation row as int8 rows (a ~ sa[m] * (128 h + l), |error| <= sa/2, i.e. 15 bits of the
-// row's range) and the per-group sums Sv[g,m] = sum_k (128 h + l).  The main kernel computes,
+// activation row as int8 rows (a ~ sa[g,m] * (128 h + l), |error| <= sa/2, i.e. 15 bits of the
+// range of the row's own group g of 128 k: an outlier costs only the 127 other values of its
+// group precision, not the whole row) and the per-group sums Sv[g,m] = sum_k (128 h + l).  The main kernel computes,
 // per group g of 128 k and per 128 output columns, with kind::i8 MMAs whose A operand are the
 // UNSIGNED weights and whose B operand are the activation rows, exact int32 sums
 // Q[n,m] = sum_k q[n,k] a_int[m,k] (spread over 2 or 4 accumulator columns per activation row,
-// see RAW below), and the epilogue folds  s[n,g] * (Q - zp[n,g] * Sv[g,m])  into fp32 registers.
+// see RAW below), and the epilogue folds  s[n,g] * sa[g,m] * (Q - zp[n,g] * Sv[g,m])  into fp32
+// registers.
 // The only inexact steps are the 15-bit activation rounding and the fp32 sum over groups; the
 // reference (src/onnx/parse_matmulnbits.cpp:85-158 IR on the ref target) rounds every
 // dequantised weight to fp16 instead, which is the coarser of the two.
@@ -47,7 +49,7 @@ constexpr int TC_ISSUERS  = 4;   // MMA-issuing threads, one per group of a work
 constexpr int TC_ACC_COLS = 128; // accumulator columns per buffer (two buffers)
 constexpr int TC_A_COL0   = 256; // first tensor-memory column of the A operand buffers
 constexpr int TC_A_COLS   = TC_GROUP_K / 4; // 32 columns per group
-constexpr int TC_EPI      = 3 * 128 * (5 + 3 + 1) * 4 + 64; // epilogue metadata
+constexpr int TC_EPI      = 3 * 128 * (5 + 3 + 2) * 4 + 64; // epilogue metadata
 
 // ring depth by B-operand width; a stage = 32 KB of weights + 4 NB x 128 bytes of activations
 template <int NB>
@@ -63,7 +65,7 @@ struct tc_params
 {
     const __half* scales;
     const uint8_t* zp; // may be null
-    const float* sa;   // [MB] per-row activation scale
+    const float* sa;   // [K/128][MB] activation scale of every (group, row)
     const int* sv;     // [K/128][MB] per-group sums of the quantised activations
     __half* D;
     float* partial;    // [slots][M][N]
@@ -83,7 +85,7 @@ struct tc_params
 //         nibbles L_j = q[2j] and whose last 64 bytes are the packed bytes B_j = 16 q[2j+1] + L_j
 //         themselves: rows [e | 0] and [-o | o] for each of h and l, e_j = a[2j], o_j = a[2j+1], so
 //         that  sum_j L_j e_j  and  sum_j (B_j - L_j) o_j = 16 sum_j q[2j+1] o_j  come out.
-// Also written: sv (per-group sums of q), sa, zeroed tile counters.
+// Also written: sv (per-group sums of q), sa (per-group scales), zeroed tile counters.
 template <int MB, bool RAW>
 __global__ void __launch_bounds__(1024)
     w4_prepare_acts_kernel(const __half* __restrict__ A, int64_t lda, int64_t M, int64_t K,
@@ -97,8 +99,6 @@ __global__ void __launch_bounds__(1024)
     // finished (which may still read the workspace, or be writing A)
     grid_dependency_wait();
     constexpr int RPM = RAW ? 4 : 2; // int8 rows per activation row
-    __shared__ float red[32];
-    __shared__ float s_scale;
     const int m   = blockIdx.x;
     const int tid = threadIdx.x;
     int8_t* rows  = aq + static_cast<int64_t>(RPM * m) * K;
@@ -109,55 +109,32 @@ __global__ void __launch_bounds__(1024)
         for(int64_t k = tid * 16; k < RPM * K; k += 1024 * 16)
             *reinterpret_cast<uint4*>(rows + k) = make_uint4(0u, 0u, 0u, 0u);
         for(int64_t g = tid; g < K / 128; g += 1024)
+        {
             sv[g * MB + m] = 0;
-        if(tid == 0)
-            sa[m] = 0.0f;
+            sa[g * MB + m] = 0.0f;
+        }
         return;
     }
     const __half* row = A + m * lda;
-    float mx          = 0.0f;
-    uint4 first       = make_uint4(0u, 0u, 0u, 0u); // this thread's first octet stays in registers
-    for(int64_t k = tid * 8; k < K; k += 1024 * 8)
+    for(int64_t kb = 0; kb < K; kb += 1024 * 8)
     {
-        const uint4 v = *reinterpret_cast<const uint4*>(row + k);
-        if(k < 1024 * 8)
-            first = v;
+        // every thread of a warp takes the same trips (the reductions below are warp shuffles);
+        // 16 consecutive threads hold one group of 128 k
+        const int64_t k  = kb + tid * 8;
+        const bool valid = k < K;
+        const uint4 v    = valid ? *reinterpret_cast<const uint4*>(row + k) : make_uint4(0u, 0u, 0u, 0u);
         const __half* vh = reinterpret_cast<const __half*>(&v);
+        float mx         = 0.0f;
 #pragma unroll
         for(int e = 0; e < 8; ++e)
             mx = fmaxf(mx, fabsf(__half2float(vh[e])));
-    }
 #pragma unroll
-    for(int o = 16; o > 0; o >>= 1)
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if((tid & 31) == 0)
-        red[tid >> 5] = mx;
-    __syncthreads();
-    if(tid < 32)
-    {
-        float t = red[tid];
-#pragma unroll
-        for(int o = 16; o > 0; o >>= 1)
-            t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
-        if(tid == 0)
-        {
-            // 128 h + l spans [-16256, 16256] with h in [-127, 127], l in [-64, 63]
-            s_scale = t > 0.0f ? t / 16256.0f : 1.0f;
-            sa[m]   = s_scale;
-        }
-    }
-    __syncthreads();
-    const float inv = 1.0f / s_scale;
-    for(int64_t kb = 0; kb < K; kb += 1024 * 8)
-    {
-        // every thread of a warp takes the same trips (the sums below are warp shuffles)
-        const int64_t k  = kb + tid * 8;
-        const bool valid = k < K;
-        const uint4 v    = kb == 0 ? first
-                                   : (valid ? *reinterpret_cast<const uint4*>(row + k)
-                                            : make_uint4(0u, 0u, 0u, 0u));
-        const __half* vh = reinterpret_cast<const __half*>(&v);
-        int sum          = 0;
+        for(int o = 8; o > 0; o >>= 1)
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        // 128 h + l spans [-16256, 16256] with h in [-127, 127], l in [-64, 63]
+        const float scale = mx > 0.0f ? mx / 16256.0f : 1.0f;
+        const float inv   = 1.0f / scale;
+        int sum           = 0;
         // bytes of the evens (e = 0, 2, 4, 6) and of the odds, for h and for l
         uint32_t he = 0u, ho = 0u, le = 0u, lo = 0u, nho = 0u, nlo = 0u;
 #pragma unroll
@@ -203,12 +180,14 @@ __global__ void __launch_bounds__(1024)
                 *reinterpret_cast<uint2*>(rows + K + k) = make_uint2(le, lo);
             }
         }
-        // 16 consecutive threads hold one group of 128 k
 #pragma unroll
         for(int o = 8; o > 0; o >>= 1)
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
         if(valid and (tid & 15) == 0)
+        {
             sv[(k >> 7) * MB + m] = sum;
+            sa[(k >> 7) * MB + m] = scale;
+        }
     }
 }
 
@@ -287,10 +266,11 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
     volatile uint32_t* abort_flag = tmem_slot + 1;
     // epilogue metadata, three buffers each: per output column the aligned 32-bit words that
     // hold the scales (at most 5) and zero points (at most 3) of a pass, GPP x MB activation
-    // group sums
+    // group sums and group scales
     uint32_t* epi_sw = reinterpret_cast<uint32_t*>(bar_base + 512);     // [3][128][5]
     uint32_t* epi_zw = epi_sw + 3 * 128 * 5;                            // [3][128][3]
     int* epi_sv      = reinterpret_cast<int*>(epi_zw + 3 * 128 * 3);    // [3][128]
+    float* epi_sa    = reinterpret_cast<float*>(epi_sv + 3 * 128);      // [3][128]
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -448,7 +428,7 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
         // (consecutive lanes copy consecutive words of a column's run, so a request touches
         // few sectors) and of the activation group sums.  Each of the two warps serves 64
         // output columns.
-        grid_dependency_wait(); // sv comes from the pre-kernel
+        grid_dependency_wait(); // sv and sa come from the pre-kernel
         const int half  = warp - 13;
         const int rshift = 31 - __clz(p.group / TC_GROUP_K); // groups are powers of two
         const uint32_t sbase0 = static_cast<uint32_t>(reinterpret_cast<uintptr_t>(p.scales) & 3u);
@@ -497,10 +477,13 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
                         cp_async4(epi_zw + (vb * 128 + half * 64 + r) * 3 + w, zptr + a + 4 * w);
                 }
             }
-            // group sums: count x MB floats, half of them per warp
+            // group sums and group scales: count x MB words each, half of them per warp
             for(int i = half * 64 + lane; i < count * MB; i += 32)
                 if(i < half * 64 + 64)
+                {
                     cp_async4(epi_sv + vb * 128 + i, p.sv + static_cast<int64_t>(g0) * MB + i);
+                    cp_async4(epi_sa + vb * 128 + i, p.sa + static_cast<int64_t>(g0) * MB + i);
+                }
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(
                              smem_u32(&meta_bar[vb]))
                          : "memory");
@@ -594,7 +577,7 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
         for(int m = 0; m < MRW; ++m)
             out[m] = 0.0f;
         tc_walk walk(f_lo, f_hi, SG, G);
-        // one group: out[m] += sc (Q[m] - z Sv[m]) with Q = sum_k q a_int, in exact integer
+        // one group: out[m] += sc sa[m] (Q[m] - z Sv[m]) with Q = sum_k q a_int, in exact integer
         // arithmetic up to the one conversion.  soff / zoff: byte offset of the group's scale /
         // zero point inside this column's staged words
         constexpr int C  = CPM * MRW; // accumulator columns read per group
@@ -611,7 +594,8 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
                 sc *= 0.0625f; // Q is computed times 16
                 z *= 16;
             }
-            const int* svb = epi_sv + vb * 128 + gl * MB + m0;
+            const int* svb   = epi_sv + vb * 128 + gl * MB + m0;
+            const float* sab = epi_sa + vb * 128 + gl * MB + m0;
 #pragma unroll
             for(int m = 0; m < MRW; ++m)
             {
@@ -627,7 +611,7 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
                 else
                     q = static_cast<int>(acc[2 * m]) * 128 + static_cast<int>(acc[2 * m + 1]);
                 q      = q - z * svb[m];
-                out[m] = fmaf(sc, static_cast<float>(q), out[m]);
+                out[m] = fmaf(sc * sab[m], static_cast<float>(q), out[m]);
             }
         };
         // groups read from tensor memory per trip (all loads in flight before the first fold)
@@ -700,7 +684,7 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
 #pragma unroll
                     for(int m = 0; m < MRW; ++m)
                         if(m0 + m < p.M and nc < p.N)
-                            p.D[(m0 + m) * p.ldd + nc] = __float2half_rn(out[m] * __ldg(p.sa + m0 + m));
+                            p.D[(m0 + m) * p.ldd + nc] = __float2half_rn(out[m]);
                 }
                 else
                 {
@@ -746,7 +730,7 @@ __global__ void __launch_bounds__(TC_THREADS + (ESETS - 1) * 128, 1)
 #pragma unroll
                         for(int m = 0; m < MRW; ++m)
                             if(m0 + m < p.M and nc < p.N)
-                                p.D[(m0 + m) * p.ldd + nc] = __float2half_rn(v[m] * __ldg(p.sa + m0 + m));
+                                p.D[(m0 + m) * p.ldd + nc] = __float2half_rn(v[m]);
                     }
                 }
 #pragma unroll
@@ -798,8 +782,8 @@ tc_plan make_plan(const mgx_w4_desc& d)
     // CTAs that can share one tile
     pl.slots        = (pl.blocks - 1) / pl.items_per_cta + 2;
     pl.off_sa       = align_up(static_cast<size_t>(pl.nb) * d.K, 256);
-    pl.off_sv       = pl.off_sa + 256;
-    pl.off_counters = align_up(pl.off_sv + static_cast<size_t>(pl.groups) * pl.mb * sizeof(float), 256);
+    pl.off_sv       = align_up(pl.off_sa + static_cast<size_t>(pl.groups) * pl.mb * sizeof(float), 256);
+    pl.off_counters = align_up(pl.off_sv + static_cast<size_t>(pl.groups) * pl.mb * sizeof(int), 256);
     pl.off_partial  = align_up(pl.off_counters + static_cast<size_t>(pl.tiles) * 8 * sizeof(int), 256);
     pl.total        = pl.off_partial + static_cast<size_t>(pl.slots) * d.M * d.N * sizeof(float);
     return pl;

@@ -177,6 +177,7 @@ class EncoderGemms(object):
         self.cq = torch.randint(-127, 128, (t, hidden), dtype=torch.int8, device=device)
         self.hq = torch.empty((t, ffn), dtype=torch.int8, device=device)
         self.qkv = torch.empty((t, 3 * hidden), **f16)
+        self.h = torch.empty((t, ffn), **f16)  # FFN1's un-quantised result: described, never written
         self.res = torch.randn((t, hidden), **f16)
         self.o = torch.empty((t, hidden), **f16)
         self.y = torch.empty((t, hidden), **f16)
@@ -206,6 +207,6 @@ class EncoderGemms(object):
                 for i, name in enumerate(("q", "k", "v")):
                     self._gemm(self.xq, layer[name], self.qkv[:, i * h:(i + 1) * h])
             self._gemm(self.cq, layer["o"], self.o, residual=self.res)
-            self._gemm(self.xq, layer["ffn1"], self.o, q_out=self.hq, q_scale=0.03, write_d=False)
+            self._gemm(self.xq, layer["ffn1"], self.h, q_out=self.hq, q_scale=0.03, write_d=False)
             self._gemm(self.hq, layer["ffn2"], self.y, residual=self.res)
         return self.y

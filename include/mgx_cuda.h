@@ -163,6 +163,52 @@ MGX_API int mgx_cuda_reduce(const void* x, int type, int64_t ldx, int64_t rows, 
 MGX_API int mgx_cuda_softmax(const void* x, int type, int64_t ldx, void* y, int64_t ldy, int64_t rows,
                              int64_t cols, void* stream);
 
+/* ---- LayerNorm over the last axis, one launch ("next" row: the encoder's LayerNorms) ----- *
+ * y = (x - mean) * rsqrt(var + eps) * gamma + beta per row of x [rows, cols] (row strides in
+ * elements), optionally followed by a per-tensor quantizelinear of y written to q (int8 or
+ * fp8 e4m3fn, the next quantized linear's input); y or q may be NULL when only the other is
+ * wanted.  gamma / beta: [cols] in x's type, or NULL.  Stands in for the instruction chain of
+ * src/onnx/parse_layernorm.cpp:100-140 (reduce_mean, sub, mul, reduce_mean, add, rsqrt, mul, mul,
+ * add) and keeps those operators' roundings: with MGX_F16 every intermediate is truncated to half
+ * like migraphx::half arithmetic.  Types: MGX_F32 | MGX_F16; cols a multiple of 4 (fp32) / 8
+ * (fp16) and at most 2048 / 4096 (mgx_cuda_layernorm_supported); 16-byte aligned rows. */
+typedef struct mgx_layernorm_desc
+{
+    int64_t rows, cols;
+    int64_t ldx, ldy, ldq;
+    int32_t type;   /* mgx_dtype of x, gamma, beta and y */
+    float eps;
+    int32_t q_type; /* mgx_dtype of q (MGX_I8 | MGX_FP8_E4M3FN); ignored when q == NULL */
+    float q_scale;
+    float q_zero_point;
+    int32_t reserved;
+} mgx_layernorm_desc;
+
+MGX_API int mgx_cuda_layernorm_supported(int type, int64_t cols);
+MGX_API int mgx_cuda_layernorm(const mgx_layernorm_desc* d, const void* x, const void* gamma, const void* beta,
+                               void* y, void* q, void* stream);
+
+/* ---- multi-head attention on fp16 tensors, one launch ("next" row: encoder attention) ---- *
+ * o[b*seq + i, h*64 .. h*64+63] = softmax_j(scale * <q_i, k_j>) . v_j per batch b and head h,
+ * no mask.  q, k, v: row-strided [batch*seq, heads*64] fp16 matrices (a head is a 64-column
+ * slice of a row; ld* in elements, 16-byte aligned rows), read in place.  o (fp16) and / or oq
+ * (int8: the per-tensor quantizelinear of the fp16 result) receive the merged-heads result.
+ * Stands in for reshape -> transpose -> dot -> mul -> softmax -> dot -> transpose -> reshape of an
+ * encoder layer (the reference fuses the same chain for its GPU target,
+ * src/targets/gpu/fuse_mlir.cpp:1161-1234).  head_dim must be 64. */
+typedef struct mgx_attention_desc
+{
+    int64_t batch, seq, heads, head_dim;
+    int64_t ldq, ldk, ldv, ldo, ldoq;
+    float scale;
+    float q_scale;      /* quantizelinear scale / zero point of oq; ignored when oq == NULL */
+    float q_zero_point;
+    int32_t reserved;
+} mgx_attention_desc;
+
+MGX_API int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
+                               void* oq, void* stream);
+
 /* ---- gather, concat (byte movers of the "next" rows: embeddings, KV-cache append) -------- *
  * out[o, j, :] = data[o, indices[j], :] for o < outer, j < nidx, rows of inner_bytes bytes:
  * op::gather (src/include/migraphx/op/gather.hpp:107-150) on a packed tensor whose dimensions

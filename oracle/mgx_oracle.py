@@ -271,3 +271,51 @@ def w4a16_linear(a, bp, scales, zp=None, zp_const=8, group=128, act=None):
     if act not in (None, "none"):
         acc = apply_act(acc.astype(np.float32), act).astype(np.float64)
     return half_trunc(acc)
+
+
+# ----------------------------------------------------------------------------- LayerNorm / attention chains
+def _as_type(x, dtype):
+    """A double result stored in the operator's output type (half: truncating)."""
+    return half_trunc(x) if np.dtype(dtype) == np.float16 else np.asarray(x).astype(dtype)
+
+
+def layernorm_chain(x, gamma=None, beta=None, eps=1e-5):
+    """The instruction chain the ONNX parser emits for LayerNormalization over the last axis
+    (src/onnx/parse_layernorm.cpp:100-140), operator by operator in x's type: reduce_mean sums in
+    double and stores in x's type (src/include/migraphx/op/reduce_op.hpp:180-203), every
+    element-wise operator computes in fp32 / double and stores in x's type (fp16: truncating)."""
+    x = np.asarray(x)
+    dt = x.dtype
+    f = lambda a: np.asarray(a).astype(np.float64)  # noqa: E731
+    n = x.shape[-1]
+    mean = _as_type(f(x).sum(axis=-1, keepdims=True) / n, dt)
+    d = _as_type(f(x).astype(np.float32) - f(mean).astype(np.float32), dt)
+    dd = _as_type(f(d).astype(np.float32) * f(d).astype(np.float32), dt)
+    var = _as_type(f(dd).sum(axis=-1, keepdims=True) / n, dt)
+    ve = _as_type(f(var).astype(np.float32) + np.float32(_as_type(np.float64(eps), dt)), dt)
+    rs = _as_type(np.float32(1.0) / np.sqrt(f(ve).astype(np.float32)), dt)
+    y = _as_type(f(d).astype(np.float32) * f(rs).astype(np.float32), dt)
+    if gamma is not None:
+        y = _as_type(f(y).astype(np.float32) * f(gamma).astype(np.float32), dt)
+    if beta is not None:
+        y = _as_type(f(y).astype(np.float32) + f(beta).astype(np.float32), dt)
+    return y
+
+
+def attention_chain(q, k, v, batch, seq, heads, scale):
+    """reshape -> transpose -> dot -> mul(scale) -> softmax -> dot -> transpose -> reshape on fp16
+    [batch*seq, heads*d] matrices, every operator storing half (truncating): dot accumulates in
+    double (src/gemm.cpp:55-61), softmax as ref_softmax (src/targets/ref/lowering.cpp:253-320:
+    exp(x - max) stored in half, summed in fp32, divided in half arithmetic)."""
+    q, k, v = (np.asarray(a, dtype=np.float16) for a in (q, k, v))
+    d = q.shape[1] // heads
+    hd = lambda a: a.reshape(batch, seq, heads, d).transpose(0, 2, 1, 3).astype(np.float64)  # noqa: E731
+    qh, kh, vh = hd(q), hd(k), hd(v)
+    sc = half_trunc(np.matmul(qh, kh.transpose(0, 1, 3, 2)))
+    ss = half_trunc(sc.astype(np.float32) * np.float32(np.float16(scale)))
+    mx = ss.astype(np.float32).max(axis=-1, keepdims=True)
+    e = half_trunc(np.exp((ss.astype(np.float32) - mx).astype(np.float32)))
+    tot = e.astype(np.float32).sum(axis=-1, keepdims=True, dtype=np.float32)
+    p = half_trunc(e.astype(np.float32) / tot)
+    o = half_trunc(np.matmul(p.astype(np.float64), vh))
+    return np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(batch * seq, heads * d)

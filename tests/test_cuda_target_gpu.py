@@ -6,6 +6,7 @@ simplify_qdq-rewritten program; fp8 / int4 results within rtol 2e-2 / atol 1e-2.
 import json
 import os
 import subprocess
+import sys
 
 import pytest
 
@@ -18,8 +19,8 @@ pytestmark = [pytest.mark.gpu,
 CASES = ["c1_small", "c1_semantic", "int8_gelu", "int8_per_tensor", "fp8_gelu", "int4_decode",
          "int4_batch16_zp", "int4_batch8_zp", "int4_prefill", "q_dq_ops", "raw_quant_dot", "mlp_fused_q", "mlp_two_outputs",
          "pw_gelu_f16", "pw_arith_f32", "pw_transcendental_f32",
-         "layernorm_f32", "layernorm_f16", "softmax_f32", "softmax_f16", "softmax_f32_long",
-         "attention_f16", "dot_f16_const", "dot_f16_batched", "bert_layer_int8", "embed_rope_f16",
+         "layernorm_f32", "layernorm_f16", "layernorm_f32_odd", "layernorm_f16_odd", "softmax_f32", "softmax_f16", "softmax_f32_long",
+         "attention_f16", "attention_f16_d64", "dot_f16_const", "dot_f16_batched", "bert_layer_int8", "embed_rope_f16",
          "dot_f16_odd_k", "dot_f16_odd_k_const", "reduce_axes",
          "int4_group_k28672", "int4_group_k96", "quant_dot_transposed_a"]
 
@@ -43,7 +44,10 @@ def _run(case, mode=None):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
     assert lines, r.stdout + r.stderr
-    return json.loads(lines[-1])
+    res = json.loads(lines[-1])
+    if not res.get("pass"):
+        print(lines[-1], file=sys.stderr)  # the whole record (assert messages are truncated)
+    return res
 
 
 @pytest.mark.parametrize("case", CASES)

@@ -77,8 +77,17 @@ def test_quantizelinear_between_two_linears_is_fused_into_the_first():
     assert "cuda::second_output" in out and "write_d=1" in out
 
 
-def test_layernorm_lowers_to_reductions_and_fused_pointwise():
+def test_layernorm_chain_becomes_one_kernel():
     out = _passes("layernorm_f32")
+    assert out.count("cuda::layernorm[") == 1 and "has_gamma=1,has_beta=1" in out
+    assert "cuda::reduce[mode=1]" not in out and "rsqrt" not in out
+    for mode in (0, 2, 3):  # the max / min / sum the case also returns stay reductions
+        assert "cuda::reduce[mode=%d]" % mode in out
+
+
+def test_layernorm_with_unaligned_rows_lowers_to_reductions_and_fused_pointwise():
+    out = _passes("layernorm_f32_odd")
+    assert "cuda::layernorm" not in out
     # two reduce_mean of the decomposition plus the max / min / sum the case also returns
     assert out.count("cuda::reduce[mode=1]") == 2
     for mode in (0, 2, 3):
@@ -112,11 +121,19 @@ def test_constant_fp16_weight_is_relaid_out_once():
 
 def test_bert_layer_compiles_into_one_graph():
     out = _passes("bert_layer_int8")
-    assert out.count("cuda::qgemm") == 8  # six QDQ linears, Q.K^T, P.V
+    assert out.count("cuda::qgemm") == 6  # the six QDQ linears
     assert out.count("cuda::graph_begin") == 1 and out.count("cuda::graph_end") == 1
     # FFN1: GELU and the quantizelinear feeding FFN2 run in its epilogue
     assert any("act=2" in l and "q_type=5" in l and "write_d=0" in l for l in out.splitlines())
-    assert "cuda::softmax" in out and out.count("cuda::reduce[mode=1]") == 4
+    # the attention block and the two LayerNorms are one launch each
+    assert out.count("cuda::attention[") == 1 and "cuda::softmax" not in out
+    assert out.count("cuda::layernorm[") == 2 and "cuda::reduce" not in out
+
+
+def test_attention_block_with_64_wide_heads_becomes_one_kernel():
+    out = _passes("attention_f16_d64")
+    assert out.count("cuda::attention[batch=2,seq=200,heads=3,head_dim=64") == 1
+    assert "cuda::qgemm" not in out and "cuda::softmax" not in out and "cuda::pointwise" not in out
 
 
 def test_embedding_rope_and_cache_append_lower_to_movers():

@@ -93,3 +93,29 @@ def test_w4a16_rejects_bad_arguments(cuda_device):
     with pytest.raises(capi.MgxError) as e:
         capi.w4a16(a, bp, s, group=48)
     assert e.value.code == capi.E_UNSUPPORTED
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (16, 4096, 11008), (64, 2048, 4096)])
+def test_w4a16_heavy_tailed_activations(cuda_device, M, N, K):
+    """Activations with outliers (a few values per row 100x - 1000x the rest, as the outlier
+    channels of real decoder activations): the decode kernels quantise activations per row and
+    128-k group, so an outlier may only cost the other values of its own group precision.  The
+    results are sums of large terms that partly cancel; the absolute tolerance is therefore
+    scaled by the row's typical magnitude: |d| <= 1e-2 * max(1, rms(row)) + 2e-2 * |ref|."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + N + K)
+    a = rng.normal(0, 1, size=(M, K)).astype(np.float16)
+    for r in range(M):
+        cols = rng.choice(K, size=6, replace=False)
+        a[r, cols] = (rng.uniform(100, 1000, size=6) * rng.choice([-1, 1], size=6)).astype(np.float16)
+    bp = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    sc = rng.uniform(0.005, 0.02, size=(N, K // 128)).astype(np.float16)
+    t = lambda v: torch.from_numpy(v).to(cuda_device)  # noqa: E731
+    got = capi.w4a16(t(a), t(bp), t(sc), group=128).cpu().numpy().astype(np.float64)
+    torch.cuda.synchronize()
+    ref = O.w4a16_linear(a, bp, sc, None, 8, 128).astype(np.float64)
+    atol = 1e-2 * np.maximum(1.0, np.sqrt((ref ** 2).mean(axis=1, keepdims=True)))
+    assert np.all(np.abs(got - ref) <= atol + 2e-2 * np.abs(ref))
+    # the error itself is small against the rows' magnitude
+    assert np.sqrt(((got - ref) ** 2).mean()) <= 2e-3 * np.sqrt((ref ** 2).mean())
