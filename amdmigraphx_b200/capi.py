@@ -43,7 +43,10 @@ class QgemmDesc(ctypes.Structure):
                 ("stride_d", ctypes.c_int64),
                 ("ab_type", ctypes.c_int32), ("out_type", ctypes.c_int32),
                 ("b_layout", ctypes.c_int32), ("scale_mode", ctypes.c_int32),
-                ("act", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+                ("act", ctypes.c_int32), ("flags", ctypes.c_int32)]
+
+
+QGEMM_HALF_MATH = 1
 
 
 class QgemmQout(ctypes.Structure):
@@ -220,7 +223,7 @@ def transpose_8bit(src):
 
 def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=None,
           residual=None, out_dtype=None, out=None, workspace=None, q_out=None, q_scale=None,
-          q_zero_point=0.0, write_d=True):
+          q_zero_point=0.0, write_d=True, half_math=False):
     """quant_dot with the fused epilogue.  a: [M,K] or [B,M,K] int8 / float8_e4m3fn;
     b: [K,N] (B_KN) or [N,K] (B_NK), optionally batched.  q_out (int8 / float8 tensor of the
     output's shape) additionally receives quantizelinear(result, q_scale, q_zero_point);
@@ -249,7 +252,8 @@ def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=No
     desc = QgemmDesc(M=M, N=N, K=K, batch=batch, lda=a3.stride(1), ldb=b3.stride(1),
                      ldd=d3.stride(1), stride_a=a3.stride(0), stride_b=b3.stride(0),
                      stride_d=d3.stride(0), ab_type=_dtype_code(a), out_type=_dtype_code(d),
-                     b_layout=b_layout, scale_mode=scale_mode, act=ACT_BY_NAME[act], reserved=0)
+                     b_layout=b_layout, scale_mode=scale_mode, act=ACT_BY_NAME[act],
+                     flags=QGEMM_HALF_MATH if half_math else 0)
     need = lib.mgx_cuda_qgemm_workspace(ctypes.byref(desc))
     if need and workspace is None:
         workspace = torch.empty(need, dtype=torch.uint8, device=a.device)

@@ -56,7 +56,33 @@ struct qgemm_params
     int acc24;  // every accumulator is below 2^24 in magnitude (int8 operands, K < 1024)
     int q_mask; // the fused quantizelinear may take the mantissa-cut value (see launch_qgemm)
     int vec_io; // D (and residual) rows can be accessed with 16-byte (fp32/int32) / 8-byte (fp16) vectors
+    // fp16 results whose epilogue operators run in half (MGX_QGEMM_HALF_MATH): 0xFFFFE000, the
+    // mantissa cut that truncates an fp32 value in the normal half range to half; else all ones
+    uint32_t hmask;
+    float act_rcp; // erf-GELU: 1 / the constant x is divided by (sqrt 2, or its half value)
 };
+
+// v with the mantissa cut by mask (see qgemm_params::hmask); values in the half subnormal range
+// keep up to 2^-24 too much, which no later step can see
+__device__ __forceinline__ float hcut(float v, uint32_t mask)
+{
+    return __uint_as_float(__float_as_uint(v) & mask);
+}
+
+// the activation with every step rounded by hcut (all ones: the fp32 operator chain)
+template <int ACT>
+__device__ __forceinline__ float apply_act_cut(float v, uint32_t mask, float act_rcp)
+{
+    if constexpr(ACT == MGX_ACT_GELU_ERF)
+    {
+        // (x * 0.5) * (erf(x / c) + 1), operation order of src/op/builder/gelu.cpp:58-74; x * 0.5 is exact
+        const float dv = hcut(v * act_rcp, mask);
+        const float e1 = hcut(__fadd_rn(hcut(fast_erf(dv), mask), 1.0f), mask);
+        return hcut(__fmul_rn(__fmul_rn(v, 0.5f), e1), mask);
+    }
+    else
+        return apply_act<ACT>(v);
+}
 
 template <int BN>
 struct qgemm_smem
@@ -135,9 +161,19 @@ __device__ __forceinline__ void epi_store_chunk(const epi_ctx& e, int64_t col, f
                     if(p.scale_mode != MGX_SCALE_NONE)
                         x = __fmul_rn(x, s);
                 }
-                if(has_bias)
-                    x = __fadd_rn(x, bi[j]);
-                v[j] = apply_act<ACT>(x);
+                if constexpr(std::is_same<OutT, __half>::value)
+                {
+                    x = hcut(x, p.hmask);
+                    if(has_bias)
+                        x = hcut(__fadd_rn(x, bi[j]), p.hmask);
+                    v[j] = apply_act_cut<ACT>(x, p.hmask, p.act_rcp);
+                }
+                else
+                {
+                    if(has_bias)
+                        x = __fadd_rn(x, bi[j]);
+                    v[j] = apply_act<ACT>(x);
+                }
             }
             if(p.residual != nullptr)
             {
@@ -322,6 +358,7 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     // saturation before rounding: bounds are integers, so round-to-nearest stays inside
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
     const int q_bias = static_cast<int>(p.q_zp) - 0x4B400000;
+    const uint32_t hmask = p.hmask;
     const uint8_t* box = e.box + rsub * 64;
 #pragma unroll 2
     for(int it = 0; it < 4; ++it)
@@ -354,9 +391,20 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
             for(int j = 0; j < 4; ++j)
                 v[j] = __fmul_rn(__uint_as_float(wv[j]), sc[j]);
         }
+        if constexpr(std::is_same<OutT, __half>::value)
+        {
+            // fp16 model: dequantised value, bias sum and the activation's steps each rounded to half
+            // when the launch asks for it (hmask), plain fp32 operators otherwise
 #pragma unroll
-        for(int j = 0; j < 4; ++j)
-            v[j] = apply_act<ACT>(__fadd_rn(v[j], bi[j]));
+            for(int j = 0; j < 4; ++j)
+                v[j] = apply_act_cut<ACT>(hcut(__fadd_rn(hcut(v[j], hmask), bi[j]), hmask), hmask, p.act_rcp);
+        }
+        else
+        {
+#pragma unroll
+            for(int j = 0; j < 4; ++j)
+                v[j] = apply_act<ACT>(__fadd_rn(v[j], bi[j]));
+        }
         if(has_res)
         {
             float q[4];
@@ -859,6 +907,9 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
                      ? 1
                      : 0;
     }
+    p.hmask      = (std::is_same<OutT, __half>::value and (d.flags & MGX_QGEMM_HALF_MATH) != 0) ? 0xFFFFE000u
+                                                                                                 : 0xFFFFFFFFu;
+    p.act_rcp    = p.hmask != 0xFFFFFFFFu ? 1.0f / 1.4140625f : 0.70710678118654752440f;
     p.acc24      = (IS_INT and d.K < 1024) ? 1 : 0; // |a b| <= 2^14 for int8 operands
     // |v| < 2^-14 (half subnormals) divided by a scale >= 2^-12 stays below 1/4: quantises to zero
     // whatever its low bits; no zero point may shift the rounding boundary

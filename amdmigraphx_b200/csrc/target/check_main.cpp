@@ -63,6 +63,9 @@ test_case c2_encoder(std::size_t batch, std::size_t layers)
     t.ref_simplify_qdq = true;
     t.rtol = 2e-2;
     t.atol = 1e-2;
+    // quantizer flips behind the fused attention and the fp32 LayerNorm sums (see test_case)
+    t.outlier_fraction = 2e-3;
+    t.outlier_atol     = 0.1;
     return t;
 }
 
@@ -104,6 +107,12 @@ std::map<std::string, std::function<test_case()>> cases()
     big["int4_group_k28672"] = [] { return int4_linear(2, 64, 28672, 128, false, 41); };
     big["int4_group_k96"]    = [] { return int4_linear(3, 64, 96, 32, true, 42); };
     big["quant_dot_transposed_a"] = [] { return quant_dot_transposed_a(43); };
+    // programs produced by MIGraphX's own quantisation entry points
+    big["pass_quantize_int8"]  = [] { return quantized_mlp(96, 256, 320, 128, false, "ref", 51); };
+    big["pass_quantize_fp8"]   = [] { return quantized_mlp(96, 256, 320, 128, true, "ref", 52); };
+    big["pass_quantize_int8_on_cuda"] = [] { return quantized_mlp(96, 256, 320, 128, false, g_have_device ? "cuda" : "ref", 53); };
+    big["pass_int4_weights_decode"]  = [] { return int4_weights_pass_linear(4, 512, 384, 54); };
+    big["pass_int4_weights_prefill"] = [] { return int4_weights_pass_linear(160, 512, 384, 55); };
     big["c2_layer"]   = [] { return c2_encoder(1, 1); };
     big["c2_layers2"] = [] { return c2_encoder(1, 2); };
     std::map<std::string, std::function<test_case()>> small = {
@@ -147,7 +156,7 @@ std::map<std::string, std::function<test_case()>> cases()
 
 struct cmp_result
 {
-    double max_abs = 0, max_rel = 0;
+    double max_abs = 0, max_rel = 0, rms_err = 0, rms_ref = 0;
     std::size_t mismatched = 0, n = 0;
 };
 
@@ -198,10 +207,23 @@ cmp_result compare(const migraphx::argument& ref, migraphx::argument got, bool e
         r.max_abs      = std::max(r.max_abs, d);
         if(std::fabs(a[i]) > 0)
             r.max_rel = std::max(r.max_rel, d / std::fabs(a[i]));
+        r.rms_err += d * d;
+        r.rms_ref += a[i] * a[i];
         if(not(d <= row_atol + rtol * std::fabs(a[i])))
             ++r.mismatched;
     }
+    r.rms_err = std::sqrt(r.rms_err / static_cast<double>(std::max<std::size_t>(1, r.n)));
+    r.rms_ref = std::sqrt(r.rms_ref / static_cast<double>(std::max<std::size_t>(1, r.n)));
     return r;
+}
+
+// the case's acceptance rule (see test_case::outlier_fraction)
+bool within(const cmp_result& c, const test_case& t)
+{
+    if(c.mismatched == 0)
+        return true;
+    return not t.exact and static_cast<double>(c.mismatched) <= t.outlier_fraction * static_cast<double>(c.n) and
+           c.max_abs <= t.outlier_atol;
 }
 
 } // namespace
@@ -292,9 +314,10 @@ int main(int argc, char** argv)
         {
             auto host = offload ? cuda_out[i] : cuda_t.copy_from(cuda_out[i]);
             auto c    = compare(ref_out[i], host, t.exact, t.rtol, t.atol, rows, t.atol_row_rms);
-            ok        = ok and c.mismatched == 0;
+            ok        = ok and within(c, t);
             std::cout << (i ? ", " : "") << "{\"n\": " << c.n << ", \"mismatched\": " << c.mismatched
-                      << ", \"max_abs\": " << c.max_abs << ", \"max_rel\": " << c.max_rel << "}";
+                      << ", \"max_abs\": " << c.max_abs << ", \"max_rel\": " << c.max_rel
+                      << ", \"rms_err\": " << c.rms_err << ", \"rms_ref\": " << c.rms_ref << "}";
         }
         // the same program with other parameter buffers (the recorded graph does not apply:
         // the target has to notice, run instruction by instruction and record again)
@@ -316,7 +339,7 @@ int main(int argc, char** argv)
             rebind_ok = out2.size() == ref_out.size();
             for(std::size_t i = 0; i < ref_out.size() and i < out2.size(); ++i)
                 rebind_ok = rebind_ok and
-                            compare(ref_out[i], cuda_t.copy_from(out2[i]), t.exact, t.rtol, t.atol, rows, t.atol_row_rms).mismatched == 0;
+                            within(compare(ref_out[i], cuda_t.copy_from(out2[i]), t.exact, t.rtol, t.atol, rows, t.atol_row_rms), t);
             ok = ok and rebind_ok;
         }
         std::cout << "], \"exact\": " << (t.exact ? "true" : "false") << ", \"ref_seconds\": " << ref_s

@@ -11,6 +11,7 @@
 // (GEMM + pointwise / dequantize / unpack_int4 fusion); nothing is shared with that code.
 #include "cuda_ops.hpp"
 #include <migraphx/errors.hpp>
+#include <migraphx/dead_code_elimination.hpp>
 #include <migraphx/instruction.hpp>
 #include <migraphx/iterator_for.hpp>
 #include <migraphx/literal.hpp>
@@ -340,6 +341,15 @@ struct lowerer
                        "); the target has no CPU fallback");
     }
 
+    // MIGRAPHX_CUDA_DISABLE_FUSION: comma-separated list out of layernorm, attention, horizontal -
+    // the multi-operator fusions listed are not applied (their operators are lowered one by one),
+    // for bisecting a numerical difference or a performance change
+    static bool fusion_disabled(const std::string& what)
+    {
+        const char* e = std::getenv("MIGRAPHX_CUDA_DISABLE_FUSION");
+        return e != nullptr and contains(split_string(e, ','), what);
+    }
+
     // ---------------------------------------------------------------- quant_dot chain
     void lower_quant_dot(instruction_ref qd)
     {
@@ -392,6 +402,8 @@ struct lowerer
                    static_cast<shape::type_t>(op.out_type) == shape::float_type)
                 {
                     op.out_type = static_cast<int>(shape::half_type);
+                    // what follows the convert is half arithmetic; what came before it was fp32
+                    op.half_math = bias == m.end() and not seen_act;
                     chain.push_back(u);
                     last     = u;
                     progress = true;
@@ -439,6 +451,10 @@ struct lowerer
             {
                 std::vector<instruction_ref> g;
                 auto fin = match_gelu_erf(m, last, g);
+                // in half arithmetic the kernel divides by the half value of sqrt(2)
+                if(fin != m.end() and op.half_math and
+                   not is_const_scalar(g[1]->inputs()[1], 1.4140625f, 0.0f))
+                    fin = m.end();
                 if(fin != m.end())
                 {
                     op.act = MGX_ACT_GELU_ERF;
@@ -694,6 +710,82 @@ struct lowerer
         return true;
     }
 
+    // dot(A, dequantizelinear(unpack_int4(P), scale, zero point)) with P a compile-time constant
+    // packed along N - the form quantize_int4_weights leaves (src/quantize_int4.cpp:69-95: a
+    // per-tensor scale and zero point on the [K, N] weight, no transpose).  The weights stay int4 in
+    // device memory (the reference never folds through unpack_int4 either,
+    // src/propagate_constant.cpp:39-54); they are re-packed once, here, along K into the [N, K/2]
+    // layout the kernels stream.
+    bool lower_w4a16_kn(instruction_ref dot)
+    {
+        if(dot->inputs().size() != 2)
+            return false;
+        auto a  = dot->inputs()[0];
+        auto dq = dot->inputs()[1];
+        if(a->get_shape().type() != shape::half_type or dq->name() != "dequantizelinear" or
+           dq->get_shape().type() != shape::half_type or dq->get_shape().ndim() != 2 or dq->inputs().size() != 3)
+            return false;
+        auto unpack = dq->inputs()[0];
+        if(unpack->name() != "unpack_int4" or unpack->get_shape().type() != shape::uint8_type or
+           not unpack->inputs()[0]->can_eval() or not dq->inputs()[1]->can_eval() or not dq->inputs()[2]->can_eval())
+            return false;
+        const std::size_t k = dq->get_shape().lens()[0];
+        const std::size_t n = dq->get_shape().lens()[1];
+        if(a->get_shape().lens().back() != k or not a->get_shape().standard() or k % 32 != 0)
+            return false;
+        auto cs = classify_constant(dq->inputs()[1]);
+        auto cz = classify_constant(dq->inputs()[2]);
+        if(cs.kind != bcast_kind::scalar or cz.kind != bcast_kind::scalar)
+            return false;
+        // the unpacked [K, N] values (0..15), then nibbles paired along K, row n of the result
+        argument u = unpack->eval();
+        if(u.empty() or not u.get_shape().standard())
+            return false;
+        const auto* q = reinterpret_cast<const uint8_t*>(u.data());
+        std::vector<uint8_t> packed(n * (k / 2));
+        for(std::size_t kk = 0; kk < k; kk += 2)
+            for(std::size_t nn = 0; nn < n; ++nn)
+                packed[nn * (k / 2) + kk / 2] =
+                    static_cast<uint8_t>((q[kk * n + nn] & 0xF) | ((q[(kk + 1) * n + nn] & 0xF) << 4));
+        std::size_t group = k % 128 == 0 ? 128 : 32;
+        const std::size_t gpr = k / group;
+        std::vector<half> scales(n * gpr, half(cs.values[0]));
+        op_w4a16 op;
+        op.group    = static_cast<int>(group);
+        op.zp_const = static_cast<int>(cz.values[0]);
+        std::vector<instruction_ref> args = {
+            a, m.add_literal(literal{shape{shape::uint8_type, {n, k / 2}}, packed}),
+            m.add_literal(literal{shape{shape::half_type, {n, gpr}}, scales})};
+        mgx_w4_desc d{};
+        d.M     = static_cast<int64_t>(a->get_shape().elements() / k);
+        d.N     = static_cast<int64_t>(n);
+        d.K     = static_cast<int64_t>(k);
+        d.group = op.group;
+        const std::size_t ws = mgx_cuda_w4a16_workspace(&d);
+        if(ws > 0)
+        {
+            op.has_workspace = true;
+            args.push_back(insert_allocation(m, dot, shape{shape::int8_type, {ws}}));
+        }
+        args.push_back(insert_allocation(m, dot, dot->get_shape().as_standard()));
+        consume(dq);
+        consume(unpack);
+        for(auto i : {unpack->inputs()[0], dq->inputs()[1], dq->inputs()[2]})
+        {
+            // the constant chain behind the packed weights (pack_int4(quantizelinear(W))) is dead now
+            auto c = i;
+            while(c->outputs().size() == 1 and not is_builtin(c->name()))
+            {
+                consume(c);
+                if(c->inputs().empty())
+                    break;
+                c = c->inputs()[0];
+            }
+        }
+        consume(m.replace_instruction(dot, op, args));
+        return true;
+    }
+
     // ---------------------------------------------------------------- horizontal fusion
     // Quantized linears that read the same activations with the same kind of epilogue (the Q, K and
     // V projections of an attention block) become one cuda::qgemm over the concatenated weights;
@@ -701,6 +793,8 @@ struct lowerer
     // row-strided matrices (cuda::attention), so no slice ever has to be packed again.
     void fuse_horizontal_qgemms()
     {
+        if(fusion_disabled("horizontal"))
+            return;
         std::vector<instruction_ref> gemms;
         for(auto ins : iterator_for(m))
             if(ins->name() == "cuda::qgemm")
@@ -719,10 +813,17 @@ struct lowerer
                     return false;
                 if(in[1]->name() != "@literal" or in[2]->name() != "@literal" or in[3]->name() != "@literal")
                     return false;
-                if(g->outputs().empty())
-                    return false;
-                return std::all_of(g->outputs().begin(), g->outputs().end(),
-                                   [](auto o) { return o->name() == "cuda::attention"; });
+                // readers: attention operators only (instructions already folded into an earlier
+                // replacement are dead and do not count)
+                bool any = false;
+                for(auto o : g->outputs())
+                {
+                    if(o->name() == "cuda::attention")
+                        any = true;
+                    else if(not is_consumed(o))
+                        return false;
+                }
+                return any;
             };
             if(not eligible(first))
                 continue;
@@ -789,6 +890,8 @@ struct lowerer
     // transpose -> contiguous -> reshape: one cuda::attention that reads the heads in place.
     bool lower_attention(instruction_ref sm)
     {
+        if(fusion_disabled("attention"))
+            return false;
         const auto& ps = sm->get_shape();
         if(ps.type() != shape::half_type or ps.ndim() != 4)
             return false;
@@ -925,6 +1028,8 @@ struct lowerer
     // single-operator lowering.
     bool lower_layernorm(instruction_ref mean)
     {
+        if(fusion_disabled("layernorm"))
+            return false;
         auto x         = mean->inputs().front();
         const auto& xs = x->get_shape();
         const auto nd  = xs.ndim();
@@ -1381,7 +1486,7 @@ struct lowerer
                 lower_quant_dot(ins);
             else if(ins->name() == "dot")
             {
-                if(not lower_w4a16(ins) and not lower_half_dot(ins))
+                if(not lower_w4a16(ins) and not lower_w4a16_kn(ins) and not lower_half_dot(ins))
                     unsupported(ins, "only fp16 operands and the weight-only int4 form "
                                      "dot(A, transpose(dequantizelinear(unpack_int4(W)))) are supported");
             }
@@ -1426,6 +1531,9 @@ struct lowerer
             else
                 unsupported(ins, "no kernel");
         }
+        // the folded chains are dead: remove them, so that no stale reader sees the column slices
+        // the horizontal fusion turns some results into
+        dead_code_elimination{}.apply(m);
         fuse_horizontal_qgemms();
     }
 

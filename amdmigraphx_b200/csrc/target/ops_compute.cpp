@@ -286,6 +286,7 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     d.b_layout   = (b_nk or view_nk) ? MGX_B_NK : MGX_B_KN;
     d.scale_mode = scale_mode;
     d.act        = act;
+    d.flags      = half_math ? MGX_QGEMM_HALF_MATH : 0;
     mgx_qgemm_qout qo{};
     if(qbuf != nullptr)
     {

@@ -17,6 +17,7 @@
 #include <migraphx/simplify_qdq.hpp>
 #include <migraphx/generate.hpp>
 #include <migraphx/half.hpp>
+#include <migraphx/quantization.hpp>
 #include <chrono>
 #include <cmath>
 #include <cstring>
@@ -51,6 +52,14 @@ struct test_case
     // reference's own cross-target check included (it bounds the RMS error against the largest
     // magnitude, src/include/migraphx/verify.hpp:174-195).
     bool atol_row_rms = false;
+    // Whole layers with quantizers inside: where the target's kernels round an intermediate value
+    // differently from the reference's operator chain (a fused attention that keeps fp32 where the
+    // chain rounds to half, fp32 sums in another order), a value next to a rounding boundary of a
+    // following quantizelinear lands in the neighbouring int8 bucket, and the layer's result moves
+    // by (activation scale) x (weight) for every such flip.  Up to `outlier_fraction` of the
+    // elements may therefore miss (rtol, atol) as long as they stay within `outlier_atol`.
+    double outlier_fraction = 0.0;
+    double outlier_atol     = 0.0;
     // Cases too large for the CPU interpreter to evaluate in full: the rows of the left operand
     // are independent, so ref evaluates `ref_prog` - the same program built for fewer rows (same
     // seed, hence the same weights) - on `ref_params`, whose rows are rows `sample_rows` of the
@@ -684,12 +693,16 @@ inline test_case bert_layer_int8(std::size_t b, std::size_t sq, std::size_t h, s
     migraphx::argument xa{shape{shape::float_type, {m, hid}}};
     std::memcpy(xa.data(), xv.data(), xv.size() * sizeof(float));
     t.params["x"] = xa;
-    // measured: max abs error 7e-7.  The bound leaves room for one int8 value of the output
-    // projection's input landing in the neighbouring bucket (fp16 attention: fp32 against double
-    // accumulation), which moves an output by about scale_x * scale_w * |w| before the LayerNorm
+    // The attention block runs as one kernel that keeps fp32 where the reference's operator chain
+    // rounds to half: its results differ by ~1e-3 relative, and this case quantises them with a
+    // coarse scale (a handful of int8 levels), so some values land in the neighbouring bucket; each
+    // such flip moves an output by about scale_x * |w| before the LayerNorm.  With the attention
+    // fusion disabled (MIGRAPHX_CUDA_DISABLE_FUSION=attention) the measured max abs error is 7e-7.
     t.ref_simplify_qdq = true;
     t.rtol = 1e-2;
     t.atol = 2e-3;
+    t.outlier_fraction = 3e-2;
+    t.outlier_atol     = 6e-2;
     return t;
 }
 
@@ -738,6 +751,73 @@ inline test_case embed_rope_f16(std::size_t b, std::size_t sq, std::size_t past,
     std::memcpy(ca.data(), ch.data(), ch.size() * sizeof(migraphx::half));
     t.params["cache"] = ca;
     t.exact = true; // exactly rounded fp16 operators and byte moves
+    return t;
+}
+
+// An un-quantised fp32 MLP (dot + bias + relu, dot + bias) taken through MIGraphX's own
+// quantize_int8 / quantize_fp8 (src/quantization.cpp:88-210: capture operators, a calibration run
+// on `calib_target`, then Q/DQ pairs with the measured scales) - the program a user of the
+// reference would hand to a target.
+inline test_case quantized_mlp(std::size_t mrows, std::size_t k, std::size_t h, std::size_t n, bool fp8,
+                               const std::string& calib_target, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    auto x   = mm->add_parameter("x", shape{shape::float_type, {mrows, k}});
+    auto w1  = mm->add_literal(migraphx::literal{shape{shape::float_type, {k, h}}, rand_normal(g, k * h, 0.06f)});
+    auto b1  = mm->add_literal(migraphx::literal{shape{shape::float_type, {h}}, rand_normal(g, h, 0.1f)});
+    auto w2  = mm->add_literal(migraphx::literal{shape{shape::float_type, {h, n}}, rand_normal(g, h * n, 0.06f)});
+    auto b2  = mm->add_literal(migraphx::literal{shape{shape::float_type, {n}}, rand_normal(g, n, 0.1f)});
+    auto d1  = mm->add_instruction(migraphx::make_op("dot"), x, w1);
+    auto a1  = mm->add_instruction(migraphx::make_op("add"), d1, bcast_axis(mm, b1, 1, {mrows, h}));
+    auto r1  = mm->add_instruction(migraphx::make_op("relu"), a1);
+    auto d2  = mm->add_instruction(migraphx::make_op("dot"), r1, w2);
+    auto y   = mm->add_instruction(migraphx::make_op("add"), d2, bcast_axis(mm, b2, 1, {mrows, n}));
+    mm->add_return({y});
+    auto fill = [&](unsigned sd) {
+        std::mt19937 gg(sd);
+        auto v = rand_normal(gg, mrows * k, 1.0f);
+        migraphx::argument a{shape{shape::float_type, {mrows, k}}};
+        std::memcpy(a.data(), v.data(), v.size() * sizeof(float));
+        return a;
+    };
+    // calibration data: two seeded batches
+    std::vector<migraphx::parameter_map> calib = {{{"x", fill(seed + 1)}}, {{"x", fill(seed + 2)}}};
+    auto ct = migraphx::make_target(calib_target);
+    if(fp8)
+        migraphx::quantize_fp8(t.prog, ct, calib);
+    else
+        migraphx::quantize_int8(t.prog, ct, calib);
+    t.params["x"] = fill(seed + 3);
+    // both targets run the quantised program; ref after simplify_qdq, like every GPU pipeline
+    t.ref_simplify_qdq = true;
+    t.rtol = fp8 ? 2e-2 : 1e-5;
+    t.atol = fp8 ? 1e-2 : 2e-5;
+    return t;
+}
+
+// An fp16 linear whose weight literal went through MIGraphX's quantize_int4_weights
+// (src/quantization.cpp:189-192, src/quantize_int4.cpp:38-103): per-tensor scale and zero point,
+// [K, N] weight, nibbles packed along N.
+inline test_case int4_weights_pass_linear(std::size_t mrows, std::size_t k, std::size_t n, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    auto a   = mm->add_parameter("a", shape{shape::half_type, {mrows, k}});
+    auto wf  = rand_normal(g, k * n, 0.05f);
+    std::vector<migraphx::half> wh(wf.begin(), wf.end());
+    auto w   = mm->add_literal(migraphx::literal{shape{shape::half_type, {k, n}}, wh});
+    mm->add_return({mm->add_instruction(migraphx::make_op("dot"), a, w)});
+    migraphx::quantize_int4_weights(t.prog);
+    auto av = rand_normal(g, mrows * k, 1.0f);
+    std::vector<migraphx::half> ah(av.begin(), av.end());
+    migraphx::argument aa{shape{shape::half_type, {mrows, k}}};
+    std::memcpy(aa.data(), ah.data(), ah.size() * sizeof(migraphx::half));
+    t.params["a"] = aa;
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
     return t;
 }
 

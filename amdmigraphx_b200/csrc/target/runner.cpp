@@ -80,6 +80,8 @@ struct mgx_bert_desc
     int64_t batch, seq, layers, hidden, heads, ffn, vocab;
     uint32_t seed;
     int32_t offload_copy; // 1: eval() takes host arguments and returns host results
+    int32_t fixed_scales; // 1: typical fixed activation scales instead of a calibration run
+    int32_t reserved;
 };
 
 MGX_RUNNER_API const char* mgx_runner_last_error() { return g_error.c_str(); }
@@ -108,7 +110,9 @@ MGX_RUNNER_API int mgx_runner_create_bert(const mgx_bert_desc* d, void** out)
         if(cached != scale_cache.end())
             c.act_scales = cached->second;
         bert_program bp;
-        if(c.calibrate())
+        if(d->fixed_scales != 0)
+            bp = bert_encoder_int8_calibrated(c, false);
+        else if(c.calibrate())
         {
             bp = bert_encoder_int8_calibrated(c, true, &c.act_scales);
             scale_cache[key.str()] = c.act_scales;

@@ -109,7 +109,8 @@ class ClockSampler(object):
 # ------------------------------------------------------------------ the plug-in, through the runner
 class BertDesc(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in ("batch", "seq", "layers", "hidden", "heads", "ffn", "vocab")] + \
-               [("seed", ctypes.c_uint32), ("offload_copy", ctypes.c_int32)]
+               [("seed", ctypes.c_uint32), ("offload_copy", ctypes.c_int32), ("fixed_scales", ctypes.c_int32),
+                ("reserved", ctypes.c_int32)]
 
 
 class Runner(object):
@@ -148,10 +149,11 @@ class Runner(object):
         if rc != 0:
             raise RuntimeError(f"{what}: {cls.lib().mgx_runner_last_error().decode()}")
 
-    def __init__(self, batch, offload, seed=0, **dims):
+    def __init__(self, batch, offload, seed=0, fixed_scales=False, **dims):
         d = dict(BERT)
         d.update(dims)
-        desc = BertDesc(batch=batch, seed=seed, offload_copy=1 if offload else 0, **d)
+        desc = BertDesc(batch=batch, seed=seed, offload_copy=1 if offload else 0,
+                        fixed_scales=1 if fixed_scales else 0, reserved=0, **d)
         self.h = ctypes.c_void_p()
         self.check(self.lib().mgx_runner_create_bert(ctypes.byref(desc), ctypes.byref(self.h)),
                    "mgx_runner_create_bert")
@@ -662,6 +664,20 @@ def run_case(a):
     dev = torch.device("cuda:0")
     M, N, K = a.m, a.n, a.k
     act = None if a.act == "none" else a.act
+    if a.case == "encoder":
+        # the benchmark's program by itself: --m sequences, --n layers, fixed activation scales (no
+        # calibration run, so that the launches of the process are those of eval() alone)
+        import numpy as np
+        r = Runner(a.m, offload=False, fixed_scales=True, layers=a.n)
+        r.set_ids(np.random.default_rng(0).integers(0, BERT["vocab"], size=(a.m, BERT["seq"])))
+        for _ in range(a.case_warmup):
+            Runner.eval_many([r], 1)
+        dms, wms = Runner.eval_many([r], a.iters)
+        print(json.dumps({"case": a.case, "sequences": a.m, "layers": a.n, "launches_per_eval": r.launches,
+                          "device_ms_per_eval": dms / a.iters, "host_ms_per_eval": wms / a.iters,
+                          "tops": r.quant_ops / (dms / a.iters * 1e-3) / 1e12, "ops": r.op_counts(),
+                          "device_status": capi.device_status()}))
+        return 0
     if a.case in ("qgemm_i8", "qgemm_fp8"):
         A = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
         B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
@@ -717,7 +733,7 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
-    ap.add_argument("--case", default=None, choices=["qgemm_i8", "qgemm_fp8", "quantize", "w4a16"],
+    ap.add_argument("--case", default=None, choices=["qgemm_i8", "qgemm_fp8", "quantize", "w4a16", "encoder"],
                     help="run one kernel by itself (for profiler captures) instead of the benchmark")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)

@@ -300,8 +300,16 @@ typedef struct mgx_qgemm_desc
     int32_t b_layout;                      /* mgx_b_layout                   */
     int32_t scale_mode;                    /* mgx_scale_mode                 */
     int32_t act;                           /* mgx_act                        */
-    int32_t reserved;
+    int32_t flags;                         /* MGX_QGEMM_* bits, 0 for none   */
 } mgx_qgemm_desc;
+
+/* out_type MGX_F16 only: the operators after dequantizelinear run in half, as in an fp16 model
+ * (src/simplify_qdq.cpp:283-287 converts the dequantised value to half first): the dequantised
+ * value, the bias sum, every step of the erf-GELU ((x * 0.5) * (erf(x / half(sqrt 2)) + 1),
+ * src/op/builder/gelu.cpp:58-74) and the residual sum are each truncated to half like
+ * migraphx::half arithmetic.  Without the flag they are fp32 operations and only the final
+ * value is converted. */
+#define MGX_QGEMM_HALF_MATH 1
 
 MGX_API size_t mgx_cuda_qgemm_workspace(const mgx_qgemm_desc* desc);
 MGX_API int mgx_cuda_qgemm(const mgx_qgemm_desc* desc,

@@ -21,7 +21,8 @@ here with the same trivial content:
     MIGRAPHX_REGISTER_OP(op::<name>) (cmake/RegisterOp.cmake:24-62 over the
     operator list at src/CMakeLists.txt:177-328; the list is parsed from that
     file at build time)
-  * stubs for msgpack / sqlite (third-party libraries absent here) that throw.
+  * stand-ins for msgpack / sqlite (third-party libraries absent here): sqlite throws, the
+    msgpack entry points carry JSON text (save / load still round-trip).
 
 Usage: python oracle/build_ref.py [--ref <MIGraphX source tree>] [--jobs 8]
 """
@@ -117,17 +118,29 @@ def gen_files(ref, gen):
         write_if_changed(p, "\n".join(body))
         units.append(p)
     stub = os.path.join(gen, "stubs.cpp")
-    write_if_changed(stub, """// msgpack-c and sqlite3 are not available in this environment: the entry points
-// exist so the library links, and throw when used (.mxr json format still works).
+    write_if_changed(stub, """// msgpack-c and sqlite3 are not available in this environment.  sqlite: the entry points exist
+// so that the library links, and throw when used.  msgpack: the four entry points carry the
+// value's JSON text as their byte stream instead of msgpack (binary blobs included, as json.cpp
+// writes them), so that migraphx::save / load round-trip a program in their default format; the
+// files are not interchangeable with .mxr files written by a build that has msgpack-c.
 #include <migraphx/msgpack.hpp>
 #include <migraphx/sqlite.hpp>
+#include <migraphx/json.hpp>
 #include <migraphx/errors.hpp>
 namespace migraphx {
 inline namespace MIGRAPHX_INLINE_NS {
-void to_msgpack(const value&, std::function<void(const char*, std::size_t)>) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
-std::vector<char> to_msgpack(const value&) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
-value from_msgpack(const std::vector<char>&) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
-value from_msgpack(const char*, std::size_t) { MIGRAPHX_THROW("msgpack unavailable in this build"); }
+std::vector<char> to_msgpack(const value& v)
+{
+    const auto s = to_json_string(v);
+    return {s.begin(), s.end()};
+}
+void to_msgpack(const value& v, std::function<void(const char*, std::size_t)> writer)
+{
+    const auto s = to_json_string(v);
+    writer(s.data(), s.size());
+}
+value from_msgpack(const char* buffer, std::size_t size) { return from_json_string(std::string(buffer, size)); }
+value from_msgpack(const std::vector<char>& buffer) { return from_msgpack(buffer.data(), buffer.size()); }
 sqlite sqlite::read(const fs::path&) { MIGRAPHX_THROW("sqlite unavailable in this build"); }
 sqlite sqlite::write(const fs::path&) { MIGRAPHX_THROW("sqlite unavailable in this build"); }
 std::vector<std::unordered_map<std::string, std::string>> sqlite::execute(const std::string&) { MIGRAPHX_THROW("sqlite unavailable in this build"); }

@@ -319,3 +319,27 @@ def attention_chain(q, k, v, batch, seq, heads, scale):
     p = half_trunc(e.astype(np.float32) / tot)
     o = half_trunc(np.matmul(p.astype(np.float64), vh))
     return np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(batch * seq, heads * d)
+
+
+def qlinear_epilogue_half_chain(acc, scale, bias=None, act=None, residual=None):
+    """The operators after quant_dot in an fp16 model (src/simplify_qdq.cpp:283-287):
+    dequantizelinear in fp32, convert to half, then add(bias), the erf-GELU chain of
+    src/op/builder/gelu.cpp:58-74 and add(residual) as HALF operators - every one computes in fp32
+    and stores half (truncating)."""
+    f32 = lambda a: np.asarray(a).astype(np.float32)  # noqa: E731
+    v = half_trunc(dequantizelinear(np.asarray(acc), np.asarray(scale, dtype=np.float32)))
+    if bias is not None:
+        v = half_trunc(f32(v) + f32(np.asarray(bias, dtype=np.float16)))
+    if act == "gelu_erf":
+        mh = half_trunc(f32(v) * np.float32(0.5))
+        dv = half_trunc(f32(v) / f32(half_trunc(np.float32(np.sqrt(2.0)))))
+        er = half_trunc(_erff(f32(dv)))
+        e1 = half_trunc(f32(er) + np.float32(1.0))
+        v = half_trunc(f32(mh) * f32(e1))
+    elif act == "relu":
+        v = np.maximum(v, np.float16(0))
+    elif act not in (None, "none"):
+        raise ValueError(act)
+    if residual is not None:
+        v = half_trunc(f32(v) + f32(residual))
+    return v

@@ -121,7 +121,9 @@ def test_constant_fp16_weight_is_relaid_out_once():
 
 def test_bert_layer_compiles_into_one_graph():
     out = _passes("bert_layer_int8")
-    assert out.count("cuda::qgemm") == 6  # the six QDQ linears
+    # the Q, K and V projections as one GEMM over the concatenated weights, then O, FFN1, FFN2
+    assert out.count("cuda::qgemm") == 4 and "half_type, {128, 768}, {768, 1}" in out
+    assert out.count("slice[axes={1}") == 3
     assert out.count("cuda::graph_begin") == 1 and out.count("cuda::graph_end") == 1
     # FFN1: GELU and the quantizelinear feeding FFN2 run in its epilogue
     assert any("act=2" in l and "q_type=5" in l and "write_d=0" in l for l in out.splitlines())

@@ -273,7 +273,7 @@ def test_skinny_without_workspace_runs_as_tiles(cuda_device):
     d = torch.empty((4, 384), dtype=torch.int32, device=cuda_device)
     desc = capi.QgemmDesc(M=4, N=384, K=256, batch=1, lda=256, ldb=256, ldd=384, stride_a=0, stride_b=0,
                           stride_d=0, ab_type=capi.I8, out_type=capi.I32, b_layout=capi.B_NK,
-                          scale_mode=capi.SCALE_NONE, act=0, reserved=0)
+                          scale_mode=capi.SCALE_NONE, act=0, flags=0)
     assert lib.mgx_cuda_qgemm_workspace(ctypes.byref(desc)) > 0
     capi.check(lib.mgx_cuda_qgemm(ctypes.byref(desc), capi._ptr(at), capi._ptr(wt), capi._ptr(d), None,
                                   None, None, None, 0, capi._stream()), "mgx_cuda_qgemm")
@@ -301,3 +301,33 @@ def test_qlinear_int8_fp16_tiny_outputs_bit_exact(cuda_device, act):
                      out_dtype=torch.float16).cpu().numpy()
     assert np.count_nonzero(np.abs(ref.astype(np.float32)) < 6.1e-5) > ref.size // 2
     np.testing.assert_array_equal(got, ref)
+
+
+@pytest.mark.parametrize("M,N,K,act,res", [(384, 3072, 768, "gelu_erf", False), (256, 768, 3072, None, True),
+                                           (130, 200, 96, "gelu_erf", True), (384, 768, 768, "relu", False)])
+def test_int8_half_math_epilogue_matches_half_operator_chain(cuda_device, M, N, K, act, res):
+    """fp16 model: after dequantizelinear the value is converted to half and bias add, erf-GELU and
+    residual add are half operators, each rounding (truncating) to half.  With MGX_QGEMM_HALF_MATH
+    the fused epilogue makes the same roundings: identical bits except where the kernel's erf and
+    its multiplication by 1 / half(sqrt 2) land in the neighbouring half (< 0.1 % of the elements,
+    one half step)."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + N)
+    a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
+    scale = (0.03 * rng.uniform(0.4, 1.2, size=N) / (127.0 * np.sqrt(K))).astype(np.float32)
+    bias = rng.normal(0, 0.2, size=N).astype(np.float16)
+    resid = rng.normal(0, 1, size=(M, N)).astype(np.float16) if res else None
+    t = lambda v: torch.from_numpy(np.ascontiguousarray(v)).to(cuda_device)  # noqa: E731
+    got = capi.qgemm(t(a), t(b), b_layout=capi.B_NK, scale=t(scale), bias=t(bias.astype(np.float32)), act=act,
+                     residual=None if resid is None else t(resid), out_dtype=torch.float16, half_math=True)
+    torch.cuda.synchronize()
+    ref = O.qlinear_epilogue_half_chain(O.quant_dot_int8(a, b.T), scale[None, :], bias, act, resid)
+    g, r = got.cpu().numpy(), ref
+    diff = g.view(np.uint16) != r.view(np.uint16)
+    if act == "gelu_erf":
+        assert diff.mean() < 1e-3
+        np.testing.assert_allclose(g.astype(np.float32), r.astype(np.float32), rtol=2e-3, atol=1e-6)
+    else:
+        assert not diff.any()

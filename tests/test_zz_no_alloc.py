@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 def _desc(capi, M, N, K, out_type, scale_mode=0, act=0):
     return capi.QgemmDesc(M=M, N=N, K=K, batch=1, lda=K, ldb=N, ldd=N, stride_a=M * K,
                           stride_b=K * N, stride_d=M * N, ab_type=capi.I8, out_type=out_type,
-                          b_layout=capi.B_KN, scale_mode=scale_mode, act=act, reserved=0)
+                          b_layout=capi.B_KN, scale_mode=scale_mode, act=act, flags=0)
 
 
 def test_static_scratch_matches_workspace_entry_point(cuda_device):
@@ -85,7 +85,7 @@ def test_static_scratch_weight_streaming_route(cuda_device):
         d = capi.QgemmDesc(M=M, N=N, K=K, batch=1, lda=K, ldb=K, ldd=N, stride_a=M * K, stride_b=N * K,
                            stride_d=M * N, ab_type=capi.I8, out_type=capi.F32 if fused else capi.I32,
                            b_layout=capi.B_NK, scale_mode=capi.SCALE_PER_COL if fused else capi.SCALE_NONE,
-                           act=capi.ACT_RELU if fused else capi.ACT_NONE, reserved=0)
+                           act=capi.ACT_RELU if fused else capi.ACT_NONE, flags=0)
         need = lib.mgx_cuda_qgemm_workspace(ctypes.byref(d))
         assert 0 < need <= lib.mgx_cuda_qgemm_static_scratch_limit()  # the streaming route is taken
         odt = torch.float32 if fused else torch.int32
@@ -120,7 +120,7 @@ def test_static_scratch_falls_back_to_tiles_beyond_the_limit(cuda_device):
     M, N, K = 16, 151936, 128
     d = capi.QgemmDesc(M=M, N=N, K=K, batch=1, lda=K, ldb=K, ldd=N, stride_a=M * K, stride_b=N * K,
                        stride_d=M * N, ab_type=capi.I8, out_type=capi.I32, b_layout=capi.B_NK,
-                       scale_mode=capi.SCALE_NONE, act=capi.ACT_NONE, reserved=0)
+                       scale_mode=capi.SCALE_NONE, act=capi.ACT_NONE, flags=0)
     if lib.mgx_cuda_qgemm_workspace(ctypes.byref(d)) <= lib.mgx_cuda_qgemm_static_scratch_limit():
         pytest.skip("this shape's partial sums fit the static array")
     a = torch.from_numpy(rng.integers(-128, 128, size=(M, K), dtype=np.int8)).to(cuda_device)
