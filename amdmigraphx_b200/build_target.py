@@ -49,7 +49,7 @@ def build_target(verbose=False, force=False):
         os.makedirs(d, exist_ok=True)
     cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
     cuda_lib = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/lib64"
-    flags = ["-std=c++17", "-O2", "-fPIC", "-w", "-pthread", "-fvisibility=hidden",
+    flags = ["-std=c++17", "-O2", "-DNDEBUG", "-fPIC", "-w", "-pthread", "-fvisibility=hidden",
              "-DMIGRAPHX_USE_EIGEN=0", f"-I{gen}", f"-I{inc}", f"-I{cuda_inc}"]
     headers = [os.path.join(SRC, f) for f in os.listdir(SRC) if f.endswith(".hpp")]
     headers.append(os.path.join(ROOT, "include", "mgx_cuda.h"))

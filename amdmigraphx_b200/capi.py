@@ -25,7 +25,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
+    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_ex", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -311,9 +311,10 @@ class LayernormDesc(ctypes.Structure):
                 ("q_zero_point", ctypes.c_float), ("reserved", ctypes.c_int32)]
 
 
-def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0, write_y=True):
+def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0, write_y=True, dq_scale=None):
     """LayerNorm over the last axis of a 2-D tensor; returns (y or None, q or None) where q is the
-    int8 quantizelinear(y, q_scale, q_zero_point) written by the same launch."""
+    int8 quantizelinear(y, q_scale, q_zero_point) written by the same launch; with dq_scale a third
+    tensor, dequantizelinear(q, dq_scale, q_zero_point) in x's type, is returned too."""
     import torch
     lib = load()
     rows, cols = x.shape
@@ -321,6 +322,13 @@ def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0
     q = torch.empty((rows, cols), dtype=torch.int8, device=x.device) if q_scale is not None else None
     d = LayernormDesc(rows=rows, cols=cols, ldx=x.stride(0), ldy=cols, ldq=cols, type=_dtype_code(x), eps=eps,
                       q_type=I8, q_scale=float(q_scale or 1.0), q_zero_point=float(q_zero_point), reserved=0)
+    if dq_scale is not None:
+        dq = torch.empty_like(x)
+        lib.mgx_cuda_layernorm_ex.argtypes = [ctypes.POINTER(LayernormDesc)] + [ctypes.c_void_p] * 6 + \
+            [ctypes.c_int64, ctypes.c_float, ctypes.c_void_p]
+        check(lib.mgx_cuda_layernorm_ex(ctypes.byref(d), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(q), _ptr(dq),
+                                        cols, float(dq_scale), _stream()), "mgx_cuda_layernorm_ex")
+        return y, q, dq
     lib.mgx_cuda_layernorm.argtypes = [ctypes.POINTER(LayernormDesc)] + [ctypes.c_void_p] * 6
     check(lib.mgx_cuda_layernorm(ctypes.byref(d), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(q), _stream()),
           "mgx_cuda_layernorm")

@@ -78,6 +78,14 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// 2^x for x <= 0 (and -inf-like arguments, which give 0): one instruction
+__device__ __forceinline__ float fast_exp2(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // A [rows, 64] fp16 tile in shared memory: 128-byte rows, the 16-byte chunk index XOR-ed with the
 // row's low three bits.
 __device__ __forceinline__ __half* tile_ptr(__half* tile, int row, int chunk)
@@ -164,32 +172,36 @@ __global__ void __launch_bounds__(128) attention_f16_kernel(const attention_para
                 mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
             }
         }
-        // ---- scores as the separate operators round them, keys beyond the sequence masked
+        // ---- scores as the separate operators round them (dot -> half, * scale -> half; the mantissa
+        // cut is the truncation for every value in the normal half range, and smaller ones vanish in
+        // the softmax anyway), keys beyond the sequence masked (only the last block can hold any)
         const int kbase = kb * AT_BN;
         float mx[2] = {-FLT_MAX, -FLT_MAX};
+        const bool tail = kbase + AT_BN > p.seq;
 #pragma unroll
         for(int j = 0; j < 8; ++j)
         {
 #pragma unroll
             for(int e = 0; e < 4; ++e)
             {
-                float x = truncate_to_half_precision(s[j][e]);
-                x       = truncate_to_half_precision(x * p.scale);
-                const int key = kbase + j * 8 + 2 * t + (e & 1);
-                x       = key < p.seq ? x : -FLT_MAX;
+                float x = __uint_as_float(__float_as_uint(s[j][e]) & 0xFFFFE000u);
+                x       = __uint_as_float(__float_as_uint(x * p.scale) & 0xFFFFE000u);
+                if(tail)
+                    x = kbase + j * 8 + 2 * t + (e & 1) < p.seq ? x : -FLT_MAX;
                 s[j][e] = x;
                 mx[e >> 1] = fmaxf(mx[e >> 1], x);
             }
         }
-        float corr[2];
+        float corr[2], mneg[2];
 #pragma unroll
         for(int r = 0; r < 2; ++r)
         {
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
             mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
             const float m_new = fmaxf(m_run[r], mx[r]);
-            corr[r]  = exp2f((m_run[r] - m_new) * log2e);
+            corr[r]  = fast_exp2((m_run[r] - m_new) * log2e);
             m_run[r] = m_new;
+            mneg[r]  = -m_new * log2e;
             l_run[r] *= corr[r];
         }
 #pragma unroll
@@ -207,7 +219,7 @@ __global__ void __launch_bounds__(128) attention_f16_kernel(const attention_para
 #pragma unroll
             for(int i = 0; i < 4; ++i)
             {
-                e[i] = exp2f((s[j][i] - m_run[i >> 1]) * log2e);
+                e[i] = fast_exp2(fmaf(s[j][i], log2e, mneg[i >> 1])); // exp(s - max)
                 l_run[i >> 1] += e[i];
             }
             const __half2 lo = __floats2half2_rn(e[0], e[1]); // row g

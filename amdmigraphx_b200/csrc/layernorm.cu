@@ -33,11 +33,13 @@ struct ln_params
     const void* beta;
     void* y;
     void* q;
-    int64_t rows, ldx, ldy, ldq;
+    void* dq; // dequantizelinear(q) in x's type, or null
+    int64_t rows, ldx, ldy, ldq, lddq;
     int cols;
     float eps;
     float inv_n;
     float q_scale, q_rcp, q_zp;
+    float dq_scale;
     int q_fp8;
 };
 
@@ -183,6 +185,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
             // truncated to half), round half to even, + zero point, saturate
             // (src/include/migraphx/op/quantizelinear.hpp:89-103)
             uint8_t qb[VE];
+            float dqv[VE]; // (q - zero point) * scale, the dequantised copy some programs read next
 #pragma unroll
             for(int j = 0; j < VE; ++j)
             {
@@ -191,15 +194,27 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
                 qv              = ln_round<T>(__fmaf_rn(rem, p.q_rcp, qv)); // correctly rounded quotient
                 if(p.q_fp8)
                 {
-                    qv    = fmaxf(-448.0f, fminf(448.0f, qv + p.q_zp));
-                    qb[j] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
+                    qv     = fmaxf(-448.0f, fminf(448.0f, qv + p.q_zp));
+                    qb[j]  = static_cast<uint8_t>(__nv_cvt_float_to_fp8(qv, __NV_SATFINITE, __NV_E4M3));
+                    dqv[j] = 0.0f; // not offered for fp8 (rejected on the host)
                 }
                 else
                 {
-                    qv    = fmaxf(q_lo, fminf(q_hi, qv));
-                    qb[j] = static_cast<uint8_t>(__float_as_int(__fadd_rn(qv, 12582912.0f)) - 0x4B400000 +
-                                                 static_cast<int>(p.q_zp));
+                    qv           = fmaxf(q_lo, fminf(q_hi, qv));
+                    const int qr = __float_as_int(__fadd_rn(qv, 12582912.0f)) - 0x4B400000; // q - zero point
+                    qb[j]        = static_cast<uint8_t>(qr + static_cast<int>(p.q_zp));
+                    dqv[j]       = ln_round<T>(static_cast<float>(qr) * p.dq_scale);
                 }
+            }
+            if(p.dq != nullptr)
+            {
+                T* dr = static_cast<T*>(p.dq) + row * p.lddq + vi * VE;
+                if constexpr(std::is_same<T, float>::value)
+                    *reinterpret_cast<float4*>(dr) = make_float4(dqv[0], dqv[1], dqv[2], dqv[3]);
+                else
+                    *reinterpret_cast<uint4*>(dr) =
+                        make_uint4(cvt_rz_f16x2(dqv[0], dqv[1]), cvt_rz_f16x2(dqv[2], dqv[3]),
+                                   cvt_rz_f16x2(dqv[4], dqv[5]), cvt_rz_f16x2(dqv[6], dqv[7]));
             }
             uint8_t* qr = static_cast<uint8_t*>(p.q) + row * p.ldq + vi * VE;
             if constexpr(VE == 8)
@@ -252,6 +267,12 @@ extern "C" int mgx_cuda_layernorm_supported(int type, int64_t cols)
 extern "C" int mgx_cuda_layernorm(const mgx_layernorm_desc* d, const void* x, const void* gamma, const void* beta,
                                   void* y, void* q, void* stream_)
 {
+    return mgx_cuda_layernorm_ex(d, x, gamma, beta, y, q, nullptr, 0, 0.0f, stream_);
+}
+
+extern "C" int mgx_cuda_layernorm_ex(const mgx_layernorm_desc* d, const void* x, const void* gamma, const void* beta,
+                                     void* y, void* q, void* dq, int64_t lddq, float dq_scale, void* stream_)
+{
     using namespace mgx;
     if(d == nullptr or x == nullptr or (y == nullptr and q == nullptr))
         return MGX_E_INVALID_ARG;
@@ -275,12 +296,24 @@ extern "C" int mgx_cuda_layernorm(const mgx_layernorm_desc* d, const void* x, co
     }
     if(y != nullptr and d->ldy < d->cols)
         return MGX_E_INVALID_ARG;
+    if(dq != nullptr)
+    {
+        if(q == nullptr or d->q_type != MGX_I8)
+            return MGX_E_UNSUPPORTED;
+        if(lddq < d->cols)
+            return MGX_E_INVALID_ARG;
+        if(misaligned(dq, lddq, 16))
+            return MGX_E_ALIGNMENT;
+    }
     ln_params p{};
     p.x       = x;
     p.gamma   = gamma;
     p.beta    = beta;
     p.y       = y;
     p.q       = q;
+    p.dq      = dq;
+    p.lddq    = lddq;
+    p.dq_scale = dq_scale;
     p.rows    = d->rows;
     p.cols    = static_cast<int>(d->cols);
     p.ldx     = d->ldx;

@@ -110,7 +110,6 @@ std::map<std::string, std::function<test_case()>> cases()
     // programs produced by MIGraphX's own quantisation entry points
     big["pass_quantize_int8"]  = [] { return quantized_mlp(96, 256, 320, 128, false, "ref", 51); };
     big["pass_quantize_fp8"]   = [] { return quantized_mlp(96, 256, 320, 128, true, "ref", 52); };
-    big["pass_quantize_int8_on_cuda"] = [] { return quantized_mlp(96, 256, 320, 128, false, g_have_device ? "cuda" : "ref", 53); };
     big["pass_int4_weights_decode"]  = [] { return int4_weights_pass_linear(4, 512, 384, 54); };
     big["pass_int4_weights_prefill"] = [] { return int4_weights_pass_linear(160, 512, 384, 55); };
     big["c2_layer"]   = [] { return c2_encoder(1, 1); };

@@ -301,9 +301,10 @@ struct op_reduce
 // LayerNorm over the innermost axis in one launch (mgx_cuda_layernorm), the fusion of the chain
 // reduce_mean, sub, mul, reduce_mean, add(eps), rsqrt, mul, [mul(gamma)], [add(beta)] the ONNX
 // parser emits (src/onnx/parse_layernorm.cpp:100-140), optionally with the per-tensor
-// quantizelinear that reads its result.  Inputs: x, [gamma [cols]], [beta [cols]], then - as for
-// cuda::qgemm - the quantised buffer (q_type != 0) and / or the output buffer; the last input is
-// what compute() returns.
+// quantizelinear that reads its result and the dequantizelinear of that quantised tensor (has_dq:
+// the dequantised copy simplify_qdq makes other readers use).  Inputs: x, [gamma [cols]],
+// [beta [cols]], [dequantised buffer], then - as for cuda::qgemm - the quantised buffer
+// (q_type != 0) and / or the output buffer; the last input is what compute() returns.
 struct op_layernorm
 {
     float eps      = 1e-5f;
@@ -313,12 +314,14 @@ struct op_layernorm
     float q_scale  = 1.0f;
     float q_zp     = 0.0f;
     bool write_y   = true;
+    bool has_dq    = false;
+    float dq_scale = 1.0f;
     template <class Self, class F>
     static auto reflect(Self& self, F f)
     {
         return pack(f(self.eps, "eps"), f(self.has_gamma, "has_gamma"), f(self.has_beta, "has_beta"),
                     f(self.q_type, "q_type"), f(self.q_scale, "q_scale"), f(self.q_zp, "q_zp"),
-                    f(self.write_y, "write_y"));
+                    f(self.write_y, "write_y"), f(self.has_dq, "has_dq"), f(self.dq_scale, "dq_scale"));
     }
     std::string name() const { return "cuda::layernorm"; }
     shape compute_shape(const std::vector<shape>& inputs) const;

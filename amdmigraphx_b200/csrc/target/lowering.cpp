@@ -482,18 +482,35 @@ struct lowerer
             unsupported(last, "residual type differs from the output type");
 
         // A: K-contiguous rows; with batch dimensions the entries must be evenly spaced, so a
-        // transposed / sliced view (heads of an attention block) is packed first
+        // transposed / sliced view (heads of an attention block) is packed first; rows whose length
+        // is no multiple of 16 bytes (the tensor maps' pitch rule) are copied into padded rows
         {
-            const auto& as = a->get_shape();
-            const auto nd  = as.ndim();
+            const auto as = a->get_shape();
+            const auto nd = as.ndim();
+            const auto k  = as.lens()[nd - 1];
             const bool rows_ok = as.strides()[nd - 1] == 1 and as.strides()[nd - 2] % 16 == 0;
             if(not as.standard() and (nd > 2 or not rows_ok))
                 a = standard_copy(qd, a);
+            if(k % 16 != 0)
+            {
+                if(not a->get_shape().standard())
+                    a = standard_copy(qd, a);
+                const std::size_t kp = (k + 15) / 16 * 16;
+                auto lens            = as.lens();
+                std::vector<std::size_t> strides(nd, 1);
+                strides[nd - 2] = kp;
+                for(std::size_t j = nd - 2; j-- > 0;)
+                    strides[j] = strides[j + 1] * lens[j + 1];
+                auto buf = insert_allocation(m, qd, shape{in_type, lens, strides});
+                a        = m.insert_instruction(qd, op_pad_rows{}, a, buf);
+                consume(a);
+            }
         }
         // B operand: constants are re-laid out K-contiguous once, here
         std::vector<instruction_ref> args = {a, b};
         instruction_ref workspace = m.end();
-        if(b->can_eval())
+        const bool k_aligned = a->get_shape().lens().back() % 16 == 0;
+        if(b->can_eval() and k_aligned)
         {
             args[1]  = add_transposed_8bit_literal(m, b);
             op.b_nk  = true;
@@ -520,8 +537,10 @@ struct lowerer
         }
         else
         {
+            // re-laid out per evaluation into the workspace (rows padded to 16 bytes); a strided
+            // view (a transposed parameter) is packed first
             if(not b->get_shape().standard())
-                unsupported(qd, "a non-constant right operand must be a standard [K,N] tensor");
+                args[1] = standard_copy(qd, b);
             const auto& bl       = b->get_shape().lens();
             const std::size_t k  = bl[bl.size() - 2];
             const std::size_t kp = (k + 15) / 16 * 16;
@@ -1158,6 +1177,37 @@ struct lowerer
             qz         = o;
             break;
         }
+        // ... and so is a dequantizelinear of that quantised tensor with the same zero point (what
+        // simplify_qdq turns other reads of the un-quantised tensor into, src/simplify_qdq.cpp:401-432)
+        instruction_ref dqz = m.end();
+        if(qz != m.end() and qz->get_shape().type() == shape::int8_type)
+        {
+            for(auto o : qz->outputs())
+            {
+                if(o->name() != "dequantizelinear" or o->inputs()[0] != qz or o->get_shape().type() != xs.type() or
+                   not o->inputs()[1]->can_eval())
+                    continue;
+                auto ds = classify_constant(o->inputs()[1]);
+                if(ds.kind != bcast_kind::scalar)
+                    continue;
+                float zp = 0.0f;
+                if(o->inputs().size() == 3)
+                {
+                    if(not o->inputs()[2]->can_eval())
+                        continue;
+                    auto dz = classify_constant(o->inputs()[2]);
+                    if(dz.kind != bcast_kind::scalar)
+                        continue;
+                    zp = dz.values[0];
+                }
+                if(zp != op.q_zp)
+                    continue;
+                op.has_dq   = true;
+                op.dq_scale = ds.values[0];
+                dqz         = o;
+                break;
+            }
+        }
         const bool only_q = qz != m.end() and last->outputs().size() == 1;
         for(auto c : chain)
         {
@@ -1166,20 +1216,37 @@ struct lowerer
                 if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
                     consume(i);
         }
+        instruction_ref dqbuf = m.end();
+        auto first_result     = only_q ? qz : last;
+        if(dqz != m.end())
+        {
+            dqbuf = insert_allocation(m, first_result, dqz->get_shape().as_standard());
+            args.push_back(dqbuf);
+        }
+        instruction_ref rep;
         if(only_q)
         {
             op.write_y = false;
             args.push_back(insert_allocation(m, qz, qz->get_shape().as_standard()));
-            consume(m.replace_instruction(qz, op, args));
-            return true;
+            rep = m.replace_instruction(qz, op, args);
+            consume(rep);
         }
-        if(qz != m.end())
-            args.push_back(insert_allocation(m, last, qz->get_shape().as_standard()));
-        args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
-        auto rep = m.replace_instruction(last, op, args);
-        consume(rep);
-        if(qz != m.end())
-            consume(m.replace_instruction(qz, op_second_output{}, rep, args[args.size() - 2]));
+        else
+        {
+            instruction_ref qbuf = m.end();
+            if(qz != m.end())
+            {
+                qbuf = insert_allocation(m, last, qz->get_shape().as_standard());
+                args.push_back(qbuf);
+            }
+            args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+            rep = m.replace_instruction(last, op, args);
+            consume(rep);
+            if(qz != m.end())
+                consume(m.replace_instruction(qz, op_second_output{}, rep, qbuf));
+        }
+        if(dqz != m.end())
+            consume(m.replace_instruction(dqz, op_second_output{}, rep, dqbuf));
         return true;
     }
 

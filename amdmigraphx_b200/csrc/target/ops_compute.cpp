@@ -488,7 +488,7 @@ argument op_reduce::compute(context& ctx, const shape&, const std::vector<argume
 // ------------------------------------------------------------------ layernorm
 shape op_layernorm::compute_shape(const std::vector<shape>& inputs) const
 {
-    const std::size_t n = 1 + has_gamma + has_beta + (q_type != 0 ? 1 : 0) + (write_y ? 1 : 0);
+    const std::size_t n = 1 + has_gamma + has_beta + has_dq + (q_type != 0 ? 1 : 0) + (write_y ? 1 : 0);
     check_shapes{inputs, *this}.has(n);
     const auto& x = inputs[0];
     if(x.type() != shape::float_type and x.type() != shape::half_type)
@@ -508,6 +508,7 @@ argument op_layernorm::compute(context& ctx, const shape&, const std::vector<arg
     std::size_t i         = 1;
     const argument* gamma = has_gamma ? &args[i++] : nullptr;
     const argument* beta  = has_beta ? &args[i++] : nullptr;
+    const argument* dqbuf = has_dq ? &args[i++] : nullptr;
     const argument* qbuf  = q_type != 0 ? &args[i++] : nullptr;
     const argument* ybuf  = write_y ? &args[i++] : nullptr;
     const auto m          = as_matrix(args[0].get_shape(), "layernorm input");
@@ -525,9 +526,12 @@ argument op_layernorm::compute(context& ctx, const shape&, const std::vector<arg
         d.q_scale      = q_scale;
         d.q_zero_point = q_zp;
     }
-    check_mgx(mgx_cuda_layernorm(&d, args[0].data(), gamma != nullptr ? gamma->data() : nullptr,
-                                 beta != nullptr ? beta->data() : nullptr, ybuf != nullptr ? ybuf->data() : nullptr,
-                                 qbuf != nullptr ? qbuf->data() : nullptr, ctx.stream()),
+    check_mgx(mgx_cuda_layernorm_ex(&d, args[0].data(), gamma != nullptr ? gamma->data() : nullptr,
+                                    beta != nullptr ? beta->data() : nullptr, ybuf != nullptr ? ybuf->data() : nullptr,
+                                    qbuf != nullptr ? qbuf->data() : nullptr,
+                                    dqbuf != nullptr ? dqbuf->data() : nullptr,
+                                    dqbuf != nullptr ? as_matrix(dqbuf->get_shape(), "layernorm dequantised output").ld : 0,
+                                    dq_scale, ctx.stream()),
               "mgx_cuda_layernorm");
     return args.back();
 }

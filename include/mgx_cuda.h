@@ -187,6 +187,11 @@ typedef struct mgx_layernorm_desc
 MGX_API int mgx_cuda_layernorm_supported(int type, int64_t cols);
 MGX_API int mgx_cuda_layernorm(const mgx_layernorm_desc* d, const void* x, const void* gamma, const void* beta,
                                void* y, void* q, void* stream);
+/* The same with a third result: dq = dequantizelinear(q, dq_scale, zero point) in x's type
+ * ((q - zero point) * dq_scale, fp16: truncated), the dequantised copy simplify_qdq makes other
+ * readers of a quantised tensor use (src/simplify_qdq.cpp:401-432).  Needs q, int8 only. */
+MGX_API int mgx_cuda_layernorm_ex(const mgx_layernorm_desc* d, const void* x, const void* gamma, const void* beta,
+                                  void* y, void* q, void* dq, int64_t lddq, float dq_scale, void* stream);
 
 /* ---- multi-head attention on fp16 tensors, one launch ("next" row: encoder attention) ---- *
  * o[b*seq + i, h*64 .. h*64+63] = softmax_j(scale * <q_i, k_j>) . v_j per batch b and head h,

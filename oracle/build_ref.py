@@ -192,7 +192,7 @@ def main():
     refdir = os.path.join(src, "targets", "ref")
     reft = [os.path.join(refdir, f) for f in ("target.cpp", "lowering.cpp")]
 
-    base = ["-std=c++17", "-fPIC", "-w", "-pthread",
+    base = ["-std=c++17", "-fPIC", "-w", "-pthread", "-DNDEBUG",
             "-DMIGRAPHX_USE_EIGEN=0", "-DMIGRAPHX_HAS_EXECUTORS=0",
             '-DMIGRAPHX_CXX_COMPILER="g++"',
             f"-I{gen}/include", f"-I{src}/include", f"-I{bdir}/include",

@@ -45,7 +45,8 @@ def test_layernorm_only_quantised_output_and_no_affine(cuda_device):
     x = rng.normal(0, 1, size=(50, 768)).astype(np.float16)
     xd = torch.from_numpy(x).to(cuda_device)
     y, _ = capi.layernorm(xd, None, None, eps=1e-5)
-    y2, q = capi.layernorm(xd, None, None, eps=1e-5, q_scale=0.03125, q_zero_point=3.0, write_y=False)
+    y2, q, dq = capi.layernorm(xd, None, None, eps=1e-5, q_scale=0.03125, q_zero_point=3.0, write_y=False,
+                               dq_scale=0.03125)
     torch.cuda.synchronize()
     assert y2 is None
     np.testing.assert_allclose(y.cpu().numpy().astype(np.float32),
@@ -53,6 +54,9 @@ def test_layernorm_only_quantised_output_and_no_affine(cuda_device):
     q_ref = O.quantizelinear(y.cpu().numpy(), np.array([0.03125], dtype=np.float16),
                              np.array([3], dtype=np.int8), "int8")
     np.testing.assert_array_equal(q.cpu().numpy(), q_ref)
+    # the third result is dequantizelinear of the quantised tensor, bit for bit
+    dq_ref = O.dequantizelinear(q_ref, np.array([0.03125], dtype=np.float16), np.array([3], dtype=np.int8))
+    np.testing.assert_array_equal(dq.cpu().numpy().view(np.uint16), np.asarray(dq_ref, dtype=np.float16).view(np.uint16))
 
 
 @pytest.mark.parametrize("batch,seq,heads", [(1, 384, 12), (2, 200, 4), (3, 64, 2), (1, 77, 1), (8, 384, 12)])
