@@ -8,11 +8,18 @@
 // and merge need no copies; the result can additionally (or only) be written through a
 // per-tensor quantizelinear as int8, the input of the quantized output projection.
 //
-// Arithmetic: fp16 tensor-core products with fp32 accumulation; scores are rounded the way the
-// separate operators round them (dot -> half, * scale -> half, both truncating like
-// migraphx::half), the softmax runs in fp32 over key blocks with a running maximum and sum, the
-// probabilities enter the second product as fp16.  Against the reference's chain (every operator
-// rounded to half): within the fp16 tolerance of the tests (rtol 2e-2 / atol 1e-2).
+// Two kernels.  attention_f16_chain_kernel (sequences of up to 1024 keys) makes every rounding of
+// the operator chain it stands in for: the scores of a CTA's 64 query rows stay in shared memory as
+// half (dot -> half, * scale -> half, truncating like migraphx::half), the softmax is ref_softmax's
+// (src/targets/ref/lowering.cpp:253-320: exp(x - max) stored as half, summed in fp32, divided and
+// stored as half), and the second product multiplies those half probabilities with V.  What
+// differs from the reference is the order of the fp32 sums (its dot accumulates in double) and
+// the last bit of exp: a result lands in the neighbouring half for about one element in a
+// thousand.  That matters because a quantizelinear usually follows: a kernel that keeps more
+// precision than the chain (the second kernel) moves values across its rounding boundaries.
+// attention_f16_kernel (longer sequences) runs the softmax in fp32 over key blocks with a running
+// maximum and sum (flash-attention style); against the chain it stays within the fp16 tolerance
+// of the tests (rtol 2e-2 / atol 1e-2).
 //
 // One CTA = 4 warps = 64 query rows of one head; keys / values stream through shared memory in
 // 64-row blocks (cp.async double buffering, 16-byte chunks XOR-swizzled against bank conflicts);
@@ -287,6 +294,226 @@ __global__ void __launch_bounds__(128) attention_f16_kernel(const attention_para
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The operator chain's own roundings (see the head of the file).  Dynamic shared memory:
+// Q tile | two K / V tiles | scores [64][sp] half (sp = keys rounded up to 64, + 8 against bank
+// conflicts) | row maxima.
+constexpr int AT_CHAIN_MAX_SEQ = 1024;
+
+// v >= 0 truncated to half precision, subnormal halves included (multiples of 2^-24 below 2^-14:
+// v + 0.5 rounded toward zero keeps exactly those bits)
+__device__ __forceinline__ float trunc_half_nonneg(float v)
+{
+    const float big   = __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+    const float small = __fsub_rn(__fadd_rz(v, 0.5f), 0.5f);
+    return v < 6.103515625e-5f ? small : big;
+}
+
+__global__ void __launch_bounds__(128) attention_f16_chain_kernel(const attention_params p, const int sp)
+{
+    extern __shared__ __align__(128) uint8_t at_smem[];
+    __half* sq     = reinterpret_cast<__half*>(at_smem);
+    __half* skv[2] = {sq + AT_BM * AT_D, sq + AT_BM * AT_D + AT_BN * AT_D};
+    __half* sc     = sq + AT_BM * AT_D + 2 * AT_BN * AT_D; // [64][sp]
+    float* rowmax  = reinterpret_cast<float*>(sc + AT_BM * sp);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int q0   = blockIdx.x * AT_BM;
+    const int head = blockIdx.y;
+    const int64_t row_base = static_cast<int64_t>(blockIdx.z) * p.seq;
+    const __half* qg = p.q + (row_base + q0) * p.ldq + head * AT_D;
+    const __half* kg = p.k + row_base * p.ldk + head * AT_D;
+    const __half* vg = p.v + row_base * p.ldv + head * AT_D;
+    const int nblocks = (p.seq + AT_BN - 1) / AT_BN;
+
+    load_tile(sq, qg, p.ldq, p.seq - q0, tid);
+    load_tile(skv[0], kg, p.ldk, p.seq, tid);
+    cp_async_commit();
+
+    // ---- phase 1: scores = half(half(Q K^T) * scale) into shared memory, row maxima
+    uint32_t qa[4][4];
+    float mx[2] = {-FLT_MAX, -FLT_MAX};
+    for(int kb = 0; kb < nblocks; ++kb)
+    {
+        const int buf = kb & 1;
+        if(kb + 1 < nblocks)
+        {
+            const int k1 = (kb + 1) * AT_BN;
+            load_tile(skv[buf ^ 1], kg + static_cast<int64_t>(k1) * p.ldk, p.ldk, p.seq - k1, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        }
+        else
+            cp_async_wait<0>();
+        __syncthreads();
+        if(kb == 0)
+        {
+#pragma unroll
+            for(int ks = 0; ks < 4; ++ks)
+                ldmatrix_x4(qa[ks], tile_ptr(sq, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * ks + (lane >> 4)));
+        }
+        float s[8][4];
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+        for(int ks = 0; ks < 4; ++ks)
+        {
+#pragma unroll
+            for(int jp = 0; jp < 4; ++jp)
+            {
+                uint32_t kf[4];
+                ldmatrix_x4(kf, tile_ptr(skv[buf], jp * 16 + (lane & 7) + (lane >> 4) * 8, 2 * ks + ((lane >> 3) & 1)));
+                mma_16816(s[2 * jp], qa[ks], kf[0], kf[1]);
+                mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
+            }
+        }
+        const int kbase = kb * AT_BN;
+        const bool tail = kbase + AT_BN > p.seq;
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+            float x[4];
+#pragma unroll
+            for(int e = 0; e < 4; ++e)
+            {
+                x[e] = __uint_as_float(__float_as_uint(s[j][e]) & 0xFFFFE000u);
+                x[e] = __uint_as_float(__float_as_uint(x[e] * p.scale) & 0xFFFFE000u);
+                if(tail and kbase + j * 8 + 2 * t + (e & 1) >= p.seq)
+                    x[e] = -65504.0f; // a key that does not exist: its exponential is 0
+                else
+                    mx[e >> 1] = fmaxf(mx[e >> 1], x[e]);
+            }
+            const int col = kbase + j * 8 + 2 * t;
+            *reinterpret_cast<__half2*>(sc + (warp * 16 + g) * sp + col)     = __floats2half2_rn(x[0], x[1]);
+            *reinterpret_cast<__half2*>(sc + (warp * 16 + g + 8) * sp + col) = __floats2half2_rn(x[2], x[3]);
+        }
+        __syncthreads(); // the other tile is overwritten by the next iteration's load
+    }
+    // V's first tile travels while the softmax runs
+    load_tile(skv[0], vg, p.ldv, p.seq, tid);
+    cp_async_commit();
+#pragma unroll
+    for(int r = 0; r < 2; ++r)
+    {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+    }
+    if(t == 0)
+    {
+        rowmax[warp * 16 + g]     = mx[0];
+        rowmax[warp * 16 + g + 8] = mx[1];
+    }
+    __syncwarp();
+
+    // ---- phase 2: ref_softmax on this warp's 16 rows, in place: e = half(exp(x - max)),
+    // sum over the stored halves in fp32, p = half(e / sum)
+    const int nv = nblocks; // half2 pairs per lane and row: keys / 64
+#pragma unroll 1
+    for(int r = 0; r < 16; ++r)
+    {
+        __half* rowp  = sc + (warp * 16 + r) * sp;
+        const float m = rowmax[warp * 16 + r];
+        float e[2 * (AT_CHAIN_MAX_SEQ / 64)];
+        float sum = 0.0f;
+#pragma unroll
+        for(int i = 0; i < AT_CHAIN_MAX_SEQ / 64; ++i)
+        {
+            if(i < nv)
+            {
+                const float2 x = __half22float2(*reinterpret_cast<const __half2*>(rowp + i * 64 + lane * 2));
+                e[2 * i]     = trunc_half_nonneg(expf(x.x - m));
+                e[2 * i + 1] = trunc_half_nonneg(expf(x.y - m));
+                sum += e[2 * i] + e[2 * i + 1];
+            }
+        }
+#pragma unroll
+        for(int o = 16; o > 0; o >>= 1)
+            sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+        for(int i = 0; i < AT_CHAIN_MAX_SEQ / 64; ++i)
+        {
+            if(i < nv)
+            {
+                const float a = trunc_half_nonneg(__fdiv_rn(e[2 * i], sum));
+                const float b = trunc_half_nonneg(__fdiv_rn(e[2 * i + 1], sum));
+                *reinterpret_cast<__half2*>(rowp + i * 64 + lane * 2) = __floats2half2_rn(a, b);
+            }
+        }
+    }
+    __syncwarp();
+
+    // ---- phase 3: O = P V with the half probabilities as A fragments straight from shared memory
+    float o[8][4];
+#pragma unroll
+    for(int j = 0; j < 8; ++j)
+        o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    for(int kb = 0; kb < nblocks; ++kb)
+    {
+        const int buf = kb & 1;
+        if(kb + 1 < nblocks)
+        {
+            const int k1 = (kb + 1) * AT_BN;
+            load_tile(skv[buf ^ 1], vg + static_cast<int64_t>(k1) * p.ldv, p.ldv, p.seq - k1, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        }
+        else
+            cp_async_wait<0>();
+        __syncthreads();
+#pragma unroll
+        for(int ks = 0; ks < 4; ++ks)
+        {
+            uint32_t pa[4];
+            ldmatrix_x4(pa, sc + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * sp + kb * AT_BN + ks * 16 +
+                                (lane >> 4) * 8);
+#pragma unroll
+            for(int jp = 0; jp < 4; ++jp)
+            {
+                uint32_t vf[4];
+                ldmatrix_x4_trans(vf, tile_ptr(skv[buf], ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * jp + (lane >> 4)));
+                mma_16816(o[2 * jp], pa, vf[0], vf[1]);
+                mma_16816(o[2 * jp + 1], pa, vf[2], vf[3]);
+            }
+        }
+        __syncthreads();
+    }
+    const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
+#pragma unroll
+    for(int r = 0; r < 2; ++r)
+    {
+        const int row = q0 + warp * 16 + g + r * 8;
+        if(row >= p.seq)
+            continue;
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+            const float a = truncate_to_half_precision(o[j][2 * r]);
+            const float b = truncate_to_half_precision(o[j][2 * r + 1]);
+            const int col = head * AT_D + j * 8 + 2 * t;
+            if(p.o != nullptr)
+                *reinterpret_cast<uint32_t*>(p.o + (row_base + row) * p.ldo + col) = cvt_rz_f16x2(a, b);
+            if(p.oq != nullptr)
+            {
+                uint32_t qb[2];
+                const float vals[2] = {a, b};
+#pragma unroll
+                for(int e = 0; e < 2; ++e)
+                {
+                    float qv        = __fmul_rn(vals[e], p.q_rcp);
+                    const float rem = __fmaf_rn(-p.q_scale, qv, vals[e]);
+                    qv              = truncate_to_half_precision(__fmaf_rn(rem, p.q_rcp, qv));
+                    qv              = fmaxf(q_lo, fminf(q_hi, qv));
+                    qb[e] = static_cast<uint32_t>(__float_as_int(__fadd_rn(qv, 12582912.0f)) - 0x4B400000 +
+                                                  static_cast<int>(p.q_zp)) & 0xFFu;
+                }
+                *reinterpret_cast<uint16_t*>(p.oq + (row_base + row) * p.ldoq + col) =
+                    static_cast<uint16_t>(qb[0] | (qb[1] << 8));
+            }
+        }
+    }
+}
+
 } // namespace mgx
 
 extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
@@ -326,6 +553,17 @@ extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, co
     p.q_zp    = d->q_zero_point;
     const dim3 grid(static_cast<unsigned>((d->seq + AT_BM - 1) / AT_BM), static_cast<unsigned>(d->heads),
                     static_cast<unsigned>(d->batch));
-    attention_f16_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream_)>>>(p);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(d->seq <= AT_CHAIN_MAX_SEQ)
+    {
+        const int sp    = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
+        const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + AT_BM * 4;
+        const int rc    = ensure_smem_optin(reinterpret_cast<const void*>(attention_f16_chain_kernel), bytes);
+        if(rc != MGX_OK)
+            return rc;
+        attention_f16_chain_kernel<<<grid, 128, bytes, stream>>>(p, sp);
+    }
+    else
+        attention_f16_kernel<<<grid, 128, 0, stream>>>(p);
     return static_cast<int>(cudaGetLastError());
 }

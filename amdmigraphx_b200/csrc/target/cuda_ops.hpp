@@ -252,6 +252,19 @@ struct op_qgemm
     std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
 };
 
+// (x, a 64-byte double buffer) -> x.  memory_coloring places every buffer of the arena at a
+// multiple of ONE alignment, the largest any allocation asks for by its element type and count
+// (src/memory_coloring.cpp:158-172, 290-300); programs of int8 / fp16 tensors alone would get 4 or
+// 8 bytes.  The double[8] allocation this operator keeps alive asks for 32, which is what the
+// kernels' 16-byte vector and tensor-map accesses need.
+struct op_align_anchor
+{
+    std::string name() const { return "cuda::align_anchor"; }
+    shape compute_shape(const std::vector<shape>& inputs) const { return inputs.at(0); }
+    argument compute(const shape&, const std::vector<argument>& args) const { return args.at(0); }
+    std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {0}; }
+};
+
 // (producer result, buffer the producer also wrote) -> that buffer: gives the second result
 // of an operator with two outputs its own instruction, ordered after the producer.
 struct op_second_output

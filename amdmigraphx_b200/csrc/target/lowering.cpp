@@ -1623,6 +1623,20 @@ void lowering::apply(module_pass_manager& mpm) const
     module& m = mpm.get_module();
     lowerer l{m, {}};
     l.run();
+    // every arena offset a multiple of 32 bytes (see op_align_anchor)
+    {
+        auto ret = std::prev(m.end());
+        bool any = false;
+        for(auto ins : iterator_for(m))
+            any = any or ins->name() == "allocate";
+        if(any and ret->name() == "@return" and not ret->inputs().empty())
+        {
+            auto x      = ret->inputs().front();
+            auto anchor = insert_allocation(m, ret, shape{shape::double_type, {8}});
+            auto a      = m.insert_instruction(ret, op_align_anchor{}, x, anchor);
+            instruction::replace_argument(ret, x, a);
+        }
+    }
     if(not offload_copy)
         return;
     // offload_copy: parameters arrive as host buffers and results are returned on the host

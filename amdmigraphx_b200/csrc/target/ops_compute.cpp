@@ -373,9 +373,11 @@ argument op_second_output::compute(context&, const shape&, const std::vector<arg
 }
 
 // ------------------------------------------------------------------ element-wise
-static int pw_type(shape::type_t t)
+static int pw_type(shape::type_t t, bool byte_copy = false)
 {
-    // a bool is a byte holding 0 or 1
+    // a bool is a byte holding 0 or 1; a pure copy moves 8-bit elements of any type as bytes
+    if(byte_copy and shape{t}.type_size() == 1)
+        return MGX_U8;
     return t == shape::bool_type ? MGX_I8 : mgx_type(t);
 }
 
@@ -417,11 +419,14 @@ argument op_pointwise::compute(context& ctx, const shape&, const std::vector<arg
     d.ninsns  = static_cast<int32_t>(ops.size());
     for(std::size_t k = 0; k < lens.size(); ++k)
         d.lens[k] = static_cast<int64_t>(lens[k]);
+    // a packed copy of a strided view (one identity instruction, same type in and out)
+    const bool byte_copy = ops.size() == 1 and ops[0] == MGX_PW_IDENTITY and args.size() == 2 and
+                           args[0].get_shape().type() == os.type();
     const void* ptrs[MGX_PW_MAXIN] = {};
     for(std::size_t i = 0; i + 1 < args.size(); ++i)
     {
         const auto& s = args[i].get_shape();
-        d.in_type[i]  = pw_type(s.type());
+        d.in_type[i]  = pw_type(s.type(), byte_copy);
         ptrs[i]       = args[i].data();
         if(flat)
             d.in_strides[i][0] = 1;
@@ -432,7 +437,7 @@ argument op_pointwise::compute(context& ctx, const shape&, const std::vector<arg
     for(std::size_t n = 0; n < ops.size(); ++n)
     {
         d.insn[n].op   = ops[n];
-        d.insn[n].type = pw_type(static_cast<shape::type_t>(types[n]));
+        d.insn[n].type = pw_type(static_cast<shape::type_t>(types[n]), byte_copy);
         d.insn[n].imm  = imms[n];
         for(int j = 0; j < 3; ++j)
             d.insn[n].src[j] = srcs[3 * n + j];
@@ -724,6 +729,7 @@ MIGRAPHX_REGISTER_OP(op_layernorm)
 MIGRAPHX_REGISTER_OP(op_attention)
 MIGRAPHX_REGISTER_OP(op_pointwise)
 MIGRAPHX_REGISTER_OP(op_second_output)
+MIGRAPHX_REGISTER_OP(op_align_anchor)
 MIGRAPHX_REGISTER_OP(op_all_reduce)
 MIGRAPHX_REGISTER_OP(op_quantizelinear)
 MIGRAPHX_REGISTER_OP(op_dequantizelinear)
