@@ -123,6 +123,27 @@ struct op_graph_end
     }
 };
 
+// Evaluates its submodule (see insert_graph_ops): instruction by instruction at first, as one
+// recorded CUDA graph afterwards.  Inputs: the submodule's parameters in the order of `params`.
+// Result: the tuple of the submodule's results.
+struct op_graph_run
+{
+    std::vector<std::string> params;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.params, "params"));
+    }
+    std::string name() const { return "cuda::graph_run"; }
+    shape compute_shape(const std::vector<shape>& inputs, std::vector<module_ref> mods) const;
+    argument compute(context& ctx,
+                     const shape& out,
+                     const std::vector<argument>& args,
+                     const std::vector<module_ref>& mods,
+                     const std::function<std::vector<argument>(
+                         module_ref&, const std::unordered_map<std::string, argument>&)>& run) const;
+};
+
 // ---- stream scheduling (inserted by the generic schedule pass through schedule_model) ----
 struct op_set_stream
 {

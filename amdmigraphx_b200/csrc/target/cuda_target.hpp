@@ -19,6 +19,7 @@
 #include <migraphx/value.hpp>
 #include <migraphx/any_ptr.hpp>
 #include <cuda_runtime.h>
+#include <functional>
 #include <memory>
 #include <string>
 #include <unordered_map>
@@ -67,7 +68,8 @@ struct context_state
     };
     graph_mode gmode        = graph_mode::off;
     int warm_evals          = 0;
-    bool replaying          = false; // the graph was launched: launching operators do nothing
+    bool replaying          = false; // (kept false: replayed submodules are not evaluated at all)
+    std::vector<argument> graph_results; // what the recorded submodule returned
     cudaGraph_t graph       = nullptr;
     cudaGraphExec_t gexec   = nullptr;
     std::vector<const void*> graph_params; // parameter buffers the graph was captured with
@@ -98,6 +100,10 @@ struct MGX_CUDA_EXPORT context
     void graph_begin(const std::vector<const void*>& params);
     void graph_end();
     void enable_graph();
+    // runs body() - the evaluation of a submodule - or, once it has been recorded for these
+    // parameter buffers, launches the recorded graph instead and returns the recorded results
+    std::vector<argument> run_graph(const std::vector<const void*>& params,
+                                    const std::function<std::vector<argument>()>& body);
 
     // migraphx::context interface
     void finish() const;
@@ -178,11 +184,12 @@ struct fuse_cuda_pointwise
     void apply(module& m) const;
 };
 
-// Brackets the launching instructions of the main module with cuda::graph_begin /
-// cuda::graph_end: from the third eval() on, the whole instruction stream is one
-// cudaGraphLaunch as long as the caller passes the same parameter buffers (host time per
-// eval() is then independent of the number of instructions; src/program.cpp:472-565 is the
-// loop this short-cuts).  With offload_copy the bracket lies between the last host-to-device and
+// Moves the instructions of the main module into a submodule behind ONE cuda::graph_run
+// instruction: the first two eval() calls evaluate the submodule instruction by instruction, the
+// third records it with stream capture, and from then on an eval() is one cudaGraphLaunch - the
+// submodule's instructions (hundreds of literals, views and launches) are not visited at all -
+// as long as the caller passes the same parameter buffers (src/program.cpp:472-565 is the loop
+// this short-cuts).  With offload_copy the bracket lies between the last host-to-device and
 // the first device-to-host copy (the copies' device buffers are arena addresses, which never
 // change).  Not applied with several streams or collectives; MIGRAPHX_CUDA_GRAPH=0 turns it off.
 struct insert_graph_ops
@@ -190,7 +197,7 @@ struct insert_graph_ops
     context* ctx      = nullptr;
     bool offload_copy = false;
     std::string name() const { return "cuda::insert_graph_ops"; }
-    void apply(module& m) const;
+    void apply(module_pass_manager& mpm) const;
 };
 
 // Synchronises the stream before results copied to the host are returned.

@@ -14,6 +14,7 @@
 #include <migraphx/dead_code_elimination.hpp>
 #include <migraphx/instruction.hpp>
 #include <migraphx/iterator_for.hpp>
+#include <migraphx/builtin.hpp>
 #include <migraphx/literal.hpp>
 #include <migraphx/make_op.hpp>
 #include <migraphx/module.hpp>
@@ -23,6 +24,7 @@
 #include <migraphx/half.hpp>
 #include "../../../include/mgx_cuda.h"
 #include <algorithm>
+#include <functional>
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
@@ -1818,10 +1820,12 @@ void fuse_cuda_pointwise::apply(module& m) const
 }
 
 // ------------------------------------------------------------------ insert_graph_ops
-void insert_graph_ops::apply(module& m) const
+void insert_graph_ops::apply(module_pass_manager& mpm) const
 {
+    module& m       = mpm.get_module();
     const char* env = std::getenv("MIGRAPHX_CUDA_GRAPH");
-    if(ctx == nullptr or ctx->nstreams() > 1 or (env != nullptr and env[0] == '0'))
+    if(ctx == nullptr or &m != mpm.get_root_module() or ctx->nstreams() > 1 or
+       (env != nullptr and env[0] == '0'))
         return;
     auto launches = [](const std::string& n) {
         return n == "cuda::quantizelinear" or n == "cuda::dequantizelinear" or n == "cuda::qgemm" or
@@ -1830,61 +1834,117 @@ void insert_graph_ops::apply(module& m) const
                n == "cuda::gather" or n == "cuda::concat" or n == "cuda::pad_rows" or
                n == "cuda::layernorm" or n == "cuda::attention";
     };
-    instruction_ref first = m.end(), last_launch = m.end();
-    instruction_ref last_copy_to = m.end(), first_copy_from = m.end();
+    auto last = std::prev(m.end());
+    if(last->name() != "@return" or last->inputs().empty())
+        return;
+    // What stays in the main module: parameters, the return, host copies and the final
+    // synchronisation (none of them may run inside a stream capture), and whatever the
+    // host-to-device copies need (their arena buffers).  Everything else moves.
+    std::unordered_set<instruction*> stays;
+    bool seen_launch = false, seen_copy_from = false;
     std::size_t nlaunch = 0;
     for(auto ins : iterator_for(m))
     {
         const auto n = ins->name();
-        // explicit synchronisation and collectives stay outside graphs
+        // explicit stream scheduling and collectives are not captured
         if(n == "cuda::all_reduce" or n == "cuda::set_stream" or n == "cuda::record_event" or
-           n == "cuda::wait_event")
+           n == "cuda::wait_event" or not ins->module_inputs().empty())
             return;
-        if(n == "cuda::copy_to")
-        {
-            if(first != m.end())
-                return; // a host-to-device copy after the first launch: no single bracket
-            last_copy_to = ins;
-        }
-        if(n == "cuda::copy_from" and first_copy_from == m.end())
-            first_copy_from = ins;
+        if(n == "cuda::copy_to" and seen_launch)
+            return; // a host-to-device copy after the first launch: no single bracket
+        if(n == "cuda::copy_from" or n == "cuda::sync_stream")
+            seen_copy_from = true;
         if(launches(n))
         {
-            if(first_copy_from != m.end())
+            if(seen_copy_from)
                 return; // a launch after the first device-to-host copy
-            if(first == m.end())
-                first = ins;
-            last_launch = ins;
+            seen_launch = true;
             ++nlaunch;
         }
+        if(n == "@param" or n == "@return" or n == "cuda::copy_to" or n == "cuda::copy_from" or
+           n == "cuda::sync_stream")
+            stays.insert(&*ins);
     }
-    auto last = std::prev(m.end());
-    if(nlaunch == 0 or last->name() != "@return" or last->inputs().empty())
+    if(nlaunch == 0)
         return;
-    if(offload_copy)
-    {
-        // host copies in, the bracket, host copies out.  The device sides of the copies are
-        // arena addresses, the same for every eval(), so the graph depends on no parameter.
-        m.insert_instruction(first, op_graph_begin{});
-        m.insert_instruction(std::next(last_launch), op_graph_end{});
-        ctx->enable_graph();
-        return;
-    }
-    // graph_begin must see every parameter buffer: parameters (which views ahead of the first
-    // launch may already use) move to the front of the module
-    std::vector<instruction_ref> params;
+    std::function<void(instruction_ref)> keep_inputs = [&](instruction_ref ins) {
+        for(auto i : ins->inputs())
+            if(stays.insert(&*i).second)
+                keep_inputs(i);
+    };
     for(auto ins : iterator_for(m))
-        if(ins->name() == "@param")
-            params.push_back(ins);
-    for(auto p : params)
-        m.move_instruction(p, m.begin());
-    m.insert_instruction(first, op_graph_begin{}, params);
-    // graph_end passes the first result through, in front of the final synchronisation
-    auto res = last->inputs().front();
-    auto pos = res->name() == "cuda::sync_stream" ? res : last;
-    auto src = res->name() == "cuda::sync_stream" ? res->inputs().front() : res;
-    auto end = m.insert_instruction(pos, op_graph_end{}, src);
-    instruction::replace_argument(pos, src, end);
+        if(ins->name() == "cuda::copy_to")
+            keep_inputs(ins);
+
+    // the submodule: the moved instructions in their order; values they read from instructions
+    // that stay become its parameters, values the staying instructions read from it its results
+    module* sub = mpm.create_module(m.name() + ":graph");
+    std::unordered_map<instruction*, instruction_ref> inside; // moved instruction -> its clone
+    std::unordered_map<instruction*, instruction_ref> as_param;
+    std::vector<instruction_ref> ext_inputs;
+    std::vector<std::string> ext_names;
+    std::vector<instruction_ref> moved;
+    for(auto ins : iterator_for(m))
+    {
+        if(stays.count(&*ins) > 0)
+            continue;
+        std::vector<instruction_ref> args;
+        for(auto i : ins->inputs())
+        {
+            if(stays.count(&*i) == 0)
+            {
+                args.push_back(inside.at(&*i));
+                continue;
+            }
+            auto it = as_param.find(&*i);
+            if(it == as_param.end())
+            {
+                const std::string name = i->name() == "@param"
+                                             ? any_cast<builtin::param>(i->get_operator()).parameter
+                                             : "#in" + std::to_string(ext_inputs.size());
+                it = as_param.emplace(&*i, sub->add_parameter(name, i->get_shape())).first;
+                ext_inputs.push_back(i);
+                ext_names.push_back(name);
+            }
+            args.push_back(it->second);
+        }
+        inside[&*ins] = sub->add_instruction(ins->get_operator(), args);
+        moved.push_back(ins);
+    }
+    // results: moved instructions some staying instruction reads, in program order
+    std::vector<instruction_ref> results;
+    for(auto ins : moved)
+        if(std::any_of(ins->outputs().begin(), ins->outputs().end(),
+                       [&](auto o) { return stays.count(&*o) > 0; }))
+            results.push_back(ins);
+    if(results.empty())
+        return;
+    std::vector<instruction_ref> sub_results;
+    for(auto r : results)
+        sub_results.push_back(inside.at(&*r));
+    sub->add_return(sub_results);
+    // the call, in front of the first staying reader of a result
+    instruction_ref pos = m.end();
+    for(auto ins : iterator_for(m))
+        if(stays.count(&*ins) > 0 and std::any_of(ins->inputs().begin(), ins->inputs().end(), [&](auto i) {
+               return std::find(results.begin(), results.end(), i) != results.end();
+           }))
+        {
+            pos = ins;
+            break;
+        }
+    op_graph_run call;
+    call.params = ext_names;
+    auto gr     = m.insert_instruction(pos, call, ext_inputs, {sub});
+    for(std::size_t k = 0; k < results.size(); ++k)
+    {
+        auto elem = m.insert_instruction(pos, make_op("get_tuple_elem", {{"index", k}}), gr);
+        for(auto user : std::vector<instruction_ref>(results[k]->outputs()))
+            if(stays.count(&*user) > 0)
+                instruction::replace_argument(user, results[k], elem);
+    }
+    for(auto it = moved.rbegin(); it != moved.rend(); ++it)
+        m.remove_instruction(*it);
     ctx->enable_graph();
 }
 

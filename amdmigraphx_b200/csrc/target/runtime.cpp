@@ -10,6 +10,7 @@
 #include <migraphx/env.hpp>
 #include "../../../include/mgx_cuda.h"
 #include <cstring>
+#include <migraphx/module.hpp>
 
 namespace migraphx {
 inline namespace MIGRAPHX_INLINE_NS {
@@ -273,6 +274,87 @@ void context::graph_end()
     st.gmode = mode::ready;
 }
 
+std::vector<argument> context::run_graph(const std::vector<const void*>& params,
+                                         const std::function<std::vector<argument>()>& body)
+{
+    using mode = context_state::graph_mode;
+    auto& st   = *state;
+    if(st.gmode == mode::ready)
+    {
+        if(params == st.graph_params)
+        {
+            check_cuda(cudaGraphLaunch(st.gexec, stream()), "cudaGraphLaunch");
+            return st.graph_results;
+        }
+        // other buffers: evaluate instruction by instruction and record again
+        (void)cudaGraphExecDestroy(st.gexec);
+        (void)cudaGraphDestroy(st.graph);
+        st.gexec = nullptr;
+        st.graph = nullptr;
+        st.graph_results.clear();
+        st.gmode      = mode::warm;
+        st.warm_evals = 1;
+        return body();
+    }
+    // the first two evaluations run eagerly: one-time set-up (kernel attributes, entry point
+    // look-ups) must not happen inside a capture
+    if(st.gmode == mode::warm and ++st.warm_evals > 2)
+    {
+        check_cuda(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+        st.gmode = mode::off; // whatever fails below, no second attempt
+        std::vector<argument> results;
+        try
+        {
+            results = body();
+        }
+        catch(...)
+        {
+            cudaGraph_t broken = nullptr;
+            (void)cudaStreamEndCapture(stream(), &broken);
+            if(broken != nullptr)
+                (void)cudaGraphDestroy(broken);
+            throw;
+        }
+        check_cuda(cudaStreamEndCapture(stream(), &st.graph), "cudaStreamEndCapture");
+        check_cuda(cudaGraphInstantiate(&st.gexec, st.graph, 0), "cudaGraphInstantiate");
+        // nothing of this evaluation has run yet: the recorded work is launched as the new graph
+        check_cuda(cudaGraphLaunch(st.gexec, stream()), "cudaGraphLaunch");
+        st.graph_params  = params;
+        st.graph_results = results;
+        st.gmode         = mode::ready;
+        return results;
+    }
+    return body();
+}
+
+shape op_graph_run::compute_shape(const std::vector<shape>& inputs, std::vector<module_ref> mods) const
+{
+    if(mods.size() != 1 or inputs.size() != params.size())
+        MIGRAPHX_THROW("cuda::graph_run: expects one submodule and one input per parameter name");
+    return shape(mods.front()->get_output_shapes());
+}
+
+argument op_graph_run::compute(context& ctx,
+                               const shape&,
+                               const std::vector<argument>& args,
+                               const std::vector<module_ref>& mods,
+                               const std::function<std::vector<argument>(
+                                   module_ref&, const std::unordered_map<std::string, argument>&)>& run) const
+{
+    std::vector<const void*> ptrs;
+    ptrs.reserve(args.size());
+    for(const auto& a : args)
+        ptrs.push_back(a.empty() ? nullptr : a.data());
+    module_ref mod = mods.front();
+    auto results   = ctx.run_graph(ptrs, [&] {
+        std::unordered_map<std::string, argument> pm;
+        for(std::size_t i = 0; i < args.size(); ++i)
+            pm[params[i]] = args[i];
+        return run(mod, pm);
+    });
+    return argument{results};
+}
+
 argument op_graph_begin::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     std::vector<const void*> params;
@@ -443,6 +525,7 @@ MIGRAPHX_REGISTER_OP(op_copy_to)
 MIGRAPHX_REGISTER_OP(op_copy_from)
 MIGRAPHX_REGISTER_OP(op_copy)
 MIGRAPHX_REGISTER_OP(op_sync_stream)
+MIGRAPHX_REGISTER_OP(op_graph_run)
 MIGRAPHX_REGISTER_OP(op_graph_begin)
 MIGRAPHX_REGISTER_OP(op_graph_end)
 MIGRAPHX_REGISTER_OP(op_set_stream)

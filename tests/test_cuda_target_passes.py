@@ -105,8 +105,9 @@ def test_attention_lowers_to_fp16_gemms_softmax_and_packed_copies():
     # reshape of the packed parameters is a view; the head transposes are copied once
     assert "reshape_lazy" in out and " reshape[" not in out and "contiguous" not in out
     assert out.count("cuda::pointwise[ops={32}") >= 3
-    # the parameters precede the views that read them, and the graph bracket sees them all
-    assert "cuda::graph_begin(main:#output_0,v,k,q)" in out
+    # everything runs inside the submodule of one cuda::graph_run, which takes all parameters
+    call = [l for l in out.splitlines() if "= cuda::graph_run[" in l]
+    assert len(call) == 1 and all(p in call[0] for p in ("main:#output_0", "q", "k", "v"))
 
 
 def test_constant_fp16_weight_is_relaid_out_once():
@@ -124,7 +125,7 @@ def test_bert_layer_compiles_into_one_graph():
     # the Q, K and V projections as one GEMM over the concatenated weights, then O, FFN1, FFN2
     assert out.count("cuda::qgemm") == 4 and "half_type, {128, 768}, {768, 1}" in out
     assert out.count("slice[axes={1}") == 3
-    assert out.count("cuda::graph_begin") == 1 and out.count("cuda::graph_end") == 1
+    assert out.count("= cuda::graph_run[") == 1 and 'module: "main:graph"' in out
     # FFN1: GELU and the quantizelinear feeding FFN2 run in its epilogue
     assert any("act=2" in l and "q_type=5" in l and "write_d=0" in l for l in out.splitlines())
     # the attention block and the two LayerNorms are one launch each
@@ -185,10 +186,12 @@ def test_transposed_batched_left_operand_is_packed_first():
 
 def test_offload_copy_program_is_graph_bracketed():
     out = _passes("int8_gelu", "offload")
-    order = [n for l in out.splitlines() for n in ("cuda::copy_to", "cuda::graph_begin", "cuda::qgemm",
-                                                   "cuda::graph_end", "cuda::copy_from") if "= " + n in l]
-    assert order.index("cuda::copy_to") < order.index("cuda::graph_begin") < order.index("cuda::qgemm") \
-        < order.index("cuda::graph_end") < order.index("cuda::copy_from")
+    main, sub = out.split('module: "main:graph"')
+    order = [n for l in main.splitlines() for n in ("cuda::copy_to", "cuda::graph_run", "cuda::copy_from")
+             if "= " + n in l]
+    # host copies stay in the main module around the one call; the launches live in the submodule
+    assert order == ["cuda::copy_to", "cuda::graph_run", "cuda::copy_from"]
+    assert "cuda::qgemm" in sub and "cuda::qgemm" not in main and "cuda::copy" not in sub.replace("cuda::copy_", "")
 
 
 def test_config2_layer_lowers_at_real_dimensions():
