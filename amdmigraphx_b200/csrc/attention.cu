@@ -309,7 +309,7 @@ __device__ __forceinline__ float trunc_half_nonneg(float v)
     return v < 6.103515625e-5f ? small : big;
 }
 
-__global__ void __launch_bounds__(128) attention_f16_chain_kernel(const attention_params p, const int sp)
+__global__ void __launch_bounds__(128, 3) attention_f16_chain_kernel(const attention_params p, const int sp)
 {
     extern __shared__ __align__(128) uint8_t at_smem[];
     __half* sq     = reinterpret_cast<__half*>(at_smem);
@@ -407,8 +407,11 @@ __global__ void __launch_bounds__(128) attention_f16_chain_kernel(const attentio
     __syncwarp();
 
     // ---- phase 2: ref_softmax on this warp's 16 rows, in place: e = half(exp(x - max)),
-    // sum over the stored halves in fp32, p = half(e / sum)
+    // sum over the stored halves in fp32, p = half(e / sum).  exp through ex2.approx (relative error
+    // ~1e-6 against the 5e-4 spacing of the halves it is truncated to), the quotient from one
+    // reciprocal per row and a remainder correction (correctly rounded before the truncation).
     const int nv = nblocks; // half2 pairs per lane and row: keys / 64
+    constexpr float log2e = 1.4426950408889634f;
 #pragma unroll 1
     for(int r = 0; r < 16; ++r)
     {
@@ -422,22 +425,25 @@ __global__ void __launch_bounds__(128) attention_f16_chain_kernel(const attentio
             if(i < nv)
             {
                 const float2 x = __half22float2(*reinterpret_cast<const __half2*>(rowp + i * 64 + lane * 2));
-                e[2 * i]     = trunc_half_nonneg(expf(x.x - m));
-                e[2 * i + 1] = trunc_half_nonneg(expf(x.y - m));
+                e[2 * i]     = trunc_half_nonneg(fast_exp2((x.x - m) * log2e));
+                e[2 * i + 1] = trunc_half_nonneg(fast_exp2((x.y - m) * log2e));
                 sum += e[2 * i] + e[2 * i + 1];
             }
         }
 #pragma unroll
         for(int o = 16; o > 0; o >>= 1)
             sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const float rcp = __frcp_rn(sum);
 #pragma unroll
         for(int i = 0; i < AT_CHAIN_MAX_SEQ / 64; ++i)
         {
             if(i < nv)
             {
-                const float a = trunc_half_nonneg(__fdiv_rn(e[2 * i], sum));
-                const float b = trunc_half_nonneg(__fdiv_rn(e[2 * i + 1], sum));
-                *reinterpret_cast<__half2*>(rowp + i * 64 + lane * 2) = __floats2half2_rn(a, b);
+                float a = e[2 * i] * rcp, b = e[2 * i + 1] * rcp;
+                a       = __fmaf_rn(__fmaf_rn(-a, sum, e[2 * i]), rcp, a);
+                b       = __fmaf_rn(__fmaf_rn(-b, sum, e[2 * i + 1]), rcp, b);
+                *reinterpret_cast<__half2*>(rowp + i * 64 + lane * 2) =
+                    __floats2half2_rn(trunc_half_nonneg(a), trunc_half_nonneg(b));
             }
         }
     }
@@ -554,11 +560,13 @@ extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, co
     const dim3 grid(static_cast<unsigned>((d->seq + AT_BM - 1) / AT_BM), static_cast<unsigned>(d->heads),
                     static_cast<unsigned>(d->batch));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if(d->seq <= AT_CHAIN_MAX_SEQ)
+    if(d->seq <= AT_CHAIN_MAX_SEQ and (d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0)
     {
         const int sp    = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
         const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + AT_BM * 4;
-        const int rc    = ensure_smem_optin(reinterpret_cast<const void*>(attention_f16_chain_kernel), bytes);
+        // opted in once, to the size the longest supported sequence needs
+        constexpr int max_bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * (AT_CHAIN_MAX_SEQ + 8)) * 2 + AT_BM * 4;
+        const int rc = ensure_smem_optin(reinterpret_cast<const void*>(attention_f16_chain_kernel), max_bytes);
         if(rc != MGX_OK)
             return rc;
         attention_f16_chain_kernel<<<grid, 128, bytes, stream>>>(p, sp);

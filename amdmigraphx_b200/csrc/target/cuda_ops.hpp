@@ -375,12 +375,13 @@ struct op_attention
     float q_scale = 1.0f;
     float q_zp    = 0.0f;
     bool write_o  = true;
+    bool fp32_softmax = false; // MGX_ATTENTION_FP32_SOFTMAX (MIGRAPHX_CUDA_ATTENTION=fp32 at compile time)
     template <class Self, class F>
     static auto reflect(Self& self, F f)
     {
         return pack(f(self.batch, "batch"), f(self.seq, "seq"), f(self.heads, "heads"), f(self.head_dim, "head_dim"),
                     f(self.scale, "scale"), f(self.q_type, "q_type"), f(self.q_scale, "q_scale"),
-                    f(self.q_zp, "q_zp"), f(self.write_o, "write_o"));
+                    f(self.q_zp, "q_zp"), f(self.write_o, "write_o"), f(self.fp32_softmax, "fp32_softmax"));
     }
     std::string name() const { return "cuda::attention"; }
     shape compute_shape(const std::vector<shape>& inputs) const;

@@ -996,6 +996,9 @@ struct lowerer
         op_attention op;
         op.batch = b, op.seq = sq, op.heads = h, op.head_dim = d;
         op.scale = scale;
+        // MIGRAPHX_CUDA_ATTENTION=fp32: the faster kernel that does not make the chain's half roundings
+        const char* att = std::getenv("MIGRAPHX_CUDA_ATTENTION");
+        op.fp32_softmax = att != nullptr and std::string(att) == "fp32";
         std::vector<instruction_ref> args = {qx, kx, vx};
         instruction_ref last = cr;
         instruction_ref qz   = m.end();
@@ -1637,6 +1640,12 @@ void lowering::apply(module_pass_manager& mpm) const
             auto anchor = insert_allocation(m, ret, shape{shape::double_type, {8}});
             auto a      = m.insert_instruction(ret, op_align_anchor{}, x, anchor);
             instruction::replace_argument(ret, x, a);
+        }
+        else if(any and not is_builtin(ret->name()))
+        {
+            // no @return: the last instruction is the program's result
+            auto anchor = insert_allocation(m, m.end(), shape{shape::double_type, {8}});
+            m.add_instruction(op_align_anchor{}, ret, anchor);
         }
     }
     if(not offload_copy)

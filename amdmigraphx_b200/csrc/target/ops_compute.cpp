@@ -585,6 +585,7 @@ argument op_attention::compute(context& ctx, const shape&, const std::vector<arg
     d.scale    = scale;
     d.q_scale  = q_scale;
     d.q_zero_point = q_zp;
+    d.flags        = fp32_softmax ? MGX_ATTENTION_FP32_SOFTMAX : 0;
     check_mgx(mgx_cuda_attention(&d, args[0].data(), args[1].data(), args[2].data(),
                                  obuf != nullptr ? obuf->data() : nullptr, qbuf != nullptr ? qbuf->data() : nullptr,
                                  ctx.stream()),

@@ -200,7 +200,10 @@ MGX_API int mgx_cuda_layernorm_ex(const mgx_layernorm_desc* d, const void* x, co
  * (int8: the per-tensor quantizelinear of the fp16 result) receive the merged-heads result.
  * Stands in for reshape -> transpose -> dot -> mul -> softmax -> dot -> transpose -> reshape of an
  * encoder layer (the reference fuses the same chain for its GPU target,
- * src/targets/gpu/fuse_mlir.cpp:1161-1234).  head_dim must be 64. */
+ * src/targets/gpu/fuse_mlir.cpp:1161-1234).  head_dim must be 64.  Up to 1024 keys the kernel
+ * keeps the chain's own roundings (scores and probabilities stored as half, ref_softmax's order of
+ * operations): results are the reference's halves except for about one element in a thousand
+ * (neighbouring halves, from the order of the fp32 sums and the last bit of exp). */
 typedef struct mgx_attention_desc
 {
     int64_t batch, seq, heads, head_dim;
@@ -208,8 +211,14 @@ typedef struct mgx_attention_desc
     float scale;
     float q_scale;      /* quantizelinear scale / zero point of oq; ignored when oq == NULL */
     float q_zero_point;
-    int32_t reserved;
+    int32_t flags;      /* MGX_ATTENTION_* bits, 0 for none */
 } mgx_attention_desc;
+
+/* Run the softmax in fp32 over key blocks (running maximum and sum) instead of making the
+ * operator chain's half roundings: about a third of the time for 384 keys, results within the
+ * fp16 tolerance (rtol 2e-2 / atol 1e-2) of the chain instead of (nearly) its bits.  Sequences
+ * longer than 1024 keys always run this way. */
+#define MGX_ATTENTION_FP32_SOFTMAX 1
 
 MGX_API int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
                                void* oq, void* stream);
