@@ -21,7 +21,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "lib")
 OBJ = os.path.join(PKG, "build")
 
-KERNEL_SOURCES = ["runtime.cu", "quantize.cu", "qgemm.cu", "qgemv.cu", "pointwise.cu", "reduce.cu", "layernorm.cu", "attention.cu", "gather.cu", "w4a16.cu", "w4a16_tc.cu", "w4a16_prefill.cu", "comm.cu"]
+KERNEL_SOURCES = ["runtime.cu", "quantize.cu", "qgemm.cu", "qgemv.cu", "pointwise.cu", "reduce.cu", "layernorm.cu", "attention.cu", "kvcache.cu", "gqa_decode.cu", "gather.cu", "w4a16.cu", "w4a16_tc.cu", "w4a16_prefill.cu", "comm.cu"]
 KERNEL_LIB = os.path.join(LIB, "libmgx_cuda_kernels.so")
 
 NVCC_FLAGS = [

@@ -50,7 +50,8 @@ def build_target(verbose=False, force=False):
     cuda_inc = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/include"
     cuda_lib = os.environ.get("CUDA_HOME", "/usr/local/cuda") + "/lib64"
     flags = ["-std=c++17", "-O2", "-DNDEBUG", "-fPIC", "-w", "-pthread", "-fvisibility=hidden",
-             "-DMIGRAPHX_USE_EIGEN=0", f"-I{gen}", f"-I{inc}", f"-I{cuda_inc}"]
+             "-DMIGRAPHX_USE_EIGEN=0", f"-I{gen}", f"-I{inc}",
+             f"-I{os.path.join(mgx_src, 'src', 'op', 'builder', 'include')}", f"-I{cuda_inc}"]
     headers = [os.path.join(SRC, f) for f in os.listdir(SRC) if f.endswith(".hpp")]
     headers.append(os.path.join(ROOT, "include", "mgx_cuda.h"))
 

@@ -12,7 +12,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 KERNEL_LIB_PATH = os.path.join(_PKG, "lib", "libmgx_cuda_kernels.so")
 
 # mgx_dtype
-F32, F16, I8, U8, I32, FP8_E4M3FN = 0, 1, 2, 3, 4, 5
+F32, F16, I8, U8, I32, FP8_E4M3FN, I64 = 0, 1, 2, 3, 4, 5, 6
 # mgx_scale_mode
 SCALE_NONE, SCALE_PER_TENSOR, SCALE_PER_COL, SCALE_PER_ROW = 0, 1, 2, 3
 # mgx_act
@@ -25,7 +25,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_ex", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
+    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_ex", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_concat_past_present", "mgx_cuda_gqa_rotary_embedding", "mgx_cuda_gqa_decode_attention", "mgx_cuda_gqa_decode_supported", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -333,6 +333,67 @@ def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0
     check(lib.mgx_cuda_layernorm(ctypes.byref(d), _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), _ptr(q), _stream()),
           "mgx_cuda_layernorm")
     return y, q
+
+
+class GqaDecodeDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("batch", "heads", "kv_heads", "head", "cache_seq", "q_batch_stride",
+                                              "q_head_stride")] + \
+               [("scale", ctypes.c_float), ("seqlens_type", ctypes.c_int32)]
+
+
+def concat_past_present(present, seqlens, past):
+    """Appends present [batch, kv_heads, seq, head] (rows contiguous) to the cache past
+    [batch, kv_heads, cache_seq, head] in place: at row seqlens[b] when seq == 1, at row 0 otherwise."""
+    import torch
+    lib = load()
+    batch, kv_heads, seq, head = present.shape
+    es = present.element_size()
+    strides = (ctypes.c_int64 * 3)(present.stride(0) * es, present.stride(1) * es, present.stride(2) * es)
+    lib.mgx_cuda_concat_past_present.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)] + \
+        [ctypes.c_int64] * 4 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+    check(lib.mgx_cuda_concat_past_present(_ptr(present), strides, batch, kv_heads, seq, head * es, _ptr(seqlens),
+                                           I64 if seqlens.dtype == torch.int64 else I32, _ptr(past), past.shape[2],
+                                           _stream()), "mgx_cuda_concat_past_present")
+    return past
+
+
+def gqa_rotary_embedding(qkv, seqlens, cos_cache, sin_cache, heads, kv_heads, interleaved=False):
+    """Rotary embedding of the Q and K heads of packed [batch, heads + 2 kv_heads, seq, head]."""
+    import torch
+    lib = load()
+    batch, _, seq, head = qkv.shape
+    out = torch.empty_like(qkv)
+    lib.mgx_cuda_gqa_rotary_embedding.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_int64] * 5 + \
+        [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+         ctypes.c_void_p, ctypes.c_void_p]
+    check(lib.mgx_cuda_gqa_rotary_embedding(_ptr(qkv), _dtype_code(qkv), batch, heads, kv_heads, seq, head,
+                                            _ptr(cos_cache), _ptr(sin_cache), cos_cache.shape[0],
+                                            cos_cache.shape[1] * 2, _ptr(seqlens),
+                                            I64 if seqlens.dtype == torch.int64 else I32, 1 if interleaved else 0,
+                                            _ptr(out), _stream()), "mgx_cuda_gqa_rotary_embedding")
+    return out
+
+
+def gqa_decode_supported(batch, heads, kv_heads, head, cache_seq):
+    lib = load()
+    lib.mgx_cuda_gqa_decode_supported.argtypes = [ctypes.c_int64] * 5
+    return bool(lib.mgx_cuda_gqa_decode_supported(batch, heads, kv_heads, head, cache_seq))
+
+
+def gqa_decode_attention(q, k_cache, v_cache, seqlens, scale):
+    """softmax(scale * q K^T) V over cache positions 0 .. seqlens[b] for q [batch, heads, head] (rows
+    contiguous) against caches [batch, kv_heads, cache_seq, head]; returns [batch, heads * head]."""
+    import torch
+    lib = load()
+    batch, heads, head = q.shape
+    out = torch.empty((batch, heads * head), dtype=torch.float16, device=q.device)
+    d = GqaDecodeDesc(batch=batch, heads=heads, kv_heads=k_cache.shape[1], head=head, cache_seq=k_cache.shape[2],
+                      q_batch_stride=q.stride(0), q_head_stride=q.stride(1), scale=float(scale),
+                      seqlens_type=I64 if seqlens.dtype == torch.int64 else I32)
+    lib.mgx_cuda_gqa_decode_attention.argtypes = [ctypes.POINTER(GqaDecodeDesc)] + [ctypes.c_void_p] * 6
+    check(lib.mgx_cuda_gqa_decode_attention(ctypes.byref(d), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(seqlens),
+                                            _ptr(out), _stream()), "mgx_cuda_gqa_decode_attention")
+    return out
 
 
 class AttentionDesc(ctypes.Structure):

@@ -8,6 +8,7 @@
 #include "ptx.cuh"
 #include "qgemm_math.cuh"
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 namespace mgx {
 
@@ -25,6 +26,17 @@ struct pw_args
     uint32_t keep;
 };
 
+// fp8 e4m3fn as the reference's float8 class converts (src/include/migraphx/float8_impl.hpp:
+// round to nearest even, clipped to the largest finite value; NaN stays NaN)
+__device__ __forceinline__ float fp8_e4m3fn_value(uint8_t b)
+{
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+}
+__device__ __forceinline__ uint8_t fp8_e4m3fn_bits(float v)
+{
+    return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
 __device__ __forceinline__ float pw_load(const void* p, int type, int64_t i)
 {
     switch(type)
@@ -33,6 +45,7 @@ __device__ __forceinline__ float pw_load(const void* p, int type, int64_t i)
     case MGX_F16: return __half2float(static_cast<const __half*>(p)[i]);
     case MGX_I8: return static_cast<float>(static_cast<const int8_t*>(p)[i]);
     case MGX_U8: return static_cast<float>(static_cast<const uint8_t*>(p)[i]);
+    case MGX_FP8_E4M3FN: return fp8_e4m3fn_value(static_cast<const uint8_t*>(p)[i]);
     default: return static_cast<float>(static_cast<const int32_t*>(p)[i]);
     }
 }
@@ -46,6 +59,7 @@ __device__ __forceinline__ float pw_as_type(float v, int type)
     case MGX_F16: return truncate_to_half_precision(v);
     case MGX_I8: return static_cast<float>(static_cast<int8_t>(static_cast<int>(v)));
     case MGX_U8: return static_cast<float>(static_cast<uint8_t>(static_cast<int>(v)));
+    case MGX_FP8_E4M3FN: return fp8_e4m3fn_value(fp8_e4m3fn_bits(v));
     default: return static_cast<float>(static_cast<int32_t>(v));
     }
 }
@@ -58,6 +72,7 @@ __device__ __forceinline__ void pw_store(void* p, int type, int64_t i, float v)
     case MGX_F16: static_cast<__half*>(p)[i] = __float2half_rz(v); break;
     case MGX_I8: static_cast<int8_t*>(p)[i] = static_cast<int8_t>(static_cast<int>(v)); break;
     case MGX_U8: static_cast<uint8_t*>(p)[i] = static_cast<uint8_t>(static_cast<int>(v)); break;
+    case MGX_FP8_E4M3FN: static_cast<uint8_t*>(p)[i] = fp8_e4m3fn_bits(v); break;
     default: static_cast<int32_t*>(p)[i] = static_cast<int32_t>(v); break;
     }
 }
@@ -391,14 +406,14 @@ extern "C" int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* input
     }
     for(int i = 0; i < d->ninputs; ++i)
     {
-        if(inputs[i] == nullptr or d->in_type[i] < MGX_F32 or d->in_type[i] > MGX_I32)
+        if(inputs[i] == nullptr or d->in_type[i] < MGX_F32 or d->in_type[i] > MGX_FP8_E4M3FN)
             return MGX_E_INVALID_ARG;
         a.in[i] = inputs[i];
     }
     for(int n = 0; n < d->ninsns; ++n)
     {
         const auto& ins = d->insn[n];
-        if(ins.op < 0 or ins.op >= MGX_PW_OP_COUNT or ins.type < MGX_F32 or ins.type > MGX_I32)
+        if(ins.op < 0 or ins.op >= MGX_PW_OP_COUNT or ins.type < MGX_F32 or ins.type > MGX_FP8_E4M3FN)
             return MGX_E_UNSUPPORTED;
         for(int s : ins.src)
             if(s < 0 or s >= d->ninputs + n)

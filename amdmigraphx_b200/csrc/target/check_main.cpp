@@ -112,6 +112,16 @@ std::map<std::string, std::function<test_case()>> cases()
     big["pass_quantize_fp8"]   = [] { return quantized_mlp(96, 256, 320, 128, true, "ref", 52); };
     big["pass_int4_weights_decode"]  = [] { return int4_weights_pass_linear(4, 512, 384, 54); };
     big["pass_int4_weights_prefill"] = [] { return int4_weights_pass_linear(160, 512, 384, 55); };
+    // decoder attention with an fp16 KV cache, grouped-query heads and rotary embedding
+    big["gqa_decode_small"]  = [] { return gqa_attention(2, 4, 2, 32, 1, 48, false, 61); };
+    big["gqa_prompt_small"]  = [] { return gqa_attention(1, 4, 2, 32, 16, 48, false, 62); };
+    big["gqa_decode_rotary_op"] = [] { return gqa_attention(2, 4, 2, 32, 1, 48, true, 63); };
+    big["gqa_decode_d64_f4"]    = [] { return gqa_attention(3, 8, 2, 64, 1, 200, false, 67); };
+    big["gqa_decode_d128_f2"]   = [] { return gqa_attention(2, 4, 2, 128, 1, 333, false, 68); };
+    big["gqa_decode_d64_f8"]    = [] { return gqa_attention(2, 8, 1, 64, 1, 1100, false, 69); };
+    big["c4_attention_decode"]  = [] { return gqa_attention(1, 32, 32, 128, 1, 2048, false, 64); };
+    big["c4_attention_decode_b16"] = [] { return gqa_attention(16, 32, 32, 128, 1, 2048, false, 65); };
+    big["c5_attention_decode_tp8"] = [] { return gqa_attention(16, 8, 1, 128, 1, 4096, false, 66); };
     big["c2_layer"]   = [] { return c2_encoder(1, 1); };
     big["c2_layers2"] = [] { return c2_encoder(1, 2); };
     std::map<std::string, std::function<test_case()>> small = {

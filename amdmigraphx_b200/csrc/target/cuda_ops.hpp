@@ -441,6 +441,63 @@ struct op_concat
     std::vector<std::size_t> output_alias(const std::vector<shape>& args) const { return {args.size() - 1}; }
 };
 
+// op::concat_past_present on the device (src/include/migraphx/op/concat_past_present.hpp): inputs
+// present [B, kv_heads, L, D] (any strides with contiguous rows), seqlens_k [B] (int32 / int64),
+// the cache [B, kv_heads, T, D] (packed), which is updated in place and returned.
+struct op_concat_past_present
+{
+    std::size_t kv_num_heads = 0;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.kv_num_heads, "kv_num_heads"));
+    }
+    std::string name() const { return "cuda::concat_past_present"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>&) const { return {2}; }
+};
+
+// op::gqa_rotary_embedding on the device (src/include/migraphx/op/gqa_rotary_embedding.hpp): inputs
+// packed QKV [B, heads + 2 kv_heads, S, D] (packed), seqlens_k [B], cos cache, sin cache, out.
+struct op_gqa_rotary_embedding
+{
+    std::size_t num_heads    = 0;
+    std::size_t kv_num_heads = 0;
+    bool interleaved         = false;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.num_heads, "num_heads"), f(self.kv_num_heads, "kv_num_heads"),
+                    f(self.interleaved, "interleaved"));
+    }
+    std::string name() const { return "cuda::gqa_rotary_embedding"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// Decode-step attention against the KV cache: the chain dot(Q, K^T), mul, where(mask), softmax,
+// dot(P, V) of a GroupQueryAttention node with one query row per head
+// (src/onnx/parse_group_query_attention.cpp:184-262) as one launch.  Inputs: Q [B, heads, 1, D]
+// (rows contiguous, any batch / head strides), K cache and V cache [B, kv_heads, T, D] (packed),
+// seqlens_k [B, 1] or [B], out [B, heads, 1, D] (packed).
+struct op_gqa_decode_attention
+{
+    std::size_t num_heads    = 0;
+    std::size_t kv_num_heads = 0;
+    float scale              = 1.0f;
+    template <class Self, class F>
+    static auto reflect(Self& self, F f)
+    {
+        return pack(f(self.num_heads, "num_heads"), f(self.kv_num_heads, "kv_num_heads"), f(self.scale, "scale"));
+    }
+    std::string name() const { return "cuda::gqa_decode_attention"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
 // Weight-only int4 linear (unpack_int4 + dequantizelinear + transpose + dot fused).
 // Inputs: A fp16 [M,K], packed weights uint8 [N,K/2], scales fp16 [N,K/group],
 // [zero points uint8 [N,K/group]], [workspace], out fp16 [M,N].

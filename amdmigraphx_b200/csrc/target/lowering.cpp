@@ -1044,6 +1044,150 @@ struct lowerer
         return true;
     }
 
+    // ---------------------------------------------------------------- decode-step GQA attention
+    // softmax(where(position > seqlens_k, -inf, mul(dot(Q, transpose(K')), scale))) followed by
+    // dot(P, V'), K' / V' the caches with their KV heads broadcast to the query heads, one query
+    // row per head (src/onnx/parse_group_query_attention.cpp:184-262): one cuda::gqa_decode_attention
+    // in place of the second dot.  Anything else (a prompt, another mask) keeps the operators.
+    bool lower_gqa_decode(instruction_ref sm)
+    {
+        if(fusion_disabled("attention"))
+            return false;
+        const auto& ps = sm->get_shape(); // [B, heads, 1, T]
+        if(ps.type() != shape::half_type or ps.ndim() != 4 or ps.lens()[2] != 1)
+            return false;
+        const auto ax = sm->get_operator().to_value().at("axis").to<int64_t>();
+        if(ax != 3 and ax != -1)
+            return false;
+        const std::size_t b = ps.lens()[0], nh = ps.lens()[1], t = ps.lens()[3];
+        auto is_transpose = [](instruction_ref x, std::vector<int64_t> perm) {
+            return x->name() == "transpose" and
+                   x->get_operator().to_value().at("permutation").to_vector<int64_t>() == perm;
+        };
+        // the cache behind the grouped-query broadcast: reshape(multibroadcast(unsqueeze(cache, 2)))
+        std::vector<instruction_ref> chain = {sm};
+        auto cache_of = [&](instruction_ref x, std::size_t d) -> instruction_ref {
+            if(x->name() == "reshape" or x->name() == "reshape_lazy")
+            {
+                auto mb = x->inputs().front();
+                if(mb->name() != "multibroadcast" or mb->get_shape().ndim() != 5)
+                    return m.end();
+                auto us = mb->inputs().front();
+                if(us->name() != "unsqueeze" or
+                   us->get_operator().to_value().at("axes").to_vector<int64_t>() != std::vector<int64_t>{2})
+                    return m.end();
+                chain.insert(chain.end(), {x, mb, us});
+                x = us->inputs().front();
+            }
+            const auto& xs = x->get_shape();
+            if(xs.type() != shape::half_type or xs.ndim() != 4 or not xs.standard() or xs.lens()[0] != b or
+               xs.lens()[2] != t or xs.lens()[3] != d or nh % xs.lens()[1] != 0)
+                return m.end();
+            return x;
+        };
+        // where(mask, -inf, scores)
+        auto wh = sm->inputs().front();
+        if(wh->name() != "where" or wh->outputs().size() != 1)
+            return false;
+        auto mask = wh->inputs()[0], fill = wh->inputs()[1], mul = wh->inputs()[2];
+        if(not fill->can_eval())
+            return false;
+        {
+            auto fv = classify_constant(fill);
+            if(fv.kind != bcast_kind::scalar or not(std::isinf(fv.values[0]) and fv.values[0] < 0))
+                return false;
+        }
+        if(mask->name() == "convert")
+        {
+            chain.push_back(mask);
+            mask = mask->inputs().front();
+        }
+        if(mask->name() != "greater")
+            return false;
+        // greater(positions 0 .. T-1 along the last axis, seqlens_k of the batch entry)
+        auto range = mask->inputs()[0], lens = mask->inputs()[1];
+        if(not range->can_eval())
+            return false;
+        {
+            auto rv = range->eval();
+            const auto& rs = rv.get_shape();
+            if(rs.lens() != ps.lens() or rs.strides()[0] != 0 or rs.strides()[1] != 0 or rs.strides()[3] != 1)
+                return false;
+            bool iota = true;
+            rv.visit([&](auto view) {
+                for(std::size_t j = 0; j < t and iota; ++j)
+                    iota = static_cast<std::size_t>(view[j]) == j;
+            });
+            if(not iota)
+                return false;
+        }
+        chain.push_back(mask);
+        // the past lengths behind broadcasts and reshapes: one value per batch entry
+        while(lens->name() == "multibroadcast" or lens->name() == "reshape" or lens->name() == "reshape_lazy")
+        {
+            const auto& ls = lens->get_shape();
+            // every view on the way must vary along the batch only
+            if(ls.lens()[0] != b)
+                return false;
+            chain.push_back(lens);
+            lens = lens->inputs().front();
+        }
+        const auto& lsh = lens->get_shape();
+        if(lsh.elements() != b or not lsh.standard() or
+           (lsh.type() != shape::int32_type and lsh.type() != shape::int64_type))
+            return false;
+        // scores = mul(dot(Q, K'^T), scale)
+        if(mul->name() != "mul" or mul->outputs().size() != 1)
+            return false;
+        instruction_ref c = m.end();
+        for(auto i : mul->inputs())
+            if(i->can_eval())
+                c = i;
+        if(c == m.end())
+            return false;
+        auto cv = classify_constant(c);
+        if(cv.kind != bcast_kind::scalar)
+            return false;
+        auto d1 = other_input(mul, c);
+        if(d1->name() != "dot" or d1->outputs().size() != 1)
+            return false;
+        auto q  = d1->inputs()[0];
+        auto kt = d1->inputs()[1];
+        const auto& qs = q->get_shape();
+        if(qs.type() != shape::half_type or qs.ndim() != 4 or qs.lens()[0] != b or qs.lens()[1] != nh or
+           qs.lens()[2] != 1 or qs.strides().back() != 1)
+            return false;
+        const std::size_t d = qs.lens()[3];
+        if(not is_transpose(kt, {0, 1, 3, 2}))
+            return false;
+        auto kc = cache_of(kt->inputs().front(), d);
+        auto d2 = single_user(m, sm);
+        if(kc == m.end() or not valid(d2, m) or d2->name() != "dot" or d2->inputs()[0] != sm)
+            return false;
+        auto vc = cache_of(d2->inputs()[1], d);
+        if(vc == m.end() or vc->get_shape() != kc->get_shape())
+            return false;
+        const std::size_t kvh = kc->get_shape().lens()[1];
+        if(mgx_cuda_gqa_decode_supported(static_cast<int64_t>(b), static_cast<int64_t>(nh), static_cast<int64_t>(kvh),
+                                         static_cast<int64_t>(d), static_cast<int64_t>(t)) == 0)
+            return false;
+        chain.insert(chain.end(), {wh, mul, d1, kt});
+        for(auto x : chain)
+        {
+            consume(x);
+            for(auto i : x->inputs())
+                if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
+                    consume(i);
+        }
+        op_gqa_decode_attention op;
+        op.num_heads    = nh;
+        op.kv_num_heads = kvh;
+        op.scale        = cv.values[0];
+        auto buf = insert_allocation(m, d2, d2->get_shape().as_standard());
+        consume(m.replace_instruction(d2, op, q, kc, vc, lens, buf));
+        return true;
+    }
+
     // ---------------------------------------------------------------- LayerNorm
     // mean = reduce_mean(x, last axis); d = sub(x, bcast(mean)); var = reduce_mean(mul(d, d) |
     // sqdiff(x, bcast(mean))); rs = rsqrt(add(var, eps)); y = mul(d, bcast(rs)) [* gamma] [+ beta]
@@ -1306,6 +1450,73 @@ struct lowerer
         return true;
     }
 
+    // the decoder's cache / rotary operators and gathernd over single row indices
+    bool lower_decoder_op(instruction_ref ins)
+    {
+        const auto name = ins->name();
+        if(name == "concat_past_present")
+        {
+            auto args = ins->inputs();
+            if(args.size() != 3)
+                unsupported(ins, "expects present, seqlens_k and the cache");
+            const auto& pr = args[0]->get_shape();
+            if(pr.ndim() != 4 or pr.strides().back() != 1)
+                args[0] = standard_copy(ins, args[0]);
+            if(not args[1]->get_shape().standard())
+                args[1] = standard_copy(ins, args[1]);
+            if(not args[2]->get_shape().standard())
+                unsupported(ins, "the cache must be a packed tensor");
+            op_concat_past_present op;
+            op.kv_num_heads = ins->get_operator().to_value().at("kv_num_heads").to<std::size_t>();
+            consume(m.replace_instruction(ins, op, args));
+            return true;
+        }
+        if(name == "gqa_rotary_embedding")
+        {
+            auto args = ins->inputs();
+            if(args.size() != 4)
+                unsupported(ins, "expects packed QKV, seqlens_k and the cos / sin caches");
+            for(auto& a : args)
+                if(not a->get_shape().standard())
+                    a = standard_copy(ins, a);
+            const auto v = ins->get_operator().to_value();
+            op_gqa_rotary_embedding op;
+            op.num_heads    = v.at("num_heads").to<std::size_t>();
+            op.kv_num_heads = v.at("kv_num_heads").to<std::size_t>();
+            op.interleaved  = v.at("interleaved").to<bool>();
+            args.push_back(insert_allocation(m, ins, ins->get_shape().as_standard()));
+            consume(m.replace_instruction(ins, op, args));
+            return true;
+        }
+        if(name == "gathernd")
+        {
+            // indices [.., 1] without batch dimensions select whole slices along axis 0: a gather
+            // (src/include/migraphx/op/gathernd.hpp); what the rotary-embedding builder uses to pick the
+            // cos / sin rows of the positions (src/op/builder/rotary_embedding.cpp:151-154)
+            const auto v   = ins->get_operator().to_value();
+            auto data      = ins->inputs()[0];
+            auto idx       = ins->inputs()[1];
+            const auto& is = idx->get_shape();
+            if(v.at("batch_dims").to<int64_t>() != 0 or is.lens().back() != 1)
+                unsupported(ins, "only indices of one component without batch dimensions");
+            if(is.type() != shape::int32_type and is.type() != shape::int64_type)
+                unsupported(ins, "indices must be int32 or int64");
+            if(not data->get_shape().standard())
+                data = standard_copy(ins, data);
+            if(not is.standard())
+                idx = standard_copy(ins, idx);
+            auto il = is.lens();
+            il.pop_back();
+            if(il.empty())
+                il.push_back(1);
+            auto flat = m.insert_instruction(ins, make_op("reshape_lazy", {{"dims", il}}), idx);
+            auto buf  = insert_allocation(m, ins, ins->get_shape().as_standard());
+            consume(m.replace_instruction(ins, op_gather{0}, data, flat, buf));
+            return true;
+        }
+        return false;
+    }
+
     // gather and concat: byte movers on packed tensors (strided operands are packed first)
     bool lower_mover(instruction_ref ins)
     {
@@ -1547,7 +1758,10 @@ struct lowerer
         // whole attention blocks first (their two dots must not be lowered one by one)
         for(auto ins : order)
             if(not skip(ins) and ins->name() == "softmax")
-                lower_attention(ins);
+            {
+                if(not lower_gqa_decode(ins))
+                    lower_attention(ins);
+            }
         // GEMM sub-graphs next: their operands (packed int4 weights, scale expressions) must
         // still be in their original form, not folded into dense constants
         for(auto ins : order)
@@ -1599,6 +1813,8 @@ struct lowerer
             else if(lower_row_op(ins))
                 continue;
             else if(lower_mover(ins))
+                continue;
+            else if(lower_decoder_op(ins))
                 continue;
             else
                 unsupported(ins, "no kernel");
@@ -1841,7 +2057,8 @@ void insert_graph_ops::apply(module_pass_manager& mpm) const
                n == "cuda::w4a16" or n == "cuda::unpack_int4" or n == "cuda::pack_int4" or
                n == "cuda::copy" or n == "cuda::pointwise" or n == "cuda::reduce" or n == "cuda::softmax" or
                n == "cuda::gather" or n == "cuda::concat" or n == "cuda::pad_rows" or
-               n == "cuda::layernorm" or n == "cuda::attention";
+               n == "cuda::layernorm" or n == "cuda::attention" or n == "cuda::concat_past_present" or
+               n == "cuda::gqa_rotary_embedding";
     };
     auto last = std::prev(m.end());
     if(last->name() != "@return" or last->inputs().empty())

@@ -593,6 +593,118 @@ argument op_attention::compute(context& ctx, const shape&, const std::vector<arg
     return args.back();
 }
 
+// ------------------------------------------------------------------ KV cache, rotary embedding
+static int index_type(shape::type_t t)
+{
+    if(t == shape::int32_type)
+        return MGX_I32;
+    if(t == shape::int64_type)
+        return MGX_I64;
+    MIGRAPHX_THROW("cuda target: sequence lengths must be int32 or int64");
+}
+
+shape op_concat_past_present::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(3);
+    const auto& pr = inputs[0];
+    const auto& pa = inputs[2];
+    if(pr.ndim() != 4 or pa.ndim() != 4 or pr.type() != pa.type() or not pa.standard() or
+       pr.strides().back() != 1 or pr.lens()[0] != pa.lens()[0] or pr.lens()[1] != pa.lens()[1] or
+       pr.lens()[3] != pa.lens()[3])
+        MIGRAPHX_THROW("cuda::concat_past_present: expects present [B, H, L, D] with contiguous rows and a packed "
+                       "cache [B, H, T, D] of the same type");
+    return pa;
+}
+
+argument op_concat_past_present::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    if(ctx.replaying())
+        return args[2];
+    const auto& pr = args[0].get_shape();
+    const auto& pa = args[2].get_shape();
+    const auto es  = static_cast<int64_t>(pr.type_size());
+    const int64_t strides[3] = {static_cast<int64_t>(pr.strides()[0]) * es, static_cast<int64_t>(pr.strides()[1]) * es,
+                                static_cast<int64_t>(pr.strides()[2]) * es};
+    check_mgx(mgx_cuda_concat_past_present(args[0].data(), strides, static_cast<int64_t>(pr.lens()[0]),
+                                           static_cast<int64_t>(pr.lens()[1]), static_cast<int64_t>(pr.lens()[2]),
+                                           static_cast<int64_t>(pr.lens()[3]) * es, args[1].data(),
+                                           index_type(args[1].get_shape().type()), args[2].data(),
+                                           static_cast<int64_t>(pa.lens()[2]), ctx.stream()),
+              "mgx_cuda_concat_past_present");
+    return args[2];
+}
+
+shape op_gqa_rotary_embedding::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(5);
+    const auto& x = inputs[0];
+    if(x.ndim() != 4 or not x.standard() or x.lens()[1] != num_heads + 2 * kv_num_heads or
+       (x.type() != shape::half_type and x.type() != shape::float_type) or inputs[2].type() != x.type() or
+       inputs[3].type() != x.type() or inputs[2].ndim() != 2 or not inputs[2].standard() or
+       not inputs[3].standard() or inputs[4].lens() != x.lens() or not inputs[4].standard())
+        MIGRAPHX_THROW("cuda::gqa_rotary_embedding: expects packed QKV [B, heads + 2 kv_heads, S, D], 2-D caches of "
+                       "the same type and a packed output");
+    return inputs[4];
+}
+
+argument op_gqa_rotary_embedding::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& x = args[0].get_shape();
+    const auto& c = args[2].get_shape();
+    check_mgx(mgx_cuda_gqa_rotary_embedding(
+                  args[0].data(), mgx_type(x.type()), static_cast<int64_t>(x.lens()[0]), static_cast<int64_t>(num_heads),
+                  static_cast<int64_t>(kv_num_heads), static_cast<int64_t>(x.lens()[2]), static_cast<int64_t>(x.lens()[3]),
+                  args[2].data(), args[3].data(), static_cast<int64_t>(c.lens()[0]), static_cast<int64_t>(c.lens()[1]) * 2,
+                  args[1].data(), index_type(args[1].get_shape().type()), interleaved ? 1 : 0, out.data(), ctx.stream()),
+              "mgx_cuda_gqa_rotary_embedding");
+    return out;
+}
+
+shape op_gqa_decode_attention::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(5);
+    const auto& q = inputs[0];
+    const auto& k = inputs[1];
+    if(q.ndim() != 4 or q.type() != shape::half_type or q.lens()[1] != num_heads or q.lens()[2] != 1 or
+       q.strides().back() != 1)
+        MIGRAPHX_THROW("cuda::gqa_decode_attention: expects fp16 queries [B, heads, 1, D] with contiguous rows");
+    if(k.ndim() != 4 or not k.standard() or k.type() != shape::half_type or k.lens()[0] != q.lens()[0] or
+       k.lens()[1] != kv_num_heads or k.lens()[3] != q.lens()[3] or inputs[2] != k)
+        MIGRAPHX_THROW("cuda::gqa_decode_attention: expects packed fp16 caches [B, kv_heads, T, D]");
+    if(inputs[3].elements() != q.lens()[0] or not inputs[3].standard() or
+       (inputs[3].type() != shape::int32_type and inputs[3].type() != shape::int64_type))
+        MIGRAPHX_THROW("cuda::gqa_decode_attention: expects one int32 / int64 past length per batch entry");
+    if(inputs[4].lens() != q.lens() or not inputs[4].standard() or inputs[4].type() != shape::half_type)
+        MIGRAPHX_THROW("cuda::gqa_decode_attention: output must be a packed fp16 tensor of the queries' shape");
+    return inputs[4];
+}
+
+argument op_gqa_decode_attention::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& q = args[0].get_shape();
+    const auto& k = args[1].get_shape();
+    mgx_gqa_decode_desc d{};
+    d.batch          = static_cast<int64_t>(q.lens()[0]);
+    d.heads          = static_cast<int64_t>(num_heads);
+    d.kv_heads       = static_cast<int64_t>(kv_num_heads);
+    d.head           = static_cast<int64_t>(q.lens()[3]);
+    d.cache_seq      = static_cast<int64_t>(k.lens()[2]);
+    d.q_batch_stride = static_cast<int64_t>(q.strides()[0]);
+    d.q_head_stride  = static_cast<int64_t>(q.strides()[1]);
+    d.scale          = scale;
+    d.seqlens_type   = index_type(args[3].get_shape().type());
+    check_mgx(mgx_cuda_gqa_decode_attention(&d, args[0].data(), args[1].data(), args[2].data(), args[3].data(),
+                                            out.data(), ctx.stream()),
+              "mgx_cuda_gqa_decode_attention");
+    return out;
+}
+
 shape op_softmax::compute_shape(const std::vector<shape>& inputs) const
 {
     check_shapes{inputs, *this}.has(2);
@@ -728,6 +840,9 @@ MIGRAPHX_REGISTER_OP(op_reduce)
 MIGRAPHX_REGISTER_OP(op_softmax)
 MIGRAPHX_REGISTER_OP(op_layernorm)
 MIGRAPHX_REGISTER_OP(op_attention)
+MIGRAPHX_REGISTER_OP(op_concat_past_present)
+MIGRAPHX_REGISTER_OP(op_gqa_rotary_embedding)
+MIGRAPHX_REGISTER_OP(op_gqa_decode_attention)
 MIGRAPHX_REGISTER_OP(op_pointwise)
 MIGRAPHX_REGISTER_OP(op_second_output)
 MIGRAPHX_REGISTER_OP(op_align_anchor)

@@ -18,6 +18,7 @@
 #include <migraphx/generate.hpp>
 #include <migraphx/half.hpp>
 #include <migraphx/quantization.hpp>
+#include <migraphx/op/builder/insert.hpp>
 #include <chrono>
 #include <cmath>
 #include <cstring>
@@ -26,6 +27,8 @@
 #include <random>
 #include <functional>
 #include <algorithm>
+#include <numeric>
+#include <limits>
 
 namespace mgx_programs {
 
@@ -1099,6 +1102,154 @@ inline bert_program bert_encoder_int8(const bert_config& c)
     rets.insert(rets.end(), calib_out.begin(), calib_out.end());
     mm->add_return(rets);
     return bp;
+}
+
+// ---------------------------------------------------------------------------------------------
+// GroupQueryAttention of a decoder layer exactly as the ONNX parser decomposes it
+// (src/onnx/parse_group_query_attention.cpp:113-268): packed QKV -> heads, rotary embedding of Q
+// and K through the rotary_embedding builder (src/op/builder/rotary_embedding.cpp: gathernd of the
+// cos / sin caches at the positions, rotate-half, mul, add), concat_past_present of K and V into
+// the fp16 caches, grouped-query broadcast of the KV heads, Q K^T over the whole cache length,
+// masks by position and by past length, softmax, P V, heads merged.  seq = 1: a decode step at the
+// past lengths `seqlens`; seq > 1: the prompt.  Returns {attention output, K cache, V cache}.
+inline std::vector<instruction_ref> add_gqa(migraphx::module* mm, instruction_ref qkv, instruction_ref past_k,
+                                            instruction_ref past_v, instruction_ref slk, instruction_ref cos_cache,
+                                            instruction_ref sin_cache, std::size_t num_heads,
+                                            std::size_t kv_num_heads, bool use_rotary_op = false)
+{
+    using migraphx::make_op;
+    const auto& q_lens                = qkv->get_shape().lens();
+    const std::size_t batch_size      = q_lens[0];
+    const std::size_t sequence_length = q_lens[1];
+    const std::size_t head_size       = q_lens[2] / (num_heads + 2 * kv_num_heads);
+    const auto dtype                  = qkv->get_shape().type();
+    std::vector<std::size_t> bsnh{batch_size, sequence_length, num_heads + 2 * kv_num_heads, head_size};
+    auto tq = mm->add_instruction(make_op("reshape", {{"dims", bsnh}}), qkv);
+    tq      = mm->add_instruction(make_op("transpose", {{"permutation", {0, 2, 1, 3}}}), tq);
+    instruction_ref qk, cur_v;
+    if(use_rotary_op)
+    {
+        // the single-operator form (op::gqa_rotary_embedding rotates Q and K of the packed tensor)
+        auto rot = mm->add_instruction(
+            make_op("gqa_rotary_embedding",
+                    {{"num_heads", num_heads}, {"kv_num_heads", kv_num_heads}, {"interleaved", false}}),
+            mm->add_instruction(make_op("contiguous"), tq), slk, cos_cache, sin_cache);
+        qk    = mm->add_instruction(make_op("slice", {{"axes", {1}}, {"starts", {0}}, {"ends", {num_heads + kv_num_heads}}}), rot);
+        cur_v = mm->add_instruction(make_op("slice", {{"axes", {1}}, {"starts", {num_heads + kv_num_heads}}, {"ends", {num_heads + 2 * kv_num_heads}}}), rot);
+    }
+    else
+    {
+        qk    = mm->add_instruction(make_op("slice", {{"axes", {1}}, {"starts", {0}}, {"ends", {num_heads + kv_num_heads}}}), tq);
+        cur_v = mm->add_instruction(make_op("slice", {{"axes", {1}}, {"starts", {num_heads + kv_num_heads}}, {"ends", {num_heads + 2 * kv_num_heads}}}), tq);
+        auto pos_ids = slk;
+        if(sequence_length > 1)
+            pos_ids = mm->add_literal(migraphx::literal{shape{slk->get_shape().type(), {1}}, {0}});
+        qk = migraphx::op::builder::add("rotary_embedding", *mm, {qk, pos_ids, cos_cache, sin_cache},
+                                        {{"interleaved", false}})
+                 .at(0);
+    }
+    auto q     = mm->add_instruction(make_op("slice", {{"axes", {1}}, {"starts", {0}}, {"ends", {num_heads}}}), qk);
+    auto cur_k = mm->add_instruction(make_op("slice", {{"axes", {1}}, {"starts", {num_heads}}, {"ends", {num_heads + kv_num_heads}}}), qk);
+    auto k = mm->add_instruction(make_op("concat_past_present", {{"kv_num_heads", kv_num_heads}}), cur_k, slk, past_k);
+    auto v = mm->add_instruction(make_op("concat_past_present", {{"kv_num_heads", kv_num_heads}}), cur_v, slk, past_v);
+    auto k_out = k, v_out = v;
+    const auto factor      = num_heads / kv_num_heads;
+    const auto max_seq_len = k->get_shape().lens()[2];
+    auto past_sl = mm->add_instruction(make_op("multibroadcast", {{"out_lens", {batch_size, num_heads}}}), slk);
+    if(factor != 1)
+    {
+        auto kv_new_lens  = k->get_shape().lens();
+        kv_new_lens.at(1) = num_heads;
+        k = mm->add_instruction(make_op("unsqueeze", {{"axes", {2}}}), k);
+        v = mm->add_instruction(make_op("unsqueeze", {{"axes", {2}}}), v);
+        auto ul  = k->get_shape().lens();
+        ul.at(2) = factor;
+        k = mm->add_instruction(make_op("multibroadcast", {{"out_lens", ul}}), k);
+        v = mm->add_instruction(make_op("multibroadcast", {{"out_lens", ul}}), v);
+        k = mm->add_instruction(make_op("reshape", {{"dims", kv_new_lens}}), k);
+        v = mm->add_instruction(make_op("reshape", {{"dims", kv_new_lens}}), v);
+    }
+    auto kt    = mm->add_instruction(make_op("transpose", {{"permutation", {0, 1, 3, 2}}}), k);
+    auto gemm1 = mm->add_instruction(make_op("dot"), q, kt);
+    std::vector<int> range_vec(max_seq_len);
+    std::iota(range_vec.begin(), range_vec.end(), 0);
+    auto range = mm->add_literal(migraphx::literal{shape{past_sl->get_shape().type(), {max_seq_len}}, range_vec});
+    std::vector<std::size_t> bnsm{batch_size, num_heads, sequence_length, max_seq_len};
+    auto bc_range = mm->add_instruction(make_op("multibroadcast", {{"out_lens", bnsm}}), range);
+    const shape scalar_s{dtype, {1}};
+    auto ninf = mm->add_literal(migraphx::literal{scalar_s, {-std::numeric_limits<float>::infinity()}});
+    ninf      = mm->add_instruction(make_op("multibroadcast", {{"out_lens", bnsm}}), ninf);
+    auto scale_ins = mm->add_literal(migraphx::literal{scalar_s, {1.0f / std::sqrt(static_cast<float>(head_size))}});
+    scale_ins      = mm->add_instruction(make_op("multibroadcast", {{"out_lens", bnsm}}), scale_ins);
+    auto mul       = mm->add_instruction(make_op("mul"), gemm1, scale_ins);
+    if(sequence_length > 1)
+    {
+        std::vector<int> sr(sequence_length);
+        std::iota(sr.begin(), sr.end(), 0);
+        auto seq_range = mm->add_literal(migraphx::literal{shape{past_sl->get_shape().type(), {sequence_length}}, sr});
+        seq_range = mm->add_instruction(make_op("reshape", {{"dims", {sequence_length, 1}}}), seq_range);
+        seq_range = mm->add_instruction(make_op("multibroadcast", {{"out_lens", bnsm}}), seq_range);
+        auto causal = mm->add_instruction(make_op("greater"), bc_range, seq_range);
+        causal = mm->add_instruction(make_op("convert", {{"target_type", migraphx::to_value(shape::bool_type)}}), causal);
+        mul    = mm->add_instruction(make_op("where"), causal, ninf, mul);
+    }
+    auto bc_past_sl = mm->add_instruction(make_op("reshape", {{"dims", {batch_size, num_heads, 1, 1}}}), past_sl);
+    auto mask_comp  = mm->add_instruction(make_op("multibroadcast", {{"out_lens", bnsm}}), bc_past_sl);
+    auto mask       = mm->add_instruction(make_op("greater"), bc_range, mask_comp);
+    mask = mm->add_instruction(make_op("convert", {{"target_type", migraphx::to_value(shape::bool_type)}}), mask);
+    auto where   = mm->add_instruction(make_op("where"), mask, ninf, mul);
+    auto softmax = mm->add_instruction(make_op("softmax", {{"axis", 3}}), where);
+    auto scores  = mm->add_instruction(make_op("dot"), softmax, v);
+    auto out     = mm->add_instruction(make_op("transpose", {{"permutation", {0, 2, 1, 3}}}), scores);
+    out = mm->add_instruction(make_op("reshape", {{"dims", {batch_size, sequence_length, head_size * num_heads}}}), out);
+    return {out, k_out, v_out};
+}
+
+// The attention block of a decoder layer by itself, on parameters.  For a decode step the past
+// lengths differ per batch entry; the caches hold random history.
+inline test_case gqa_attention(std::size_t batch, std::size_t num_heads, std::size_t kv_heads, std::size_t head,
+                               std::size_t seq, std::size_t cache_len, bool use_rotary_op, unsigned seed)
+{
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const std::size_t width = (num_heads + 2 * kv_heads) * head;
+    auto half_arg = [&](const shape& s, float sd) {
+        auto v = rand_normal(g, s.elements(), sd);
+        std::vector<migraphx::half> h(v.begin(), v.end());
+        migraphx::argument a{s};
+        std::memcpy(a.data(), h.data(), h.size() * sizeof(migraphx::half));
+        return a;
+    };
+    const shape qkv_s{shape::half_type, {batch, seq, width}};
+    const shape kv_s{shape::half_type, {batch, kv_heads, cache_len, head}};
+    const shape slk_s{shape::int32_type, {batch, 1}};
+    auto qkv    = mm->add_parameter("qkv", qkv_s);
+    auto past_k = mm->add_parameter("past_k", kv_s);
+    auto past_v = mm->add_parameter("past_v", kv_s);
+    auto slk    = mm->add_parameter("seqlens_k", slk_s);
+    std::vector<migraphx::half> cosv(cache_len * head / 2), sinv(cache_len * head / 2);
+    for(std::size_t p = 0; p < cache_len; ++p)
+        for(std::size_t i = 0; i < head / 2; ++i)
+        {
+            const double ang = static_cast<double>(p) * std::pow(10000.0, -2.0 * static_cast<double>(i) / head);
+            cosv[p * head / 2 + i] = migraphx::half(static_cast<float>(std::cos(ang)));
+            sinv[p * head / 2 + i] = migraphx::half(static_cast<float>(std::sin(ang)));
+        }
+    auto cosl = mm->add_literal(migraphx::literal{shape{shape::half_type, {cache_len, head / 2}}, cosv});
+    auto sinl = mm->add_literal(migraphx::literal{shape{shape::half_type, {cache_len, head / 2}}, sinv});
+    mm->add_return(add_gqa(mm, qkv, past_k, past_v, slk, cosl, sinl, num_heads, kv_heads, use_rotary_op));
+    t.params["qkv"]    = half_arg(qkv_s, 1.0f);
+    t.params["past_k"] = half_arg(kv_s, 1.0f);
+    t.params["past_v"] = half_arg(kv_s, 1.0f);
+    migraphx::argument sa{slk_s};
+    std::uniform_int_distribution<int32_t> pick(static_cast<int32_t>(cache_len / 2), static_cast<int32_t>(cache_len - seq - 1));
+    for(std::size_t b = 0; b < batch; ++b)
+        reinterpret_cast<int32_t*>(sa.data())[b] = seq == 1 ? pick(g) : static_cast<int32_t>(seq - 1);
+    t.params["seqlens_k"] = sa;
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
+    return t;
 }
 
 // seeded token ids in [0, vocab)

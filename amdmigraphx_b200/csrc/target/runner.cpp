@@ -126,12 +126,14 @@ MGX_RUNNER_API int mgx_runner_create_bert(const mgx_bert_desc* d, void** out)
         migraphx::compile_options opts;
         opts.offload_copy = r->offload;
         r->prog.compile(r->tgt, opts);
-        for(auto ins : migraphx::iterator_for(*r->prog.get_main_module()))
-        {
-            ++r->op_counts[ins->name()];
-            if(launching(ins->name()))
-                ++r->launches;
-        }
+        // every module: the compiled body sits in a submodule behind cuda::graph_run
+        for(auto* mod : r->prog.get_modules())
+            for(auto ins : migraphx::iterator_for(*mod))
+            {
+                ++r->op_counts[ins->name()];
+                if(launching(ins->name()))
+                    ++r->launches;
+            }
         auto& ctx = migraphx::any_cast<migraphx::cuda::context>(r->prog.get_context());
         r->stream = ctx.stream();
         if(cudaEventCreate(&r->e0) != cudaSuccess or cudaEventCreate(&r->e1) != cudaSuccess)

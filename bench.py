@@ -703,6 +703,28 @@ def run_case(a):
         s = torch.tensor([0.02], device=dev, dtype=x.dtype)
         fn = lambda: capi.quantizelinear(x, s, out_dtype=torch.int8)  # noqa: E731
         work, unit = (x.element_size() + 1.0) * M * N, "GB/s"
+    elif a.case == "attention":
+        # --m sequences of --n tokens, --k heads of 64: the encoder's attention on a fused QKV buffer
+        width = K * 64
+        qkv = torch.randn((M * N, 3 * width), device=dev, dtype=torch.float16)
+        q, k_, v = qkv[:, :width], qkv[:, width:2 * width], qkv[:, 2 * width:]
+        fn = lambda: capi.attention(q, k_, v, M, N, K, 0.125, q_scale=0.006,  # noqa: E731
+                                    fp32_softmax=a.act == "fp32")
+        work, unit = 4.0 * M * K * N * N * 64, "TOPS"
+    elif a.case == "gqa_decode":
+        # --m batch entries, --n cache positions (all valid), --k query heads, --kv-heads KV heads of 128
+        kc = torch.randn((M, a.kv_heads, N, 128), device=dev, dtype=torch.float16)
+        vc = torch.randn((M, a.kv_heads, N, 128), device=dev, dtype=torch.float16)
+        qd = torch.randn((M, K, 128), device=dev, dtype=torch.float16)
+        lens = torch.full((M, 1), N - 1, dtype=torch.int32, device=dev)
+        fn = lambda: capi.gqa_decode_attention(qd, kc, vc, lens, 0.08837890625)  # noqa: E731
+        work, unit = 2.0 * kc.numel() * 2, "GB/s"
+    elif a.case == "layernorm":
+        x = torch.randn((M, N), device=dev, dtype=torch.float16)
+        g = torch.randn(N, device=dev, dtype=torch.float16)
+        b_ = torch.randn(N, device=dev, dtype=torch.float16)
+        fn = lambda: capi.layernorm(x, g, b_, 1e-12, q_scale=0.04, dq_scale=0.04)  # noqa: E731
+        work, unit = (2.0 + 2.0 + 1.0 + 2.0) * M * N, "GB/s"
     else:
         x = torch.randn((M, K), device=dev, dtype=torch.float16)
         bp = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev)
@@ -733,11 +755,13 @@ def main():
     ap.add_argument("--impl", default="own", choices=["own", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
-    ap.add_argument("--case", default=None, choices=["qgemm_i8", "qgemm_fp8", "quantize", "w4a16", "encoder"],
+    ap.add_argument("--case", default=None, choices=["qgemm_i8", "qgemm_fp8", "quantize", "w4a16", "encoder", "attention", "layernorm",
+                                                        "gqa_decode"],
                     help="run one kernel by itself (for profiler captures) instead of the benchmark")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--kv-heads", type=int, default=32)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--case-warmup", type=int, default=1)
     ap.add_argument("--act", default="gelu_erf")

@@ -223,6 +223,50 @@ typedef struct mgx_attention_desc
 MGX_API int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
                                void* oq, void* stream);
 
+/* ---- decoder KV cache and rotary embedding ("next" rows: Llama-shaped layers) ------------- *
+ * concat_past_present: the new keys / values of a step, present [batch, kv_heads, seq, head]
+ * (byte strides along batch / head / row in present_strides, rows contiguous), are copied into
+ * the cache past [batch, kv_heads, cache_seq, head] in place: at row seqlens[b] of every head when
+ * seq == 1 (decode), at row 0 otherwise (prompt).  Stands in for op::concat_past_present::compute
+ * (src/include/migraphx/op/concat_past_present.hpp:84-155).  Rows that would fall beyond
+ * cache_seq are not written.  seqlens_type: MGX_I32 | MGX_I64. */
+MGX_API int mgx_cuda_concat_past_present(const void* present, const int64_t present_strides[3], int64_t batch,
+                                         int64_t kv_heads, int64_t seq, int64_t head_bytes, const void* seqlens,
+                                         int seqlens_type, void* past, int64_t cache_seq, void* stream);
+
+/* gqa_rotary_embedding: rotary position embedding of the Q and K heads of a packed
+ * [batch, heads + 2 kv_heads, seq, head] tensor (V heads and columns beyond rotary_dim pass
+ * through), positions s (prompt) or seqlens[b] (decode, seq == 1), cos / sin caches
+ * [max_seq, rotary_dim / 2] in the tensor's type.  Stands in for
+ * op::gqa_rotary_embedding::compute (src/include/migraphx/op/gqa_rotary_embedding.hpp:72-221) with
+ * its roundings.  type: MGX_F16 | MGX_F32. */
+MGX_API int mgx_cuda_gqa_rotary_embedding(const void* qkv, int type, int64_t batch, int64_t heads, int64_t kv_heads,
+                                          int64_t seq, int64_t head, const void* cos_cache, const void* sin_cache,
+                                          int64_t max_seq, int64_t rotary_dim, const void* seqlens, int seqlens_type,
+                                          int interleaved, void* out, void* stream);
+
+/* Decode-step attention against the fp16 KV cache, one launch: for every batch entry b and query
+ * head h (sharing KV head h / (heads / kv_heads)), softmax(scale * q K^T) V over the cache
+ * positions 0 .. seqlens[b], positions beyond it masked out.  Stands in for the operator chain
+ * the GroupQueryAttention parser emits after concat_past_present
+ * (src/onnx/parse_group_query_attention.cpp:184-262: KV-head broadcast, dot, mul, where, softmax,
+ * dot) with that chain's fp16 roundings.  q: rows of `head` halves at q + b * q_batch_stride +
+ * h * q_head_stride (elements); caches packed [batch, kv_heads, cache_seq, head], 16-byte aligned;
+ * out packed [batch, heads * head].  head: 64 | 128; heads / kv_heads: 1 | 2 | 4 | 8.
+ * MGX_E_TOO_LARGE when a CTA's share of the cache positions does not fit shared memory
+ * (mgx_cuda_gqa_decode_supported tells beforehand). */
+typedef struct mgx_gqa_decode_desc
+{
+    int64_t batch, heads, kv_heads, head, cache_seq;
+    int64_t q_batch_stride, q_head_stride;
+    float scale;
+    int32_t seqlens_type; /* MGX_I32 | MGX_I64 */
+} mgx_gqa_decode_desc;
+MGX_API int mgx_cuda_gqa_decode_attention(const mgx_gqa_decode_desc* d, const void* q, const void* k_cache,
+                                          const void* v_cache, const void* seqlens, void* out, void* stream);
+MGX_API int mgx_cuda_gqa_decode_supported(int64_t batch, int64_t heads, int64_t kv_heads, int64_t head,
+                                          int64_t cache_seq);
+
 /* ---- gather, concat (byte movers of the "next" rows: embeddings, KV-cache append) -------- *
  * out[o, j, :] = data[o, indices[j], :] for o < outer, j < nidx, rows of inner_bytes bytes:
  * op::gather (src/include/migraphx/op/gather.hpp:107-150) on a packed tensor whose dimensions

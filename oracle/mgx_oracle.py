@@ -321,6 +321,68 @@ def attention_chain(q, k, v, batch, seq, heads, scale):
     return np.ascontiguousarray(o.transpose(0, 2, 1, 3)).reshape(batch * seq, heads * d)
 
 
+def concat_past_present(present, seqlens, past):
+    """op::concat_past_present::compute (src/include/migraphx/op/concat_past_present.hpp:84-155): the
+    chunk of `seq` rows of every (batch entry, KV head) goes to row seqlens[b] of the cache when seq == 1,
+    to row 0 otherwise; returns the updated cache."""
+    out = np.array(past, copy=True)
+    batch, kvh, seq, _ = present.shape
+    for b in range(batch):
+        pos = int(np.asarray(seqlens).reshape(-1)[b]) if seq == 1 else 0
+        out[b, :, pos:pos + seq, :] = present[b]
+    return out
+
+
+def gqa_rotary_embedding(qkv, seqlens, cos_cache, sin_cache, heads, kv_heads, interleaved=False):
+    """op::gqa_rotary_embedding::compute (src/include/migraphx/op/gqa_rotary_embedding.hpp:72-221) on
+    packed fp16 [batch, heads + 2 kv_heads, seq, head]: x * cos is a half product (truncated),
+    sign * x' * sin stays fp32, the sum is stored as half; V heads pass through."""
+    qkv = np.asarray(qkv, dtype=np.float16)
+    out = qkv.copy()
+    batch, _, seq, head = qkv.shape
+    rot = 2 * cos_cache.shape[1]
+    half = rot // 2
+    i = np.arange(rot)
+    if interleaved:
+        ci, sign, j = (i // 2) % half, np.where(i % 2 == 0, -1.0, 1.0), np.where(i % 2 == 0, i + 1, i - 1)
+    else:
+        ci, sign, j = i % half, np.where(i < half, -1.0, 1.0), (i + half) % rot
+    for b in range(batch):
+        for s_ in range(seq):
+            pos = int(np.asarray(seqlens).reshape(-1)[b]) if seq == 1 else s_
+            c = cos_cache[pos, ci].astype(np.float32)
+            sn = sin_cache[pos, ci].astype(np.float32)
+            x = qkv[b, :heads + kv_heads, s_, :rot].astype(np.float32)
+            t1 = half_trunc(x * c).astype(np.float32)
+            t2 = (sign.astype(np.float32) * x[:, j]) * sn
+            out[b, :heads + kv_heads, s_, :rot] = half_trunc(t1 + t2)
+    return out
+
+
+def gqa_decode_chain(q, k_cache, v_cache, seqlens, scale):
+    """The decode step of GroupQueryAttention as the parser decomposes it
+    (src/onnx/parse_group_query_attention.cpp:184-262) on fp16: q [batch, heads, head] against caches
+    [batch, kv_heads, T, head]; positions beyond seqlens[b] masked with -inf; every operator stores
+    half (truncating); returns [batch, heads * head]."""
+    q = np.asarray(q, dtype=np.float16)
+    batch, heads, head = q.shape
+    kvh, t = k_cache.shape[1], k_cache.shape[2]
+    rep = heads // kvh
+    out = np.zeros((batch, heads * head), dtype=np.float16)
+    for b in range(batch):
+        n = int(np.asarray(seqlens).reshape(-1)[b]) + 1
+        for h in range(heads):
+            kk = k_cache[b, h // rep, :n].astype(np.float64)
+            vv = v_cache[b, h // rep, :n].astype(np.float64)
+            sc = half_trunc(kk @ q[b, h].astype(np.float64))
+            ss = half_trunc(sc.astype(np.float32) * np.float32(np.float16(scale))).astype(np.float32)
+            e = half_trunc(np.exp((ss - ss.max()).astype(np.float32)))
+            tot = e.astype(np.float32).sum(dtype=np.float32)
+            p = half_trunc(e.astype(np.float32) / tot)
+            out[b, h * head:(h + 1) * head] = half_trunc(p.astype(np.float64) @ vv)
+    return out
+
+
 def qlinear_epilogue_half_chain(acc, scale, bias=None, act=None, residual=None):
     """The operators after quant_dot in an fp16 model (src/simplify_qdq.cpp:283-287):
     dequantizelinear in fp32, convert to half, then add(bias), the erf-GELU chain of

@@ -199,3 +199,27 @@ def test_config2_layer_lowers_at_real_dimensions():
     gemms = [l for l in out.splitlines() if "cuda::qgemm" in l]
     assert any("half_type, {384, 768}" in l for l in gemms)
     assert "cuda::gather" in out and "cuda::softmax" in out or "cuda::attention" in out
+
+
+def test_gqa_decode_step_becomes_cache_appends_and_one_attention_kernel():
+    # the parser's decomposition of a GroupQueryAttention node at a decode step (rotary embedding by
+    # the builder, concat_past_present, KV-head broadcast, dot / mul / where / softmax / dot)
+    out = _passes("gqa_decode_d64_f4")
+    assert out.count("cuda::concat_past_present") == 2
+    assert out.count("cuda::gqa_decode_attention[num_heads=8,kv_num_heads=2") == 1
+    assert "cuda::softmax" not in out and "cuda::qgemm" not in out
+    # the rotary embedding's cos / sin rows are gathered at the positions
+    assert out.count("cuda::gather") == 2
+
+
+def test_gqa_prompt_and_unsupported_head_sizes_keep_the_operator_chain():
+    for case in ("gqa_prompt_small", "gqa_decode_small"):
+        out = _passes(case)
+        assert "cuda::gqa_decode_attention" not in out
+        assert out.count("cuda::concat_past_present") == 2 and out.count("cuda::softmax") == 1
+        assert out.count("cuda::qgemm") == 2
+
+
+def test_gqa_rotary_embedding_operator_is_lowered():
+    out = _passes("gqa_decode_rotary_op")
+    assert out.count("cuda::gqa_rotary_embedding[num_heads=4,kv_num_heads=2,interleaved=0]") == 1
