@@ -23,6 +23,7 @@ OBJ = os.path.join(PKG, "build")
 TARGET_LIB = os.path.join(LIB, "libmigraphx_cuda.so")
 CHECK_BIN = os.path.join(BIN, "cuda_target_check")
 RUNNER_LIB = os.path.join(LIB, "libmgx_cuda_runner.so")
+DLOPEN_BIN = os.path.join(BIN, "cuda_dlopen_check")
 SOURCES = ["runtime.cpp", "ops_compute.cpp", "lowering.cpp", "target.cpp"]
 
 
@@ -98,6 +99,14 @@ def build_target(verbose=False, force=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"g++ failed for {check_src}:\n{r.stderr[-6000:]}")
+    # an application that links libmigraphx.so only: both targets arrive through dlopen
+    dl_src = os.path.join(SRC, "dlopen_main.cpp")
+    if os.path.exists(dl_src) and (force or _newer(DLOPEN_BIN, [dl_src] + headers)):
+        cmd = ["g++", dl_src, "-o", DLOPEN_BIN] + flags + [
+            f"-L{mgx_lib}", "-lmigraphx", "-ldl", "-Wl,-rpath,$ORIGIN/../../baseline/_ref/lib"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed for {dl_src}:\n{r.stderr[-6000:]}")
     return TARGET_LIB
 
 

@@ -42,9 +42,10 @@ CONFIG_SIZE = (["c2_layer", "c4_attention_decode", "c4_attention_decode_b16", "c
                 "int4_heavy_tail_m512"] + C2_LINEARS + C3_SWEEP + C4_LINEARS + C5_LINEARS)
 
 
-def _run(case, mode=None):
+def _run(case, mode=None, env=None):
     cmd = [CHECK, "run", case] + ([mode] if mode else [])
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900,
+                       env=dict(os.environ, **env) if env else None)
     lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
     assert lines, r.stdout + r.stderr
     res = json.loads(lines[-1])
@@ -56,6 +57,14 @@ def _run(case, mode=None):
 @pytest.mark.parametrize("case", CASES)
 def test_program_matches_ref(cuda_device, case):
     res = _run(case)
+    assert res.get("pass"), res
+
+
+@pytest.mark.parametrize("case", ["c1_small", "mlp_two_outputs", "attention_f16", "bert_layer_int8", "embed_rope_f16"])
+def test_program_matches_ref_on_two_streams(cuda_device, case):
+    # MIGraphX's schedule pass with the target's two-stream model: record / wait events between
+    # the streams; the un-fused layer has independent branches to spread
+    res = _run(case, env={"MIGRAPHX_CUDA_NSTREAMS": "2", "MIGRAPHX_CUDA_DISABLE_FUSION": "horizontal,attention"})
     assert res.get("pass"), res
 
 
@@ -82,3 +91,19 @@ def test_config1_full_size_bit_exact(cuda_device):
     res = _run("c1")
     assert res.get("pass") and res["exact"], res
     assert res["outputs"][0]["mismatched"] == 0
+
+
+def test_plugin_is_found_by_make_target_through_dlopen(cuda_device):
+    # an application linked with libmigraphx.so only: make_target("cuda") dlopens
+    # libmigraphx_cuda.so.<so-major> from the library path (src/register_target.cpp:56-80)
+    exe = os.path.join(os.path.dirname(CHECK), "cuda_dlopen_check")
+    root = os.path.dirname(os.path.dirname(os.path.dirname(exe)))
+    libs = [os.path.join(root, "amdmigraphx_b200", "lib"), os.path.join(root, "oracle", "_ref", "lib")]
+    env = dict(os.environ, LD_LIBRARY_PATH=":".join(libs + [os.environ.get("LD_LIBRARY_PATH", "")]))
+    ldd = subprocess.run(["ldd", exe], capture_output=True, text=True, env=env).stdout
+    assert "libmigraphx_cuda" not in ldd and "libmigraphx_ref" not in ldd and "libmgx_cuda" not in ldd, ldd
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600, env=env)
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert r.returncode == 0 and lines, r.stdout + r.stderr
+    assert lines[0]["cuda"] == "cuda" and lines[0]["ref"] == "ref" and lines[0]["targets_before"] == 0
+    assert [l["case"] for l in lines[1:]] == ["int8_relu", "fp8_gelu", "int4"] and all(l["pass"] for l in lines[1:])

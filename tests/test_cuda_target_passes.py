@@ -13,9 +13,10 @@ CHECK = os.path.join(ROOT, "amdmigraphx_b200", "bin", "cuda_target_check")
 pytestmark = pytest.mark.skipif(not os.path.exists(CHECK), reason="plug-in driver not built")
 
 
-def _passes(case, mode=None):
+def _passes(case, mode=None, env=None):
     cmd = [CHECK, "passes", case] + ([mode] if mode else [])
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, **env) if env else None)
     assert r.returncode == 0, r.stdout + r.stderr
     return r.stdout
 
@@ -223,3 +224,34 @@ def test_gqa_prompt_and_unsupported_head_sizes_keep_the_operator_chain():
 def test_gqa_rotary_embedding_operator_is_lowered():
     out = _passes("gqa_decode_rotary_op")
     assert out.count("cuda::gqa_rotary_embedding[num_heads=4,kv_num_heads=2,interleaved=0]") == 1
+
+
+def test_two_streams_schedule_parallel_branches_with_events():
+    # MIGRAPHX_CUDA_NSTREAMS=2: MIGraphX's schedule pass (src/schedule.cpp) places the independent
+    # Q / K / V projections on two streams through the target's schedule model; every cross-stream
+    # read is ordered by a record / wait pair
+    out = _passes("bert_layer_int8", env={"MIGRAPHX_CUDA_NSTREAMS": "2",
+                                          "MIGRAPHX_CUDA_DISABLE_FUSION": "horizontal,attention"})
+    assert "cuda::set_stream[stream=1]" in out and "cuda::set_stream[stream=0]" in out
+    records = [l for l in out.splitlines() if "cuda::record_event" in l]
+    waits = [l for l in out.splitlines() if "cuda::wait_event" in l]
+    assert len(records) >= 2 and len(waits) >= len(records)
+    # several streams: evaluated instruction by instruction, no graph submodule
+    assert "cuda::graph_run" not in out
+
+
+def test_make_target_loads_the_plugin_by_name_and_fails_loudly_without_a_device():
+    # an application linked with libmigraphx.so only; the plug-in and the ref target come through
+    # dlopen (src/register_target.cpp:56-80).  Without a GPU the first device call throws: the
+    # target has no CPU fallback.
+    import json
+    import torch
+    exe = os.path.join(os.path.dirname(CHECK), "cuda_dlopen_check")
+    root = os.path.dirname(os.path.dirname(os.path.dirname(exe)))
+    libs = [os.path.join(root, "amdmigraphx_b200", "lib"), os.path.join(root, "oracle", "_ref", "lib")]
+    env = dict(os.environ, LD_LIBRARY_PATH=":".join(libs + [os.environ.get("LD_LIBRARY_PATH", "")]))
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=600, env=env)
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert lines and lines[0] == {"targets_before": 0, "cuda": "cuda", "ref": "ref"}, r.stdout + r.stderr
+    if not torch.cuda.is_available():
+        assert r.returncode == 2 and "cuda target: cudaSetDevice" in lines[-1]["error"]
