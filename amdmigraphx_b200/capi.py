@@ -52,7 +52,10 @@ QGEMM_HALF_MATH = 1
 class QgemmQout(ctypes.Structure):
     _fields_ = [("q", ctypes.c_void_p), ("ldq", ctypes.c_int64), ("stride_q", ctypes.c_int64),
                 ("q_type", ctypes.c_int32), ("scale", ctypes.c_float),
-                ("zero_point", ctypes.c_float), ("reserved", ctypes.c_int32)]
+                ("zero_point", ctypes.c_float), ("flags", ctypes.c_int32), ("lut", ctypes.c_void_p)]
+
+
+QOUT_LUT = 1
 
 
 class W4Desc(ctypes.Structure):
@@ -223,7 +226,7 @@ def transpose_8bit(src):
 
 def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=None,
           residual=None, out_dtype=None, out=None, workspace=None, q_out=None, q_scale=None,
-          q_zero_point=0.0, write_d=True, half_math=False):
+          q_zero_point=0.0, write_d=True, half_math=False, lut=None):
     """quant_dot with the fused epilogue.  a: [M,K] or [B,M,K] int8 / float8_e4m3fn;
     b: [K,N] (B_KN) or [N,K] (B_NK), optionally batched.  q_out (int8 / float8 tensor of the
     output's shape) additionally receives quantizelinear(result, q_scale, q_zero_point);
@@ -265,7 +268,7 @@ def qgemm(a, b, *, b_layout=B_KN, scale=None, scale_mode=None, bias=None, act=No
         q3 = q_out if q_out.dim() == 3 else q_out.unsqueeze(0)
         qd = QgemmQout(q=q3.data_ptr(), ldq=q3.stride(1), stride_q=q3.stride(0),
                        q_type=_dtype_code(q3), scale=float(q_scale), zero_point=float(q_zero_point),
-                       reserved=0)
+                       flags=QOUT_LUT if lut is not None else 0, lut=_ptr(lut))
         code = lib.mgx_cuda_qgemm_ex(ctypes.byref(desc), _ptr(a3), _ptr(b3),
                                      _ptr(d3) if write_d else None, _ptr(scale), _ptr(bias),
                                      _ptr(residual), ctypes.byref(qd), _ptr(workspace),

@@ -309,15 +309,38 @@ __device__ __forceinline__ float trunc_half_nonneg(float v)
     return v < 6.103515625e-5f ? small : big;
 }
 
-__global__ void __launch_bounds__(128, 3) attention_f16_chain_kernel(const attention_params p, const int sp)
+constexpr int ATC_THREADS = 256;
+
+// load_tile for a block of ATC_THREADS threads
+__device__ __forceinline__ void load_tile_256(__half* tile, const __half* g, int64_t ld, int rows_left, int tid)
+{
+#pragma unroll
+    for(int i = 0; i < 2; ++i)
+    {
+        const int c   = tid + i * ATC_THREADS; // 512 chunks of 16 bytes
+        const int row = c >> 3, chunk = c & 7;
+        const bool ok = row < rows_left;
+        cp_async_16(tile_ptr(tile, row, chunk), g + (ok ? row : 0) * ld + chunk * 8, ok);
+    }
+}
+
+// Eight warps per 64 query rows: in the two matrix phases warp (rg, kh) owns the 16 rows of row
+// group rg and half kh of every 64-key tile (its scores / its share of P V, the two shares added
+// through shared memory at the end); in the softmax phase every warp owns 8 whole rows.  Twice the
+// warps of one-warp-per-16-rows at half the accumulator registers each: the kernel is bound by
+// the latency of dependent instructions, which only more resident warps hide.
+// NVMAX: half2 pairs per lane and row the softmax phase holds in registers (keys <= 64 NVMAX).
+template <int NVMAX>
+__global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(const attention_params p, const int sp)
 {
     extern __shared__ __align__(128) uint8_t at_smem[];
     __half* sq     = reinterpret_cast<__half*>(at_smem);
     __half* skv[2] = {sq + AT_BM * AT_D, sq + AT_BM * AT_D + AT_BN * AT_D};
     __half* sc     = sq + AT_BM * AT_D + 2 * AT_BN * AT_D; // [64][sp]
-    float* rowmax  = reinterpret_cast<float*>(sc + AT_BM * sp);
+    float* rowmax  = reinterpret_cast<float*>(sc + AT_BM * sp); // [2][64]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int rg = warp & 3, kh = warp >> 2;
     const int q0   = blockIdx.x * AT_BM;
     const int head = blockIdx.y;
     const int64_t row_base = static_cast<int64_t>(blockIdx.z) * p.seq;
@@ -326,130 +349,147 @@ __global__ void __launch_bounds__(128, 3) attention_f16_chain_kernel(const atten
     const __half* vg = p.v + row_base * p.ldv + head * AT_D;
     const int nblocks = (p.seq + AT_BN - 1) / AT_BN;
 
-    load_tile(sq, qg, p.ldq, p.seq - q0, tid);
-    load_tile(skv[0], kg, p.ldk, p.seq, tid);
+    load_tile_256(sq, qg, p.ldq, p.seq - q0, tid);
+    load_tile_256(skv[0], kg, p.ldk, p.seq, tid);
     cp_async_commit();
 
     // ---- phase 1: scores = half(half(Q K^T) * scale) into shared memory, row maxima
-    uint32_t qa[4][4];
-    float mx[2] = {-FLT_MAX, -FLT_MAX};
-    for(int kb = 0; kb < nblocks; ++kb)
     {
-        const int buf = kb & 1;
-        if(kb + 1 < nblocks)
+        uint32_t qa[4][4];
+        // running maxima of the stored halves, packed: mxh[r] = {max over even keys, max over odd
+        // keys} of row g + 8 r
+        const __half2 lowest = __floats2half2_rn(-65504.0f, -65504.0f);
+        __half2 mxh[2]       = {lowest, lowest};
+        for(int kb = 0; kb < nblocks; ++kb)
         {
-            const int k1 = (kb + 1) * AT_BN;
-            load_tile(skv[buf ^ 1], kg + static_cast<int64_t>(k1) * p.ldk, p.ldk, p.seq - k1, tid);
-            cp_async_commit();
-            cp_async_wait<1>();
-        }
-        else
-            cp_async_wait<0>();
-        __syncthreads();
-        if(kb == 0)
-        {
+            const int buf = kb & 1;
+            if(kb + 1 < nblocks)
+            {
+                const int k1 = (kb + 1) * AT_BN;
+                load_tile_256(skv[buf ^ 1], kg + static_cast<int64_t>(k1) * p.ldk, p.ldk, p.seq - k1, tid);
+                cp_async_commit();
+                cp_async_wait<1>();
+            }
+            else
+                cp_async_wait<0>();
+            __syncthreads();
+            if(kb == 0)
+            {
+#pragma unroll
+                for(int ks = 0; ks < 4; ++ks)
+                    ldmatrix_x4(qa[ks], tile_ptr(sq, rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * ks + (lane >> 4)));
+            }
+            float s[4][4];
+#pragma unroll
+            for(int j = 0; j < 4; ++j)
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
             for(int ks = 0; ks < 4; ++ks)
-                ldmatrix_x4(qa[ks], tile_ptr(sq, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * ks + (lane >> 4)));
-        }
-        float s[8][4];
-#pragma unroll
-        for(int j = 0; j < 8; ++j)
-            s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
-#pragma unroll
-        for(int ks = 0; ks < 4; ++ks)
-        {
-#pragma unroll
-            for(int jp = 0; jp < 4; ++jp)
             {
-                uint32_t kf[4];
-                ldmatrix_x4(kf, tile_ptr(skv[buf], jp * 16 + (lane & 7) + (lane >> 4) * 8, 2 * ks + ((lane >> 3) & 1)));
-                mma_16816(s[2 * jp], qa[ks], kf[0], kf[1]);
-                mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
+#pragma unroll
+                for(int jp = 0; jp < 2; ++jp)
+                {
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, tile_ptr(skv[buf], (kh * 2 + jp) * 16 + (lane & 7) + (lane >> 4) * 8,
+                                             2 * ks + ((lane >> 3) & 1)));
+                    mma_16816(s[2 * jp], qa[ks], kf[0], kf[1]);
+                    mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
+                }
             }
-        }
-        const int kbase = kb * AT_BN;
-        const bool tail = kbase + AT_BN > p.seq;
+            const int kbase = kb * AT_BN + kh * 32;
+            const bool tail = kbase + 32 > p.seq;
+            // half(Q K^T): mantissa cut (a score in the half subnormal range keeps a few more bits:
+            // below 2^-24 absolute, invisible after the exponential); half(score * scale): the
+            // packing conversion itself rounds toward zero, subnormal halves included
 #pragma unroll
-        for(int j = 0; j < 8; ++j)
-        {
-            float x[4];
-#pragma unroll
-            for(int e = 0; e < 4; ++e)
+            for(int j = 0; j < 4; ++j)
             {
-                x[e] = __uint_as_float(__float_as_uint(s[j][e]) & 0xFFFFE000u);
-                x[e] = __uint_as_float(__float_as_uint(x[e] * p.scale) & 0xFFFFE000u);
-                if(tail and kbase + j * 8 + 2 * t + (e & 1) >= p.seq)
-                    x[e] = -65504.0f; // a key that does not exist: its exponential is 0
-                else
-                    mx[e >> 1] = fmaxf(mx[e >> 1], x[e]);
-            }
-            const int col = kbase + j * 8 + 2 * t;
-            *reinterpret_cast<__half2*>(sc + (warp * 16 + g) * sp + col)     = __floats2half2_rn(x[0], x[1]);
-            *reinterpret_cast<__half2*>(sc + (warp * 16 + g + 8) * sp + col) = __floats2half2_rn(x[2], x[3]);
-        }
-        __syncthreads(); // the other tile is overwritten by the next iteration's load
-    }
-    // V's first tile travels while the softmax runs
-    load_tile(skv[0], vg, p.ldv, p.seq, tid);
-    cp_async_commit();
+                float x[4];
 #pragma unroll
-    for(int r = 0; r < 2; ++r)
-    {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                for(int e = 0; e < 4; ++e)
+                    x[e] = __uint_as_float(__float_as_uint(s[j][e]) & 0xFFFFE000u) * p.scale;
+                if(tail)
+                {
+                    // keys that do not exist: the lowest half, whose exponential is 0
+#pragma unroll
+                    for(int e = 0; e < 4; ++e)
+                        if(kbase + j * 8 + 2 * t + (e & 1) >= p.seq)
+                            x[e] = -65504.0f;
+                }
+                const uint32_t w0 = cvt_rz_f16x2(x[0], x[1]), w1 = cvt_rz_f16x2(x[2], x[3]);
+                mxh[0]            = __hmax2(mxh[0], *reinterpret_cast<const __half2*>(&w0));
+                mxh[1]            = __hmax2(mxh[1], *reinterpret_cast<const __half2*>(&w1));
+                const int col     = kbase + j * 8 + 2 * t;
+                *reinterpret_cast<uint32_t*>(sc + (rg * 16 + g) * sp + col)     = w0;
+                *reinterpret_cast<uint32_t*>(sc + (rg * 16 + g + 8) * sp + col) = w1;
+            }
+            __syncthreads(); // the other tile is overwritten by the next iteration's load
+        }
+        // V's first tile travels while the softmax runs
+        load_tile_256(skv[0], vg, p.ldv, p.seq, tid);
+        cp_async_commit();
+#pragma unroll
+        for(int r = 0; r < 2; ++r)
+        {
+            const float2 m2 = __half22float2(mxh[r]);
+            float mx        = fmaxf(m2.x, m2.y);
+            mx              = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx              = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            if(t == 0)
+                rowmax[kh * AT_BM + rg * 16 + g + r * 8] = mx;
+        }
     }
-    if(t == 0)
-    {
-        rowmax[warp * 16 + g]     = mx[0];
-        rowmax[warp * 16 + g + 8] = mx[1];
-    }
-    __syncwarp();
+    __syncthreads();
 
-    // ---- phase 2: ref_softmax on this warp's 16 rows, in place: e = half(exp(x - max)),
-    // sum over the stored halves in fp32, p = half(e / sum).  exp through ex2.approx (relative error
-    // ~1e-6 against the 5e-4 spacing of the halves it is truncated to), the quotient from one
-    // reciprocal per row and a remainder correction (correctly rounded before the truncation).
-    const int nv = nblocks; // half2 pairs per lane and row: keys / 64
-    constexpr float log2e = 1.4426950408889634f;
+    // ---- phase 2: ref_softmax on this warp's 8 rows, in place: e = half(exp(x - max)), sum over
+    // the stored halves in fp32, p = half(e / sum).  exp through ex2.approx (relative error ~1e-6
+    // against the 5e-4 spacing of the halves it is truncated to), the quotient from one reciprocal
+    // per row and a remainder correction (correctly rounded before the truncation).
+    {
+        const int nv = nblocks; // half2 pairs per lane and row: keys / 64
+        constexpr float log2e = 1.4426950408889634f;
 #pragma unroll 1
-    for(int r = 0; r < 16; ++r)
-    {
-        __half* rowp  = sc + (warp * 16 + r) * sp;
-        const float m = rowmax[warp * 16 + r];
-        float e[2 * (AT_CHAIN_MAX_SEQ / 64)];
-        float sum = 0.0f;
-#pragma unroll
-        for(int i = 0; i < AT_CHAIN_MAX_SEQ / 64; ++i)
+        for(int r = 0; r < 8; ++r)
         {
-            if(i < nv)
+            const int row = warp * 8 + r;
+            __half* rowp  = sc + row * sp;
+            const float m = fmaxf(rowmax[row], rowmax[AT_BM + row]);
+            // the packing conversion rounds toward zero (subnormal halves included); the sum runs
+            // over the stored halves
+            float2 e[NVMAX];
+            float sum = 0.0f;
+#pragma unroll
+            for(int i = 0; i < NVMAX; ++i)
             {
-                const float2 x = __half22float2(*reinterpret_cast<const __half2*>(rowp + i * 64 + lane * 2));
-                e[2 * i]     = trunc_half_nonneg(fast_exp2((x.x - m) * log2e));
-                e[2 * i + 1] = trunc_half_nonneg(fast_exp2((x.y - m) * log2e));
-                sum += e[2 * i] + e[2 * i + 1];
+                if(i < nv)
+                {
+                    const float2 x   = __half22float2(*reinterpret_cast<const __half2*>(rowp + i * 64 + lane * 2));
+                    const uint32_t h = cvt_rz_f16x2(fast_exp2((x.x - m) * log2e), fast_exp2((x.y - m) * log2e));
+                    e[i]             = __half22float2(*reinterpret_cast<const __half2*>(&h));
+                    sum += e[i].x + e[i].y;
+                }
             }
-        }
 #pragma unroll
-        for(int o = 16; o > 0; o >>= 1)
-            sum += __shfl_xor_sync(0xffffffffu, sum, o);
-        const float rcp = __frcp_rn(sum);
+            for(int o = 16; o > 0; o >>= 1)
+                sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float rcp = __frcp_rn(sum);
 #pragma unroll
-        for(int i = 0; i < AT_CHAIN_MAX_SEQ / 64; ++i)
-        {
-            if(i < nv)
+            for(int i = 0; i < NVMAX; ++i)
             {
-                float a = e[2 * i] * rcp, b = e[2 * i + 1] * rcp;
-                a       = __fmaf_rn(__fmaf_rn(-a, sum, e[2 * i]), rcp, a);
-                b       = __fmaf_rn(__fmaf_rn(-b, sum, e[2 * i + 1]), rcp, b);
-                *reinterpret_cast<__half2*>(rowp + i * 64 + lane * 2) =
-                    __floats2half2_rn(trunc_half_nonneg(a), trunc_half_nonneg(b));
+                if(i < nv)
+                {
+                    float a = e[i].x * rcp, b = e[i].y * rcp;
+                    a       = __fmaf_rn(__fmaf_rn(-a, sum, e[i].x), rcp, a);
+                    b       = __fmaf_rn(__fmaf_rn(-b, sum, e[i].y), rcp, b);
+                    *reinterpret_cast<uint32_t*>(rowp + i * 64 + lane * 2) = cvt_rz_f16x2(a, b);
+                }
             }
         }
     }
-    __syncwarp();
+    __syncthreads();
 
-    // ---- phase 3: O = P V with the half probabilities as A fragments straight from shared memory
+    // ---- phase 3: O = P V with the half probabilities as A fragments straight from shared
+    // memory; this warp's half of every tile's keys
     float o[8][4];
 #pragma unroll
     for(int j = 0; j < 8; ++j)
@@ -460,7 +500,7 @@ __global__ void __launch_bounds__(128, 3) attention_f16_chain_kernel(const atten
         if(kb + 1 < nblocks)
         {
             const int k1 = (kb + 1) * AT_BN;
-            load_tile(skv[buf ^ 1], vg + static_cast<int64_t>(k1) * p.ldv, p.ldv, p.seq - k1, tid);
+            load_tile_256(skv[buf ^ 1], vg + static_cast<int64_t>(k1) * p.ldv, p.ldv, p.seq - k1, tid);
             cp_async_commit();
             cp_async_wait<1>();
         }
@@ -468,10 +508,11 @@ __global__ void __launch_bounds__(128, 3) attention_f16_chain_kernel(const atten
             cp_async_wait<0>();
         __syncthreads();
 #pragma unroll
-        for(int ks = 0; ks < 4; ++ks)
+        for(int k2 = 0; k2 < 2; ++k2)
         {
+            const int ks = kh * 2 + k2;
             uint32_t pa[4];
-            ldmatrix_x4(pa, sc + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * sp + kb * AT_BN + ks * 16 +
+            ldmatrix_x4(pa, sc + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * sp + kb * AT_BN + ks * 16 +
                                 (lane >> 4) * 8);
 #pragma unroll
             for(int jp = 0; jp < 4; ++jp)
@@ -484,11 +525,35 @@ __global__ void __launch_bounds__(128, 3) attention_f16_chain_kernel(const atten
         }
         __syncthreads();
     }
+    // the two key halves are added in a fixed order: the upper half's partial sums go through
+    // shared memory (the Q / K / V tiles are free now: 16 KB of the 24 KB they take)
+    float* red = reinterpret_cast<float*>(at_smem);
+    if(kh == 1)
+    {
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+#pragma unroll
+            for(int r = 0; r < 2; ++r)
+                *reinterpret_cast<float2*>(red + (rg * 16 + g + r * 8) * AT_D + j * 8 + 2 * t) =
+                    make_float2(o[j][2 * r], o[j][2 * r + 1]);
+    }
+    __syncthreads();
+    if(kh == 1)
+        return;
+#pragma unroll
+    for(int j = 0; j < 8; ++j)
+#pragma unroll
+        for(int r = 0; r < 2; ++r)
+        {
+            const float2 u = *reinterpret_cast<const float2*>(red + (rg * 16 + g + r * 8) * AT_D + j * 8 + 2 * t);
+            o[j][2 * r] += u.x;
+            o[j][2 * r + 1] += u.y;
+        }
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
 #pragma unroll
     for(int r = 0; r < 2; ++r)
     {
-        const int row = q0 + warp * 16 + g + r * 8;
+        const int row = q0 + rg * 16 + g + r * 8;
         if(row >= p.seq)
             continue;
 #pragma unroll
@@ -563,13 +628,21 @@ extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, co
     if(d->seq <= AT_CHAIN_MAX_SEQ and (d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0)
     {
         const int sp    = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
-        const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + AT_BM * 4;
-        // opted in once, to the size the longest supported sequence needs
-        constexpr int max_bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * (AT_CHAIN_MAX_SEQ + 8)) * 2 + AT_BM * 4;
-        const int rc = ensure_smem_optin(reinterpret_cast<const void*>(attention_f16_chain_kernel), max_bytes);
-        if(rc != MGX_OK)
-            return rc;
-        attention_f16_chain_kernel<<<grid, 128, bytes, stream>>>(p, sp);
+        const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + 2 * AT_BM * 4;
+        // opted in once per instantiation, to the size its longest sequence needs
+        auto launch = [&](auto kernel, int max_seq) {
+            const int max_bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * (max_seq + 8)) * 2 + 2 * AT_BM * 4;
+            const int rc        = ensure_smem_optin(reinterpret_cast<const void*>(kernel), max_bytes);
+            if(rc != MGX_OK)
+                return rc;
+            kernel<<<grid, ATC_THREADS, bytes, stream>>>(p, sp);
+            return static_cast<int>(cudaGetLastError());
+        };
+        if(d->seq <= 384)
+            return launch(attention_f16_chain_kernel<6>, 384);
+        if(d->seq <= 512)
+            return launch(attention_f16_chain_kernel<8>, 512);
+        return launch(attention_f16_chain_kernel<AT_CHAIN_MAX_SEQ / 64>, AT_CHAIN_MAX_SEQ);
     }
     else
         attention_f16_kernel<<<grid, 128, 0, stream>>>(p);

@@ -323,7 +323,7 @@ int launch_gqa_decode(const gqa_decode_params& p, int batch, int nsplit, cudaStr
         return MGX_E_TOO_LARGE;
     auto* kernel = gqa_decode_kernel<D, FACT>;
     static size_t opted = 0;
-    if(smem > 48 * 1024 and smem > opted)
+    if(opted == 0) // (the static arrays count toward the 48 KB a kernel gets without opting in)
     {
         const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if(e != cudaSuccess)
@@ -348,11 +348,12 @@ int launch_gqa_decode(const gqa_decode_params& p, int batch, int nsplit, cudaStr
 } // namespace mgx
 
 namespace mgx {
-// splits: enough CTAs for the 148 SMs, at most the portable cluster size, at least 64 positions each
+// splits: about four CTAs per SM (the loads in flight that saturate HBM), at most the portable
+// cluster size, at least 64 positions each
 static int gqa_decode_splits(int64_t batch, int64_t kv_heads, int64_t cache_seq)
 {
     int nsplit = 1;
-    while(nsplit < 8 and batch * kv_heads * nsplit < 148 and cache_seq / (2 * nsplit) >= 64)
+    while(nsplit < 8 and batch * kv_heads * nsplit < 4 * 148 and cache_seq / (2 * nsplit) >= 64)
         nsplit *= 2;
     return nsplit;
 }

@@ -59,6 +59,7 @@ struct qgemm_params
     // fp16 results whose epilogue operators run in half (MGX_QGEMM_HALF_MATH): 0xFFFFE000, the
     // mantissa cut that truncates an fp32 value in the normal half range to half; else all ones
     uint32_t hmask;
+    const uint8_t* lut; // activation + quantizelinear of every half as a table (MGX_QOUT_LUT), or null
     float act_rcp; // erf-GELU: 1 / the constant x is divided by (sqrt 2, or its half value)
 };
 
@@ -351,8 +352,8 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     const int64_t dstep = 8 * p.ldd, qstep = 8 * p.ldq;
     // 5 = 2 and 6 = 4 with accumulators below 2^24 (and the mantissa-cut quantizelinear input)
     const bool has_res = MODE == 1 ? p.residual != nullptr : MODE == 3;
-    const bool has_q   = MODE == 1 ? p.Dq != nullptr : (MODE == 3 or MODE == 4 or MODE == 6);
-    const bool wr      = MODE == 1 ? p.write_d != 0 : (MODE != 4 and MODE != 6);
+    const bool has_q   = MODE == 1 ? p.Dq != nullptr : (MODE == 3 or MODE == 4 or MODE == 6 or MODE == 7);
+    const bool wr      = MODE == 1 ? p.write_d != 0 : (MODE != 4 and MODE != 6 and MODE != 7);
     const bool acc24   = MODE >= 5 ? true : p.acc24 != 0;
     const bool q_mask  = MODE == 6 ? true : (has_q and p.q_mask != 0);
     // saturation before rounding: bounds are integers, so round-to-nearest stays inside
@@ -390,6 +391,18 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
 #pragma unroll
             for(int j = 0; j < 4; ++j)
                 v[j] = __fmul_rn(__uint_as_float(wv[j]), sc[j]);
+        }
+        if constexpr(MODE == 7)
+        {
+            // the half the chain holds after dequantizelinear and bias (the packing conversion
+            // truncates, subnormal halves included) indexes the table of activation + quantizelinear
+            const uint32_t i01 = cvt_rz_f16x2(__fadd_rn(hcut(v[0], hmask), bi[0]), __fadd_rn(hcut(v[1], hmask), bi[1]));
+            const uint32_t i23 = cvt_rz_f16x2(__fadd_rn(hcut(v[2], hmask), bi[2]), __fadd_rn(hcut(v[3], hmask), bi[3]));
+            const uint32_t b0 = __ldg(p.lut + (i01 & 0xFFFFu)), b1 = __ldg(p.lut + (i01 >> 16));
+            const uint32_t b2 = __ldg(p.lut + (i23 & 0xFFFFu)), b3 = __ldg(p.lut + (i23 >> 16));
+            *reinterpret_cast<uint32_t*>(qdst) = b0 | (b1 << 8) | (b2 << 16) | (b3 << 24);
+            qdst += qstep;
+            continue;
         }
         if constexpr(std::is_same<OutT, __half>::value)
         {
@@ -785,6 +798,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
                            : (m_res and m_q and m_wr)         ? 3
                            : (not m_res and m_q and not m_wr) ? ((m_24 and p.q_mask != 0) ? 6 : 4)
                                                               : 1;
+        if(std::is_same<OutT, __half>::value and p.lut != nullptr and p.fast != 0 and not m_res and m_q and not m_wr)
+        {
+            if constexpr(std::is_same<OutT, __half>::value)
+                MGX_EPI_MODE(MGX_ACT_NONE, 7);
+        }
+        else
         switch(std::is_same<OutT, int32_t>::value ? MGX_ACT_NONE : p.act)
         {
         case MGX_ACT_RELU: MGX_EPILOGUE(MGX_ACT_RELU); break;
@@ -824,6 +843,7 @@ struct qout_args
     float zp        = 0.0f;
     int fp8         = 0;
     int write_d     = 1;
+    const void* lut = nullptr;
 };
 
 static int encode_operand_map(CUtensorMap* map, const void* base, int64_t k, int64_t rows,
@@ -910,6 +930,8 @@ static int launch_qgemm(const mgx_qgemm_desc& d, const void* A, const void* B, v
     p.hmask      = (std::is_same<OutT, __half>::value and (d.flags & MGX_QGEMM_HALF_MATH) != 0) ? 0xFFFFE000u
                                                                                                  : 0xFFFFFFFFu;
     p.act_rcp    = p.hmask != 0xFFFFFFFFu ? 1.0f / 1.4140625f : 0.70710678118654752440f;
+    // the table stands for activation + quantizelinear of a half: only where the chain holds one
+    p.lut        = (p.hmask != 0xFFFFFFFFu and qo.fp8 == 0) ? static_cast<const uint8_t*>(qo.lut) : nullptr;
     p.acc24      = (IS_INT and d.K < 1024) ? 1 : 0; // |a b| <= 2^14 for int8 operands
     // |v| < 2^-14 (half subnormals) divided by a scale >= 2^-12 stays below 1/4: quantises to zero
     // whatever its low bits; no zero point may shift the rounding boundary
@@ -1046,6 +1068,7 @@ extern "C" int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* d, const void* A, const v
         qo.zp       = q->zero_point;
         qo.fp8      = q->q_type == MGX_FP8_E4M3FN ? 1 : 0;
         qo.write_d  = D != nullptr ? 1 : 0;
+        qo.lut      = (q->flags & MGX_QOUT_LUT) != 0 ? q->lut : nullptr;
     }
     else if(D == nullptr)
         return MGX_E_INVALID_ARG;

@@ -63,8 +63,10 @@ test_case c2_encoder(std::size_t batch, std::size_t layers)
     t.ref_simplify_qdq = true;
     t.rtol = 2e-2;
     t.atol = 1e-2;
-    // quantizer flips behind the fused attention and the fp32 LayerNorm sums (see test_case)
-    t.outlier_fraction = 2e-3;
+    // quantizer flips behind the fused attention and the fp32 LayerNorm sums (see test_case): a layer
+    // has four activation quantisers, and a flipped int8 value moves a few results of every layer
+    // after it by a quantisation step, so the allowance grows with the depth
+    t.outlier_fraction = 2e-3 * static_cast<double>(layers);
     t.outlier_atol     = 0.1;
     return t;
 }

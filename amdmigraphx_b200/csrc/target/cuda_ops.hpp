@@ -258,10 +258,13 @@ struct op_qgemm
     // fp16 result whose epilogue operators (bias add, activation, residual add) are half operators
     // in the program (the convert to half directly follows dequantizelinear): each is rounded to half
     bool half_math = false;
+    // an extra input after the residual: 65536 bytes, activation + quantizelinear of every half
+    // (half_math with the quantised tensor as the only result; see MGX_QOUT_LUT)
+    bool has_lut = false;
     template <class Self, class F>
     static auto reflect(Self& self, F f)
     {
-        return pack(f(self.half_math, "half_math"), f(self.scale_mode, "scale_mode"), f(self.act, "act"),
+        return pack(f(self.half_math, "half_math"), f(self.has_lut, "has_lut"), f(self.scale_mode, "scale_mode"), f(self.act, "act"),
                     f(self.has_bias, "has_bias"), f(self.has_residual, "has_residual"),
                     f(self.b_nk, "b_nk"), f(self.has_workspace, "has_workspace"),
                     f(self.out_type, "out_type"), f(self.q_type, "q_type"),

@@ -590,6 +590,16 @@ struct lowerer
             }
         }
         const bool only_q = qz != m.end() and last->outputs().size() == 1;
+        // fp16 chain whose only result is the int8 tensor: activation + quantizelinear of the half
+        // the chain holds after the bias is a function of 16 bits - one table look-up in the epilogue
+        if(only_q and op.half_math and not op.has_residual and op.q_type == static_cast<int>(shape::int8_type) and
+           (op.act == MGX_ACT_GELU_ERF or op.act == MGX_ACT_RELU))
+        {
+            op.has_lut = true;
+            auto lut   = m.add_literal(act_quant_table(op.act, op.q_scale, op.q_zp));
+            // the table sits after the residual slot and before the workspace
+            args.insert(workspace != m.end() ? args.end() - 1 : args.end(), lut);
+        }
         if(only_q)
         {
             op.write_d = false;
@@ -620,6 +630,41 @@ struct lowerer
         consume(rep);
         if(qz != m.end())
             consume(m.replace_instruction(qz, op_second_output{}, rep, args[args.size() - 2]));
+    }
+
+    // int8 quantizelinear(activation(x), scale, zero point) for every half x, indexed by x's bit
+    // pattern, evaluated with migraphx::half exactly as a chain of half operators on the ref target
+    // evaluates it: every operator computes in fp32 and stores (truncates to) half
+    // (erf-GELU: src/op/builder/gelu.cpp:58-74; quantizelinear: src/include/migraphx/op/quantizelinear.hpp:71-108)
+    static literal act_quant_table(int act, float q_scale, float q_zp)
+    {
+        auto h = [](float f) { return static_cast<float>(migraphx::half(f)); };
+        std::vector<int8_t> table(65536);
+        const float sqrt2 = h(static_cast<float>(M_SQRT2));
+        for(std::uint32_t bits = 0; bits < 65536; ++bits)
+        {
+            const auto b16 = static_cast<std::uint16_t>(bits);
+            migraphx::half xh;
+            std::memcpy(&xh, &b16, sizeof(b16));
+            const float x = static_cast<float>(xh);
+            float v       = x;
+            if(act == MGX_ACT_GELU_ERF)
+            {
+                const float mh = h(x * 0.5f);
+                const float dv = h(x / sqrt2);
+                const float e1 = h(h(std::erf(dv)) + 1.0f);
+                v              = h(mh * e1);
+            }
+            else if(act == MGX_ACT_RELU)
+                v = std::max(x, 0.0f);
+            else if(act == MGX_ACT_GELU_TANH or act == MGX_ACT_SILU)
+                MIGRAPHX_THROW("cuda: no table form of this activation");
+            // quantizelinear of a half tensor: the quotient is a half, then nearbyint + zero point, saturated
+            const double q = static_cast<double>(std::nearbyint(h(v / q_scale))) + static_cast<double>(q_zp);
+            // std::max(lowest, std::min(max, q)) as the reference writes it: a NaN compares false and gives max
+            table[bits] = static_cast<int8_t>(std::max(-128.0, std::min(127.0, q)));
+        }
+        return literal{shape{shape::int8_type, {65536}}, table.data()};
     }
 
     // ---------------------------------------------------------------- weight-only int4

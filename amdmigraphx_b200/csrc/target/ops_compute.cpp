@@ -179,7 +179,7 @@ argument op_pack_int4::compute(context& ctx, const shape&, const std::vector<arg
 shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
 {
     const bool dual          = q_type != 0 and write_d;
-    const std::size_t expect = 3 + (scale_mode != MGX_SCALE_NONE) + has_bias + has_residual + has_workspace + dual;
+    const std::size_t expect = 3 + (scale_mode != MGX_SCALE_NONE) + has_bias + has_residual + has_lut + has_workspace + dual;
     check_shapes{inputs, *this}.has(expect);
     const auto& a = inputs[0];
     const auto& b = inputs[1];
@@ -216,6 +216,7 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
     const argument* scale  = scale_mode != MGX_SCALE_NONE ? &args[i++] : nullptr;
     const argument* bias   = has_bias ? &args[i++] : nullptr;
     const argument* resid  = has_residual ? &args[i++] : nullptr;
+    const argument* lut    = has_lut ? &args[i++] : nullptr;
     const argument* wspace = has_workspace ? &args[i++] : nullptr;
     const bool dual        = q_type != 0 and write_d;
     const bool only_q      = q_type != 0 and not write_d;
@@ -296,6 +297,13 @@ argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argumen
         qo.q_type     = mgx_type(static_cast<shape::type_t>(q_type));
         qo.scale      = q_scale;
         qo.zero_point = q_zp;
+        if(lut != nullptr)
+        {
+            if(lut->get_shape().bytes() != 65536)
+                MIGRAPHX_THROW("cuda::qgemm: the activation / quantizelinear table must hold 65536 bytes");
+            qo.flags = MGX_QOUT_LUT;
+            qo.lut   = lut->data();
+        }
     }
     check_mgx(mgx_cuda_qgemm_ex(&d, args[0].data(), args[1].data(), only_q ? nullptr : out.data(),
                                 scale != nullptr ? reinterpret_cast<const float*>(scale->data()) : nullptr,

@@ -464,6 +464,56 @@ def secondary_measurements(dev, peaks, failures):
 
 
 # ------------------------------------------------------------------ own arm
+def tp_decode_secondary(dev, world, rank, batch=16, reps=20, nlayers=3):
+    """Config 5's tensor parallelism on the ranks of this run: the int4 weight-only linears of a
+    Llama-2-70B-shaped decoder layer (hidden 8192, 64 query / 8 KV heads of 128, FFN 28672, group 128)
+    at batch 16, QKV and gate/up split by output columns, o_proj and down_proj by input rows with one
+    mgx_cuda_all_reduce (NCCL, in place, on the compute stream) after each.  Every rank calls this;
+    returns time per layer (max over ranks) and the packed-weight bytes all ranks stream per second."""
+    import torch
+    import torch.distributed as dist
+    from amdmigraphx_b200 import capi
+    ids = [capi.Communicator.make_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0, device=dev)
+    comm = capi.Communicator(ids[0], world, rank)
+    hid, kv, ffn, group = 8192, 2048, 28672, 128
+    shapes = [((hid + kv) // world, hid, False), (hid, hid // world, True),
+              (2 * ffn // world, hid, False), (hid, ffn // world, True)]
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(1 + rank)
+    layers = [[(torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device=dev, generator=gen),
+                (torch.rand(n, k // group, device=dev, generator=gen) * 0.015 + 0.005).half(), red)
+               for (n, k, red) in shapes] for _ in range(nlayers)]
+    xs = {k: torch.randn(batch, k, device=dev, dtype=torch.float16) for (_, k, _) in shapes}
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+    wbytes = sum(n * k // 2 + n * (k // group) * 2 for (n, k, _) in shapes)
+
+    def one_layer(lw):
+        for (bp, sc, red) in lw:
+            y = capi.w4a16(xs[bp.shape[1] * 2], bp, sc, group=group, workspace=ws)
+            if red:
+                comm.all_reduce_(y)
+
+    for i in range(3):
+        one_layer(layers[i % nlayers])
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(reps):
+        one_layer(layers[i % nlayers])
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps * 1e3], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.item())
+    comm.destroy()
+    return {"workload": "llama-2-70b-shaped int4 decode linears of one layer, tensor parallel over the run's GPUs "
+                        "(column / row split, two all-reduces per layer)",
+            "batch": batch, "us_per_layer": us, "weight_gbs_all_ranks": world * wbytes / us / 1e3,
+            "all_reduce_bytes": batch * hid * 2, "launches_per_layer": "4 linears (3 kernels each) + 2 all-reduces"}
+
+
 def read_traffic():
     """DRAM bytes per launch of the dominant kernel from the machine-readable record written next
     to its ncu summary (profiles/qgemm_traffic.json); None when there is no record."""
@@ -590,6 +640,13 @@ def run_own_arm(args):
     g_n = chains[0].gemms_per_step()
     status = capi.device_status()
     clocks = sampler.stop() if sampler is not None else None
+    tp = None
+    if world > 1 and not args.no_secondary:
+        # after the timed regions and the clock samples of the headline
+        try:
+            tp = tp_decode_secondary(dev, world, rank)
+        except Exception as e:  # the secondary figure must not take the headline down with it
+            tp = {"error": f"{type(e).__name__}: {e}"}
 
     if rank == 0:
         peaks, basis = measured_peaks()
@@ -637,6 +694,8 @@ def run_own_arm(args):
         }
         if world == 1 and not args.no_secondary:
             line["secondary"] = secondary_measurements(dev, peaks, failures)
+        if tp is not None:
+            line["secondary"] = {"tp_int4_decode_llama70b": tp}
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = {k: v for k, v in cpu_reference(3, 1, 20.0).items()
                                     if k in ("value", "unit", "cores", "kind", "sample")}
@@ -696,7 +755,7 @@ def run_case(a):
             qo = torch.empty((1, M, N), dtype=torch.int8, device=dev) if a.qout else None
             fn = lambda: capi.qgemm(A, B, b_layout=capi.B_NK, scale=scale, bias=bias, act=act, out=out,  # noqa: E731
                                     residual=res, q_out=qo, q_scale=0.02 if a.qout else None,
-                                    write_d=not a.qonly)
+                                    write_d=not a.qonly, half_math=a.half_math)
         work, unit = 2.0 * M * N * K, "TOPS"
     elif a.case == "quantize":
         x = torch.randn((M, N), device=dev, dtype=torch.float16 if a.out == "f16" else torch.float32)
@@ -734,13 +793,13 @@ def run_case(a):
     for _ in range(a.case_warmup):
         fn()
     torch.cuda.synchronize()
-    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s.record()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
     for _ in range(a.iters):
         fn()
-    e.record()
+    ev1.record()
     torch.cuda.synchronize()
-    ms = s.elapsed_time(e) / a.iters
+    ms = ev0.elapsed_time(ev1) / a.iters
     rate = work / (ms * 1e-3) / (1e12 if unit == "TOPS" else 1e9)
     print(json.dumps({"case": a.case, "m": M, "n": N, "k": K, "us_per_launch": ms * 1e3,
                       "rate": rate, "unit": unit, "device_status": capi.device_status()}))
@@ -768,6 +827,8 @@ def main():
     ap.add_argument("--out", default="f16", choices=["f16", "f32", "raw"])
     ap.add_argument("--residual", action="store_true", help="--case: add a residual of the output type")
     ap.add_argument("--qout", action="store_true", help="--case: also write the int8 quantizelinear of the output")
+    ap.add_argument("--half-math", action="store_true",
+                    help="--case: fp16 output whose epilogue operators round to half one by one (fp16 models)")
     ap.add_argument("--qonly", action="store_true", help="--case: with --qout, write only the quantised output")
     args = ap.parse_args()
     if args.case is not None:

@@ -396,8 +396,17 @@ typedef struct mgx_qgemm_qout
     int32_t q_type;     /* MGX_I8 | MGX_FP8_E4M3FN                */
     float scale;        /* > 0                                    */
     float zero_point;   /* integral for MGX_I8                    */
-    int32_t reserved;
+    int32_t flags;      /* 0 | MGX_QOUT_LUT                       */
+    /* MGX_QOUT_LUT (fp16 result with MGX_QGEMM_HALF_MATH, q is the only output, no residual): the
+     * activation and the quantizelinear are one table look-up.  lut[h] is the quantised byte for the
+     * value whose fp16 bit pattern is h after dequantizelinear and bias: 65536 bytes in device memory
+     * that the caller filled with activation + quantizelinear of every half (what a chain of fp16
+     * operators makes of it, desc->act included).  The table is used where the launch takes the
+     * epilogue's vector path (M a multiple of 128, N of 16, aligned rows), otherwise the same values
+     * are computed.  Read only when the flag is set. */
+    const void* lut;
 } mgx_qgemm_qout;
+#define MGX_QOUT_LUT 1
 
 MGX_API int mgx_cuda_qgemm_ex(const mgx_qgemm_desc* desc,
                               const void* A,

@@ -38,7 +38,7 @@ C4_LINEARS = [f"c4_m{m}_n{n}_k{k}" for m in (1, 16, 512)
 C5_LINEARS = [f"c5_m16_n{n}_k{k}" for (n, k) in ((8192, 8192), (1024, 8192), (28672, 8192), (8192, 28672),
                                                   (4096, 8192), (512, 8192), (14336, 8192), (8192, 14336),
                                                   (8192, 4096))]
-CONFIG_SIZE = (["c2_layer", "c4_attention_decode", "c4_attention_decode_b16", "c5_attention_decode_tp8", "int8_8192", "int8_8192_raw", "int4_heavy_tail_m1", "int4_heavy_tail_m16",
+CONFIG_SIZE = (["c2_layer", "c2_layers2", "c4_attention_decode", "c4_attention_decode_b16", "c5_attention_decode_tp8", "int8_8192", "int8_8192_raw", "int4_heavy_tail_m1", "int4_heavy_tail_m16",
                 "int4_heavy_tail_m512"] + C2_LINEARS + C3_SWEEP + C4_LINEARS + C5_LINEARS)
 
 

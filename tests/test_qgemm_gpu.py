@@ -331,3 +331,39 @@ def test_int8_half_math_epilogue_matches_half_operator_chain(cuda_device, M, N, 
         np.testing.assert_allclose(g.astype(np.float32), r.astype(np.float32), rtol=2e-3, atol=1e-6)
     else:
         assert not diff.any()
+
+
+@pytest.mark.parametrize("M,N,K,act", [(256, 320, 256, "gelu_erf"), (128, 64, 768, "relu"), (384, 3072, 768, "gelu_erf")])
+def test_int8_lut_epilogue_is_the_half_operator_chain(cuda_device, M, N, K, act):
+    """fp16 model whose linear feeds only the next quantizelinear: activation + quantizelinear of the
+    half the chain holds after the bias is one look-up in a 65536-entry table (MGX_QOUT_LUT).  With a
+    table made by the reference's arithmetic the int8 tensor is the operator chain's bit for bit; the
+    arithmetic epilogue differs from it only where its erf lands in the neighbouring half."""
+    import warnings
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(M + N + 1)
+    a = rng.integers(-127, 128, size=(M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(N, K), dtype=np.int8)
+    scale = (2.0 * rng.uniform(0.4, 1.2, size=N) / (127.0 * np.sqrt(K))).astype(np.float32)
+    bias = rng.normal(0, 0.2, size=N).astype(np.float16)
+    q_scale = np.float16(0.03)
+    halves = np.arange(65536, dtype=np.uint32).astype(np.uint16).view(np.float16)
+    with warnings.catch_warnings(), np.errstate(all="ignore"):
+        warnings.simplefilter("ignore")
+        acted = O.qlinear_epilogue_half_chain(halves.astype(np.float32), np.float32(1.0), None, act)
+        table = O.quantizelinear(acted, np.array([q_scale]), None, "int8")
+    t = lambda v: torch.from_numpy(np.ascontiguousarray(v)).to(cuda_device)  # noqa: E731
+    outs = []
+    for lut in (None, t(table)):
+        q = torch.empty((M, N), dtype=torch.int8, device=cuda_device)
+        capi.qgemm(t(a), t(b), b_layout=capi.B_NK, scale=t(scale), bias=t(bias.astype(np.float32)), act=act,
+                   out_dtype=torch.float16, half_math=True, q_out=q, q_scale=float(q_scale), write_d=False, lut=lut)
+        torch.cuda.synchronize()
+        outs.append(q.cpu().numpy())
+    v = O.qlinear_epilogue_half_chain(O.quant_dot_int8(a, b.T), scale[None, :], bias, act)
+    ref = O.quantizelinear(v, np.array([q_scale]), None, "int8")
+    np.testing.assert_array_equal(outs[1], ref)
+    d = np.abs(outs[0].astype(np.int32) - ref.astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 2e-3
+    assert capi.device_status() == 0
