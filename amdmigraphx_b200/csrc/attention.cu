@@ -585,6 +585,238 @@ __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(con
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The operator chain's roundings without a score buffer: three passes over the keys, each
+// recomputing the 16 x 64 score tile on the tensor cores (the tensor pipe is nearly idle in this
+// kernel, the instruction slots of the element-wise work are what it is short of):
+//   pass 0: row maxima of the half scores;
+//   pass 1: sum over e = half(exp(x - max));
+//   pass 2: p = half(e / sum) straight into the A fragments of P V.
+// Every value is rounded exactly as in attention_f16_chain_kernel; only the order of the fp32
+// additions of the row sum differs.  40 KB of static shared memory (Q, two K and two V tiles) and
+// no limit on the number of keys.
+__global__ void __launch_bounds__(128, 4) attention_f16_chain3_kernel(const attention_params p)
+{
+    __shared__ __align__(128) __half sq[AT_BM * AT_D];
+    __shared__ __align__(128) __half sk[2][AT_BN * AT_D];
+    __shared__ __align__(128) __half sv[2][AT_BN * AT_D];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int q0   = blockIdx.x * AT_BM;
+    const int head = blockIdx.y;
+    const int64_t row_base = static_cast<int64_t>(blockIdx.z) * p.seq;
+    const __half* qg = p.q + (row_base + q0) * p.ldq + head * AT_D;
+    const __half* kg = p.k + row_base * p.ldk + head * AT_D;
+    const __half* vg = p.v + row_base * p.ldv + head * AT_D;
+    const int nblocks = (p.seq + AT_BN - 1) / AT_BN;
+    const int total   = 3 * nblocks;
+
+    load_tile(sq, qg, p.ldq, p.seq - q0, tid);
+    load_tile(sk[0], kg, p.ldk, p.seq, tid);
+    cp_async_commit();
+
+    uint32_t qa[4][4];
+    float o[8][4];
+#pragma unroll
+    for(int j = 0; j < 8; ++j)
+        o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    const __half2 lowest = __floats2half2_rn(-65504.0f, -65504.0f);
+    __half2 mxh[2]       = {lowest, lowest};
+    float m[2] = {0.0f, 0.0f}, sum[2] = {0.0f, 0.0f}, rcp[2] = {0.0f, 0.0f};
+    constexpr float log2e = 1.4426950408889634f;
+
+    int pass = 0, kb = 0;
+    for(int it = 0; it < total; ++it)
+    {
+        const int buf = it & 1;
+        if(it + 1 < total)
+        {
+            const int kn    = kb + 1 == nblocks ? 0 : kb + 1;
+            const int pn    = kb + 1 == nblocks ? pass + 1 : pass;
+            const int k1    = kn * AT_BN;
+            load_tile(sk[buf ^ 1], kg + static_cast<int64_t>(k1) * p.ldk, p.ldk, p.seq - k1, tid);
+            if(pn == 2)
+                load_tile(sv[buf ^ 1], vg + static_cast<int64_t>(k1) * p.ldv, p.ldv, p.seq - k1, tid);
+            cp_async_commit();
+            cp_async_wait<1>();
+        }
+        else
+            cp_async_wait<0>();
+        __syncthreads();
+        if(it == 0)
+        {
+#pragma unroll
+            for(int ks = 0; ks < 4; ++ks)
+                ldmatrix_x4(qa[ks], tile_ptr(sq, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * ks + (lane >> 4)));
+        }
+        // ---- the tile's scores as halves: w[j][r] = keys 8 j + 2 t, + 1 of row g + 8 r
+        uint32_t w[8][2];
+        {
+            float s[8][4];
+#pragma unroll
+            for(int j = 0; j < 8; ++j)
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+            for(int ks = 0; ks < 4; ++ks)
+            {
+#pragma unroll
+                for(int jp = 0; jp < 4; ++jp)
+                {
+                    uint32_t kf[4];
+                    ldmatrix_x4(kf, tile_ptr(sk[buf], jp * 16 + (lane & 7) + (lane >> 4) * 8, 2 * ks + ((lane >> 3) & 1)));
+                    mma_16816(s[2 * jp], qa[ks], kf[0], kf[1]);
+                    mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
+                }
+            }
+            const int kbase = kb * AT_BN;
+            const bool tail = kbase + AT_BN > p.seq;
+            // half(Q K^T): mantissa cut; half(score * scale): the packing conversion rounds toward zero
+#pragma unroll
+            for(int j = 0; j < 8; ++j)
+            {
+                float x[4];
+#pragma unroll
+                for(int e = 0; e < 4; ++e)
+                    x[e] = __uint_as_float(__float_as_uint(s[j][e]) & 0xFFFFE000u) * p.scale;
+                if(tail)
+                {
+                    // keys that do not exist: the lowest half, whose exponential is 0
+#pragma unroll
+                    for(int e = 0; e < 4; ++e)
+                        if(kbase + j * 8 + 2 * t + (e & 1) >= p.seq)
+                            x[e] = -65504.0f;
+                }
+                w[j][0] = cvt_rz_f16x2(x[0], x[1]);
+                w[j][1] = cvt_rz_f16x2(x[2], x[3]);
+            }
+        }
+        if(pass == 0)
+        {
+#pragma unroll
+            for(int j = 0; j < 8; ++j)
+            {
+                mxh[0] = __hmax2(mxh[0], *reinterpret_cast<const __half2*>(&w[j][0]));
+                mxh[1] = __hmax2(mxh[1], *reinterpret_cast<const __half2*>(&w[j][1]));
+            }
+            if(kb + 1 == nblocks)
+            {
+#pragma unroll
+                for(int r = 0; r < 2; ++r)
+                {
+                    const float2 m2 = __half22float2(mxh[r]);
+                    float mx        = fmaxf(m2.x, m2.y);
+                    mx              = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx              = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    m[r]            = mx;
+                }
+            }
+        }
+        else
+        {
+            // e = half(exp(x - max)) of both passes: the same instructions, the same bits
+            uint32_t eh[8][2];
+#pragma unroll
+            for(int j = 0; j < 8; ++j)
+#pragma unroll
+                for(int r = 0; r < 2; ++r)
+                {
+                    const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&w[j][r]));
+                    eh[j][r] = cvt_rz_f16x2(fast_exp2((x.x - m[r]) * log2e), fast_exp2((x.y - m[r]) * log2e));
+                }
+            if(pass == 1)
+            {
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+#pragma unroll
+                    for(int r = 0; r < 2; ++r)
+                    {
+                        const float2 e = __half22float2(*reinterpret_cast<const __half2*>(&eh[j][r]));
+                        sum[r] += e.x + e.y;
+                    }
+                if(kb + 1 == nblocks)
+                {
+#pragma unroll
+                    for(int r = 0; r < 2; ++r)
+                    {
+                        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+                        sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+                        rcp[r] = __frcp_rn(sum[r]);
+                    }
+                }
+            }
+            else
+            {
+                // p = half(e / sum): reciprocal and remainder correction, packed as the A fragments of
+                // the four 16-key steps (tiles 2 ks and 2 ks + 1)
+                uint32_t pa[4][4];
+#pragma unroll
+                for(int j = 0; j < 8; ++j)
+#pragma unroll
+                    for(int r = 0; r < 2; ++r)
+                    {
+                        const float2 e = __half22float2(*reinterpret_cast<const __half2*>(&eh[j][r]));
+                        float a = e.x * rcp[r], b = e.y * rcp[r];
+                        a       = __fmaf_rn(__fmaf_rn(-a, sum[r], e.x), rcp[r], a);
+                        b       = __fmaf_rn(__fmaf_rn(-b, sum[r], e.y), rcp[r], b);
+                        pa[j >> 1][(j & 1) * 2 + r] = cvt_rz_f16x2(a, b);
+                    }
+#pragma unroll
+                for(int ks = 0; ks < 4; ++ks)
+                {
+#pragma unroll
+                    for(int jp = 0; jp < 4; ++jp)
+                    {
+                        uint32_t vf[4];
+                        ldmatrix_x4_trans(vf, tile_ptr(sv[buf], ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * jp + (lane >> 4)));
+                        mma_16816(o[2 * jp], pa[ks], vf[0], vf[1]);
+                        mma_16816(o[2 * jp + 1], pa[ks], vf[2], vf[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads(); // the other buffers are overwritten by the next iteration's loads
+        if(++kb == nblocks)
+        {
+            kb = 0;
+            ++pass;
+        }
+    }
+    const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
+#pragma unroll
+    for(int r = 0; r < 2; ++r)
+    {
+        const int row = q0 + warp * 16 + g + r * 8;
+        if(row >= p.seq)
+            continue;
+#pragma unroll
+        for(int j = 0; j < 8; ++j)
+        {
+            const float a = truncate_to_half_precision(o[j][2 * r]);
+            const float b = truncate_to_half_precision(o[j][2 * r + 1]);
+            const int col = head * AT_D + j * 8 + 2 * t;
+            if(p.o != nullptr)
+                *reinterpret_cast<uint32_t*>(p.o + (row_base + row) * p.ldo + col) = cvt_rz_f16x2(a, b);
+            if(p.oq != nullptr)
+            {
+                uint32_t qb[2];
+                const float vals[2] = {a, b};
+#pragma unroll
+                for(int e = 0; e < 2; ++e)
+                {
+                    float qv        = __fmul_rn(vals[e], p.q_rcp);
+                    const float rem = __fmaf_rn(-p.q_scale, qv, vals[e]);
+                    qv              = truncate_to_half_precision(__fmaf_rn(rem, p.q_rcp, qv));
+                    qv              = fmaxf(q_lo, fminf(q_hi, qv));
+                    qb[e] = static_cast<uint32_t>(__float_as_int(__fadd_rn(qv, 12582912.0f)) - 0x4B400000 +
+                                                  static_cast<int>(p.q_zp)) & 0xFFu;
+                }
+                *reinterpret_cast<uint16_t*>(p.oq + (row_base + row) * p.ldoq + col) =
+                    static_cast<uint16_t>(qb[0] | (qb[1] << 8));
+            }
+        }
+    }
+}
+
 } // namespace mgx
 
 extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
@@ -625,8 +857,15 @@ extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, co
     const dim3 grid(static_cast<unsigned>((d->seq + AT_BM - 1) / AT_BM), static_cast<unsigned>(d->heads),
                     static_cast<unsigned>(d->batch));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if((d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0 and
+       ((d->flags & MGX_ATTENTION_SCORE_BUFFER) == 0 or d->seq > AT_CHAIN_MAX_SEQ))
+    {
+        attention_f16_chain3_kernel<<<grid, 128, 0, stream>>>(p);
+        return static_cast<int>(cudaGetLastError());
+    }
     if(d->seq <= AT_CHAIN_MAX_SEQ and (d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0)
     {
+        // MGX_ATTENTION_SCORE_BUFFER
         const int sp    = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
         const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + 2 * AT_BM * 4;
         // opted in once per instantiation, to the size its longest sequence needs

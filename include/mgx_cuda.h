@@ -200,10 +200,11 @@ MGX_API int mgx_cuda_layernorm_ex(const mgx_layernorm_desc* d, const void* x, co
  * (int8: the per-tensor quantizelinear of the fp16 result) receive the merged-heads result.
  * Stands in for reshape -> transpose -> dot -> mul -> softmax -> dot -> transpose -> reshape of an
  * encoder layer (the reference fuses the same chain for its GPU target,
- * src/targets/gpu/fuse_mlir.cpp:1161-1234).  head_dim must be 64.  Up to 1024 keys the kernel
- * keeps the chain's own roundings (scores and probabilities stored as half, ref_softmax's order of
- * operations): results are the reference's halves except for about one element in a thousand
- * (neighbouring halves, from the order of the fp32 sums and the last bit of exp). */
+ * src/targets/gpu/fuse_mlir.cpp:1161-1234).  head_dim must be 64.  The kernel keeps the chain's own
+ * roundings (scores, exponentials and probabilities rounded to half where the operators store them,
+ * ref_softmax's order of operations): results are the reference's halves except for about one
+ * element in a hundred (neighbouring halves, from the order of the fp32 sums and the last bit of
+ * exp). */
 typedef struct mgx_attention_desc
 {
     int64_t batch, seq, heads, head_dim;
@@ -214,11 +215,14 @@ typedef struct mgx_attention_desc
     int32_t flags;      /* MGX_ATTENTION_* bits, 0 for none */
 } mgx_attention_desc;
 
-/* Run the softmax in fp32 over key blocks (running maximum and sum) instead of making the
- * operator chain's half roundings: about a third of the time for 384 keys, results within the
- * fp16 tolerance (rtol 2e-2 / atol 1e-2) of the chain instead of (nearly) its bits.  Sequences
- * longer than 1024 keys always run this way. */
+/* Run the softmax in fp32 over key blocks (running maximum and sum, one pass over the keys)
+ * instead of making the operator chain's half roundings (three passes): results within the fp16
+ * tolerance (rtol 2e-2 / atol 1e-2) of the chain instead of (nearly) its bits. */
 #define MGX_ATTENTION_FP32_SOFTMAX 1
+/* The chain's roundings with the scores kept in shared memory between the passes (one pass over
+ * the keys per matrix product; at most 1024 keys, longer sequences ignore the flag): the first
+ * form of the chain-faithful kernel, kept for comparison. */
+#define MGX_ATTENTION_SCORE_BUFFER 2
 
 MGX_API int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, const void* k, const void* v, void* o,
                                void* oq, void* stream);
