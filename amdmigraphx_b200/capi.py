@@ -406,7 +406,7 @@ class AttentionDesc(ctypes.Structure):
 
 
 def attention(q, k, v, batch, seq, heads, scale, q_scale=None, q_zero_point=0.0, write_o=True, fp32_softmax=False,
-              score_buffer=False):
+              three_pass=False):
     """softmax(scale * Q K^T) V per batch entry and head on [batch*seq, heads*64] fp16 matrices (row
     strided views allowed); returns (o or None, oq or None)."""
     import torch
@@ -416,7 +416,7 @@ def attention(q, k, v, batch, seq, heads, scale, q_scale=None, q_zero_point=0.0,
     oq = torch.empty((batch * seq, width), dtype=torch.int8, device=q.device) if q_scale is not None else None
     d = AttentionDesc(batch=batch, seq=seq, heads=heads, head_dim=64, ldq=q.stride(0), ldk=k.stride(0),
                       ldv=v.stride(0), ldo=width, ldoq=width, scale=float(scale), q_scale=float(q_scale or 1.0),
-                      q_zero_point=float(q_zero_point), flags=(1 if fp32_softmax else 0) | (2 if score_buffer else 0))
+                      q_zero_point=float(q_zero_point), flags=(1 if fp32_softmax else 0) | (2 if three_pass else 0))
     lib.mgx_cuda_attention.argtypes = [ctypes.POINTER(AttentionDesc)] + [ctypes.c_void_p] * 6
     check(lib.mgx_cuda_attention(ctypes.byref(d), _ptr(q), _ptr(k), _ptr(v), _ptr(o), _ptr(oq), _stream()),
           "mgx_cuda_attention")

@@ -858,14 +858,13 @@ extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, co
                     static_cast<unsigned>(d->batch));
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     if((d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0 and
-       ((d->flags & MGX_ATTENTION_SCORE_BUFFER) == 0 or d->seq > AT_CHAIN_MAX_SEQ))
+       ((d->flags & MGX_ATTENTION_THREE_PASS) != 0 or d->seq > AT_CHAIN_MAX_SEQ))
     {
         attention_f16_chain3_kernel<<<grid, 128, 0, stream>>>(p);
         return static_cast<int>(cudaGetLastError());
     }
     if(d->seq <= AT_CHAIN_MAX_SEQ and (d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0)
     {
-        // MGX_ATTENTION_SCORE_BUFFER
         const int sp    = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
         const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + 2 * AT_BM * 4;
         // opted in once per instantiation, to the size its longest sequence needs

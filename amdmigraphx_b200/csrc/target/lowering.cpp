@@ -592,7 +592,12 @@ struct lowerer
         const bool only_q = qz != m.end() and last->outputs().size() == 1;
         // fp16 chain whose only result is the int8 tensor: activation + quantizelinear of the half
         // the chain holds after the bias is a function of 16 bits - one table look-up in the epilogue
-        if(only_q and op.half_math and not op.has_residual and op.q_type == static_cast<int>(shape::int8_type) and
+        // (MIGRAPHX_CUDA_QGEMM_LUT=1.  Off by default: the table is the reference's own arithmetic, but
+        // one uncoalesced byte load per element costs the FFN1 launch of a BERT-base layer more than the
+        // ~30 instructions it saves - 29.6 us against 24.4 us per cold launch.)
+        const char* lut_env = std::getenv("MIGRAPHX_CUDA_QGEMM_LUT");
+        if(lut_env != nullptr and std::string(lut_env) == "1" and only_q and op.half_math and not op.has_residual and
+           op.q_type == static_cast<int>(shape::int8_type) and
            (op.act == MGX_ACT_GELU_ERF or op.act == MGX_ACT_RELU))
         {
             op.has_lut = true;

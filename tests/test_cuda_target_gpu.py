@@ -68,6 +68,13 @@ def test_program_matches_ref_on_two_streams(cuda_device, case):
     assert res.get("pass"), res
 
 
+def test_encoder_layer_matches_ref_with_the_activation_table(cuda_device):
+    # MIGRAPHX_CUDA_QGEMM_LUT=1: erf-GELU + quantizelinear of FFN1 as a table made with the
+    # reference's half arithmetic
+    res = _run("c2_layer", env={"MIGRAPHX_CUDA_QGEMM_LUT": "1"})
+    assert res.get("pass"), res
+
+
 @pytest.mark.parametrize("case", CONFIG_SIZE)
 def test_config_size_program_matches_ref(cuda_device, case):
     res = _run(case)

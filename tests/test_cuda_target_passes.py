@@ -255,3 +255,14 @@ def test_make_target_loads_the_plugin_by_name_and_fails_loudly_without_a_device(
     assert lines and lines[0] == {"targets_before": 0, "cuda": "cuda", "ref": "ref"}, r.stdout + r.stderr
     if not torch.cuda.is_available():
         assert r.returncode == 2 and "cuda target: cudaSetDevice" in lines[-1]["error"]
+
+
+def test_activation_and_quantizelinear_table_is_opt_in():
+    # fp16 chain whose only result is the int8 tensor (FFN1 of an encoder layer): with
+    # MIGRAPHX_CUDA_QGEMM_LUT=1 the erf-GELU and the quantizelinear become a 65536-entry table input
+    plain = _passes("c2_layer")
+    assert "has_lut=1" not in plain
+    out = _passes("c2_layer", env={"MIGRAPHX_CUDA_QGEMM_LUT": "1"})
+    lines = [l for l in out.splitlines() if "cuda::qgemm" in l and "has_lut=1" in l]
+    assert len(lines) == 1 and "act=2" in lines[0] and "write_d=0" in lines[0]
+    assert "int8_type, {65536}" in out
