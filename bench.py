@@ -833,9 +833,18 @@ def main():
     args = ap.parse_args()
     if args.case is not None:
         return run_case(args)
-    if args.impl == "reference":
-        return run_reference_arm(args)
-    return run_own_arm(args)
+    # One JSON line on stdout, whatever libraries print (NCCL announces its version there): during
+    # the run file descriptor 1 points at stderr, and print() goes to the real stdout.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    sys.stdout = real_stdout
+    try:
+        if args.impl == "reference":
+            return run_reference_arm(args)
+        return run_own_arm(args)
+    finally:
+        real_stdout.flush()
 
 
 if __name__ == "__main__":
