@@ -330,18 +330,22 @@ __device__ __forceinline__ void load_tile_256(__half* tile, const __half* g, int
 // warps of one-warp-per-16-rows at half the accumulator registers each: the kernel is bound by
 // the latency of dependent instructions, which only more resident warps hide.
 // NVMAX: half2 pairs per lane and row the softmax phase holds in registers (keys <= 64 NVMAX).
-template <int NVMAX>
+template <int NVMAX, int RG>
 __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(const attention_params p, const int sp)
 {
+    constexpr int BMC = RG * 16;      // query rows per CTA
+    constexpr int KS  = 8 / RG;       // warps that share a row group: each takes 64 / KS keys of a tile
+    constexpr int JPW = 4 / KS;       // 16-key groups of a tile per warp
+    constexpr int RPW = BMC / 8;      // whole rows per warp in the softmax phase
     extern __shared__ __align__(128) uint8_t at_smem[];
     __half* sq     = reinterpret_cast<__half*>(at_smem);
     __half* skv[2] = {sq + AT_BM * AT_D, sq + AT_BM * AT_D + AT_BN * AT_D};
-    __half* sc     = sq + AT_BM * AT_D + 2 * AT_BN * AT_D; // [64][sp]
-    float* rowmax  = reinterpret_cast<float*>(sc + AT_BM * sp); // [2][64]
+    __half* sc     = sq + AT_BM * AT_D + 2 * AT_BN * AT_D; // [BMC][sp]
+    float* rowmax  = reinterpret_cast<float*>(sc + BMC * sp); // [KS][BMC]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int rg = warp & 3, kh = warp >> 2;
-    const int q0   = blockIdx.x * AT_BM;
+    const int rg = warp % RG, kh = warp / RG;
+    const int q0   = blockIdx.x * BMC;
     const int head = blockIdx.y;
     const int64_t row_base = static_cast<int64_t>(blockIdx.z) * p.seq;
     const __half* qg = p.q + (row_base + q0) * p.ldq + head * AT_D;
@@ -379,30 +383,30 @@ __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(con
                 for(int ks = 0; ks < 4; ++ks)
                     ldmatrix_x4(qa[ks], tile_ptr(sq, rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, 2 * ks + (lane >> 4)));
             }
-            float s[4][4];
+            float s[2 * JPW][4];
 #pragma unroll
-            for(int j = 0; j < 4; ++j)
+            for(int j = 0; j < 2 * JPW; ++j)
                 s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
             for(int ks = 0; ks < 4; ++ks)
             {
 #pragma unroll
-                for(int jp = 0; jp < 2; ++jp)
+                for(int jp = 0; jp < JPW; ++jp)
                 {
                     uint32_t kf[4];
-                    ldmatrix_x4(kf, tile_ptr(skv[buf], (kh * 2 + jp) * 16 + (lane & 7) + (lane >> 4) * 8,
+                    ldmatrix_x4(kf, tile_ptr(skv[buf], (kh * JPW + jp) * 16 + (lane & 7) + (lane >> 4) * 8,
                                              2 * ks + ((lane >> 3) & 1)));
                     mma_16816(s[2 * jp], qa[ks], kf[0], kf[1]);
                     mma_16816(s[2 * jp + 1], qa[ks], kf[2], kf[3]);
                 }
             }
-            const int kbase = kb * AT_BN + kh * 32;
-            const bool tail = kbase + 32 > p.seq;
+            const int kbase = kb * AT_BN + kh * (16 * JPW);
+            const bool tail = kbase + 16 * JPW > p.seq;
             // half(Q K^T): mantissa cut (a score in the half subnormal range keeps a few more bits:
             // below 2^-24 absolute, invisible after the exponential); half(score * scale): the
             // packing conversion itself rounds toward zero, subnormal halves included
 #pragma unroll
-            for(int j = 0; j < 4; ++j)
+            for(int j = 0; j < 2 * JPW; ++j)
             {
                 float x[4];
 #pragma unroll
@@ -436,7 +440,7 @@ __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(con
             mx              = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx              = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             if(t == 0)
-                rowmax[kh * AT_BM + rg * 16 + g + r * 8] = mx;
+                rowmax[kh * BMC + rg * 16 + g + r * 8] = mx;
         }
     }
     __syncthreads();
@@ -449,11 +453,14 @@ __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(con
         const int nv = nblocks; // half2 pairs per lane and row: keys / 64
         constexpr float log2e = 1.4426950408889634f;
 #pragma unroll 1
-        for(int r = 0; r < 8; ++r)
+        for(int r = 0; r < RPW; ++r)
         {
-            const int row = warp * 8 + r;
+            const int row = warp * RPW + r;
             __half* rowp  = sc + row * sp;
-            const float m = fmaxf(rowmax[row], rowmax[AT_BM + row]);
+            float m       = rowmax[row];
+#pragma unroll
+            for(int h = 1; h < KS; ++h)
+                m = fmaxf(m, rowmax[h * BMC + row]);
             // the packing conversion rounds toward zero (subnormal halves included); the sum runs
             // over the stored halves
             float2 e[NVMAX];
@@ -508,9 +515,9 @@ __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(con
             cp_async_wait<0>();
         __syncthreads();
 #pragma unroll
-        for(int k2 = 0; k2 < 2; ++k2)
+        for(int k2 = 0; k2 < JPW; ++k2)
         {
-            const int ks = kh * 2 + k2;
+            const int ks = kh * JPW + k2;
             uint32_t pa[4];
             ldmatrix_x4(pa, sc + (rg * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * sp + kb * AT_BN + ks * 16 +
                                 (lane >> 4) * 8);
@@ -525,30 +532,33 @@ __global__ void __launch_bounds__(ATC_THREADS, 3) attention_f16_chain_kernel(con
         }
         __syncthreads();
     }
-    // the two key halves are added in a fixed order: the upper half's partial sums go through
-    // shared memory (the Q / K / V tiles are free now: 16 KB of the 24 KB they take)
+    // the key shares are added in a fixed order: the partial sums of shares 1 .. KS-1 go through
+    // shared memory (tiles and scores are free now; (KS - 1) BMC x 64 floats = 16 or 24 KB from the start)
     float* red = reinterpret_cast<float*>(at_smem);
-    if(kh == 1)
+    if(kh != 0)
     {
 #pragma unroll
         for(int j = 0; j < 8; ++j)
 #pragma unroll
             for(int r = 0; r < 2; ++r)
-                *reinterpret_cast<float2*>(red + (rg * 16 + g + r * 8) * AT_D + j * 8 + 2 * t) =
+                *reinterpret_cast<float2*>(red + ((kh - 1) * BMC + rg * 16 + g + r * 8) * AT_D + j * 8 + 2 * t) =
                     make_float2(o[j][2 * r], o[j][2 * r + 1]);
     }
     __syncthreads();
-    if(kh == 1)
+    if(kh != 0)
         return;
 #pragma unroll
-    for(int j = 0; j < 8; ++j)
+    for(int h = 1; h < KS; ++h)
 #pragma unroll
-        for(int r = 0; r < 2; ++r)
-        {
-            const float2 u = *reinterpret_cast<const float2*>(red + (rg * 16 + g + r * 8) * AT_D + j * 8 + 2 * t);
-            o[j][2 * r] += u.x;
-            o[j][2 * r + 1] += u.y;
-        }
+        for(int j = 0; j < 8; ++j)
+#pragma unroll
+            for(int r = 0; r < 2; ++r)
+            {
+                const float2 u =
+                    *reinterpret_cast<const float2*>(red + ((h - 1) * BMC + rg * 16 + g + r * 8) * AT_D + j * 8 + 2 * t);
+                o[j][2 * r] += u.x;
+                o[j][2 * r + 1] += u.y;
+            }
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
 #pragma unroll
     for(int r = 0; r < 2; ++r)
@@ -865,22 +875,34 @@ extern "C" int mgx_cuda_attention(const mgx_attention_desc* d, const void* q, co
     }
     if(d->seq <= AT_CHAIN_MAX_SEQ and (d->flags & MGX_ATTENTION_FP32_SOFTMAX) == 0)
     {
-        const int sp    = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
-        const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * sp) * 2 + 2 * AT_BM * 4;
+        const int sp = static_cast<int>((d->seq + AT_BN - 1) / AT_BN * AT_BN) + 8;
+        // 64 query rows per CTA, or 32 where that leaves SMs without a CTA (a single sequence per GPU)
+        const bool narrow = static_cast<int64_t>(grid.x) * grid.y * grid.z < device_sm_count();
+        const int rows    = narrow ? 32 : AT_BM;
+        const dim3 cgrid(static_cast<unsigned>((d->seq + rows - 1) / rows), grid.y, grid.z);
+        const int bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + rows * sp) * 2 + 2 * AT_BM * 4;
         // opted in once per instantiation, to the size its longest sequence needs
         auto launch = [&](auto kernel, int max_seq) {
             const int max_bytes = (AT_BM * AT_D + 2 * AT_BN * AT_D + AT_BM * (max_seq + 8)) * 2 + 2 * AT_BM * 4;
             const int rc        = ensure_smem_optin(reinterpret_cast<const void*>(kernel), max_bytes);
             if(rc != MGX_OK)
                 return rc;
-            kernel<<<grid, ATC_THREADS, bytes, stream>>>(p, sp);
+            kernel<<<cgrid, ATC_THREADS, bytes, stream>>>(p, sp);
             return static_cast<int>(cudaGetLastError());
         };
+        if(narrow)
+        {
+            if(d->seq <= 384)
+                return launch(attention_f16_chain_kernel<6, 2>, 384);
+            if(d->seq <= 512)
+                return launch(attention_f16_chain_kernel<8, 2>, 512);
+            return launch(attention_f16_chain_kernel<AT_CHAIN_MAX_SEQ / 64, 2>, AT_CHAIN_MAX_SEQ);
+        }
         if(d->seq <= 384)
-            return launch(attention_f16_chain_kernel<6>, 384);
+            return launch(attention_f16_chain_kernel<6, 4>, 384);
         if(d->seq <= 512)
-            return launch(attention_f16_chain_kernel<8>, 512);
-        return launch(attention_f16_chain_kernel<AT_CHAIN_MAX_SEQ / 64>, AT_CHAIN_MAX_SEQ);
+            return launch(attention_f16_chain_kernel<8, 4>, 512);
+        return launch(attention_f16_chain_kernel<AT_CHAIN_MAX_SEQ / 64, 4>, AT_CHAIN_MAX_SEQ);
     }
     else
         attention_f16_kernel<<<grid, 128, 0, stream>>>(p);
