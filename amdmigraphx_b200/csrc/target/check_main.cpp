@@ -124,6 +124,11 @@ std::map<std::string, std::function<test_case()>> cases()
     big["c4_attention_decode"]  = [] { return gqa_attention(1, 32, 32, 128, 1, 2048, false, 64); };
     big["c4_attention_decode_b16"] = [] { return gqa_attention(16, 32, 32, 128, 1, 2048, false, 65); };
     big["c5_attention_decode_tp8"] = [] { return gqa_attention(16, 8, 1, 128, 1, 4096, false, 66); };
+    // whole decoder layers at a decode step: RMSNorm, int4 linears, GQA with KV cache, SwiGLU
+    big["llama_layer_small"]     = [] { return llama_decoder_layer(2, 256, 4, 2, 64, 512, 96, 128, 71); };
+    big["llama_layer_small_d128"] = [] { return llama_decoder_layer(3, 512, 4, 4, 128, 1024, 160, 128, 72); };
+    big["c4_layer_decode"]       = [] { return llama_decoder_layer(1, 4096, 32, 32, 128, 11008, 2048, 128, 73); };
+    big["c5_layer_decode_tp8"]   = [] { return llama_decoder_layer(16, 8192, 8, 1, 128, 3584, 4096, 128, 74); };
     big["c2_layer"]   = [] { return c2_encoder(1, 1); };
     big["c2_layers2"] = [] { return c2_encoder(1, 2); };
     std::map<std::string, std::function<test_case()>> small = {

@@ -18,6 +18,7 @@
 #include <migraphx/generate.hpp>
 #include <migraphx/half.hpp>
 #include <migraphx/quantization.hpp>
+#include <migraphx/common.hpp>
 #include <migraphx/op/builder/insert.hpp>
 #include <chrono>
 #include <cmath>
@@ -1246,6 +1247,114 @@ inline test_case gqa_attention(std::size_t batch, std::size_t num_heads, std::si
     std::uniform_int_distribution<int32_t> pick(static_cast<int32_t>(cache_len / 2), static_cast<int32_t>(cache_len - seq - 1));
     for(std::size_t b = 0; b < batch; ++b)
         reinterpret_cast<int32_t*>(sa.data())[b] = seq == 1 ? pick(g) : static_cast<int32_t>(seq - 1);
+    t.params["seqlens_k"] = sa;
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
+    return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One Llama-shaped decoder layer at a decode step, as a front end hands it over: RMSNorm in the
+// parser's decomposition (src/onnx/parse_simplified_layer_normalization.cpp:91-106: convert to
+// float, mul, reduce_mean, convert back, add eps, rsqrt, mul, mul), weight-only int4 linears in the
+// MatMulNBits IR (src/onnx/parse_matmulnbits.cpp:85-158; packed QKV, O, gate, up, down),
+// GroupQueryAttention in the parser's decomposition (add_gqa above) against fp16 KV caches, SwiGLU
+// (mul(gate, sigmoid(gate)) * up) and the two residual adds.  Returns {layer output, K cache, V cache}.
+inline instruction_ref add_int4_matmul(migraphx::module* mm, instruction_ref a, std::size_t n, std::size_t k,
+                                       std::size_t g, std::mt19937& gen)
+{
+    auto bp = mm->add_literal(
+        migraphx::literal{shape{shape::uint8_type, {n, k / 2}}, rand_ints<uint8_t>(gen, n * k / 2, 0, 255)});
+    // scales that keep the result of order one for inputs of order one (nibbles - 8 have rms 4.6)
+    const float s0 = 1.0f / (4.6f * std::sqrt(static_cast<float>(k)));
+    auto sf        = rand_uniform(gen, n * (k / g), 0.6f * s0, 1.4f * s0);
+    std::vector<migraphx::half> sh(sf.begin(), sf.end());
+    auto scales = mm->add_literal(migraphx::literal{shape{shape::half_type, {n, k / g}}, sh});
+    auto u      = mm->add_instruction(migraphx::make_op("unsqueeze", {{"axes", {2}}}), scales);
+    auto mb     = mm->add_instruction(migraphx::make_op("multibroadcast", {{"out_lens", {n, k / g, g}}}), u);
+    auto se     = mm->add_instruction(migraphx::make_op("reshape", {{"dims", {n, k}}}), mb);
+    auto z8     = mm->add_literal(migraphx::literal{shape{shape::uint8_type}, std::vector<uint8_t>{8}});
+    auto zp     = mbcast(mm, z8, {n, k});
+    auto unpacked = mm->add_instruction(migraphx::make_op("unpack_int4"), bp);
+    auto dq       = mm->add_instruction(migraphx::make_op("dequantizelinear"), unpacked, se, zp);
+    auto bt       = mm->add_instruction(migraphx::make_op("transpose", {{"permutation", {1, 0}}}), dq);
+    return mm->add_instruction(migraphx::make_op("dot"), a, bt);
+}
+
+inline instruction_ref add_rmsnorm(migraphx::module* mm, instruction_ref x, std::size_t hidden, std::mt19937& gen)
+{
+    using migraphx::make_op;
+    auto gv = rand_uniform(gen, hidden, 0.8f, 1.2f);
+    std::vector<migraphx::half> gh(gv.begin(), gv.end());
+    auto gamma = mm->add_literal(migraphx::literal{shape{shape::half_type, {hidden}}, gh});
+    auto fx    = mm->add_instruction(make_op("convert", {{"target_type", migraphx::to_value(shape::float_type)}}), x);
+    auto sq    = migraphx::add_common_op(*mm, make_op("mul"), {fx, fx});
+    auto rms   = mm->add_instruction(make_op("reduce_mean", {{"axes", {1}}}), sq);
+    rms        = mm->add_instruction(make_op("convert", {{"target_type", migraphx::to_value(shape::half_type)}}), rms);
+    auto eps   = mm->add_literal(migraphx::literal{shape{shape::half_type}, {1e-5f}});
+    rms        = migraphx::add_common_op(*mm, make_op("add"), {rms, eps});
+    auto rrms  = mm->add_instruction(make_op("rsqrt"), rms);
+    auto y     = migraphx::add_common_op(*mm, make_op("mul"), {x, rrms});
+    return migraphx::add_common_op(*mm, make_op("mul"), {y, gamma});
+}
+
+inline test_case llama_decoder_layer(std::size_t batch, std::size_t hidden, std::size_t heads, std::size_t kv_heads,
+                                     std::size_t head, std::size_t ffn, std::size_t cache_len, std::size_t group,
+                                     unsigned seed)
+{
+    using migraphx::make_op;
+    test_case t;
+    std::mt19937 g(seed);
+    auto* mm = t.prog.get_main_module();
+    const std::size_t width = (heads + 2 * kv_heads) * head;
+    const shape x_s{shape::half_type, {batch, hidden}}; // one token per batch entry
+    const shape kv_s{shape::half_type, {batch, kv_heads, cache_len, head}};
+    const shape slk_s{shape::int32_type, {batch, 1}};
+    auto x      = mm->add_parameter("x", x_s);
+    auto past_k = mm->add_parameter("past_k", kv_s);
+    auto past_v = mm->add_parameter("past_v", kv_s);
+    auto slk    = mm->add_parameter("seqlens_k", slk_s);
+    std::vector<migraphx::half> cosv(cache_len * head / 2), sinv(cache_len * head / 2);
+    for(std::size_t p = 0; p < cache_len; ++p)
+        for(std::size_t i = 0; i < head / 2; ++i)
+        {
+            const double ang = static_cast<double>(p) * std::pow(10000.0, -2.0 * static_cast<double>(i) / head);
+            cosv[p * head / 2 + i] = migraphx::half(static_cast<float>(std::cos(ang)));
+            sinv[p * head / 2 + i] = migraphx::half(static_cast<float>(std::sin(ang)));
+        }
+    auto cosl = mm->add_literal(migraphx::literal{shape{shape::half_type, {cache_len, head / 2}}, cosv});
+    auto sinl = mm->add_literal(migraphx::literal{shape{shape::half_type, {cache_len, head / 2}}, sinv});
+
+    auto h1   = add_rmsnorm(mm, x, hidden, g);
+    auto qkv  = add_int4_matmul(mm, h1, width, hidden, group, g);
+    auto qkv3 = mm->add_instruction(make_op("reshape", {{"dims", {batch, std::size_t{1}, width}}}), qkv);
+    auto att  = add_gqa(mm, qkv3, past_k, past_v, slk, cosl, sinl, heads, kv_heads);
+    auto a2   = mm->add_instruction(make_op("reshape", {{"dims", {batch, heads * head}}}), att[0]);
+    auto o    = add_int4_matmul(mm, a2, hidden, heads * head, group, g);
+    auto r1   = mm->add_instruction(make_op("add"), x, o);
+    auto h2   = add_rmsnorm(mm, r1, hidden, g);
+    auto gate = add_int4_matmul(mm, h2, ffn, hidden, group, g);
+    auto up   = add_int4_matmul(mm, h2, ffn, hidden, group, g);
+    auto sg   = mm->add_instruction(make_op("sigmoid"), gate);
+    auto act  = mm->add_instruction(make_op("mul"), mm->add_instruction(make_op("mul"), gate, sg), up);
+    auto down = add_int4_matmul(mm, act, hidden, ffn, group, g);
+    auto y    = mm->add_instruction(make_op("add"), r1, down);
+    mm->add_return({y, att[1], att[2]});
+
+    auto half_arg = [&](const shape& s, float sd) {
+        auto v = rand_normal(g, s.elements(), sd);
+        std::vector<migraphx::half> h(v.begin(), v.end());
+        migraphx::argument a{s};
+        std::memcpy(a.data(), h.data(), h.size() * sizeof(migraphx::half));
+        return a;
+    };
+    t.params["x"]      = half_arg(x_s, 1.0f);
+    t.params["past_k"] = half_arg(kv_s, 1.0f);
+    t.params["past_v"] = half_arg(kv_s, 1.0f);
+    migraphx::argument sa{slk_s};
+    std::uniform_int_distribution<int32_t> pick(static_cast<int32_t>(cache_len / 2), static_cast<int32_t>(cache_len - 2));
+    for(std::size_t b = 0; b < batch; ++b)
+        reinterpret_cast<int32_t*>(sa.data())[b] = pick(g);
     t.params["seqlens_k"] = sa;
     t.rtol = 2e-2;
     t.atol = 1e-2;

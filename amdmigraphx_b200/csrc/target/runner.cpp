@@ -48,7 +48,9 @@ bool launching(const std::string& n)
     static const char* names[] = {"cuda::quantizelinear", "cuda::dequantizelinear", "cuda::qgemm", "cuda::w4a16",
                                   "cuda::unpack_int4",    "cuda::pack_int4",        "cuda::copy",  "cuda::pointwise",
                                   "cuda::reduce",         "cuda::softmax",          "cuda::gather", "cuda::concat",
-                                  "cuda::pad_rows",       "cuda::layernorm",        "cuda::attention"};
+                                  "cuda::pad_rows",       "cuda::layernorm",        "cuda::attention",
+                                  "cuda::concat_past_present", "cuda::gqa_rotary_embedding",
+                                  "cuda::gqa_decode_attention"};
     for(auto* s : names)
         if(n == s)
             return true;
@@ -156,6 +158,50 @@ MGX_RUNNER_API int mgx_runner_create_bert(const mgx_bert_desc* d, void** out)
             }
             else
                 r->params[ps.first] = r->tgt.allocate(ps.second);
+        }
+        *out = r.release();
+        return 0;
+    });
+}
+
+// One Llama-shaped decoder layer at a decode step (programs.hpp: llama_decoder_layer) compiled for
+// the cuda target with device-resident parameters (activations, KV caches, past lengths, filled with
+// the case's seeded values).  mgx_runner_eval / _launches / _op_counts work on the handle.
+struct mgx_llama_desc
+{
+    int64_t batch, hidden, heads, kv_heads, head, ffn, cache, group;
+    uint32_t seed;
+    int32_t reserved;
+};
+
+MGX_RUNNER_API int mgx_runner_create_llama_layer(const mgx_llama_desc* d, void** out)
+{
+    return guarded([&] {
+        if(d == nullptr or out == nullptr)
+            MIGRAPHX_THROW("mgx_runner_create_llama_layer: null argument");
+        auto r = std::make_unique<runner>();
+        auto t = llama_decoder_layer(static_cast<std::size_t>(d->batch), static_cast<std::size_t>(d->hidden),
+                                     static_cast<std::size_t>(d->heads), static_cast<std::size_t>(d->kv_heads),
+                                     static_cast<std::size_t>(d->head), static_cast<std::size_t>(d->ffn),
+                                     static_cast<std::size_t>(d->cache), static_cast<std::size_t>(d->group), d->seed);
+        r->prog   = std::move(t.prog);
+        r->tokens = static_cast<std::size_t>(d->batch);
+        r->prog.compile(r->tgt, migraphx::compile_options{});
+        for(auto* mod : r->prog.get_modules())
+            for(auto ins : migraphx::iterator_for(*mod))
+            {
+                ++r->op_counts[ins->name()];
+                if(launching(ins->name()))
+                    ++r->launches;
+            }
+        auto& ctx = migraphx::any_cast<migraphx::cuda::context>(r->prog.get_context());
+        r->stream = ctx.stream();
+        if(cudaEventCreate(&r->e0) != cudaSuccess or cudaEventCreate(&r->e1) != cudaSuccess)
+            MIGRAPHX_THROW("cudaEventCreate failed");
+        for(const auto& ps : r->prog.get_parameter_shapes())
+        {
+            auto it = t.params.find(ps.first);
+            r->params[ps.first] = it != t.params.end() ? r->tgt.copy_to(it->second) : r->tgt.allocate(ps.second);
         }
         *out = r.release();
         return 0;

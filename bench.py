@@ -194,6 +194,25 @@ class Runner(object):
             self.h = None
 
 
+class LlamaDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int64) for n in ("batch", "hidden", "heads", "kv_heads", "head", "ffn", "cache", "group")] + \
+               [("seed", ctypes.c_uint32), ("reserved", ctypes.c_int32)]
+
+
+class LlamaLayerRunner(Runner):
+    """One Llama-shaped decoder layer at a decode step as a compiled cuda program (device-resident)."""
+
+    def __init__(self, batch, hidden, heads, kv_heads, head, ffn, cache, group=128, seed=1):
+        lib = self.lib()
+        lib.mgx_runner_create_llama_layer.argtypes = [ctypes.POINTER(LlamaDesc), ctypes.POINTER(ctypes.c_void_p)]
+        desc = LlamaDesc(batch=batch, hidden=hidden, heads=heads, kv_heads=kv_heads, head=head, ffn=ffn, cache=cache,
+                         group=group, seed=seed, reserved=0)
+        self.h = ctypes.c_void_p()
+        self.check(lib.mgx_runner_create_llama_layer(ctypes.byref(desc), ctypes.byref(self.h)),
+                   "mgx_runner_create_llama_layer")
+        self.launches = lib.mgx_runner_launches(self.h)
+
+
 # ------------------------------------------------------------------ CPU reference legs
 def _ref_sample_tokens(budget_s):
     """Tokens of one encoder layer the ref target gets through in about budget_s seconds."""
@@ -460,6 +479,40 @@ def secondary_measurements(dev, peaks, failures):
             "us": us, "weight_gbs": gbs, "frac_of_measured_hbm": gbs / float(peaks["hbm_gbs"]),
             "what": "one int4 weight-only linear N=28672 K=8192 (group 128), 3 rotating weight "
                     "copies of 117 MB"}
+    del big
+    torch.cuda.empty_cache()
+    # configs 4 and 5 as programs: one decoder layer at a decode step through the plug-in (RMSNorm,
+    # packed-QKV / O / gate / up / down int4 linears, rotary embedding, KV-cache append, decode attention,
+    # SwiGLU, residual adds), two compiled instances with their own weights (2 x 101 MB for config 4: more
+    # than the L2) and caches taking turns
+    for name, dims, layers in (("c4_llama7b_layer_decode_batch1",
+                                dict(batch=1, hidden=4096, heads=32, kv_heads=32, head=128, ffn=11008, cache=2048), 32),
+                               ("c4_llama7b_layer_decode_batch16",
+                                dict(batch=16, hidden=4096, heads=32, kv_heads=32, head=128, ffn=11008, cache=2048), 32),
+                               ("c5_llama70b_tp8_shard_layer_decode_batch16",
+                                dict(batch=16, hidden=8192, heads=8, kv_heads=1, head=128, ffn=3584, cache=4096), 80)):
+        try:
+            layers_r = [LlamaLayerRunner(seed=81 + i, **dims) for i in range(2)]
+            for _ in range(4):
+                Runner.eval_many(layers_r, 2)
+            dms, _ = Runner.eval_many(layers_r, 30)
+            us = dms / 30 * 1e3
+            d = dims
+            wbytes = sum(n * k // 2 + n * (k // 128) * 2 for (n, k) in (
+                ((d["heads"] + 2 * d["kv_heads"]) * d["head"], d["hidden"]), (d["hidden"], d["heads"] * d["head"]),
+                (d["ffn"], d["hidden"]), (d["ffn"], d["hidden"]), (d["hidden"], d["ffn"])))
+            # the caches are ~3/4 full in the seeded case (past lengths uniform in [cache / 2, cache))
+            kvbytes = 2 * d["batch"] * d["kv_heads"] * int(0.75 * d["cache"]) * d["head"] * 2
+            out[name] = {"us_per_layer": us, "launches_per_layer": layers_r[0].launches,
+                         "tokens_per_s_at_this_depth": d["batch"] / (layers * us * 1e-6), "layers": layers,
+                         "weight_and_cache_gbs": (wbytes + kvbytes) / us / 1e3,
+                         "frac_of_measured_hbm": (wbytes + kvbytes) / us / 1e3 / float(peaks["hbm_gbs"]),
+                         "what": "one decoder layer per eval() through make_target(\"cuda\") -> compile -> eval, "
+                                 "weights + the read part of the KV caches / time"}
+            for r in layers_r:
+                r.close()
+        except RuntimeError as e:
+            out[name] = {"error": str(e)[:300]}
     return out
 
 

@@ -25,7 +25,7 @@ CASES = ["c1_small", "c1_semantic", "int8_gelu", "int8_per_tensor", "fp8_gelu", 
          "int4_group_k28672", "int4_group_k96", "quant_dot_transposed_a",
          "pass_quantize_int8", "pass_quantize_fp8", "pass_int4_weights_decode", "pass_int4_weights_prefill",
          "gqa_decode_small", "gqa_prompt_small", "gqa_decode_rotary_op", "gqa_decode_d64_f4", "gqa_decode_d128_f2",
-         "gqa_decode_d64_f8"]
+         "gqa_decode_d64_f8", "llama_layer_small", "llama_layer_small_d128"]
 
 # The configurations of the benchmark at their real dimensions.  Where MIGraphX's CPU interpreter
 # would need minutes, it evaluates a seeded sample of rows of the same problem (same weights) and
@@ -38,7 +38,7 @@ C4_LINEARS = [f"c4_m{m}_n{n}_k{k}" for m in (1, 16, 512)
 C5_LINEARS = [f"c5_m16_n{n}_k{k}" for (n, k) in ((8192, 8192), (1024, 8192), (28672, 8192), (8192, 28672),
                                                   (4096, 8192), (512, 8192), (14336, 8192), (8192, 14336),
                                                   (8192, 4096))]
-CONFIG_SIZE = (["c2_layer", "c2_layers2", "c4_attention_decode", "c4_attention_decode_b16", "c5_attention_decode_tp8", "int8_8192", "int8_8192_raw", "int4_heavy_tail_m1", "int4_heavy_tail_m16",
+CONFIG_SIZE = (["c2_layer", "c2_layers2", "c4_layer_decode", "c5_layer_decode_tp8", "c4_attention_decode", "c4_attention_decode_b16", "c5_attention_decode_tp8", "int8_8192", "int8_8192_raw", "int4_heavy_tail_m1", "int4_heavy_tail_m16",
                 "int4_heavy_tail_m512"] + C2_LINEARS + C3_SWEEP + C4_LINEARS + C5_LINEARS)
 
 

@@ -266,3 +266,13 @@ def test_activation_and_quantizelinear_table_is_opt_in():
     lines = [l for l in out.splitlines() if "cuda::qgemm" in l and "has_lut=1" in l]
     assert len(lines) == 1 and "act=2" in lines[0] and "write_d=0" in lines[0]
     assert "int8_type, {65536}" in out
+
+
+def test_llama_decoder_layer_lowers_to_int4_linears_cache_appends_and_decode_attention():
+    # RMSNorm (parser decomposition), five MatMulNBits linears, GroupQueryAttention decomposition with
+    # KV cache, SwiGLU, residual adds: every operator has a kernel, the layer is one graph_run
+    out = _passes("llama_layer_small")
+    assert out.count("cuda::w4a16[") == 5
+    assert out.count("cuda::concat_past_present") == 2 and out.count("cuda::gqa_decode_attention") == 1
+    assert out.count("cuda::reduce[") == 2 and "cuda::graph_run" in out
+    assert "cuda::qgemm" not in out and "cuda::softmax" not in out
