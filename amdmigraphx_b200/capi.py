@@ -25,7 +25,7 @@ E_INVALID_ARG, E_UNSUPPORTED, E_ALIGNMENT, E_WORKSPACE, E_TOO_LARGE = -1, -2, -3
 
 EXPORTED_SYMBOLS = [
     "mgx_cuda_quantizelinear", "mgx_cuda_dequantizelinear", "mgx_cuda_unpack_int4",
-    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_ex", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_concat_past_present", "mgx_cuda_gqa_rotary_embedding", "mgx_cuda_gqa_decode_attention", "mgx_cuda_gqa_decode_supported", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
+    "mgx_cuda_pack_int4", "mgx_cuda_pointwise", "mgx_cuda_reduce", "mgx_cuda_softmax", "mgx_cuda_layernorm", "mgx_cuda_layernorm_ex", "mgx_cuda_layernorm_supported", "mgx_cuda_attention", "mgx_cuda_concat_past_present", "mgx_cuda_gqa_rotary_embedding", "mgx_cuda_rotary_embedding", "mgx_cuda_gqa_decode_attention", "mgx_cuda_gqa_decode_supported", "mgx_cuda_gather", "mgx_cuda_copy_rows", "mgx_cuda_qgemm_workspace", "mgx_cuda_qgemm", "mgx_cuda_qgemm_ex",
     "mgx_cuda_qgemm_static_scratch_limit", "mgx_cuda_qgemm_static_scratch",
     "mgx_cuda_transpose_8bit", "mgx_cuda_w4a16_workspace", "mgx_cuda_w4a16_gemv",
     "mgx_cuda_w4a16_gemm", "mgx_cuda_w4a16", "mgx_cuda_device_status",
@@ -311,10 +311,11 @@ class LayernormDesc(ctypes.Structure):
     _fields_ = [("rows", ctypes.c_int64), ("cols", ctypes.c_int64), ("ldx", ctypes.c_int64),
                 ("ldy", ctypes.c_int64), ("ldq", ctypes.c_int64), ("type", ctypes.c_int32),
                 ("eps", ctypes.c_float), ("q_type", ctypes.c_int32), ("q_scale", ctypes.c_float),
-                ("q_zero_point", ctypes.c_float), ("reserved", ctypes.c_int32)]
+                ("q_zero_point", ctypes.c_float), ("flags", ctypes.c_int32)]
 
 
-def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0, write_y=True, dq_scale=None):
+def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0, write_y=True, dq_scale=None,
+              rms=False):
     """LayerNorm over the last axis of a 2-D tensor; returns (y or None, q or None) where q is the
     int8 quantizelinear(y, q_scale, q_zero_point) written by the same launch; with dq_scale a third
     tensor, dequantizelinear(q, dq_scale, q_zero_point) in x's type, is returned too."""
@@ -324,7 +325,7 @@ def layernorm(x, gamma=None, beta=None, eps=1e-5, q_scale=None, q_zero_point=0.0
     y = torch.empty_like(x) if write_y else None
     q = torch.empty((rows, cols), dtype=torch.int8, device=x.device) if q_scale is not None else None
     d = LayernormDesc(rows=rows, cols=cols, ldx=x.stride(0), ldy=cols, ldq=cols, type=_dtype_code(x), eps=eps,
-                      q_type=I8, q_scale=float(q_scale or 1.0), q_zero_point=float(q_zero_point), reserved=0)
+                      q_type=I8, q_scale=float(q_scale or 1.0), q_zero_point=float(q_zero_point), flags=1 if rms else 0)
     if dq_scale is not None:
         dq = torch.empty_like(x)
         lib.mgx_cuda_layernorm_ex.argtypes = [ctypes.POINTER(LayernormDesc)] + [ctypes.c_void_p] * 6 + \
@@ -374,6 +375,24 @@ def gqa_rotary_embedding(qkv, seqlens, cos_cache, sin_cache, heads, kv_heads, in
                                             cos_cache.shape[1] * 2, _ptr(seqlens),
                                             I64 if seqlens.dtype == torch.int64 else I32, 1 if interleaved else 0,
                                             _ptr(out), _stream()), "mgx_cuda_gqa_rotary_embedding")
+    return out
+
+
+def rotary_embedding(x, positions, cos_cache, sin_cache):
+    """The rotary_embedding builder's rotation of x [batch, heads, seq, head] (rows contiguous, any other
+    strides) at positions [batch, seq]; returns a packed tensor."""
+    import torch
+    lib = load()
+    batch, heads, seq, head = x.shape
+    out = torch.empty((batch, heads, seq, head), dtype=x.dtype, device=x.device)
+    strides = (ctypes.c_int64 * 3)(x.stride(0), x.stride(1), x.stride(2))
+    lib.mgx_cuda_rotary_embedding.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)] + \
+        [ctypes.c_int64] * 4 + [ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                ctypes.c_void_p, ctypes.c_void_p]
+    check(lib.mgx_cuda_rotary_embedding(_ptr(x), _dtype_code(x), strides, batch, heads, seq, head, _ptr(positions),
+                                        I64 if positions.dtype == torch.int64 else I32, _ptr(cos_cache),
+                                        _ptr(sin_cache), cos_cache.shape[0], _ptr(out), _stream()),
+          "mgx_cuda_rotary_embedding")
     return out
 
 

@@ -134,7 +134,93 @@ __global__ void gqa_rotary_kernel(const rope_params p)
     }
 }
 
+// The rotation of the rotary_embedding builder (src/op/builder/rotary_embedding.cpp:177-230,
+// non-interleaved): out = x * cos + concat(x[half:], x[:half]) * (signs * sin), every product and the
+// sum stored in T (half: truncated) as the builder's separate mul / mul / mul / add operators do;
+// cos / sin rows gathered at positions[b, s].  x: [batch, heads, seq, head] with element strides
+// sb / sh / ss (rows contiguous); out packed.
+struct rope_builder_params
+{
+    const void* x;
+    void* out;
+    const void* cosc;
+    const void* sinc;
+    const void* pos;
+    int pos_i64;
+    int64_t sb, sh, ss;
+    int64_t batch, heads, seq, head, max_pos;
+};
+
+template <class T>
+__global__ void rotary_builder_kernel(const rope_builder_params p)
+{
+    const int64_t n = p.batch * p.heads * p.seq * p.head;
+    const T* in     = static_cast<const T*>(p.x);
+    T* out          = static_cast<T*>(p.out);
+    const T* cosc   = static_cast<const T*>(p.cosc);
+    const T* sinc   = static_cast<const T*>(p.sinc);
+    const int half  = static_cast<int>(p.head / 2);
+    for(int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < n;
+        idx += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    {
+        const int i      = static_cast<int>(idx % p.head);
+        const int64_t s  = (idx / p.head) % p.seq;
+        const int64_t h  = (idx / (p.head * p.seq)) % p.heads;
+        const int64_t b  = idx / (p.head * p.seq * p.heads);
+        int64_t pos      = p.pos_i64 ? static_cast<const int64_t*>(p.pos)[b * p.seq + s]
+                                     : static_cast<int64_t>(static_cast<const int32_t*>(p.pos)[b * p.seq + s]);
+        if(pos < 0)
+            pos += p.max_pos; // gathernd counts negative indices from the end
+        pos = pos < 0 ? 0 : (pos >= p.max_pos ? p.max_pos - 1 : pos);
+        const T* row   = in + b * p.sb + h * p.sh + s * p.ss;
+        const int ci   = i < half ? i : i - half;
+        const float x  = rope_load(row, i);
+        const float xr = rope_load(row, i < half ? i + half : i - half);
+        const float c  = rope_load(cosc, pos * half + ci);
+        const float sn = rope_load(sinc, pos * half + ci);
+        const float ss = i < half ? -sn : sn; // signs * sin: exact
+        if constexpr(std::is_same<T, float>::value)
+            out[idx] = __fadd_rn(__fmul_rn(x, c), __fmul_rn(xr, ss));
+        else
+        {
+            const float t1 = truncate_to_half_precision(__fmul_rn(x, c));
+            const float t2 = truncate_to_half_precision(__fmul_rn(xr, ss));
+            out[idx]       = __float2half_rz(__fadd_rn(t1, t2));
+        }
+    }
+}
+
 } // namespace mgx
+
+extern "C" int mgx_cuda_rotary_embedding(const void* x, int type, const int64_t x_strides[3], int64_t batch,
+                                         int64_t heads, int64_t seq, int64_t head, const void* positions,
+                                         int positions_type, const void* cos_cache, const void* sin_cache,
+                                         int64_t max_pos, void* out, void* stream_)
+{
+    using namespace mgx;
+    if(x == nullptr or out == nullptr or cos_cache == nullptr or sin_cache == nullptr or positions == nullptr or
+       x_strides == nullptr)
+        return MGX_E_INVALID_ARG;
+    if(batch <= 0 or heads <= 0 or seq <= 0 or head <= 0 or head % 2 != 0 or max_pos <= 0)
+        return MGX_E_INVALID_ARG;
+    if(type != MGX_F16 and type != MGX_F32)
+        return MGX_E_UNSUPPORTED;
+    if(positions_type != MGX_I32 and positions_type != MGX_I64)
+        return MGX_E_UNSUPPORTED;
+    rope_builder_params p{};
+    p.x = x, p.out = out, p.cosc = cos_cache, p.sinc = sin_cache, p.pos = positions;
+    p.pos_i64 = positions_type == MGX_I64 ? 1 : 0;
+    p.sb = x_strides[0], p.sh = x_strides[1], p.ss = x_strides[2];
+    p.batch = batch, p.heads = heads, p.seq = seq, p.head = head, p.max_pos = max_pos;
+    const int64_t n       = batch * heads * seq * head;
+    const unsigned blocks = static_cast<unsigned>((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    cudaStream_t stream   = static_cast<cudaStream_t>(stream_);
+    if(type == MGX_F16)
+        rotary_builder_kernel<__half><<<blocks, 256, 0, stream>>>(p);
+    else
+        rotary_builder_kernel<float><<<blocks, 256, 0, stream>>>(p);
+    return static_cast<int>(cudaGetLastError());
+}
 
 extern "C" int mgx_cuda_concat_past_present(const void* present, const int64_t present_strides[3], int64_t batch,
                                             int64_t kv_heads, int64_t seq, int64_t head_bytes, const void* seqlens,

@@ -46,6 +46,7 @@ struct ln_params
     float q_scale, q_rcp, q_zp;
     float dq_scale;
     int q_fp8;
+    int rms; // RMS normalisation: no mean, squares and their mean in fp32 (see mgx_layernorm_desc::flags)
 };
 
 // T: float or __half.  NV: 16-byte vectors per lane (a lane owns vectors lane, lane + 32, ...).
@@ -100,16 +101,32 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
         sum += __shfl_xor_sync(0xffffffffu, sum, o);
     const float mean = ln_round<T>(sum * p.inv_n);
     float sq = 0.0f;
-#pragma unroll
-    for(int i = 0; i < NV; ++i)
+    if(p.rms)
     {
-        if(lane + 32 * i < nvec)
-        {
+        // SimplifiedLayerNormalization (src/onnx/parse_simplified_layer_normalization.cpp:91-106): x is
+        // converted to float, squared and averaged in fp32; only the mean is stored in T again
 #pragma unroll
-            for(int j = 0; j < VE; ++j)
+        for(int i = 0; i < NV; ++i)
+            if(lane + 32 * i < nvec)
             {
-                v[i][j] = ln_round<T>(v[i][j] - mean);
-                sq += ln_round<T>(v[i][j] * v[i][j]);
+#pragma unroll
+                for(int j = 0; j < VE; ++j)
+                    sq += __fmul_rn(v[i][j], v[i][j]);
+            }
+    }
+    else
+    {
+#pragma unroll
+        for(int i = 0; i < NV; ++i)
+        {
+            if(lane + 32 * i < nvec)
+            {
+#pragma unroll
+                for(int j = 0; j < VE; ++j)
+                {
+                    v[i][j] = ln_round<T>(v[i][j] - mean);
+                    sq += ln_round<T>(v[i][j] * v[i][j]);
+                }
             }
         }
     }
@@ -330,6 +347,7 @@ extern "C" int mgx_cuda_layernorm_ex(const mgx_layernorm_desc* d, const void* x,
     p.q_rcp   = q != nullptr ? static_cast<float>(1.0 / static_cast<double>(d->q_scale)) : 0.0f;
     p.q_zp    = d->q_zero_point;
     p.q_fp8   = d->q_type == MGX_FP8_E4M3FN ? 1 : 0;
+    p.rms     = (d->flags & MGX_LAYERNORM_RMS) != 0 ? 1 : 0;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
     return d->type == MGX_F16 ? launch_layernorm<__half>(p, stream) : launch_layernorm<float>(p, stream);
 }

@@ -353,10 +353,11 @@ struct op_layernorm
     bool write_y   = true;
     bool has_dq    = false;
     float dq_scale = 1.0f;
+    bool rms       = false; // RMS normalisation (MGX_LAYERNORM_RMS): no mean, no beta
     template <class Self, class F>
     static auto reflect(Self& self, F f)
     {
-        return pack(f(self.eps, "eps"), f(self.has_gamma, "has_gamma"), f(self.has_beta, "has_beta"),
+        return pack(f(self.rms, "rms"), f(self.eps, "eps"), f(self.has_gamma, "has_gamma"), f(self.has_beta, "has_beta"),
                     f(self.q_type, "q_type"), f(self.q_scale, "q_scale"), f(self.q_zp, "q_zp"),
                     f(self.write_y, "write_y"), f(self.has_dq, "has_dq"), f(self.dq_scale, "dq_scale"));
     }
@@ -475,6 +476,18 @@ struct op_gqa_rotary_embedding
                     f(self.interleaved, "interleaved"));
     }
     std::string name() const { return "cuda::gqa_rotary_embedding"; }
+    shape compute_shape(const std::vector<shape>& inputs) const;
+    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
+    std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }
+};
+
+// The rotation the rotary_embedding builder emits (src/op/builder/rotary_embedding.cpp:60-230,
+// non-interleaved: gathernd of the cos / sin rows, concat, rotate-half, mul, mul, mul, add) as one
+// launch.  Inputs: x [B, heads, S, D] (rows contiguous), positions [B, S, 1], cos cache, sin cache
+// [max_pos, D / 2], out [B, heads, S, D] (packed).
+struct op_rotary_embedding
+{
+    std::string name() const { return "cuda::rotary_embedding"; }
     shape compute_shape(const std::vector<shape>& inputs) const;
     argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
     std::vector<std::size_t> output_alias(const std::vector<shape>& s) const { return {s.size() - 1}; }

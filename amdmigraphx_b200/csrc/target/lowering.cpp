@@ -1094,6 +1094,141 @@ struct lowerer
         return true;
     }
 
+    // ---------------------------------------------------------------- rotary embedding (builder form)
+    // add(mul(X, C), mul(concat(X[half:], X[:half]), mul(signs, S))) with C / S the cos / sin rows
+    // gathernd-ed at the positions, doubled along the last axis and broadcast over the heads
+    // (src/op/builder/rotary_embedding.cpp:60-230, non-interleaved): one cuda::rotary_embedding.
+    bool lower_rotary(instruction_ref add)
+    {
+        if(fusion_disabled("rotary") or add->name() != "add" or add->inputs().size() != 2)
+            return false;
+        const auto& os = add->get_shape();
+        if(os.ndim() != 4 or (os.type() != shape::half_type and os.type() != shape::float_type) or os.lens()[3] % 2 != 0)
+            return false;
+        const std::size_t d = os.lens()[3], half = d / 2;
+        auto is_axis_last = [&](instruction_ref c) {
+            const auto ax = c->get_operator().to_value().at("axis").to<int64_t>();
+            return ax == -1 or ax == static_cast<int64_t>(c->get_shape().ndim()) - 1;
+        };
+        // multibroadcast(reshape[B,1,S,D](concat(G, G))), G = gathernd(cache, idx); returns {cache, idx}
+        std::vector<instruction_ref> chain = {add};
+        auto cache_rows = [&](instruction_ref x) -> std::pair<instruction_ref, instruction_ref> {
+            const std::pair<instruction_ref, instruction_ref> none{m.end(), m.end()};
+            if(x->name() == "multibroadcast")
+            {
+                chain.push_back(x);
+                x = x->inputs().front();
+            }
+            if(x->name() != "reshape" and x->name() != "reshape_lazy")
+                return none;
+            const auto& rl = x->get_shape().lens();
+            if(rl.size() != 4 or rl[0] != os.lens()[0] or rl[1] != 1 or rl[2] != os.lens()[2] or rl[3] != d)
+                return none;
+            auto cc = x->inputs().front();
+            if(cc->name() != "concat" or not is_axis_last(cc) or cc->inputs().size() != 2 or
+               cc->inputs()[0] != cc->inputs()[1])
+                return none;
+            auto gn = cc->inputs()[0];
+            if(gn->name() != "gathernd" or gn->get_operator().to_value().at("batch_dims").to<int64_t>() != 0)
+                return none;
+            chain.insert(chain.end(), {x, cc, gn});
+            return {gn->inputs()[0], gn->inputs()[1]};
+        };
+        for(int swap = 0; swap < 2; ++swap)
+        {
+            auto mc = add->inputs()[swap], ms2 = add->inputs()[1 - swap];
+            if(mc->name() != "mul" or ms2->name() != "mul" or mc->outputs().size() != 1 or ms2->outputs().size() != 1)
+                continue;
+            // ms2 = mul(rotated, mul(signs, sin))
+            instruction_ref rot = m.end(), msin = m.end();
+            for(auto i : ms2->inputs())
+            {
+                if(i->name() == "concat")
+                    rot = i;
+                else if(i->name() == "mul")
+                    msin = i;
+            }
+            if(rot == m.end() or msin == m.end() or not is_axis_last(rot) or rot->inputs().size() != 2)
+                continue;
+            auto s2 = rot->inputs()[0], s1 = rot->inputs()[1];
+            auto is_slice = [&](instruction_ref sl, std::size_t lo, std::size_t hi) {
+                if(sl->name() != "slice")
+                    return false;
+                const auto v  = sl->get_operator().to_value();
+                const auto ax = v.at("axes").to_vector<int64_t>();
+                return ax.size() == 1 and (ax[0] == -1 or ax[0] == 3) and
+                       v.at("starts").to_vector<int64_t>() == std::vector<int64_t>{static_cast<int64_t>(lo)} and
+                       v.at("ends").to_vector<int64_t>() == std::vector<int64_t>{static_cast<int64_t>(hi)};
+            };
+            if(not is_slice(s2, half, d) or not is_slice(s1, 0, half) or s1->inputs()[0] != s2->inputs()[0])
+                continue;
+            auto x = s1->inputs()[0];
+            if(x->get_shape().lens() != os.lens() or x->get_shape().strides().back() != 1)
+                continue;
+            // mc = mul(x, cos rows)
+            if(mc->inputs()[0] != x and mc->inputs()[1] != x)
+                continue;
+            auto cosb = mc->inputs()[0] == x ? mc->inputs()[1] : mc->inputs()[0];
+            // msin = mul(signs, sin rows): signs constant, -1 on the first half of every row, +1 on the second
+            instruction_ref sg = m.end(), sinb = m.end();
+            for(auto i : msin->inputs())
+            {
+                if(i->can_eval())
+                    sg = i;
+                else
+                    sinb = i;
+            }
+            if(sg == m.end() or sinb == m.end() or sg->get_shape().lens() != os.lens())
+                continue;
+            bool signs_ok = true;
+            sg->eval().visit([&](auto view) {
+                for(std::size_t i = 0; i < view.size() and signs_ok; ++i)
+                    signs_ok = static_cast<float>(view[i]) == ((i % d) < half ? -1.0f : 1.0f);
+            });
+            if(not signs_ok)
+                continue;
+            const std::size_t mark = chain.size();
+            auto cr = cache_rows(cosb);
+            auto sr = cache_rows(sinb);
+            if(cr.first == m.end() or sr.first == m.end() or cr.second != sr.second)
+            {
+                chain.resize(mark);
+                continue;
+            }
+            auto idx       = cr.second;
+            const auto& is = idx->get_shape();
+            const auto& cs = cr.first->get_shape();
+            if(is.elements() != os.lens()[0] * os.lens()[2] or is.lens().back() != 1 or
+               (is.type() != shape::int32_type and is.type() != shape::int64_type) or cs.type() != os.type() or
+               cs.ndim() != 2 or cs.lens()[1] != half or sr.first->get_shape().lens() != cs.lens() or
+               sr.first->get_shape().type() != os.type())
+            {
+                chain.resize(mark);
+                continue;
+            }
+            chain.insert(chain.end(), {mc, ms2, rot, s1, s2, msin});
+            for(auto c : chain)
+            {
+                consume(c);
+                for(auto i : c->inputs())
+                    if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
+                        consume(i);
+            }
+            auto pos = idx;
+            if(not is.standard())
+                pos = standard_copy(add, idx);
+            auto cosc = cr.first, sinc = sr.first;
+            if(not cosc->get_shape().standard())
+                cosc = standard_copy(add, cosc);
+            if(not sinc->get_shape().standard())
+                sinc = standard_copy(add, sinc);
+            auto buf = insert_allocation(m, add, os.as_standard());
+            consume(m.replace_instruction(add, op_rotary_embedding{}, x, pos, cosc, sinc, buf));
+            return true;
+        }
+        return false;
+    }
+
     // ---------------------------------------------------------------- decode-step GQA attention
     // softmax(where(position > seqlens_k, -inf, mul(dot(Q, transpose(K')), scale))) followed by
     // dot(P, V'), K' / V' the caches with their KV heads broadcast to the query heads, one query
@@ -1446,6 +1581,107 @@ struct lowerer
         }
         if(dqz != m.end())
             consume(m.replace_instruction(dqz, op_second_output{}, rep, dqbuf));
+        return true;
+    }
+
+    // ---------------------------------------------------------------- RMSNorm
+    // SimplifiedLayerNormalization as the parser decomposes it
+    // (src/onnx/parse_simplified_layer_normalization.cpp:91-106): fx = convert<float>(x);
+    // ms = convert<T>(reduce_mean(mul(fx, fx))); rr = rsqrt(add(ms, eps)); y = mul(mul(x, bcast(rr)), gamma)
+    // becomes one cuda::layernorm with rms set.
+    bool lower_rmsnorm(instruction_ref rm)
+    {
+        if(fusion_disabled("layernorm") or rm->inputs().size() != 1 or rm->outputs().size() != 1)
+            return false;
+        auto sq = rm->inputs().front();
+        if(sq->name() != "mul" or sq->inputs()[0] != sq->inputs()[1] or sq->outputs().size() != 1)
+            return false;
+        auto fx = sq->inputs()[0];
+        auto x  = fx;
+        std::vector<instruction_ref> chain = {rm, sq};
+        if(fx->name() == "convert" and fx->get_shape().type() == shape::float_type)
+        {
+            if(fx->outputs().size() != 1)
+                return false;
+            x = fx->inputs().front();
+            chain.push_back(fx);
+        }
+        const auto& xs = x->get_shape();
+        const auto nd  = xs.ndim();
+        if(nd < 2 or not xs.standard() or (xs.type() != shape::float_type and xs.type() != shape::half_type))
+            return false;
+        if(not mgx_cuda_layernorm_supported(xs.type() == shape::half_type ? MGX_F16 : MGX_F32,
+                                            static_cast<int64_t>(xs.lens().back())))
+            return false;
+        auto axes = rm->get_operator().to_value().at("axes").to_vector<int64_t>();
+        if(axes.size() != 1 or (axes[0] != -1 and axes[0] != static_cast<int64_t>(nd) - 1))
+            return false;
+        auto cur = single_user(m, rm);
+        if(valid(cur, m) and cur->name() == "convert" and cur->get_shape().type() == xs.type())
+        {
+            chain.push_back(cur);
+            cur = single_user(m, cur);
+        }
+        else if(xs.type() != shape::float_type)
+            return false;
+        if(not valid(cur, m) or cur->name() != "add")
+            return false;
+        auto ve = cur;
+        instruction_ref ecst = m.end();
+        for(auto i : ve->inputs())
+            if(i->can_eval())
+                ecst = i;
+        if(ecst == m.end())
+            return false;
+        auto ec = classify_constant(ecst);
+        if(ec.kind != bcast_kind::scalar)
+            return false;
+        auto rs = single_user(m, ve);
+        if(not valid(rs, m) or rs->name() != "rsqrt")
+            return false;
+        auto mb = single_user(m, rs);
+        if(not valid(mb, m) or mb->name() != "multibroadcast" or mb->get_shape().lens() != xs.lens())
+            return false;
+        auto nv = single_user(m, mb);
+        if(not valid(nv, m) or nv->name() != "mul" or other_input(nv, mb) != x)
+            return false;
+        chain.insert(chain.end(), {ve, rs, mb, nv});
+        op_layernorm op;
+        op.rms = true;
+        op.eps = ec.values[0];
+        instruction_ref last = nv;
+        std::vector<instruction_ref> args = {x};
+        auto u = single_user(m, last);
+        if(valid(u, m) and u->name() == "mul" and other_input(u, last)->can_eval())
+        {
+            auto cv = classify_constant(other_input(u, last));
+            if(cv.kind == bcast_kind::scalar)
+                cv.values.assign(xs.lens().back(), cv.values[0]);
+            if(cv.kind == bcast_kind::scalar or cv.kind == bcast_kind::per_col)
+            {
+                instruction_ref g;
+                if(xs.type() == shape::half_type)
+                {
+                    std::vector<half> h(cv.values.begin(), cv.values.end());
+                    g = m.add_literal(literal{shape{shape::half_type, {h.size()}}, h});
+                }
+                else
+                    g = add_float_literal(m, cv.values);
+                op.has_gamma = true;
+                args.push_back(g);
+                chain.push_back(u);
+                last = u;
+            }
+        }
+        for(auto c : chain)
+        {
+            consume(c);
+            for(auto i : c->inputs())
+                if(i->can_eval() and i->outputs().size() == 1 and not is_builtin(i->name()))
+                    consume(i);
+        }
+        args.push_back(insert_allocation(m, last, last->get_shape().as_standard()));
+        consume(m.replace_instruction(last, op, args));
         return true;
     }
 
@@ -1812,6 +2048,10 @@ struct lowerer
                 if(not lower_gqa_decode(ins))
                     lower_attention(ins);
             }
+        // the rotary-embedding builder's rotation
+        for(auto ins : order)
+            if(not skip(ins) and ins->name() == "add")
+                lower_rotary(ins);
         // GEMM sub-graphs next: their operands (packed int4 weights, scale expressions) must
         // still be in their original form, not folded into dense constants
         for(auto ins : order)
@@ -1832,7 +2072,10 @@ struct lowerer
             if(skip(ins))
                 continue;
             if(ins->name() == "reduce_mean" and ins->inputs().size() == 1)
-                lower_layernorm(ins);
+            {
+                if(not lower_rmsnorm(ins))
+                    lower_layernorm(ins);
+            }
         }
         for(auto ins : order)
         {

@@ -533,6 +533,7 @@ argument op_layernorm::compute(context& ctx, const shape&, const std::vector<arg
     d.ldq  = qbuf != nullptr ? as_matrix(qbuf->get_shape(), "layernorm quantised output").ld : 0;
     d.type = mgx_type(args[0].get_shape().type());
     d.eps  = eps;
+    d.flags = rms ? MGX_LAYERNORM_RMS : 0;
     if(qbuf != nullptr)
     {
         d.q_type       = mgx_type(static_cast<shape::type_t>(q_type));
@@ -668,6 +669,42 @@ argument op_gqa_rotary_embedding::compute(context& ctx, const shape&, const std:
                   args[2].data(), args[3].data(), static_cast<int64_t>(c.lens()[0]), static_cast<int64_t>(c.lens()[1]) * 2,
                   args[1].data(), index_type(args[1].get_shape().type()), interleaved ? 1 : 0, out.data(), ctx.stream()),
               "mgx_cuda_gqa_rotary_embedding");
+    return out;
+}
+
+shape op_rotary_embedding::compute_shape(const std::vector<shape>& inputs) const
+{
+    check_shapes{inputs, *this}.has(5);
+    const auto& x = inputs[0];
+    if(x.ndim() != 4 or x.strides().back() != 1 or x.lens()[3] % 2 != 0 or
+       (x.type() != shape::half_type and x.type() != shape::float_type))
+        MIGRAPHX_THROW("cuda::rotary_embedding: expects fp16 / fp32 [B, heads, S, D] with contiguous rows");
+    if(inputs[1].elements() != x.lens()[0] * x.lens()[2] or not inputs[1].standard() or
+       (inputs[1].type() != shape::int32_type and inputs[1].type() != shape::int64_type))
+        MIGRAPHX_THROW("cuda::rotary_embedding: expects one int32 / int64 position per (batch entry, row)");
+    for(int i : {2, 3})
+        if(inputs[i].type() != x.type() or inputs[i].ndim() != 2 or not inputs[i].standard() or
+           inputs[i].lens()[1] * 2 != x.lens()[3] or inputs[i].lens() != inputs[2].lens())
+            MIGRAPHX_THROW("cuda::rotary_embedding: expects packed [max_pos, D / 2] caches of x's type");
+    if(inputs[4].lens() != x.lens() or inputs[4].type() != x.type() or not inputs[4].standard())
+        MIGRAPHX_THROW("cuda::rotary_embedding: output must be a packed tensor of x's shape");
+    return inputs[4];
+}
+
+argument op_rotary_embedding::compute(context& ctx, const shape&, const std::vector<argument>& args) const
+{
+    const auto& out = args.back();
+    if(ctx.replaying())
+        return out;
+    const auto& x = args[0].get_shape();
+    const int64_t strides[3] = {static_cast<int64_t>(x.strides()[0]), static_cast<int64_t>(x.strides()[1]),
+                                static_cast<int64_t>(x.strides()[2])};
+    check_mgx(mgx_cuda_rotary_embedding(args[0].data(), mgx_type(x.type()), strides, static_cast<int64_t>(x.lens()[0]),
+                                        static_cast<int64_t>(x.lens()[1]), static_cast<int64_t>(x.lens()[2]),
+                                        static_cast<int64_t>(x.lens()[3]), args[1].data(),
+                                        index_type(args[1].get_shape().type()), args[2].data(), args[3].data(),
+                                        static_cast<int64_t>(args[2].get_shape().lens()[0]), out.data(), ctx.stream()),
+              "mgx_cuda_rotary_embedding");
     return out;
 }
 
@@ -851,6 +888,7 @@ MIGRAPHX_REGISTER_OP(op_attention)
 MIGRAPHX_REGISTER_OP(op_concat_past_present)
 MIGRAPHX_REGISTER_OP(op_gqa_rotary_embedding)
 MIGRAPHX_REGISTER_OP(op_gqa_decode_attention)
+MIGRAPHX_REGISTER_OP(op_rotary_embedding)
 MIGRAPHX_REGISTER_OP(op_pointwise)
 MIGRAPHX_REGISTER_OP(op_second_output)
 MIGRAPHX_REGISTER_OP(op_align_anchor)

@@ -181,8 +181,13 @@ typedef struct mgx_layernorm_desc
     int32_t q_type; /* mgx_dtype of q (MGX_I8 | MGX_FP8_E4M3FN); ignored when q == NULL */
     float q_scale;
     float q_zero_point;
-    int32_t reserved;
+    int32_t flags;  /* 0 | MGX_LAYERNORM_RMS */
 } mgx_layernorm_desc;
+/* RMS normalisation as the SimplifiedLayerNormalization parser decomposes it
+ * (src/onnx/parse_simplified_layer_normalization.cpp:91-106): y = x * rsqrt(mean(float(x)^2) + eps) *
+ * gamma; the squares and their mean in fp32, the mean, the sum with eps, the rsqrt and the two products
+ * stored in x's type.  beta must be NULL. */
+#define MGX_LAYERNORM_RMS 1
 
 MGX_API int mgx_cuda_layernorm_supported(int type, int64_t cols);
 MGX_API int mgx_cuda_layernorm(const mgx_layernorm_desc* d, const void* x, const void* gamma, const void* beta,
@@ -248,6 +253,18 @@ MGX_API int mgx_cuda_gqa_rotary_embedding(const void* qkv, int type, int64_t bat
                                           int64_t seq, int64_t head, const void* cos_cache, const void* sin_cache,
                                           int64_t max_seq, int64_t rotary_dim, const void* seqlens, int seqlens_type,
                                           int interleaved, void* out, void* stream);
+
+/* The rotation of the rotary_embedding builder, non-interleaved
+ * (src/op/builder/rotary_embedding.cpp:60-230: gathernd of the cos / sin rows at the positions,
+ * rotate-half, mul, mul, mul, add) as one launch with that chain's roundings: out = x * cos +
+ * concat(x[half:], x[:half]) * (signs * sin), every product and the sum stored in the tensor's type.
+ * x: [batch, heads, seq, head] with element strides x_strides = {batch, head, row} (rows
+ * contiguous); positions [batch * seq] (MGX_I32 | MGX_I64); caches [max_pos, head / 2] in x's type;
+ * out packed.  type: MGX_F16 | MGX_F32. */
+MGX_API int mgx_cuda_rotary_embedding(const void* x, int type, const int64_t x_strides[3], int64_t batch,
+                                      int64_t heads, int64_t seq, int64_t head, const void* positions,
+                                      int positions_type, const void* cos_cache, const void* sin_cache,
+                                      int64_t max_pos, void* out, void* stream);
 
 /* Decode-step attention against the fp16 KV cache, one launch: for every batch entry b and query
  * head h (sharing KV head h / (heads / kv_heads)), softmax(scale * q K^T) V over the cache

@@ -359,6 +359,38 @@ def gqa_rotary_embedding(qkv, seqlens, cos_cache, sin_cache, heads, kv_heads, in
     return out
 
 
+def rotary_builder_chain(x, positions, cos_cache, sin_cache):
+    """The rotary_embedding builder's rotation (src/op/builder/rotary_embedding.cpp:60-230,
+    non-interleaved) on fp16 x [batch, heads, seq, head]: cos / sin rows gathered at positions
+    [batch, seq] and doubled; mul(x, cos), mul(signs, sin), mul(rotate_half(x), .), add - every
+    operator stores half (truncating)."""
+    x = np.asarray(x, dtype=np.float16)
+    half = x.shape[3] // 2
+    pos = np.asarray(positions).reshape(x.shape[0], x.shape[2])
+    c = np.concatenate([cos_cache[pos], cos_cache[pos]], axis=-1)[:, None, :, :].astype(np.float32)
+    sn = np.concatenate([sin_cache[pos], sin_cache[pos]], axis=-1)[:, None, :, :].astype(np.float32)
+    signs = np.concatenate([-np.ones(half, np.float32), np.ones(half, np.float32)])
+    rot = np.concatenate([x[..., half:], x[..., :half]], axis=-1).astype(np.float32)
+    t1 = half_trunc(x.astype(np.float32) * c).astype(np.float32)
+    ms = half_trunc(signs * sn).astype(np.float32)
+    t2 = half_trunc(rot * ms).astype(np.float32)
+    return half_trunc(t1 + t2)
+
+
+def rmsnorm_chain(x, gamma, eps):
+    """SimplifiedLayerNormalization as the parser decomposes it
+    (src/onnx/parse_simplified_layer_normalization.cpp:91-106) on fp16 rows: squares and their mean in
+    fp32 (reduce_mean accumulates in double), the mean, mean + eps, rsqrt and the two products stored
+    in half (truncating)."""
+    x = np.asarray(x, dtype=np.float16)
+    fx = x.astype(np.float32)
+    ms = half_trunc(((fx * fx).astype(np.float64).sum(axis=-1, keepdims=True) / x.shape[-1]).astype(np.float32))
+    ve = half_trunc(ms.astype(np.float32) + np.float32(np.float16(half_trunc(np.float32(eps)))))
+    rr = half_trunc(np.float32(1.0) / np.sqrt(ve.astype(np.float32)))
+    y = half_trunc(fx * rr.astype(np.float32))
+    return half_trunc(y.astype(np.float32) * np.asarray(gamma, dtype=np.float16).astype(np.float32))
+
+
 def gqa_decode_chain(q, k_cache, v_cache, seqlens, scale):
     """The decode step of GroupQueryAttention as the parser decomposes it
     (src/onnx/parse_group_query_attention.cpp:184-262) on fp16: q [batch, heads, head] against caches

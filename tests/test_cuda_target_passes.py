@@ -209,8 +209,8 @@ def test_gqa_decode_step_becomes_cache_appends_and_one_attention_kernel():
     assert out.count("cuda::concat_past_present") == 2
     assert out.count("cuda::gqa_decode_attention[num_heads=8,kv_num_heads=2") == 1
     assert "cuda::softmax" not in out and "cuda::qgemm" not in out
-    # the rotary embedding's cos / sin rows are gathered at the positions
-    assert out.count("cuda::gather") == 2
+    # the rotary-embedding builder's chain (gathernd of cos / sin rows, rotate-half, three muls, add)
+    assert out.count("cuda::rotary_embedding") == 1 and "cuda::gather" not in out and "cuda::concat[" not in out
 
 
 def test_gqa_prompt_and_unsupported_head_sizes_keep_the_operator_chain():
@@ -274,5 +274,9 @@ def test_llama_decoder_layer_lowers_to_int4_linears_cache_appends_and_decode_att
     out = _passes("llama_layer_small")
     assert out.count("cuda::w4a16[") == 5
     assert out.count("cuda::concat_past_present") == 2 and out.count("cuda::gqa_decode_attention") == 1
-    assert out.count("cuda::reduce[") == 2 and "cuda::graph_run" in out
+    assert out.count("cuda::layernorm[rms=1") == 2 and out.count("cuda::rotary_embedding") == 1
+    assert "cuda::reduce[" not in out and "cuda::graph_run" in out
     assert "cuda::qgemm" not in out and "cuda::softmax" not in out
+    # 14 launches: 5 linears, 2 RMSNorms, rotary, 2 cache appends, attention, residual add,
+    # SwiGLU, residual add
+    assert out.count("cuda::pointwise[") == 3
