@@ -862,6 +862,109 @@ struct lowerer
     // V projections of an attention block) become one cuda::qgemm over the concatenated weights;
     // the former results are column slices of its output.  Only done when every reader takes
     // row-strided matrices (cuda::attention), so no slice ever has to be packed again.
+    // cuda::w4a16 operators that read the same activations (gate and up projections of a SwiGLU
+    // block) and whose results only element-wise kernels read (which take strided operands) become
+    // one operator over the concatenated packed weights, scales and zero points: one stream over the
+    // weights instead of two launches' fixed costs.
+    void fuse_horizontal_w4a16()
+    {
+        if(fusion_disabled("horizontal"))
+            return;
+        std::vector<instruction_ref> lins;
+        for(auto ins : iterator_for(m))
+            if(ins->name() == "cuda::w4a16")
+                lins.push_back(ins);
+        std::unordered_set<instruction*> done;
+        for(auto first : lins)
+        {
+            if(done.count(&*first) > 0)
+                continue;
+            const auto fop = any_cast<op_w4a16>(first->get_operator());
+            auto eligible  = [&](instruction_ref g) {
+                const auto op  = any_cast<op_w4a16>(g->get_operator());
+                const auto& in = g->inputs();
+                if(op.group != fop.group or op.zp_const != fop.zp_const or op.has_zp != fop.has_zp)
+                    return false;
+                if(in[0]->get_shape().ndim() != 2 or in[1]->name() != "@literal" or in[2]->name() != "@literal" or
+                   (op.has_zp and in[3]->name() != "@literal"))
+                    return false;
+                bool any = false;
+                for(auto o : g->outputs())
+                {
+                    if(o->name() == "cuda::pointwise" and o->inputs().back() != g)
+                        any = true;
+                    else if(not is_consumed(o))
+                        return false;
+                }
+                return any;
+            };
+            if(not eligible(first))
+                continue;
+            std::vector<instruction_ref> group = {first};
+            for(auto g : lins)
+                if(g != first and done.count(&*g) == 0 and g->inputs()[0] == first->inputs()[0] and eligible(g) and
+                   g->inputs()[1]->get_shape().lens()[1] == first->inputs()[1]->get_shape().lens()[1])
+                    group.push_back(g);
+            if(group.size() < 2)
+                continue;
+            const std::size_t k2  = first->inputs()[1]->get_shape().lens()[1]; // K / 2
+            const std::size_t gpr = first->inputs()[2]->get_shape().lens()[1]; // groups per row
+            std::vector<char> w, sc, zp;
+            std::vector<std::size_t> widths;
+            for(auto g : group)
+            {
+                auto wl = g->inputs()[1]->get_literal();
+                auto sl = g->inputs()[2]->get_literal();
+                w.insert(w.end(), wl.data(), wl.data() + wl.get_shape().bytes());
+                sc.insert(sc.end(), sl.data(), sl.data() + sl.get_shape().bytes());
+                if(fop.has_zp)
+                {
+                    auto zl = g->inputs()[3]->get_literal();
+                    zp.insert(zp.end(), zl.data(), zl.data() + zl.get_shape().bytes());
+                }
+                widths.push_back(wl.get_shape().lens()[0]);
+            }
+            std::size_t n = 0;
+            for(auto wd : widths)
+                n += wd;
+            const std::size_t mm = first->inputs()[0]->get_shape().lens()[0];
+            std::vector<instruction_ref> args = {
+                first->inputs()[0], m.add_literal(literal{shape{shape::uint8_type, {n, k2}}, w.data()}),
+                m.add_literal(literal{shape{shape::half_type, {n, gpr}}, sc.data()})};
+            if(fop.has_zp)
+                args.push_back(m.add_literal(literal{shape{shape::uint8_type, {n, gpr}}, zp.data()}));
+            instruction_ref pos = group.front();
+            for(auto ins : iterator_for(m))
+                if(std::find(group.begin(), group.end(), ins) != group.end())
+                {
+                    pos = ins;
+                    break;
+                }
+            op_w4a16 op = fop;
+            mgx_w4_desc d{};
+            d.M     = static_cast<int64_t>(mm);
+            d.N     = static_cast<int64_t>(n);
+            d.K     = static_cast<int64_t>(k2 * 2);
+            d.group = op.group;
+            const std::size_t ws = mgx_cuda_w4a16_workspace(&d);
+            op.has_workspace     = ws > 0;
+            if(ws > 0)
+                args.push_back(insert_allocation(m, pos, shape{shape::int8_type, {ws}}));
+            args.push_back(insert_allocation(m, pos, shape{shape::half_type, {mm, n}}));
+            auto fused = m.insert_instruction(pos, op, args);
+            consume(fused);
+            std::size_t c0 = 0;
+            for(std::size_t i = 0; i < group.size(); ++i)
+            {
+                done.insert(&*group[i]);
+                m.replace_instruction(group[i],
+                                      make_op("slice", {{"axes", {1}}, {"starts", {c0}}, {"ends", {c0 + widths[i]}}}),
+                                      fused);
+                c0 += widths[i];
+            }
+        }
+    }
+
     void fuse_horizontal_qgemms()
     {
         if(fusion_disabled("horizontal"))
@@ -2116,6 +2219,7 @@ struct lowerer
         // the horizontal fusion turns some results into
         dead_code_elimination{}.apply(m);
         fuse_horizontal_qgemms();
+        fuse_horizontal_w4a16();
     }
 
     // packed row-major copy of a host argument with arbitrary strides

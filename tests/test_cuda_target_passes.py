@@ -272,11 +272,13 @@ def test_llama_decoder_layer_lowers_to_int4_linears_cache_appends_and_decode_att
     # RMSNorm (parser decomposition), five MatMulNBits linears, GroupQueryAttention decomposition with
     # KV cache, SwiGLU, residual adds: every operator has a kernel, the layer is one graph_run
     out = _passes("llama_layer_small")
-    assert out.count("cuda::w4a16[") == 5
+    # packed QKV, O, gate + up as one operator over the concatenated weights, down
+    assert out.count("cuda::w4a16[") == 4
+    assert "-> half_type, {2, 1024}, {1024, 1}" in out and out.count("slice[axes={1},starts={512},ends={1024}]") == 1
     assert out.count("cuda::concat_past_present") == 2 and out.count("cuda::gqa_decode_attention") == 1
     assert out.count("cuda::layernorm[rms=1") == 2 and out.count("cuda::rotary_embedding") == 1
     assert "cuda::reduce[" not in out and "cuda::graph_run" in out
     assert "cuda::qgemm" not in out and "cuda::softmax" not in out
-    # 14 launches: 5 linears, 2 RMSNorms, rotary, 2 cache appends, attention, residual add,
+    # 13 launches: 4 linears, 2 RMSNorms, rotary, 2 cache appends, attention, residual add,
     # SwiGLU, residual add
     assert out.count("cuda::pointwise[") == 3
