@@ -9,6 +9,10 @@
 //   cuda_target_check list
 #include "programs.hpp"
 #include <migraphx/register_target.hpp>
+#include "../../../include/mgx_cuda.h"
+#include <cuda_runtime.h>
+#include <fstream>
+#include <thread>
 
 using namespace mgx_programs;
 
@@ -129,6 +133,14 @@ std::map<std::string, std::function<test_case()>> cases()
     big["llama_layer_small_d128"] = [] { return llama_decoder_layer(3, 512, 4, 4, 128, 1024, 160, 128, 72); };
     big["c4_layer_decode"]       = [] { return llama_decoder_layer(1, 4096, 32, 32, 128, 11008, 2048, 128, 73); };
     big["c5_layer_decode_tp8"]   = [] { return llama_decoder_layer(16, 8192, 8, 1, 128, 3584, 4096, 128, 74); };
+    // one rank's shard of a tensor-parallel int4 MLP with cuda::all_reduce inside the program (run as
+    // one process per GPU with MGX_TP_RANK / MGX_TP_WORLD / MGX_TP_ID_FILE set; a single process is
+    // rank 0 of 1, whose all-reduce needs no communicator partner but still a communicator)
+    big["tp_int4_mlp"] = [] {
+        const char* r = std::getenv("MGX_TP_RANK");
+        const char* w = std::getenv("MGX_TP_WORLD");
+        return tp_int4_mlp(r != nullptr ? std::stoul(r) : 0, w != nullptr ? std::stoul(w) : 1, 16, 1024, 2048, 128, 91);
+    };
     big["c2_layer"]   = [] { return c2_encoder(1, 1); };
     big["c2_layers2"] = [] { return c2_encoder(1, 2); };
     std::map<std::string, std::function<test_case()>> small = {
@@ -244,6 +256,48 @@ bool within(const cmp_result& c, const test_case& t)
 
 } // namespace
 
+// One process per GPU: rank 0 makes the NCCL id and leaves it in MGX_TP_ID_FILE, the others wait for
+// the file (at most a minute); every rank creates its communicator and makes it the default one,
+// which is what cuda::all_reduce uses.  The device of the rank is chosen by MIGRAPHX_CUDA_DEVICE.
+void join_tensor_parallel_group()
+{
+    const int rank  = std::stoi(std::getenv("MGX_TP_RANK"));
+    const int world = std::stoi(std::getenv("MGX_TP_WORLD"));
+    const std::string path = std::getenv("MGX_TP_ID_FILE");
+    const char* dev = std::getenv("MIGRAPHX_CUDA_DEVICE");
+    if(cudaSetDevice(dev != nullptr ? std::stoi(dev) : rank) != cudaSuccess)
+        throw std::runtime_error("cudaSetDevice failed");
+    std::vector<char> id(128, 0);
+    if(rank == 0)
+    {
+        if(mgx_cuda_comm_unique_id(id.data()) != 0)
+            throw std::runtime_error("mgx_cuda_comm_unique_id failed");
+        std::ofstream f(path + ".tmp", std::ios::binary);
+        f.write(id.data(), 128);
+        f.close();
+        std::rename((path + ".tmp").c_str(), path.c_str());
+    }
+    else
+    {
+        bool got = false;
+        for(int i = 0; i < 600 and not got; ++i)
+        {
+            std::ifstream f(path, std::ios::binary);
+            if(f.good() and f.read(id.data(), 128) and f.gcount() == 128)
+                got = true;
+            else
+                std::this_thread::sleep_for(std::chrono::milliseconds(100));
+        }
+        if(not got)
+            throw std::runtime_error("no NCCL id from rank 0 within a minute");
+    }
+    void* comm = nullptr;
+    const int rc = mgx_cuda_comm_create(id.data(), world, rank, &comm);
+    if(rc != 0)
+        throw std::runtime_error("mgx_cuda_comm_create failed: " + std::to_string(rc));
+    mgx_cuda_comm_set_default(comm);
+}
+
 int main(int argc, char** argv)
 {
     const auto all = cases();
@@ -265,6 +319,8 @@ int main(int argc, char** argv)
     try
     {
         g_have_device = mode != "passes";
+        if(mode != "passes" and std::getenv("MGX_TP_ID_FILE") != nullptr)
+            join_tensor_parallel_group();
         const auto tb0 = std::chrono::steady_clock::now();
         test_case t = all.at(name)();
         const double build_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - tb0).count();

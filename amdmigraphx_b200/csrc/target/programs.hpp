@@ -1361,6 +1361,76 @@ inline test_case llama_decoder_layer(std::size_t batch, std::size_t hidden, std:
     return t;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-parallel int4 MLP of one rank (config 5's sharding): up projection split by output
+// columns, down projection by input rows, the partial result summed over the ranks by
+// cuda::all_reduce inside the compiled program.  ref_prog is the unsharded MLP (the oracle);
+// every rank builds the same seeded full weights and keeps its slice.
+inline test_case tp_int4_mlp(std::size_t rank, std::size_t world, std::size_t m, std::size_t hidden, std::size_t ffn,
+                             std::size_t g, unsigned seed)
+{
+    using migraphx::make_op;
+    test_case t;
+    std::mt19937 gen(seed);
+    const auto up_w = rand_ints<uint8_t>(gen, ffn * hidden / 2, 0, 255);    // [ffn, hidden / 2]
+    const auto dn_w = rand_ints<uint8_t>(gen, hidden * ffn / 2, 0, 255);    // [hidden, ffn / 2]
+    auto to_half    = [](const std::vector<float>& v) { return std::vector<migraphx::half>(v.begin(), v.end()); };
+    const auto up_s = to_half(rand_uniform(gen, ffn * (hidden / g), 0.6f / (4.6f * std::sqrt(float(hidden))),
+                                           1.4f / (4.6f * std::sqrt(float(hidden)))));
+    const auto dn_s = to_half(rand_uniform(gen, hidden * (ffn / g), 0.6f / (4.6f * std::sqrt(float(ffn))),
+                                           1.4f / (4.6f * std::sqrt(float(ffn)))));
+    auto linear = [&](migraphx::module* mm, instruction_ref a, const std::vector<uint8_t>& w,
+                      const std::vector<migraphx::half>& sc, std::size_t n, std::size_t k) {
+        auto bp     = mm->add_literal(migraphx::literal{shape{shape::uint8_type, {n, k / 2}}, w});
+        auto scales = mm->add_literal(migraphx::literal{shape{shape::half_type, {n, k / g}}, sc});
+        auto u      = mm->add_instruction(make_op("unsqueeze", {{"axes", {2}}}), scales);
+        auto mb     = mm->add_instruction(make_op("multibroadcast", {{"out_lens", {n, k / g, g}}}), u);
+        auto se     = mm->add_instruction(make_op("reshape", {{"dims", {n, k}}}), mb);
+        auto z8     = mm->add_literal(migraphx::literal{shape{shape::uint8_type}, std::vector<uint8_t>{8}});
+        auto dq     = mm->add_instruction(make_op("dequantizelinear"), mm->add_instruction(make_op("unpack_int4"), bp),
+                                      se, mbcast(mm, z8, {n, k}));
+        return mm->add_instruction(make_op("dot"), a,
+                                   mm->add_instruction(make_op("transpose", {{"permutation", {1, 0}}}), dq));
+    };
+    const shape xs{shape::half_type, {m, hidden}};
+    {
+        // the unsharded MLP
+        auto* mm = t.ref_prog.get_main_module();
+        auto x   = mm->add_parameter("x", xs);
+        auto h   = linear(mm, x, up_w, up_s, ffn, hidden);
+        mm->add_return({linear(mm, h, dn_w, dn_s, hidden, ffn)});
+    }
+    {
+        const std::size_t fr = ffn / world; // this rank's columns of the hidden layer
+        std::vector<uint8_t> uw(up_w.begin() + rank * fr * hidden / 2, up_w.begin() + (rank + 1) * fr * hidden / 2);
+        std::vector<migraphx::half> us(up_s.begin() + rank * fr * (hidden / g), up_s.begin() + (rank + 1) * fr * (hidden / g));
+        std::vector<uint8_t> dw(hidden * fr / 2);
+        std::vector<migraphx::half> ds(hidden * (fr / g));
+        for(std::size_t r = 0; r < hidden; ++r)
+        {
+            std::copy_n(dn_w.begin() + r * ffn / 2 + rank * fr / 2, fr / 2, dw.begin() + r * fr / 2);
+            std::copy_n(dn_s.begin() + r * (ffn / g) + rank * (fr / g), fr / g, ds.begin() + r * (fr / g));
+        }
+        auto* mm = t.prog.get_main_module();
+        auto x   = mm->add_parameter("x", xs);
+        auto h   = linear(mm, x, uw, us, fr, hidden);
+        auto y   = linear(mm, h, dw, ds, hidden, fr);
+        mm->add_return({mm->add_instruction(make_op("cuda::all_reduce"), y)});
+    }
+    auto xv = rand_normal(gen, m * hidden, 1.0f);
+    std::vector<migraphx::half> xh(xv.begin(), xv.end());
+    migraphx::argument xa{xs};
+    std::memcpy(xa.data(), xh.data(), xh.size() * sizeof(migraphx::half));
+    t.params["x"]     = xa;
+    t.ref_params["x"] = xa;
+    t.sampled         = true;
+    t.sample_rows.resize(m);
+    std::iota(t.sample_rows.begin(), t.sample_rows.end(), std::size_t{0});
+    t.rtol = 2e-2;
+    t.atol = 1e-2;
+    return t;
+}
+
 // seeded token ids in [0, vocab)
 inline migraphx::argument bert_ids(const bert_config& c, unsigned seed)
 {

@@ -68,3 +68,39 @@ def test_tensor_parallel_int4_mlp(cuda_device):
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world))
+
+
+def test_all_reduce_inside_a_compiled_program(cuda_device, tmp_path):
+    """One process per GPU, each compiling ITS shard of a tensor-parallel int4 MLP - column-split up
+    projection, row-split down projection, cuda::all_reduce as the last instruction - through
+    make_target("cuda") -> program::compile -> program::eval; every rank's result against the
+    unsharded MLP on MIGraphX's ref target (cuda_target_check run tp_int4_mlp)."""
+    import json
+    import subprocess
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "amdmigraphx_b200", "bin", "cuda_target_check")
+    world = 2
+    idfile = str(tmp_path / "nccl_id")
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, MGX_TP_RANK=str(rank), MGX_TP_WORLD=str(world), MGX_TP_ID_FILE=idfile,
+                   MIGRAPHX_CUDA_DEVICE=str(rank), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([exe, "run", "tp_int4_mlp"], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, err = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append((p.returncode, out, err))
+    for rc, out, err in outs:
+        lines = [l for l in out.splitlines() if l.startswith("{")]
+        assert lines, out + err[-2000:]
+        res = json.loads(lines[-1])
+        assert res.get("pass"), res
