@@ -101,28 +101,6 @@ struct op_sync_stream
     }
 };
 
-// First and last instruction of the part of a program that a CUDA graph can stand in for (see
-// insert_graph_ops).  graph_begin sees every parameter buffer; graph_end passes its input through.
-struct op_graph_begin
-{
-    std::string name() const { return "cuda::graph_begin"; }
-    shape compute_shape(const std::vector<shape>&) const { return {}; }
-    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
-};
-
-struct op_graph_end
-{
-    std::string name() const { return "cuda::graph_end"; }
-    shape compute_shape(const std::vector<shape>& inputs) const;
-    argument compute(context& ctx, const shape& out, const std::vector<argument>& args) const;
-    std::vector<std::size_t> output_alias(const std::vector<shape>& args) const
-    {
-        if(args.empty())
-            return {};
-        return {0};
-    }
-};
-
 // Evaluates its submodule (see insert_graph_ops): instruction by instruction at first, as one
 // recorded CUDA graph afterwards.  Inputs: the submodule's parameters in the order of `params`.
 // Result: the tuple of the submodule's results.

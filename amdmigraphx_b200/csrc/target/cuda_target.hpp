@@ -58,7 +58,7 @@ struct context_state
     // a buffer is reused once the caller has dropped the argument that referred to it
     std::vector<std::pair<std::size_t, std::shared_ptr<void>>> host_pool;
     bool ready = false;
-    // CUDA-graph replay of the instruction stream (cuda::graph_begin / cuda::graph_end)
+    // CUDA-graph replay of the instruction stream (cuda::graph_run)
     enum class graph_mode
     {
         off,       // not used for this program
@@ -68,7 +68,6 @@ struct context_state
     };
     graph_mode gmode        = graph_mode::off;
     int warm_evals          = 0;
-    bool replaying          = false; // (kept false: replayed submodules are not evaluated at all)
     std::vector<argument> graph_results; // what the recorded submodule returned
     cudaGraph_t graph       = nullptr;
     cudaGraphExec_t gexec   = nullptr;
@@ -96,9 +95,6 @@ struct MGX_CUDA_EXPORT context
     argument get_preallocation(const std::string& id) const;
     // true while a captured graph stands in for the instruction stream: operators that would
     // launch work return their output buffer instead
-    bool replaying() const { return state->replaying; }
-    void graph_begin(const std::vector<const void*>& params);
-    void graph_end();
     void enable_graph();
     // runs body() - the evaluation of a submodule - or, once it has been recorded for these
     // parameter buffers, launches the recorded graph instead and returns the recorded results

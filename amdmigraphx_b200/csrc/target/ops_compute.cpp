@@ -99,8 +99,6 @@ argument op_quantizelinear::compute(context& ctx, const shape&, const std::vecto
 {
     const auto& xs  = args[0].get_shape();
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto m    = as_matrix(xs, "quantizelinear input");
     const auto mo   = as_matrix(out.get_shape(), "quantizelinear output");
     int64_t ss[2] = {0, 0}, zs[2] = {0, 0};
@@ -126,8 +124,6 @@ argument op_dequantizelinear::compute(context& ctx, const shape&, const std::vec
 {
     const auto& xs  = args[0].get_shape();
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto m    = as_matrix(xs, "dequantizelinear input");
     const auto mo   = as_matrix(out.get_shape(), "dequantizelinear output");
     int64_t ss[2] = {0, 0}, zs[2] = {0, 0};
@@ -150,8 +146,6 @@ shape op_unpack_int4::compute_shape(const std::vector<shape>& inputs) const
 }
 argument op_unpack_int4::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args[1];
     const auto m = as_matrix(args[0].get_shape(), "unpack_int4 input");
     check_mgx(mgx_cuda_unpack_int4(args[0].data(), args[1].data(),
                                    mgx_type(args[0].get_shape().type()), m.rows, m.cols, ctx.stream()),
@@ -166,8 +160,6 @@ shape op_pack_int4::compute_shape(const std::vector<shape>& inputs) const
 }
 argument op_pack_int4::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args[1];
     const auto m = as_matrix(args[1].get_shape(), "pack_int4 output");
     check_mgx(mgx_cuda_pack_int4(args[0].data(), args[1].data(), mgx_type(args[0].get_shape().type()),
                                  m.rows, m.cols, ctx.stream()),
@@ -210,8 +202,6 @@ shape op_qgemm::compute_shape(const std::vector<shape>& inputs) const
 
 argument op_qgemm::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args.back(); // the output buffer (the un-quantised one of a pair)
     std::size_t i          = 2;
     const argument* scale  = scale_mode != MGX_SCALE_NONE ? &args[i++] : nullptr;
     const argument* bias   = has_bias ? &args[i++] : nullptr;
@@ -331,8 +321,6 @@ shape op_w4a16::compute_shape(const std::vector<shape>& inputs) const
 
 argument op_w4a16::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args.back();
     std::size_t i          = 3;
     const argument* zp     = has_zp ? &args[i++] : nullptr;
     const argument* wspace = has_workspace ? &args[i++] : nullptr;
@@ -408,8 +396,6 @@ shape op_pointwise::compute_shape(const std::vector<shape>& inputs) const
 argument op_pointwise::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& os = out.get_shape();
     mgx_pw_desc d{};
     // more dimensions than the kernel indexes: fold the leading ones when every operand is packed
@@ -488,8 +474,6 @@ shape op_reduce::compute_shape(const std::vector<shape>& inputs) const
 argument op_reduce::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& xs     = args[0].get_shape();
     const int64_t rows = static_cast<int64_t>(out.get_shape().elements());
     const int64_t cols = static_cast<int64_t>(xs.elements()) / rows;
@@ -516,8 +500,6 @@ shape op_layernorm::compute_shape(const std::vector<shape>& inputs) const
 
 argument op_layernorm::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args.back();
     std::size_t i         = 1;
     const argument* gamma = has_gamma ? &args[i++] : nullptr;
     const argument* beta  = has_beta ? &args[i++] : nullptr;
@@ -571,8 +553,6 @@ shape op_attention::compute_shape(const std::vector<shape>& inputs) const
 
 argument op_attention::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args.back();
     std::size_t i        = 3;
     const argument* qbuf = q_type != 0 ? &args[i++] : nullptr;
     const argument* obuf = write_o ? &args[i++] : nullptr;
@@ -627,8 +607,6 @@ shape op_concat_past_present::compute_shape(const std::vector<shape>& inputs) co
 
 argument op_concat_past_present::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args[2];
     const auto& pr = args[0].get_shape();
     const auto& pa = args[2].get_shape();
     const auto es  = static_cast<int64_t>(pr.type_size());
@@ -659,8 +637,6 @@ shape op_gqa_rotary_embedding::compute_shape(const std::vector<shape>& inputs) c
 argument op_gqa_rotary_embedding::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& x = args[0].get_shape();
     const auto& c = args[2].get_shape();
     check_mgx(mgx_cuda_gqa_rotary_embedding(
@@ -694,8 +670,6 @@ shape op_rotary_embedding::compute_shape(const std::vector<shape>& inputs) const
 argument op_rotary_embedding::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& x = args[0].get_shape();
     const int64_t strides[3] = {static_cast<int64_t>(x.strides()[0]), static_cast<int64_t>(x.strides()[1]),
                                 static_cast<int64_t>(x.strides()[2])};
@@ -730,8 +704,6 @@ shape op_gqa_decode_attention::compute_shape(const std::vector<shape>& inputs) c
 argument op_gqa_decode_attention::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& q = args[0].get_shape();
     const auto& k = args[1].get_shape();
     mgx_gqa_decode_desc d{};
@@ -762,8 +734,6 @@ shape op_softmax::compute_shape(const std::vector<shape>& inputs) const
 argument op_softmax::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& xs     = args[0].get_shape();
     const int64_t cols = static_cast<int64_t>(xs.lens().back());
     const int64_t rows = static_cast<int64_t>(xs.elements()) / cols;
@@ -788,8 +758,6 @@ shape op_gather::compute_shape(const std::vector<shape>& inputs) const
 argument op_gather::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& ds = args[0].get_shape();
     int64_t outer = 1, inner = static_cast<int64_t>(ds.type_size());
     for(int64_t i = 0; i < axis; ++i)
@@ -830,8 +798,6 @@ shape op_concat::compute_shape(const std::vector<shape>& inputs) const
 argument op_concat::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& os = out.get_shape();
     int64_t outer = 1, inner = static_cast<int64_t>(os.type_size());
     for(int64_t i = 0; i < axis; ++i)
@@ -865,8 +831,6 @@ shape op_pad_rows::compute_shape(const std::vector<shape>& inputs) const
 argument op_pad_rows::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
     const auto& out = args.back();
-    if(ctx.replaying())
-        return out;
     const auto& xs      = args[0].get_shape();
     const auto& os      = out.get_shape();
     const int64_t es    = static_cast<int64_t>(xs.type_size());

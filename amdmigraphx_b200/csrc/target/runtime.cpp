@@ -221,59 +221,6 @@ void context::enable_graph()
         state->gmode = context_state::graph_mode::warm;
 }
 
-void context::graph_begin(const std::vector<const void*>& params)
-{
-    using mode = context_state::graph_mode;
-    auto& st   = *state;
-    if(st.gmode == mode::off)
-        return;
-    if(st.gmode == mode::ready)
-    {
-        if(params == st.graph_params)
-        {
-            check_cuda(cudaGraphLaunch(st.gexec, stream()), "cudaGraphLaunch");
-            st.replaying = true;
-            return;
-        }
-        // other buffers: run instruction by instruction and capture again
-        (void)cudaGraphExecDestroy(st.gexec);
-        (void)cudaGraphDestroy(st.graph);
-        st.gexec      = nullptr;
-        st.graph      = nullptr;
-        st.gmode      = mode::warm;
-        st.warm_evals = 1;
-        return;
-    }
-    // the first two evals run eagerly: one-time set-up (kernel attributes, entry point
-    // look-ups) must not happen inside a capture
-    if(st.gmode == mode::warm and ++st.warm_evals > 2)
-    {
-        check_cuda(cudaStreamBeginCapture(stream(), cudaStreamCaptureModeThreadLocal),
-                   "cudaStreamBeginCapture");
-        st.graph_params = params;
-        st.gmode        = mode::capturing;
-    }
-}
-
-void context::graph_end()
-{
-    using mode = context_state::graph_mode;
-    auto& st   = *state;
-    if(st.replaying)
-    {
-        st.replaying = false;
-        return;
-    }
-    if(st.gmode != mode::capturing)
-        return;
-    // nothing of this eval has run yet: the captured work is launched as the new graph
-    st.gmode = mode::off; // whatever fails below, no second attempt
-    check_cuda(cudaStreamEndCapture(stream(), &st.graph), "cudaStreamEndCapture");
-    check_cuda(cudaGraphInstantiate(&st.gexec, st.graph, 0), "cudaGraphInstantiate");
-    check_cuda(cudaGraphLaunch(st.gexec, stream()), "cudaGraphLaunch");
-    st.gmode = mode::ready;
-}
-
 std::vector<argument> context::run_graph(const std::vector<const void*>& params,
                                          const std::function<std::vector<argument>()>& body)
 {
@@ -353,30 +300,6 @@ argument op_graph_run::compute(context& ctx,
         return run(mod, pm);
     });
     return argument{results};
-}
-
-argument op_graph_begin::compute(context& ctx, const shape&, const std::vector<argument>& args) const
-{
-    std::vector<const void*> params;
-    params.reserve(args.size());
-    for(const auto& a : args)
-        params.push_back(a.empty() ? nullptr : a.data());
-    ctx.graph_begin(params);
-    return {};
-}
-
-shape op_graph_end::compute_shape(const std::vector<shape>& inputs) const
-{
-    if(inputs.empty())
-        return {};
-    return inputs.front();
-}
-argument op_graph_end::compute(context& ctx, const shape&, const std::vector<argument>& args) const
-{
-    ctx.graph_end();
-    if(args.empty())
-        return {};
-    return args.front();
 }
 
 // ------------------------------------------------------------------ memory operators
@@ -464,8 +387,6 @@ shape op_copy::compute_shape(const std::vector<shape>& inputs) const
 }
 argument op_copy::compute(context& ctx, const shape&, const std::vector<argument>& args) const
 {
-    if(ctx.replaying())
-        return args[1];
     const auto bytes = args[0].get_shape().bytes();
     if(bytes > 0)
         check_cuda(cudaMemcpyAsync(args[1].data(), args[0].data(), bytes, cudaMemcpyDeviceToDevice,
@@ -526,8 +447,6 @@ MIGRAPHX_REGISTER_OP(op_copy_from)
 MIGRAPHX_REGISTER_OP(op_copy)
 MIGRAPHX_REGISTER_OP(op_sync_stream)
 MIGRAPHX_REGISTER_OP(op_graph_run)
-MIGRAPHX_REGISTER_OP(op_graph_begin)
-MIGRAPHX_REGISTER_OP(op_graph_end)
 MIGRAPHX_REGISTER_OP(op_set_stream)
 MIGRAPHX_REGISTER_OP(op_record_event)
 MIGRAPHX_REGISTER_OP(op_wait_event)
