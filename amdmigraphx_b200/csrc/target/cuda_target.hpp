@@ -185,9 +185,8 @@ struct fuse_cuda_pointwise
 // third records it with stream capture, and from then on an eval() is one cudaGraphLaunch - the
 // submodule's instructions (hundreds of literals, views and launches) are not visited at all -
 // as long as the caller passes the same parameter buffers (src/program.cpp:472-565 is the loop
-// this short-cuts).  With offload_copy the bracket lies between the last host-to-device and
-// the first device-to-host copy (the copies' device buffers are arena addresses, which never
-// change).  Not applied with several streams or collectives; MIGRAPHX_CUDA_GRAPH=0 turns it off.
+// this short-cuts).  With offload_copy the host-to-device and device-to-host copies stay in the
+// main module around the call (their device buffers are arena addresses, which never change).  Not applied with several streams or collectives; MIGRAPHX_CUDA_GRAPH=0 turns it off.
 struct insert_graph_ops
 {
     context* ctx      = nullptr;

@@ -2474,7 +2474,7 @@ void insert_graph_ops::apply(module_pass_manager& mpm) const
            n == "cuda::wait_event" or not ins->module_inputs().empty())
             return;
         if(n == "cuda::copy_to" and seen_launch)
-            return; // a host-to-device copy after the first launch: no single bracket
+            return; // a host-to-device copy after the first launch: the launches are not one contiguous run
         if(n == "cuda::copy_from" or n == "cuda::sync_stream")
             seen_copy_from = true;
         if(launches(n))

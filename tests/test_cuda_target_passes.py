@@ -185,7 +185,7 @@ def test_transposed_batched_left_operand_is_packed_first():
     assert copy[0].split(" = ")[0] in gemm
 
 
-def test_offload_copy_program_is_graph_bracketed():
+def test_offload_copy_program_keeps_host_copies_around_the_graph_run():
     out = _passes("int8_gelu", "offload")
     main, sub = out.split('module: "main:graph"')
     order = [n for l in main.splitlines() for n in ("cuda::copy_to", "cuda::graph_run", "cuda::copy_from")
