@@ -49,15 +49,37 @@ struct ln_params
     int rms; // RMS normalisation: no mean, squares and their mean in fp32 (see mgx_layernorm_desc::flags)
 };
 
-// T: float or __half.  NV: 16-byte vectors per lane (a lane owns vectors lane, lane + 32, ...).
-template <class T, int NV>
+// T: float or __half.  NV: 16-byte vectors per thread.  WPR: warps per row - 1 (a warp per row, a
+// thread owns vectors lane, lane + 32, ...) or 8 (a block per row: few, long rows, e.g. the single
+// token of a decode step, where one warp per row would leave a 4096-element row to 32 threads).
+template <class T, int NV, int WPR>
 __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
 {
-    constexpr int VE = 16 / sizeof(T); // elements per vector
-    const int lane   = threadIdx.x & 31;
-    const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr int VE  = 16 / sizeof(T); // elements per vector
+    constexpr int TPR = 32 * WPR;       // threads per row
+    __shared__ float red[2][8];
+    const int lane    = WPR == 1 ? (threadIdx.x & 31) : threadIdx.x;
+    const int64_t row = WPR == 1 ? static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5)
+                                 : static_cast<int64_t>(blockIdx.x);
     if(row >= p.rows)
-        return;
+        return; // (a whole block when WPR > 1: nobody is left waiting at a barrier)
+    // sum over the row's threads
+    auto row_sum = [&](float v, int slot) {
+#pragma unroll
+        for(int o = 16; o > 0; o >>= 1)
+            v += __shfl_xor_sync(0xffffffffu, v, o);
+        if constexpr(WPR > 1)
+        {
+            if((threadIdx.x & 31) == 0)
+                red[slot][threadIdx.x >> 5] = v;
+            __syncthreads();
+            v = 0.0f;
+#pragma unroll
+            for(int w = 0; w < WPR; ++w)
+                v += red[slot][w];
+        }
+        return v;
+    };
     const int nvec = p.cols / VE; // vectors in a row
     const T* xr    = static_cast<const T*>(p.x) + row * p.ldx;
     float v[NV][VE];
@@ -65,7 +87,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
 #pragma unroll
     for(int i = 0; i < NV; ++i)
     {
-        const int vi = lane + 32 * i;
+        const int vi = lane + TPR * i;
         if(vi < nvec)
         {
             const uint4 w = *reinterpret_cast<const uint4*>(xr + vi * VE);
@@ -96,9 +118,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
                 v[i][j] = 0.0f;
         }
     }
-#pragma unroll
-    for(int o = 16; o > 0; o >>= 1)
-        sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    sum = row_sum(sum, 0);
     const float mean = ln_round<T>(sum * p.inv_n);
     float sq = 0.0f;
     if(p.rms)
@@ -107,7 +127,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
         // converted to float, squared and averaged in fp32; only the mean is stored in T again
 #pragma unroll
         for(int i = 0; i < NV; ++i)
-            if(lane + 32 * i < nvec)
+            if(lane + TPR * i < nvec)
             {
 #pragma unroll
                 for(int j = 0; j < VE; ++j)
@@ -119,7 +139,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
 #pragma unroll
         for(int i = 0; i < NV; ++i)
         {
-            if(lane + 32 * i < nvec)
+            if(lane + TPR * i < nvec)
             {
 #pragma unroll
                 for(int j = 0; j < VE; ++j)
@@ -130,9 +150,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
             }
         }
     }
-#pragma unroll
-    for(int o = 16; o > 0; o >>= 1)
-        sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    sq = row_sum(sq, 1);
     const float var = ln_round<T>(sq * p.inv_n);
     const float ve  = ln_round<T>(var + p.eps);
     // rsqrt as the reference computes it: 1 / sqrt(x), both correctly rounded in fp32
@@ -143,7 +161,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const ln_params p)
 #pragma unroll
     for(int i = 0; i < NV; ++i)
     {
-        const int vi = lane + 32 * i;
+        const int vi = lane + TPR * i;
         if(vi >= nvec)
             continue;
         float gv[VE], bv[VE];
@@ -252,24 +270,43 @@ static int launch_layernorm(const ln_params& p, cudaStream_t stream)
 {
     constexpr int VE = 16 / sizeof(T);
     const int nvec   = p.cols / VE;
-    const int nv     = (nvec + 31) / 32;
-    const int warps  = 8;
+    // few rows: a block per row (each thread at most 8 vectors); otherwise a warp per row, for rows of up
+    // to 16 vectors per lane
+    const bool block_per_row = p.rows < 2 * device_sm_count() or nvec > 32 * 16;
+    if(block_per_row)
+    {
+        const int nv = (nvec + 255) / 256;
+        const dim3 grid(static_cast<unsigned>(p.rows));
+        if(nv <= 1)
+            layernorm_kernel<T, 1, 8><<<grid, 256, 0, stream>>>(p);
+        else if(nv <= 2)
+            layernorm_kernel<T, 2, 8><<<grid, 256, 0, stream>>>(p);
+        else if(nv <= 4)
+            layernorm_kernel<T, 4, 8><<<grid, 256, 0, stream>>>(p);
+        else if(nv <= 8)
+            layernorm_kernel<T, 8, 8><<<grid, 256, 0, stream>>>(p);
+        else
+            return MGX_E_UNSUPPORTED;
+        return static_cast<int>(cudaGetLastError());
+    }
+    const int nv    = (nvec + 31) / 32;
+    const int warps = 8;
     const dim3 grid(static_cast<unsigned>((p.rows + warps - 1) / warps));
     const dim3 block(32 * warps);
     if(nv <= 1)
-        layernorm_kernel<T, 1><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 1, 1><<<grid, block, 0, stream>>>(p);
     else if(nv <= 2)
-        layernorm_kernel<T, 2><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 2, 1><<<grid, block, 0, stream>>>(p);
     else if(nv <= 3)
-        layernorm_kernel<T, 3><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 3, 1><<<grid, block, 0, stream>>>(p);
     else if(nv <= 4)
-        layernorm_kernel<T, 4><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 4, 1><<<grid, block, 0, stream>>>(p);
     else if(nv <= 6)
-        layernorm_kernel<T, 6><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 6, 1><<<grid, block, 0, stream>>>(p);
     else if(nv <= 8)
-        layernorm_kernel<T, 8><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 8, 1><<<grid, block, 0, stream>>>(p);
     else if(nv <= 16)
-        layernorm_kernel<T, 16><<<grid, block, 0, stream>>>(p);
+        layernorm_kernel<T, 16, 1><<<grid, block, 0, stream>>>(p);
     else
         return MGX_E_UNSUPPORTED;
     return static_cast<int>(cudaGetLastError());
@@ -279,10 +316,11 @@ static int launch_layernorm(const ln_params& p, cudaStream_t stream)
 
 extern "C" int mgx_cuda_layernorm_supported(int type, int64_t cols)
 {
+    // (a block per row: 256 threads x 8 vectors)
     if(type == MGX_F16)
-        return cols > 0 and cols % 8 == 0 and cols <= 8 * 32 * 16;
+        return cols > 0 and cols % 8 == 0 and cols <= 8 * 256 * 8;
     if(type == MGX_F32)
-        return cols > 0 and cols % 4 == 0 and cols <= 4 * 32 * 16;
+        return cols > 0 and cols % 4 == 0 and cols <= 4 * 256 * 8;
     return 0;
 }
 

@@ -50,7 +50,7 @@ bool launching(const std::string& n)
                                   "cuda::reduce",         "cuda::softmax",          "cuda::gather", "cuda::concat",
                                   "cuda::pad_rows",       "cuda::layernorm",        "cuda::attention",
                                   "cuda::concat_past_present", "cuda::gqa_rotary_embedding",
-                                  "cuda::gqa_decode_attention"};
+                                  "cuda::gqa_decode_attention", "cuda::rotary_embedding"};
     for(auto* s : names)
         if(n == s)
             return true;

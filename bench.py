@@ -790,6 +790,16 @@ def run_case(a):
                           "tops": r.quant_ops / (dms / a.iters * 1e-3) / 1e12, "ops": r.op_counts(),
                           "device_status": capi.device_status()}))
         return 0
+    if a.case == "llama_layer":
+        # a config-4 decoder layer at a decode step through the plug-in: --m batch entries, 2048 cached positions
+        r = LlamaLayerRunner(batch=a.m, hidden=4096, heads=32, kv_heads=32, head=128, ffn=11008, cache=2048)
+        for _ in range(a.case_warmup):
+            Runner.eval_many([r], 1)
+        dms, wms = Runner.eval_many([r], a.iters)
+        print(json.dumps({"case": a.case, "batch": a.m, "launches_per_eval": r.launches,
+                          "device_us_per_eval": dms / a.iters * 1e3, "host_us_per_eval": wms / a.iters * 1e3,
+                          "ops": r.op_counts(), "device_status": capi.device_status()}))
+        return 0
     if a.case in ("qgemm_i8", "qgemm_fp8"):
         A = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev)
         B = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev)
@@ -868,7 +878,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true")
     ap.add_argument("--case", default=None, choices=["qgemm_i8", "qgemm_fp8", "quantize", "w4a16", "encoder", "attention", "layernorm",
-                                                        "gqa_decode"],
+                                                        "gqa_decode", "llama_layer"],
                     help="run one kernel by itself (for profiler captures) instead of the benchmark")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)

@@ -171,7 +171,8 @@ MGX_API int mgx_cuda_softmax(const void* x, int type, int64_t ldx, void* y, int6
  * src/onnx/parse_layernorm.cpp:100-140 (reduce_mean, sub, mul, reduce_mean, add, rsqrt, mul, mul,
  * add) and keeps those operators' roundings: with MGX_F16 every intermediate is truncated to half
  * like migraphx::half arithmetic.  Types: MGX_F32 | MGX_F16; cols a multiple of 4 (fp32) / 8
- * (fp16) and at most 2048 / 4096 (mgx_cuda_layernorm_supported); 16-byte aligned rows. */
+ * (fp16) and at most 8192 / 16384 (mgx_cuda_layernorm_supported); 16-byte aligned rows.  A warp per row,
+ * or a block per row where there are few rows or long ones. */
 typedef struct mgx_layernorm_desc
 {
     int64_t rows, cols;
