@@ -335,8 +335,8 @@ __device__ __forceinline__ void truncate4_to_half_precision(float (&v)[4])
 // there is none), bi4 is -0.0 without a bias (x + -0.0 == x for every x), an optional
 // quantizelinear output is int8 with 4-byte aligned rows.  Same arithmetic as epi_store_chunk.
 // MODE 1: residual / quantizelinear / D chosen by the launch's parameters; 2: D only;
-// 3: residual, D and quantizelinear; 4: quantizelinear only (the combinations of an encoder
-// layer's four GEMMs get branch-free loops of their own).
+// 3: residual, D and quantizelinear; 4: quantizelinear only; 8: residual and D (the combinations
+// of an encoder layer's four GEMMs get branch-free loops of their own); 7: the table look-up.
 template <bool IS_INT, class OutT, int ACT, int MODE>
 __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t col, float4 sc4, float4 bi4)
 {
@@ -351,10 +351,10 @@ __device__ __forceinline__ void epi_store_chunk_fast(const epi_ctx& e, int64_t c
     uint8_t* qdst = static_cast<uint8_t*>(p.Dq) + e.batch_off_q + (e.row0 + rsub) * p.ldq + col + pc * 4;
     const int64_t dstep = 8 * p.ldd, qstep = 8 * p.ldq;
     // 5 = 2 and 6 = 4 with accumulators below 2^24 (and the mantissa-cut quantizelinear input)
-    const bool has_res = MODE == 1 ? p.residual != nullptr : MODE == 3;
+    const bool has_res = MODE == 1 ? p.residual != nullptr : (MODE == 3 or MODE == 8);
     const bool has_q   = MODE == 1 ? p.Dq != nullptr : (MODE == 3 or MODE == 4 or MODE == 6 or MODE == 7);
     const bool wr      = MODE == 1 ? p.write_d != 0 : (MODE != 4 and MODE != 6 and MODE != 7);
-    const bool acc24   = MODE >= 5 ? true : p.acc24 != 0;
+    const bool acc24   = (MODE == 5 or MODE == 6) ? true : p.acc24 != 0;
     const bool q_mask  = MODE == 6 ? true : (has_q and p.q_mask != 0);
     // saturation before rounding: bounds are integers, so round-to-nearest stays inside
     const float q_lo = -128.0f - p.q_zp, q_hi = 127.0f - p.q_zp;
@@ -789,6 +789,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
     case 4: MGX_EPI_MODE(ACT, 4); break;     \
     case 5: MGX_EPI_MODE(ACT, 5); break;     \
     case 6: MGX_EPI_MODE(ACT, 6); break;     \
+    case 8: MGX_EPI_MODE(ACT, 8); break;     \
     default: MGX_EPI_MODE(ACT, 1); break;    \
     }
         const bool m_res = p.residual != nullptr, m_q = p.Dq != nullptr, m_wr = p.write_d != 0;
@@ -796,6 +797,7 @@ __global__ void __launch_bounds__(NTHREADS, 1)
         const int mode   = p.fast == 0 ? 0
                            : (not m_res and not m_q and m_wr) ? (m_24 ? 5 : 2)
                            : (m_res and m_q and m_wr)         ? 3
+                           : (m_res and not m_q and m_wr)     ? 8
                            : (not m_res and m_q and not m_wr) ? ((m_24 and p.q_mask != 0) ? 6 : 4)
                                                               : 1;
         if(std::is_same<OutT, __half>::value and p.lut != nullptr and p.fast != 0 and not m_res and m_q and not m_wr)

@@ -333,7 +333,8 @@ def test_int8_half_math_epilogue_matches_half_operator_chain(cuda_device, M, N, 
         assert not diff.any()
 
 
-@pytest.mark.parametrize("M,N,K,act", [(256, 320, 256, "gelu_erf"), (128, 64, 768, "relu"), (384, 3072, 768, "gelu_erf")])
+@pytest.mark.parametrize("M,N,K,act", [(256, 320, 256, "gelu_erf"), (128, 64, 768, "relu"), (384, 3072, 768, "gelu_erf"),
+                                         (128, 128, 2048, "gelu_erf")])
 def test_int8_lut_epilogue_is_the_half_operator_chain(cuda_device, M, N, K, act):
     """fp16 model whose linear feeds only the next quantizelinear: activation + quantizelinear of the
     half the chain holds after the bias is one look-up in a 65536-entry table (MGX_QOUT_LUT).  With a
