@@ -194,9 +194,11 @@ class EncoderGemms(object):
                 (t, h, f, "f16", None)]
 
     def _gemm(self, xq, lin, out, residual=None, q_out=None, q_scale=None, write_d=True):
+        # half_math: the program is an fp16 model (the convert to half follows dequantizelinear
+        # directly), so the lowering asks for every epilogue operator's half rounding
         capi.qgemm(xq, lin.w, b_layout=capi.B_NK, scale=lin.scale, scale_mode=capi.SCALE_PER_COL,
                    bias=lin.bias, act=lin.act, residual=residual, out=out, q_out=q_out,
-                   q_scale=q_scale, write_d=write_d)
+                   q_scale=q_scale, write_d=write_d, half_math=True)
 
     def step(self):
         h = self.hidden

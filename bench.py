@@ -267,9 +267,10 @@ def _sample_rows(m, n, seed):
     return np.sort(np.concatenate(([0, m - 1], rng.choice(np.arange(1, m - 1), size=n - 2, replace=False))))
 
 
-def check_qgemm(dev, m, n, k, kind, out, act, rows=64, seed=0):
+def check_qgemm(dev, m, n, k, kind, out, act, rows=64, seed=0, half_math=False):
     """One launch of the shape against the CPU oracle on a seeded sample of rows (all columns).
-    kind: "i8" | "fp8"; out: "f32" | "f16".  Returns None when it agrees, else a description."""
+    kind: "i8" | "fp8"; out: "f32" | "f16"; half_math: the fp16 model's epilogue (every operator
+    rounded to half).  Returns None when it agrees, else a description."""
     import numpy as np
     import torch
     from amdmigraphx_b200 import capi
@@ -287,13 +288,16 @@ def check_qgemm(dev, m, n, k, kind, out, act, rows=64, seed=0):
         scale = np.full(1, 3e-2, dtype=np.float32)
     d = capi.qgemm(ta, tb, b_layout=capi.B_NK, scale=torch.from_numpy(scale).to(dev),
                    scale_mode=capi.SCALE_PER_TENSOR if kind == "fp8" else capi.SCALE_PER_COL,
-                   bias=torch.from_numpy(bias).to(dev), act=act, out_dtype=odt)
+                   bias=torch.from_numpy(bias).to(dev), act=act, out_dtype=odt, half_math=half_math)
     torch.cuda.synchronize()
     pick = _sample_rows(m, rows, seed + 1)
     got = d[torch.from_numpy(pick).to(dev)].float().cpu().numpy()
     if kind == "i8":
         acc = O.quant_dot_int8(a[pick], b.T)
-        ref = O.qlinear_epilogue(acc, scale[None, :], bias, act, None, np.float16 if out == "f16" else np.float32)
+        if half_math:
+            ref = O.qlinear_epilogue_half_chain(acc, scale[None, :], bias.astype(np.float16), act)
+        else:
+            ref = O.qlinear_epilogue(acc, scale[None, :], bias, act, None, np.float16 if out == "f16" else np.float32)
         rtol, atol = (2e-2, 1e-2) if out == "f16" else (1e-5, 1e-5)
     else:
         acc = O.quant_dot_fp8(ta[torch.from_numpy(pick).to(dev)].view(torch.uint8).cpu().numpy(),
@@ -660,7 +664,7 @@ def run_own_arm(args):
     stream = torch.cuda.Stream()
     chains = [EncoderGemms(dev, tokens=batch * BERT["seq"], seed=s) for s in range(nsets)]
     for (m, n, k, out, act) in chains[0].distinct_shapes():
-        bad = check_qgemm(dev, m, n, k, "i8", out, act, rows=48, seed=n + k)
+        bad = check_qgemm(dev, m, n, k, "i8", out, act, rows=48, seed=n + k, half_math=out == "f16")
         if bad:
             failures.append(bad)
     with torch.cuda.stream(stream):
