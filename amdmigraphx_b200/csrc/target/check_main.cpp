@@ -143,6 +143,7 @@ std::map<std::string, std::function<test_case()>> cases()
     };
     big["c2_layer"]   = [] { return c2_encoder(1, 1); };
     big["c2_layers2"] = [] { return c2_encoder(1, 2); };
+    big["c2_full"]    = [] { return c2_encoder(1, 12); }; // the whole 12-layer program, one sequence
     std::map<std::string, std::function<test_case()>> small = {
         {"c1", [] { auto t = qdq_linear(256, 1024, 1024, shape::int8_type, "relu", true, 0); t.exact = true; return t; }},
         {"c1_small", [] { auto t = qdq_linear(64, 256, 96, shape::int8_type, "relu", true, 1); t.exact = true; return t; }},

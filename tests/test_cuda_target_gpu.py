@@ -68,6 +68,19 @@ def test_program_matches_ref_on_two_streams(cuda_device, case):
     assert res.get("pass"), res
 
 
+def test_whole_encoder_drift_against_ref_is_bounded(cuda_device):
+    # All 12 layers of config 2 on one sequence.  NOT a parity claim: two implementations of a deep
+    # int8 network that are not bit-identical drift apart - one flipped quantizelinear tie in layer 1
+    # perturbs every later quantiser (2 elements outside the tolerance after one layer, 725 after two,
+    # most of them after twelve).  What is bounded here is the size of the drift: its RMS stays below
+    # a tenth of the output's RMS (measured 0.065), i.e. at the level of the int8 quantisation noise
+    # itself, and nothing is non-finite.  Parity is claimed per layer and per linear.
+    res = _run("c2_full")
+    out = res["outputs"][0]
+    assert out["rms_err"] <= 0.1 * out["rms_ref"], res
+    assert out["max_abs"] < 2.0, res
+
+
 def test_encoder_layer_matches_ref_with_the_activation_table(cuda_device):
     # MIGRAPHX_CUDA_QGEMM_LUT=1: erf-GELU + quantizelinear of FFN1 as a table made with the
     # reference's half arithmetic
