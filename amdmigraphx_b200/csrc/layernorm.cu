@@ -270,9 +270,10 @@ static int launch_layernorm(const ln_params& p, cudaStream_t stream)
 {
     constexpr int VE = 16 / sizeof(T);
     const int nvec   = p.cols / VE;
-    // few rows: a block per row (each thread at most 8 vectors); otherwise a warp per row, for rows of up
-    // to 16 vectors per lane
-    const bool block_per_row = p.rows < 2 * device_sm_count() or nvec > 32 * 16;
+    // few rows: a block per row (each thread at most 8 vectors), so that a launch of a few hundred rows
+    // is spread over all SMs with one vector or two per thread; otherwise a warp per row, for rows of
+    // up to 16 vectors per lane
+    const bool block_per_row = p.rows <= 4 * device_sm_count() or nvec > 32 * 16;
     if(block_per_row)
     {
         const int nv = (nvec + 255) / 256;
