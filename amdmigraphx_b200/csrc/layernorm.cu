@@ -272,8 +272,9 @@ static int launch_layernorm(const ln_params& p, cudaStream_t stream)
     const int nvec   = p.cols / VE;
     // few rows: a block per row (each thread at most 8 vectors), so that a launch of a few hundred rows
     // is spread over all SMs with one vector or two per thread; otherwise a warp per row, for rows of
-    // up to 16 vectors per lane
-    const bool block_per_row = p.rows <= 4 * device_sm_count() or nvec > 32 * 16;
+    // up to 16 vectors per lane (measured on 768-wide fp16 rows inside the encoder program: the block form
+    // wins at 384 and 768 rows, the warp form at 3072)
+    const bool block_per_row = p.rows <= 8 * device_sm_count() or nvec > 32 * 16;
     if(block_per_row)
     {
         const int nv = (nvec + 255) / 256;
