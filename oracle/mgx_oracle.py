@@ -4,9 +4,12 @@ TEST INFRASTRUCTURE ONLY.  Nothing in the product imports this module: it is the
 checker used by tests/, by __graft_entry__.smoke() and by bench.py's cpu_baseline
 leg.  Every function restates one operator of the reference and cites the lines it
 follows (paths relative to the MIGraphX source tree).  The restatement is pinned
-against MIGraphX's own `ref` target built from the reference sources (oracle/_ref,
-see oracle/build_ref.py and tests/golden/make_golden.py) and against the golden
-vectors of the reference's test/ref/*.cpp files (tests/golden/reference_vectors.json).
+bit for bit against MIGraphX's own `ref` target built from the reference sources
+(oracle/_ref, see oracle/build_ref.py): live in tests/test_oracle_vs_ref_target.py and
+tests/test_oracle_chains_vs_ref_target.py, and through the committed fixtures
+tests/golden/ref_fixtures.npz (made by tests/golden/make_golden.py).  The reference's
+own golden tests (test/ref/*.cpp) run against that build in
+tests/test_reference_golden_tests.py.
 """
 import numpy as np
 
