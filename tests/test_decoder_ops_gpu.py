@@ -65,7 +65,7 @@ def test_gqa_rotary_embedding(cuda_device, batch, heads, kvh, seq, head, interle
 
 @pytest.mark.parametrize("batch,heads,kvh,head,cache", [(1, 32, 32, 128, 2048), (16, 8, 1, 128, 4096), (3, 8, 2, 64, 200),
                                                         (2, 4, 2, 128, 333), (2, 8, 1, 64, 1100), (5, 4, 4, 64, 65),
-                                                        (300, 2, 1, 64, 130)])
+                                                        (300, 2, 1, 64, 130), (2, 8, 2, 128, 300), (1, 64, 8, 128, 515)])
 def test_gqa_decode_attention_matches_chain(cuda_device, batch, heads, kvh, head, cache):
     import torch
     from amdmigraphx_b200 import capi
