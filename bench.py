@@ -795,8 +795,12 @@ def run_case(a):
                           "device_status": capi.device_status()}))
         return 0
     if a.case == "llama_layer":
-        # a config-4 decoder layer at a decode step through the plug-in: --m batch entries, 2048 cached positions
-        r = LlamaLayerRunner(batch=a.m, hidden=4096, heads=32, kv_heads=32, head=128, ffn=11008, cache=2048)
+        # a decoder layer at a decode step through the plug-in, --m batch entries: config 4 (2048 cached
+        # positions), or with --kv-heads 1 one tensor-parallel shard (of 8) of config 5 (4096 cached positions)
+        if a.kv_heads == 1:
+            r = LlamaLayerRunner(batch=a.m, hidden=8192, heads=8, kv_heads=1, head=128, ffn=3584, cache=4096)
+        else:
+            r = LlamaLayerRunner(batch=a.m, hidden=4096, heads=32, kv_heads=32, head=128, ffn=11008, cache=2048)
         for _ in range(a.case_warmup):
             Runner.eval_many([r], 1)
         dms, wms = Runner.eval_many([r], a.iters)
