@@ -383,6 +383,112 @@ static int launch_pointwise(const pw_args& a, cudaStream_t stream)
     return static_cast<int>(cudaGetLastError());
 }
 
+// ---- fixed-function forms of the two programs a decoder layer evaluates once per token -------
+// The register machine above costs several microseconds per launch whatever the size (program
+// decoding, a large instruction footprint); a residual add and the SwiGLU gate are evaluated here
+// with the same operations and the same roundings, 8 halves per thread.
+struct pw_f16_args
+{
+    const __half* in0;
+    const __half* in1;
+    __half* out;
+    int64_t stride0, stride1; // elements between rows of the two operands
+    uint32_t rows, row_vecs;  // 16-byte vectors per row
+    int op;                   // PW_FORM_BINARY: MGX_PW_ADD | MGX_PW_SUB | MGX_PW_MUL
+};
+enum { PW_FORM_BINARY, PW_FORM_SWIGLU };
+
+template <int FORM>
+__global__ void __launch_bounds__(256) pointwise_f16_kernel(const pw_f16_args a)
+{
+    const uint32_t nvec = a.rows * a.row_vecs;
+    for(uint32_t vec = blockIdx.x * 256u + threadIdx.x; vec < nvec; vec += gridDim.x * 256u)
+    {
+        const uint32_t row = vec / a.row_vecs, col = vec - row * a.row_vecs;
+        float x[8], y[8], r[8];
+        pw_load_vec<8>(a.in0, MGX_F16, row * a.stride0 + col * 8, 1, x);
+        pw_load_vec<8>(a.in1, MGX_F16, row * a.stride1 + col * 8, 1, y);
+        if constexpr(FORM == PW_FORM_BINARY)
+        {
+#pragma unroll
+            for(int v = 0; v < 8; ++v)
+                r[v] = a.op == MGX_PW_ADD ? __fadd_rn(x[v], y[v])
+                                          : (a.op == MGX_PW_SUB ? __fsub_rn(x[v], y[v]) : __fmul_rn(x[v], y[v]));
+        }
+        else
+        {
+            // sigmoid(x), x * sigmoid(x), (x * sigmoid(x)) * y: a half after every operator
+#pragma unroll
+            for(int v = 0; v < 8; ++v)
+            {
+                const float s = truncate_to_half_precision(__fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x[v]))));
+                const float t = truncate_to_half_precision(__fmul_rn(x[v], s));
+                r[v]          = __fmul_rn(t, y[v]);
+            }
+        }
+        pw_store_vec<8>(a.out, MGX_F16, static_cast<int64_t>(vec) * 8, r);
+    }
+}
+
+// true (and the launch done, its status in `status`) when the program is one of the fixed forms
+// over fp16 operands whose rows are contiguous and 16-byte aligned
+static bool launch_pointwise_f16_form(const pw_args& a, cudaStream_t stream, int& status)
+{
+    const mgx_pw_desc& d = a.d;
+    if(d.ninputs != 2 or d.ndim > 2 or a.total >= (int64_t{1} << 31))
+        return false;
+    const int last      = d.ndim - 1;
+    const int64_t inner = d.lens[last];
+    if(inner % 8 != 0 or reinterpret_cast<uintptr_t>(a.out) % 16 != 0)
+        return false;
+    for(int i = 0; i < 2; ++i)
+    {
+        if(d.in_type[i] != MGX_F16 or d.in_strides[i][last] != 1 or reinterpret_cast<uintptr_t>(a.in[i]) % 16 != 0)
+            return false;
+        if(d.ndim == 2 and (d.in_strides[i][0] % 8 != 0 or d.in_strides[i][0] < 0))
+            return false;
+    }
+    for(int n = 0; n < d.ninsns; ++n)
+        if(d.insn[n].type != MGX_F16)
+            return false;
+    auto reads = [&](int n, int p, int q) {
+        const auto& s = d.insn[n].src;
+        return (s[0] == p and s[1] == q) or (s[0] == q and s[1] == p);
+    };
+    int form = -1, first = 0; // first: the input that is x (the gate) of the SwiGLU form
+    if(d.ninsns == 1 and (d.insn[0].op == MGX_PW_ADD or d.insn[0].op == MGX_PW_MUL) and reads(0, 0, 1))
+        form = PW_FORM_BINARY;
+    else if(d.ninsns == 1 and d.insn[0].op == MGX_PW_SUB and d.insn[0].src[0] == 0 and d.insn[0].src[1] == 1)
+        form = PW_FORM_BINARY;
+    else if(d.ninsns == 3 and d.insn[0].op == MGX_PW_SIGMOID and d.insn[0].src[0] < 2 and
+            d.insn[1].op == MGX_PW_MUL and d.insn[2].op == MGX_PW_MUL)
+    {
+        first = d.insn[0].src[0];
+        if(reads(1, first, 2) and reads(2, 3, 1 - first))
+            form = PW_FORM_SWIGLU;
+    }
+    if(form < 0)
+        return false;
+    pw_f16_args f{};
+    f.in0      = static_cast<const __half*>(a.in[first]);
+    f.in1      = static_cast<const __half*>(a.in[1 - first]);
+    f.out      = static_cast<__half*>(a.out);
+    f.rows     = d.ndim == 2 ? static_cast<uint32_t>(d.lens[0]) : 1u;
+    f.row_vecs = static_cast<uint32_t>(inner / 8);
+    f.stride0  = d.ndim == 2 ? d.in_strides[first][0] : 0;
+    f.stride1  = d.ndim == 2 ? d.in_strides[1 - first][0] : 0;
+    f.op       = d.insn[0].op;
+    const int64_t blocks = ceil_div(a.total / 8, 256);
+    const int64_t cap    = static_cast<int64_t>(device_sm_count()) * 8;
+    const int grid       = static_cast<int>(blocks < cap ? blocks : cap);
+    if(form == PW_FORM_BINARY)
+        pointwise_f16_kernel<PW_FORM_BINARY><<<grid, 256, 0, stream>>>(f);
+    else
+        pointwise_f16_kernel<PW_FORM_SWIGLU><<<grid, 256, 0, stream>>>(f);
+    status = static_cast<int>(cudaGetLastError());
+    return true;
+}
+
 } // namespace mgx
 
 using namespace mgx;
@@ -476,6 +582,9 @@ extern "C" int mgx_cuda_pointwise(const mgx_pw_desc* d, const void* const* input
     // vectors never straddle a row: V divides the innermost length
     const int64_t inner = a.d.lens[a.d.ndim - 1];
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    int status          = MGX_OK;
+    if(launch_pointwise_f16_form(a, stream, status))
+        return status;
     if(inner % 8 == 0)
         return launch_pointwise<8>(a, stream);
     if(inner % 2 == 0)

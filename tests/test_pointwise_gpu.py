@@ -116,3 +116,41 @@ def test_pointwise_rejects_bad_programs(cuda_device):
     with pytest.raises(capi.MgxError) as e:
         capi.pointwise([x], [("add", capi.F32, (0, 3), 0.0)], (4, 4))  # operand 3 does not exist
     assert e.value.code == capi.E_INVALID_ARG
+
+
+@pytest.mark.parametrize("rows,cols,strided", [(1, 4096, False), (16, 11008, True), (3, 64, True), (5, 264, False)])
+def test_fixed_fp16_forms_match_the_register_machine(cuda_device, rows, cols, strided):
+    """A residual add / sub / mul and the SwiGLU gate take a fixed-function kernel when their fp16
+    operands have contiguous, 16-byte aligned rows.  The same programs behind a leading identity
+    (which changes no value) go through the register machine: the bits must agree, values in the
+    fp16 subnormal range and zeros included; add / sub / mul also against numpy."""
+    import torch
+    from amdmigraphx_b200 import capi
+    rng = np.random.default_rng(rows * 1000 + cols)
+    h = capi.F16
+    both = rng.normal(0, 2, size=(rows, 2 * cols)).astype(np.float16)
+    both[:, ::7] *= np.float16(1e-3)
+    both[0, :8] = [0.0, -0.0, 6e-8, -6e-8, 6.1e-5, -6.1e-5, 30000.0, -30000.0]
+    both[0, cols:cols + 8] = [1.0, 0.0, 3e-4, 1e-4, 1e-3, 6e-5, 2.0, 2.0]
+    if strided:  # two column slices of one packed buffer, like gate and up of a fused linear
+        packed = _t(both, cuda_device)
+        xt, yt = packed[:, :cols], packed[:, cols:]
+    else:
+        xt, yt = _t(both[:, :cols], cuda_device), _t(both[:, cols:], cuda_device)
+    x, y = both[:, :cols], both[:, cols:]
+    for op in ("add", "sub", "mul"):
+        fast = capi.pointwise([xt, yt], [(op, h, (0, 1), 0.0)], (rows, cols))
+        slow = capi.pointwise([xt, yt], [("identity", h, (0,), 0.0), (op, h, (2, 1), 0.0)], (rows, cols))
+        assert torch.equal(fast.view(torch.int16), slow.view(torch.int16)), op
+        ref = _numpy_program([x, y], [(op, h, (0, 1), 0.0)])
+        np.testing.assert_array_equal(fast.cpu().numpy().astype(np.float32), ref)
+    swiglu = [("sigmoid", h, (0,), 0.0), ("mul", h, (0, 2), 0.0), ("mul", h, (3, 1), 0.0)]
+    behind = [("identity", h, (0,), 0.0), ("sigmoid", h, (2,), 0.0), ("mul", h, (2, 3), 0.0), ("mul", h, (4, 1), 0.0)]
+    fast = capi.pointwise([xt, yt], swiglu, (rows, cols))
+    slow = capi.pointwise([xt, yt], behind, (rows, cols))
+    assert torch.equal(fast.view(torch.int16), slow.view(torch.int16))
+    # the gate as the second input
+    fast2 = capi.pointwise([yt, xt], [("sigmoid", h, (1,), 0.0), ("mul", h, (2, 1), 0.0), ("mul", h, (0, 3), 0.0)],
+                           (rows, cols))
+    assert torch.equal(fast2.view(torch.int16), slow.view(torch.int16))
+    assert capi.device_status() == 0
