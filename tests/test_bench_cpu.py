@@ -45,3 +45,22 @@ def test_product_arm_needs_a_gpu():
                        timeout=300, cwd=ROOT)
     assert r.returncode != 0 and r.stdout.strip() == ""
     assert "CUDA device" in r.stderr
+
+
+def test_reference_linear_timing_script_runs():
+    """oracle/time_ref_linears.py (the per-linear CPU baselines of the results table) prints one JSON
+    object per line; --quick takes the smallest shape of each kind."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "oracle", "time_ref_linears.py"), "--quick"],
+                         capture_output=True, text=True, timeout=300)
+    lines = [json.loads(ln) for ln in out.stdout.splitlines() if ln.strip()]
+    if "unavailable" in lines[0]:
+        assert out.returncode == 1
+        return
+    assert out.returncode == 0 and lines[0]["threads"] >= 1
+    assert lines[1]["op"].startswith("quant_dot") and lines[1]["seconds"] > 0
+    assert lines[2]["weight_bytes"] == 4096 * 2048 + 2 * 4096 * 32 and lines[2]["seconds"] > 0
