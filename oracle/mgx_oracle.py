@@ -9,7 +9,9 @@ bit for bit against MIGraphX's own `ref` target built from the reference sources
 tests/test_oracle_chains_vs_ref_target.py, and through the committed fixtures
 tests/golden/ref_fixtures.npz (made by tests/golden/make_golden.py).  The reference's
 own golden tests (test/ref/*.cpp) run against that build in
-tests/test_reference_golden_tests.py.
+tests/test_reference_golden_tests.py, and the known answers of its MatMulNBits tests
+(test/onnx/verify/matmulnbits_tests.cpp, extracted into tests/golden/matmulnbits_goldens.json)
+pin the int4 operators in tests/test_oracle_golden.py.
 """
 import numpy as np
 
